@@ -1,0 +1,304 @@
+/*
+ * slha_b200.h -- C ABI of libslha_b200.so, a B200 (sm_100a) implementation of
+ * the SLHA v2 KV-cache tile hot path: key -> 128-byte tile encode, eq. 2.3
+ * scoring over tiles without decompression, deterministic top-k, and the CCOS
+ * elastic tile pool kept resident in HBM.
+ *
+ * Part 1 re-declares, name for name and argument for argument, the C ABI the
+ * reference exports from its `slha-c` crate (slha-c/include/slha.h), so a
+ * program linked against `libslha` can be relinked against this library.
+ * Part 2 adds batched / device-resident entry points that the reference does
+ * not have; each says which reference function(s) it batches.
+ *
+ * All functions return one of the SLHA_* status codes unless stated otherwise
+ * and record a per-thread message retrievable with slha_last_error_message().
+ * Outputs are left untouched on failure.  There is no CPU fallback: without a
+ * CUDA device every compute entry point fails with SLHA_ERR_DEVICE.
+ */
+#ifndef SLHA_B200_H
+#define SLHA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ *
+ * Part 1: the reference ABI (slha-c/include/slha.h, ABI version 1)    *
+ * ------------------------------------------------------------------ */
+
+#define SLHA_ABI_VERSION 1u /* slha.h:11 */
+
+#define SLHA_D_C 128u /* latent dims per tile            slha.h:13-17 */
+#define SLHA_D_S 256u /* sign-LSH residual bits */
+#define SLHA_LATENT_BYTES 64u
+#define SLHA_RESIDUAL_WORDS 4u
+#define SLHA_N_GROUPS 8u
+
+/* status codes, slha.h:20-29 */
+#define SLHA_OK 0
+#define SLHA_ERR_NULL (-1)
+#define SLHA_ERR_PANIC (-2)
+#define SLHA_ERR_DIMENSION (-3)
+#define SLHA_ERR_CODEC (-4)
+#define SLHA_ERR_NONFINITE (-5)
+#define SLHA_ERR_INVALID_TILE (-6)
+#define SLHA_ERR_INVALID_HANDLE (-7)
+#define SLHA_ERR_IO (-8)
+#define SLHA_ERR_UTF8 (-9)
+/* additions of this library (not in the reference) */
+#define SLHA_ERR_DEVICE (-100)   /* no CUDA device / CUDA runtime error */
+#define SLHA_ERR_CAPACITY (-101) /* pool or scratch capacity exceeded */
+
+/* codec ids, slha.h:32-37 */
+#define SLHA_CODEC_INT4_SINGLE 0
+#define SLHA_CODEC_INT4_GROUPED 1
+#define SLHA_CODEC_NF4 2
+#define SLHA_CODEC_MIXED 3
+#define SLHA_CODEC_TQ3 4
+#define SLHA_CODEC_MIX3 5
+/* addition: MX INT4 with 32-dim groups on the unchanged tile layout (the
+ * same scale byte is written for both 16-dim halves, so every decoder of the
+ * reference layout reads it unmodified). */
+#define SLHA_B200_CODEC_INT4_GROUPED32 6
+
+/* tile flags, slha.h:40-46 */
+#define SLHA_FLAG_HOT 0u
+#define SLHA_FLAG_WARM (1u << 0)
+#define SLHA_FLAG_NF4 (1u << 1)
+#define SLHA_FLAG_MIXED (1u << 2)
+#define SLHA_FLAG_TQ3 (1u << 3)
+#define SLHA_FLAG_TQ3_NOCORR (1u << 4)
+#define SLHA_FLAG_MIX3 (1u << 5)
+
+#define SLHA_TILE_ALIGN 64u
+
+/* The 128-byte tile, slha.h:87-110.  Little-endian, no padding. */
+typedef struct
+#if defined(__GNUC__) || defined(__clang__)
+    __attribute__((aligned(SLHA_TILE_ALIGN)))
+#endif
+{
+    uint8_t latent_kv[SLHA_LATENT_BYTES];           /*   0 */
+    uint64_t residual_bitmap[SLHA_RESIDUAL_WORDS];  /*  64 */
+    float scale;                                    /*  96 */
+    float dynamic_lambda;                           /* 100 */
+    float residual_sigma;                           /* 104 */
+    uint32_t token_id;                              /* 108 */
+    uint32_t position;                              /* 112 */
+    uint16_t head_id;                               /* 116 */
+    uint16_t flags;                                 /* 118 */
+    uint8_t group_scales[SLHA_N_GROUPS];            /* 120 */
+} SciRustSlhaTile;
+
+typedef struct SlhaContext SlhaContext; /* slha.h:119 */
+typedef struct SlhaModel SlhaModel;     /* slha.h:120 */
+
+uint32_t slha_abi_version(void);           /* slha.h:123 */
+size_t slha_tile_size(void);               /* slha.h:124 */
+size_t slha_tile_align(void);              /* slha.h:125 */
+const char* slha_last_error_message(void); /* slha.h:133 */
+void slha_clear_error(void);               /* slha.h:134 */
+SlhaContext* slha_init(void);              /* slha.h:140 */
+int32_t slha_shutdown(SlhaContext* context); /* slha.h:147 */
+
+/* slha.h:153-158.  One tile, one prepared query, host pointers. */
+int32_t slha_process_tile(const SciRustSlhaTile* tile, const float* q_coarse,
+                          const uint64_t* q_sign, float* score_out);
+/* slha.h:167-173.  q (d floats) -> q_coarse (128 floats) + q_sign (4 words). */
+int32_t slha_prepare_query(const SlhaModel* model, const float* q, size_t d, float* q_coarse,
+                           uint64_t* q_sign);
+/* slha.h:182-188 */
+int32_t slha_score_tile(const SlhaModel* model, const SciRustSlhaTile* tile,
+                        const float* q_coarse, const uint64_t* q_sign, float* score_out);
+/* slha.h:197-204.  n_tiles <= 1<<20 (slha-c/src/lib.rs:208). */
+int32_t slha_score_tiles(const SlhaModel* model, const SciRustSlhaTile* tiles, size_t n_tiles,
+                         const float* q_coarse, const uint64_t* q_sign, float* scores_out);
+char* slha_audit(void);               /* slha.h:210 */
+void slha_free_string(char* string);  /* slha.h:213 */
+SlhaModel* slha_weights_load(const char* path); /* slha.h:219 */
+size_t slha_model_dim(const SlhaModel* model);  /* slha.h:225 */
+/* slha.h:233-240 */
+int32_t slha_encode_key(const SlhaModel* model, const float* key, size_t d, uint32_t position,
+                        int32_t codec, SciRustSlhaTile* out_tile);
+/* slha.h:248-253 */
+int32_t slha_decode_latent(const SlhaModel* model, const SciRustSlhaTile* tile, float* out,
+                           size_t d);
+/* slha.h:262-267 */
+int32_t slha_decode_key(const SlhaModel* model, const SciRustSlhaTile* tile, float* out, size_t d);
+int32_t slha_weights_release(SlhaModel* model); /* slha.h:272 */
+void slha_weights_free(SlhaModel* model);       /* slha.h:278 */
+
+/* ------------------------------------------------------------------ *
+ * Part 2: batched and device-resident entry points                    *
+ *                                                                      *
+ * Data pointers marked "host or device" are classified at run time;    *
+ * host buffers are staged through the library's stream.  Work is       *
+ * enqueued on the calling thread's stream (slha_b200_set_stream) and   *
+ * the call returns after that stream has been synchronised unless the  *
+ * documentation of the function says "asynchronous".                  *
+ * ------------------------------------------------------------------ */
+
+/* Number of CUDA devices visible; 0 when there is none. */
+int32_t slha_b200_device_count(void);
+/* Select the device used by the calling thread's subsequent calls. */
+int32_t slha_b200_set_device(int32_t device);
+/* Use `cuda_stream` (a cudaStream_t) for the calling thread's subsequent
+ * calls; NULL restores the library's own per-device stream. */
+int32_t slha_b200_set_stream(void* cuda_stream);
+/* Kernels launched by this library in this process so far. */
+uint64_t slha_b200_launch_count(void);
+/* Raw device memory for callers that have no CUDA runtime of their own. */
+int32_t slha_b200_malloc(size_t bytes, void** out);
+int32_t slha_b200_free(void* ptr);
+int32_t slha_b200_memcpy(void* dst, const void* src, size_t bytes); /* any direction, synchronous */
+int32_t slha_b200_synchronize(void);
+
+/*
+ * Build a model from an in-memory projection: the library-side equivalent of
+ * LearnedModel::try_from_projection_with (scirust/src/learned.rs:204-238),
+ * needed because slha_weights_load rejects d <= 128
+ * (scirust/src/weights.rs:195-199).  `projection` is 128 x d row-major.
+ * `scale` (128 floats, may be NULL = all ones) is the per-component whitening
+ * scale s_k of learned.rs:257-273.  `z` (256 x d_pad, may be NULL) overrides
+ * the sign-LSH matrix that is otherwise drawn from SplitMix64(seed) exactly as
+ * learned.rs:168-170 does.  Returns NULL on error.
+ */
+SlhaModel* slha_b200_model_create(const float* projection, size_t d, uint64_t seed, int32_t rht,
+                                  const float* scale, const float* z);
+
+#define SLHA_B200_F32 0
+#define SLHA_B200_BF16 1
+
+/*
+ * Encode n keys into n tiles: slha_encode_key (slha.h:233) over a batch.
+ * keys: n x d, float32 or bfloat16 (key_dtype), host or device.
+ * positions: n uint32 (host or device) or NULL for position_base + i.
+ * head_ids: n uint16 (host or device) or NULL for 0 (the reference always
+ * writes 0, learned.rs:404).  tiles_out: n tiles, host or device.
+ * Tile bytes equal those of the reference's scalar encoder bit for bit.
+ */
+int32_t slha_b200_encode_keys(const SlhaModel* model, const void* keys, int32_t key_dtype,
+                              size_t n, const uint32_t* positions, uint32_t position_base,
+                              const uint16_t* head_ids, int32_t codec, SciRustSlhaTile* tiles_out);
+
+/* slha_prepare_query (slha.h:167) over nq queries: q is nq x d float32,
+ * q_coarse_out nq x 128 floats, q_sign_out nq x 4 words; host or device. */
+int32_t slha_b200_prepare_queries(const SlhaModel* model, const float* q, size_t nq,
+                                  float* q_coarse_out, uint64_t* q_sign_out);
+
+/* slha_score_tiles (slha.h:197) for nq prepared queries over n tiles without
+ * the 1<<20 cap: scores_out[j*n + i] = compute_score(tile i, query j).
+ * All pointers host or device. */
+int32_t slha_b200_score_tiles(const SciRustSlhaTile* tiles, size_t n, const float* q_coarse,
+                              const uint64_t* q_sign, size_t nq, float* scores_out);
+
+/*
+ * A segment is a contiguous run of tiles scored by a contiguous group of
+ * queries (one KV head and its GQA query heads; one token shard).  The tiles
+ * of a segment are read once for the whole group.
+ */
+typedef struct {
+    uint64_t tile_begin;  /* index of the segment's first tile in `tiles` */
+    uint32_t n_tiles;     /* tiles in the segment */
+    uint32_t query_begin; /* first query row scored against it */
+    uint32_t n_queries;   /* queries in the group */
+    uint32_t index_base;  /* added to the in-segment tile index in the results */
+} SlhaB200Segment;
+
+/*
+ * Fused eq. 2.3 scoring + top-k.  For every query j of every segment, writes
+ * the k best (index, score) pairs of that segment to out_index[j*k ..] /
+ * out_score[j*k ..], ordered by score descending with ties resolved towards
+ * the lower index (the ordering convention of scirust/src/metrics.rs:186-192;
+ * the reference itself has no top-k step).  Rows with fewer than k tiles are
+ * padded with index 0xFFFFFFFF and score -inf; out_count[j] (may be NULL) is
+ * the number of valid entries.  tiles must be device memory; segments,
+ * queries and outputs are host or device.  Full score vectors are never
+ * written to memory.
+ */
+int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment* segments,
+                             size_t n_segments, const float* q_coarse, const uint64_t* q_sign,
+                             size_t n_queries, uint32_t k, uint32_t* out_index, float* out_score,
+                             uint32_t* out_count);
+
+/*
+ * Merge n_lists candidate lists per query (layout [list][query][k_in], as an
+ * all-gather of per-shard slha_b200_score_topk outputs produces) into the
+ * global top k_out per query with the same ordering rule.  Device pointers.
+ */
+int32_t slha_b200_topk_merge(const uint32_t* cand_index, const float* cand_score,
+                             uint32_t n_lists, uint32_t n_queries, uint32_t k_in, uint32_t k_out,
+                             uint32_t* out_index, float* out_score);
+
+/* -------- CCOS elastic tile pool (scirust/src/ccos.rs ElasticKvCache) -------- */
+
+typedef struct SlhaB200Pool SlhaB200Pool;
+
+#define SLHA_B200_STATE_HOT 0
+#define SLHA_B200_STATE_WARM 1
+#define SLHA_B200_STATE_COLD 2
+#define SLHA_B200_PAGE_LOWEST_IMPACT_FIRST 0 /* ccos.rs:47-56 PageOutPolicy */
+#define SLHA_B200_PAGE_OLDEST_FIRST 1
+#define SLHA_B200_EVICT_CAUSAL 0 /* ccos.rs:64-89 EvictionPolicy */
+#define SLHA_B200_EVICT_IMPORTANCE 1
+
+typedef struct {
+    uint64_t capacity_tiles; /* slots reserved in HBM (128 B tile + 13 B bookkeeping each) */
+    uint64_t budget_bytes;   /* logical byte budget of enforce_budget */
+    int32_t page_policy;
+    int32_t evict_policy;
+    uint32_t sink_window;    /* EvictionPolicy::Importance{sink_window}, ccos.rs:76-89 */
+    uint32_t recent_window;  /* addition: also pin the newest positions; 0 = reference behaviour */
+} SlhaB200PoolConfig;
+
+/* ElasticKvCache::new / with_budget / with_eviction, ccos.rs:132-214 */
+int32_t slha_b200_pool_create(const SlhaB200PoolConfig* config, SlhaB200Pool** out);
+int32_t slha_b200_pool_destroy(SlhaB200Pool* pool);
+/* ElasticKvCache::insert (ccos.rs:217-259) for n ready-made tiles, in order;
+ * slots_out (n uint32, host, may be NULL) receives the slot of each. */
+int32_t slha_b200_pool_insert_tiles(SlhaB200Pool* pool, const SciRustSlhaTile* tiles, size_t n,
+                                    uint32_t* slots_out);
+/* encode_with + insert without the tiles leaving HBM. */
+int32_t slha_b200_pool_append_keys(SlhaB200Pool* pool, const SlhaModel* model, const void* keys,
+                                   int32_t key_dtype, size_t n, const uint32_t* positions,
+                                   uint32_t position_base, const uint16_t* head_ids, int32_t codec,
+                                   uint32_t* slots_out);
+/* ElasticKvCache::score_all (ccos.rs:346-355): (slot, score) of every
+ * non-COLD slot in slot order for one query; n_out receives the count.
+ * slots_out / scores_out (host or device) must hold pool length entries. */
+int32_t slha_b200_pool_score_all(SlhaB200Pool* pool, const float* q_coarse, const uint64_t* q_sign,
+                                 uint32_t* slots_out, float* scores_out, uint64_t* n_out);
+/* score_all + top-k over the live slots for nq queries; indices are slots. */
+int32_t slha_b200_pool_score_topk(SlhaB200Pool* pool, const float* q_coarse,
+                                  const uint64_t* q_sign, size_t nq, uint32_t k,
+                                  uint32_t* out_slot, float* out_score, uint32_t* out_count);
+/* ElasticKvCache::observe_scores (ccos.rs:275-314) */
+int32_t slha_b200_pool_observe_scores(SlhaB200Pool* pool, const uint32_t* slots,
+                                      const float* scores, size_t n, float temperature);
+/* score_all followed by observe_scores, entirely on the device. */
+int32_t slha_b200_pool_observe_query(SlhaB200Pool* pool, const float* q_coarse,
+                                     const uint64_t* q_sign, float temperature);
+int32_t slha_b200_pool_page_out(SlhaB200Pool* pool, uint32_t slot);                      /* ccos.rs:365 */
+int32_t slha_b200_pool_drop_correction(SlhaB200Pool* pool, uint32_t slot, int32_t* dropped); /* ccos.rs:386 */
+int32_t slha_b200_pool_evict(SlhaB200Pool* pool, uint32_t slot, int32_t* evicted);        /* ccos.rs:404 */
+/* ElasticKvCache::enforce_budget (ccos.rs:555-614); within_budget gets its bool. */
+int32_t slha_b200_pool_enforce_budget(SlhaB200Pool* pool, int32_t* within_budget);
+int32_t slha_b200_pool_set_budget(SlhaB200Pool* pool, uint64_t budget_bytes);
+/* len, live_bytes (ccos.rs:484), counts (ccos.rs:510), nocorr_count,
+ * reclaimed_correction_bytes (ccos.rs:488-508) in one read-back:
+ * out[0..7] = len, live_bytes, hot, warm, cold, nocorr, reclaimed, free_len */
+int32_t slha_b200_pool_stats(SlhaB200Pool* pool, uint64_t out[8]);
+/* Copy-outs for parity checks: tile(), state(), importance(), seq of ccos.rs:357-363, :262 */
+int32_t slha_b200_pool_read(SlhaB200Pool* pool, uint64_t first, uint64_t n,
+                            SciRustSlhaTile* tiles_out, uint8_t* state_out,
+                            float* importance_out, uint64_t* seq_out);
+/* Device address of the pool's tile array (slot-indexed), for zero-copy scoring. */
+const SciRustSlhaTile* slha_b200_pool_tiles_device(SlhaB200Pool* pool);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLHA_B200_H */

@@ -1,0 +1,567 @@
+// Key -> tile encode, query preparation and tile decode for sm_100a.
+//
+// Restates LearnedModel::{latent, reconstruct, sign_bits, encode_with,
+// query_coarse} (scirust/src/learned.rs:247-408), the six quantisers
+// (scirust/src/attention/slha_v2/codec/*.rs) and the randomised Hadamard
+// transform (scirust/src/incoherence.rs:45-125).
+//
+// Bit-exactness contract: every decision the reference takes on a float
+// (round-half-away, `acc < 0.0`, `t - level > 0.0`, first-minimum NF4 search)
+// sits on a float32 sum that the reference accumulates strictly left to right
+// with a separate multiply and add.  This kernel keeps that order: each thread
+// owns whole output rows and walks the contraction index sequentially with
+// __fmul_rn / __fadd_rn (never contracted into FMA), divisions are __fdiv_rn and
+// square roots __fsqrt_rn.  Parallelism comes from rows x keys, not from
+// splitting a sum, so the tile bytes equal the scalar reference's bit for bit.
+#include "common.cuh"
+
+namespace slha {
+namespace {
+
+constexpr int ENC_THREADS = 256;
+
+struct EncodeArgs {
+    const void* keys;        // [n][d] f32 or bf16
+    int key_dtype;
+    uint64_t n;
+    uint32_t d, d_pad, log2_pad;
+    const float* p;          // [128][d]
+    const float* pt;         // [d][128]
+    const float* scale;      // [128]
+    const float* zt;         // [d_pad][256]
+    const float* diag;       // [d_pad] or null
+    float fwht_inv;          // 1/sqrt(d_pad), rounded as the reference rounds it
+    float lambda_c;          // sqrt(pi/512) in f32
+    const uint32_t* positions;
+    uint32_t position_base;
+    const uint16_t* heads;
+    int codec;
+    unsigned char* tiles;    // output tiles (encode)
+    const uint32_t* slots;   // optional scatter: tile i goes to tiles[slots[i]]
+    float* q_coarse;         // [n][128]  (query mode)
+    uint64_t* q_sign;        // [n][4]    (query mode)
+    int kb;                  // keys per CTA pass (power of two, <= 16)
+};
+
+__device__ __forceinline__ float rnd_half_away(float x) { return roundf(x); }
+__device__ __forceinline__ int sat_i32(float x) {
+    // Rust `x as i32`: NaN -> 0, saturating
+    if (x != x) return 0;
+    if (x >= 2147483648.0f) return 2147483647;
+    if (x <= -2147483648.0f) return (-2147483647 - 1);
+    return (int)x;
+}
+__device__ __forceinline__ int clampi(int v, int lo, int hi) { return min(max(v, lo), hi); }
+__device__ __forceinline__ uint32_t scale_byte(float step, float global) {
+    // `(step / global * 255.0).round().clamp(1.0, 255.0) as u8`  (int4.rs:48-49)
+    float r = rnd_half_away(__fmul_rn(__fdiv_rn(step, global), 255.0f));
+    if (r != r) return 0;
+    return (uint32_t)fminf(fmaxf(r, 1.0f), 255.0f);
+}
+__device__ __forceinline__ uint32_t int4_nibble(float v, float step) {
+    return (uint32_t)(clampi(sat_i32(rnd_half_away(__fdiv_rn(v, step))), -8, 7) + 8) & 15u;
+}
+__device__ __forceinline__ uint32_t nf4_nearest(float t) {
+    // nf4.rs:7-18: linear scan, first minimum wins
+    const float cb[16] = {-1.0f,   -0.7075f, -0.5421f, -0.4165f, -0.3108f, -0.2158f,
+                          -0.1272f, -0.0421f, 0.0421f,  0.1272f,  0.2158f,  0.3108f,
+                          0.4165f,  0.5421f,  0.7075f,  1.0f};
+    uint32_t best = 0;
+    float best_d = INFINITY;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float dd = fabsf(__fsub_rn(t, cb[i]));
+        if (dd < best_d) { best_d = dd; best = i; }
+    }
+    return best;
+}
+__device__ __forceinline__ float quad_max(float v) {  // max over the 4 lanes sharing lane>>2
+    v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, 2));
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    return v;
+}
+
+// Quantise one 128-float latent held as 4 consecutive dims per lane into the
+// 64 latent bytes + scale + 8 scale bytes of a tile in shared memory.
+// One warp per key.  `tile` points at 128 zeroed bytes.
+__device__ void quantize_warp(const float* h, int codec, unsigned char* tile, int lane) {
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = h[4 * lane + j];
+    uint32_t* tw = reinterpret_cast<uint32_t*>(tile);
+    const float amax4 = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    float global;
+    uint32_t gsb;  // this lane's scale byte
+    const bool headbody = codec == SLHA_CODEC_MIXED || codec == SLHA_CODEC_MIX3;
+    int unit;      // scale-byte index of this lane's dims
+    if (codec == SLHA_CODEC_INT4_SINGLE) {  // int4.rs:9-24
+        const float mx = warp_max(amax4);
+        global = mx > 0.0f ? __fdiv_rn(mx, 7.0f) : 1.0f;
+        gsb = 255;
+        unit = lane >> 2;
+    } else if (!headbody) {
+        // grouped codecs: step = absmax / {7, 1, 3.5}; int4.rs:34-63, nf4.rs:23-57, tq3.rs:10-49
+        float mx = quad_max(amax4);
+        if (codec == SLHA_B200_CODEC_INT4_GROUPED32) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 4));
+        const float div = codec == SLHA_CODEC_NF4 ? 1.0f : (codec == SLHA_CODEC_TQ3 ? 3.5f : 7.0f);
+        const float step = codec == SLHA_CODEC_NF4 ? mx : __fdiv_rn(mx, div);
+        const float g = warp_max(step);
+        global = g > 0.0f ? g : 1.0f;
+        gsb = scale_byte(step, global);
+        unit = lane >> 2;
+    } else {
+        // head (dims 0..7 = lanes 0,1) + 7 body groups of 16 dims starting at dim 8
+        // (mixed.rs:15-33, mix3.rs:13-31): body group of dim D is (D-8)/16, i.e.
+        // unit u >= 1 spans lanes 4u-2 .. 4u+1; lanes 30,31 hold the dropped tail.
+        const int d0 = 4 * lane;
+        unit = lane < 2 ? 0 : (d0 < 120 ? 1 + (d0 - 8) / 16 : 8);
+        const int first = lane < 2 ? 0 : (unit < 8 ? 4 * unit - 2 : lane);
+        const int span = lane < 2 ? 2 : (unit < 8 ? 4 : 1);
+        float mx = 0.0f;
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const float o = __shfl_sync(0xFFFFFFFFu, amax4, min(first + l, 31));
+            if (l < span) mx = fmaxf(mx, o);
+        }
+        const float step = lane < 2 ? __fdiv_rn(mx, 127.0f)
+                                    : __fdiv_rn(mx, codec == SLHA_CODEC_MIXED ? 7.0f : 3.5f);
+        const float g = warp_max(unit < 8 ? step : 0.0f);
+        global = g > 0.0f ? g : 1.0f;
+        gsb = unit < 8 ? scale_byte(step, global) : 0;
+    }
+    // publish scale bytes: the first lane of every unit writes its byte
+    if (codec == SLHA_CODEC_INT4_SINGLE) {
+        if (lane < 8) tile[120 + lane] = 255;
+    } else if (!headbody) {
+        if ((lane & 3) == 0) tile[120 + unit] = (unsigned char)gsb;
+    } else {
+        if (lane == 0 || (lane >= 2 && lane < 30 && ((lane - 2) & 3) == 0)) tile[120 + unit] = (unsigned char)gsb;
+    }
+    if (lane == 0) *reinterpret_cast<float*>(tile + 96) = global;
+    const float eff = __fmul_rn(global, __fdiv_rn((float)gsb, 255.0f));
+
+    if (codec == SLHA_CODEC_INT4_SINGLE || codec == SLHA_CODEC_INT4_GROUPED ||
+        codec == SLHA_B200_CODEC_INT4_GROUPED32 || codec == SLHA_CODEC_NF4) {
+        uint32_t nib[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (codec == SLHA_CODEC_INT4_SINGLE) {
+                nib[j] = int4_nibble(v[j], global);
+            } else if (codec == SLHA_CODEC_NF4) {
+                float tt = 0.0f;
+                if (eff > 0.0f) tt = fminf(fmaxf(__fdiv_rn(v[j], eff), -1.0f), 1.0f);
+                nib[j] = nf4_nearest(tt);
+            } else {
+                nib[j] = int4_nibble(v[j], eff);
+            }
+        }
+        reinterpret_cast<uint16_t*>(tile)[lane] =
+            (uint16_t)(nib[0] | (nib[1] << 4) | (nib[2] << 8) | (nib[3] << 12));
+    } else if (codec == SLHA_CODEC_TQ3) {
+        uint32_t codes = 0, corr = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float tt = __fdiv_rn(v[j], eff);
+            const int code = clampi(sat_i32(rnd_half_away(__fadd_rn(tt, 3.5f))), 0, 7);
+            codes |= (uint32_t)code << (3 * j);
+            if (__fsub_rn(tt, __fsub_rn((float)code, 3.5f)) > 0.0f) corr |= 1u << j;
+        }
+        const int bit = 12 * lane;  // 4 dims x 3 bits
+        atomicOr(&tw[bit >> 5], codes << (bit & 31));
+        if ((bit & 31) > 20) atomicOr(&tw[(bit >> 5) + 1], codes >> (32 - (bit & 31)));
+        atomicOr(&tw[12 + (lane >> 3)], corr << (4 * (lane & 7)));
+    } else {
+        // head+body
+        const int d0 = 4 * lane;
+        if (lane < 2) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int q = clampi(sat_i32(rnd_half_away(__fdiv_rn(v[j], eff))), -128, 127) + 128;
+                w |= (uint32_t)q << (8 * j);
+            }
+            tw[lane] = w;
+        } else if (d0 < 120) {
+            const int ld0 = d0 - 8;
+            if (codec == SLHA_CODEC_MIXED) {
+                uint32_t nibs = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) nibs |= int4_nibble(v[j], eff) << (4 * j);
+                reinterpret_cast<uint16_t*>(tile)[4 + (ld0 >> 2)] = (uint16_t)nibs;
+            } else {
+                uint32_t codes = 0, corr = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float tt = __fdiv_rn(v[j], eff);
+                    const int code = clampi(sat_i32(rnd_half_away(__fadd_rn(tt, 3.5f))), 0, 7);
+                    codes |= (uint32_t)code << (3 * j);
+                    if (__fsub_rn(tt, __fsub_rn((float)code, 3.5f)) > 0.0f) corr |= 1u << j;
+                }
+                const int bit = 64 + 3 * ld0;  // code plane starts at byte 8
+                atomicOr(&tw[bit >> 5], codes << (bit & 31));
+                if ((bit & 31) > 20) atomicOr(&tw[(bit >> 5) + 1], codes >> (32 - (bit & 31)));
+                const int cbit = 400 + ld0;    // correction plane starts at byte 50
+                atomicOr(&tw[cbit >> 5], corr << (cbit & 31));
+            }
+        }
+    }
+}
+
+template <bool QUERY>
+__global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int KB = a.kb;
+    const uint32_t d = a.d, dp = a.d_pad;
+    // shared: tiles [KB][128 B] | h [KB][128] | keyT [d][KB] | bufT [d_pad][KB]
+    // (keys and the sign-LSH input are stored transposed so that one thread
+    // reads the KB values of a contraction index with 16-byte loads)
+    unsigned char* tl = smem;
+    float* hs = reinterpret_cast<float*>(tl + (size_t)KB * TILE_BYTES);
+    float* keyT = hs + (size_t)KB * D_C;
+    float* buf = keyT + (((size_t)d * KB + 3) & ~size_t(3));
+
+    for (uint64_t base = (uint64_t)blockIdx.x * KB; base < a.n; base += (uint64_t)gridDim.x * KB) {
+        const int nk = (int)min((uint64_t)KB, a.n - base);
+        __syncthreads();
+        // ---- load keys (transposed: keyT[i][j]); absent keys are zero ------
+        for (uint32_t e = tid; e < d * (uint32_t)KB; e += ENC_THREADS) {
+            const int j = e / d;
+            const uint32_t i = e % d;
+            float x = 0.0f;
+            if (j < nk) {
+                const uint64_t o = (base + j) * d + i;
+                x = a.key_dtype == SLHA_B200_F32
+                        ? reinterpret_cast<const float*>(a.keys)[o]
+                        : __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(a.keys)[o] << 16);
+            }
+            keyT[(size_t)i * KB + j] = x;
+        }
+        for (int e = tid; e < KB * 32; e += ENC_THREADS) reinterpret_cast<uint32_t*>(tl)[e] = 0;
+        __syncthreads();
+
+        // ---- latent / q_coarse: row k = tid & 127, keys of half (tid >> 7) ---
+        {
+            const int k = tid & 127, half = tid >> 7;
+            const int per = max(KB / 2, 1);
+            const int j0 = (KB >= 2) ? half * per : 0;
+            if (KB >= 2 || half == 0) {
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+                for (uint32_t i = 0; i < d; ++i) {
+                    const float pv = a.pt[(size_t)i * D_C + k];
+                    const float* kr = keyT + (size_t)i * KB + j0;
+                    if (KB == 16) {
+                        const float4 k0 = reinterpret_cast<const float4*>(kr)[0];
+                        const float4 k1 = reinterpret_cast<const float4*>(kr)[1];
+                        acc[0] = __fadd_rn(acc[0], __fmul_rn(pv, k0.x));
+                        acc[1] = __fadd_rn(acc[1], __fmul_rn(pv, k0.y));
+                        acc[2] = __fadd_rn(acc[2], __fmul_rn(pv, k0.z));
+                        acc[3] = __fadd_rn(acc[3], __fmul_rn(pv, k0.w));
+                        acc[4] = __fadd_rn(acc[4], __fmul_rn(pv, k1.x));
+                        acc[5] = __fadd_rn(acc[5], __fmul_rn(pv, k1.y));
+                        acc[6] = __fadd_rn(acc[6], __fmul_rn(pv, k1.z));
+                        acc[7] = __fadd_rn(acc[7], __fmul_rn(pv, k1.w));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (j < per) acc[j] = __fadd_rn(acc[j], __fmul_rn(pv, kr[j]));
+                    }
+                }
+                const float sk = a.scale[k];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (j < per) {
+                        const float hv = QUERY ? __fmul_rn(acc[j], sk) : __fdiv_rn(acc[j], sk);
+                        hs[(size_t)(j0 + j) * D_C + k] = hv;
+                    }
+            }
+        }
+        __syncthreads();
+
+        if (QUERY) {
+            for (int e = tid; e < nk * D_C; e += ENC_THREADS)
+                a.q_coarse[(base + e / D_C) * D_C + (e % D_C)] = hs[e];
+            // sign-LSH input is the raw query
+            for (uint32_t e = tid; e < dp * (uint32_t)KB; e += ENC_THREADS)
+                buf[e] = (e / KB) < d ? keyT[e] : 0.0f;
+        } else {
+            // ---- quantise: one warp per key ---------------------------------
+            for (int j = warp; j < KB; j += ENC_THREADS / 32)
+                quantize_warp(hs + (size_t)j * D_C, a.codec, tl + (size_t)j * TILE_BYTES, lane);
+            // ---- residual e = key - sum_k (h_k*s_k) * P[k][:]  (k outer) ------
+            for (uint32_t e = tid; e < dp * (uint32_t)KB; e += ENC_THREADS) {
+                // thread owns column i of key j; consecutive threads -> consecutive i
+                const int j = e / dp;
+                const uint32_t i = e % dp;
+                float r = 0.0f;
+                if (i < d) {
+                    float acc = 0.0f;
+                    const float* hj = hs + (size_t)j * D_C;
+                    for (int k = 0; k < D_C; ++k) {
+                        const float w = __fmul_rn(hj[k], a.scale[k]);
+                        acc = __fadd_rn(acc, __fmul_rn(w, a.p[(size_t)k * d + i]));
+                    }
+                    r = __fsub_rn(keyT[(size_t)i * KB + j], acc);
+                }
+                buf[(size_t)i * KB + j] = r;
+            }
+        }
+        __syncthreads();
+
+        // ---- sigma_E (f32, sequential over i) and tile metadata ---------------
+        if (!QUERY && tid < nk) {
+            const int j = tid;
+            float ss = 0.0f;
+            for (uint32_t i = 0; i < d; ++i) {
+                const float x = buf[(size_t)i * KB + j];
+                ss = __fadd_rn(ss, __fmul_rn(x, x));
+            }
+            const float sigma = __fsqrt_rn(__fdiv_rn(ss, (float)d));
+            unsigned char* tile = tl + (size_t)j * TILE_BYTES;
+            const uint32_t pos = a.positions ? a.positions[base + j] : a.position_base + (uint32_t)(base + j);
+            *reinterpret_cast<float*>(tile + 100) = __fmul_rn(sigma, a.lambda_c);
+            *reinterpret_cast<float*>(tile + 104) = sigma;
+            *reinterpret_cast<uint32_t*>(tile + 108) = pos;
+            *reinterpret_cast<uint32_t*>(tile + 112) = pos;
+            const uint32_t head = a.heads ? a.heads[base + j] : 0u;
+            uint32_t cflag = 0;
+            if (a.codec == SLHA_CODEC_NF4) cflag = F_NF4;
+            else if (a.codec == SLHA_CODEC_MIXED) cflag = F_MIXED;
+            else if (a.codec == SLHA_CODEC_TQ3) cflag = F_TQ3;
+            else if (a.codec == SLHA_CODEC_MIX3) cflag = F_MIX3;
+            *reinterpret_cast<uint32_t*>(tile + 116) = head | (cflag << 16);
+        }
+        __syncthreads();
+
+        // ---- optional randomised Hadamard transform of buf ------------------
+        if (a.diag) {
+            for (uint32_t e = tid; e < dp * (uint32_t)KB; e += ENC_THREADS)
+                buf[e] = __fmul_rn(buf[e], a.diag[e / KB]);
+            __syncthreads();
+            for (uint32_t h = 1; h < dp; h <<= 1) {
+                for (uint32_t e = tid; e < (dp / 2) * (uint32_t)KB; e += ENC_THREADS) {
+                    const uint32_t j = e % KB, pr = e / KB;
+                    const uint32_t lo = ((pr / h) * 2 * h) + (pr % h);
+                    float* col = buf + j;
+                    const float x = col[(size_t)lo * KB], y = col[(size_t)(lo + h) * KB];
+                    col[(size_t)lo * KB] = __fadd_rn(x, y);
+                    col[(size_t)(lo + h) * KB] = __fsub_rn(x, y);
+                }
+                __syncthreads();
+            }
+            for (uint32_t e = tid; e < dp * (uint32_t)KB; e += ENC_THREADS)
+                buf[e] = __fmul_rn(buf[e], a.fwht_inv);
+            __syncthreads();
+        }
+
+        // ---- sign-LSH: thread s owns hyperplane s for all KB keys ------------
+        {
+            const int s = tid;  // ENC_THREADS == D_S
+            float acc[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+            for (uint32_t i = 0; i < dp; ++i) {
+                const float zv = a.zt[(size_t)i * D_S + s];
+                const float* br = buf + (size_t)i * KB;
+                if (KB == 16) {
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; ++j4) {
+                        const float4 b4 = reinterpret_cast<const float4*>(br)[j4];
+                        acc[4 * j4 + 0] = __fadd_rn(acc[4 * j4 + 0], __fmul_rn(zv, b4.x));
+                        acc[4 * j4 + 1] = __fadd_rn(acc[4 * j4 + 1], __fmul_rn(zv, b4.y));
+                        acc[4 * j4 + 2] = __fadd_rn(acc[4 * j4 + 2], __fmul_rn(zv, b4.z));
+                        acc[4 * j4 + 3] = __fadd_rn(acc[4 * j4 + 3], __fmul_rn(zv, b4.w));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (j < KB) acc[j] = __fadd_rn(acc[j], __fmul_rn(zv, br[j]));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (j < KB) {
+                    const unsigned b = __ballot_sync(0xFFFFFFFFu, acc[j] < 0.0f);
+                    if (lane == 0 && j < nk) {
+                        if (QUERY)
+                            reinterpret_cast<uint32_t*>(a.q_sign)[(base + j) * 8 + warp] = b;
+                        else
+                            reinterpret_cast<uint32_t*>(tl + (size_t)j * TILE_BYTES + 64)[warp] = b;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- write tiles: 8 x 16 B per tile ------------------------------------
+        if (!QUERY) {
+            for (int e = tid; e < nk * 8; e += ENC_THREADS) {
+                const int j = e >> 3, c = e & 7;
+                const uint64_t dst = a.slots ? a.slots[base + j] : base + j;
+                reinterpret_cast<uint4*>(a.tiles + dst * TILE_BYTES)[c] =
+                    reinterpret_cast<const uint4*>(tl + (size_t)j * TILE_BYTES)[c];
+            }
+        }
+    }
+}
+
+// reconstruct (learned.rs:276-286) from the dequantised latent of one tile, and
+// optionally the sign-sketch estimate of reconstruct_from_tile (learned.rs:290-322)
+__global__ void decode_kernel(const unsigned char* tile, const float* p, const float* scale,
+                              const float* z, uint32_t d, uint32_t d_pad, int with_residual,
+                              float* out) {
+    __shared__ float k[D_C];
+    __shared__ float sgn[D_S];
+    const uint32_t flags = *reinterpret_cast<const uint16_t*>(tile + 118);
+    const float sc = *reinterpret_cast<const float*>(tile + 96);
+    for (int dd = threadIdx.x; dd < D_C; dd += blockDim.x) {
+        // tile.rs:133-255
+        float v;
+        auto alt = [&](int g) { return __fdiv_rn(__fmul_rn(sc, (float)tile[120 + g]), 255.0f); };
+        auto grp = [&](int dim) { return __fmul_rn(sc, __fdiv_rn((float)tile[120 + dim / 16], 255.0f)); };
+        auto code3 = [&](int off, int end, int ld) {
+            const int bit = 3 * ld, byte = off + (bit >> 3), sh = bit & 7;
+            const uint32_t lo = tile[byte], hi = (byte + 1 < end) ? ((uint32_t)tile[byte + 1] << 8) : 0u;
+            return (int)(((lo | hi) >> sh) & 7u);
+        };
+        if (flags & F_MIXED) {
+            if (dd < 8) v = __fmul_rn((float)((int)tile[dd] - 128), alt(0));
+            else if (dd < 120) {
+                const int ld = dd - 8;
+                const uint32_t b = tile[8 + (ld >> 1)];
+                v = __fmul_rn((float)((int)((ld & 1) ? (b >> 4) : (b & 15)) - 8), alt(1 + ld / 16));
+            } else v = 0.0f;
+        } else if (flags & F_TQ3) {
+            float level = (float)code3(0, 48, dd) - 3.5f;
+            if (!(flags & F_NOCORR)) level += ((tile[48 + (dd >> 3)] >> (dd & 7)) & 1) ? 0.25f : -0.25f;
+            v = __fmul_rn(level, grp(dd));
+        } else if (flags & F_MIX3) {
+            if (dd < 8) v = __fmul_rn((float)((int)tile[dd] - 128), alt(0));
+            else if (dd >= 120) v = 0.0f;
+            else {
+                const int ld = dd - 8;
+                float level = (float)code3(8, 50, ld) - 3.5f;
+                if (!(flags & F_NOCORR)) level += ((tile[50 + (ld >> 3)] >> (ld & 7)) & 1) ? 0.25f : -0.25f;
+                v = __fmul_rn(level, alt(1 + ld / 16));
+            }
+        } else {
+            const uint32_t b = tile[dd >> 1];
+            const uint32_t nib = (dd & 1) ? (b >> 4) : (b & 15);
+            const float cb[16] = {-1.0f,   -0.7075f, -0.5421f, -0.4165f, -0.3108f, -0.2158f,
+                                  -0.1272f, -0.0421f, 0.0421f,  0.1272f,  0.2158f,  0.3108f,
+                                  0.4165f,  0.5421f,  0.7075f,  1.0f};
+            const float level = (flags & F_NF4) ? cb[nib] : (float)((int)nib - 8);
+            v = __fmul_rn(level, grp(dd));
+        }
+        k[dd] = v;
+    }
+    const float sigma = *reinterpret_cast<const float*>(tile + 104);
+    const float rs = __fdiv_rn(__fmul_rn(sigma, __fsqrt_rn(__fdiv_rn(3.14159265358979323846f, 2.0f))), (float)D_S);
+    for (int s = threadIdx.x; s < D_S; s += blockDim.x) {
+        const uint64_t w = reinterpret_cast<const uint64_t*>(tile + 64)[s >> 6];
+        sgn[s] = ((w >> (s & 63)) & 1ull) ? -1.0f : 1.0f;
+    }
+    __syncthreads();
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < d; i += gridDim.x * blockDim.x) {
+        float acc = 0.0f;
+        for (int kk = 0; kk < D_C; ++kk)
+            acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(k[kk], scale[kk]), p[(size_t)kk * d + i]));
+        if (with_residual)
+            for (int s = 0; s < D_S; ++s)
+                acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sgn[s], rs), z[(size_t)s * d_pad + i]));
+        out[i] = acc;
+    }
+}
+
+size_t encode_smem(uint32_t d, uint32_t dp, int kb) {
+    return ((((size_t)d * kb + 3) & ~size_t(3)) + (size_t)kb * D_C + (size_t)kb * dp) * 4 + (size_t)kb * TILE_BYTES;
+}
+
+Status fill_args(const Model* m, EncodeArgs& a, int* kb_out) {
+    a.d = (uint32_t)m->d;
+    a.d_pad = (uint32_t)m->d_pad;
+    a.p = m->d_p;
+    a.pt = m->d_pt;
+    a.scale = m->d_scale;
+    a.zt = m->d_zt;
+    a.diag = m->d_diag;
+    a.fwht_inv = 1.0f / sqrtf((float)m->d_pad);
+    a.lambda_c = sqrtf(3.14159265358979323846f / (2.0f * (float)D_S));
+    int kb = 16;
+    while (kb > 1 && encode_smem(a.d, a.d_pad, kb) > 200 * 1024) kb >>= 1;
+    if (encode_smem(a.d, a.d_pad, kb) > 200 * 1024)
+        return Status(SLHA_ERR_DIMENSION, "model dimension too large for the encode kernel");
+    *kb_out = kb;
+    a.kb = kb;
+    return Status();
+}
+
+template <bool QUERY>
+Status run_encode(Ctx* c, EncodeArgs& a) {
+    const size_t smem = encode_smem(a.d, a.d_pad, a.kb);
+    static thread_local bool configured = false;
+    if (!configured) {
+        SLHA_CUDA(cudaFuncSetAttribute(encode_kernel<QUERY>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured = true;
+    }
+    const uint64_t groups = (a.n + a.kb - 1) / a.kb;
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, 148ull * 8);
+    encode_kernel<QUERY><<<grid, ENC_THREADS, smem, c->stream>>>(a);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    return Status();
+}
+
+}  // namespace
+
+Status launch_encode(Ctx* c, const Model* m, const void* d_keys, int key_dtype, size_t n,
+                     const uint32_t* d_positions, uint32_t position_base, const uint16_t* d_heads,
+                     int codec, SciRustSlhaTile* d_tiles, const uint32_t* d_slots) {
+    if (n == 0) return Status();
+    EncodeArgs a{};
+    int kb;
+    SLHA_TRY(fill_args(m, a, &kb));
+    a.keys = d_keys;
+    a.key_dtype = key_dtype;
+    a.n = n;
+    a.positions = d_positions;
+    a.position_base = position_base;
+    a.heads = d_heads;
+    a.codec = codec;
+    a.tiles = reinterpret_cast<unsigned char*>(d_tiles);
+    a.slots = d_slots;
+    return run_encode<false>(c, a);
+}
+
+Status launch_prepare_queries(Ctx* c, const Model* m, const float* d_q, size_t nq,
+                              float* d_q_coarse, uint64_t* d_q_sign) {
+    if (nq == 0) return Status();
+    EncodeArgs a{};
+    int kb;
+    SLHA_TRY(fill_args(m, a, &kb));
+    a.keys = d_q;
+    a.key_dtype = SLHA_B200_F32;
+    a.n = nq;
+    a.q_coarse = d_q_coarse;
+    a.q_sign = d_q_sign;
+    return run_encode<true>(c, a);
+}
+
+Status launch_decode(Ctx* c, const Model* m, const SciRustSlhaTile* d_tile, float* d_out,
+                     bool with_residual) {
+    const uint32_t d = (uint32_t)m->d;
+    decode_kernel<<<(d + 127) / 128, 128, 0, c->stream>>>(
+        reinterpret_cast<const unsigned char*>(d_tile), m->d_p, m->d_scale, m->d_z, d,
+        (uint32_t)m->d_pad, with_residual && !m->rht, d_out);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    return Status();
+}
+
+}  // namespace slha

@@ -1,0 +1,538 @@
+// Device-resident CCOS elastic tile pool: the ElasticKvCache of
+// scirust/src/ccos.rs with its arena, per-slot state/seq/importance arrays,
+// LIFO free list and logical byte counter all kept in HBM.  Every transition
+// (insert, page_out, drop_correction, evict, enforce_budget, observe_scores)
+// runs as kernels; the host only reads back a 64-byte counter block.
+//
+// enforce_budget reproduces the reference's four ordered phases
+// (ccos.rs:555-614).  A phase sorts its candidates by the reference's key
+// (cub::DeviceRadixSort on a unique 64-bit key), prefix-sums the bytes each
+// candidate would free, and applies the operation to exactly the prefix the
+// reference's sequential loop would have reached.
+#include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_scan.cuh>
+
+#include "common.cuh"
+#include "pool.cuh"
+
+namespace slha {
+namespace {
+
+__device__ __forceinline__ uint32_t f32_total_key(float f) {
+    uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ uint32_t corr_bytes(uint32_t flags) {  // tile.rs:118-126
+    return (flags & F_TQ3) ? 16u : ((flags & F_MIX3) ? 14u : 0u);
+}
+__device__ __forceinline__ uint32_t live_bytes_of(uint8_t st, uint32_t flags) {  // ccos.rs:468-482
+    if (st == ST_COLD) return 0;
+    const uint32_t base = st == ST_HOT ? 128u : 96u;
+    return base - ((flags & F_NOCORR) ? corr_bytes(flags) : 0u);
+}
+__device__ __forceinline__ uint32_t tile_flags(const unsigned char* tiles, uint64_t slot) {
+    return *reinterpret_cast<const uint16_t*>(tiles + slot * TILE_BYTES + 118);
+}
+
+// ---- insert (ccos.rs:217-259) ------------------------------------------------
+// Tile j of the batch takes free_list[free_len-1-j] while the free list lasts
+// (LIFO pops), then fresh slots len, len+1, ...
+__global__ void insert_kernel(PoolDev p, const unsigned char* src, uint64_t n, uint64_t pops,
+                              uint64_t len0, uint64_t free0, uint64_t seq0, uint32_t* slots_out) {
+    const uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    uint32_t bytes = 0;
+    if (j < n) {
+        const uint32_t slot = j < pops ? p.free_list[free0 - 1 - j] : (uint32_t)(len0 + (j - pops));
+        uint32_t flags = 0;
+        if (src) flags = *reinterpret_cast<const uint16_t*>(src + j * TILE_BYTES + 118);
+        const uint8_t st = (flags & F_WARM) ? ST_WARM : ST_HOT;
+        p.state[slot] = st;
+        p.seq[slot] = seq0 + j;
+        p.importance[slot] = 0.0f;
+        slots_out[j] = slot;
+        bytes = live_bytes_of(st, flags);
+    }
+    for (int o = 16; o; o >>= 1) bytes += __shfl_xor_sync(0xFFFFFFFFu, bytes, o);
+    if ((threadIdx.x & 31) == 0 && bytes) atomicAdd((unsigned long long*)&p.cnt->live, (unsigned long long)bytes);
+    if (j == 0) {
+        p.cnt->free_len = free0 - pops;
+        p.cnt->len = len0 + (n - pops);
+        p.cnt->next_seq = seq0 + n;
+    }
+}
+__global__ void scatter_tiles_kernel(unsigned char* tiles, const unsigned char* src,
+                                     const uint32_t* slots, uint64_t n) {
+    const uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < n * 8) {
+        const uint64_t j = e >> 3, c = e & 7;
+        reinterpret_cast<uint4*>(tiles + (uint64_t)slots[j] * TILE_BYTES)[c] =
+            reinterpret_cast<const uint4*>(src + j * TILE_BYTES)[c];
+    }
+}
+
+// ---- single-slot transitions ---------------------------------------------------
+__device__ bool do_page_out(const PoolDev& p, uint32_t slot, int64_t* delta) {  // ccos.rs:365-380
+    if (p.state[slot] != ST_HOT) return false;
+    unsigned char* t = p.tiles + (uint64_t)slot * TILE_BYTES;
+    uint4 z = make_uint4(0, 0, 0, 0);
+    reinterpret_cast<uint4*>(t + 64)[0] = z;
+    reinterpret_cast<uint4*>(t + 64)[1] = z;
+    *reinterpret_cast<float*>(t + 100) = 0.0f;
+    *reinterpret_cast<uint16_t*>(t + 118) |= F_WARM;
+    p.state[slot] = ST_WARM;
+    *delta -= 32;
+    return true;
+}
+__device__ bool do_drop_correction(const PoolDev& p, uint32_t slot, int64_t* delta) {  // ccos.rs:386-397
+    unsigned char* t = p.tiles + (uint64_t)slot * TILE_BYTES;
+    const uint32_t flags = *reinterpret_cast<uint16_t*>(t + 118);
+    const uint32_t nb = corr_bytes(flags);
+    if (p.state[slot] == ST_COLD || nb == 0 || (flags & F_NOCORR)) return false;
+    for (uint32_t b = 64 - nb; b < 64; ++b) t[b] = 0;
+    *reinterpret_cast<uint16_t*>(t + 118) = (uint16_t)(flags | F_NOCORR);
+    *delta -= (int64_t)nb;
+    return true;
+}
+__global__ void single_op_kernel(PoolDev p, int op, uint32_t slot, int32_t* result) {
+    int64_t delta = 0;
+    bool done = false;
+    if (slot < p.cnt->len) {
+        if (op == 0) done = do_page_out(p, slot, &delta);
+        else if (op == 1) done = do_drop_correction(p, slot, &delta);
+        else if (p.state[slot] != ST_COLD) {  // evict, ccos.rs:404-438 (no event log)
+            delta = -(int64_t)live_bytes_of(p.state[slot], tile_flags(p.tiles, slot));
+            p.state[slot] = ST_COLD;
+            p.free_list[p.cnt->free_len++] = slot;
+            done = true;
+        }
+    }
+    p.cnt->live = (uint64_t)((int64_t)p.cnt->live + delta);
+    *result = done ? 1 : 0;
+}
+
+// ---- enforce_budget phases -------------------------------------------------------
+enum Phase { PH_CORR_HOT = 0, PH_PAGE = 1, PH_CORR_WARM = 2, PH_EVICT = 3, PH_EVICT_PINNED = 4 };
+constexpr uint64_t SENTINEL = ~0ull;
+
+// max live position (for the recent-window extension)
+__global__ void max_pos_kernel(PoolDev p) {
+    const uint64_t len = p.cnt->len;
+    uint32_t m = 0;
+    for (uint64_t s = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; s < len; s += (uint64_t)gridDim.x * blockDim.x)
+        if (p.state[s] != ST_COLD) m = max(m, *reinterpret_cast<const uint32_t*>(p.tiles + s * TILE_BYTES + 112));
+    for (int o = 16; o; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(&p.cnt->max_pos, m);
+}
+
+__device__ __forceinline__ bool is_pinned(const PoolDev& p, uint32_t pos, uint32_t max_pos) {
+    if (pos < p.sink_window) return true;  // ccos.rs:592-594
+    return p.recent_window && (max_pos - pos) < p.recent_window;
+}
+
+// candidate key + bytes freed, per slot, for one phase
+__global__ void phase_build_kernel(PoolDev p, int phase, uint64_t* keys, uint32_t* vals) {
+    const uint64_t len = p.cnt->len;
+    const bool over = p.cnt->live > p.cnt->budget;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        p.cnt->phase_deficit = over ? p.cnt->live - p.cnt->budget : 0;
+        p.cnt->phase_applied = 0;
+    }
+    const uint32_t max_pos = p.cnt->max_pos;
+    for (uint64_t s = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; s < len; s += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t key = SENTINEL;
+        if (over) {
+            const uint8_t st = p.state[s];
+            const unsigned char* t = p.tiles + s * TILE_BYTES;
+            const uint32_t flags = *reinterpret_cast<const uint16_t*>(t + 118);
+            bool cand = false;
+            if (phase == PH_CORR_HOT) cand = st == ST_HOT && corr_bytes(flags) && !(flags & F_NOCORR);
+            else if (phase == PH_PAGE) cand = st == ST_HOT;
+            else if (phase == PH_CORR_WARM) cand = st == ST_WARM && corr_bytes(flags) && !(flags & F_NOCORR);
+            else if (st != ST_COLD) {
+                const bool pin = p.evict_policy == SLHA_B200_EVICT_IMPORTANCE &&
+                                 is_pinned(p, *reinterpret_cast<const uint32_t*>(t + 112), max_pos);
+                cand = (phase == PH_EVICT_PINNED) == pin;
+            }
+            if (cand) {
+                const uint32_t seq32 = (uint32_t)p.seq[s];
+                if (phase <= PH_CORR_WARM) {
+                    // slots_in_paging_order, ccos.rs:526-539: stable sort of the
+                    // slot-ascending list by sigma (total order) or by seq
+                    key = p.page_policy == SLHA_B200_PAGE_LOWEST_IMPACT_FIRST
+                              ? ((uint64_t)f32_total_key(*reinterpret_cast<const float*>(t + 104)) << 32) | (uint32_t)s
+                              : (uint64_t)seq32;
+                } else {
+                    // ccos.rs:586-603: causal = by seq; importance = (importance, seq)
+                    key = p.evict_policy == SLHA_B200_EVICT_CAUSAL
+                              ? (uint64_t)seq32
+                              : ((uint64_t)f32_total_key(p.importance[s]) << 32) | seq32;
+                }
+            }
+        }
+        keys[s] = key;
+        vals[s] = (uint32_t)s;
+    }
+}
+
+__global__ void phase_weights_kernel(PoolDev p, int phase, const uint64_t* keys_sorted,
+                                     const uint32_t* slots_sorted, uint32_t* w) {
+    const uint64_t len = p.cnt->len;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint32_t bytes = 0;
+        if (keys_sorted[i] != SENTINEL) {
+            const uint32_t s = slots_sorted[i];
+            const uint32_t flags = tile_flags(p.tiles, s);
+            if (phase == PH_PAGE) bytes = 32;
+            else if (phase <= PH_CORR_WARM) bytes = corr_bytes(flags);
+            else bytes = live_bytes_of(p.state[s], flags);
+        }
+        w[i] = bytes;
+    }
+}
+
+// Apply the phase operation to the sorted prefix whose exclusive byte prefix is
+// below the deficit: exactly the items the reference's `for s in order { if
+// live <= budget {return}; op(s) }` loop reaches.
+__global__ void phase_apply_kernel(PoolDev p, int phase, const uint64_t* keys_sorted,
+                                   const uint32_t* slots_sorted, const uint32_t* w,
+                                   const uint64_t* excl) {
+    const uint64_t len = p.cnt->len;
+    const uint64_t deficit = p.cnt->phase_deficit;
+    const uint64_t free0 = p.cnt->free_len;
+    int64_t delta = 0;
+    uint32_t applied = 0;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += (uint64_t)gridDim.x * blockDim.x) {
+        if (keys_sorted[i] == SENTINEL || deficit == 0 || excl[i] >= deficit) continue;
+        const uint32_t s = slots_sorted[i];
+        if (phase == PH_PAGE) do_page_out(p, s, &delta);
+        else if (phase <= PH_CORR_WARM) do_drop_correction(p, s, &delta);
+        else {
+            delta -= (int64_t)w[i];
+            p.state[s] = ST_COLD;
+            p.free_list[free0 + i] = s;  // pushes happen in sorted order (applied items are a prefix)
+            ++applied;
+        }
+    }
+    for (int o = 16; o; o >>= 1) {
+        delta += __shfl_xor_sync(0xFFFFFFFFu, delta, o);
+        applied += __shfl_xor_sync(0xFFFFFFFFu, applied, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        if (delta) atomicAdd((unsigned long long*)&p.cnt->live_delta, (unsigned long long)delta);
+        if (applied) atomicAdd((unsigned long long*)&p.cnt->phase_applied, (unsigned long long)applied);
+    }
+}
+__global__ void phase_commit_kernel(PoolDev p) {
+    p.cnt->live = (uint64_t)((int64_t)p.cnt->live + (int64_t)p.cnt->live_delta);
+    p.cnt->live_delta = 0;
+    p.cnt->free_len += p.cnt->phase_applied;
+    p.cnt->phase_applied = 0;
+}
+
+// ---- observe_scores (ccos.rs:275-314) -----------------------------------------
+struct ObserveTmp {
+    uint32_t max_key;   // order-preserving key of the max live score
+    uint32_t bad;       // a live score is non-finite
+    uint32_t live;      // number of live entries
+    uint32_t pad;
+    float sum;
+};
+__global__ void observe_pass1(PoolDev p, const uint32_t* slots, const float* scores, uint64_t n, ObserveTmp* tmp) {
+    const uint64_t len = p.cnt->len;
+    uint32_t mk = 0, bad = 0, live = 0;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t s = slots ? slots[i] : (uint32_t)i;
+        if (s < len && p.state[s] != ST_COLD) {
+            const float v = scores[i];
+            ++live;
+            if (!isfinite(v)) bad = 1;
+            mk = max(mk, f32_total_key(v));
+        }
+    }
+    for (int o = 16; o; o >>= 1) {
+        mk = max(mk, __shfl_xor_sync(0xFFFFFFFFu, mk, o));
+        bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
+        live += __shfl_xor_sync(0xFFFFFFFFu, live, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicMax(&tmp->max_key, mk);
+        if (bad) atomicOr(&tmp->bad, 1u);
+        if (live) atomicAdd(&tmp->live, live);
+    }
+}
+__device__ __forceinline__ float key_to_f32(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+// per-CTA partial sums of exp((s-m)/T) in a fixed order (deterministic)
+__global__ void observe_pass2(PoolDev p, const uint32_t* slots, const float* scores, uint64_t n,
+                              float temperature, const ObserveTmp* tmp, float* partial) {
+    __shared__ float red[32];
+    const uint64_t len = p.cnt->len;
+    const float m = key_to_f32(tmp->max_key);
+    float acc = 0.0f;
+    if (!tmp->bad && tmp->live) {
+        const uint64_t per = (n + gridDim.x - 1) / gridDim.x;
+        const uint64_t lo = (uint64_t)blockIdx.x * per, hi = min(n, lo + per);
+        for (uint64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            const uint32_t s = slots ? slots[i] : (uint32_t)i;
+            if (s < len && p.state[s] != ST_COLD) acc += expf((scores[i] - m) / temperature);
+        }
+    }
+    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+        partial[blockIdx.x] = t;
+    }
+}
+__global__ void observe_pass3(PoolDev p, const uint32_t* slots, const float* scores, uint64_t n,
+                              float temperature, ObserveTmp* tmp, const float* partial, int n_partial) {
+    __shared__ float s_inv;
+    if (threadIdx.x == 0) {
+        float sum = 0.0f;
+        for (int i = 0; i < n_partial; ++i) sum += partial[i];
+        s_inv = (tmp->bad || !tmp->live || !isfinite(sum) || sum <= 0.0f) ? 0.0f : 1.0f / sum;
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    if (inv == 0.0f) return;
+    const uint64_t len = p.cnt->len;
+    const float m = key_to_f32(tmp->max_key);
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t s = slots ? slots[i] : (uint32_t)i;
+        if (s < len && p.state[s] != ST_COLD) atomicAdd(&p.importance[s], expf((scores[i] - m) / temperature) * inv);
+    }
+}
+
+// ---- stats / compaction ---------------------------------------------------------
+__global__ void stats_kernel(PoolDev p, unsigned long long* out) {
+    const uint64_t len = p.cnt->len;
+    unsigned long long h = 0, w = 0, c = 0, nc = 0, rec = 0;
+    for (uint64_t s = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; s < len; s += (uint64_t)gridDim.x * blockDim.x) {
+        const uint8_t st = p.state[s];
+        if (st == ST_HOT) ++h; else if (st == ST_WARM) ++w; else ++c;
+        const uint32_t flags = tile_flags(p.tiles, s);
+        if (st != ST_COLD && (flags & F_NOCORR)) { ++nc; rec += corr_bytes(flags); }
+    }
+    for (int o = 16; o; o >>= 1) {
+        h += __shfl_xor_sync(0xFFFFFFFFu, h, o); w += __shfl_xor_sync(0xFFFFFFFFu, w, o);
+        c += __shfl_xor_sync(0xFFFFFFFFu, c, o); nc += __shfl_xor_sync(0xFFFFFFFFu, nc, o);
+        rec += __shfl_xor_sync(0xFFFFFFFFu, rec, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd(&out[2], h); atomicAdd(&out[3], w); atomicAdd(&out[4], c);
+        atomicAdd(&out[5], nc); atomicAdd(&out[6], rec);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        out[0] = p.cnt->len; out[1] = p.cnt->live; out[7] = p.cnt->free_len;
+    }
+}
+// ordered compaction of the non-COLD (slot, score) pairs; one CTA
+__global__ void compact_live_kernel(PoolDev p, const float* scores, uint32_t* slots_out,
+                                    float* scores_out, unsigned long long* n_out) {
+    __shared__ uint32_t warp_tot[32];
+    __shared__ uint32_t base_s;
+    const uint64_t len = p.cnt->len;
+    if (threadIdx.x == 0) base_s = 0;
+    __syncthreads();
+    for (uint64_t b = 0; b < len; b += blockDim.x) {
+        const uint64_t s = b + threadIdx.x;
+        const bool live = s < len && p.state[s] != ST_COLD;
+        const unsigned bal = __ballot_sync(0xFFFFFFFFu, live);
+        const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+        if (lane == 0) warp_tot[wp] = __popc(bal);
+        __syncthreads();
+        uint32_t off = base_s;
+        for (int w = 0; w < wp; ++w) off += warp_tot[w];
+        if (live) {
+            const uint32_t o = off + __popc(bal & ((1u << lane) - 1));
+            slots_out[o] = (uint32_t)s;
+            scores_out[o] = scores[s];
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t t = 0;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += warp_tot[w];
+            base_s += t;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *n_out = base_s;
+}
+
+inline uint32_t grid_for(uint64_t n, int threads = 256) {
+    return (uint32_t)std::min<uint64_t>(std::max<uint64_t>(1, (n + threads - 1) / threads), 148 * 8);
+}
+
+}  // namespace
+
+Status pool_sync_counters(Ctx* c, Pool* pl) {
+    SLHA_CUDA(cudaMemcpyAsync(&pl->h_cnt, pl->dev.cnt, sizeof(PoolCounters), cudaMemcpyDeviceToHost, c->stream));
+    SLHA_CUDA(cudaStreamSynchronize(c->stream));
+    return Status();
+}
+
+Status pool_create(Ctx* c, const SlhaB200PoolConfig& cfg, Pool** out) {
+    auto* pl = new Pool();
+    pl->cfg = cfg;
+    pl->device = c->device;
+    const uint64_t cap = cfg.capacity_tiles;
+    PoolDev& d = pl->dev;
+    cudaError_t e = cudaSuccess;
+    auto alloc = [&](void** p, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(p, std::max<size_t>(bytes, 256)); };
+    alloc((void**)&d.tiles, cap * TILE_BYTES);
+    alloc((void**)&d.state, cap);
+    alloc((void**)&d.seq, cap * 8);
+    alloc((void**)&d.importance, cap * 4);
+    alloc((void**)&d.free_list, cap * 4);
+    alloc((void**)&d.cnt, sizeof(PoolCounters));
+    if (e != cudaSuccess) {
+        pool_destroy(pl);
+        return cuda_status(e, "cudaMalloc(pool)");
+    }
+    d.page_policy = cfg.page_policy;
+    d.evict_policy = cfg.evict_policy;
+    d.sink_window = cfg.sink_window;
+    d.recent_window = cfg.recent_window;
+    PoolCounters z{};
+    z.budget = cfg.budget_bytes;
+    pl->h_cnt = z;
+    SLHA_CUDA(cudaMemcpyAsync(d.cnt, &pl->h_cnt, sizeof(z), cudaMemcpyHostToDevice, c->stream));
+    SLHA_CUDA(cudaStreamSynchronize(c->stream));
+    *out = pl;
+    return Status();
+}
+
+void pool_destroy(Pool* pl) {
+    if (!pl) return;
+    cudaFree(pl->dev.tiles);
+    cudaFree(pl->dev.state);
+    cudaFree(pl->dev.seq);
+    cudaFree(pl->dev.importance);
+    cudaFree(pl->dev.free_list);
+    cudaFree(pl->dev.cnt);
+    cudaFree(pl->d_observe);
+    delete pl;
+}
+
+// Reserve slots for n tiles (bookkeeping only); d_slots receives the slot ids.
+Status pool_reserve(Ctx* c, Pool* pl, const unsigned char* d_src_tiles, uint64_t n, uint32_t* d_slots) {
+    PoolCounters& h = pl->h_cnt;
+    if (h.next_seq + n > 0xFFFFFFFFull)
+        return Status(SLHA_ERR_CAPACITY, "pool: insertion counter exhausted (2^32 inserts)");
+    const uint64_t pops = std::min<uint64_t>(n, h.free_len);
+    if (h.len + (n - pops) > pl->cfg.capacity_tiles)
+        return Status(SLHA_ERR_CAPACITY, "pool: capacity_tiles exceeded");
+    insert_kernel<<<(uint32_t)((n + 255) / 256), 256, 0, c->stream>>>(pl->dev, d_src_tiles, n, pops, h.len,
+                                                                      h.free_len, h.next_seq, d_slots);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    h.free_len -= pops;
+    h.len += n - pops;
+    h.next_seq += n;
+    return Status();
+}
+
+Status pool_scatter(Ctx* c, Pool* pl, const unsigned char* d_src_tiles, const uint32_t* d_slots, uint64_t n) {
+    scatter_tiles_kernel<<<(uint32_t)((n * 8 + 255) / 256), 256, 0, c->stream>>>(pl->dev.tiles, d_src_tiles, d_slots, n);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    return Status();
+}
+
+Status pool_single_op(Ctx* c, Pool* pl, int op, uint32_t slot, int32_t* result) {
+    int32_t* d_res;
+    SLHA_TRY(ctx_device_scratch(c, 256, (void**)&d_res));
+    single_op_kernel<<<1, 1, 0, c->stream>>>(pl->dev, op, slot, d_res);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    SLHA_CUDA(cudaMemcpyAsync(result, d_res, 4, cudaMemcpyDeviceToHost, c->stream));
+    return pool_sync_counters(c, pl);
+}
+
+Status pool_enforce_budget(Ctx* c, Pool* pl, int32_t* within) {
+    SLHA_TRY(pool_sync_counters(c, pl));
+    PoolCounters& h = pl->h_cnt;
+    if (h.live <= h.budget) {
+        *within = 1;
+        return Status();
+    }
+    const uint64_t len = h.len;
+    size_t tmp_sort = 0, tmp_scan = 0;
+    cub::DeviceRadixSort::SortPairs(nullptr, tmp_sort, (uint64_t*)nullptr, (uint64_t*)nullptr,
+                                    (uint32_t*)nullptr, (uint32_t*)nullptr, (int)len);
+    cub::DeviceScan::ExclusiveSum(nullptr, tmp_scan, (uint32_t*)nullptr, (uint64_t*)nullptr, (int)len);
+    const size_t tmp_bytes = std::max(tmp_sort, tmp_scan);
+    Scratch sc{c};
+    SLHA_TRY(sc.reserve(pad256(len * 8) * 3 + pad256(len * 4) * 3 + pad256(tmp_bytes) + 4096));
+    uint64_t* keys = sc.take<uint64_t>(len);
+    uint64_t* keys_s = sc.take<uint64_t>(len);
+    uint64_t* excl = sc.take<uint64_t>(len);
+    uint32_t* vals = sc.take<uint32_t>(len);
+    uint32_t* vals_s = sc.take<uint32_t>(len);
+    uint32_t* w = sc.take<uint32_t>(len);
+    void* tmp = sc.take<unsigned char>(tmp_bytes);
+    const uint32_t grid = grid_for(len);
+
+    SLHA_CUDA(cudaMemsetAsync(&pl->dev.cnt->max_pos, 0, 4, c->stream));
+    if (pl->cfg.recent_window) {
+        max_pos_kernel<<<grid, 256, 0, c->stream>>>(pl->dev);
+        count_launch();
+    }
+    const int phases[5] = {PH_CORR_HOT, PH_PAGE, PH_CORR_WARM, PH_EVICT, PH_EVICT_PINNED};
+    for (int ph : phases) {
+        if (ph == PH_EVICT_PINNED && pl->cfg.evict_policy != SLHA_B200_EVICT_IMPORTANCE) continue;
+        phase_build_kernel<<<grid, 256, 0, c->stream>>>(pl->dev, ph, keys, vals);
+        size_t tb = tmp_bytes;
+        SLHA_CUDA(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys_s, vals, vals_s, (int)len, 0, 64, c->stream));
+        phase_weights_kernel<<<grid, 256, 0, c->stream>>>(pl->dev, ph, keys_s, vals_s, w);
+        tb = tmp_bytes;
+        SLHA_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tb, w, excl, (int)len, c->stream));
+        phase_apply_kernel<<<grid, 256, 0, c->stream>>>(pl->dev, ph, keys_s, vals_s, w, excl);
+        phase_commit_kernel<<<1, 1, 0, c->stream>>>(pl->dev);
+        count_launch(4);
+        SLHA_CUDA(cudaGetLastError());
+    }
+    SLHA_TRY(pool_sync_counters(c, pl));
+    *within = pl->h_cnt.live <= pl->h_cnt.budget ? 1 : 0;
+    return Status();
+}
+
+Status pool_observe(Ctx* c, Pool* pl, const uint32_t* d_slots, const float* d_scores, uint64_t n, float temperature) {
+    if (n == 0 || !std::isfinite(temperature) || temperature <= 0.0f) return Status();
+    const int nparts = 256;
+    if (!pl->d_observe) SLHA_CUDA(cudaMalloc(&pl->d_observe, sizeof(ObserveTmp) + nparts * 4));
+    ObserveTmp* tmp = reinterpret_cast<ObserveTmp*>(pl->d_observe);
+    float* partial = reinterpret_cast<float*>(tmp + 1);
+    SLHA_CUDA(cudaMemsetAsync(tmp, 0, sizeof(ObserveTmp), c->stream));
+    observe_pass1<<<grid_for(n), 256, 0, c->stream>>>(pl->dev, d_slots, d_scores, n, tmp);
+    observe_pass2<<<nparts, 256, 0, c->stream>>>(pl->dev, d_slots, d_scores, n, temperature, tmp, partial);
+    observe_pass3<<<grid_for(n), 256, 0, c->stream>>>(pl->dev, d_slots, d_scores, n, temperature, tmp, partial, nparts);
+    count_launch(3);
+    SLHA_CUDA(cudaGetLastError());
+    return Status();
+}
+
+Status pool_stats(Ctx* c, Pool* pl, uint64_t out[8]) {
+    unsigned long long* d;
+    SLHA_TRY(ctx_device_scratch(c, 256, (void**)&d));
+    SLHA_CUDA(cudaMemsetAsync(d, 0, 64, c->stream));
+    stats_kernel<<<grid_for(std::max<uint64_t>(pl->h_cnt.len, 1)), 256, 0, c->stream>>>(pl->dev, d);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    SLHA_CUDA(cudaMemcpyAsync(out, d, 64, cudaMemcpyDeviceToHost, c->stream));
+    SLHA_CUDA(cudaStreamSynchronize(c->stream));
+    return Status();
+}
+
+Status pool_compact_live(Ctx* c, Pool* pl, const float* d_scores, uint32_t* d_slots_out, float* d_scores_out,
+                         unsigned long long* d_n_out) {
+    compact_live_kernel<<<1, 1024, 0, c->stream>>>(pl->dev, d_scores, d_slots_out, d_scores_out, d_n_out);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    return Status();
+}
+
+}  // namespace slha

@@ -1,0 +1,278 @@
+// Host side of the scoring path: work decomposition ("plan"), kernel launches.
+// Included by score.cu.
+#pragma once
+
+#include <cstdlib>
+#include <memory>
+
+namespace slha {
+
+namespace {
+
+constexpr size_t MAX_SMEM = 227 * 1024;
+
+int env_int(const char* name, int dflt) {
+    const char* v = std::getenv(name);
+    return (v && *v) ? std::atoi(v) : dflt;
+}
+
+size_t score_smem_bytes(int G, int nwarps, bool topk, uint32_t cap) {
+    size_t b = (size_t)G * D_C * 4 + 16 * 32 * 4 + (size_t)nwarps * DEPTH * BLK_BYTES;
+    if (topk) b += (size_t)G * cap * 8;
+    b += (size_t)G * 8 + (size_t)G * 4 + 260 * 4 + 16;
+    return b;
+}
+
+template <int G, bool TOPK>
+Status launch_score_t(Ctx* c, const ScoreArgs& a, uint32_t grid, int threads, size_t smem) {
+    static thread_local size_t configured[8] = {0};
+    int dev = c->device & 7;
+    if (configured[dev] < smem) {
+        SLHA_CUDA(cudaFuncSetAttribute(score_kernel<G, TOPK>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+        configured[dev] = MAX_SMEM;
+    }
+    score_kernel<G, TOPK><<<grid, threads, smem, c->stream>>>(a);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    return Status();
+}
+
+template <bool TOPK>
+Status launch_score(Ctx* c, int G, const ScoreArgs& a, uint32_t grid, int threads, size_t smem) {
+    switch (G) {
+        case 1: return launch_score_t<1, TOPK>(c, a, grid, threads, smem);
+        case 2: return launch_score_t<2, TOPK>(c, a, grid, threads, smem);
+        default: return launch_score_t<4, TOPK>(c, a, grid, threads, smem);
+    }
+}
+
+int group_width(uint32_t nq) { return nq >= 3 ? 4 : (int)nq; }
+
+// The cached decomposition of one score_topk call shape.
+struct Plan {
+    std::vector<unsigned char> key;
+    int device = -1;
+    uint32_t k = 0, cap = 0, kp2 = 0, nq = 0, n_lists = 0;
+    int threads = 128;
+    struct Class { int G; uint32_t first, count; };
+    std::vector<Class> classes;
+    WorkItem* d_items = nullptr;
+    uint32_t* d_q_list_begin = nullptr;
+    uint32_t* d_q_list_count = nullptr;
+    uint64_t* d_cand_keys = nullptr;
+    uint32_t* d_cand_cnt = nullptr;
+    ~Plan() {
+        cudaFree(d_items);
+        cudaFree(d_q_list_begin);
+        cudaFree(d_q_list_count);
+        cudaFree(d_cand_keys);
+        cudaFree(d_cand_cnt);
+    }
+};
+
+Status build_plan(Ctx* c, const SlhaB200Segment* segs, size_t n_segs, size_t nq, uint32_t k,
+                  std::unique_ptr<Plan>& slot) {
+    std::vector<unsigned char> key(sizeof(SlhaB200Segment) * n_segs + 16);
+    std::memcpy(key.data(), segs, sizeof(SlhaB200Segment) * n_segs);
+    uint64_t nq64 = nq;
+    std::memcpy(key.data() + sizeof(SlhaB200Segment) * n_segs, &nq64, 8);
+    std::memcpy(key.data() + sizeof(SlhaB200Segment) * n_segs + 8, &k, 4);
+    if (slot && slot->device == c->device && slot->key == key) return Status();
+
+    auto p = std::make_unique<Plan>();
+    p->key = std::move(key);
+    p->device = c->device;
+    p->k = k;
+    p->nq = (uint32_t)nq;
+    p->kp2 = 2;
+    while (p->kp2 < k) p->kp2 <<= 1;
+    p->threads = env_int("SLHA_B200_SCORE_THREADS", k > 1024 ? 256 : 128);
+    const int nwarps = p->threads / 32;
+    const uint32_t round = (uint32_t)nwarps * BLK_TILES;
+    uint32_t cap = std::max<uint32_t>(2 * k, k + 2 * round);
+    while (cap > k + round && score_smem_bytes(4, nwarps, true, cap) > MAX_SMEM) cap -= round;
+    if (score_smem_bytes(4, nwarps, true, cap) > MAX_SMEM || (size_t)p->kp2 * 8 + 2048 > MAX_SMEM)
+        return Status(SLHA_ERR_CAPACITY, "top-k: k is too large for the shared-memory selection state");
+    p->cap = cap;
+
+    // item size: large enough that candidate traffic stays a few percent of the
+    // tile stream, small enough to balance 148 SMs
+    uint64_t total = 0;
+    for (size_t i = 0; i < n_segs; ++i) total += (uint64_t)segs[i].n_tiles * ((segs[i].n_queries + 3) / 4);
+    uint32_t item_tiles = (uint32_t)env_int("SLHA_B200_ITEM_TILES", 0);
+    if (!item_tiles) {
+        item_tiles = std::max<uint32_t>(8192, 8 * k);
+        while (item_tiles > 2048 && total / item_tiles < 592) item_tiles /= 2;
+    }
+    item_tiles = std::max(round, (item_tiles + round - 1) / round * round);
+
+    std::vector<WorkItem> items[3];  // by class G = 1, 2, 4
+    std::vector<uint32_t> q_begin(nq, 0), q_count(nq, 0);
+    uint32_t n_lists = 0;
+    for (size_t i = 0; i < n_segs; ++i) {
+        const SlhaB200Segment& s = segs[i];
+        if ((uint64_t)s.query_begin + s.n_queries > nq)
+            return Status(SLHA_ERR_DIMENSION, "segment query range exceeds n_queries");
+        const uint32_t parts = s.n_tiles ? (s.n_tiles + item_tiles - 1) / item_tiles : 0;
+        for (uint32_t q0 = 0; q0 < s.n_queries; q0 += 4) {
+            const uint32_t gq = std::min<uint32_t>(4, s.n_queries - q0);
+            const int G = group_width(gq);
+            for (uint32_t g = 0; g < gq; ++g) {
+                const uint32_t Q = s.query_begin + q0 + g;
+                if (q_count[Q]) return Status(SLHA_ERR_DIMENSION, "a query row belongs to two segments");
+                q_begin[Q] = n_lists + g;  // lists of one item are consecutive: stride gq per part
+                q_count[Q] = parts;
+            }
+            for (uint32_t part = 0; part < parts; ++part) {
+                WorkItem w;
+                w.tile_begin = s.tile_begin + (uint64_t)part * item_tiles;
+                w.n_tiles = std::min<uint32_t>(item_tiles, s.n_tiles - part * item_tiles);
+                w.index_base = s.index_base + part * item_tiles;
+                w.query_begin = s.query_begin + q0;
+                w.n_queries = gq;
+                w.list_begin = n_lists + part * gq;
+                w.pad = gq;  // list stride between parts, used by the merge accessor
+                items[G == 1 ? 0 : (G == 2 ? 1 : 2)].push_back(w);
+            }
+            n_lists += parts * gq;
+        }
+    }
+    p->n_lists = n_lists;
+    std::vector<WorkItem> all;
+    for (int cls = 0; cls < 3; ++cls) {
+        if (items[cls].empty()) continue;
+        p->classes.push_back({cls == 0 ? 1 : (cls == 1 ? 2 : 4), (uint32_t)all.size(), (uint32_t)items[cls].size()});
+        all.insert(all.end(), items[cls].begin(), items[cls].end());
+    }
+    // per query: list id of part p is q_begin + p * stride; store stride in the count's high bits
+    std::vector<uint32_t> q_stride(nq, 1);
+    for (const WorkItem& w : all)
+        for (uint32_t g = 0; g < w.n_queries; ++g) q_stride[w.query_begin + g] = w.pad;
+    SLHA_CUDA(cudaMalloc(&p->d_items, std::max<size_t>(1, all.size()) * sizeof(WorkItem)));
+    SLHA_CUDA(cudaMalloc(&p->d_q_list_begin, std::max<size_t>(1, nq) * 4));
+    SLHA_CUDA(cudaMalloc(&p->d_q_list_count, std::max<size_t>(1, nq) * 4));
+    SLHA_CUDA(cudaMalloc(&p->d_cand_keys, std::max<size_t>(1, (size_t)n_lists * k) * 8));
+    SLHA_CUDA(cudaMalloc(&p->d_cand_cnt, std::max<size_t>(1, n_lists) * 4));
+    for (size_t Q = 0; Q < nq; ++Q) q_count[Q] |= q_stride[Q] << 24;
+    SLHA_CUDA(cudaMemcpyAsync(p->d_items, all.data(), all.size() * sizeof(WorkItem), cudaMemcpyHostToDevice, c->stream));
+    SLHA_CUDA(cudaMemcpyAsync(p->d_q_list_begin, q_begin.data(), nq * 4, cudaMemcpyHostToDevice, c->stream));
+    SLHA_CUDA(cudaMemcpyAsync(p->d_q_list_count, q_count.data(), nq * 4, cudaMemcpyHostToDevice, c->stream));
+    SLHA_CUDA(cudaStreamSynchronize(c->stream));  // host vectors die with this scope
+    slot = std::move(p);
+    return Status();
+}
+
+}  // namespace
+
+namespace {
+// slha-c/src/lib.rs:244-286 per tile; status = min over bad tiles of (index << 8 | -code)
+__global__ void validate_tiles_kernel(const unsigned char* tiles, uint64_t n, unsigned long long* status) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const unsigned char* t = tiles + i * TILE_BYTES;
+    const uint32_t flags = *reinterpret_cast<const uint16_t*>(t + 118);
+    const float sc = *reinterpret_cast<const float*>(t + 96), lam = *reinterpret_cast<const float*>(t + 100),
+                sg = *reinterpret_cast<const float*>(t + 104);
+    int code = 0;
+    if (flags & ~0x3Fu) code = 6;
+    else if (__popc(flags & (F_NF4 | F_MIXED | F_TQ3 | F_MIX3)) > 1) code = 6;
+    else if ((flags & F_NOCORR) && !(flags & (F_TQ3 | F_MIX3))) code = 6;
+    else if (!isfinite(sc) || !isfinite(lam) || !isfinite(sg)) code = 5;
+    else if (sc < 0.0f || lam < 0.0f || sg < 0.0f) code = 6;
+    if (code) atomicMin(status, (unsigned long long)((i << 8) | (uint64_t)code));
+}
+}  // namespace
+
+Status launch_validate_tiles(Ctx* c, const SciRustSlhaTile* tiles, size_t n, unsigned long long* d_status) {
+    if (n == 0) return Status();
+    validate_tiles_kernel<<<(uint32_t)((n + 255) / 256), 256, 0, c->stream>>>(
+        reinterpret_cast<const unsigned char*>(tiles), n, d_status);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    return Status();
+}
+
+Status launch_score_full(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* state, size_t n,
+                         const float* q_coarse, const uint64_t* q_sign, size_t nq, float* scores) {
+    if (n == 0 || nq == 0) return Status();
+    const int threads = 128, nwarps = threads / 32;
+    const uint32_t item_tiles = 4096;
+    const uint32_t chunks = (uint32_t)((n + item_tiles - 1) / item_tiles);
+    size_t q0 = 0;
+    while (q0 < nq) {
+        const size_t gq = std::min<size_t>(4, nq - q0);
+        const int G = group_width((uint32_t)gq);
+        ScoreArgs a{};
+        a.tiles = reinterpret_cast<const unsigned char*>(tiles);
+        a.state = state;
+        a.items = nullptr;
+        a.q_coarse = q_coarse + q0 * D_C;
+        a.q_sign = reinterpret_cast<const uint32_t*>(q_sign + q0 * 4);
+        a.scores = scores + q0 * n;
+        a.score_stride = n;
+        a.total_tiles = n;
+        a.item_tiles = item_tiles;
+        a.nq_launch = (uint32_t)gq;
+        SLHA_TRY(launch_score<false>(c, G, a, chunks, threads, score_smem_bytes(G, nwarps, false, 0)));
+        q0 += gq;
+    }
+    return Status();
+}
+
+Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* state,
+                         const SlhaB200Segment* segs, size_t n_segs, const float* d_q_coarse,
+                         const uint64_t* d_q_sign, size_t nq, uint32_t k, uint32_t* d_out_index,
+                         float* d_out_score, uint32_t* d_out_count) {
+    if (nq == 0) return Status();
+    if (k == 0 || k > 8192) return Status(SLHA_ERR_DIMENSION, "top-k: k must be in 1..8192");
+    static thread_local std::unique_ptr<Plan> cache;
+    SLHA_TRY(build_plan(c, segs, n_segs, nq, k, cache));
+    Plan* p = cache.get();
+    const int nwarps = p->threads / 32;
+    for (const Plan::Class& cl : p->classes) {
+        ScoreArgs a{};
+        a.tiles = reinterpret_cast<const unsigned char*>(tiles);
+        a.state = state;
+        a.items = p->d_items + cl.first;
+        a.q_coarse = d_q_coarse;
+        a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);
+        a.k = k;
+        a.cap = p->cap;
+        a.cand_keys = p->d_cand_keys;
+        a.cand_cnt = p->d_cand_cnt;
+        SLHA_TRY(launch_score<true>(c, cl.G, a, cl.count, p->threads, score_smem_bytes(cl.G, nwarps, true, p->cap)));
+    }
+    CompLists L{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, k};
+    const size_t smem = (size_t)p->kp2 * 8 + 260 * 4;
+    static thread_local bool configured = false;
+    if (!configured) {
+        SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<CompLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+        configured = true;
+    }
+    topk_merge_kernel<CompLists><<<(uint32_t)nq, 256, smem, c->stream>>>(L, k, p->kp2, d_out_index, d_out_score, d_out_count);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    return Status();
+}
+
+Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* cand_score,
+                               uint32_t n_lists, uint32_t n_queries, uint32_t k_in, uint32_t k_out,
+                               uint32_t* out_index, float* out_score) {
+    if (n_queries == 0) return Status();
+    if (k_out == 0 || k_out > 8192) return Status(SLHA_ERR_DIMENSION, "merge: k_out must be in 1..8192");
+    uint32_t kp2 = 2;
+    while (kp2 < k_out) kp2 <<= 1;
+    PairLists L{cand_index, cand_score, n_lists, n_queries, k_in};
+    static thread_local bool configured = false;
+    if (!configured) {
+        SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+        configured = true;
+    }
+    topk_merge_kernel<PairLists><<<n_queries, 256, (size_t)kp2 * 8 + 260 * 4, c->stream>>>(L, k_out, kp2, out_index, out_score, nullptr);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    return Status();
+}
+
+}  // namespace slha

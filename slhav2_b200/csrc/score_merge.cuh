@@ -1,0 +1,139 @@
+// Second stage of the top-k: one CTA per query merges candidate lists (the
+// per-work-item survivors of score_kernel, or per-shard results gathered from
+// other GPUs) into the final k entries, sorted by score descending with ties
+// towards the lower index (ordering of scirust/src/metrics.rs:186-192).
+// Included by score.cu.
+#pragma once
+
+namespace slha {
+namespace {
+
+// Candidate accessors: element e of query Q as a composite key, 0 = absent.
+struct CompLists {  // lists written by score_kernel
+    const uint64_t* keys;      // [n_lists][k]
+    const uint32_t* cnt;       // [n_lists]
+    const uint32_t* q_list_begin;  // [nq]
+    const uint32_t* q_list_count;  // [nq]: parts in bits 0..23, list stride between parts in bits 24..31
+    uint32_t k;
+    __device__ uint32_t size(uint32_t Q) const { return (q_list_count[Q] & 0xFFFFFFu) * k; }
+    __device__ uint64_t get(uint32_t Q, uint32_t e) const {
+        const uint32_t l = q_list_begin[Q] + (e / k) * (q_list_count[Q] >> 24), j = e % k;
+        return j < cnt[l] ? keys[(size_t)l * k + j] : 0ull;
+    }
+};
+struct PairLists {  // (index, score) lists laid out [list][query][k_in]
+    const uint32_t* idx;
+    const float* score;
+    uint32_t n_lists, n_queries, k_in;
+    __device__ uint32_t size(uint32_t) const { return n_lists * k_in; }
+    __device__ uint64_t get(uint32_t Q, uint32_t e) const {
+        const uint32_t l = e / k_in, j = e % k_in;
+        const size_t o = ((size_t)l * n_queries + Q) * k_in + j;
+        const uint32_t i = idx[o];
+        return i == 0xFFFFFFFFu ? 0ull : make_comp(score[o], i);
+    }
+};
+
+template <typename Lists>
+__global__ void __launch_bounds__(256) topk_merge_kernel(Lists L, uint32_t k, uint32_t kp2,
+                                                         uint32_t* out_index, float* out_score,
+                                                         uint32_t* out_count) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    uint64_t* buf = reinterpret_cast<uint64_t*>(smem);  // [kp2]
+    int* hist = reinterpret_cast<int*>(buf + kp2);      // 260
+    const uint32_t Q = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    const uint32_t T = L.size(Q);
+
+    // number of present candidates
+    if (tid == 0) hist[259] = 0;
+    __syncthreads();
+    int local = 0;
+    for (uint32_t e = tid; e < T; e += nt) local += L.get(Q, e) != 0ull;
+    for (int o = 16; o; o >>= 1) local += __shfl_xor_sync(0xFFFFFFFFu, local, o);
+    if ((tid & 31) == 0 && local) atomicAdd(&hist[259], local);
+    __syncthreads();
+    const uint32_t present = (uint32_t)hist[259];
+    __syncthreads();
+
+    uint64_t pivot = 1;  // every present candidate (>= 1) wins when present <= k
+    if (present > k) {
+        uint64_t prefix = 0;
+        uint32_t need = k;
+        int shift = 56;
+        for (;; shift -= 8) {
+            for (uint32_t b = tid; b < 256; b += nt) hist[b] = 0;
+            __syncthreads();
+            for (uint32_t e = tid; e < T; e += nt) {
+                const uint64_t key = L.get(Q, e);
+                if (key && (shift == 56 || (key >> (shift + 8)) == prefix))
+                    atomicAdd(&hist[(key >> shift) & 255], 1);
+            }
+            __syncthreads();
+            if (tid < 32) {
+                int c[8], tot = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { c[j] = hist[255 - 8 * tid - j]; tot += c[j]; }
+                int incl = tot;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    int y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                    if ((int)tid >= o) incl += y;
+                }
+                const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= (int)need);
+                if ((int)tid == __ffs(ok) - 1) {
+                    int run = incl - tot;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (run + c[j] >= (int)need) {
+                            hist[256] = 255 - 8 * tid - j;
+                            hist[257] = run;
+                            hist[258] = c[j];
+                            break;
+                        }
+                        run += c[j];
+                    }
+                }
+            }
+            __syncthreads();
+            const int digit = hist[256], above = hist[257], binc = hist[258];
+            __syncthreads();
+            need -= (uint32_t)above;
+            prefix = (prefix << 8) | (uint64_t)digit;
+            if ((uint32_t)binc == need || shift == 0) break;
+        }
+        pivot = prefix << shift;
+    }
+    const uint32_t m = present < k ? present : k;
+
+    // gather the winners, pad, sort descending
+    if (tid == 0) hist[259] = 0;
+    for (uint32_t i = tid; i < kp2; i += nt) buf[i] = 0ull;
+    __syncthreads();
+    for (uint32_t e = tid; e < T; e += nt) {
+        const uint64_t key = L.get(Q, e);
+        if (key >= pivot && key) buf[atomicAdd(&hist[259], 1)] = key;
+    }
+    __syncthreads();
+    for (uint32_t size = 2; size <= kp2; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride; stride >>= 1) {
+            for (uint32_t i = tid; i < kp2 / 2; i += nt) {
+                const uint32_t lo = 2 * i - (i & (stride - 1));
+                const uint32_t hi = lo + stride;
+                const bool desc = (lo & size) == 0;
+                const uint64_t x = buf[lo], y = buf[hi];
+                if ((x < y) == desc) { buf[lo] = y; buf[hi] = x; }
+            }
+            __syncthreads();
+        }
+    }
+    for (uint32_t r = tid; r < k; r += nt) {
+        const bool v = r < m;
+        const uint64_t key = v ? buf[r] : 0ull;
+        out_index[(size_t)Q * k + r] = v ? 0xFFFFFFFFu - (uint32_t)key : 0xFFFFFFFFu;
+        out_score[(size_t)Q * k + r] = v ? key_score((uint32_t)(key >> 32)) : -INFINITY;
+    }
+    if (out_count && tid == 0) out_count[Q] = m;
+}
+
+}  // namespace
+}  // namespace slha

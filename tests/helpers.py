@@ -70,3 +70,40 @@ def to_bf16_f32(x):
     u = np.ascontiguousarray(x, F).view(np.uint32).astype(np.uint64)
     r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
     return r.astype(np.uint32).view(F)
+
+
+# ---- configuration-shaped synthetic inputs (seeded, oracle PRNG) -----------------
+def make_model_pair(d=128, seed=7, rht=False, pseed=11):
+    """(oracle model, projection) for a seeded row-orthonormal projection."""
+    p = orthogonal_projection(pseed, d)
+    return ora.Model(p, d, seed=seed, rht=rht), p
+
+
+def random_tiles(n, codec, seed, d=128, warm_every=0, nocorr_every=0, model=None):
+    """Oracle-encoded tiles of seeded Gaussian keys (optionally some WARM / NOCORR)."""
+    if model is None:
+        model, _ = make_model_pair(d)
+    keys = gaussian_keys(seed, n, model.d, outlier_channels=(7, 93))
+    tiles = model.encode_batch(keys, codec)
+    if warm_every:
+        idx = np.arange(n) % warm_every == 0
+        tiles["flags"][idx] |= ora.FLAG_WARM
+        tiles["residual_bitmap"][idx] = 0
+        tiles["dynamic_lambda"][idx] = 0
+    if nocorr_every and codec in (4, 5):
+        idx = np.arange(n) % nocorr_every == 1
+        nb = 16 if codec == 4 else 14
+        tiles["latent_kv"][idx, 64 - nb:] = 0
+        tiles["flags"][idx] |= ora.FLAG_TQ3_NOCORR
+    return tiles
+
+
+def random_queries(nq, seed):
+    rng = ora.Rng(seed)
+    qc = rng.gaussian(nq * 128).reshape(nq, 128)
+    qs = np.array([[rng.next_u64() for _ in range(4)] for _ in range(nq)], np.uint64)
+    return qc, qs
+
+
+def oracle_scores(tiles, qc, qs):
+    return np.stack([ora.score_tiles(tiles, qc[j], qs[j]) for j in range(len(qc))])

@@ -1,0 +1,98 @@
+"""CUDA encode / prepare_query vs the oracle: tile bytes bit-exact."""
+import numpy as np
+import pytest
+
+from oracle import pyoracle as ora
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+S = pytest.importorskip("slhav2_b200")
+F = np.float32
+
+
+def _models(d, rht, seed=7):
+    om, p = H.make_model_pair(d, seed=seed, rht=rht)
+    return om, S.Model.from_projection(p, d, seed, rht=rht)
+
+
+def _diff(a, b):
+    bad = np.nonzero(a.view(np.uint8).reshape(-1, 128) != b.view(np.uint8).reshape(-1, 128))
+    return "first mismatch tile %d byte %d" % (bad[0][0], bad[1][0]) if len(bad[0]) else ""
+
+
+@pytest.mark.parametrize("codec", range(7))
+@pytest.mark.parametrize("d,rht", [(128, False), (160, False), (160, True), (128, True)])
+def test_encode_bit_exact(codec, d, rht):
+    om, gm = _models(d, rht)
+    n = 300
+    keys = H.gaussian_keys(50 + codec, n, d, outlier_channels=(7, 93))
+    keys[5] = 0.0  # all-zero key: scale falls back to 1.0
+    pos = np.arange(1000, 1000 + n, dtype=np.uint32)
+    heads = (np.arange(n) % 8).astype(np.uint16)
+    want = om.encode_batch(keys, codec, pos=pos, head=heads)
+    got = gm.encode_keys(keys, codec, positions=pos, head_ids=heads)
+    assert got.tobytes() == want.tobytes(), _diff(got, want)
+
+
+@pytest.mark.parametrize("n", [1, 15, 16, 17, 33])
+def test_encode_ragged_batches_and_bf16(n):
+    om, gm = _models(128, False)
+    keys = H.to_bf16_f32(H.gaussian_keys(n, n, 128))
+    want = om.encode_batch(keys, 2, pos=np.arange(n, dtype=np.uint32) + 7)
+    bf16 = (keys.view(np.uint32) >> 16).astype(np.uint16)
+    got = gm.encode_keys(bf16, 2, n=n, key_dtype=S.BF16, position_base=7)
+    assert got.tobytes() == want.tobytes(), _diff(got, want)
+
+
+def test_single_key_abi_matches_batch_and_oracle():
+    om, gm = _models(160, False)
+    keys = H.gaussian_keys(3, 4, 160)
+    for codec in range(6):
+        batch = gm.encode_keys(keys, codec)
+        for i in range(4):
+            one = gm.encode_key(keys[i], position=i, codec=codec)
+            assert one.tobytes() == batch[i:i + 1].tobytes() == om.encode(keys[i], i, codec=codec).tobytes()
+
+
+@pytest.mark.parametrize("d,rht", [(128, False), (160, True)])
+def test_prepare_queries_bit_exact(d, rht):
+    om, gm = _models(d, rht)
+    q = H.gaussian_keys(9, 37, d)
+    qc, qs = gm.prepare_queries(q)
+    for j in range(len(q)):
+        wc, ws = om.prepare_query(q[j])
+        assert np.array_equal(qs[j], ws)
+        assert np.array_equal(qc[j].view(np.uint32), wc.view(np.uint32))
+    c1, s1 = gm.prepare_query(q[0])
+    assert np.array_equal(c1, qc[0]) and np.array_equal(s1, qs[0])
+
+
+def test_whitened_model_and_decode():
+    p = H.orthogonal_projection(21, 160)
+    scale = (0.5 + np.abs(ora.Rng(22).gaussian(128))).astype(F)
+    om = ora.Model(p, 160, seed=5, scale=scale)
+    gm = S.Model.from_projection(p, 160, 5, scale=scale)
+    keys = H.gaussian_keys(23, 64, 160)
+    want = om.encode_batch(keys, 3)
+    got = gm.encode_keys(keys, 3)
+    assert got.tobytes() == want.tobytes(), _diff(got, want)
+    for i in (0, 17):
+        assert np.allclose(gm.decode_latent(got[i:i + 1]), om.decode_latent(want[i:i + 1]), atol=1e-5)
+        assert np.allclose(gm.decode_key(got[i:i + 1]), om.decode_key(want[i:i + 1]), atol=1e-4)
+
+
+def test_encode_then_score_end_to_end_config1_shape():
+    # BASELINE config 1 at reduced length: INT4 single, d=128, outlier channels, top-64
+    om, gm = _models(128, False, seed=0)
+    n = 2048
+    keys = H.gaussian_keys(0, n, 128, outlier_channels=(7, 93))
+    dt = S.DeviceBuffer(n * 128)
+    gm.encode_keys(keys, 0, out=dt)
+    tiles = dt.download(S.TILE_DTYPE, n)
+    assert tiles.tobytes() == om.encode_batch(keys, 0).tobytes()
+    q = ora.Rng(1).gaussian(128)
+    qc, qs = gm.prepare_queries(q[None])
+    gi, gsc, gc = S.score_topk(dt, S.make_segments([(0, n, 0, 1, 0)]), qc, qs, 1, 64)
+    want = ora.score_tiles(tiles, qc[0], qs[0])
+    oi, ov = ora.topk(want, 64)
+    assert set(gi[0]) == set(oi) or np.all(np.abs(np.sort(gsc[0])[::-1] - ov) <= 1e-3)

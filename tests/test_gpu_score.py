@@ -1,0 +1,91 @@
+"""CUDA scoring vs the CPU oracle (compute_score_scalar), through the C ABI.
+
+Tolerance: scores within 1e-3 absolute of the scalar path and within the
+reference's own SIMD-vs-scalar bound 1e-3*(1+|s|)
+(scirust/src/attention/slha_v2/tests.rs:542, slhav2-vram/tests/cuda.rs:381);
+Hamming distances bit-exact."""
+import numpy as np
+import pytest
+
+from oracle import pyoracle as ora
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+S = pytest.importorskip("slhav2_b200")
+F = np.float32
+
+
+def _close(got, want):
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert np.all(err <= 1e-3), float(err.max())
+    assert np.all(err <= 1e-3 * (1 + np.abs(want)))
+
+
+@pytest.mark.parametrize("codec", range(7))
+@pytest.mark.parametrize("nq", [1, 2, 3, 4, 5])
+def test_score_tiles_all_codecs(codec, nq):
+    n = 1000 + 37 * codec
+    tiles = H.random_tiles(n, codec, seed=100 + codec, warm_every=7, nocorr_every=5)
+    qc, qs = H.random_queries(nq, 200 + codec)
+    got = S.score_tiles(tiles, n, qc, qs, nq)
+    _close(got, H.oracle_scores(tiles, qc, qs))
+
+
+@pytest.mark.parametrize("n", [1, 3, 31, 32, 33, 127, 128, 129, 255, 257, 4095, 4097])
+def test_score_tiles_ragged_sizes(n):
+    tiles = H.random_tiles(n, 2, seed=n)
+    qc, qs = H.random_queries(1, n + 1)
+    _close(S.score_tiles(tiles, n, qc, qs, 1), H.oracle_scores(tiles, qc, qs))
+
+
+def test_empty_input_is_a_noop():
+    assert S.score_tiles(np.zeros(0, S.TILE_DTYPE), 0, np.zeros((1, 128), F), np.zeros((1, 4), np.uint64), 1).shape == (1, 0)
+
+
+def test_hamming_term_is_bit_exact():
+    # zero-level INT4 latent (0x88), lambda = 1: score == 256 - 2*hamming exactly
+    rng = ora.Rng(0x4D31)
+    n = 4000
+    tiles = np.zeros(n, S.TILE_DTYPE)
+    tiles["latent_kv"] = 0x88
+    tiles["scale"] = 1.0
+    tiles["group_scales"] = 255
+    tiles["dynamic_lambda"] = 1.0
+    tiles["residual_bitmap"] = np.array([[rng.next_u64() for _ in range(4)] for _ in range(n)], np.uint64)
+    qc, qs = H.random_queries(3, 5)
+    got = S.score_tiles(tiles, n, qc, qs, 3)
+    for j in range(3):
+        ham = np.array([ora.hamming(qs[j], tiles["residual_bitmap"][i]) for i in range(n)])
+        assert np.array_equal(got[j], (256 - 2 * ham).astype(F))
+
+
+@pytest.mark.parametrize("byte,expected", [(0x88, 0.0), (0x00, -1024.0), (0xFF, 896.0)])
+def test_int4_known_answers_through_legacy_abi(byte, expected):
+    # slhav2-vram/tests/cpu.rs:53-115
+    t = np.zeros(1, S.TILE_DTYPE)
+    t["latent_kv"] = byte
+    t["scale"] = 1.0
+    t["group_scales"] = 255
+    assert abs(S.process_tile(t, np.ones(128, F), np.zeros(4, np.uint64)) - expected) < 1e-4
+
+
+def test_readme_basic_usage_through_legacy_abi():
+    v = ((np.arange(128, dtype=F) - 64) / 16).astype(F)
+    lat, scale, gs = ora.quantize(v, 0)
+    t = ora.make_tile(lat, scale, gs, lam=0.5)
+    qc = np.zeros(128, F)
+    qc[:2] = 1
+    s = S.process_tile(t, qc, np.full(4, 0x123456789ABCDEF0, np.uint64))
+    assert "%.6f" % s == "-8.000000"
+
+
+def test_device_resident_inputs_and_outputs():
+    n, nq = 5000, 4
+    tiles = H.random_tiles(n, 1, seed=3)
+    qc, qs = H.random_queries(nq, 4)
+    dt, dq, ds = S.to_device(tiles), S.to_device(qc), S.to_device(qs)
+    dout = S.DeviceBuffer(n * nq * 4)
+    S.score_tiles(dt, n, dq, ds, nq, out=dout)
+    S.synchronize()
+    _close(dout.download(F, n * nq).reshape(nq, n), H.oracle_scores(tiles, qc, qs))
+    assert S.launch_count() > 0

@@ -1,0 +1,91 @@
+"""Fused scoring + top-k vs the oracle (score desc, ties -> lower index)."""
+import numpy as np
+import pytest
+
+from oracle import pyoracle as ora
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+S = pytest.importorskip("slhav2_b200")
+F = np.float32
+
+
+def check_topk(tiles, segs, qc, qs, k, got_idx, got_sc, got_cnt):
+    """Index sets must match except where scores tie within 1e-3."""
+    for (tb, nt, qb, nq, base) in segs:
+        seg_tiles = tiles[tb:tb + nt]
+        for j in range(qb, qb + nq):
+            want = ora.score_tiles(seg_tiles, qc[j], qs[j]) if nt else np.zeros(0, F)
+            kk = min(k, nt)
+            assert got_cnt[j] == kk
+            idx = got_idx[j, :kk].astype(np.int64) - base
+            assert np.all((idx >= 0) & (idx < nt)) and len(set(idx)) == kk
+            # reported scores are the tile scores, sorted descending
+            assert np.all(np.abs(got_sc[j, :kk] - want[idx]) <= 1e-3)
+            assert np.all(np.diff(got_sc[j, :kk]) <= 0)
+            eq = got_sc[j, :kk][1:] == got_sc[j, :kk][:-1]
+            assert np.all(got_idx[j, :kk][1:][eq] > got_idx[j, :kk][:-1][eq])  # ties -> lower index first
+            if kk < nt:
+                oi, ov = ora.topk(want, kk)
+                missing = set(oi) - set(idx)
+                extra = set(idx) - set(oi)
+                thr = ov[-1]
+                assert all(abs(want[i] - thr) <= 2e-3 for i in missing | extra), (len(missing), len(extra))
+            assert np.all(got_idx[j, kk:] == 0xFFFFFFFF) and np.all(np.isneginf(got_sc[j, kk:]))
+
+
+@pytest.mark.parametrize("n,k,nq,codec", [(4096, 64, 1, 0), (5000, 100, 4, 2), (333, 1024, 2, 1), (20000, 1024, 4, 2),
+                                           (9000, 2048, 3, 6), (257, 1, 1, 4), (70000, 512, 5, 3)])
+def test_single_segment(n, k, nq, codec):
+    tiles = H.random_tiles(n, codec, seed=n + k, warm_every=9)
+    qc, qs = H.random_queries(nq, k)
+    segs = [(0, n, 0, nq, 0)]
+    dt = S.to_device(tiles)
+    gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, nq, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+
+
+def test_gqa_segments_ragged_and_empty():
+    # several KV heads (segments) of different lengths, 4 query heads each, a
+    # global index base per segment, one empty segment
+    lens = [3000, 1, 0, 8191, 513]
+    tiles = H.random_tiles(sum(lens), 2, seed=77)
+    nq = 4 * len(lens)
+    qc, qs = H.random_queries(nq, 78)
+    segs, off = [], 0
+    for i, ln in enumerate(lens):
+        segs.append((off, ln, 4 * i, 4, 1000 * i))
+        off += ln
+    dt = S.to_device(tiles)
+    gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, nq, 128)
+    check_topk(tiles, segs, qc, qs, 128, gi, gs_, gc)
+
+
+def test_ties_resolve_to_lower_index():
+    base = H.random_tiles(50, 1, seed=5)
+    tiles = np.concatenate([base] * 40)  # every score appears 40 times
+    qc, qs = H.random_queries(2, 6)
+    n = len(tiles)
+    dt = S.to_device(tiles)
+    gi, gs_, gc = S.score_topk(dt, S.make_segments([(0, n, 0, 2, 0)]), qc, qs, 2, 100)
+    for j in range(2):
+        want = ora.score_tiles(tiles, qc[j], qs[j])
+        gpu_all = S.score_tiles(tiles, n, qc[j:j + 1], qs[j:j + 1], 1)[0]
+        oi, _ = ora.topk(gpu_all, 100)  # exact order on the GPU's own scores
+        assert np.array_equal(gi[j], oi)
+        assert np.all(np.abs(gs_[j] - want[oi]) <= 1e-3)
+
+
+def test_topk_merge_of_shard_lists():
+    # two "shards" score disjoint token ranges; merged result == single pass
+    n, k, nq = 6000, 256, 4
+    tiles = H.random_tiles(n, 6, seed=9)
+    qc, qs = H.random_queries(nq, 10)
+    dt = S.to_device(tiles)
+    full = S.score_topk(dt, S.make_segments([(0, n, 0, nq, 0)]), qc, qs, nq, k)
+    a = S.score_topk(dt, S.make_segments([(0, 2500, 0, nq, 0)]), qc, qs, nq, k)
+    b = S.score_topk(dt, S.make_segments([(2500, n - 2500, 0, nq, 2500)]), qc, qs, nq, k)
+    ci = np.stack([a[0], b[0]])
+    cs = np.stack([a[1], b[1]])
+    mi, ms = S.topk_merge(ci, cs, 2, nq, k, k)
+    assert np.array_equal(mi, full[0]) and np.array_equal(ms, full[1])
