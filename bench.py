@@ -1,0 +1,413 @@
+#!/usr/bin/env python
+"""Benchmark of the SLHA v2 tile hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--workload c2|c5] [--impl reference]
+
+A "step" is one pass of fused eq. 2.3 scoring + top-k over every tile a rank
+holds.  Default workload (N=1): BASELINE config 2, Llama-3-8B-shaped decode KV --
+32 layers x 8 KV heads x 32768 tokens = 8.4M NF4 tiles (1.07 GB), 32 query heads
+per layer in GQA groups of 4, top-1024 per query head.  For N>1 every rank holds
+such a shard of a N x 32768-token context (weak scaling by token range), takes
+its own top-1024 and the shards are merged with one NCCL all-gather + a merge
+kernel.  `--workload c5` is BASELINE config 5 (1M tokens x 8 KV heads, INT4
+MX-32, top-2048, token range split over the ranks: strong scaling).
+
+Synthetic data stands in for real activations: seeded N(0,1) keys scaled by
+per-channel log-normal(0, 0.5) factors with RoPE (theta = 500000) applied, bf16,
+encoded on the GPU by this library; seeded N(0,1) queries.
+
+Rank 0 prints ONE JSON line.  `--impl reference` times the CPU restatement of the
+reference's vectorised compute_score (oracle/) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "c2": dict(name="config2 llama3-8b decode KV", layers=32, kv_heads=8, tokens=32768, group=4, codec=2,
+               codec_name="nf4", k=1024, scaling="weak"),
+    "c5": dict(name="config5 long-context sharded", layers=1, kv_heads=8, tokens=1048576, group=4, codec=6,
+               codec_name="int4-mx32", k=2048, scaling="strong"),
+}
+HEAD_DIM = 128
+ROPE_THETA = 500000.0
+
+
+def workload_config(w, n_gpus):
+    return {
+        "workload": "%s: %d layers x %d KV heads x %d tokens%s, %s tiles, GQA group %d, top-%d per query head"
+        % (w["name"], w["layers"], w["kv_heads"], w["tokens"], " per GPU" if w["scaling"] == "weak" else " total",
+           w["codec_name"], w["group"], w["k"]),
+        "tiles_per_gpu": tiles_per_rank(w, n_gpus),
+        "queries_per_tile": w["group"],
+        "head_dim": HEAD_DIM,
+        "sharding": "token range, merge by NCCL all-gather" if n_gpus > 1 else "single GPU",
+        "l2_policy": "tile stream per step (>= 134 MB per GPU) exceeds the 126 MB L2; no explicit flush",
+    }
+
+
+def tiles_per_rank(w, n_gpus):
+    t = w["tokens"] if w["scaling"] == "weak" else w["tokens"] // n_gpus
+    return w["layers"] * w["kv_heads"] * t
+
+
+def seeded_projection(seed):
+    """Seeded orthogonal 128x128 projection (QR of a Gaussian), float32."""
+    g = np.random.default_rng(seed).standard_normal((HEAD_DIM, HEAD_DIM))
+    q, _ = np.linalg.qr(g)
+    return np.ascontiguousarray(q.T, np.float32)
+
+
+def synth_keys_numpy(seed, n_heads, tokens, pos0):
+    """CPU twin of the key generator (used by the reference arm)."""
+    rng = np.random.default_rng(seed)
+    chan = np.exp(0.5 * rng.standard_normal(HEAD_DIM)).astype(np.float32)
+    k = rng.standard_normal((n_heads, tokens, HEAD_DIM), dtype=np.float32) * chan
+    pos = np.arange(pos0, pos0 + tokens, dtype=np.float64)
+    inv = ROPE_THETA ** (-np.arange(0, HEAD_DIM, 2, dtype=np.float64) / HEAD_DIM)
+    ang = pos[:, None] * inv[None, :]
+    c, s = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    a, b = k[..., 0::2].copy(), k[..., 1::2].copy()
+    k[..., 0::2] = a * c - b * s
+    k[..., 1::2] = a * s + b * c
+    u = k.view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16  # round to bf16, widen back
+    return r.astype(np.uint32).view(np.float32)
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1]))
+                    mx.append(float(p[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def measured_peak_gbs():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_score_rate(tiles, qc, qs, group, heads, min_seconds, threads):
+    """Tiles/s of the CPU port over `tiles` ([heads][tokens] tiles, `group` queries per
+    head): every tile is scored against its head's `group` queries."""
+    from oracle import pyoracle as ora
+
+    per_head = len(tiles) // heads
+    t0, reps = time.perf_counter(), 0
+    while True:
+        for h in range(heads):
+            seg = tiles[h * per_head:(h + 1) * per_head]
+            for g in range(group):
+                ora.score_sink(seg, qc[h * group + g], qs[h * group + g], -1, threads)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds:
+            return reps * len(tiles) / dt, dt, reps
+
+
+def reference_arm(args, w):
+    """The reference's own CPU path for this workload: vectorised compute_score
+    (AVX-512 > AVX2 > scalar dispatch) over a contiguous tile array, all host
+    threads.  The reference has no top-k step, so none is timed here."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import pyoracle as ora
+
+    threads = os.cpu_count() or 1
+    heads, tokens = w["kv_heads"], min(w["tokens"], 32768)
+    keys = synth_keys_numpy(1234, heads, tokens, 0).reshape(-1, HEAD_DIM)
+    model = ora.Model(seeded_projection(100), HEAD_DIM, seed=100)
+    tiles = model.encode_batch(keys, w["codec"])
+    rng = np.random.default_rng(7)
+    q = rng.standard_normal((heads * w["group"], HEAD_DIM), dtype=np.float32)
+    prep = [model.prepare_query(x) for x in q]
+    qc, qs = np.stack([p[0] for p in prep]), np.stack([p[1] for p in prep])
+    for _ in range(max(args.warmup, 1)):
+        cpu_score_rate(tiles, qc, qs, w["group"], heads, 0.0, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_score_rate(tiles, qc, qs, w["group"], heads, 0.0, threads)
+    dt = time.perf_counter() - t0
+    value = args.steps * len(tiles) / dt
+    sample = "%d tiles (%d KV heads x %d tokens of one layer) x %d queries per step" % (len(tiles), heads, tokens, w["group"])
+    line = {
+        "impl": "reference", "metric": "tiles_scored_per_s", "value": value, "unit": "tiles/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
+        "scaling": w["scaling"], "vs_baseline": None, "dtype": "int4->f32", "data": "synthetic",
+        "config": workload_config(w, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tiles/s", "cores": threads, "kind": "port", "sample": sample,
+                         "isa": ["scalar", "avx2", "avx512"][ora.simd_level()]},
+        "e2e": {"value": value, "unit": "tiles/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference binary unavailable (Rust, no toolchain): C restatement of its AVX-512/AVX2 compute_score; "
+                "scoring only (the reference has no top-k)",
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- GPU arm
+def build_shard(S, torch, w, rank, world, dev):
+    """Generate this rank's keys on the device, encode them into tiles, prepare the queries.
+    Returns (tiles_u8, segments, q_coarse, q_sign, n_tiles, encode_tiles_per_s)."""
+    L, H, G = w["layers"], w["kv_heads"], w["group"]
+    T = w["tokens"] if w["scaling"] == "weak" else w["tokens"] // world
+    pos0 = rank * T
+    n_tiles = L * H * T
+    tiles = torch.empty(n_tiles * 128, dtype=torch.uint8, device=dev)
+    nq = L * H * G
+    q_coarse = torch.empty(nq, 128, dtype=torch.float32, device=dev)
+    q_sign = torch.empty(nq, 4, dtype=torch.int64, device=dev)
+    gen = torch.Generator(device=dev)
+    pos = torch.arange(pos0, pos0 + T, device=dev, dtype=torch.float64)
+    inv = ROPE_THETA ** (-torch.arange(0, HEAD_DIM, 2, device=dev, dtype=torch.float64) / HEAD_DIM)
+    ang = pos[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    positions = torch.arange(pos0, pos0 + T, device=dev, dtype=torch.int32).repeat(H).contiguous()
+    heads = torch.arange(H, device=dev, dtype=torch.int16).repeat_interleave(T).contiguous()
+    segs = []
+    enc_ms = 0.0
+    chunk_tokens = min(T, 131072)
+    for l in range(L):
+        model = S.Model.from_projection(seeded_projection(100 + l), HEAD_DIM, 100 + l)
+        gen.manual_seed(1234 + l + 7919 * rank)  # every rank holds different tokens
+        chan = torch.exp(0.5 * torch.randn(HEAD_DIM, generator=gen, device=dev))
+        for h in range(H):
+            for t0 in range(0, T, chunk_tokens):
+                t1 = min(T, t0 + chunk_tokens)
+                k = torch.randn(t1 - t0, HEAD_DIM, generator=gen, device=dev) * chan
+                a, b = k[:, 0::2].clone(), k[:, 1::2].clone()
+                k[:, 0::2] = a * cos[t0:t1] - b * sin[t0:t1]
+                k[:, 1::2] = a * sin[t0:t1] + b * cos[t0:t1]
+                kb = k.to(torch.bfloat16).contiguous()
+                off = ((l * H + h) * T + t0) * 128
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                model.encode_keys(kb, w["codec"], n=t1 - t0, key_dtype=S.BF16, positions=positions[h * T + t0:h * T + t1],
+                                  head_ids=heads[h * T + t0:h * T + t1], out=tiles[off:off + (t1 - t0) * 128])
+                e1.record()
+                torch.cuda.synchronize()
+                enc_ms += e0.elapsed_time(e1)
+            segs.append(((l * H + h) * T, T, (l * H + h) * G, G, pos0))
+        gen.manual_seed(99 + l)  # queries are the same on every rank
+        q = torch.randn(H * G, HEAD_DIM, generator=gen, device=dev)
+        model.prepare_queries(q, nq=H * G, q_coarse_out=q_coarse[l * H * G:(l + 1) * H * G], q_sign_out=q_sign[l * H * G:(l + 1) * H * G])
+        torch.cuda.synchronize()
+        model.release()
+    return tiles, S.make_segments(segs), q_coarse, q_sign, n_tiles, n_tiles / (enc_ms * 1e-3)
+
+
+def gpu_arm(args, w):
+    import torch
+
+    import slhav2_b200 as S
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == args.gpus, "launch with torchrun --nproc-per-node N for --gpus N"
+    if not torch.cuda.is_available() or S.device_count() == 0:
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    S.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    stream = torch.cuda.current_stream()
+    S.set_stream(stream.cuda_stream)
+
+    tiles, segs, q_coarse, q_sign, n_tiles, enc_rate = build_shard(S, torch, w, rank, world, dev)
+    nq, k = q_coarse.shape[0], w["k"]
+    # candidate block: [2][nq][k] (indices, then score bits) so one all-gather moves both
+    cand = torch.empty(2, nq, k, dtype=torch.int32, device=dev)
+    cnt = torch.empty(nq, dtype=torch.int32, device=dev)
+    gathered = torch.empty(world, 2, nq, k, dtype=torch.int32, device=dev) if world > 1 else None
+    out = torch.empty(2, nq, k, dtype=torch.int32, device=dev)
+
+    def step():
+        S.score_topk(tiles, segs, q_coarse, q_sign, nq, k, out_index=cand[0], out_score=cand[1], out_count=cnt)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, cand)
+            S.topk_merge(gathered, gathered[0, 1], world, nq, k, k, out_index=out[0], out_score=out[1], list_stride=2 * nq * k)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = S.launch_count()
+    S.timing_begin(args.steps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see the timed region only
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    torch.cuda.profiler.stop()
+    ms = e0.elapsed_time(e1)
+    launches = S.launch_count() - launches0
+    score_ms, merge_ms = S.timing_end(args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the C ABI with host buffers (pinned): queries up, top-k down
+    hq = q_coarse.cpu().pin_memory()
+    hs = q_sign.cpu().pin_memory()
+    h_idx = torch.empty(nq, k, dtype=torch.int32).pin_memory()
+    h_sc = torch.empty(nq, k, dtype=torch.float32).pin_memory()
+    h_cnt = torch.empty(nq, dtype=torch.int32).pin_memory()
+
+    def e2e_step():
+        if world == 1:
+            S.score_topk(tiles, segs, hq, hs, nq, k, out_index=h_idx, out_score=h_sc, out_count=h_cnt)
+        else:
+            S.score_topk(tiles, segs, hq, hs, nq, k, out_index=cand[0], out_score=cand[1], out_count=cnt)
+            dist.all_gather_into_tensor(gathered, cand)
+            S.topk_merge(gathered, gathered[0, 1], world, nq, k, k, out_index=h_idx, out_score=h_sc, list_stride=2 * nq * k)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e_ms = max(f0.elapsed_time(f1), 1e3 * (time.perf_counter() - t0))  # host waits are part of an end-to-end call
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    total_tiles = n_tiles * world
+    ms_step = ms / args.steps
+    value = total_tiles / (ms_step * 1e-3)
+    peak, peak_kind = measured_peak_gbs()
+    k_ms = float(np.mean(score_ms)) if len(score_ms) else float("nan")
+    achieved = n_tiles * 128 / (k_ms * 1e-3) / 1e9
+    line = {
+        "metric": "tiles_scored_per_s", "value": value, "unit": "tiles/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": w["scaling"],
+        "vs_baseline": None, "dtype": "int4->f32", "data": "synthetic", "config": workload_config(w, world),
+        "scores_per_s": value * w["group"],
+        "hbm_gbs_whole_step": total_tiles * 128 / (ms_step * 1e-3) / 1e9,
+        "roofline": {"bound": "hbm", "kernel": "score_kernel<4,topk>", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
+                     "kernel_ms": k_ms, "merge_kernel_ms": float(np.mean(merge_ms)) if len(merge_ms) else None,
+                     "algorithmic_bytes_per_launch": n_tiles * 128, "traffic": None},
+        "e2e": {"value": total_tiles / (e2e_ms / args.steps * 1e-3), "unit": "tiles/s", "ms_per_step": e2e_ms / args.steps,
+                "h2d_bytes_per_step": int(nq * (512 + 32)), "d2h_bytes_per_step": int(nq * k * 8 + (nq * 4 if world == 1 else 0))},
+        "gpu_launches": int(launches),
+        "encode_tiles_per_s": enc_rate,
+        "clocks": clocks,
+    }
+    if world == 1:
+        n_s = min(n_tiles, w["kv_heads"] * min(w["tokens"], 32768))
+        heads = w["kv_heads"]
+        host_tiles = np.frombuffer(tiles[: n_s * 128].cpu().numpy().tobytes(), S.TILE_DTYPE)
+        threads = os.cpu_count() or 1
+        hqc = hq[: heads * w["group"]].numpy()
+        hqs = hs[: heads * w["group"]].numpy().view(np.uint64)
+        rate, dt, reps = cpu_score_rate(host_tiles, hqc, hqs, w["group"], heads, 3.0, threads)
+        from oracle import pyoracle as ora
+
+        line["cpu_baseline"] = {
+            "value": rate, "unit": "tiles/s", "cores": threads, "kind": "port",
+            "isa": ["scalar", "avx2", "avx512"][ora.simd_level()],
+            "sample": "%d tiles (%d KV heads x %d tokens) x %d queries, %d passes in %.1f s" % (n_s, heads, n_s // heads, w["group"], reps, dt),
+        }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        reference_arm(args, w)
+    else:
+        gpu_arm(args, w)
+
+
+if __name__ == "__main__":
+    main()

@@ -136,9 +136,11 @@ void slha_weights_free(SlhaModel* model);       /* slha.h:278 */
  *                                                                      *
  * Data pointers marked "host or device" are classified at run time;    *
  * host buffers are staged through the library's stream.  Work is       *
- * enqueued on the calling thread's stream (slha_b200_set_stream) and   *
- * the call returns after that stream has been synchronised unless the  *
- * documentation of the function says "asynchronous".                  *
+ * enqueued on the calling thread's stream.  With the library's own     *
+ * stream a call returns after the stream has been drained.  After      *
+ * slha_b200_set_stream(s) the caller owns synchronisation: calls whose *
+ * outputs are device memory only enqueue work on s and return; calls   *
+ * with host outputs still wait for their own copies.                  *
  * ------------------------------------------------------------------ */
 
 /* Number of CUDA devices visible; 0 when there is none. */
@@ -150,6 +152,14 @@ int32_t slha_b200_set_device(int32_t device);
 int32_t slha_b200_set_stream(void* cuda_stream);
 /* Kernels launched by this library in this process so far. */
 uint64_t slha_b200_launch_count(void);
+/* Device timing of the fused score + top-k path: after timing_begin, each of
+ * the calling thread's next `max_calls` slha_b200_score_topk /
+ * slha_b200_pool_score_topk calls records CUDA events on its stream around the
+ * scoring kernel(s) and around the merge kernel.  timing_end drains the stream,
+ * writes per-call milliseconds (host arrays of `capacity` floats, may be NULL)
+ * and the number of recorded calls, and stops recording. */
+int32_t slha_b200_timing_begin(uint32_t max_calls);
+int32_t slha_b200_timing_end(float* score_ms, float* merge_ms, uint32_t capacity, uint32_t* n_out);
 /* Raw device memory for callers that have no CUDA runtime of their own. */
 int32_t slha_b200_malloc(size_t bytes, void** out);
 int32_t slha_b200_free(void* ptr);
@@ -232,6 +242,13 @@ int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment
 int32_t slha_b200_topk_merge(const uint32_t* cand_index, const float* cand_score,
                              uint32_t n_lists, uint32_t n_queries, uint32_t k_in, uint32_t k_out,
                              uint32_t* out_index, float* out_score);
+
+/* Same, for lists whose per-list blocks are `list_stride` elements apart (for
+ * instance index and score blocks interleaved in one gathered buffer). */
+int32_t slha_b200_topk_merge_strided(const uint32_t* cand_index, const float* cand_score,
+                                     uint32_t n_lists, uint64_t list_stride, uint32_t n_queries,
+                                     uint32_t k_in, uint32_t k_out, uint32_t* out_index,
+                                     float* out_score);
 
 /* -------- CCOS elastic tile pool (scirust/src/ccos.rs ElasticKvCache) -------- */
 

@@ -73,6 +73,8 @@ SIGNATURES = {
     "slha_b200_set_device": (_i32, [_i32]),
     "slha_b200_set_stream": (_i32, [_vp]),
     "slha_b200_launch_count": (_u64, []),
+    "slha_b200_timing_begin": (_i32, [_u32]),
+    "slha_b200_timing_end": (_i32, [_vp, _vp, _u32, _vp]),
     "slha_b200_malloc": (_i32, [_sz, C.POINTER(_vp)]),
     "slha_b200_free": (_i32, [_vp]),
     "slha_b200_memcpy": (_i32, [_vp, _vp, _sz]),
@@ -83,6 +85,7 @@ SIGNATURES = {
     "slha_b200_score_tiles": (_i32, [_vp, _sz, _vp, _vp, _sz, _vp]),
     "slha_b200_score_topk": (_i32, [_vp, _vp, _sz, _vp, _vp, _sz, _u32, _vp, _vp, _vp]),
     "slha_b200_topk_merge": (_i32, [_vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
+    "slha_b200_topk_merge_strided": (_i32, [_vp, _vp, _u32, _u64, _u32, _u32, _u32, _vp, _vp]),
     "slha_b200_pool_create": (_i32, [_vp, C.POINTER(_vp)]),
     "slha_b200_pool_destroy": (_i32, [_vp]),
     "slha_b200_pool_insert_tiles": (_i32, [_vp, _vp, _sz, _vp]),
@@ -171,6 +174,19 @@ def set_stream(stream):
 
 def launch_count():
     return load_library().slha_b200_launch_count()
+
+
+def timing_begin(max_calls):
+    _check(load_library().slha_b200_timing_begin(max_calls))
+
+
+def timing_end(capacity):
+    """(score_kernel_ms[], merge_kernel_ms[]) of the calls recorded since timing_begin."""
+    a, b = np.zeros(capacity, np.float32), np.zeros(capacity, np.float32)
+    n = C.c_uint32()
+    _check(load_library().slha_b200_timing_end(ptr(a), ptr(b), capacity, C.addressof(n)))
+    m = min(n.value, capacity)
+    return a[:m], b[:m]
 
 
 def synchronize():
@@ -348,16 +364,18 @@ def score_topk(tiles, segments, q_coarse, q_sign, nq, k, out_index=None, out_sco
     return out_index, out_score, out_count
 
 
-def topk_merge(cand_index, cand_score, n_lists, n_queries, k_in, k_out, out_index=None, out_score=None):
-    """Merge per-shard top-k lists laid out [list][query][k_in]."""
+def topk_merge(cand_index, cand_score, n_lists, n_queries, k_in, k_out, out_index=None, out_score=None, list_stride=None):
+    """Merge per-shard top-k lists laid out [list][query][k_in] (list blocks `list_stride` elements apart)."""
     if out_index is None:
         out_index = np.zeros((n_queries, k_out), np.uint32)
     if out_score is None:
         out_score = np.zeros((n_queries, k_out), np.float32)
+    if list_stride is None:
+        list_stride = n_queries * k_in
     _check(
-        load_library().slha_b200_topk_merge(
-            ptr(_np(cand_index, np.uint32)), ptr(_np(cand_score, np.float32)), n_lists, n_queries, k_in, k_out,
-            ptr(out_index), ptr(out_score),
+        load_library().slha_b200_topk_merge_strided(
+            ptr(_np(cand_index, np.uint32)), ptr(_np(cand_score, np.float32)), n_lists, list_stride, n_queries, k_in,
+            k_out, ptr(out_index), ptr(out_score),
         )
     )
     return out_index, out_score

@@ -45,6 +45,20 @@ int32_t slha_b200_set_stream(void* cuda_stream) {
     return SLHA_OK;
 }
 uint64_t slha_b200_launch_count(void) { return launch_count(); }
+int32_t slha_b200_timing_begin(uint32_t max_calls) {
+    return ffi([&]() -> Status {
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        return timing_begin(max_calls);
+    });
+}
+int32_t slha_b200_timing_end(float* score_ms, float* merge_ms, uint32_t capacity, uint32_t* n_out) {
+    return ffi([&]() -> Status {
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        return timing_end(c, score_ms, merge_ms, capacity, n_out);
+    });
+}
 
 int32_t slha_b200_malloc(size_t bytes, void** out) {
     return ffi([&]() -> Status {
@@ -198,16 +212,18 @@ int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment
     });
 }
 
-int32_t slha_b200_topk_merge(const uint32_t* cand_index, const float* cand_score, uint32_t n_lists,
-                             uint32_t n_queries, uint32_t k_in, uint32_t k_out, uint32_t* out_index,
-                             float* out_score) {
+int32_t slha_b200_topk_merge_strided(const uint32_t* cand_index, const float* cand_score, uint32_t n_lists,
+                                     uint64_t list_stride, uint32_t n_queries, uint32_t k_in, uint32_t k_out,
+                                     uint32_t* out_index, float* out_score) {
     return ffi([&]() -> Status {
         if (!cand_index || !cand_score || !out_index || !out_score)
             return Status(SLHA_ERR_NULL, "slha_b200_topk_merge received a NULL pointer");
+        if (list_stride < (uint64_t)n_queries * k_in)
+            return Status(SLHA_ERR_DIMENSION, "list_stride is smaller than n_queries * k_in");
         CallScope cs;
         if (!cs.ok()) return cs.st;
         Ctx* c = cs.c;
-        const size_t nc = (size_t)n_lists * n_queries * k_in;
+        const size_t nc = n_lists ? (size_t)(n_lists - 1) * list_stride + (size_t)n_queries * k_in : 0;
         const uint32_t* di;
         const float* dsc;
         SLHA_TRY(stage_in_t(c, cand_index, nc, &di));
@@ -215,10 +231,16 @@ int32_t slha_b200_topk_merge(const uint32_t* cand_index, const float* cand_score
         std::vector<StagedOut> outs(2);
         SLHA_TRY(stage_out(c, out_index, (size_t)n_queries * k_out * 4, &outs[0]));
         SLHA_TRY(stage_out(c, out_score, (size_t)n_queries * k_out * 4, &outs[1]));
-        SLHA_TRY(launch_topk_merge_pairs(c, di, dsc, n_lists, n_queries, k_in, k_out, (uint32_t*)outs[0].dev,
-                                         (float*)outs[1].dev));
+        SLHA_TRY(launch_topk_merge_pairs(c, di, dsc, n_lists, list_stride, n_queries, k_in, k_out,
+                                         (uint32_t*)outs[0].dev, (float*)outs[1].dev));
         return finish_outputs(c, outs, sync_by_default(c));
     });
+}
+int32_t slha_b200_topk_merge(const uint32_t* cand_index, const float* cand_score, uint32_t n_lists,
+                             uint32_t n_queries, uint32_t k_in, uint32_t k_out, uint32_t* out_index,
+                             float* out_score) {
+    return slha_b200_topk_merge_strided(cand_index, cand_score, n_lists, (uint64_t)n_queries * k_in, n_queries, k_in,
+                                        k_out, out_index, out_score);
 }
 
 // ------------------------------------------------------------------ pool

@@ -106,9 +106,11 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
                          const float* d_q_coarse, const uint64_t* d_q_sign, size_t n_queries,
                          uint32_t k, uint32_t* d_out_index, float* d_out_score,
                          uint32_t* d_out_count);
+Status timing_begin(uint32_t max_calls);
+Status timing_end(Ctx* c, float* score_ms, float* merge_ms, uint32_t capacity, uint32_t* n_out);
 Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* cand_score,
-                               uint32_t n_lists, uint32_t n_queries, uint32_t k_in, uint32_t k_out,
-                               uint32_t* out_index, float* out_score);
+                               uint32_t n_lists, uint64_t list_stride, uint32_t n_queries, uint32_t k_in,
+                               uint32_t k_out, uint32_t* out_index, float* out_score);
 
 Status launch_encode(Ctx* c, const Model* m, const void* d_keys, int key_dtype, size_t n,
                      const uint32_t* d_positions, uint32_t position_base, const uint16_t* d_heads,

@@ -49,6 +49,14 @@ Status launch_score(Ctx* c, int G, const ScoreArgs& a, uint32_t grid, int thread
 
 int group_width(uint32_t nq) { return nq >= 3 ? 4 : (int)nq; }
 
+// Optional per-call CUDA-event timing of the two kernels of score_topk
+// (slha_b200_timing_begin / _end).  Events are recorded on the launching stream.
+struct Timing {
+    std::vector<cudaEvent_t> ev;  // 3 per call: before score, after score, after merge
+    uint32_t max_calls = 0, calls = 0;
+};
+thread_local Timing g_timing;
+
 // The cached decomposition of one score_topk call shape.
 struct Plan {
     std::vector<unsigned char> key;
@@ -230,6 +238,9 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     SLHA_TRY(build_plan(c, segs, n_segs, nq, k, cache));
     Plan* p = cache.get();
     const int nwarps = p->threads / 32;
+    const bool timed = g_timing.calls < g_timing.max_calls;
+    cudaEvent_t* tev = timed ? &g_timing.ev[3 * g_timing.calls] : nullptr;
+    if (timed) SLHA_CUDA(cudaEventRecord(tev[0], c->stream));
     for (const Plan::Class& cl : p->classes) {
         ScoreArgs a{};
         a.tiles = reinterpret_cast<const unsigned char*>(tiles);
@@ -243,6 +254,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.cand_cnt = p->d_cand_cnt;
         SLHA_TRY(launch_score<true>(c, cl.G, a, cl.count, p->threads, score_smem_bytes(cl.G, nwarps, true, p->cap)));
     }
+    if (timed) SLHA_CUDA(cudaEventRecord(tev[1], c->stream));
     CompLists L{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, k};
     const size_t smem = (size_t)p->kp2 * 8 + 260 * 4;
     static thread_local bool configured = false;
@@ -253,17 +265,47 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     topk_merge_kernel<CompLists><<<(uint32_t)nq, 256, smem, c->stream>>>(L, k, p->kp2, d_out_index, d_out_score, d_out_count);
     count_launch();
     SLHA_CUDA(cudaGetLastError());
+    if (timed) {
+        SLHA_CUDA(cudaEventRecord(tev[2], c->stream));
+        ++g_timing.calls;
+    }
+    return Status();
+}
+
+Status timing_begin(uint32_t max_calls) {
+    for (cudaEvent_t e : g_timing.ev) cudaEventDestroy(e);
+    g_timing.ev.assign((size_t)3 * max_calls, nullptr);
+    for (cudaEvent_t& e : g_timing.ev) SLHA_CUDA(cudaEventCreate(&e));
+    g_timing.max_calls = max_calls;
+    g_timing.calls = 0;
+    return Status();
+}
+
+Status timing_end(Ctx* c, float* score_ms, float* merge_ms, uint32_t capacity, uint32_t* n_out) {
+    SLHA_CUDA(cudaStreamSynchronize(c->stream));
+    const uint32_t n = std::min(g_timing.calls, capacity);
+    for (uint32_t i = 0; i < n; ++i) {
+        float a = 0, b = 0;
+        SLHA_CUDA(cudaEventElapsedTime(&a, g_timing.ev[3 * i], g_timing.ev[3 * i + 1]));
+        SLHA_CUDA(cudaEventElapsedTime(&b, g_timing.ev[3 * i + 1], g_timing.ev[3 * i + 2]));
+        if (score_ms) score_ms[i] = a;
+        if (merge_ms) merge_ms[i] = b;
+    }
+    if (n_out) *n_out = g_timing.calls;
+    for (cudaEvent_t e : g_timing.ev) cudaEventDestroy(e);
+    g_timing.ev.clear();
+    g_timing.max_calls = g_timing.calls = 0;
     return Status();
 }
 
 Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* cand_score,
-                               uint32_t n_lists, uint32_t n_queries, uint32_t k_in, uint32_t k_out,
-                               uint32_t* out_index, float* out_score) {
+                               uint32_t n_lists, uint64_t list_stride, uint32_t n_queries, uint32_t k_in,
+                               uint32_t k_out, uint32_t* out_index, float* out_score) {
     if (n_queries == 0) return Status();
     if (k_out == 0 || k_out > 8192) return Status(SLHA_ERR_DIMENSION, "merge: k_out must be in 1..8192");
     uint32_t kp2 = 2;
     while (kp2 < k_out) kp2 <<= 1;
-    PairLists L{cand_index, cand_score, n_lists, n_queries, k_in};
+    PairLists L{cand_index, cand_score, n_lists, n_queries, k_in, list_stride};
     static thread_local bool configured = false;
     if (!configured) {
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));

@@ -25,10 +25,11 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     const uint32_t* idx;
     const float* score;
     uint32_t n_lists, n_queries, k_in;
+    uint64_t list_stride;  // elements between the blocks of consecutive lists
     __device__ uint32_t size(uint32_t) const { return n_lists * k_in; }
     __device__ uint64_t get(uint32_t Q, uint32_t e) const {
         const uint32_t l = e / k_in, j = e % k_in;
-        const size_t o = ((size_t)l * n_queries + Q) * k_in + j;
+        const size_t o = (size_t)l * list_stride + (size_t)Q * k_in + j;
         const uint32_t i = idx[o];
         return i == 0xFFFFFFFFu ? 0ull : make_comp(score[o], i);
     }
