@@ -4,3 +4,4 @@ C ABI.  The compute lives in libslha_b200.so (CUDA); this package is the thin
 host-side mirror of the reference's operator surface."""
 from .api import *  # noqa: F401,F403
 from .api import load_library, LIB_PATH, SIGNATURES  # noqa: F401
+from . import shard  # noqa: F401

@@ -15,6 +15,8 @@
 // the finished scores of one tile.  Scores either go to memory (full mode) or
 // straight into a per-CTA streaming top-k (threshold filter + radix reselect in
 // shared memory); full score vectors are never written in top-k mode.
+#include <cuda_fp16.h>
+
 #include <cfloat>
 #include <cstring>
 #include <vector>
@@ -284,6 +286,13 @@ struct ScoreArgs {
     // `item_tiles` consecutive tiles of one array against the launch's queries
     uint64_t total_tiles;
     uint32_t item_tiles, nq_launch;
+    // hand-over between the tensor-core kernel and the generic kernel: the former
+    // marks work items it cannot decode, the latter (when `retry` is set) runs
+    // only those
+    uint32_t n_items;
+    uint32_t* retry;
+    const uint32_t* cta_begin;    // tensor-core kernel: item range of every persistent CTA
+    unsigned long long* gpivot;   // tensor-core kernel: per query row, shared selection threshold
 };
 
 template <int G, bool TOPK>
@@ -293,6 +302,7 @@ __global__ void __launch_bounds__(256) score_kernel(ScoreArgs a) {
     const int t = lane >> 3, s = lane & 7;
     WorkItem it;
     if (a.items) {
+        if (a.retry && a.retry[blockIdx.x] == 0) return;
         it = a.items[blockIdx.x];
     } else {
         it.tile_begin = (uint64_t)blockIdx.x * a.item_tiles;
@@ -425,5 +435,6 @@ __global__ void __launch_bounds__(256) score_kernel(ScoreArgs a) {
 }  // namespace
 }  // namespace slha
 
+#include "score_mma.cuh"
 #include "score_merge.cuh"
 #include "score_host.cuh"

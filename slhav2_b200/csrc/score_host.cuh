@@ -16,6 +16,11 @@ int env_int(const char* name, int dflt) {
     return (v && *v) ? std::atoi(v) : dflt;
 }
 
+size_t mma_smem_bytes(int nwarps, uint32_t cap) {
+    return (size_t)NF4_LUT_BYTES + (size_t)nwarps * MMA_DEPTH * MMA_SET_BYTES + (size_t)4 * cap * 8 + 4 * 8 +
+           (4 + 2 + 2 + 260) * 4 + 16;
+}
+
 size_t score_smem_bytes(int G, int nwarps, bool topk, uint32_t cap) {
     size_t b = (size_t)G * D_C * 4 + 16 * 32 * 4 + (size_t)nwarps * DEPTH * BLK_BYTES;
     if (topk) b += (size_t)G * cap * 8;
@@ -49,6 +54,13 @@ Status launch_score(Ctx* c, int G, const ScoreArgs& a, uint32_t grid, int thread
 
 int group_width(uint32_t nq) { return nq >= 3 ? 4 : (int)nq; }
 
+// shared-memory candidate slots of the merge kernel for at most `total` candidates per query
+uint32_t merge_cap(uint64_t total, uint32_t kp2) {
+    const uint64_t want = std::max<uint64_t>(kp2, (total + 255) / 256 * 256);
+    return (uint32_t)std::min<uint64_t>(want, std::max<uint32_t>(kp2, 24576));
+}
+size_t merge_smem(uint32_t cap_s) { return (size_t)cap_s * 8 + 8 + 264 * 4; }
+
 // Optional per-call CUDA-event timing of the two kernels of score_topk
 // (slha_b200_timing_begin / _end).  Events are recorded on the launching stream.
 struct Timing {
@@ -70,7 +82,19 @@ struct Plan {
     uint32_t* d_q_list_count = nullptr;
     uint64_t* d_cand_keys = nullptr;
     uint32_t* d_cand_cnt = nullptr;
+    uint32_t* d_retry = nullptr;   // per work item: 1 = the tensor-core kernel handed it back
+    uint32_t* d_cta_begin = nullptr;  // tensor-core kernel: items [cta_begin[b], cta_begin[b+1]) belong to CTA b
+    unsigned long long* d_gpivot = nullptr;  // per query: best selection threshold any CTA has proven so far
+    uint32_t n_items = 0;
+    uint32_t max_parts = 1;  // most candidate lists any query has
+    bool use_mma = false;
+    int mma_threads = 256;
+    uint32_t mma_cap = 0, mma_grid = 0;
+    size_t mma_smem = 0;
     ~Plan() {
+        cudaFree(d_retry);
+        cudaFree(d_cta_begin);
+        cudaFree(d_gpivot);
         cudaFree(d_items);
         cudaFree(d_q_list_begin);
         cudaFree(d_q_list_count);
@@ -104,8 +128,27 @@ Status build_plan(Ctx* c, const SlhaB200Segment* segs, size_t n_segs, size_t nq,
         return Status(SLHA_ERR_CAPACITY, "top-k: k is too large for the shared-memory selection state");
     p->cap = cap;
 
-    // item size: large enough that candidate traffic stays a few percent of the
-    // tile stream, small enough to balance 148 SMs
+    // tensor-core kernel: persistent CTAs (one per SM unless shared memory allows more)
+    p->mma_threads = env_int("SLHA_B200_MMA_THREADS", 512);
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
+    {
+        const int mw = p->mma_threads / 32;
+        const uint32_t mround = (uint32_t)mw * 2 * MMA_SET_TILES;  // appends that may follow a raised flag
+        uint32_t mcap = std::max<uint32_t>(3 * k, k + 4 * mround);
+        while (mcap > k + 2 * mround && mma_smem_bytes(mw, mcap) > MAX_SMEM) mcap -= 256;
+        p->use_mma = env_int("SLHA_B200_SCORE_IMPL", 1) != 0 && mma_smem_bytes(mw, mcap) <= MAX_SMEM;
+        p->mma_cap = mcap;
+        p->mma_smem = mma_smem_bytes(mw, mcap);
+        const uint32_t per_sm = (uint32_t)std::max<size_t>(1, MAX_SMEM / (p->mma_smem + 1024));
+        p->mma_grid = (uint32_t)sms * per_sm;
+    }
+
+    // Work items.  Generic kernel: fixed-size runs, large enough that candidate
+    // traffic stays a few percent of the tile stream and small enough to balance
+    // the SMs through the hardware CTA scheduler.  Tensor-core kernel: the
+    // concatenated tile stream is cut into one equal share per persistent CTA
+    // (and at segment ends), so per-item costs are paid once per ~total/grid tiles.
     uint64_t total = 0;
     for (size_t i = 0; i < n_segs; ++i) total += (uint64_t)segs[i].n_tiles * ((segs[i].n_queries + 3) / 4);
     uint32_t item_tiles = (uint32_t)env_int("SLHA_B200_ITEM_TILES", 0);
@@ -114,18 +157,40 @@ Status build_plan(Ctx* c, const SlhaB200Segment* segs, size_t n_segs, size_t nq,
         while (item_tiles > 2048 && total / item_tiles < 592) item_tiles /= 2;
     }
     item_tiles = std::max(round, (item_tiles + round - 1) / round * round);
+    uint64_t share = (total + p->mma_grid - 1) / std::max<uint32_t>(p->mma_grid, 1);
+    share = std::max<uint64_t>(2048, (share + MMA_SET_TILES - 1) / MMA_SET_TILES * MMA_SET_TILES);
+    uint64_t filled = 0;  // tiles already given to the current CTA (tensor-core mode)
+    std::vector<uint32_t> cta_begin(1, 0);
 
-    std::vector<WorkItem> items[3];  // by class G = 1, 2, 4
+    std::vector<WorkItem> items[3];  // by class G = 1, 2, 4 (generic mode); all in [2] in tensor-core mode
     std::vector<uint32_t> q_begin(nq, 0), q_count(nq, 0);
     uint32_t n_lists = 0;
     for (size_t i = 0; i < n_segs; ++i) {
         const SlhaB200Segment& s = segs[i];
         if ((uint64_t)s.query_begin + s.n_queries > nq)
             return Status(SLHA_ERR_DIMENSION, "segment query range exceeds n_queries");
-        const uint32_t parts = s.n_tiles ? (s.n_tiles + item_tiles - 1) / item_tiles : 0;
         for (uint32_t q0 = 0; q0 < s.n_queries; q0 += 4) {
             const uint32_t gq = std::min<uint32_t>(4, s.n_queries - q0);
             const int G = group_width(gq);
+            // cut points of this (segment, query group) stream
+            std::vector<std::pair<uint32_t, uint32_t>> cuts;  // (offset, length)
+            for (uint32_t pos = 0; pos < s.n_tiles;) {
+                uint32_t take;
+                if (p->use_mma) {
+                    take = (uint32_t)std::min<uint64_t>(s.n_tiles - pos, share - filled);
+                    filled += take;
+                } else {
+                    take = std::min<uint32_t>(item_tiles, s.n_tiles - pos);
+                }
+                cuts.push_back({pos, take});
+                pos += take;
+                if (p->use_mma && filled == share) {
+                    filled = 0;
+                    cta_begin.push_back((uint32_t)items[2].size() + (uint32_t)cuts.size());
+                }
+            }
+            const uint32_t parts = (uint32_t)cuts.size();
+            p->max_parts = std::max(p->max_parts, parts);
             for (uint32_t g = 0; g < gq; ++g) {
                 const uint32_t Q = s.query_begin + q0 + g;
                 if (q_count[Q]) return Status(SLHA_ERR_DIMENSION, "a query row belongs to two segments");
@@ -134,14 +199,14 @@ Status build_plan(Ctx* c, const SlhaB200Segment* segs, size_t n_segs, size_t nq,
             }
             for (uint32_t part = 0; part < parts; ++part) {
                 WorkItem w;
-                w.tile_begin = s.tile_begin + (uint64_t)part * item_tiles;
-                w.n_tiles = std::min<uint32_t>(item_tiles, s.n_tiles - part * item_tiles);
-                w.index_base = s.index_base + part * item_tiles;
+                w.tile_begin = s.tile_begin + cuts[part].first;
+                w.n_tiles = cuts[part].second;
+                w.index_base = s.index_base + cuts[part].first;
                 w.query_begin = s.query_begin + q0;
                 w.n_queries = gq;
                 w.list_begin = n_lists + part * gq;
                 w.pad = gq;  // list stride between parts, used by the merge accessor
-                items[G == 1 ? 0 : (G == 2 ? 1 : 2)].push_back(w);
+                items[p->use_mma ? 2 : (G == 1 ? 0 : (G == 2 ? 1 : 2))].push_back(w);
             }
             n_lists += parts * gq;
         }
@@ -153,6 +218,9 @@ Status build_plan(Ctx* c, const SlhaB200Segment* segs, size_t n_segs, size_t nq,
         p->classes.push_back({cls == 0 ? 1 : (cls == 1 ? 2 : 4), (uint32_t)all.size(), (uint32_t)items[cls].size()});
         all.insert(all.end(), items[cls].begin(), items[cls].end());
     }
+    if (cta_begin.back() != (uint32_t)all.size()) cta_begin.push_back((uint32_t)all.size());
+    if (all.empty()) p->use_mma = false;
+    p->mma_grid = (uint32_t)cta_begin.size() - 1;
     // per query: list id of part p is q_begin + p * stride; store stride in the count's high bits
     std::vector<uint32_t> q_stride(nq, 1);
     for (const WorkItem& w : all)
@@ -162,6 +230,11 @@ Status build_plan(Ctx* c, const SlhaB200Segment* segs, size_t n_segs, size_t nq,
     SLHA_CUDA(cudaMalloc(&p->d_q_list_count, std::max<size_t>(1, nq) * 4));
     SLHA_CUDA(cudaMalloc(&p->d_cand_keys, std::max<size_t>(1, (size_t)n_lists * k) * 8));
     SLHA_CUDA(cudaMalloc(&p->d_cand_cnt, std::max<size_t>(1, n_lists) * 4));
+    SLHA_CUDA(cudaMalloc(&p->d_retry, std::max<size_t>(1, all.size()) * 4));
+    p->n_items = (uint32_t)all.size();
+    SLHA_CUDA(cudaMalloc(&p->d_cta_begin, cta_begin.size() * 4));
+    SLHA_CUDA(cudaMalloc(&p->d_gpivot, std::max<size_t>(1, nq) * 8));
+    SLHA_CUDA(cudaMemcpyAsync(p->d_cta_begin, cta_begin.data(), cta_begin.size() * 4, cudaMemcpyHostToDevice, c->stream));
     for (size_t Q = 0; Q < nq; ++Q) q_count[Q] |= q_stride[Q] << 24;
     SLHA_CUDA(cudaMemcpyAsync(p->d_items, all.data(), all.size() * sizeof(WorkItem), cudaMemcpyHostToDevice, c->stream));
     SLHA_CUDA(cudaMemcpyAsync(p->d_q_list_begin, q_begin.data(), nq * 4, cudaMemcpyHostToDevice, c->stream));
@@ -231,7 +304,7 @@ Status launch_score_full(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
 Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* state,
                          const SlhaB200Segment* segs, size_t n_segs, const float* d_q_coarse,
                          const uint64_t* d_q_sign, size_t nq, uint32_t k, uint32_t* d_out_index,
-                         float* d_out_score, uint32_t* d_out_count) {
+                         float* d_out_score, uint32_t* d_out_count, bool prefer_generic) {
     if (nq == 0) return Status();
     if (k == 0 || k > 8192) return Status(SLHA_ERR_DIMENSION, "top-k: k must be in 1..8192");
     static thread_local std::unique_ptr<Plan> cache;
@@ -241,8 +314,36 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     const bool timed = g_timing.calls < g_timing.max_calls;
     cudaEvent_t* tev = timed ? &g_timing.ev[3 * g_timing.calls] : nullptr;
     if (timed) SLHA_CUDA(cudaEventRecord(tev[0], c->stream));
+    const bool mma = p->use_mma && !prefer_generic;
+    if (mma) {
+        SLHA_CUDA(cudaMemsetAsync(p->d_retry, 0, (size_t)p->n_items * 4, c->stream));
+        SLHA_CUDA(cudaMemsetAsync(p->d_gpivot, 0, nq * 8, c->stream));
+        ScoreArgs a{};
+        a.tiles = reinterpret_cast<const unsigned char*>(tiles);
+        a.state = state;
+        a.items = p->d_items;
+        a.n_items = p->n_items;
+        a.retry = p->d_retry;
+        a.cta_begin = p->d_cta_begin;
+        a.gpivot = p->d_gpivot;
+        a.q_coarse = d_q_coarse;
+        a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);
+        a.k = k;
+        a.cap = p->mma_cap;
+        a.cand_keys = p->d_cand_keys;
+        a.cand_cnt = p->d_cand_cnt;
+        static thread_local bool mma_configured = false;
+        if (!mma_configured) {
+            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            mma_configured = true;
+        }
+        score_mma_kernel<true><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a);
+        count_launch();
+        SLHA_CUDA(cudaGetLastError());
+    }
     for (const Plan::Class& cl : p->classes) {
         ScoreArgs a{};
+        a.retry = mma ? p->d_retry + cl.first : nullptr;
         a.tiles = reinterpret_cast<const unsigned char*>(tiles);
         a.state = state;
         a.items = p->d_items + cl.first;
@@ -256,13 +357,14 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     }
     if (timed) SLHA_CUDA(cudaEventRecord(tev[1], c->stream));
     CompLists L{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, k};
-    const size_t smem = (size_t)p->kp2 * 8 + 260 * 4;
+    const uint32_t cap_s = merge_cap(p->max_parts * k, p->kp2);
+    const size_t smem = merge_smem(cap_s);
     static thread_local bool configured = false;
     if (!configured) {
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<CompLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
         configured = true;
     }
-    topk_merge_kernel<CompLists><<<(uint32_t)nq, 256, smem, c->stream>>>(L, k, p->kp2, d_out_index, d_out_score, d_out_count);
+    topk_merge_kernel<CompLists><<<(uint32_t)nq, cap_s > 4096 ? 512 : 256, smem, c->stream>>>(L, k, p->kp2, cap_s, d_out_index, d_out_score, d_out_count);
     count_launch();
     SLHA_CUDA(cudaGetLastError());
     if (timed) {
@@ -311,7 +413,8 @@ Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* 
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
         configured = true;
     }
-    topk_merge_kernel<PairLists><<<n_queries, 256, (size_t)kp2 * 8 + 260 * 4, c->stream>>>(L, k_out, kp2, out_index, out_score, nullptr);
+    const uint32_t cap_s = merge_cap(n_lists * k_in, kp2);
+    topk_merge_kernel<PairLists><<<n_queries, cap_s > 4096 ? 512 : 256, merge_smem(cap_s), c->stream>>>(L, k_out, kp2, cap_s, out_index, out_score, nullptr);
     count_launch();
     SLHA_CUDA(cudaGetLastError());
     return Status();

@@ -16,6 +16,13 @@ struct CompLists {  // lists written by score_kernel
     const uint32_t* q_list_count;  // [nq]: parts in bits 0..23, list stride between parts in bits 24..31
     uint32_t k;
     __device__ uint32_t size(uint32_t Q) const { return (q_list_count[Q] & 0xFFFFFFu) * k; }
+    __device__ uint32_t lists(uint32_t Q) const { return q_list_count[Q] & 0xFFFFFFu; }
+    __device__ uint32_t list_len(uint32_t Q, uint32_t part) const {
+        return cnt[q_list_begin[Q] + part * (q_list_count[Q] >> 24)];
+    }
+    __device__ uint64_t at(uint32_t Q, uint32_t part, uint32_t j) const {
+        return keys[(size_t)(q_list_begin[Q] + part * (q_list_count[Q] >> 24)) * k + j];
+    }
     __device__ uint64_t get(uint32_t Q, uint32_t e) const {
         const uint32_t l = q_list_begin[Q] + (e / k) * (q_list_count[Q] >> 24), j = e % k;
         return j < cnt[l] ? keys[(size_t)l * k + j] : 0ull;
@@ -27,6 +34,13 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     uint32_t n_lists, n_queries, k_in;
     uint64_t list_stride;  // elements between the blocks of consecutive lists
     __device__ uint32_t size(uint32_t) const { return n_lists * k_in; }
+    __device__ uint32_t lists(uint32_t) const { return n_lists; }
+    __device__ uint32_t list_len(uint32_t, uint32_t) const { return k_in; }
+    __device__ uint64_t at(uint32_t Q, uint32_t part, uint32_t j) const {
+        const size_t o = (size_t)part * list_stride + (size_t)Q * k_in + j;
+        const uint32_t i = idx[o];
+        return i == 0xFFFFFFFFu ? 0ull : make_comp(score[o], i);
+    }
     __device__ uint64_t get(uint32_t Q, uint32_t e) const {
         const uint32_t l = e / k_in, j = e % k_in;
         const size_t o = (size_t)l * list_stride + (size_t)Q * k_in + j;
@@ -35,15 +49,74 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     }
 };
 
+// Sort buf[0..kp2) descending (bitonic, kp2 a power of two) and write the k outputs of query Q.
+__device__ void sort_and_emit(uint64_t* buf, uint32_t kp2, uint32_t m, uint32_t k, uint32_t Q,
+                              uint32_t* out_index, float* out_score, uint32_t* out_count) {
+    const uint32_t tid = threadIdx.x, nt = blockDim.x;
+    for (uint32_t size = 2; size <= kp2; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride; stride >>= 1) {
+            for (uint32_t i = tid; i < kp2 / 2; i += nt) {
+                const uint32_t lo = 2 * i - (i & (stride - 1));
+                const uint32_t hi = lo + stride;
+                const bool desc = (lo & size) == 0;
+                const uint64_t x = buf[lo], y = buf[hi];
+                if ((x < y) == desc) { buf[lo] = y; buf[hi] = x; }
+            }
+            __syncthreads();
+        }
+    }
+    for (uint32_t r = tid; r < k; r += nt) {
+        const bool v = r < m;
+        const uint64_t key = v ? buf[r] : 0ull;
+        out_index[(size_t)Q * k + r] = v ? 0xFFFFFFFFu - (uint32_t)key : 0xFFFFFFFFu;
+        out_score[(size_t)Q * k + r] = v ? key_score((uint32_t)(key >> 32)) : -INFINITY;
+    }
+    if (out_count && tid == 0) out_count[Q] = m;
+}
+
+// cap_s: candidate slots of the shared-memory buffer (>= kp2).  When the query's
+// candidates fit they are gathered once and selected / sorted in shared memory;
+// otherwise the radix select runs over global memory.
 template <typename Lists>
-__global__ void __launch_bounds__(256) topk_merge_kernel(Lists L, uint32_t k, uint32_t kp2,
+__global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, uint32_t kp2, uint32_t cap_s,
                                                          uint32_t* out_index, float* out_score,
                                                          uint32_t* out_count) {
     extern __shared__ __align__(16) unsigned char smem[];
-    uint64_t* buf = reinterpret_cast<uint64_t*>(smem);  // [kp2]
-    int* hist = reinterpret_cast<int*>(buf + kp2);      // 260
+    uint64_t* buf = reinterpret_cast<uint64_t*>(smem);  // [cap_s]
+    uint64_t* pivot_s = buf + cap_s;                    // [1]
+    int* hist = reinterpret_cast<int*>(pivot_s + 1);    // 260 (+2)
+    int* n_s = hist + 260;
     const uint32_t Q = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const uint32_t T = L.size(Q);
+
+    // upper bound of the number of candidates
+    uint32_t total = 0;
+    for (uint32_t l = 0; l < L.lists(Q); ++l) total += L.list_len(Q, l);
+    if (total <= cap_s) {
+        if (tid == 0) *n_s = 0;
+        __syncthreads();
+        for (uint32_t l = 0; l < L.lists(Q); ++l) {
+            const uint32_t len = L.list_len(Q, l);
+            for (uint32_t j0 = 0; j0 < len; j0 += nt) {
+                const uint32_t j = j0 + tid;
+                const uint64_t key = j < len ? L.at(Q, l, j) : 0ull;
+                const unsigned bal = __ballot_sync(0xFFFFFFFFu, key != 0ull);
+                int base = 0;
+                if ((tid & 31) == 0 && bal) base = atomicAdd(n_s, __popc(bal));
+                base = __shfl_sync(0xFFFFFFFFu, base, 0);
+                if (key) buf[base + __popc(bal & ((1u << (tid & 31)) - 1))] = key;
+            }
+        }
+        __syncthreads();
+        const uint32_t present = (uint32_t)*n_s;
+        __syncthreads();
+        if (present > k) block_select_topk(buf, n_s, k, pivot_s, hist);
+        const uint32_t m = present < k ? present : k;
+        for (uint32_t i = m + tid; i < kp2; i += nt) buf[i] = 0ull;
+        __syncthreads();
+        sort_and_emit(buf, kp2, m, k, Q, out_index, out_score, out_count);
+        return;
+    }
 
     // number of present candidates
     if (tid == 0) hist[259] = 0;
@@ -115,25 +188,7 @@ __global__ void __launch_bounds__(256) topk_merge_kernel(Lists L, uint32_t k, ui
         if (key >= pivot && key) buf[atomicAdd(&hist[259], 1)] = key;
     }
     __syncthreads();
-    for (uint32_t size = 2; size <= kp2; size <<= 1) {
-        for (uint32_t stride = size >> 1; stride; stride >>= 1) {
-            for (uint32_t i = tid; i < kp2 / 2; i += nt) {
-                const uint32_t lo = 2 * i - (i & (stride - 1));
-                const uint32_t hi = lo + stride;
-                const bool desc = (lo & size) == 0;
-                const uint64_t x = buf[lo], y = buf[hi];
-                if ((x < y) == desc) { buf[lo] = y; buf[hi] = x; }
-            }
-            __syncthreads();
-        }
-    }
-    for (uint32_t r = tid; r < k; r += nt) {
-        const bool v = r < m;
-        const uint64_t key = v ? buf[r] : 0ull;
-        out_index[(size_t)Q * k + r] = v ? 0xFFFFFFFFu - (uint32_t)key : 0xFFFFFFFFu;
-        out_score[(size_t)Q * k + r] = v ? key_score((uint32_t)(key >> 32)) : -INFINITY;
-    }
-    if (out_count && tid == 0) out_count[Q] = m;
+    sort_and_emit(buf, kp2, m, k, Q, out_index, out_score, out_count);
 }
 
 }  // namespace

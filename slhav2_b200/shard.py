@@ -1,0 +1,86 @@
+"""Token-range sharding of a tile context over the GPUs of one node.
+
+Every rank owns a contiguous token range of every KV head, scores only its own
+tiles (resident in its own HBM) and keeps its own top-k per query head; the
+per-rank candidates are exchanged with ONE all-gather and merged by every rank
+with the same deterministic rule (score descending, ties towards the lower
+global index).  The reference has no multi-device path; the per-tile
+independence this relies on is ElasticKvCache::score_all
+(scirust/src/ccos.rs:346-355).
+
+The collective is torch.distributed's (NCCL on GPUs, gloo in the CPU tests);
+local scoring and the merge are the C-ABI calls slha_b200_score_topk and
+slha_b200_topk_merge_strided.
+"""
+import numpy as np
+
+from . import api
+
+
+def shard_range(total_tokens, rank, world):
+    """Contiguous token range [start, start+count) of `rank`; ranges differ by at most one token."""
+    base, rem = divmod(total_tokens, world)
+    start = rank * base + min(rank, rem)
+    return start, base + (1 if rank < rem else 0)
+
+
+def shard_segments(n_layers, kv_heads, tokens_local, group, position_base):
+    """Segment table of one rank: tiles laid out [layer][kv_head][token]; the
+    queries of (layer, kv_head) are rows (layer*kv_heads + kv_head)*group + g.
+    Reported indices are global token positions (position_base + local token)."""
+    rows = []
+    for l in range(n_layers):
+        for h in range(kv_heads):
+            s = l * kv_heads + h
+            rows.append((s * tokens_local, tokens_local, s * group, group, position_base))
+    return api.make_segments(rows)
+
+
+class ShardedScorer:
+    """One decode-step scorer of a rank.
+
+    Buffers (anything with data_ptr(), int32 storage):
+      cand     [2][nq][k]         this rank's indices, then score bits
+      gathered [world][2][nq][k]  every rank's block after the all-gather
+      out      [2][nq][k]         merged indices, then score bits
+    """
+
+    def __init__(self, world, nq, k, cand, gathered, out, all_gather, count=None):
+        self.world, self.nq, self.k = world, nq, k
+        self.cand, self.gathered, self.out, self.count = cand, gathered, out, count
+        self.all_gather = all_gather  # callable(gathered, cand)
+        self.block = 2 * nq * k       # int32 elements per rank in `gathered`
+
+    # the two device steps; the CPU tests substitute checker implementations
+    def local_topk(self, tiles, segments, q_coarse, q_sign):
+        api.score_topk(tiles, segments, q_coarse, q_sign, self.nq, self.k, out_index=self.cand[0], out_score=self.cand[1],
+                       out_count=self.count)
+
+    def merge(self, out_index=None, out_score=None):
+        api.topk_merge(self.gathered, self.gathered[0][1], self.world, self.nq, self.k, self.k,
+                       out_index=self.out[0] if out_index is None else out_index,
+                       out_score=self.out[1] if out_score is None else out_score, list_stride=self.block)
+
+    def step(self, tiles, segments, q_coarse, q_sign, out_index=None, out_score=None):
+        self.local_topk(tiles, segments, q_coarse, q_sign)
+        if self.world == 1:
+            return self.cand
+        self.all_gather(self.gathered, self.cand)
+        self.merge(out_index, out_score)
+        return self.out
+
+
+def merge_reference(gathered_index, gathered_score, k):
+    """numpy statement of the merge rule for [world][nq][k] candidate blocks
+    (index 0xFFFFFFFF = absent): used by the CPU tests as the checker."""
+    world, nq, kin = gathered_index.shape
+    oi = np.full((nq, k), 0xFFFFFFFF, np.uint32)
+    osc = np.full((nq, k), -np.inf, np.float32)
+    for j in range(nq):
+        idx = gathered_index[:, j, :].reshape(-1)
+        sc = gathered_score[:, j, :].reshape(-1)
+        keep = idx != 0xFFFFFFFF
+        idx, sc = idx[keep], sc[keep]
+        order = np.lexsort((idx, -sc.astype(np.float64)))[:k]
+        oi[j, : len(order)], osc[j, : len(order)] = idx[order], sc[order]
+    return oi, osc

@@ -89,3 +89,58 @@ def test_topk_merge_of_shard_lists():
     cs = np.stack([a[1], b[1]])
     mi, ms = S.topk_merge(ci, cs, 2, nq, k, k)
     assert np.array_equal(mi, full[0]) and np.array_equal(ms, full[1])
+
+
+def test_merge_with_more_candidates_than_the_shared_buffer():
+    # 8 lists x 4096 candidates per query exceeds the in-shared-memory path
+    rng = np.random.default_rng(3)
+    n_lists, nq, k_in, k_out = 8, 3, 4096, 2048
+    sc = rng.standard_normal((n_lists, nq, k_in)).astype(F)
+    idx = rng.permutation(n_lists * nq * k_in).astype(np.uint32).reshape(n_lists, nq, k_in)
+    idx[2, 1, 100:] = 0xFFFFFFFF  # a short list
+    mi, ms = S.topk_merge(idx, sc, n_lists, nq, k_in, k_out)
+    from slhav2_b200 import shard
+
+    wi, ws = shard.merge_reference(idx, sc, k_out)
+    assert np.array_equal(mi, wi) and np.array_equal(ms, ws)
+
+
+def test_long_segment_many_items_shares_thresholds():
+    # one long segment scanned by many CTAs (config-5 shape at reduced length)
+    n, k, nq = 300000, 2048, 4
+    base = H.random_tiles(5000, 6, seed=11)
+    tiles = np.tile(base, n // 5000)
+    tiles["dynamic_lambda"] *= (1 + np.random.default_rng(1).random(n)).astype(F)
+    qc, qs = H.random_queries(nq, 12)
+    dt = S.to_device(tiles)
+    segs = [(0, n, 0, nq, 7)]
+    gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, nq, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+
+
+def test_generic_kernel_only_mode_matches():
+    # SLHA_B200_SCORE_IMPL=0 disables the tensor-core kernel: same answers from the generic one
+    import subprocess
+    import sys
+    import os
+
+    code = (
+        "import numpy as np, slhav2_b200 as S\n"
+        "from tests import helpers as H\n"
+        "t = H.random_tiles(20000, 2, seed=4); qc, qs = H.random_queries(4, 5)\n"
+        "d = S.to_device(t)\n"
+        "i, s, c = S.score_topk(d, S.make_segments([(0, 20000, 0, 4, 0)]), qc, qs, 4, 256)\n"
+        "np.save(sys.argv[1] if False else __import__('sys').argv[1], np.concatenate([i.astype(np.float64), s.astype(np.float64)]))\n"
+    )
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    outs = []
+    for impl in ("0", "1"):
+        path = os.path.join(root, "gpurun_out", "impl%s.npy" % impl)
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        env = dict(os.environ, SLHA_B200_SCORE_IMPL=impl, PYTHONPATH=root)
+        subprocess.check_call([sys.executable, "-c", code, path], env=env, cwd=root)
+        outs.append(np.load(path))
+    i0, s0 = outs[0][:4], outs[0][4:]
+    i1, s1 = outs[1][:4], outs[1][4:]
+    assert np.all(np.abs(s0 - s1) <= 1e-3)
+    assert np.mean(i0 == i1) > 0.98
