@@ -22,9 +22,8 @@ reference's vectorised compute_score (oracle/) on the host cores instead.
 import argparse
 import json
 import os
-import subprocess
 import sys
-import tempfile
+import threading
 import time
 
 import numpy as np
@@ -86,53 +85,67 @@ def synth_keys_numpy(seed, n_heads, tokens, pos0):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+    """SM clock and throttle reasons sampled through NVML (read-only) in a
+    background thread while the timed region runs."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    def __init__(self, gpu_index, period_s=0.02):
+        self.gpu, self.period = gpu_index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
 
-    def __init__(self, gpu_index):
-        self.gpu, self.proc, self.path = gpu_index, None, None
+    def _run(self):
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            uuid = None
+            try:
+                import torch
+
+                uuid = str(torch.cuda.get_device_properties(self.gpu).uuid)
+            except Exception:
+                pass
+            h = None
+            if uuid:
+                for cand in ("GPU-" + uuid, uuid):
+                    try:
+                        h = nv.nvmlDeviceGetHandleByUUID(cand.encode() if isinstance(cand, str) else cand)
+                        break
+                    except Exception:
+                        h = None
+            if h is None:
+                h = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            names = {
+                "hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap,
+            }
+            while not self._stop.is_set():
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+                time.sleep(self.period)
+        except Exception as e:  # no NVML: report nothing rather than fail the bench
+            self.error = repr(e)
 
     def start(self):
-        try:
-            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
-            self.path = f.name
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=f, stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        try:
-            for line in open(self.path):
-                p = [x.strip() for x in line.split(",")]
-                if len(p) < 9:
-                    continue
-                try:
-                    sm.append(float(p[1]))
-                    mx.append(float(p[2]))
-                except ValueError:
-                    continue
-                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
-                    if v.lower().startswith("active"):
-                        reasons.add(name)
-            os.unlink(self.path)
-        except Exception:
-            pass
-        if sm:
-            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(mx)), reasons=sorted(reasons), samples=len(sm))
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=5)
+        out = {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        if self.samples:
+            out["sm_mhz"] = float(np.median(self.samples))
+        if getattr(self, "error", None):
+            out["error"] = self.error
         return out
 
 
@@ -207,8 +220,10 @@ def build_shard(S, torch, w, rank, world, dev):
     """Generate this rank's keys on the device, encode them into tiles, prepare the queries.
     Returns (tiles_u8, segments, q_coarse, q_sign, n_tiles, encode_tiles_per_s)."""
     L, H, G = w["layers"], w["kv_heads"], w["group"]
-    T = w["tokens"] if w["scaling"] == "weak" else w["tokens"] // world
-    pos0 = rank * T
+    if w["scaling"] == "weak":
+        T, pos0 = w["tokens"], rank * w["tokens"]
+    else:
+        pos0, T = S.shard.shard_range(w["tokens"], rank, world)
     n_tiles = L * H * T
     tiles = torch.empty(n_tiles * 128, dtype=torch.uint8, device=dev)
     nq = L * H * G
@@ -221,7 +236,6 @@ def build_shard(S, torch, w, rank, world, dev):
     cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
     positions = torch.arange(pos0, pos0 + T, device=dev, dtype=torch.int32).repeat(H).contiguous()
     heads = torch.arange(H, device=dev, dtype=torch.int16).repeat_interleave(T).contiguous()
-    segs = []
     enc_ms = 0.0
     chunk_tokens = min(T, 131072)
     for l in range(L):
@@ -244,13 +258,12 @@ def build_shard(S, torch, w, rank, world, dev):
                 e1.record()
                 torch.cuda.synchronize()
                 enc_ms += e0.elapsed_time(e1)
-            segs.append(((l * H + h) * T, T, (l * H + h) * G, G, pos0))
         gen.manual_seed(99 + l)  # queries are the same on every rank
         q = torch.randn(H * G, HEAD_DIM, generator=gen, device=dev)
         model.prepare_queries(q, nq=H * G, q_coarse_out=q_coarse[l * H * G:(l + 1) * H * G], q_sign_out=q_sign[l * H * G:(l + 1) * H * G])
         torch.cuda.synchronize()
         model.release()
-    return tiles, S.make_segments(segs), q_coarse, q_sign, n_tiles, n_tiles / (enc_ms * 1e-3)
+    return tiles, S.shard.shard_segments(L, H, T, G, pos0), q_coarse, q_sign, n_tiles, n_tiles / (enc_ms * 1e-3)
 
 
 def gpu_arm(args, w):
@@ -283,11 +296,11 @@ def gpu_arm(args, w):
     gathered = torch.empty(world, 2, nq, k, dtype=torch.int32, device=dev) if world > 1 else None
     out = torch.empty(2, nq, k, dtype=torch.int32, device=dev)
 
+    scorer = S.shard.ShardedScorer(world, nq, k, cand, gathered, out,
+                                   (lambda g, c: dist.all_gather_into_tensor(g, c)) if world > 1 else None, count=cnt)
+
     def step():
-        S.score_topk(tiles, segs, q_coarse, q_sign, nq, k, out_index=cand[0], out_score=cand[1], out_count=cnt)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, cand)
-            S.topk_merge(gathered, gathered[0, 1], world, nq, k, k, out_index=out[0], out_score=out[1], list_stride=2 * nq * k)
+        scorer.step(tiles, segs, q_coarse, q_sign)
 
     def barrier():
         if world > 1:
@@ -327,9 +340,7 @@ def gpu_arm(args, w):
         if world == 1:
             S.score_topk(tiles, segs, hq, hs, nq, k, out_index=h_idx, out_score=h_sc, out_count=h_cnt)
         else:
-            S.score_topk(tiles, segs, hq, hs, nq, k, out_index=cand[0], out_score=cand[1], out_count=cnt)
-            dist.all_gather_into_tensor(gathered, cand)
-            S.topk_merge(gathered, gathered[0, 1], world, nq, k, k, out_index=h_idx, out_score=h_sc, list_stride=2 * nq * k)
+            scorer.step(tiles, segs, hq, hs, out_index=h_idx, out_score=h_sc)
 
     for _ in range(3):
         e2e_step()
@@ -397,8 +408,8 @@ def gpu_arm(args, w):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     args = ap.parse_args()
