@@ -88,7 +88,7 @@ class ClockSampler:
     """SM clock and throttle reasons sampled through NVML (read-only) in a
     background thread while the timed region runs."""
 
-    def __init__(self, gpu_index, period_s=0.02):
+    def __init__(self, gpu_index, period_s=0.005):
         self.gpu, self.period = gpu_index, period_s
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
@@ -375,7 +375,7 @@ def gpu_arm(args, w):
         "vs_baseline": None, "dtype": "int4->f32", "data": "synthetic", "config": workload_config(w, world),
         "scores_per_s": value * w["group"],
         "hbm_gbs_whole_step": total_tiles * 128 / (ms_step * 1e-3) / 1e9,
-        "roofline": {"bound": "hbm", "kernel": "score_kernel<4,topk>", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "roofline": {"bound": "hbm", "kernel": "score_mma_kernel (fused score + top-k)", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
                      "kernel_ms": k_ms, "merge_kernel_ms": float(np.mean(merge_ms)) if len(merge_ms) else None,
                      "algorithmic_bytes_per_launch": n_tiles * 128, "traffic": None},
