@@ -235,6 +235,41 @@ int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment
                              uint32_t* out_count);
 
 /*
+ * slha_b200_score_topk for callers that must not allocate.  It has no
+ * counterpart in the reference.
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits -- a decode loop
+ * inside a latency budget that cannot absorb an allocation (cudaMalloc takes
+ * a device-wide lock and may synchronise), an inference server whose memory
+ * pool owns every byte of HBM so that a stray allocation fails or fragments
+ * it, or a host thread that is forbidden to enter the allocator.  The regular
+ * entry point sizes its work lists and candidate buffers per call shape and
+ * obtains them with cudaMalloc; this one keeps them in one fixed array that
+ * lives inside the library.
+ *
+ * Same arguments and results as slha_b200_score_topk, except:
+ *  - tiles, q_coarse, q_sign and the three outputs must be device memory,
+ *    segments must be host memory (nothing is staged);
+ *  - limits of the fixed array (4 MiB + 22 KiB per GPU, held from library load
+ *    until the process exits): k <= 1024, n_queries <= 256, at most 96
+ *    segments (more may fit when they are short), 512 work items / candidate
+ *    lists in total.  A call beyond them fails with SLHA_ERR_CAPACITY and says
+ *    which limit it hit;
+ *  - the first call on each device resolves the array's device address and
+ *    raises the kernels' shared-memory limit; make that first call outside any
+ *    stream capture;
+ *  - all calls on a device share the array, which keeps what the previous call
+ *    left in it; a call overwrites everything it later reads, so back-to-back
+ *    calls on one stream are safe, but two calls that overlap on the GPU
+ *    (different streams or threads without ordering) race on it.
+ * It calls no cudaMalloc / cudaFree and no allocating library routine.
+ */
+int32_t slha_b200_score_topk_noalloc(const SciRustSlhaTile* tiles, const SlhaB200Segment* segments,
+                                     size_t n_segments, const float* q_coarse, const uint64_t* q_sign,
+                                     size_t n_queries, uint32_t k, uint32_t* out_index,
+                                     float* out_score, uint32_t* out_count);
+
+/*
  * Merge n_lists candidate lists per query (layout [list][query][k_in], as an
  * all-gather of per-shard slha_b200_score_topk outputs produces) into the
  * global top k_out per query with the same ordering rule.  Device pointers.

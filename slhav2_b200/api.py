@@ -84,6 +84,7 @@ SIGNATURES = {
     "slha_b200_prepare_queries": (_i32, [_vp, _vp, _sz, _vp, _vp]),
     "slha_b200_score_tiles": (_i32, [_vp, _sz, _vp, _vp, _sz, _vp]),
     "slha_b200_score_topk": (_i32, [_vp, _vp, _sz, _vp, _vp, _sz, _u32, _vp, _vp, _vp]),
+    "slha_b200_score_topk_noalloc": (_i32, [_vp, _vp, _sz, _vp, _vp, _sz, _u32, _vp, _vp, _vp]),
     "slha_b200_topk_merge": (_i32, [_vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
     "slha_b200_topk_merge_strided": (_i32, [_vp, _vp, _u32, _u64, _u32, _u32, _u32, _vp, _vp]),
     "slha_b200_pool_create": (_i32, [_vp, C.POINTER(_vp)]),
@@ -362,6 +363,18 @@ def score_topk(tiles, segments, q_coarse, q_sign, nq, k, out_index=None, out_sco
         )
     )
     return out_index, out_score, out_count
+
+
+def score_topk_noalloc(tiles, segments, q_coarse, q_sign, nq, k, out_index, out_score, out_count=None):
+    """score_topk for callers that may not allocate: all buffers are device memory
+    supplied by the caller, the working memory is a fixed array inside the library
+    (k <= 1024, nq <= 256; see include/slha_b200.h)."""
+    seg = np.ascontiguousarray(segments, SEGMENT_DTYPE)
+    _check(
+        load_library().slha_b200_score_topk_noalloc(
+            ptr(tiles), ptr(seg), len(seg), ptr(q_coarse), ptr(q_sign), nq, k, ptr(out_index), ptr(out_score), ptr(out_count)
+        )
+    )
 
 
 def topk_merge(cand_index, cand_score, n_lists, n_queries, k_in, k_out, out_index=None, out_score=None, list_stride=None):

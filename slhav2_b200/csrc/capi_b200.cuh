@@ -212,6 +212,31 @@ int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment
     });
 }
 
+int32_t slha_b200_score_topk_noalloc(const SciRustSlhaTile* tiles, const SlhaB200Segment* segments, size_t n_segments,
+                                     const float* q_coarse, const uint64_t* q_sign, size_t n_queries, uint32_t k,
+                                     uint32_t* out_index, float* out_score, uint32_t* out_count) {
+    // Deliberately no CallScope / staging here: those may grow (allocate) the
+    // per-thread scratch arena.  Every data pointer except `segments` must
+    // already be device memory; the only working memory is the library's fixed
+    // device array (see score.cu).
+    return ffi([&]() -> Status {
+        if (n_queries == 0) return Status();
+        if (!tiles || !segments || !q_coarse || !q_sign || !out_index || !out_score)
+            return Status(SLHA_ERR_NULL, "slha_b200_score_topk_noalloc received a NULL pointer");
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        if (!is_device_ptr(tiles) || !is_device_ptr(q_coarse) || !is_device_ptr(q_sign) || !is_device_ptr(out_index) ||
+            !is_device_ptr(out_score) || (out_count && !is_device_ptr(out_count)))
+            return Status(SLHA_ERR_DEVICE, "slha_b200_score_topk_noalloc: tiles, queries and outputs must be device memory");
+        if (is_device_ptr(segments))
+            return Status(SLHA_ERR_DEVICE, "slha_b200_score_topk_noalloc: segments must be host memory");
+        SLHA_TRY(score_topk_noalloc(c, tiles, segments, n_segments, q_coarse, q_sign, n_queries, k, out_index, out_score,
+                                    out_count));
+        if (sync_by_default(c)) SLHA_CUDA(cudaStreamSynchronize(c->stream));
+        return Status();
+    });
+}
+
 int32_t slha_b200_topk_merge_strided(const uint32_t* cand_index, const float* cand_score, uint32_t n_lists,
                                      uint64_t list_stride, uint32_t n_queries, uint32_t k_in, uint32_t k_out,
                                      uint32_t* out_index, float* out_score) {

@@ -19,6 +19,7 @@
 
 #include <cfloat>
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -438,3 +439,150 @@ __global__ void __launch_bounds__(256) score_kernel(ScoreArgs a) {
 #include "score_mma.cuh"
 #include "score_merge.cuh"
 #include "score_host.cuh"
+
+// ---------------------------------------------------------------------------
+// slha_b200_score_topk_noalloc: fused score + top-k whose working memory is a
+// fixed array inside this library instead of memory obtained at call time.
+// ---------------------------------------------------------------------------
+namespace slha {
+namespace {
+
+constexpr uint32_t NA_MAX_ITEMS = 512;    // work items per call
+constexpr uint32_t NA_MAX_LISTS = 512;    // candidate lists (work item x query) per call
+constexpr uint32_t NA_MAX_QUERIES = 256;  // query rows per call
+constexpr uint32_t NA_MAX_K = 1024;       // results per query
+
+struct NoAllocScratch {
+    WorkItem items[NA_MAX_ITEMS];
+    uint32_t q_list_begin[NA_MAX_QUERIES];
+    uint32_t q_list_count[NA_MAX_QUERIES];
+    uint32_t cand_cnt[NA_MAX_LISTS];
+    uint64_t cand_keys[(size_t)NA_MAX_LISTS * NA_MAX_K];
+};
+
+// The scratch itself: 4 MiB + 22 KiB of device memory held by every GPU that
+// loads this library, until the process exits.  In host code this name is only
+// a stand-in for the symbol; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];
+
+struct NoAllocDevice {
+    bool ready = false;
+    NoAllocScratch* scratch = nullptr;  // device address of g_noalloc_scratch on this device
+};
+NoAllocDevice g_noalloc_dev[16];
+std::mutex g_noalloc_mu;
+
+// Once per device, with that device current: resolve the scratch address and
+// raise the kernels' dynamic shared-memory limits.
+Status noalloc_setup(Ctx* c, NoAllocScratch** out) {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    NoAllocDevice& d = g_noalloc_dev[c->device & 15];
+    if (!d.ready) {
+        SLHA_CUDA(cudaSetDevice(c->device));
+        void* p = nullptr;
+        SLHA_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        SLHA_CUDA(cudaFuncSetAttribute(score_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+        SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<CompLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+        d.scratch = reinterpret_cast<NoAllocScratch*>(p);
+        d.ready = true;
+    }
+    *out = d.scratch;
+    return Status();
+}
+
+}  // namespace
+
+Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* segs, size_t n_segs,
+                          const float* d_q_coarse, const uint64_t* d_q_sign, size_t nq, uint32_t k,
+                          uint32_t* d_out_index, float* d_out_score, uint32_t* d_out_count) {
+    if (nq == 0) return Status();
+    if (k == 0 || k > NA_MAX_K)
+        return Status(SLHA_ERR_CAPACITY, "score_topk_noalloc: k must be in 1.." + std::to_string(NA_MAX_K));
+    if (nq > NA_MAX_QUERIES)
+        return Status(SLHA_ERR_CAPACITY, "score_topk_noalloc: at most " + std::to_string(NA_MAX_QUERIES) + " query rows per call");
+    NoAllocScratch* sc;
+    SLHA_TRY(noalloc_setup(c, &sc));
+
+    // work decomposition in fixed-size host arrays (nothing is allocated)
+    static thread_local WorkItem items[NA_MAX_ITEMS];
+    static thread_local uint32_t q_begin[NA_MAX_QUERIES], q_count[NA_MAX_QUERIES];
+    std::memset(q_count, 0, sizeof(uint32_t) * nq);
+    std::memset(q_begin, 0, sizeof(uint32_t) * nq);
+    const int threads = 128, nwarps = threads / 32;
+    const uint32_t round = (uint32_t)nwarps * BLK_TILES;
+    uint64_t total = 0;
+    for (size_t i = 0; i < n_segs; ++i) total += (uint64_t)segs[i].n_tiles * ((segs[i].n_queries + 3) / 4);
+    // every (segment, group of <= 4 queries) stream is cut into items of equal size; the
+    // item size is chosen so that items x 4 lists stay within the fixed scratch
+    const uint64_t target_items = NA_MAX_LISTS / 4 - std::min<uint64_t>(n_segs, NA_MAX_LISTS / 4 - 32);
+    uint64_t item_tiles = std::max<uint64_t>(4096, (total + target_items - 1) / target_items);
+    item_tiles = (item_tiles + round - 1) / round * round;
+    uint32_t n_items = 0, n_lists = 0, max_parts = 1;
+    for (size_t i = 0; i < n_segs; ++i) {
+        const SlhaB200Segment& s = segs[i];
+        if ((uint64_t)s.query_begin + s.n_queries > nq)
+            return Status(SLHA_ERR_DIMENSION, "segment query range exceeds n_queries");
+        const uint32_t parts = (uint32_t)((s.n_tiles + item_tiles - 1) / item_tiles);
+        max_parts = std::max(max_parts, parts);
+        for (uint32_t q0 = 0; q0 < s.n_queries; q0 += 4) {
+            const uint32_t gq = std::min<uint32_t>(4, s.n_queries - q0);
+            if (n_items + parts > NA_MAX_ITEMS || n_lists + parts * gq > NA_MAX_LISTS)
+                return Status(SLHA_ERR_CAPACITY,
+                              "score_topk_noalloc: the call needs more than " + std::to_string(NA_MAX_ITEMS) +
+                                  " work items or " + std::to_string(NA_MAX_LISTS) +
+                                  " candidate lists (too many segments x query groups for the fixed scratch)");
+            for (uint32_t g = 0; g < gq; ++g) {
+                const uint32_t Q = s.query_begin + q0 + g;
+                if (q_count[Q]) return Status(SLHA_ERR_DIMENSION, "a query row belongs to two segments");
+                q_begin[Q] = n_lists + g;
+                q_count[Q] = parts | (gq << 24);
+            }
+            for (uint32_t part = 0; part < parts; ++part) {
+                WorkItem& w = items[n_items++];
+                w.tile_begin = s.tile_begin + (uint64_t)part * item_tiles;
+                w.n_tiles = (uint32_t)std::min<uint64_t>(item_tiles, s.n_tiles - (uint64_t)part * item_tiles);
+                w.index_base = s.index_base + (uint32_t)(part * item_tiles);
+                w.query_begin = s.query_begin + q0;
+                w.n_queries = gq;
+                w.list_begin = n_lists + part * gq;
+                w.pad = gq;
+            }
+            n_lists += parts * gq;
+        }
+    }
+    // queries without tiles still need a defined (empty) list range
+    for (size_t Q = 0; Q < nq; ++Q)
+        if (!q_count[Q]) q_count[Q] = 1u << 24;
+    if (n_items)
+        SLHA_CUDA(cudaMemcpyAsync(sc->items, items, sizeof(WorkItem) * n_items, cudaMemcpyHostToDevice, c->stream));
+    SLHA_CUDA(cudaMemcpyAsync(sc->q_list_begin, q_begin, 4 * nq, cudaMemcpyHostToDevice, c->stream));
+    SLHA_CUDA(cudaMemcpyAsync(sc->q_list_count, q_count, 4 * nq, cudaMemcpyHostToDevice, c->stream));
+    // Every list count is rewritten by the scoring kernel and lists are read only up
+    // to their count, so nothing left in the scratch by the previous call is visible.
+    const uint32_t cap = std::max<uint32_t>(2 * k, k + 2 * round);
+    if (n_items) {
+        ScoreArgs a{};
+        a.tiles = reinterpret_cast<const unsigned char*>(tiles);
+        a.items = sc->items;
+        a.q_coarse = d_q_coarse;
+        a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);
+        a.k = k;
+        a.cap = cap;
+        a.cand_keys = sc->cand_keys;
+        a.cand_cnt = sc->cand_cnt;
+        score_kernel<4, true><<<n_items, threads, score_smem_bytes(4, nwarps, true, cap), c->stream>>>(a);
+        count_launch();
+        SLHA_CUDA(cudaGetLastError());
+    }
+    uint32_t kp2 = 2;
+    while (kp2 < k) kp2 <<= 1;
+    CompLists L{sc->cand_keys, sc->cand_cnt, sc->q_list_begin, sc->q_list_count, k};
+    const uint32_t cap_s = merge_cap((uint64_t)max_parts * k, kp2);
+    topk_merge_kernel<CompLists><<<(uint32_t)nq, cap_s > 4096 ? 512 : 256, merge_smem(cap_s), c->stream>>>(
+        L, k, kp2, cap_s, d_out_index, d_out_score, d_out_count);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    return Status();
+}
+
+}  // namespace slha
