@@ -294,6 +294,7 @@ struct ScoreArgs {
     uint32_t* retry;
     const uint32_t* cta_begin;    // tensor-core kernel: item range of every persistent CTA
     unsigned long long* gpivot;   // tensor-core kernel: per query row, shared selection threshold
+    uint32_t nf4_table;           // tensor-core kernel: build the NF4 shared-memory table (else NF4 tiles are handed back)
 };
 
 template <int G, bool TOPK>

@@ -16,8 +16,8 @@ int env_int(const char* name, int dflt) {
     return (v && *v) ? std::atoi(v) : dflt;
 }
 
-size_t mma_smem_bytes(int nwarps, uint32_t cap) {
-    return (size_t)NF4_LUT_BYTES + (size_t)nwarps * MMA_DEPTH * MMA_SET_BYTES + (size_t)4 * cap * 8 + 4 * 8 +
+size_t mma_smem_bytes(int nwarps, uint32_t cap, bool nf4_table) {
+    return (size_t)(nf4_table ? NF4_LUT_BYTES : 0) + (size_t)nwarps * MMA_DEPTH * MMA_SET_BYTES + (size_t)4 * cap * 8 + 4 * 8 +
            (4 + 2 + 2 + 260) * 4 + 16;
 }
 
@@ -88,6 +88,7 @@ struct Plan {
     uint32_t n_items = 0;
     uint32_t max_parts = 1;  // most candidate lists any query has
     bool use_mma = false;
+    bool nf4_table = true;
     int mma_threads = 256;
     uint32_t mma_cap = 0, mma_grid = 0;
     size_t mma_smem = 0;
@@ -103,8 +104,8 @@ struct Plan {
     }
 };
 
-Status build_plan(Ctx* c, const SlhaB200Segment* segs, size_t n_segs, size_t nq, uint32_t k,
-                  std::unique_ptr<Plan>& slot) {
+Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* segs, size_t n_segs, size_t nq,
+                  uint32_t k, std::unique_ptr<Plan>& slot) {
     std::vector<unsigned char> key(sizeof(SlhaB200Segment) * n_segs + 16);
     std::memcpy(key.data(), segs, sizeof(SlhaB200Segment) * n_segs);
     uint64_t nq64 = nq;
@@ -135,11 +136,24 @@ Status build_plan(Ctx* c, const SlhaB200Segment* segs, size_t n_segs, size_t nq,
     {
         const int mw = p->mma_threads / 32;
         const uint32_t mround = (uint32_t)mw * 2 * MMA_SET_TILES;  // appends that may follow a raised flag
+        // Codec hint: the flags of the first tile of the first non-empty segment decide
+        // whether the NF4 table occupies shared memory.  A wrong hint costs speed only
+        // (NF4 tiles met without the table are handed to the generic kernel).
+        p->nf4_table = true;
+        for (size_t i = 0; i < n_segs; ++i)
+            if (segs[i].n_tiles) {
+                uint16_t flags = 0;
+                const unsigned char* t0 = reinterpret_cast<const unsigned char*>(tiles) + segs[i].tile_begin * TILE_BYTES;
+                SLHA_CUDA(cudaMemcpyAsync(&flags, t0 + 118, 2, cudaMemcpyDeviceToHost, c->stream));
+                SLHA_CUDA(cudaStreamSynchronize(c->stream));
+                p->nf4_table = (flags & F_NF4) != 0;
+                break;
+            }
         uint32_t mcap = std::max<uint32_t>(3 * k, k + 4 * mround);
-        while (mcap > k + 2 * mround && mma_smem_bytes(mw, mcap) > MAX_SMEM) mcap -= 256;
-        p->use_mma = env_int("SLHA_B200_SCORE_IMPL", 1) != 0 && mma_smem_bytes(mw, mcap) <= MAX_SMEM;
+        while (mcap > k + 2 * mround && mma_smem_bytes(mw, mcap, p->nf4_table) > MAX_SMEM) mcap -= 256;
+        p->use_mma = env_int("SLHA_B200_SCORE_IMPL", 1) != 0 && mma_smem_bytes(mw, mcap, p->nf4_table) <= MAX_SMEM;
         p->mma_cap = mcap;
-        p->mma_smem = mma_smem_bytes(mw, mcap);
+        p->mma_smem = mma_smem_bytes(mw, mcap, p->nf4_table);
         const uint32_t per_sm = (uint32_t)std::max<size_t>(1, MAX_SMEM / (p->mma_smem + 1024));
         p->mma_grid = (uint32_t)sms * per_sm;
     }
@@ -308,7 +322,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     if (nq == 0) return Status();
     if (k == 0 || k > 8192) return Status(SLHA_ERR_DIMENSION, "top-k: k must be in 1..8192");
     static thread_local std::unique_ptr<Plan> cache;
-    SLHA_TRY(build_plan(c, segs, n_segs, nq, k, cache));
+    SLHA_TRY(build_plan(c, tiles, segs, n_segs, nq, k, cache));
     Plan* p = cache.get();
     const int nwarps = p->threads / 32;
     const bool timed = g_timing.calls < g_timing.max_calls;
@@ -326,6 +340,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.retry = p->d_retry;
         a.cta_begin = p->d_cta_begin;
         a.gpivot = p->d_gpivot;
+        a.nf4_table = p->nf4_table ? 1u : 0u;
         a.q_coarse = d_q_coarse;
         a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);
         a.k = k;

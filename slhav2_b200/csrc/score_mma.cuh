@@ -166,8 +166,9 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     // shared layout: nf4 table | stage ring | [keys | pivot | cnt | ctl | hist]
+    const uint32_t lut_bytes = a.nf4_table ? NF4_LUT_BYTES : 0;  // the table is left out when no NF4 tile is expected
     uint2* lut = reinterpret_cast<uint2*>(smem);
-    unsigned char* tail = smem + NF4_LUT_BYTES + (size_t)nwarps * MMA_DEPTH * MMA_SET_BYTES;
+    unsigned char* tail = smem + lut_bytes + (size_t)nwarps * MMA_DEPTH * MMA_SET_BYTES;
     uint64_t* keys = reinterpret_cast<uint64_t*>(tail);            // [4][cap]
     uint64_t* pivot = keys + (TOPK ? (size_t)4 * a.cap : 0);       // [4]
     int* cnt = reinterpret_cast<int*>(pivot + 4);                  // [4]
@@ -175,10 +176,10 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
     int* bail = ctl + 3;
     int* hist = ctl + 4;  // 260
     const uint32_t smem_s = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t stage_s = smem_s + NF4_LUT_BYTES + (uint32_t)warp * MMA_DEPTH * MMA_SET_BYTES;
+    const uint32_t stage_s = smem_s + lut_bytes + (uint32_t)warp * MMA_DEPTH * MMA_SET_BYTES;
 
     // NF4 codebook as fp16 hi + lo pairs per byte (two nibbles), 16 bank-aligned replicas
-    for (int e = tid; e < 256 * 16; e += blockDim.x) {
+    for (int e = tid; e < (a.nf4_table ? 256 * 16 : 0); e += blockDim.x) {
         const int b = e >> 4;
         const float c0 = c_nf4[b & 15], c1 = c_nf4[b >> 4];
         lut[e] = make_uint2(pack_half2(c0, c1), pack_half2(half_residual(c0), half_residual(c1)));
@@ -313,7 +314,7 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
                 const uint4 x0 = lds_v4(r0 + L.c7), x1 = lds_v4(r1 + L.c7);  // position, head|flags, gs[8]
                 const uint32_t f0 = x0.y >> 16, f1 = x1.y >> 16;
                 const uint32_t fo = __reduce_or_sync(0xFFFFFFFFu, f0 | f1);
-                if (fo & (F_MIXED | F_TQ3 | F_MIX3)) {
+                if ((fo & (F_MIXED | F_TQ3 | F_MIX3)) || ((fo & F_NF4) && !a.nf4_table)) {
                     gave_up = true;  // a codec this kernel does not decode: hand the item back
                     if (lane == 0) bail[0] = 1;
                 } else {
@@ -387,14 +388,24 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
                     block_select_topk(keys + (size_t)qq * a.cap, &cnt[qq], a.k, &pivot[qq], hist);
                     if (tid == 0) atomicMax(a.gpivot + it.query_begin + qq, (unsigned long long)pivot[qq]);
                 }
+                // write the survivors that still clear the query's shared threshold, compacted
                 const int c = cnt[qq];
                 uint64_t* dst = a.cand_keys + (size_t)(it.list_begin + qq) * a.k;
                 const unsigned long long gp = *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + qq);
-                for (int i = tid; i < c; i += blockDim.x) {
-                    const uint64_t key = keys[(size_t)qq * a.cap + i];
-                    dst[i] = key >= gp ? key : 0ull;  // 0 = absent for the merge
+                if (tid == 0) hist[0] = 0;
+                __syncthreads();
+                for (int i0 = 0; i0 < c; i0 += blockDim.x) {
+                    const int i = i0 + tid;
+                    const uint64_t key = i < c ? keys[(size_t)qq * a.cap + i] : 0ull;
+                    const bool keep = i < c && key >= gp;
+                    const unsigned bal = __ballot_sync(0xFFFFFFFFu, keep);
+                    int base = 0;
+                    if (lane == 0 && bal) base = atomicAdd(&hist[0], __popc(bal));
+                    base = __shfl_sync(0xFFFFFFFFu, base, 0);
+                    if (keep) dst[base + __popc(bal & ((1u << lane) - 1))] = key;
                 }
-                if (tid == 0) a.cand_cnt[it.list_begin + qq] = (uint32_t)c;
+                __syncthreads();
+                if (tid == 0) a.cand_cnt[it.list_begin + qq] = (uint32_t)hist[0];
             }
         }
     }
