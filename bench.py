@@ -149,6 +149,12 @@ class ClockSampler:
         return out
 
 
+# DRAM bytes per tile (read + write) of the score kernel, from the ncu captures summarised in
+# profiles/score_mma_kernel_c2_nf4_4layers.md and profiles/score_mma_kernel_c5_int4_128k_tokens.md;
+# traffic grows in proportion to the tile count, so it is scaled to the tiles of a launch.
+NCU_DRAM_BYTES_PER_TILE = {"c2": 131.9, "c5": 132.0}
+
+
 def measured_peak_gbs():
     try:
         return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
@@ -378,7 +384,9 @@ def gpu_arm(args, w):
         "roofline": {"bound": "hbm", "kernel": "score_mma_kernel (fused score + top-k)", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
                      "kernel_ms": k_ms, "merge_kernel_ms": float(np.mean(merge_ms)) if len(merge_ms) else None,
-                     "algorithmic_bytes_per_launch": n_tiles * 128, "traffic": None},
+                     "algorithmic_bytes_per_launch": n_tiles * 128,
+                     "traffic": NCU_DRAM_BYTES_PER_TILE.get(args.workload, 132.0) * n_tiles,
+                     "traffic_source": "ncu dram__bytes_read+write per tile on a reduced case, scaled by tiles (profiles/)"},
         "e2e": {"value": total_tiles / (e2e_ms / args.steps * 1e-3), "unit": "tiles/s", "ms_per_step": e2e_ms / args.steps,
                 "h2d_bytes_per_step": int(nq * (512 + 32)), "d2h_bytes_per_step": int(nq * k * 8 + (nq * 4 if world == 1 else 0))},
         "gpu_launches": int(launches),
@@ -412,8 +420,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=0, help="profiling aid: shrink the workload to this many layers")
+    ap.add_argument("--tokens", type=int, default=0, help="profiling aid: shrink the workload to this many tokens")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.layers:
+        w["layers"] = args.layers
+        w["name"] += " (reduced to %d layers)" % args.layers
+    if args.tokens:
+        w["tokens"] = args.tokens
+        w["name"] += " (reduced to %d tokens)" % args.tokens
     if args.impl == "reference":
         reference_arm(args, w)
     else:

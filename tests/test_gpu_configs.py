@@ -1,0 +1,129 @@
+"""The BASELINE configurations as parity cases (reduced lengths where the oracle
+would take minutes; full length through size-independent properties)."""
+import numpy as np
+import pytest
+
+from oracle import pyoracle as ora
+from tests import helpers as H
+from tests.test_gpu_topk import check_topk
+
+pytestmark = pytest.mark.gpu
+S = pytest.importorskip("slhav2_b200")
+F = np.float32
+
+
+def test_config1_single_head_cpu_runnable_reference():
+    # 4096 x 128 f32 N(0,1) seed 0, channels 7 and 93 x8, orthogonal 128x128 P, INT4 single, top-64
+    n, d, k = 4096, 128, 64
+    om, p = H.make_model_pair(d, seed=0, pseed=0)
+    gm = S.Model.from_projection(p, d, 0)
+    keys = H.gaussian_keys(0, n, d, outlier_channels=(7, 93))
+    dt = S.DeviceBuffer(n * 128)
+    gm.encode_keys(keys, S.CODEC_INT4_SINGLE, out=dt)
+    tiles = dt.download(S.TILE_DTYPE, n)
+    assert tiles.tobytes() == om.encode_batch(keys, 0).tobytes()
+    q = ora.Rng(1).gaussian(d)
+    qc, qs = gm.prepare_queries(q[None])
+    segs = [(0, n, 0, 1, 0)]
+    gi, gsc, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, 1, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gsc, gc)
+
+
+def student_t_keys(seed, n, d):
+    rng = ora.Rng(seed)
+    g = rng.gaussian(n * d * 5).reshape(n, d, 5)
+    t = g[..., 0] / np.sqrt((g[..., 1:] ** 2).sum(-1) / 4.0)
+    out = np.nonzero(ora.Rng(seed + 1).gaussian(n * d).reshape(n, d) > 2.326)  # ~1 % of the entries
+    t[out] *= 20.0
+    return H.to_bf16_f32(t.astype(F))
+
+
+def test_config3_tq3_rht_many_queries_per_head():
+    # TQ3 + Hadamard RHT, Student-t(4) keys with 1 % x20 outliers, 64 queries per KV head
+    d, heads, tokens, qph, k = 128, 2, 2048, 64, 32
+    om, p = H.make_model_pair(d, seed=3, rht=True, pseed=4)
+    gm = S.Model.from_projection(p, d, 3, rht=True)
+    keys = student_t_keys(5, heads * tokens, d)
+    dt = S.DeviceBuffer(heads * tokens * 128)
+    bf16 = (keys.view(np.uint32) >> 16).astype(np.uint16)
+    gm.encode_keys(bf16, S.CODEC_TQ3, n=heads * tokens, key_dtype=S.BF16, out=dt)
+    tiles = dt.download(S.TILE_DTYPE, heads * tokens)
+    assert tiles.tobytes() == om.encode_batch(keys, 4).tobytes()
+    q = H.gaussian_keys(6, heads * qph, d)
+    qc, qs = gm.prepare_queries(q)
+    for j in (0, 77):
+        wc, ws = om.prepare_query(q[j])
+        assert np.array_equal(qs[j], ws) and np.array_equal(qc[j], wc)
+    segs = [(h * tokens, tokens, h * qph, qph, 0) for h in range(heads)]
+    gi, gsc, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, heads * qph, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gsc, gc)
+
+
+def test_config4_ccos_under_budget_interleaved_appends_and_decode_steps():
+    # mixed 8/4 codec, budget 60 % of full-HOT, H2O importance with sink 4 + recent window,
+    # appends interleaved with decode-step scoring over the device-resident arena
+    d, steps, per_step = 128, 96, 8
+    om, p = H.make_model_pair(d, seed=8, pseed=9)
+    gm = S.Model.from_projection(p, d, 8)
+    total = steps * per_step
+    budget = int(0.6 * 128 * total)
+    pool = S.TilePool(total, budget, S.PAGE_LOWEST_IMPACT_FIRST, S.EVICT_IMPORTANCE, sink_window=4, recent_window=64)
+    cache = ora.Cache(budget, 0, 1, 4, 64)
+    keys = H.gaussian_keys(10, total, d)
+    q = H.gaussian_keys(11, steps, d)
+    qc, qs = gm.prepare_queries(q)
+    for s in range(steps):
+        chunk = keys[s * per_step:(s + 1) * per_step]
+        pos = np.arange(s * per_step, (s + 1) * per_step, dtype=np.uint32)
+        slots = pool.append_keys(gm, chunk, S.CODEC_MIXED, positions=pos)
+        want = om.encode_batch(chunk, 3, pos=pos)
+        assert list(slots) == [cache.insert(want[i:i + 1]) for i in range(per_step)]
+        # decode step: score the arena, feed the scores back as H2O observations
+        gsl, gsv = pool.score_all(qc[s], qs[s])
+        wsl, wsv = cache.score_all(qc[s], qs[s])
+        assert np.array_equal(gsl, wsl) and np.all(np.abs(gsv - wsv) <= 1e-3)
+        pool.observe_scores(wsl, wsv, 1.0)  # identical inputs on both sides keep eviction order comparable
+        cache.observe_scores(wsl, wsv, 1.0)
+        if s % 4 == 3:
+            assert pool.enforce_budget() == cache.enforce_budget()
+            st = pool.stats()
+            assert st["live_bytes"] <= budget and st["live_bytes"] == cache.live_bytes()
+            assert (st["hot"], st["warm"], st["cold"]) == cache.counts()
+    tiles, state, imp, _ = pool.read()
+    assert np.array_equal(state, cache.states())
+    assert {ora.WARM, ora.COLD} <= set(state.tolist())  # paged and evicted tiles both present (60 % < all-WARM 75 %)
+    live = state != ora.COLD
+    assert tiles[live].tobytes() == cache.tiles()[live].tobytes()
+    wi = np.array([cache.importance(s) for s in range(len(cache))], F)
+    assert np.all(np.abs(imp[live] - wi[live]) <= 1e-5)
+
+
+def test_config5_full_length_head_fused_topk_equals_sort_of_full_scores():
+    # one KV head of the 1M-token context (134 MB of tiles), MX-32 INT4, 4 queries, top-2048:
+    # the fused path must return exactly the top of the library's own full score vectors
+    n, d, k, nq = 1 << 20, 128, 2048, 4
+    _, p = H.make_model_pair(d, seed=12, pseed=13)
+    gm = S.Model.from_projection(p, d, 12)
+    import torch
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    keys = torch.randn(n, d, generator=g, device="cuda").to(torch.bfloat16).contiguous()
+    tiles = torch.empty(n * 128, dtype=torch.uint8, device="cuda")
+    gm.encode_keys(keys, S.CODEC_INT4_GROUPED32, n=n, key_dtype=S.BF16, out=tiles)
+    q = H.gaussian_keys(14, nq, d)
+    qc, qs = gm.prepare_queries(q)
+    full = torch.empty(nq, n, dtype=torch.float32, device="cuda")
+    S.score_tiles(tiles, n, qc, qs, nq, out=full)
+    gi, gsc, gc = S.score_topk(tiles, S.make_segments([(0, n, 0, nq, 0)]), qc, qs, nq, k)
+    full = full.cpu().numpy()
+    assert np.all(gc == k)
+    for j in range(nq):
+        oi, ov = ora.topk(full[j], k)
+        assert np.all(np.abs(gsc[j] - ov) <= 1e-3)
+        assert np.all(np.abs(full[j][gi[j]] - gsc[j]) <= 1e-3) and len(set(gi[j])) == k
+        thr = ov[-1]
+        assert all(abs(full[j][i] - thr) <= 2e-3 for i in set(oi) ^ set(gi[j]))
+    # encode -> decode_latent round trip on a sample: reconstruction within one INT4 step per latent dim
+    sample = np.frombuffer(tiles[:128 * 4].cpu().numpy().tobytes(), S.TILE_DTYPE)
+    assert np.all(sample["position"] == np.arange(4)) and np.all(sample["flags"] == 0)
