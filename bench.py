@@ -248,19 +248,23 @@ def build_shard(S, torch, w, rank, world, dev):
         model = S.Model.from_projection(seeded_projection(100 + l), HEAD_DIM, 100 + l)
         gen.manual_seed(1234 + l + 7919 * rank)  # every rank holds different tokens
         chan = torch.exp(0.5 * torch.randn(HEAD_DIM, generator=gen, device=dev))
-        for h in range(H):
+        # one encode call covers a whole layer when its heads fit one chunk, else one head's chunk
+        heads_per_call = H if T <= chunk_tokens else 1
+        for h in range(0, H, heads_per_call):
             for t0 in range(0, T, chunk_tokens):
                 t1 = min(T, t0 + chunk_tokens)
-                k = torch.randn(t1 - t0, HEAD_DIM, generator=gen, device=dev) * chan
-                a, b = k[:, 0::2].clone(), k[:, 1::2].clone()
-                k[:, 0::2] = a * cos[t0:t1] - b * sin[t0:t1]
-                k[:, 1::2] = a * sin[t0:t1] + b * cos[t0:t1]
+                k = torch.randn(heads_per_call, t1 - t0, HEAD_DIM, generator=gen, device=dev) * chan
+                a, b = k[..., 0::2].clone(), k[..., 1::2].clone()
+                k[..., 0::2] = a * cos[t0:t1] - b * sin[t0:t1]
+                k[..., 1::2] = a * sin[t0:t1] + b * cos[t0:t1]
                 kb = k.to(torch.bfloat16).contiguous()
+                n = heads_per_call * (t1 - t0)
                 off = ((l * H + h) * T + t0) * 128
+                lo = h * T + t0
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-                model.encode_keys(kb, w["codec"], n=t1 - t0, key_dtype=S.BF16, positions=positions[h * T + t0:h * T + t1],
-                                  head_ids=heads[h * T + t0:h * T + t1], out=tiles[off:off + (t1 - t0) * 128])
+                model.encode_keys(kb, w["codec"], n=n, key_dtype=S.BF16, positions=positions[lo:lo + n],
+                                  head_ids=heads[lo:lo + n], out=tiles[off:off + n * 128])
                 e1.record()
                 torch.cuda.synchronize()
                 enc_ms += e0.elapsed_time(e1)

@@ -316,6 +316,7 @@ int32_t slha_b200_pool_insert_tiles(SlhaB200Pool* pool, const SciRustSlhaTile* t
         }
         SLHA_TRY(pool_reserve(c, pl, dt, n, dslots));
         SLHA_TRY(pool_scatter(c, pl, dt, dslots, n));
+        pl->codec_mask |= 0x80000000u;
         return finish_outputs(c, outs, sync_by_default(c));
     });
 }
@@ -354,6 +355,7 @@ int32_t slha_b200_pool_append_keys(SlhaB200Pool* pool, const SlhaModel* model, c
         SLHA_TRY(pool_reserve(c, pl, nullptr, n, dslots));
         SLHA_TRY(launch_encode(c, m.get(), dk, key_dtype, n, dpos, position_base, dhead, codec,
                                reinterpret_cast<SciRustSlhaTile*>(pl->dev.tiles), dslots));
+        pl->codec_mask |= 1u << codec;
         return finish_outputs(c, outs, sync_by_default(c));
     });
 }
@@ -415,9 +417,13 @@ int32_t slha_b200_pool_score_topk(SlhaB200Pool* pool, const float* q_coarse, con
         SLHA_TRY(stage_out(c, out_score, nq * k * 4, &outs[1]));
         SLHA_TRY(stage_out(c, out_count, nq * 4, &outs[2]));
         SlhaB200Segment seg{0, (uint32_t)pl->h_cnt.len, 0, (uint32_t)nq, 0};
+        const uint32_t cm = pl->codec_mask;
+        const bool known = !(cm & 0x80000000u);
+        const uint32_t nibble = (1u << SLHA_CODEC_INT4_SINGLE) | (1u << SLHA_CODEC_INT4_GROUPED) | (1u << SLHA_CODEC_NF4) | (1u << 6);
         SLHA_TRY(score_topk_device(c, reinterpret_cast<const SciRustSlhaTile*>(pl->dev.tiles), pl->dev.state, &seg, 1,
                                    dq, ds, nq, k, (uint32_t*)outs[0].dev, (float*)outs[1].dev,
-                                   (uint32_t*)outs[2].dev));
+                                   (uint32_t*)outs[2].dev, /*prefer_generic=*/known && cm && !(cm & nibble),
+                                   known ? (int)((cm >> SLHA_CODEC_NF4) & 1u) : -1));
         return finish_outputs(c, outs, sync_by_default(c));
     });
 }

@@ -105,7 +105,8 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
                          const SlhaB200Segment* h_segments, size_t n_segments,
                          const float* d_q_coarse, const uint64_t* d_q_sign, size_t n_queries,
                          uint32_t k, uint32_t* d_out_index, float* d_out_score,
-                         uint32_t* d_out_count, bool prefer_generic = false);
+                         uint32_t* d_out_count, bool prefer_generic = false,
+                         int codec_hint = -1);  // codec_hint: -1 look at the tiles, 0 no NF4 tiles, 1 NF4 tiles
 Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* h_segments, size_t n_segments,
                           const float* d_q_coarse, const uint64_t* d_q_sign, size_t n_queries, uint32_t k,
                           uint32_t* d_out_index, float* d_out_score, uint32_t* d_out_count);

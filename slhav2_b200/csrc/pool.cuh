@@ -37,6 +37,9 @@ struct Pool {
     PoolDev dev;
     PoolCounters h_cnt;      // host mirror
     void* d_observe = nullptr;  // scratch of observe_scores (reduction cell + partial sums)
+    // codecs the pool may hold: bit i = codec id i appended through append_keys; bit 31 = tiles of
+    // unknown codec were inserted. Lets the scorer pick its kernel variant without reading tiles back.
+    uint32_t codec_mask = 0;
 };
 
 Status pool_create(Ctx* c, const SlhaB200PoolConfig& cfg, Pool** out);

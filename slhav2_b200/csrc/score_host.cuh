@@ -69,6 +69,24 @@ struct Timing {
 };
 thread_local Timing g_timing;
 
+// Grow-only device buffer owned by a plan (kept when the plan object is recycled).
+struct DevBuf {
+    void* p = nullptr;
+    size_t cap = 0;
+    Status ensure(size_t need) {
+        need = std::max<size_t>(need, 256);
+        if (need <= cap) return Status();
+        if (p) cudaFree(p);
+        p = nullptr;
+        cap = 0;
+        const size_t want = need + need / 2;
+        SLHA_CUDA(cudaMalloc(&p, want));
+        cap = want;
+        return Status();
+    }
+    ~DevBuf() { cudaFree(p); }
+};
+
 // The cached decomposition of one score_topk call shape.
 struct Plan {
     std::vector<unsigned char> key;
@@ -89,34 +107,49 @@ struct Plan {
     uint32_t max_parts = 1;  // most candidate lists any query has
     bool use_mma = false;
     bool nf4_table = true;
+    int codec_hint_in = -1;
     int mma_threads = 256;
     uint32_t mma_cap = 0, mma_grid = 0;
     size_t mma_smem = 0;
-    ~Plan() {
-        cudaFree(d_retry);
-        cudaFree(d_cta_begin);
-        cudaFree(d_gpivot);
-        cudaFree(d_items);
-        cudaFree(d_q_list_begin);
-        cudaFree(d_q_list_count);
-        cudaFree(d_cand_keys);
-        cudaFree(d_cand_cnt);
-    }
+    DevBuf b_items, b_qbegin, b_qcount, b_keys, b_cnt, b_retry, b_cta, b_gpivot;
+    uint64_t last_use = 0;
 };
 
 Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* segs, size_t n_segs, size_t nq,
-                  uint32_t k, std::unique_ptr<Plan>& slot) {
+                  uint32_t k, int codec_hint, Plan** out) {
     std::vector<unsigned char> key(sizeof(SlhaB200Segment) * n_segs + 16);
     std::memcpy(key.data(), segs, sizeof(SlhaB200Segment) * n_segs);
     uint64_t nq64 = nq;
     std::memcpy(key.data() + sizeof(SlhaB200Segment) * n_segs, &nq64, 8);
     std::memcpy(key.data() + sizeof(SlhaB200Segment) * n_segs + 8, &k, 4);
-    if (slot && slot->device == c->device && slot->key == key) return Status();
-
-    auto p = std::make_unique<Plan>();
+    // small per-thread cache of plans (call shapes alternate in practice: appends
+    // change a pool's length, layers differ); a recycled plan keeps its device buffers
+    static thread_local std::vector<std::unique_ptr<Plan>> cache;
+    static thread_local uint64_t tick = 0;
+    ++tick;
+    for (auto& e : cache)
+        if (e->device == c->device && e->codec_hint_in == codec_hint && e->key == key) {
+            e->last_use = tick;
+            *out = e.get();
+            return Status();
+        }
+    Plan* p;
+    if (cache.size() < 4) {
+        cache.push_back(std::make_unique<Plan>());
+        p = cache.back().get();
+    } else {
+        p = cache[0].get();
+        for (auto& e : cache)
+            if (e->last_use < p->last_use) p = e.get();
+        p->classes.clear();
+        p->max_parts = 1;
+    }
+    p->last_use = tick;
+    p->codec_hint_in = codec_hint;
     p->key = std::move(key);
     p->device = c->device;
     p->k = k;
+    p->n_lists = 0;
     p->nq = (uint32_t)nq;
     p->kp2 = 2;
     while (p->kp2 < k) p->kp2 <<= 1;
@@ -139,8 +172,8 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
         // Codec hint: the flags of the first tile of the first non-empty segment decide
         // whether the NF4 table occupies shared memory.  A wrong hint costs speed only
         // (NF4 tiles met without the table are handed to the generic kernel).
-        p->nf4_table = true;
-        for (size_t i = 0; i < n_segs; ++i)
+        p->nf4_table = codec_hint != 0;
+        for (size_t i = 0; i < n_segs && codec_hint < 0; ++i)
             if (segs[i].n_tiles) {
                 uint16_t flags = 0;
                 const unsigned char* t0 = reinterpret_cast<const unsigned char*>(tiles) + segs[i].tile_begin * TILE_BYTES;
@@ -239,22 +272,30 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     std::vector<uint32_t> q_stride(nq, 1);
     for (const WorkItem& w : all)
         for (uint32_t g = 0; g < w.n_queries; ++g) q_stride[w.query_begin + g] = w.pad;
-    SLHA_CUDA(cudaMalloc(&p->d_items, std::max<size_t>(1, all.size()) * sizeof(WorkItem)));
-    SLHA_CUDA(cudaMalloc(&p->d_q_list_begin, std::max<size_t>(1, nq) * 4));
-    SLHA_CUDA(cudaMalloc(&p->d_q_list_count, std::max<size_t>(1, nq) * 4));
-    SLHA_CUDA(cudaMalloc(&p->d_cand_keys, std::max<size_t>(1, (size_t)n_lists * k) * 8));
-    SLHA_CUDA(cudaMalloc(&p->d_cand_cnt, std::max<size_t>(1, n_lists) * 4));
-    SLHA_CUDA(cudaMalloc(&p->d_retry, std::max<size_t>(1, all.size()) * 4));
+    SLHA_TRY(p->b_items.ensure(all.size() * sizeof(WorkItem)));
+    SLHA_TRY(p->b_qbegin.ensure(nq * 4));
+    SLHA_TRY(p->b_qcount.ensure(nq * 4));
+    SLHA_TRY(p->b_keys.ensure((size_t)n_lists * k * 8));
+    SLHA_TRY(p->b_cnt.ensure((size_t)n_lists * 4));
+    SLHA_TRY(p->b_retry.ensure(all.size() * 4));
+    SLHA_TRY(p->b_cta.ensure(cta_begin.size() * 4));
+    SLHA_TRY(p->b_gpivot.ensure(nq * 8));
+    p->d_items = (WorkItem*)p->b_items.p;
+    p->d_q_list_begin = (uint32_t*)p->b_qbegin.p;
+    p->d_q_list_count = (uint32_t*)p->b_qcount.p;
+    p->d_cand_keys = (uint64_t*)p->b_keys.p;
+    p->d_cand_cnt = (uint32_t*)p->b_cnt.p;
+    p->d_retry = (uint32_t*)p->b_retry.p;
+    p->d_cta_begin = (uint32_t*)p->b_cta.p;
+    p->d_gpivot = (unsigned long long*)p->b_gpivot.p;
     p->n_items = (uint32_t)all.size();
-    SLHA_CUDA(cudaMalloc(&p->d_cta_begin, cta_begin.size() * 4));
-    SLHA_CUDA(cudaMalloc(&p->d_gpivot, std::max<size_t>(1, nq) * 8));
+    // (pageable sources: cudaMemcpyAsync returns once they are staged, so the vectors may die)
     SLHA_CUDA(cudaMemcpyAsync(p->d_cta_begin, cta_begin.data(), cta_begin.size() * 4, cudaMemcpyHostToDevice, c->stream));
     for (size_t Q = 0; Q < nq; ++Q) q_count[Q] |= q_stride[Q] << 24;
     SLHA_CUDA(cudaMemcpyAsync(p->d_items, all.data(), all.size() * sizeof(WorkItem), cudaMemcpyHostToDevice, c->stream));
     SLHA_CUDA(cudaMemcpyAsync(p->d_q_list_begin, q_begin.data(), nq * 4, cudaMemcpyHostToDevice, c->stream));
     SLHA_CUDA(cudaMemcpyAsync(p->d_q_list_count, q_count.data(), nq * 4, cudaMemcpyHostToDevice, c->stream));
-    SLHA_CUDA(cudaStreamSynchronize(c->stream));  // host vectors die with this scope
-    slot = std::move(p);
+    *out = p;
     return Status();
 }
 
@@ -318,12 +359,11 @@ Status launch_score_full(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
 Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* state,
                          const SlhaB200Segment* segs, size_t n_segs, const float* d_q_coarse,
                          const uint64_t* d_q_sign, size_t nq, uint32_t k, uint32_t* d_out_index,
-                         float* d_out_score, uint32_t* d_out_count, bool prefer_generic) {
+                         float* d_out_score, uint32_t* d_out_count, bool prefer_generic, int codec_hint) {
     if (nq == 0) return Status();
     if (k == 0 || k > 8192) return Status(SLHA_ERR_DIMENSION, "top-k: k must be in 1..8192");
-    static thread_local std::unique_ptr<Plan> cache;
-    SLHA_TRY(build_plan(c, tiles, segs, n_segs, nq, k, cache));
-    Plan* p = cache.get();
+    Plan* p = nullptr;
+    SLHA_TRY(build_plan(c, tiles, segs, n_segs, nq, k, codec_hint, &p));
     const int nwarps = p->threads / 32;
     const bool timed = g_timing.calls < g_timing.max_calls;
     cudaEvent_t* tev = timed ? &g_timing.ev[3 * g_timing.calls] : nullptr;
