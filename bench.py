@@ -295,7 +295,10 @@ def gpu_arm(args, w):
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
-    stream = torch.cuda.current_stream()
+    # one explicit stream for torch and the library: the library treats a NULL stream as
+    # "use my own non-blocking stream", which would not be ordered after torch's default stream
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
     S.set_stream(stream.cuda_stream)
 
     tiles, segs, q_coarse, q_sign, n_tiles, enc_rate = build_shard(S, torch, w, rank, world, dev)

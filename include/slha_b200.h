@@ -148,7 +148,10 @@ int32_t slha_b200_device_count(void);
 /* Select the device used by the calling thread's subsequent calls. */
 int32_t slha_b200_set_device(int32_t device);
 /* Use `cuda_stream` (a cudaStream_t) for the calling thread's subsequent
- * calls; NULL restores the library's own per-device stream. */
+ * calls; NULL restores the library's own per-device stream, which is
+ * non-blocking: it is NOT ordered after work on the CUDA default stream.
+ * A caller whose producers run on the default stream passes cudaStreamLegacy
+ * or cudaStreamPerThread explicitly, or synchronizes before calling. */
 int32_t slha_b200_set_stream(void* cuda_stream);
 /* Kernels launched by this library in this process so far. */
 uint64_t slha_b200_launch_count(void);

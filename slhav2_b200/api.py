@@ -169,7 +169,10 @@ def set_device(i):
 
 
 def set_stream(stream):
-    """cudaStream_t address (e.g. torch.cuda.current_stream().cuda_stream) or None."""
+    """cudaStream_t address of a stream the caller created (e.g. torch.cuda.Stream().cuda_stream), or
+    None / 0 for the library's own non-blocking stream.  0 is NOT the CUDA default stream here: work
+    a framework enqueued on its default stream is not ordered before calls made on the library's stream,
+    so either synchronize first or pass a real stream (cudaStreamLegacy is the handle 1)."""
     _check(load_library().slha_b200_set_stream(stream))
 
 

@@ -281,7 +281,8 @@ struct ScoreArgs {
     uint64_t score_stride;
     // top-k mode
     uint32_t k, cap;
-    uint64_t* cand_keys;      // [n_lists][k]
+    uint32_t list_cap;        // slots per candidate list (>= k)
+    uint64_t* cand_keys;      // [n_lists][list_cap]
     uint32_t* cand_cnt;       // [n_lists]
     // implicit work decomposition (items == nullptr): every CTA takes
     // `item_tiles` consecutive tiles of one array against the launch's queries
@@ -427,7 +428,7 @@ __global__ void __launch_bounds__(256) score_kernel(ScoreArgs a) {
         for (int g = 0; g < (int)it.n_queries; ++g) {
             if (cnt[g] > (int)a.k) block_select_topk(keys + (size_t)g * a.cap, &cnt[g], a.k, &pivot[g], hist);
             const int c = cnt[g];
-            uint64_t* dst = a.cand_keys + (size_t)(it.list_begin + g) * a.k;
+            uint64_t* dst = a.cand_keys + (size_t)(it.list_begin + g) * a.list_cap;
             for (int i = tid; i < c; i += blockDim.x) dst[i] = keys[(size_t)g * a.cap + i];
             if (tid == 0) a.cand_cnt[it.list_begin + g] = (uint32_t)c;
         }
@@ -569,6 +570,7 @@ Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Se
         a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);
         a.k = k;
         a.cap = cap;
+        a.list_cap = k;
         a.cand_keys = sc->cand_keys;
         a.cand_cnt = sc->cand_cnt;
         score_kernel<4, true><<<n_items, threads, score_smem_bytes(4, nwarps, true, cap), c->stream>>>(a);
@@ -587,3 +589,17 @@ Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Se
 }
 
 }  // namespace slha
+
+#ifdef SLHA_SCORE_PROFILE
+extern "C" int slha_debug_score_prof(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, slha::g_score_prof, sizeof(unsigned long long) * 148 * 8);
+}
+extern "C" int slha_debug_sel_prof(unsigned long long* out, int reset) {
+    int rc = (int)cudaMemcpyFromSymbol(out, slha::g_sel_prof, sizeof(unsigned long long) * 148 * 8);
+    if (reset) {
+        static unsigned long long zero[148 * 8];
+        cudaMemcpyToSymbol(slha::g_sel_prof, zero, sizeof(zero));
+    }
+    return rc;
+}
+#endif

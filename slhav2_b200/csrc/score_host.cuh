@@ -17,8 +17,8 @@ int env_int(const char* name, int dflt) {
 }
 
 size_t mma_smem_bytes(int nwarps, uint32_t cap, bool nf4_table) {
-    return (size_t)(nf4_table ? NF4_LUT_BYTES : 0) + (size_t)nwarps * MMA_DEPTH * MMA_SET_BYTES + (size_t)4 * cap * 8 + 4 * 8 +
-           (4 + 2 + 2 + 260) * 4 + 16;
+    return (size_t)(nf4_table ? NF4_LUT_BYTES : 0) + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE + (size_t)4 * cap * 8 + 4 * 8 +
+           (4 + 4 + SEL_HIST_INTS) * 4 + 16;
 }
 
 size_t score_smem_bytes(int G, int nwarps, bool topk, uint32_t cap) {
@@ -59,7 +59,7 @@ uint32_t merge_cap(uint64_t total, uint32_t kp2) {
     const uint64_t want = std::max<uint64_t>(kp2, (total + 255) / 256 * 256);
     return (uint32_t)std::min<uint64_t>(want, std::max<uint32_t>(kp2, 24576));
 }
-size_t merge_smem(uint32_t cap_s) { return (size_t)cap_s * 8 + 8 + 264 * 4; }
+size_t merge_smem(uint32_t cap_s) { return (size_t)cap_s * 8 + 8 + (SEL_HIST_INTS + 4) * 4; }
 
 // Optional per-call CUDA-event timing of the two kernels of score_topk
 // (slha_b200_timing_begin / _end).  Events are recorded on the launching stream.
@@ -105,6 +105,7 @@ struct Plan {
     unsigned long long* d_gpivot = nullptr;  // per query: best selection threshold any CTA has proven so far
     uint32_t n_items = 0;
     uint32_t max_parts = 1;  // most candidate lists any query has
+    uint32_t list_cap = 0;   // slots per candidate list: k plus the slack the tensor-core kernel's last selection may leave
     bool use_mma = false;
     bool nf4_table = true;
     int codec_hint_in = -1;
@@ -275,7 +276,8 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     SLHA_TRY(p->b_items.ensure(all.size() * sizeof(WorkItem)));
     SLHA_TRY(p->b_qbegin.ensure(nq * 4));
     SLHA_TRY(p->b_qcount.ensure(nq * 4));
-    SLHA_TRY(p->b_keys.ensure((size_t)n_lists * k * 8));
+    p->list_cap = (k + std::max<uint32_t>(64, k / 4) + 31) / 32 * 32;
+    SLHA_TRY(p->b_keys.ensure((size_t)n_lists * p->list_cap * 8));
     SLHA_TRY(p->b_cnt.ensure((size_t)n_lists * 4));
     SLHA_TRY(p->b_retry.ensure(all.size() * 4));
     SLHA_TRY(p->b_cta.ensure(cta_begin.size() * 4));
@@ -384,6 +386,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.q_coarse = d_q_coarse;
         a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);
         a.k = k;
+        a.list_cap = p->list_cap;
         a.cap = p->mma_cap;
         a.cand_keys = p->d_cand_keys;
         a.cand_cnt = p->d_cand_cnt;
@@ -405,14 +408,15 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.q_coarse = d_q_coarse;
         a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);
         a.k = k;
+        a.list_cap = p->list_cap;
         a.cap = p->cap;
         a.cand_keys = p->d_cand_keys;
         a.cand_cnt = p->d_cand_cnt;
         SLHA_TRY(launch_score<true>(c, cl.G, a, cl.count, p->threads, score_smem_bytes(cl.G, nwarps, true, p->cap)));
     }
     if (timed) SLHA_CUDA(cudaEventRecord(tev[1], c->stream));
-    CompLists L{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, k};
-    const uint32_t cap_s = merge_cap(p->max_parts * k, p->kp2);
+    CompLists L{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, p->list_cap};
+    const uint32_t cap_s = merge_cap((uint64_t)p->max_parts * p->list_cap, p->kp2);
     const size_t smem = merge_smem(cap_s);
     static thread_local bool configured = false;
     if (!configured) {

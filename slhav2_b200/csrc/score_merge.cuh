@@ -10,7 +10,7 @@ namespace {
 
 // Candidate accessors: element e of query Q as a composite key, 0 = absent.
 struct CompLists {  // lists written by score_kernel
-    const uint64_t* keys;      // [n_lists][k]
+    const uint64_t* keys;      // [n_lists][k] (k here = slots per list, >= the k asked for)
     const uint32_t* cnt;       // [n_lists]
     const uint32_t* q_list_begin;  // [nq]
     const uint32_t* q_list_count;  // [nq]: parts in bits 0..23, list stride between parts in bits 24..31
@@ -84,8 +84,8 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
     extern __shared__ __align__(16) unsigned char smem[];
     uint64_t* buf = reinterpret_cast<uint64_t*>(smem);  // [cap_s]
     uint64_t* pivot_s = buf + cap_s;                    // [1]
-    int* hist = reinterpret_cast<int*>(pivot_s + 1);    // 260 (+2)
-    int* n_s = hist + 260;
+    int* hist = reinterpret_cast<int*>(pivot_s + 1);    // SEL_HIST_INTS
+    int* n_s = hist + SEL_HIST_INTS;
     const uint32_t Q = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const uint32_t T = L.size(Q);
 
@@ -110,7 +110,14 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
         __syncthreads();
         const uint32_t present = (uint32_t)*n_s;
         __syncthreads();
-        if (present > k) block_select_topk(buf, n_s, k, pivot_s, hist);
+        if (present > k) {
+            // bucket selection on the score word; equal scores around the k-th place
+            // fall back to the exact radix selection, which also orders by index
+            if (tid == 0) *pivot_s = 0ull;
+            __syncthreads();
+            if (block_select_multi(buf, cap_s, n_s, 1, k, 0u, (int)k, pivot_s, hist))
+                block_select_topk(buf, n_s, k, pivot_s, hist);
+        }
         const uint32_t m = present < k ? present : k;
         for (uint32_t i = m + tid; i < kp2; i += nt) buf[i] = 0ull;
         __syncthreads();
@@ -118,6 +125,106 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
         return;
     }
 
+    // Too many candidates for shared memory: one bucket pass over the lists where
+    // they lie (256 equal-width score buckets between the smallest and the largest
+    // score) finds a score bound that at least k candidates reach; when those fit,
+    // they alone are gathered and the selection finishes in shared memory.
+    {
+        uint32_t* rng = reinterpret_cast<uint32_t*>(hist + 1024);  // [0] min, [1] max, [2] gathered
+        if (tid == 0) { rng[0] = 0xFFFFFFFFu; rng[1] = 0u; rng[2] = 0u; *n_s = 0; }
+        for (uint32_t b = tid; b < 256; b += nt) hist[b] = 0;
+        __syncthreads();
+        uint32_t mn = 0xFFFFFFFFu, mx = 0u;
+        for (uint32_t l = 0; l < L.lists(Q); ++l) {
+            const uint32_t len = L.list_len(Q, l);
+            for (uint32_t j = tid; j < len; j += nt) {
+                const uint64_t key = L.at(Q, l, j);
+                if (key) { const uint32_t h = (uint32_t)(key >> 32); mn = min(mn, h); mx = max(mx, h); }
+            }
+        }
+        mn = __reduce_min_sync(0xFFFFFFFFu, mn);
+        mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+        if ((tid & 31) == 0) { atomicMin(&rng[0], mn); atomicMax(&rng[1], mx); }
+        __syncthreads();
+        float smin, inv;
+        const uint32_t lo = rng[0], hi = rng[1];
+        if (sel_range(lo, hi, smin, inv)) {
+            for (uint32_t l = 0; l < L.lists(Q); ++l) {
+                const uint32_t len = L.list_len(Q, l);
+                for (uint32_t j = tid; j < len; j += nt) {
+                    const uint64_t key = L.at(Q, l, j);
+                    if (key) atomicAdd(&hist[sel_bucket((uint32_t)(key >> 32), smin, inv)], 1);
+                }
+            }
+            __syncthreads();
+            if (tid < 32) {
+                // lane l owns buckets 255-8l .. 248-8l (descending)
+                int c[8], tot = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { c[j] = hist[255 - 8 * tid - j]; tot += c[j]; }
+                int incl = tot;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                    if ((int)tid >= o) incl += y;
+                }
+                const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= (int)k);
+                int bsel = -1, kept = 0;  // fewer than k present: everything stays
+                if (ok) {
+                    const int src = __ffs(ok) - 1;
+                    if ((int)tid == src) {
+                        int run = incl - tot;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (run + c[j] >= (int)k) { bsel = 255 - 8 * tid - j; kept = run + c[j]; break; }
+                            run += c[j];
+                        }
+                    }
+                    bsel = __shfl_sync(0xFFFFFFFFu, bsel, src);
+                    kept = __shfl_sync(0xFFFFFFFFu, kept, src);
+                } else {
+                    kept = __shfl_sync(0xFFFFFFFFu, incl, 31);
+                    bsel = 0;
+                }
+                if (tid == 0) { hist[256] = bsel; hist[257] = kept; }
+            }
+            __syncthreads();
+            const int bsel = hist[256];
+            const uint32_t kept = (uint32_t)hist[257];
+            if (kept <= cap_s) {
+                for (uint32_t l = 0; l < L.lists(Q); ++l) {
+                    const uint32_t len = L.list_len(Q, l);
+                    for (uint32_t j0 = 0; j0 < len; j0 += nt) {
+                        const uint32_t j = j0 + tid;
+                        const uint64_t key = j < len ? L.at(Q, l, j) : 0ull;
+                        const bool keep = key != 0ull && sel_bucket((uint32_t)(key >> 32), smin, inv) >= bsel;
+                        const unsigned bal = __ballot_sync(0xFFFFFFFFu, keep);
+                        int base = 0;
+                        if ((tid & 31) == 0 && bal) base = atomicAdd(n_s, __popc(bal));
+                        base = __shfl_sync(0xFFFFFFFFu, base, 0);
+                        if (keep) buf[base + __popc(bal & ((1u << (tid & 31)) - 1))] = key;
+                    }
+                }
+                __syncthreads();
+                const uint32_t present = (uint32_t)*n_s;
+                __syncthreads();
+                if (present > k) {
+                    if (tid == 0) *pivot_s = 0ull;
+                    __syncthreads();
+                    if (block_select_multi(buf, cap_s, n_s, 1, k, 0u, (int)k, pivot_s, hist))
+                        block_select_topk(buf, n_s, k, pivot_s, hist);
+                }
+                const uint32_t m = present < k ? present : k;
+                for (uint32_t i = m + tid; i < kp2; i += nt) buf[i] = 0ull;
+                __syncthreads();
+                sort_and_emit(buf, kp2, m, k, Q, out_index, out_score, out_count);
+                return;
+            }
+        }
+        __syncthreads();
+    }
+
+    // last resort (scores piled up in one bucket, or non-finite): radix selection over the lists
     // number of present candidates
     if (tid == 0) hist[259] = 0;
     __syncthreads();

@@ -9,17 +9,22 @@
 //   A (16 tiles x 16 dims)  = the group's nibbles turned into exact fp16 levels
 //                             (n - 8 by an fp16 magic-number trick, or the NF4
 //                             codebook entry as an fp16 hi + lo pair from a
-//                             bank-replicated shared-memory table),
+//                             bank-replicated shared-memory table); odd k slots
+//                             hold 16x the level, which the trick yields for free,
 //   B (16 dims x 8 columns) = the four queries, each as an fp16 hi and lo
 //                             column (q = hi + lo keeps ~22 bits), so a thread's
-//                             two accumulator columns add up to one query,
+//                             two accumulator columns add up to one query; even k
+//                             slots hold 16x the query, so every product is 16x
+//                             and the sum is divided by 16 at the end (exact),
 //   D fp32, started from zero for every group and folded into the running score
 //   with the tile's effective group scale (scale * gs[j] / 255) on the CUDA
 //   cores, which is what keeps per-group micro-scaling exact.
 // The MMA's k index is permuted (identically for A and B) so that the four k
 // slots a thread owns are the four nibbles of one 16-bit word of the tile.
-// The Hamming term (8 XOR + POPC per tile and query), tile staging (cp.async
-// into an XOR-swizzled ring) and the streaming top-k are as in score_kernel.
+// The Hamming term is 8 XOR + POPC per tile and query.  Tiles are staged by
+// cp.async into a per-warp ring whose rows are padded to 144 bytes: every
+// shared-memory address of the inner loop is then "row base + immediate" and
+// all fragment loads are conflict-free without an XOR swizzle.
 // Tiles of any other codec make the CTA hand the whole work item back
 // (retry flag) to score_kernel, which is launched right after.
 #pragma once
@@ -28,10 +33,16 @@ namespace slha {
 namespace {
 
 constexpr int MMA_SET_TILES = 16;
-constexpr int MMA_SET_BYTES = MMA_SET_TILES * TILE_BYTES;  // 2 KiB
-constexpr int MMA_DEPTH = 3;                               // cp.async ring slots per warp
-constexpr int MMA_NS = 1;                                  // sets per warp between checks of the reselect flag
+constexpr int MMA_SET_BYTES = MMA_SET_TILES * TILE_BYTES;  // 2 KiB of tiles in global memory
+constexpr int MMA_ROW = TILE_BYTES + 16;                   // padded row of the staging ring
+constexpr int MMA_SET_STRIDE = MMA_SET_TILES * MMA_ROW;    // one staged set
+constexpr int MMA_HALF = 8 * MMA_ROW;                      // row g -> row g + 8
+#ifndef SLHA_MMA_DEPTH
+#define SLHA_MMA_DEPTH 2
+#endif
+constexpr int MMA_DEPTH = SLHA_MMA_DEPTH;                  // cp.async ring slots per warp
 constexpr int NF4_LUT_BYTES = 256 * 16 * 8;                // [byte][16 lanes] x (hi pair, lo pair)
+constexpr int SEL_HIST_INTS = 4 * 256 + 32;                // block_select_multi: 4 histograms + state
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
@@ -62,12 +73,20 @@ __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c
     asm("fma.rn.f16x2 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-// Two nibbles of byte `sel` of w -> half2 (n_lo - 8, n_hi - 8), exact.
-//   (byte, byte) masked to (n_lo | n_hi << 20) OR-ed into 1024.0h gives
-//   (1024 + n_lo, 1024 + 16 n_hi); one fp16 FMA by (1, 1/16) + (-1032, -72).
-__device__ __forceinline__ uint32_t int4_pair(uint32_t w, uint32_t sel) {
-    const uint32_t v = lop3_and_or(prmt(w, 0u, sel), 0x00F0000Fu, 0x64006400u);
-    return hfma2_u32(v, 0x2C003C00u, 0xD480E408u);
+// The four nibbles n0..n3 of a 16-bit word h (n0 lowest) -> half2 (n0 - 8, 16 (n1 - 8))
+// and half2 (n2 - 8, 16 (n3 - 8)), exact.  h duplicated into both halves of a word
+// has n0 at bit 0 and n1 at bit 20 (after >> 8: n2 and n3); OR-ing those into
+// 1024.0h gives (1024 + n0, 1024 + 16 n1), and one fp16 add of (-1032, -1152)
+// finishes.  The odd slots carry 16x the level: the B operand carries 16x the query
+// in the even slots instead, and the final score is divided by 16 (all exact).
+// `magic` is 0x64006400 held in a register the compiler cannot rebuild from an immediate.
+__device__ __forceinline__ void int4_quad(uint32_t h, uint32_t magic, uint32_t& lo, uint32_t& hi) {
+    const uint32_t t = h * 0x10001u;
+    uint32_t v0, v1;
+    asm("lop3.b32 %0, %1, 0x00F0000F, %2, 0xEA;\n" : "=r"(v0) : "r"(t), "r"(magic));
+    asm("lop3.b32 %0, %1, 0x00F0000F, %2, 0xEA;\n" : "=r"(v1) : "r"(t >> 8), "r"(magic));
+    asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(lo) : "r"(v0), "r"(0xE480E408u));
+    asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(hi) : "r"(v1), "r"(0xE480E408u));
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
@@ -76,89 +95,409 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 __device__ __forceinline__ float half_residual(float x) {  // x - fp16(x)
     return x - __half2float(__float2half_rn(x));
 }
-// shared-memory loads on 32-bit shared-window addresses (keeps the address math 32-bit)
+// shared-memory loads on 32-bit shared-window addresses plus an immediate
 template <int IMM>
-__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(addr), "n"(IMM));
-    return v;
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1+%2];\n" : "=h"(v) : "r"(addr), "n"(IMM));
+    return (uint32_t)v;
 }
+template <int IMM>
 __device__ __forceinline__ uint2 lds_v2(uint32_t addr) {
     uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(IMM));
     return v;
 }
 template <int IMM>
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr), "n"(IMM));
+    return v;
+}
+template <int SRC_IMM, int DST_IMM>
 __device__ __forceinline__ void cp_async16_s(uint32_t dst, const unsigned char* src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1+%2], 16, %3;\n" ::"r"(dst), "l"(src), "n"(IMM), "r"(src_bytes));
+    asm volatile("cp.async.cg.shared.global [%0+%1], [%2+%3], 16, %4;\n" ::"r"(dst), "n"(DST_IMM), "l"(src), "n"(SRC_IMM),
+                 "r"(src_bytes));
 }
 __device__ __forceinline__ int popc8(const uint4& a, const uint4& b, const uint32_t (&q)[8]) {
     return __popc(a.x ^ q[0]) + __popc(a.y ^ q[1]) + __popc(a.z ^ q[2]) + __popc(a.w ^ q[3]) +
            __popc(b.x ^ q[4]) + __popc(b.y ^ q[5]) + __popc(b.z ^ q[6]) + __popc(b.w ^ q[7]);
 }
 
-// Per-thread constants of the fragment gather.
-struct LaneConst {
-    uint32_t cw[4];     // byte offset (in a tile row) of my word of groups 2c, 2c+1: ((c ^ g) << 4) + 4*(t>>1)
-    uint32_t c4, c5, c6, c7;  // byte offsets of the residual / metadata chunks
-    uint32_t sel0, sel1;      // prmt selectors of my two latent bytes
-    uint32_t sh0, sh1;        // right shifts that bring (my byte << 7) to bits 7..14 (NF4 table index)
-    uint32_t lut_lane;        // shared address of my replica column of the NF4 table
-};
-
 // Coarse sums of one 16-tile set for rows g (acc0) and g+8 (acc1), query t.
+// hb = shared address of row g of the set + 2t: halfword t of every 8-byte scale
+// group holds the four nibbles this thread feeds to the MMA of that group.
 // MODE 0: every row uniform INT4, 1: every row NF4, 2: per-row choice.
-template <int MODE>
-__device__ __forceinline__ void coarse_set(uint32_t r0, uint32_t r1, const LaneConst& L, const uint32_t (&bq)[8][2],
-                                           uint32_t f0, uint32_t f1, const uint4& x0, const uint4& x1,
-                                           float& acc0, float& acc1) {
-    acc0 = 0.0f;
-    acc1 = 0.0f;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const uint32_t ad0 = r0 + L.cw[c], ad1 = r1 + L.cw[c];
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-            const int j = 2 * c + jj;
-            const uint32_t w0 = jj ? lds_u32<8>(ad0) : lds_u32<0>(ad0);
-            const uint32_t w1 = jj ? lds_u32<8>(ad1) : lds_u32<0>(ad1);
-            uint32_t a0, a1, a2, a3, l0 = 0, l1 = 0, l2 = 0, l3 = 0;
-            const bool n0 = MODE == 1 || (MODE == 2 && (f0 & F_NF4));
-            const bool n1 = MODE == 1 || (MODE == 2 && (f1 & F_NF4));
-            if (MODE != 0 && n0) {
-                const uint2 e0 = lds_v2(L.lut_lane + ((__funnelshift_r(w0, w0, L.sh0)) & 0x7F80u));
-                const uint2 e1 = lds_v2(L.lut_lane + ((__funnelshift_r(w0, w0, L.sh1)) & 0x7F80u));
-                a0 = e0.x; a2 = e1.x; l0 = e0.y; l2 = e1.y;
-            } else {
-                a0 = int4_pair(w0, L.sel0);
-                a2 = int4_pair(w0, L.sel1);
-            }
-            if (MODE != 0 && n1) {
-                const uint2 e0 = lds_v2(L.lut_lane + ((__funnelshift_r(w1, w1, L.sh0)) & 0x7F80u));
-                const uint2 e1 = lds_v2(L.lut_lane + ((__funnelshift_r(w1, w1, L.sh1)) & 0x7F80u));
-                a1 = e0.x; a3 = e1.x; l1 = e0.y; l3 = e1.y;
-            } else {
-                a1 = int4_pair(w1, L.sel0);
-                a3 = int4_pair(w1, L.sel1);
-            }
-            float d[4];
-            mma_f16_zero(d, a0, a1, a2, a3, bq[j][0], bq[j][1]);
-            if (MODE != 0) mma_f16(d, l0, l1, l2, l3, bq[j][0], bq[j][1]);
-            // gs[j] as float: byte j of (x.z, x.w) dropped into the mantissa of 2^23
-            const uint32_t gw0 = j < 4 ? x0.z : x0.w, gw1 = j < 4 ? x1.z : x1.w;
-            const float gs0 = __uint_as_float(prmt(gw0, 0x4B000000u, 0x7440u + (j & 3))) - 8388608.0f;
-            const float gs1 = __uint_as_float(prmt(gw1, 0x4B000000u, 0x7440u + (j & 3))) - 8388608.0f;
-            acc0 = fmaf(d[0] + d[1], gs0, acc0);
-            acc1 = fmaf(d[2] + d[3], gs1, acc1);
-        }
+template <int MODE, int J>
+__device__ __forceinline__ void coarse_group(uint32_t hb, uint32_t lut_lane, uint32_t magic, const uint32_t (&bq)[8][2], uint32_t f0,
+                                             uint32_t f1, const uint4& x0, const uint4& x1, float& acc0, float& acc1) {
+    const uint32_t h0 = lds_u16<8 * J>(hb), h1 = lds_u16<8 * J + MMA_HALF>(hb);
+    uint32_t a0, a1, a2, a3, l0 = 0, l1 = 0, l2 = 0, l3 = 0;
+    const bool n0 = MODE == 1 || (MODE == 2 && (f0 & F_NF4));
+    const bool n1 = MODE == 1 || (MODE == 2 && (f1 & F_NF4));
+    if (MODE != 0 && n0) {
+        // table entry of byte b at lut_lane + 128 b
+        const uint2 e0 = lds_v2<0>(lut_lane + ((h0 & 0xFFu) << 7));
+        const uint2 e1 = lds_v2<0>(lut_lane + ((h0 >> 8) << 7));
+        a0 = e0.x; a2 = e1.x; l0 = e0.y; l2 = e1.y;
+    } else {
+        int4_quad(h0, magic, a0, a2);
     }
+    if (MODE != 0 && n1) {
+        const uint2 e0 = lds_v2<0>(lut_lane + ((h1 & 0xFFu) << 7));
+        const uint2 e1 = lds_v2<0>(lut_lane + ((h1 >> 8) << 7));
+        a1 = e0.x; a3 = e1.x; l1 = e0.y; l3 = e1.y;
+    } else {
+        int4_quad(h1, magic, a1, a3);
+    }
+    float d[4];
+    mma_f16_zero(d, a0, a1, a2, a3, bq[J][0], bq[J][1]);
+    if (MODE != 0) mma_f16(d, l0, l1, l2, l3, bq[J][0], bq[J][1]);
+    // gs[J] as float: byte J of (x.z, x.w)
+    const uint32_t gw0 = J < 4 ? x0.z : x0.w, gw1 = J < 4 ? x1.z : x1.w;
+    acc0 = fmaf(d[0] + d[1], __uint2float_rn(__byte_perm(gw0, 0u, 0x4440 + (J & 3))), acc0);
+    acc1 = fmaf(d[2] + d[3], __uint2float_rn(__byte_perm(gw1, 0u, 0x4440 + (J & 3))), acc1);
 }
 
+template <int MODE>
+__device__ __forceinline__ void coarse_set(uint32_t hb, uint32_t lut_lane, uint32_t magic, const uint32_t (&bq)[8][2], uint32_t f0,
+                                           uint32_t f1, const uint4& x0, const uint4& x1, float& acc0, float& acc1) {
+    acc0 = 0.0f;
+    acc1 = 0.0f;
+    coarse_group<MODE, 0>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+    coarse_group<MODE, 1>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+    coarse_group<MODE, 2>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+    coarse_group<MODE, 3>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+    coarse_group<MODE, 4>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+    coarse_group<MODE, 5>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+    coarse_group<MODE, 6>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+    coarse_group<MODE, 7>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+}
+
+#ifdef SLHA_SCORE_PROFILE
+// development aid (never built into the shipped library): per-CTA cycle counts of warp 0
+__device__ unsigned long long g_score_prof[148 * 8];
+__device__ unsigned long long g_sel_prof[148 * 8];  // calls, passes, refines, ties, cycles: minmax, passes, compaction
+#define SEL_ADD(i, v) do { if (threadIdx.x == 0 && nq > 1 && blockIdx.x < 148) atomicAdd(&g_sel_prof[blockIdx.x * 8 + (i)], (unsigned long long)(v)); } while (0)
+#define PROF_T(x) const long long x = clock64()
+#define PROF_ADD(i, v) do { if (tid == 0) prof[i] += (unsigned long long)(v); } while (0)
+#else
+#define SEL_ADD(i, v)
+#define PROF_T(x)
+#define PROF_ADD(i, v)
+#endif
+
+// Bucket of a score inside [smin, smin + 256 / inv): monotone in the score.
+__device__ __forceinline__ int sel_bucket(uint32_t h, float smin, float inv) {
+    const int b = (int)((key_score(h) - smin) * inv);
+    return b < 0 ? 0 : (b > 255 ? 255 : b);
+}
+// Range [lo, hi] (order keys of scores) -> (smin, inv); false when the range cannot
+// be bucketed (one single score, or a non-finite bound).
+__device__ __forceinline__ bool sel_range(uint32_t lo, uint32_t hi, float& smin, float& inv) {
+    smin = key_score(lo);
+    const float smax = key_score(hi);
+    inv = 256.0f / (smax - smin);
+    return hi > lo && isfinite(smin) && isfinite(smax) && isfinite(inv);
+}
+
+// Shrinks up to four candidate buffers (keys[q][cap], counts cnt[q]) to between k
+// and k + slack entries each and raises pivot[q] accordingly; only buffers with
+// more than `trigger` entries are touched.  The four queries share every barrier.
+//
+// Selection works on the score (high word of the composite key): 256 equal-width
+// buckets over [min, max] of the scores at or above the pivot; the bucket in which
+// the count from the top reaches k is kept whole if that leaves at most k + slack
+// keys, otherwise it becomes the next range.  Scores spread smoothly over such a
+// range, so the histogram atomics do not pile up on one address the way the bytes
+// of the key do.  Keys below the current pivot are dropped (the pivot is a proven
+// lower bound of the query's k-th best key).  The new pivot is the smallest kept
+// score.  Queries whose range collapses to one score with too many keys (equal
+// scores), or holds a non-finite score, are reported in the returned bit mask
+// (uniform over the block) and left for block_select_topk, which also orders by
+// index.  hist: SEL_HIST_INTS ints.  All threads of the block must call.
+__device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, int nq, uint32_t k, uint32_t slack,
+                                       int trigger, uint64_t* pivot, int* hist) {
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
+    // [q][8]: 0 range lo, 1 range hi, 2 need, 3 active, 4 exact selection wanted, 5 kept, 6 selected, 7 pivotal bucket
+    uint32_t* st = reinterpret_cast<uint32_t*>(hist + 1024);
+    if (tid < 4) {
+        const bool act = tid < nq && cnt[tid] > trigger;
+        uint32_t* s = st + 8 * tid;
+        s[0] = 0xFFFFFFFFu;
+        s[1] = 0u;
+        s[2] = k;
+        s[3] = act;
+        s[4] = 0u;
+        s[5] = 0u;
+        s[6] = act;
+        s[7] = 0u;
+        if (act && cnt[tid] > (int)cap) cnt[tid] = (int)cap;
+    }
+    __syncthreads();
+    if (!(st[6] | st[14] | st[22] | st[30])) return 0u;
+    SEL_ADD(0, 1);
+    PROF_T(ts0);
+    // smallest and largest score at or above the pivot
+    for (int q = 0; q < nq; ++q) {
+        if (!st[8 * q + 3]) continue;
+        const uint64_t* kq = keys + (size_t)q * cap;
+        const uint32_t floor_h = (uint32_t)(pivot[q] >> 32);
+        uint32_t mx = 0u, mn = 0xFFFFFFFFu;
+        const int c = cnt[q];
+#pragma unroll 4
+        for (int i = tid; i < c; i += nt) {
+            const uint32_t h = (uint32_t)(kq[i] >> 32);
+            if (h >= floor_h) { mx = max(mx, h); mn = min(mn, h); }
+        }
+        mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+        mn = __reduce_min_sync(0xFFFFFFFFu, mn);
+        if (lane == 0) { atomicMax(&st[8 * q + 1], mx); atomicMin(&st[8 * q], mn); }
+    }
+    __syncthreads();
+    PROF_T(ts1);
+    SEL_ADD(4, ts1 - ts0);
+    for (int pass = 0; pass < 12; ++pass) {
+        if (!(st[3] | st[11] | st[19] | st[27])) break;
+        SEL_ADD(1, 1);
+        for (int b = tid; b < 1024; b += nt) hist[b] = 0;
+        __syncthreads();
+        for (int q = 0; q < nq; ++q) {
+            if (!st[8 * q + 3]) continue;
+            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
+            float smin, inv;
+            if (!sel_range(lo, hi, smin, inv)) continue;  // settled by the scan below
+            const uint64_t* kq = keys + (size_t)q * cap;
+            // four keys per round: the loads go out together, then the atomics
+            const int c = cnt[q];
+            for (int i0 = tid; i0 < c; i0 += 4 * nt) {
+                uint32_t h[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) h[u] = i0 + u * nt < c ? (uint32_t)(kq[i0 + u * nt] >> 32) : 0u;
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (i0 + u * nt < c && h[u] >= lo && h[u] <= hi) atomicAdd(&hist[256 * q + sel_bucket(h[u], smin, inv)], 1);
+            }
+        }
+        __syncthreads();
+        bool refine = false;
+        if (warp < nq && st[8 * warp + 3]) {
+            uint32_t* s = st + 8 * warp;
+            const int* hq = hist + 256 * warp;
+            const uint32_t lo = s[0], hi = s[1], need = s[2];
+            float smin, inv;
+            if (!sel_range(lo, hi, smin, inv)) {
+                // everything left in the range stays; more than allowed means equal
+                // (or non-finite) scores: the exact selection sorts it out
+                __syncwarp();
+#ifdef SLHA_SCORE_PROFILE
+                if (lane == 0 && nq > 1 && atomicAdd(&g_sel_prof[148 * 8 - 1], 1ull) < 8)
+                    printf("unbucketable: cta %d q %d lo %08x hi %08x smin %g inv %g need %u cnt %d pass %d\n", blockIdx.x, warp, lo, hi, smin, inv, need, cnt[warp], pass);
+#endif
+                if (lane == 0) { s[3] = 0u; s[4] = 1u; s[7] = 0u; }
+            } else {
+                // lane l owns buckets 255-8l .. 248-8l (descending)
+                int c[8], tot = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { c[j] = hq[255 - 8 * lane - j]; tot += c[j]; }
+                int incl = tot;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                    if (lane >= o) incl += y;
+                }
+                const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= (int)need);
+                if (ok == 0u) {
+                    // fewer than `need` keys at or above the pivot: all of them stay
+                    if (lane == 0) { s[3] = 0u; s[7] = 0u; }
+                } else {
+                    int bsel = 0, run = 0, binc = 0;
+                    if (lane == __ffs(ok) - 1) {
+                        run = incl - tot;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (run + c[j] >= (int)need) { bsel = 255 - 8 * lane - j; binc = c[j]; break; }
+                            run += c[j];
+                        }
+                    }
+                    const int src = __ffs(ok) - 1;
+                    bsel = __shfl_sync(0xFFFFFFFFu, bsel, src);
+                    run = __shfl_sync(0xFFFFFFFFu, run, src);
+                    binc = __shfl_sync(0xFFFFFFFFu, binc, src);
+                    const uint32_t kept = (k - need) + (uint32_t)(run + binc);
+                    if (kept <= k + slack) {
+                        if (lane == 0) { s[3] = 0u; s[7] = (uint32_t)bsel; }
+                    } else {
+                        // next range: the scores of the pivotal bucket
+                        refine = true;
+                        __syncwarp();
+                        if (lane == 0) { s[2] = need - (uint32_t)run; s[7] = (uint32_t)bsel; }
+                    }
+                }
+            }
+        }
+        if (!__syncthreads_or(refine)) continue;
+        SEL_ADD(2, 1);
+        // smallest and largest score inside the pivotal bucket of the queries still active
+        uint32_t nlo[4], nhi[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { nlo[q] = 0xFFFFFFFFu; nhi[q] = 0u; }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (q >= nq || !st[8 * q + 3]) continue;
+            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
+            const int bsel = (int)st[8 * q + 7];
+            float smin, inv;
+            sel_range(lo, hi, smin, inv);
+            const uint64_t* kq = keys + (size_t)q * cap;
+            for (int i = tid; i < cnt[q]; i += nt) {
+                const uint32_t h = (uint32_t)(kq[i] >> 32);
+                if (h >= lo && h <= hi && sel_bucket(h, smin, inv) == bsel) { nlo[q] = min(nlo[q], h); nhi[q] = max(nhi[q], h); }
+            }
+            nlo[q] = __reduce_min_sync(0xFFFFFFFFu, nlo[q]);
+            nhi[q] = __reduce_max_sync(0xFFFFFFFFu, nhi[q]);
+        }
+        __syncthreads();  // every thread has read the old range
+        if (tid < 4 && tid < nq && st[8 * tid + 3]) { st[8 * tid] = 0xFFFFFFFFu; st[8 * tid + 1] = 0u; }
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (q < nq && st[8 * q + 3] && lane == 0) { atomicMin(&st[8 * q], nlo[q]); atomicMax(&st[8 * q + 1], nhi[q]); }
+        __syncthreads();
+    }
+    PROF_T(ts2);
+    SEL_ADD(5, ts2 - ts1);
+    // (a range that is still open after the last pass stays whole and goes to the exact selection)
+    if (tid < 4) {
+        if (st[8 * tid + 3]) { st[8 * tid + 3] = 0u; st[8 * tid + 4] = 1u; st[8 * tid + 7] = 0u; }
+        st[8 * tid + 2] = 0xFFFFFFFFu;  // from here on: the smallest score kept
+    }
+    __syncthreads();
+    // compact the selected buffers in place: keys above the last range, and those of
+    // the range whose bucket is the pivotal one or higher, stay
+    int maxc = 0;
+    for (int q = 0; q < nq; ++q)
+        if (st[8 * q + 6]) maxc = max(maxc, cnt[q]);
+    const int R = (maxc + nt - 1) / nt;
+    if (R <= 8) {
+        // every warp owns R*32 consecutive slots: it reads them all, the warps' counts are
+        // summed once, then it writes its survivors (order preserved, no read-after-write)
+        int* wcnt = hist;  // [4][32]
+#pragma unroll 1
+        for (int q = 0; q < nq; ++q) {
+            if (!st[8 * q + 6]) continue;
+            const uint32_t rlo = st[8 * q], rhi = st[8 * q + 1];
+            int bsel = (int)st[8 * q + 7];
+            float smin, inv;
+            if (!sel_range(rlo, rhi, smin, inv)) bsel = -1;  // whole range stays
+            uint64_t* kq = keys + (size_t)q * cap;
+            const int c = cnt[q];
+            uint64_t key[8];
+            unsigned bal[8];
+            int wtot = 0;
+            uint32_t km = 0xFFFFFFFFu;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                bal[j] = 0u;
+                key[j] = 0ull;
+                if (j < R) {
+                    const int i = (warp * R + j) * 32 + lane;
+                    const bool in = i < c;
+                    key[j] = in ? kq[i] : 0ull;
+                    const uint32_t h = (uint32_t)(key[j] >> 32);
+                    const bool keep = in && h >= rlo && (h > rhi || bsel < 0 || sel_bucket(h, smin, inv) >= bsel);
+                    if (keep) km = min(km, h);
+                    bal[j] = __ballot_sync(0xFFFFFFFFu, keep);
+                    wtot += __popc(bal[j]);
+                }
+            }
+            km = __reduce_min_sync(0xFFFFFFFFu, km);
+            if (lane == 0) {
+                wcnt[q * 32 + warp] = wtot;
+                if (km != 0xFFFFFFFFu) atomicMin(&st[8 * q + 2], km);
+            }
+            __syncthreads();
+            const int v = lane < (nt >> 5) ? wcnt[q * 32 + lane] : 0;
+            int run = __reduce_add_sync(0xFFFFFFFFu, lane < warp ? v : 0);
+            const int total = __reduce_add_sync(0xFFFFFFFFu, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j < R) {
+                    if (bal[j] >> lane & 1u) kq[run + __popc(bal[j] & ((1u << lane) - 1u))] = key[j];
+                    run += __popc(bal[j]);
+                }
+            }
+            if (tid == 0) st[8 * q + 5] = (uint32_t)total;
+        }
+        __syncthreads();
+    } else {
+        float smin[4], inv[4];
+        uint32_t rlo[4], rhi[4];
+        int bsel[4];
+        uint32_t kmin[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            kmin[q] = 0xFFFFFFFFu;
+            rlo[q] = rhi[q] = 0u;
+            bsel[q] = 0;
+            smin[q] = inv[q] = 0.0f;
+            if (q < nq && st[8 * q + 6]) {
+                rlo[q] = st[8 * q];
+                rhi[q] = st[8 * q + 1];
+                bsel[q] = (int)st[8 * q + 7];
+                if (!sel_range(rlo[q], rhi[q], smin[q], inv[q])) bsel[q] = -1;  // whole range stays
+            }
+        }
+        for (int i0 = 0; i0 < maxc; i0 += nt) {
+            const int i = i0 + tid;
+            uint64_t key[4];
+            bool keep[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const bool in = q < nq && st[8 * q + 6] && i < cnt[q];
+                key[q] = in ? keys[(size_t)q * cap + i] : 0ull;
+                const uint32_t h = (uint32_t)(key[q] >> 32);
+                keep[q] = in && h >= rlo[q] && (h > rhi[q] || bsel[q] < 0 || sel_bucket(h, smin[q], inv[q]) >= bsel[q]);
+                if (keep[q]) kmin[q] = min(kmin[q], h);
+            }
+            __syncthreads();  // every read of this round precedes its writes (they land below i0 + nt)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const unsigned bal = __ballot_sync(0xFFFFFFFFu, keep[q]);
+                if (bal) {
+                    int base = 0;
+                    if (lane == 0) base = (int)atomicAdd(&st[8 * q + 5], (uint32_t)__popc(bal));
+                    base = __shfl_sync(0xFFFFFFFFu, base, 0);
+                    if (keep[q]) keys[(size_t)q * cap + base + __popc(bal & ((1u << lane) - 1u))] = key[q];
+                }
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (q >= nq || !st[8 * q + 6]) continue;
+            const uint32_t m = __reduce_min_sync(0xFFFFFFFFu, kmin[q]);
+            if (lane == 0 && m != 0xFFFFFFFFu) atomicMin(&st[8 * q + 2], m);
+        }
+        __syncthreads();
+    }
+    // the new pivot: the smallest score kept
+    if (tid < 4 && st[8 * tid + 6]) {
+        cnt[tid] = (int)st[8 * tid + 5];
+        const uint64_t np = st[8 * tid + 2] == 0xFFFFFFFFu ? 0ull : (uint64_t)st[8 * tid + 2] << 32;
+        if (np > pivot[tid]) pivot[tid] = np;
+    }
+    uint32_t ties = 0u;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        if (st[8 * q + 6] && st[8 * q + 4] && st[8 * q + 5] > k + slack) ties |= 1u << q;
+    __syncthreads();
+    PROF_T(ts3);
+    SEL_ADD(6, ts3 - ts2);
+    SEL_ADD(3, ties != 0u);
+    return ties;
+}
 
 template <bool TOPK>
 __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
@@ -168,56 +507,54 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
     // shared layout: nf4 table | stage ring | [keys | pivot | cnt | ctl | hist]
     const uint32_t lut_bytes = a.nf4_table ? NF4_LUT_BYTES : 0;  // the table is left out when no NF4 tile is expected
     uint2* lut = reinterpret_cast<uint2*>(smem);
-    unsigned char* tail = smem + lut_bytes + (size_t)nwarps * MMA_DEPTH * MMA_SET_BYTES;
+    unsigned char* tail = smem + lut_bytes + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE;
     uint64_t* keys = reinterpret_cast<uint64_t*>(tail);            // [4][cap]
     uint64_t* pivot = keys + (TOPK ? (size_t)4 * a.cap : 0);       // [4]
     int* cnt = reinterpret_cast<int*>(pivot + 4);                  // [4]
     int* ctl = cnt + 4;   // [0] want: some query's buffer is nearly full  [1] arrived  [2] done warps  [3] bail
     int* bail = ctl + 3;
-    int* hist = ctl + 4;  // 260
+    int* hist = ctl + 4;  // SEL_HIST_INTS
     const uint32_t smem_s = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t stage_s = smem_s + lut_bytes + (uint32_t)warp * MMA_DEPTH * MMA_SET_BYTES;
+    const uint32_t stage_s = smem_s + lut_bytes + (uint32_t)warp * MMA_DEPTH * MMA_SET_STRIDE;
 
     // NF4 codebook as fp16 hi + lo pairs per byte (two nibbles), 16 bank-aligned replicas
     for (int e = tid; e < (a.nf4_table ? 256 * 16 : 0); e += blockDim.x) {
         const int b = e >> 4;
-        const float c0 = c_nf4[b & 15], c1 = c_nf4[b >> 4];
+        const float c0 = c_nf4[b & 15], c1 = 16.0f * c_nf4[b >> 4];  // odd slots carry 16x (see int4_quad)
         lut[e] = make_uint2(pack_half2(c0, c1), pack_half2(half_residual(c0), half_residual(c1)));
     }
-    LaneConst L;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) L.cw[c] = (uint32_t)(((c ^ g) << 4) + 4 * (t >> 1));
-    L.c4 = (uint32_t)((4 ^ g) << 4);
-    L.c5 = (uint32_t)((5 ^ g) << 4);
-    L.c6 = (uint32_t)((6 ^ g) << 4);
-    L.c7 = (uint32_t)((7 ^ g) << 4);
-    L.sel0 = (t & 1) ? 0x4242u : 0x4040u;
-    L.sel1 = (t & 1) ? 0x4343u : 0x4141u;
-    L.sh0 = (t & 1) ? 9u : 25u;
-    L.sh1 = (t & 1) ? 17u : 1u;
-    L.lut_lane = smem_s + (uint32_t)(lane & 15) * 8u;
-    // cp.async of a set: lane copies 16-byte chunks lane, lane+32, lane+64, lane+96
-    uint32_t dst_off[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int r = (lane >> 3) + 4 * i, c = lane & 7;
-        dst_off[i] = (uint32_t)(r * TILE_BYTES + ((c ^ (r & 7)) << 4));
-    }
+    const uint32_t lut_lane = smem_s + (uint32_t)(lane & 15) * 8u;
+    uint32_t magic;  // 1024.0h twice, opaque so that it stays in one register
+    asm volatile("mov.u32 %0, 0x64006400;\n" : "=r"(magic));
+    // cp.async of a set: lane copies the 16-byte chunks lane, lane+32, lane+64, lane+96,
+    // i.e. chunk (lane & 7) of rows (lane >> 3) + {0, 4, 8, 12}
+    const uint32_t dst_lane = (uint32_t)((lane >> 3) * MMA_ROW + (lane & 7) * 16);
+    const uint32_t row_lane = (uint32_t)g * MMA_ROW;
     // appends may continue for up to two sets per warp after the flag is raised
     const uint32_t cap_soft = a.cap - (uint32_t)nwarps * 2 * MMA_SET_TILES;
     const uint32_t resel_min = (a.k + cap_soft) / 2;
+    const uint32_t resel_slack = (cap_soft - a.k) / 4;
     const uint32_t key_row = (uint32_t)t * a.cap;
 
+#ifdef SLHA_SCORE_PROFILE
+    unsigned long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
     const uint32_t item_end = a.cta_begin[blockIdx.x + 1];
     for (uint32_t item_id = a.cta_begin[blockIdx.x]; item_id < item_end; ++item_id) {
         const WorkItem it = a.items[item_id];
+        PROF_T(t_item);
         __syncthreads();  // previous item fully retired (and the table is visible)
-        if (TOPK && tid < 4) { cnt[tid] = 0; pivot[tid] = 0; }
+        if (TOPK && tid < 4) {
+            // start from the threshold other CTAs have already proven for the query
+            cnt[tid] = 0;
+            pivot[tid] = tid < (int)it.n_queries ? *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + tid) : 0ull;
+        }
         if (tid == 0) { ctl[0] = ctl[1] = ctl[2] = ctl[3] = 0; }
         // B fragments: column n = g is query g>>1, part g&1 (hi / lo); k slots
         // {2t, 2t+1, 2t+8, 2t+9} of group j carry dims 16j + 4t + {0,1,2,3}
         uint32_t bq[8][2];
         uint32_t qs[8];
+        bool big = false;
         {
             const int qi = g >> 1;
             const bool have = qi < (int)it.n_queries;
@@ -229,6 +566,8 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     if (!have) v[i] = 0.0f;
+                    big |= fabsf(v[i]) > 4000.0f;            // 16 v must stay inside fp16
+                    if (!(i & 1)) v[i] *= 16.0f;             // even slots carry 16x the query (see int4_quad)
                     if (g & 1) v[i] = half_residual(v[i]);
                 }
                 bq[j][0] = pack_half2(v[0], v[1]);
@@ -239,34 +578,40 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
             for (int w = 0; w < 8; ++w)
                 qs[w] = t < (int)it.n_queries ? a.q_sign[(size_t)(it.query_begin + t) * 8 + w] : 0u;
         }
-        __syncthreads();
+        // a query too large for the fp16 split: the generic kernel takes the item
+        const bool too_big = __syncthreads_or(big) != 0;
+        if (too_big && tid == 0) bail[0] = 1;
 
-        const unsigned char* tbase = a.tiles + it.tile_begin * TILE_BYTES + lane * 16;
         const uint8_t* sbase = a.state ? a.state + it.tile_begin : nullptr;
         const uint32_t n = it.n_tiles;
-        const uint32_t n_sets = (n + MMA_SET_TILES - 1) / MMA_SET_TILES;
-        const uint32_t my_sets = (n_sets + nwarps - 1) / nwarps;  // sets this warp walks (the last may be past the end)
-        auto set_index = [&](uint32_t q) { return q * nwarps + warp; };
-        auto issue = [&](uint32_t q) {
-            const uint32_t s = set_index(q);
-            if (q < my_sets && s < n_sets) {
-                const uint32_t dst = stage_s + (q % MMA_DEPTH) * MMA_SET_BYTES;
-                const unsigned char* src = tbase + (size_t)s * MMA_SET_BYTES;
-                if ((s + 1) * MMA_SET_TILES <= n) {
-                    cp_async16_s<0>(dst + dst_off[0], src, 16);
-                    cp_async16_s<512>(dst + dst_off[1], src, 16);
-                    cp_async16_s<1024>(dst + dst_off[2], src, 16);
-                    cp_async16_s<1536>(dst + dst_off[3], src, 16);
+        const uint32_t n_sets = too_big ? 0u : (n + MMA_SET_TILES - 1) / MMA_SET_TILES;
+        const uint32_t n_full = n / MMA_SET_TILES;
+        const bool mine = t < (int)it.n_queries;
+        // prefetch state: next set to fetch, its source and its ring slot
+        uint32_t s_next = (uint32_t)warp;
+        const unsigned char* src = a.tiles + (it.tile_begin + (size_t)warp * MMA_SET_TILES) * TILE_BYTES + lane * 16;
+        uint32_t slot_next = 0;
+        auto issue = [&]() {
+            if (s_next < n_sets) {
+                const uint32_t dst = stage_s + slot_next + dst_lane;
+                if (s_next < n_full) {
+                    cp_async16_s<0, 0>(dst, src, 16);
+                    cp_async16_s<512, 4 * MMA_ROW>(dst, src, 16);
+                    cp_async16_s<1024, 8 * MMA_ROW>(dst, src, 16);
+                    cp_async16_s<1536, 12 * MMA_ROW>(dst, src, 16);
                 } else {
                     // ragged last set: rows past the end are zero-filled (source not read)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const bool live = s * MMA_SET_TILES + (lane >> 3) + 4 * i < n;
-                        cp_async16_s<0>(dst + dst_off[i], live ? src + 512 * i : tbase, live ? 16 : 0);
-                    }
+                    const uint32_t r = s_next * MMA_SET_TILES + (uint32_t)(lane >> 3);
+                    cp_async16_s<0, 0>(dst, r < n ? src : a.tiles, r < n ? 16 : 0);
+                    cp_async16_s<0, 4 * MMA_ROW>(dst, r + 4 < n ? src + 512 : a.tiles, r + 4 < n ? 16 : 0);
+                    cp_async16_s<0, 8 * MMA_ROW>(dst, r + 8 < n ? src + 1024 : a.tiles, r + 8 < n ? 16 : 0);
+                    cp_async16_s<0, 12 * MMA_ROW>(dst, r + 12 < n ? src + 1536 : a.tiles, r + 12 < n ? 16 : 0);
                 }
             }
             cp_async_commit();
+            s_next += (uint32_t)nwarps;
+            src += (size_t)nwarps * MMA_SET_BYTES;
+            slot_next = slot_next == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot_next + MMA_SET_STRIDE;
         };
         // Thresholds are shared between the CTAs that scan the same query's tiles:
         // a CTA's pivot (k of its own elements are >= it) is a proven lower bound of
@@ -281,6 +626,7 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
         // barrier is executed in the steady state: every warp polls the flag between
         // sets, finished warps poll it in the drain loop, so everyone arrives.
         auto rendezvous = [&]() {
+            PROF_T(t_rv0);
             __syncwarp();
             if (lane == 0) atomicAdd(&ctl[1], 1);
             for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
@@ -288,83 +634,97 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
                 __nanosleep(40);
             }
             __syncthreads();
+            PROF_T(t_rv1);
+            const uint32_t ties = block_select_multi(keys, a.cap, cnt, (int)it.n_queries, a.k, resel_slack,
+                                                     (int)resel_min, pivot, hist);
 #pragma unroll 1
-            for (int qq = 0; qq < (int)it.n_queries; ++qq) {
-                if (cnt[qq] > (int)resel_min) {
-                    block_select_topk(keys + (size_t)qq * a.cap, &cnt[qq], a.k, &pivot[qq], hist);
-                    if (tid == 0) atomicMax(a.gpivot + it.query_begin + qq, (unsigned long long)pivot[qq]);
-                }
-            }
+            for (int qq = 0; qq < (int)it.n_queries; ++qq)
+                if (ties >> qq & 1u) block_select_topk(keys + (size_t)qq * a.cap, &cnt[qq], a.k, &pivot[qq], hist);
+            if (tid < (int)it.n_queries) atomicMax(a.gpivot + it.query_begin + tid, (unsigned long long)pivot[tid]);
             if (warp == 0) refresh_pivots();
             if (tid == 0) { ctl[0] = 0; ctl[1] = 0; }
             __syncthreads();
+            PROF_T(t_rv2);
+            PROF_ADD(2, t_rv1 - t_rv0);
+            PROF_ADD(3, t_rv2 - t_rv1);
+            PROF_ADD(4, 1);
         };
 #pragma unroll
-        for (int i = 0; i < MMA_DEPTH - 1; ++i) issue(i);
-        bool gave_up = false;
-        for (uint32_t q = 0; q < my_sets; ++q) {
-            issue(q + MMA_DEPTH - 1);
+        for (int i = 0; i < MMA_DEPTH - 1; ++i) issue();
+        PROF_T(t_loop0);
+        PROF_ADD(0, t_loop0 - t_item);
+        uint32_t slot = 0, polls = 0;
+        for (uint32_t s = (uint32_t)warp; s < n_sets; s += (uint32_t)nwarps) {
+            issue();
             cp_async_wait<MMA_DEPTH - 1>();
             __syncwarp();
-            const uint32_t s = set_index(q);
-            if (s < n_sets && !gave_up) {
-                const uint32_t r0 = stage_s + (q % MMA_DEPTH) * MMA_SET_BYTES + (uint32_t)g * TILE_BYTES;
-                const uint32_t r1 = r0 + 8 * TILE_BYTES;
-                const uint2 m0 = lds_v2(r0 + L.c6), m1 = lds_v2(r1 + L.c6);  // scale, lambda
-                const uint4 x0 = lds_v4(r0 + L.c7), x1 = lds_v4(r1 + L.c7);  // position, head|flags, gs[8]
-                const uint32_t f0 = x0.y >> 16, f1 = x1.y >> 16;
-                const uint32_t fo = __reduce_or_sync(0xFFFFFFFFu, f0 | f1);
-                if ((fo & (F_MIXED | F_TQ3 | F_MIX3)) || ((fo & F_NF4) && !a.nf4_table)) {
-                    gave_up = true;  // a codec this kernel does not decode: hand the item back
-                    if (lane == 0) bail[0] = 1;
-                } else {
-                    float acc0, acc1;
-                    if (!(fo & F_NF4)) {
-                        coarse_set<0>(r0, r1, L, bq, f0, f1, x0, x1, acc0, acc1);
-                    } else if (__reduce_and_sync(0xFFFFFFFFu, f0 & f1) & F_NF4) {
-                        coarse_set<1>(r0, r1, L, bq, f0, f1, x0, x1, acc0, acc1);
-                    } else {
-                        coarse_set<2>(r0, r1, L, bq, f0, f1, x0, x1, acc0, acc1);
-                    }
-                    // Hamming term of query t for both rows
-                    const int h0 = popc8(lds_v4(r0 + L.c4), lds_v4(r0 + L.c5), qs);
-                    const int h1 = popc8(lds_v4(r1 + L.c4), lds_v4(r1 + L.c5), qs);
-                    const float lam0 = (f0 & F_WARM) ? 0.0f : __uint_as_float(m0.y);
-                    const float lam1 = (f1 & F_WARM) ? 0.0f : __uint_as_float(m1.y);
-                    const float sc0 = fmaf(acc0, __uint_as_float(m0.x) * (1.0f / 255.0f), lam0 * (float)(256 - 2 * h0));
-                    const float sc1 = fmaf(acc1, __uint_as_float(m1.x) * (1.0f / 255.0f), lam1 * (float)(256 - 2 * h1));
-                    if (t < (int)it.n_queries) {
-                        const uint32_t t0 = s * MMA_SET_TILES + g, t1 = t0 + 8;
-                        const bool live0 = t0 < n && (!sbase || sbase[t0] != ST_COLD);
-                        const bool live1 = t1 < n && (!sbase || sbase[t1] != ST_COLD);
-                        if (TOPK) {
-                            const uint64_t pv = pivot[t];
-                            const uint64_t comp0 = make_comp(sc0, it.index_base + t0);
-                            const uint64_t comp1 = make_comp(sc1, it.index_base + t1);
-                            if (live0 && comp0 >= pv) {
-                                const uint32_t pos = (uint32_t)atomicAdd(&cnt[t], 1);
-                                if (pos < a.cap) keys[key_row + pos] = comp0;
-                                if (pos >= cap_soft) *reinterpret_cast<volatile int*>(ctl) = 1;
-                            }
-                            if (live1 && comp1 >= pv) {
-                                const uint32_t pos = (uint32_t)atomicAdd(&cnt[t], 1);
-                                if (pos < a.cap) keys[key_row + pos] = comp1;
-                                if (pos >= cap_soft) *reinterpret_cast<volatile int*>(ctl) = 1;
-                            }
-                        } else {
-                            float* o = a.scores + (size_t)(it.query_begin + t) * a.score_stride + it.index_base;
-                            if (t0 < n) o[t0] = live0 ? sc0 : -INFINITY;
-                            if (t1 < n) o[t1] = live1 ? sc1 : -INFINITY;
+            const uint32_t rb = stage_s + slot + row_lane;
+            slot = slot == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot + MMA_SET_STRIDE;
+            const uint2 m0 = lds_v2<96>(rb), m1 = lds_v2<96 + MMA_HALF>(rb);    // scale, lambda
+            const uint4 x0 = lds_v4<112>(rb), x1 = lds_v4<112 + MMA_HALF>(rb);  // position, head|flags, gs[8]
+            const uint32_t f0 = x0.y >> 16, f1 = x1.y >> 16;
+            const uint32_t fo = __reduce_or_sync(0xFFFFFFFFu, f0 | f1);
+            if ((fo & (F_MIXED | F_TQ3 | F_MIX3)) || ((fo & F_NF4) && !a.nf4_table)) {
+                if (lane == 0) bail[0] = 1;  // a codec this kernel does not decode: hand the item back
+                break;
+            }
+            float acc0, acc1;
+            const uint32_t hb = rb + 2u * (uint32_t)t;
+            if (!(fo & F_NF4)) {
+                coarse_set<0>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+            } else if (__reduce_and_sync(0xFFFFFFFFu, f0 & f1) & F_NF4) {
+                coarse_set<1>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+            } else {
+                coarse_set<2>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+            }
+            // Hamming term of query t for both rows
+            const int h0 = popc8(lds_v4<64>(rb), lds_v4<80>(rb), qs);
+            const int h1 = popc8(lds_v4<64 + MMA_HALF>(rb), lds_v4<80 + MMA_HALF>(rb), qs);
+            const float lam0 = (f0 & F_WARM) ? 0.0f : __uint_as_float(m0.y);
+            const float lam1 = (f1 & F_WARM) ? 0.0f : __uint_as_float(m1.y);
+            const float sc0 = fmaf(acc0, __uint_as_float(m0.x) * (1.0f / 4080.0f), lam0 * (float)(256 - 2 * h0));
+            const float sc1 = fmaf(acc1, __uint_as_float(m1.x) * (1.0f / 4080.0f), lam1 * (float)(256 - 2 * h1));
+            if (mine) {
+                const uint32_t t0 = s * MMA_SET_TILES + (uint32_t)g, t1 = t0 + 8;
+                bool live0 = t0 < n, live1 = t1 < n;
+                if (sbase) {
+                    live0 = live0 && sbase[t0] != ST_COLD;
+                    live1 = live1 && sbase[t1] != ST_COLD;
+                }
+                if (TOPK) {
+                    const uint64_t pv = pivot[t];
+                    const uint32_t pvh = (uint32_t)(pv >> 32);
+                    const uint32_t k0 = score_key(sc0), k1 = score_key(sc1);
+                    if (live0 && k0 >= pvh) {
+                        const uint64_t comp = ((uint64_t)k0 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t0));
+                        if (comp >= pv) {
+                            const uint32_t pos = (uint32_t)atomicAdd(&cnt[t], 1);
+                            if (pos < a.cap) keys[key_row + pos] = comp;
+                            if (pos >= cap_soft) *reinterpret_cast<volatile int*>(ctl) = 1;
                         }
                     }
+                    if (live1 && k1 >= pvh) {
+                        const uint64_t comp = ((uint64_t)k1 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t1));
+                        if (comp >= pv) {
+                            const uint32_t pos = (uint32_t)atomicAdd(&cnt[t], 1);
+                            if (pos < a.cap) keys[key_row + pos] = comp;
+                            if (pos >= cap_soft) *reinterpret_cast<volatile int*>(ctl) = 1;
+                        }
+                    }
+                } else {
+                    float* o = a.scores + (size_t)(it.query_begin + t) * a.score_stride + it.index_base;
+                    if (t0 < n) o[t0] = live0 ? sc0 : -INFINITY;
+                    if (t1 < n) o[t1] = live1 ? sc1 : -INFINITY;
                 }
             }
             __syncwarp();
             if (TOPK) {
                 if (*reinterpret_cast<volatile int*>(ctl)) rendezvous();
-                else if (warp == 0 && (q & 31) == 31) refresh_pivots();
+                else if (warp == 0 && (++polls & 31u) == 0u) refresh_pivots();
             }
         }
+        PROF_T(t_loop1);
+        PROF_ADD(1, t_loop1 - t_loop0);
         if (TOPK) {
             // drain: warps that ran out of sets keep serving reselect rendezvous until all are done
             __syncwarp();
@@ -377,38 +737,51 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
         }
         cp_async_wait<0>();
         __syncthreads();
+        PROF_T(t_drain1);
+        PROF_ADD(5, t_drain1 - t_loop1);
         if (bail[0]) {
             if (tid == 0) a.retry[item_id] = 1;
             continue;
         }
         if (TOPK) {
+            // at most list_cap survivors per query, then those that still clear the
+            // query's shared threshold are written out, compacted
+            const uint32_t ties = block_select_multi(keys, a.cap, cnt, (int)it.n_queries, a.k, a.list_cap - a.k,
+                                                     (int)a.list_cap, pivot, hist);
 #pragma unroll 1
             for (int qq = 0; qq < (int)it.n_queries; ++qq) {
-                if (cnt[qq] > (int)a.k) {
-                    block_select_topk(keys + (size_t)qq * a.cap, &cnt[qq], a.k, &pivot[qq], hist);
-                    if (tid == 0) atomicMax(a.gpivot + it.query_begin + qq, (unsigned long long)pivot[qq]);
-                }
-                // write the survivors that still clear the query's shared threshold, compacted
-                const int c = cnt[qq];
-                uint64_t* dst = a.cand_keys + (size_t)(it.list_begin + qq) * a.k;
+                if (ties >> qq & 1u) block_select_topk(keys + (size_t)qq * a.cap, &cnt[qq], a.k, &pivot[qq], hist);
+            }
+            if (tid < (int)it.n_queries) atomicMax(a.gpivot + it.query_begin + tid, (unsigned long long)pivot[tid]);
+            if (tid < 4) hist[tid] = 0;
+            __syncthreads();
+#pragma unroll 1
+            for (int qq = 0; qq < (int)it.n_queries; ++qq) {
+                const int c = min(cnt[qq], (int)a.list_cap);
+                uint64_t* dst = a.cand_keys + (size_t)(it.list_begin + qq) * a.list_cap;
                 const unsigned long long gp = *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + qq);
-                if (tid == 0) hist[0] = 0;
-                __syncthreads();
                 for (int i0 = 0; i0 < c; i0 += blockDim.x) {
                     const int i = i0 + tid;
                     const uint64_t key = i < c ? keys[(size_t)qq * a.cap + i] : 0ull;
                     const bool keep = i < c && key >= gp;
                     const unsigned bal = __ballot_sync(0xFFFFFFFFu, keep);
                     int base = 0;
-                    if (lane == 0 && bal) base = atomicAdd(&hist[0], __popc(bal));
+                    if (lane == 0 && bal) base = atomicAdd(&hist[qq], __popc(bal));
                     base = __shfl_sync(0xFFFFFFFFu, base, 0);
                     if (keep) dst[base + __popc(bal & ((1u << lane) - 1))] = key;
                 }
-                __syncthreads();
-                if (tid == 0) a.cand_cnt[it.list_begin + qq] = (uint32_t)hist[0];
             }
+            __syncthreads();
+            if (tid < (int)it.n_queries) a.cand_cnt[it.list_begin + tid] = (uint32_t)hist[tid];
         }
+        PROF_T(t_end);
+        PROF_ADD(6, t_end - t_drain1);
+        PROF_ADD(7, 1);
     }
+#ifdef SLHA_SCORE_PROFILE
+    if (tid == 0)
+        for (int i = 0; i < 8; ++i) g_score_prof[blockIdx.x * 8 + i] = prof[i];
+#endif
 }
 
 }  // namespace
