@@ -295,6 +295,8 @@ struct ScoreArgs {
     uint32_t* retry;
     const uint32_t* cta_begin;    // tensor-core kernel: item range of every persistent CTA
     unsigned long long* gpivot;   // tensor-core kernel: per query row, shared selection threshold
+    unsigned long long* grange;   // per query row: bucket mapping of the shared score histogram (0 = none yet)
+    uint32_t* ghist;              // per query row: 256 bucket counts of appended candidates
     uint32_t nf4_table;           // tensor-core kernel: build the NF4 shared-memory table (else NF4 tiles are handed back)
 };
 

@@ -18,7 +18,7 @@ int env_int(const char* name, int dflt) {
 
 size_t mma_smem_bytes(int nwarps, uint32_t cap, bool nf4_table) {
     return (size_t)(nf4_table ? NF4_LUT_BYTES : 0) + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE + (size_t)4 * cap * 8 + 4 * 8 +
-           (4 + 4 + SEL_HIST_INTS) * 4 + 16;
+           (4 + 20 + SEL_HIST_INTS) * 4 + 16;
 }
 
 size_t score_smem_bytes(int G, int nwarps, bool topk, uint32_t cap) {
@@ -281,7 +281,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     SLHA_TRY(p->b_cnt.ensure((size_t)n_lists * 4));
     SLHA_TRY(p->b_retry.ensure(all.size() * 4));
     SLHA_TRY(p->b_cta.ensure(cta_begin.size() * 4));
-    SLHA_TRY(p->b_gpivot.ensure(nq * 8));
+    SLHA_TRY(p->b_gpivot.ensure(nq * (8 + 8 + 1024)));  // thresholds, bucket mappings, histograms
     p->d_items = (WorkItem*)p->b_items.p;
     p->d_q_list_begin = (uint32_t*)p->b_qbegin.p;
     p->d_q_list_count = (uint32_t*)p->b_qcount.p;
@@ -373,7 +373,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     const bool mma = p->use_mma && !prefer_generic;
     if (mma) {
         SLHA_CUDA(cudaMemsetAsync(p->d_retry, 0, (size_t)p->n_items * 4, c->stream));
-        SLHA_CUDA(cudaMemsetAsync(p->d_gpivot, 0, nq * 8, c->stream));
+        SLHA_CUDA(cudaMemsetAsync(p->d_gpivot, 0, nq * (8 + 8 + 1024), c->stream));
         ScoreArgs a{};
         a.tiles = reinterpret_cast<const unsigned char*>(tiles);
         a.state = state;
@@ -382,6 +382,8 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.retry = p->d_retry;
         a.cta_begin = p->d_cta_begin;
         a.gpivot = p->d_gpivot;
+        a.grange = p->d_gpivot + nq;
+        a.ghist = reinterpret_cast<uint32_t*>(p->d_gpivot + 2 * nq);
         a.nf4_table = p->nf4_table ? 1u : 0u;
         a.q_coarse = d_q_coarse;
         a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);

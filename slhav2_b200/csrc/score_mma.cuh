@@ -190,9 +190,12 @@ __device__ unsigned long long g_sel_prof[148 * 8];  // calls, passes, refines, t
 #endif
 
 // Bucket of a score inside [smin, smin + 256 / inv): monotone in the score.
-__device__ __forceinline__ int sel_bucket(uint32_t h, float smin, float inv) {
-    const int b = (int)((key_score(h) - smin) * inv);
+__device__ __forceinline__ int sel_bucket_f(float sc, float smin, float inv) {
+    const int b = (int)((sc - smin) * inv);
     return b < 0 ? 0 : (b > 255 ? 255 : b);
+}
+__device__ __forceinline__ int sel_bucket(uint32_t h, float smin, float inv) {
+    return sel_bucket_f(key_score(h), smin, inv);
 }
 // Range [lo, hi] (order keys of scores) -> (smin, inv); false when the range cannot
 // be bucketed (one single score, or a non-finite bound).
@@ -218,18 +221,21 @@ __device__ __forceinline__ bool sel_range(uint32_t lo, uint32_t hi, float& smin,
 // scores), or holds a non-finite score, are reported in the returned bit mask
 // (uniform over the block) and left for block_select_topk, which also orders by
 // index.  hist: SEL_HIST_INTS ints.  All threads of the block must call.
+// pivot_only: no selection, the buffers are only purged of keys below the pivot.
+// qmax (optional, [4]): receives the largest score word seen by a full selection.
 __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, int nq, uint32_t k, uint32_t slack,
-                                       int trigger, uint64_t* pivot, int* hist) {
+                                       int trigger, uint64_t* pivot, int* hist, bool pivot_only = false,
+                                       uint32_t* qmax = nullptr) {
     const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
     // [q][8]: 0 range lo, 1 range hi, 2 need, 3 active, 4 exact selection wanted, 5 kept, 6 selected, 7 pivotal bucket
     uint32_t* st = reinterpret_cast<uint32_t*>(hist + 1024);
     if (tid < 4) {
         const bool act = tid < nq && cnt[tid] > trigger;
         uint32_t* s = st + 8 * tid;
-        s[0] = 0xFFFFFFFFu;
+        s[0] = pivot_only ? (tid < nq ? (uint32_t)(pivot[tid] >> 32) : 0u) : 0xFFFFFFFFu;
         s[1] = 0u;
         s[2] = k;
-        s[3] = act;
+        s[3] = act && !pivot_only;
         s[4] = 0u;
         s[5] = 0u;
         s[6] = act;
@@ -257,6 +263,7 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
         if (lane == 0) { atomicMax(&st[8 * q + 1], mx); atomicMin(&st[8 * q], mn); }
     }
     __syncthreads();
+    if (qmax && tid < nq && st[8 * tid + 3]) qmax[tid] = max(qmax[tid], st[8 * tid + 1]);
     PROF_T(ts1);
     SEL_ADD(4, ts1 - ts0);
     for (int pass = 0; pass < 12; ++pass) {
@@ -381,7 +388,7 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
     for (int q = 0; q < nq; ++q)
         if (st[8 * q + 6]) maxc = max(maxc, cnt[q]);
     const int R = (maxc + nt - 1) / nt;
-    if (R <= 8) {
+    if (R <= 10) {
         // every warp owns R*32 consecutive slots: it reads them all, the warps' counts are
         // summed once, then it writes its survivors (order preserved, no read-after-write)
         int* wcnt = hist;  // [4][32]
@@ -394,12 +401,12 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
             if (!sel_range(rlo, rhi, smin, inv)) bsel = -1;  // whole range stays
             uint64_t* kq = keys + (size_t)q * cap;
             const int c = cnt[q];
-            uint64_t key[8];
-            unsigned bal[8];
+            uint64_t key[10];
+            unsigned bal[10];
             int wtot = 0;
             uint32_t km = 0xFFFFFFFFu;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 10; ++j) {
                 bal[j] = 0u;
                 key[j] = 0ull;
                 if (j < R) {
@@ -423,7 +430,7 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
             int run = __reduce_add_sync(0xFFFFFFFFu, lane < warp ? v : 0);
             const int total = __reduce_add_sync(0xFFFFFFFFu, v);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 10; ++j) {
                 if (j < R) {
                     if (bal[j] >> lane & 1u) kq[run + __popc(bal[j] & ((1u << lane) - 1u))] = key[j];
                     run += __popc(bal[j]);
@@ -482,11 +489,11 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
         }
         __syncthreads();
     }
-    // the new pivot: the smallest score kept
+    // the new pivot: the smallest score kept, provided k keys were kept (fewer prove nothing)
     if (tid < 4 && st[8 * tid + 6]) {
         cnt[tid] = (int)st[8 * tid + 5];
         const uint64_t np = st[8 * tid + 2] == 0xFFFFFFFFu ? 0ull : (uint64_t)st[8 * tid + 2] << 32;
-        if (np > pivot[tid]) pivot[tid] = np;
+        if (st[8 * tid + 5] >= k && np > pivot[tid]) pivot[tid] = np;
     }
     uint32_t ties = 0u;
 #pragma unroll
@@ -513,7 +520,10 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
     int* cnt = reinterpret_cast<int*>(pivot + 4);                  // [4]
     int* ctl = cnt + 4;   // [0] want: some query's buffer is nearly full  [1] arrived  [2] done warps  [3] bail
     int* bail = ctl + 3;
-    int* hist = ctl + 4;  // SEL_HIST_INTS
+    uint32_t* qmax = reinterpret_cast<uint32_t*>(ctl + 4);  // [4] largest score word a selection has seen
+    int* adopt = ctl + 8;                                   // [4] query whose buffer must be counted into the shared histogram
+    float2* rng = reinterpret_cast<float2*>(ctl + 12);      // [4] (smin, inv) of the query's shared score histogram; inv 0 = none yet
+    int* hist = ctl + 20;  // SEL_HIST_INTS
     const uint32_t smem_s = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t stage_s = smem_s + lut_bytes + (uint32_t)warp * MMA_DEPTH * MMA_SET_STRIDE;
 
@@ -545,9 +555,15 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
         PROF_T(t_item);
         __syncthreads();  // previous item fully retired (and the table is visible)
         if (TOPK && tid < 4) {
-            // start from the threshold other CTAs have already proven for the query
+            // start from the threshold other CTAs have already proven for the query, and
+            // from the query's shared histogram range if one has been published
+            const bool have = tid < (int)it.n_queries;
             cnt[tid] = 0;
-            pivot[tid] = tid < (int)it.n_queries ? *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + tid) : 0ull;
+            qmax[tid] = 0u;
+            adopt[tid] = 0;
+            pivot[tid] = have ? *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + tid) : 0ull;
+            const unsigned long long pr = have ? *reinterpret_cast<volatile unsigned long long*>(a.grange + it.query_begin + tid) : 0ull;
+            rng[tid] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
         }
         if (tid == 0) { ctl[0] = ctl[1] = ctl[2] = ctl[3] = 0; }
         // B fragments: column n = g is query g>>1, part g&1 (hi / lo); k slots
@@ -587,6 +603,7 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
         const uint32_t n_sets = too_big ? 0u : (n + MMA_SET_TILES - 1) / MMA_SET_TILES;
         const uint32_t n_full = n / MMA_SET_TILES;
         const bool mine = t < (int)it.n_queries;
+        uint32_t* gh = a.ghist + (size_t)(it.query_begin + (mine ? t : 0)) * 256;  // my query's shared histogram
         // prefetch state: next set to fetch, its source and its ring slot
         uint32_t s_next = (uint32_t)warp;
         const unsigned char* src = a.tiles + (it.tile_begin + (size_t)warp * MMA_SET_TILES) * TILE_BYTES + lane * 16;
@@ -622,9 +639,121 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
                 if (seen > pivot[lane]) pivot[lane] = seen;
             }
         };
+        // Shared score histogram of a query: every CTA counts the candidates it appends
+        // into 256 buckets of global memory (one bucket mapping per query, published by
+        // the first CTA that finishes a selection).  The counts are of real tiles, so the
+        // lower edge of the highest bucket whose count from the top reaches k is a proven
+        // lower bound of the query's k-th best score - for all CTAs at once, and without a
+        // block-wide selection.  A whole warp calls this for query q.
+        auto hist_pivot = [&](int q) {
+            const float2 r = rng[q];
+            if (r.y == 0.0f) return;
+            const uint32_t* hq = a.ghist + (size_t)(it.query_begin + q) * 256 + 248 - 8 * lane;
+            uint32_t c[8];  // buckets 255-8l .. 248-8l (descending)
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[7]), "=r"(c[6]), "=r"(c[5]), "=r"(c[4]) : "l"(hq));
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[3]), "=r"(c[2]), "=r"(c[1]), "=r"(c[0]) : "l"(hq + 4));
+            uint32_t tot = 0;
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) tot += c[jj];
+            uint32_t incl = tot;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += y;
+            }
+            const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= a.k);
+            if (ok == 0u || lane != __ffs(ok) - 1) return;
+            uint32_t run = incl - tot;
+            int b = 0;
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                if (run + c[jj] >= a.k) { b = 255 - 8 * lane - jj; break; }
+                run += c[jj];
+            }
+            if (b < 1) return;
+            // half a bucket and a few ulps below the bucket's edge: every counted key of the
+            // buckets b.. is above this bound whatever the rounding of the bucket arithmetic
+            const float e = r.x + ((float)b - 0.5f) / r.y;
+            const uint32_t ek = score_key(e);
+            const unsigned long long np = (unsigned long long)(ek > 8u ? ek - 8u : 0u) << 32;
+            if (np > pivot[q]) {
+                pivot[q] = np;
+                atomicMax(a.gpivot + it.query_begin + q, np);
+            }
+        };
+        // Counts the buffer of the queries flagged in adopt[] into their shared histograms
+        // (once, when the query's bucket mapping becomes known to this CTA).
+        auto count_adopted = [&]() {
+            // per-CTA counts in shared memory first: one global atomic per occupied bucket
+            for (int b = tid; b < 1024; b += blockDim.x) hist[b] = 0;
+            __syncthreads();
+#pragma unroll 1
+            for (int q = 0; q < (int)it.n_queries; ++q) {
+                if (!adopt[q]) continue;
+                const float2 r = rng[q];
+                const int c = min(cnt[q], (int)a.cap);
+                for (int i = tid; i < c; i += blockDim.x) {
+                    const float sc = key_score((uint32_t)(keys[(size_t)q * a.cap + i] >> 32));
+                    if (sc >= r.x) atomicAdd(&hist[256 * q + sel_bucket_f(sc, r.x, r.y)], 1);
+                }
+            }
+            __syncthreads();
+            for (int b = tid; b < 1024; b += blockDim.x) {
+                const int q = b >> 8;
+                if (q < (int)it.n_queries && adopt[q] && hist[b])
+                    atomicAdd(a.ghist + (size_t)(it.query_begin + q) * 256 + (b & 255), (uint32_t)hist[b]);
+            }
+            __syncthreads();
+            if (tid < 4) adopt[tid] = 0;
+        };
         // All warps meet here when a query's buffer is nearly full (flag ctl[0]).  No
         // barrier is executed in the steady state: every warp polls the flag between
         // sets, finished warps poll it in the drain loop, so everyone arrives.
+        // final: the item is over, the buffers must come down to the list size.
+        auto settle = [&](bool final) {
+            const int trigger = final ? (int)a.list_cap : (int)resel_min;
+            // a bucket mapping another CTA has published meanwhile
+            if (tid < (int)it.n_queries && rng[tid].y == 0.0f) {
+                const unsigned long long pr = *reinterpret_cast<volatile unsigned long long*>(a.grange + it.query_begin + tid);
+                if (pr) {
+                    rng[tid] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
+                    adopt[tid] = 1;
+                }
+            }
+            __syncthreads();
+            if (adopt[0] | adopt[1] | adopt[2] | adopt[3]) count_adopted();
+            if (warp < (int)it.n_queries) hist_pivot(warp);
+            if (warp == 4) refresh_pivots();
+            __syncthreads();
+            // keys below the pivots go; a selection only where that was not enough
+            block_select_multi(keys, a.cap, cnt, (int)it.n_queries, a.k, 0u, trigger, pivot, hist, true);
+            bool more = false;
+            for (int q = 0; q < (int)it.n_queries; ++q) more |= cnt[q] > trigger;
+            if (more) {
+                const uint32_t ties = block_select_multi(keys, a.cap, cnt, (int)it.n_queries, a.k,
+                                                         final ? a.list_cap - a.k : resel_slack, trigger, pivot, hist, false, qmax);
+#pragma unroll 1
+                for (int qq = 0; qq < (int)it.n_queries; ++qq)
+                    if (ties >> qq & 1u) block_select_topk(keys + (size_t)qq * a.cap, &cnt[qq], a.k, &pivot[qq], hist);
+                // publish a bucket mapping for queries that have none: from the new pivot to a
+                // quarter of the span above the largest score seen
+                if (tid < (int)it.n_queries && rng[tid].y == 0.0f && qmax[tid]) {
+                    const float lo = key_score((uint32_t)(pivot[tid] >> 32)), top = key_score(qmax[tid]);
+                    const float hi = top + 0.25f * (top - lo);
+                    const float inv = 256.0f / (hi - lo);
+                    if (pivot[tid] && isfinite(lo) && isfinite(hi) && isfinite(inv) && inv > 0.0f) {
+                        const unsigned long long mine = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(inv) << 32);
+                        const unsigned long long old = atomicCAS(a.grange + it.query_begin + tid, 0ull, mine);
+                        const unsigned long long use = old ? old : mine;
+                        rng[tid] = make_float2(__uint_as_float((uint32_t)use), __uint_as_float((uint32_t)(use >> 32)));
+                        adopt[tid] = 1;
+                    }
+                }
+                __syncthreads();
+                if (adopt[0] | adopt[1] | adopt[2] | adopt[3]) count_adopted();
+            }
+            if (tid < (int)it.n_queries) atomicMax(a.gpivot + it.query_begin + tid, (unsigned long long)pivot[tid]);
+        };
         auto rendezvous = [&]() {
             PROF_T(t_rv0);
             __syncwarp();
@@ -635,13 +764,7 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
             }
             __syncthreads();
             PROF_T(t_rv1);
-            const uint32_t ties = block_select_multi(keys, a.cap, cnt, (int)it.n_queries, a.k, resel_slack,
-                                                     (int)resel_min, pivot, hist);
-#pragma unroll 1
-            for (int qq = 0; qq < (int)it.n_queries; ++qq)
-                if (ties >> qq & 1u) block_select_topk(keys + (size_t)qq * a.cap, &cnt[qq], a.k, &pivot[qq], hist);
-            if (tid < (int)it.n_queries) atomicMax(a.gpivot + it.query_begin + tid, (unsigned long long)pivot[tid]);
-            if (warp == 0) refresh_pivots();
+            settle(false);
             if (tid == 0) { ctl[0] = 0; ctl[1] = 0; }
             __syncthreads();
             PROF_T(t_rv2);
@@ -701,6 +824,8 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
                             const uint32_t pos = (uint32_t)atomicAdd(&cnt[t], 1);
                             if (pos < a.cap) keys[key_row + pos] = comp;
                             if (pos >= cap_soft) *reinterpret_cast<volatile int*>(ctl) = 1;
+                            const float2 r = rng[t];
+                            if (r.y != 0.0f && sc0 >= r.x) atomicAdd(gh + sel_bucket_f(sc0, r.x, r.y), 1u);
                         }
                     }
                     if (live1 && k1 >= pvh) {
@@ -709,6 +834,8 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
                             const uint32_t pos = (uint32_t)atomicAdd(&cnt[t], 1);
                             if (pos < a.cap) keys[key_row + pos] = comp;
                             if (pos >= cap_soft) *reinterpret_cast<volatile int*>(ctl) = 1;
+                            const float2 r = rng[t];
+                            if (r.y != 0.0f && sc1 >= r.x) atomicAdd(gh + sel_bucket_f(sc1, r.x, r.y), 1u);
                         }
                     }
                 } else {
@@ -720,7 +847,12 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
             __syncwarp();
             if (TOPK) {
                 if (*reinterpret_cast<volatile int*>(ctl)) rendezvous();
-                else if (warp == 0 && (++polls & 31u) == 0u) refresh_pivots();
+                else if ((++polls & 63u) == (uint32_t)(warp >> 2) * 16u + 8u) {
+                    // in turn, a warp raises the threshold of query (warp & 3)
+                    if ((warp & 3) < (int)it.n_queries) hist_pivot(warp & 3);
+                    if ((warp & 3) == 0) refresh_pivots();
+                    __syncwarp();
+                }
             }
         }
         PROF_T(t_loop1);
@@ -746,13 +878,8 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
         if (TOPK) {
             // at most list_cap survivors per query, then those that still clear the
             // query's shared threshold are written out, compacted
-            const uint32_t ties = block_select_multi(keys, a.cap, cnt, (int)it.n_queries, a.k, a.list_cap - a.k,
-                                                     (int)a.list_cap, pivot, hist);
-#pragma unroll 1
-            for (int qq = 0; qq < (int)it.n_queries; ++qq) {
-                if (ties >> qq & 1u) block_select_topk(keys + (size_t)qq * a.cap, &cnt[qq], a.k, &pivot[qq], hist);
-            }
-            if (tid < (int)it.n_queries) atomicMax(a.gpivot + it.query_begin + tid, (unsigned long long)pivot[tid]);
+            settle(true);
+            __syncthreads();
             if (tid < 4) hist[tid] = 0;
             __syncthreads();
 #pragma unroll 1

@@ -110,6 +110,7 @@ def test_config5_full_length_head_fused_topk_equals_sort_of_full_scores():
     g.manual_seed(5)
     keys = torch.randn(n, d, generator=g, device="cuda").to(torch.bfloat16).contiguous()
     tiles = torch.empty(n * 128, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()  # the library runs on its own stream: torch's producers must have finished
     gm.encode_keys(keys, S.CODEC_INT4_GROUPED32, n=n, key_dtype=S.BF16, out=tiles)
     q = H.gaussian_keys(14, nq, d)
     qc, qs = gm.prepare_queries(q)
