@@ -18,7 +18,7 @@ int env_int(const char* name, int dflt) {
 
 size_t mma_smem_bytes(int nwarps, uint32_t cap, bool nf4_table) {
     return (size_t)(nf4_table ? NF4_LUT_BYTES : 0) + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE + (size_t)4 * cap * 8 + 4 * 8 +
-           (4 + 20 + SEL_HIST_INTS) * 4 + 16;
+           (128 + 4 + 20 + SEL_HIST_INTS) * 4 + 16;
 }
 
 size_t score_smem_bytes(int G, int nwarps, bool topk, uint32_t cap) {
@@ -183,7 +183,8 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
                 p->nf4_table = (flags & F_NF4) != 0;
                 break;
             }
-        uint32_t mcap = std::max<uint32_t>(3 * k, k + 4 * mround);
+        // per query: one region per warp, so a multiple of the warp count (256 covers 8 and 16 warps)
+        uint32_t mcap = (std::max<uint32_t>(3 * k, k + 4 * mround) + 255) / 256 * 256;
         while (mcap > k + 2 * mround && mma_smem_bytes(mw, mcap, p->nf4_table) > MAX_SMEM) mcap -= 256;
         p->use_mma = env_int("SLHA_B200_SCORE_IMPL", 1) != 0 && mma_smem_bytes(mw, mcap, p->nf4_table) <= MAX_SMEM;
         p->mma_cap = mcap;

@@ -506,19 +506,381 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
     return ties;
 }
 
+// Selection over segmented candidate buffers.  Query q's candidates live in one
+// region per warp: keys[(q * nw + w) * rs ..] holds cntw[q * 32 + w] keys, appended
+// and purged by warp w alone.  For every query in `mask` this raises pivot[q] so that
+// between k and about k + slack of the query's keys stay at or above it; nothing is
+// moved - every warp purges its own regions against the new pivots afterwards.
+// Same bucket scheme as block_select_multi (256 equal-width score buckets over the
+// range of the scores at or above the pivot, the pivotal bucket refined while it is
+// too full); the new pivot is half a bucket below the pivotal bucket's lower edge.
+// Returns the queries that cannot be settled this way (equal or non-finite scores).
+// hist: SEL_HIST_INTS ints.  All threads of the block must call; warp w sweeps region w.
+__device__ uint32_t block_select_seg(const uint64_t* keys, uint32_t rs, const int* cntw, int nq, uint32_t mask,
+                                     uint32_t k, uint32_t slack, uint64_t* pivot, int* hist, uint32_t* qmax) {
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nt >> 5;
+    // [q][8]: 0 range lo, 1 range hi, 2 need, 3 active, 4 failed, 5 nothing to raise, 6 selected, 7 pivotal bucket
+    uint32_t* st = reinterpret_cast<uint32_t*>(hist + 1024);
+    if (tid < 4) {
+        const bool act = tid < nq && (mask >> tid & 1u);
+        uint32_t* s = st + 8 * tid;
+        s[0] = 0xFFFFFFFFu;
+        s[1] = 0u;
+        s[2] = k;
+        s[3] = act;
+        s[4] = 0u;
+        s[5] = 0u;
+        s[6] = act;
+        s[7] = 0u;
+    }
+    __syncthreads();
+    if (!(st[6] | st[14] | st[22] | st[30])) return 0u;
+    for (int q = 0; q < nq; ++q) {
+        if (!st[8 * q + 3]) continue;
+        const uint64_t* kq = keys + (size_t)(q * nw + warp) * rs;
+        const int c = cntw[q * 32 + warp];
+        const uint32_t floor_h = (uint32_t)(pivot[q] >> 32);
+        uint32_t mx = 0u, mn = 0xFFFFFFFFu;
+        for (int i = lane; i < c; i += 32) {
+            const uint32_t h = (uint32_t)(kq[i] >> 32);
+            if (h >= floor_h) { mx = max(mx, h); mn = min(mn, h); }
+        }
+        mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+        mn = __reduce_min_sync(0xFFFFFFFFu, mn);
+        if (lane == 0) { atomicMax(&st[8 * q + 1], mx); atomicMin(&st[8 * q], mn); }
+    }
+    __syncthreads();
+    if (qmax && tid < nq && st[8 * tid + 3]) qmax[tid] = max(qmax[tid], st[8 * tid + 1]);
+    for (int pass = 0; pass < 12; ++pass) {
+        if (!(st[3] | st[11] | st[19] | st[27])) break;
+        for (int b = tid; b < 1024; b += nt) hist[b] = 0;
+        __syncthreads();
+        for (int q = 0; q < nq; ++q) {
+            if (!st[8 * q + 3]) continue;
+            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
+            float smin, inv;
+            if (!sel_range(lo, hi, smin, inv)) continue;  // settled by the scan below
+            const uint64_t* kq = keys + (size_t)(q * nw + warp) * rs;
+            const int c = cntw[q * 32 + warp];
+            for (int i = lane; i < c; i += 32) {
+                const uint32_t h = (uint32_t)(kq[i] >> 32);
+                if (h >= lo && h <= hi) atomicAdd(&hist[256 * q + sel_bucket(h, smin, inv)], 1);
+            }
+        }
+        __syncthreads();
+        bool refine = false;
+        if (warp < nq && st[8 * warp + 3]) {
+            uint32_t* s = st + 8 * warp;
+            const int* hq = hist + 256 * warp;
+            const uint32_t lo = s[0], hi = s[1], need = s[2];
+            float smin, inv;
+            if (!sel_range(lo, hi, smin, inv)) {
+                __syncwarp();
+                if (lane == 0) { s[3] = 0u; s[4] = 1u; }
+            } else {
+                // lane l owns buckets 255-8l .. 248-8l (descending)
+                int c[8], tot = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { c[j] = hq[255 - 8 * lane - j]; tot += c[j]; }
+                int incl = tot;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                    if (lane >= o) incl += y;
+                }
+                const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= (int)need);
+                if (ok == 0u) {
+                    // fewer than `need` keys at or above the pivot: nothing can be proven
+                    if (lane == 0) { s[3] = 0u; s[5] = 1u; }
+                } else {
+                    int bsel = 0, run = 0, binc = 0;
+                    const int src = __ffs(ok) - 1;
+                    if (lane == src) {
+                        run = incl - tot;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (run + c[j] >= (int)need) { bsel = 255 - 8 * lane - j; binc = c[j]; break; }
+                            run += c[j];
+                        }
+                    }
+                    bsel = __shfl_sync(0xFFFFFFFFu, bsel, src);
+                    run = __shfl_sync(0xFFFFFFFFu, run, src);
+                    binc = __shfl_sync(0xFFFFFFFFu, binc, src);
+                    const uint32_t kept = (k - need) + (uint32_t)(run + binc);
+                    if (kept <= k + slack) {
+                        if (lane == 0) { s[3] = 0u; s[7] = (uint32_t)bsel; }
+                    } else {
+                        refine = true;  // next range: the scores of the pivotal bucket
+                        __syncwarp();
+                        if (lane == 0) { s[2] = need - (uint32_t)run; s[7] = (uint32_t)bsel; }
+                    }
+                }
+            }
+        }
+        if (!__syncthreads_or(refine)) continue;
+        // smallest and largest score inside the pivotal bucket of the queries still active
+        uint32_t nlo[4], nhi[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { nlo[q] = 0xFFFFFFFFu; nhi[q] = 0u; }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (q >= nq || !st[8 * q + 3]) continue;
+            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
+            const int bsel = (int)st[8 * q + 7];
+            float smin, inv;
+            sel_range(lo, hi, smin, inv);
+            const uint64_t* kq = keys + (size_t)(q * nw + warp) * rs;
+            const int c = cntw[q * 32 + warp];
+            for (int i = lane; i < c; i += 32) {
+                const uint32_t h = (uint32_t)(kq[i] >> 32);
+                if (h >= lo && h <= hi && sel_bucket(h, smin, inv) == bsel) { nlo[q] = min(nlo[q], h); nhi[q] = max(nhi[q], h); }
+            }
+            nlo[q] = __reduce_min_sync(0xFFFFFFFFu, nlo[q]);
+            nhi[q] = __reduce_max_sync(0xFFFFFFFFu, nhi[q]);
+        }
+        __syncthreads();  // every thread has read the old range
+        if (tid < 4 && tid < nq && st[8 * tid + 3]) { st[8 * tid] = 0xFFFFFFFFu; st[8 * tid + 1] = 0u; }
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (q < nq && st[8 * q + 3] && lane == 0) { atomicMin(&st[8 * q], nlo[q]); atomicMax(&st[8 * q + 1], nhi[q]); }
+        __syncthreads();
+    }
+    if (tid < 4 && st[8 * tid + 6]) {
+        uint32_t* s = st + 8 * tid;
+        if (s[3]) { s[3] = 0u; s[4] = 1u; }  // still open after the last pass
+        if (!s[4] && !s[5]) {
+            // at least k keys are in the buckets s[7].. of the last range or above it
+            float smin, inv;
+            sel_range(s[0], s[1], smin, inv);
+            uint32_t ek = s[0];
+            if (s[7] >= 1u) {
+                const uint32_t e = score_key(smin + ((float)s[7] - 0.5f) / inv);
+                ek = max(ek, e > 8u ? e - 8u : 0u);
+            }
+            const uint64_t np = (uint64_t)ek << 32;
+            if (np > pivot[tid]) pivot[tid] = np;
+        }
+    }
+    __syncthreads();
+    const uint32_t failed = (st[4] ? 1u : 0u) | (st[12] ? 2u : 0u) | (st[20] ? 4u : 0u) | (st[28] ? 8u : 0u);
+    __syncthreads();
+    return failed;
+}
+
+// State of one work item of score_mma_kernel that its helper functions share.
+struct MmaItem {
+    uint64_t* keys;    // [4][nwarps][rs] candidate regions
+    uint64_t* pivot;   // [4]
+    int* cntw;         // [4][32] published region counts
+    int* bail;
+    uint32_t* qmax;    // [4]
+    int* adopt;        // [4]
+    float2* rng;       // [4]
+    int* hist;         // SEL_HIST_INTS
+    uint32_t rs;       // slots per region
+    int room;          // rs - MMA_SET_TILES
+    uint32_t sel_slack;
+    uint32_t query_begin;
+    int nq;
+};
+
+// Thresholds are shared between the CTAs that scan the same query's tiles: a CTA's
+// pivot (k of its own elements are >= it) is a proven lower bound of the query's k-th
+// best composite key, so the maximum over CTAs is too.  Lanes 0..nq-1 of one warp.
+__device__ __forceinline__ void mma_refresh_pivots(const ScoreArgs& a, const MmaItem& m, int lane) {
+    if (lane < m.nq) {
+        const unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(a.gpivot + m.query_begin + lane);
+        if (seen > m.pivot[lane]) m.pivot[lane] = seen;
+    }
+}
+
+// Shared score histogram of a query: every CTA counts the candidates it appends into
+// 256 buckets of global memory (one bucket mapping per query, published by the first
+// CTA that finishes a selection).  The counts are of real tiles, so the lower edge of
+// the highest bucket whose count from the top reaches k is a proven lower bound of the
+// query's k-th best score - for all CTAs at once, and without a block-wide selection.
+// A whole warp calls this for query q.
+__device__ __forceinline__ void mma_hist_pivot(const ScoreArgs& a, const MmaItem& m, int q, int lane) {
+    const float2 r = m.rng[q];
+    if (r.y == 0.0f) return;
+    const uint32_t* hq = a.ghist + (size_t)(m.query_begin + q) * 256 + 248 - 8 * lane;
+    uint32_t c[8];  // buckets 255-8l .. 248-8l (descending)
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[7]), "=r"(c[6]), "=r"(c[5]), "=r"(c[4]) : "l"(hq));
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[3]), "=r"(c[2]), "=r"(c[1]), "=r"(c[0]) : "l"(hq + 4));
+    uint32_t tot = 0;
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) tot += c[jj];
+    uint32_t incl = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+        if (lane >= o) incl += y;
+    }
+    const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= a.k);
+    if (ok == 0u || lane != __ffs(ok) - 1) return;
+    uint32_t run = incl - tot;
+    int b = 0;
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+        if (run + c[jj] >= a.k) { b = 255 - 8 * lane - jj; break; }
+        run += c[jj];
+    }
+    if (b < 1) return;
+    // half a bucket and a few ulps below the bucket's edge: every counted key of the
+    // buckets b.. is above this bound whatever the rounding of the bucket arithmetic
+    const float e = r.x + ((float)b - 0.5f) / r.y;
+    const uint32_t ek = score_key(e);
+    const unsigned long long np = (unsigned long long)(ek > 8u ? ek - 8u : 0u) << 32;
+    if (np > m.pivot[q]) {
+        m.pivot[q] = np;
+        atomicMax(a.gpivot + m.query_begin + q, np);
+    }
+}
+
+// The calling warp drops the keys of its region of query tq that are below the pivot.
+// rc: the caller's count of the region of its own query t (updated when t == tq).
+__device__ __forceinline__ void mma_purge(const MmaItem& m, int tq, int warp, int nwarps, int lane, int t, int& rc) {
+    const int cn = __shfl_sync(0xFFFFFFFFu, rc, tq);  // lane tq is (g = 0, t = tq)
+    const uint64_t pv = m.pivot[tq];
+    uint64_t* reg = m.keys + (size_t)(tq * nwarps + warp) * m.rs;
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    int kept = 0;
+    for (int i0 = 0; i0 < cn; i0 += 32) {
+        const int i = i0 + lane;
+        const uint64_t key = i < cn ? reg[i] : 0ull;
+        const bool keep = i < cn && key >= pv;
+        const unsigned bal = __ballot_sync(0xFFFFFFFFu, keep);  // all reads of the round are done
+        if (keep) reg[kept + __popc(bal & lt_mask)] = key;      // lands at or below its old slot
+        kept += __popc(bal);
+    }
+    __syncwarp();
+    if (t == tq) rc = kept;
+}
+
+// Counts the buffers of the queries flagged in adopt[] into their shared histograms
+// (once, when the query's bucket mapping becomes known to this CTA).  Region counts
+// must have been published.  Per-CTA counts are formed in shared memory first: one
+// global atomic per occupied bucket.  All threads of the block.
+__device__ __noinline__ void mma_count_adopted(const ScoreArgs& a, const MmaItem& m) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    for (int b = tid; b < 1024; b += blockDim.x) m.hist[b] = 0;
+    __syncthreads();
+#pragma unroll 1
+    for (int q = 0; q < m.nq; ++q) {
+        if (!m.adopt[q]) continue;
+        const float2 r = m.rng[q];
+        const uint64_t* reg = m.keys + (size_t)(q * nwarps + warp) * m.rs;
+        const int c = m.cntw[q * 32 + warp];
+        for (int i = lane; i < c; i += 32) {
+            const float sc = key_score((uint32_t)(reg[i] >> 32));
+            if (sc >= r.x) atomicAdd(&m.hist[256 * q + sel_bucket_f(sc, r.x, r.y)], 1);
+        }
+    }
+    __syncthreads();
+    for (int b = tid; b < 1024; b += blockDim.x) {
+        const int q = b >> 8;
+        if (q < m.nq && m.adopt[q] && m.hist[b])
+            atomicAdd(a.ghist + (size_t)(m.query_begin + q) * 256 + (b & 255), (uint32_t)m.hist[b]);
+    }
+    __syncthreads();
+    if (tid < 4) m.adopt[tid] = 0;
+}
+
+// Block-wide step, entered by all threads after a barrier: refresh the thresholds
+// (shared histogram, other CTAs), let every warp purge its regions, and run a selection
+// only for queries that still lack room (final: whose candidates still exceed the list
+// size).  Sets *bail when a query cannot be settled.  Returns the caller's region count.
+__device__ __noinline__ int mma_settle(const ScoreArgs& a, const MmaItem& m, int rc, bool final) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5, t = lane & 3;
+    const int nq = m.nq;
+    PROF_T(s0);
+    SEL_ADD(0, 1);
+    // a bucket mapping another CTA has published meanwhile
+    if (tid < nq && m.rng[tid].y == 0.0f) {
+        const unsigned long long pr = *reinterpret_cast<volatile unsigned long long*>(a.grange + m.query_begin + tid);
+        if (pr) {
+            m.rng[tid] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
+            m.adopt[tid] = 1;
+        }
+    }
+    if (lane < 4) m.cntw[lane * 32 + warp] = rc;  // lane l < 4 is (g = 0, t = l)
+    __syncthreads();
+    if (m.adopt[0] | m.adopt[1] | m.adopt[2] | m.adopt[3]) mma_count_adopted(a, m);
+    if (warp < nq) mma_hist_pivot(a, m, warp, lane);
+    if (warp == nwarps - 1) mma_refresh_pivots(a, m, lane);
+    __syncthreads();
+    PROF_T(s1);
+    SEL_ADD(1, s1 - s0);
+#pragma unroll 1
+    for (int attempt = 0; attempt < 4; ++attempt) {
+#pragma unroll 1
+        PROF_T(s2);
+        for (int tq = 0; tq < nq; ++tq) mma_purge(m, tq, warp, nwarps, lane, t, rc);
+        if (lane < 4) m.cntw[lane * 32 + warp] = rc;
+        __syncthreads();
+        PROF_T(s3);
+        SEL_ADD(2, s3 - s2);
+        SEL_ADD(7, 1);
+        uint32_t over = 0u;
+#pragma unroll 1
+        for (int q = 0; q < nq; ++q) {
+            const int v = lane < nwarps ? m.cntw[q * 32 + lane] : 0;
+            const int tot = __reduce_add_sync(0xFFFFFFFFu, v), mx = __reduce_max_sync(0xFFFFFFFFu, v);
+            if (final ? tot > (int)a.list_cap : mx > m.room - 2 * MMA_SET_TILES) over |= 1u << q;
+        }
+        if (!over) break;
+        uint32_t failed = attempt == 3 ? over : 0u;
+        if (!failed)
+            failed = block_select_seg(m.keys, m.rs, m.cntw, nq, over, a.k, final ? a.list_cap - a.k : m.sel_slack, m.pivot,
+                                      m.hist, m.qmax);
+        PROF_T(s4);
+        SEL_ADD(3, s4 - s3);
+        if (failed) {
+            // equal scores, or one warp holds too much of the top: the generic kernel takes the item
+            if (tid == 0) *m.bail = 1;
+            break;
+        }
+        // publish a bucket mapping for queries that have none: from the new pivot to a
+        // quarter of the span above the largest score seen
+        if (tid < nq && m.rng[tid].y == 0.0f && m.qmax[tid] && m.pivot[tid]) {
+            const float lo = key_score((uint32_t)(m.pivot[tid] >> 32)), top = key_score(m.qmax[tid]);
+            const float hi = top + 0.25f * (top - lo);
+            const float inv = 256.0f / (hi - lo);
+            if (isfinite(lo) && isfinite(hi) && isfinite(inv) && inv > 0.0f) {
+                const unsigned long long mine_r = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(inv) << 32);
+                const unsigned long long old = atomicCAS(a.grange + m.query_begin + tid, 0ull, mine_r);
+                const unsigned long long use = old ? old : mine_r;
+                m.rng[tid] = make_float2(__uint_as_float((uint32_t)use), __uint_as_float((uint32_t)(use >> 32)));
+                m.adopt[tid] = 1;
+            }
+        }
+        __syncthreads();
+        if (m.adopt[0] | m.adopt[1] | m.adopt[2] | m.adopt[3]) mma_count_adopted(a, m);
+        PROF_T(s5);
+        SEL_ADD(4, s5 - s4);
+    }
+    if (tid < nq) atomicMax(a.gpivot + m.query_begin + tid, (unsigned long long)m.pivot[tid]);
+    __syncthreads();
+    return rc;
+}
+
 template <bool TOPK>
-__global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
+__global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    // shared layout: nf4 table | stage ring | [keys | pivot | cnt | ctl | hist]
+    // shared layout: nf4 table | stage ring | [keys | pivot | cntw | outpos | ctl | qmax | adopt | rng | hist]
     const uint32_t lut_bytes = a.nf4_table ? NF4_LUT_BYTES : 0;  // the table is left out when no NF4 tile is expected
     uint2* lut = reinterpret_cast<uint2*>(smem);
     unsigned char* tail = smem + lut_bytes + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE;
-    uint64_t* keys = reinterpret_cast<uint64_t*>(tail);            // [4][cap]
+    // Candidates of query q kept by warp w: keys[(q * nwarps + w) * rs ..], rs = cap / nwarps.
+    // A warp appends to and purges its own regions without any block-wide step.
+    uint64_t* keys = reinterpret_cast<uint64_t*>(tail);            // [4][nwarps][rs]
     uint64_t* pivot = keys + (TOPK ? (size_t)4 * a.cap : 0);       // [4]
-    int* cnt = reinterpret_cast<int*>(pivot + 4);                  // [4]
-    int* ctl = cnt + 4;   // [0] want: some query's buffer is nearly full  [1] arrived  [2] done warps  [3] bail
+    int* cntw = reinterpret_cast<int*>(pivot + 4);                 // [4][32] region counts, published for block-wide steps
+    int* outpos = cntw + 128;                                      // [4] write position in the item's candidate lists
+    int* ctl = outpos + 4;  // [0] want: a warp cannot make room alone  [1] arrived  [2] done warps  [3] bail
     int* bail = ctl + 3;
     uint32_t* qmax = reinterpret_cast<uint32_t*>(ctl + 4);  // [4] largest score word a selection has seen
     int* adopt = ctl + 8;                                   // [4] query whose buffer must be counted into the shared histogram
@@ -540,11 +902,11 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
     // i.e. chunk (lane & 7) of rows (lane >> 3) + {0, 4, 8, 12}
     const uint32_t dst_lane = (uint32_t)((lane >> 3) * MMA_ROW + (lane & 7) * 16);
     const uint32_t row_lane = (uint32_t)g * MMA_ROW;
-    // appends may continue for up to two sets per warp after the flag is raised
-    const uint32_t cap_soft = a.cap - (uint32_t)nwarps * 2 * MMA_SET_TILES;
-    const uint32_t resel_min = (a.k + cap_soft) / 2;
-    const uint32_t resel_slack = (cap_soft - a.k) / 4;
-    const uint32_t key_row = (uint32_t)t * a.cap;
+    const uint32_t rs = a.cap / (uint32_t)nwarps;          // slots per region
+    const int room = (int)rs - MMA_SET_TILES;              // a set adds at most 16 keys to a region
+    const uint32_t sel_slack = (a.cap - (uint32_t)nwarps * MMA_SET_TILES - a.k) / 4;
+    uint64_t* my_reg = keys + (size_t)(t * nwarps + warp) * rs;  // region of query t of this warp
+    const uint32_t lt_mask = (1u << lane) - 1u, t_mask = 0x11111111u << t;
 
 #ifdef SLHA_SCORE_PROFILE
     unsigned long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -552,15 +914,16 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
     const uint32_t item_end = a.cta_begin[blockIdx.x + 1];
     for (uint32_t item_id = a.cta_begin[blockIdx.x]; item_id < item_end; ++item_id) {
         const WorkItem it = a.items[item_id];
+        const int nq = (int)it.n_queries;
         PROF_T(t_item);
         __syncthreads();  // previous item fully retired (and the table is visible)
         if (TOPK && tid < 4) {
             // start from the threshold other CTAs have already proven for the query, and
             // from the query's shared histogram range if one has been published
-            const bool have = tid < (int)it.n_queries;
-            cnt[tid] = 0;
+            const bool have = tid < nq;
             qmax[tid] = 0u;
             adopt[tid] = 0;
+            outpos[tid] = 0;
             pivot[tid] = have ? *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + tid) : 0ull;
             const unsigned long long pr = have ? *reinterpret_cast<volatile unsigned long long*>(a.grange + it.query_begin + tid) : 0ull;
             rng[tid] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
@@ -573,7 +936,7 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
         bool big = false;
         {
             const int qi = g >> 1;
-            const bool have = qi < (int)it.n_queries;
+            const bool have = qi < nq;
             const float* q = a.q_coarse + (size_t)(it.query_begin + (have ? qi : 0)) * D_C;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -592,7 +955,7 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
             // sign words of query t (the query whose scores this thread finishes)
 #pragma unroll
             for (int w = 0; w < 8; ++w)
-                qs[w] = t < (int)it.n_queries ? a.q_sign[(size_t)(it.query_begin + t) * 8 + w] : 0u;
+                qs[w] = t < nq ? a.q_sign[(size_t)(it.query_begin + t) * 8 + w] : 0u;
         }
         // a query too large for the fp16 split: the generic kernel takes the item
         const bool too_big = __syncthreads_or(big) != 0;
@@ -602,8 +965,12 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
         const uint32_t n = it.n_tiles;
         const uint32_t n_sets = too_big ? 0u : (n + MMA_SET_TILES - 1) / MMA_SET_TILES;
         const uint32_t n_full = n / MMA_SET_TILES;
-        const bool mine = t < (int)it.n_queries;
+        const bool mine = t < nq;
         uint32_t* gh = a.ghist + (size_t)(it.query_begin + (mine ? t : 0)) * 256;  // my query's shared histogram
+        int rc = 0;  // keys in my_reg (the eight lanes of query t hold the same value)
+        MmaItem m;
+        m.keys = keys; m.pivot = pivot; m.cntw = cntw; m.bail = bail; m.qmax = qmax; m.adopt = adopt; m.rng = rng; m.hist = hist;
+        m.rs = rs; m.room = room; m.sel_slack = sel_slack; m.query_begin = it.query_begin; m.nq = nq;
         // prefetch state: next set to fetch, its source and its ring slot
         uint32_t s_next = (uint32_t)warp;
         const unsigned char* src = a.tiles + (it.tile_begin + (size_t)warp * MMA_SET_TILES) * TILE_BYTES + lane * 16;
@@ -630,130 +997,9 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
             src += (size_t)nwarps * MMA_SET_BYTES;
             slot_next = slot_next == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot_next + MMA_SET_STRIDE;
         };
-        // Thresholds are shared between the CTAs that scan the same query's tiles:
-        // a CTA's pivot (k of its own elements are >= it) is a proven lower bound of
-        // the query's k-th best composite key, so the maximum over CTAs is too.
-        auto refresh_pivots = [&]() {
-            if (lane < (int)it.n_queries) {
-                const unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + lane);
-                if (seen > pivot[lane]) pivot[lane] = seen;
-            }
-        };
-        // Shared score histogram of a query: every CTA counts the candidates it appends
-        // into 256 buckets of global memory (one bucket mapping per query, published by
-        // the first CTA that finishes a selection).  The counts are of real tiles, so the
-        // lower edge of the highest bucket whose count from the top reaches k is a proven
-        // lower bound of the query's k-th best score - for all CTAs at once, and without a
-        // block-wide selection.  A whole warp calls this for query q.
-        auto hist_pivot = [&](int q) {
-            const float2 r = rng[q];
-            if (r.y == 0.0f) return;
-            const uint32_t* hq = a.ghist + (size_t)(it.query_begin + q) * 256 + 248 - 8 * lane;
-            uint32_t c[8];  // buckets 255-8l .. 248-8l (descending)
-            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[7]), "=r"(c[6]), "=r"(c[5]), "=r"(c[4]) : "l"(hq));
-            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[3]), "=r"(c[2]), "=r"(c[1]), "=r"(c[0]) : "l"(hq + 4));
-            uint32_t tot = 0;
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) tot += c[jj];
-            uint32_t incl = tot;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                if (lane >= o) incl += y;
-            }
-            const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= a.k);
-            if (ok == 0u || lane != __ffs(ok) - 1) return;
-            uint32_t run = incl - tot;
-            int b = 0;
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-                if (run + c[jj] >= a.k) { b = 255 - 8 * lane - jj; break; }
-                run += c[jj];
-            }
-            if (b < 1) return;
-            // half a bucket and a few ulps below the bucket's edge: every counted key of the
-            // buckets b.. is above this bound whatever the rounding of the bucket arithmetic
-            const float e = r.x + ((float)b - 0.5f) / r.y;
-            const uint32_t ek = score_key(e);
-            const unsigned long long np = (unsigned long long)(ek > 8u ? ek - 8u : 0u) << 32;
-            if (np > pivot[q]) {
-                pivot[q] = np;
-                atomicMax(a.gpivot + it.query_begin + q, np);
-            }
-        };
-        // Counts the buffer of the queries flagged in adopt[] into their shared histograms
-        // (once, when the query's bucket mapping becomes known to this CTA).
-        auto count_adopted = [&]() {
-            // per-CTA counts in shared memory first: one global atomic per occupied bucket
-            for (int b = tid; b < 1024; b += blockDim.x) hist[b] = 0;
-            __syncthreads();
-#pragma unroll 1
-            for (int q = 0; q < (int)it.n_queries; ++q) {
-                if (!adopt[q]) continue;
-                const float2 r = rng[q];
-                const int c = min(cnt[q], (int)a.cap);
-                for (int i = tid; i < c; i += blockDim.x) {
-                    const float sc = key_score((uint32_t)(keys[(size_t)q * a.cap + i] >> 32));
-                    if (sc >= r.x) atomicAdd(&hist[256 * q + sel_bucket_f(sc, r.x, r.y)], 1);
-                }
-            }
-            __syncthreads();
-            for (int b = tid; b < 1024; b += blockDim.x) {
-                const int q = b >> 8;
-                if (q < (int)it.n_queries && adopt[q] && hist[b])
-                    atomicAdd(a.ghist + (size_t)(it.query_begin + q) * 256 + (b & 255), (uint32_t)hist[b]);
-            }
-            __syncthreads();
-            if (tid < 4) adopt[tid] = 0;
-        };
-        // All warps meet here when a query's buffer is nearly full (flag ctl[0]).  No
-        // barrier is executed in the steady state: every warp polls the flag between
-        // sets, finished warps poll it in the drain loop, so everyone arrives.
-        // final: the item is over, the buffers must come down to the list size.
-        auto settle = [&](bool final) {
-            const int trigger = final ? (int)a.list_cap : (int)resel_min;
-            // a bucket mapping another CTA has published meanwhile
-            if (tid < (int)it.n_queries && rng[tid].y == 0.0f) {
-                const unsigned long long pr = *reinterpret_cast<volatile unsigned long long*>(a.grange + it.query_begin + tid);
-                if (pr) {
-                    rng[tid] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
-                    adopt[tid] = 1;
-                }
-            }
-            __syncthreads();
-            if (adopt[0] | adopt[1] | adopt[2] | adopt[3]) count_adopted();
-            if (warp < (int)it.n_queries) hist_pivot(warp);
-            if (warp == 4) refresh_pivots();
-            __syncthreads();
-            // keys below the pivots go; a selection only where that was not enough
-            block_select_multi(keys, a.cap, cnt, (int)it.n_queries, a.k, 0u, trigger, pivot, hist, true);
-            bool more = false;
-            for (int q = 0; q < (int)it.n_queries; ++q) more |= cnt[q] > trigger;
-            if (more) {
-                const uint32_t ties = block_select_multi(keys, a.cap, cnt, (int)it.n_queries, a.k,
-                                                         final ? a.list_cap - a.k : resel_slack, trigger, pivot, hist, false, qmax);
-#pragma unroll 1
-                for (int qq = 0; qq < (int)it.n_queries; ++qq)
-                    if (ties >> qq & 1u) block_select_topk(keys + (size_t)qq * a.cap, &cnt[qq], a.k, &pivot[qq], hist);
-                // publish a bucket mapping for queries that have none: from the new pivot to a
-                // quarter of the span above the largest score seen
-                if (tid < (int)it.n_queries && rng[tid].y == 0.0f && qmax[tid]) {
-                    const float lo = key_score((uint32_t)(pivot[tid] >> 32)), top = key_score(qmax[tid]);
-                    const float hi = top + 0.25f * (top - lo);
-                    const float inv = 256.0f / (hi - lo);
-                    if (pivot[tid] && isfinite(lo) && isfinite(hi) && isfinite(inv) && inv > 0.0f) {
-                        const unsigned long long mine = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(inv) << 32);
-                        const unsigned long long old = atomicCAS(a.grange + it.query_begin + tid, 0ull, mine);
-                        const unsigned long long use = old ? old : mine;
-                        rng[tid] = make_float2(__uint_as_float((uint32_t)use), __uint_as_float((uint32_t)(use >> 32)));
-                        adopt[tid] = 1;
-                    }
-                }
-                __syncthreads();
-                if (adopt[0] | adopt[1] | adopt[2] | adopt[3]) count_adopted();
-            }
-            if (tid < (int)it.n_queries) atomicMax(a.gpivot + it.query_begin + tid, (unsigned long long)pivot[tid]);
-        };
+        // All warps meet here when some warp cannot make room in a region alone (flag
+        // ctl[0]).  No barrier is executed in the steady state: every warp polls the flag
+        // between sets, finished warps poll it in the drain loop, so everyone arrives.
         auto rendezvous = [&]() {
             PROF_T(t_rv0);
             __syncwarp();
@@ -764,7 +1010,7 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
             }
             __syncthreads();
             PROF_T(t_rv1);
-            settle(false);
+            rc = mma_settle(a, m, rc, false);
             if (tid == 0) { ctl[0] = 0; ctl[1] = 0; }
             __syncthreads();
             PROF_T(t_rv2);
@@ -807,50 +1053,53 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
             const float lam1 = (f1 & F_WARM) ? 0.0f : __uint_as_float(m1.y);
             const float sc0 = fmaf(acc0, __uint_as_float(m0.x) * (1.0f / 4080.0f), lam0 * (float)(256 - 2 * h0));
             const float sc1 = fmaf(acc1, __uint_as_float(m1.x) * (1.0f / 4080.0f), lam1 * (float)(256 - 2 * h1));
-            if (mine) {
-                const uint32_t t0 = s * MMA_SET_TILES + (uint32_t)g, t1 = t0 + 8;
-                bool live0 = t0 < n, live1 = t1 < n;
-                if (sbase) {
-                    live0 = live0 && sbase[t0] != ST_COLD;
-                    live1 = live1 && sbase[t1] != ST_COLD;
-                }
-                if (TOPK) {
-                    const uint64_t pv = pivot[t];
-                    const uint32_t pvh = (uint32_t)(pv >> 32);
-                    const uint32_t k0 = score_key(sc0), k1 = score_key(sc1);
-                    if (live0 && k0 >= pvh) {
-                        const uint64_t comp = ((uint64_t)k0 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t0));
-                        if (comp >= pv) {
-                            const uint32_t pos = (uint32_t)atomicAdd(&cnt[t], 1);
-                            if (pos < a.cap) keys[key_row + pos] = comp;
-                            if (pos >= cap_soft) *reinterpret_cast<volatile int*>(ctl) = 1;
-                            const float2 r = rng[t];
-                            if (r.y != 0.0f && sc0 >= r.x) atomicAdd(gh + sel_bucket_f(sc0, r.x, r.y), 1u);
-                        }
+            const uint32_t t0 = s * MMA_SET_TILES + (uint32_t)g, t1 = t0 + 8;
+            bool live0 = mine && t0 < n, live1 = mine && t1 < n;
+            if (sbase) {
+                live0 = live0 && sbase[t0] != ST_COLD;
+                live1 = live1 && sbase[t1] != ST_COLD;
+            }
+            if (TOPK) {
+                const uint64_t pv = pivot[t];
+                const uint64_t comp0 = ((uint64_t)score_key(sc0) << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t0));
+                const uint64_t comp1 = ((uint64_t)score_key(sc1) << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t1));
+                const bool p0 = live0 && comp0 >= pv, p1 = live1 && comp1 >= pv;
+                if (__any_sync(0xFFFFFFFFu, p0 || p1)) {
+                    // the lanes of query t append to the warp's region of that query: slots by ballot, no atomics
+                    const unsigned b0 = __ballot_sync(0xFFFFFFFFu, p0) & t_mask, b1 = __ballot_sync(0xFFFFFFFFu, p1) & t_mask;
+                    const int n0 = __popc(b0);
+                    const float2 r = rng[t];
+                    if (p0) {
+                        my_reg[rc + __popc(b0 & lt_mask)] = comp0;
+                        if (r.y != 0.0f && sc0 >= r.x) atomicAdd(gh + sel_bucket_f(sc0, r.x, r.y), 1u);
                     }
-                    if (live1 && k1 >= pvh) {
-                        const uint64_t comp = ((uint64_t)k1 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t1));
-                        if (comp >= pv) {
-                            const uint32_t pos = (uint32_t)atomicAdd(&cnt[t], 1);
-                            if (pos < a.cap) keys[key_row + pos] = comp;
-                            if (pos >= cap_soft) *reinterpret_cast<volatile int*>(ctl) = 1;
-                            const float2 r = rng[t];
-                            if (r.y != 0.0f && sc1 >= r.x) atomicAdd(gh + sel_bucket_f(sc1, r.x, r.y), 1u);
-                        }
+                    if (p1) {
+                        my_reg[rc + n0 + __popc(b1 & lt_mask)] = comp1;
+                        if (r.y != 0.0f && sc1 >= r.x) atomicAdd(gh + sel_bucket_f(sc1, r.x, r.y), 1u);
                     }
-                } else {
-                    float* o = a.scores + (size_t)(it.query_begin + t) * a.score_stride + it.index_base;
-                    if (t0 < n) o[t0] = live0 ? sc0 : -INFINITY;
-                    if (t1 < n) o[t1] = live1 ? sc1 : -INFINITY;
+                    rc += n0 + __popc(b1);
+                    if (__any_sync(0xFFFFFFFFu, rc > room)) {
+                        // a region may not take another set: drop what the current thresholds allow,
+                        // and ask for a block-wide step if that does not make room
+#pragma unroll 1
+                        for (int tq = 0; tq < nq; ++tq) mma_purge(m, tq, warp, nwarps, lane, t, rc);
+                        if (__any_sync(0xFFFFFFFFu, rc > room - 2 * MMA_SET_TILES) && lane == 0) *reinterpret_cast<volatile int*>(ctl) = 1;
+                    }
                 }
+            } else if (mine) {
+                float* o = a.scores + (size_t)(it.query_begin + t) * a.score_stride + it.index_base;
+                if (t0 < n) o[t0] = live0 ? sc0 : -INFINITY;
+                if (t1 < n) o[t1] = live1 ? sc1 : -INFINITY;
             }
             __syncwarp();
             if (TOPK) {
-                if (*reinterpret_cast<volatile int*>(ctl)) rendezvous();
-                else if ((++polls & 63u) == (uint32_t)(warp >> 2) * 16u + 8u) {
+                if (*reinterpret_cast<volatile int*>(ctl)) {
+                    rendezvous();
+                    if (bail[0]) break;
+                } else if ((++polls & 63u) == (uint32_t)(warp >> 2) * 16u + 8u) {
                     // in turn, a warp raises the threshold of query (warp & 3)
-                    if ((warp & 3) < (int)it.n_queries) hist_pivot(warp & 3);
-                    if ((warp & 3) == 0) refresh_pivots();
+                    if ((warp & 3) < nq) mma_hist_pivot(a, m, warp & 3, lane);
+                    if ((warp & 3) == 0) mma_refresh_pivots(a, m, lane);
                     __syncwarp();
                 }
             }
@@ -858,7 +1107,7 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
         PROF_T(t_loop1);
         PROF_ADD(1, t_loop1 - t_loop0);
         if (TOPK) {
-            // drain: warps that ran out of sets keep serving reselect rendezvous until all are done
+            // drain: warps that ran out of sets keep serving block-wide steps until all are done
             __syncwarp();
             if (lane == 0) atomicAdd(&ctl[2], 1);
             for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
@@ -871,35 +1120,26 @@ __global__ void __launch_bounds__(512) score_mma_kernel(ScoreArgs a) {
         __syncthreads();
         PROF_T(t_drain1);
         PROF_ADD(5, t_drain1 - t_loop1);
+        if (TOPK && !bail[0]) rc = mma_settle(a, m, rc, true);  // at most list_cap candidates per query remain
         if (bail[0]) {
             if (tid == 0) a.retry[item_id] = 1;
             continue;
         }
         if (TOPK) {
-            // at most list_cap survivors per query, then those that still clear the
-            // query's shared threshold are written out, compacted
-            settle(true);
-            __syncthreads();
-            if (tid < 4) hist[tid] = 0;
-            __syncthreads();
+            // every warp copies its regions behind each other into the item's candidate lists
 #pragma unroll 1
-            for (int qq = 0; qq < (int)it.n_queries; ++qq) {
-                const int c = min(cnt[qq], (int)a.list_cap);
-                uint64_t* dst = a.cand_keys + (size_t)(it.list_begin + qq) * a.list_cap;
-                const unsigned long long gp = *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + qq);
-                for (int i0 = 0; i0 < c; i0 += blockDim.x) {
-                    const int i = i0 + tid;
-                    const uint64_t key = i < c ? keys[(size_t)qq * a.cap + i] : 0ull;
-                    const bool keep = i < c && key >= gp;
-                    const unsigned bal = __ballot_sync(0xFFFFFFFFu, keep);
-                    int base = 0;
-                    if (lane == 0 && bal) base = atomicAdd(&hist[qq], __popc(bal));
-                    base = __shfl_sync(0xFFFFFFFFu, base, 0);
-                    if (keep) dst[base + __popc(bal & ((1u << lane) - 1))] = key;
-                }
+            for (int tq = 0; tq < nq; ++tq) {
+                const int cn = __shfl_sync(0xFFFFFFFFu, rc, tq);
+                int base = 0;
+                if (lane == 0 && cn) base = atomicAdd(&outpos[tq], cn);
+                base = __shfl_sync(0xFFFFFFFFu, base, 0);
+                const uint64_t* reg = keys + (size_t)(tq * nwarps + warp) * rs;
+                uint64_t* dst = a.cand_keys + (size_t)(it.list_begin + tq) * a.list_cap;
+                for (int i = lane; i < cn; i += 32)
+                    if (base + i < (int)a.list_cap) dst[base + i] = reg[i];
             }
             __syncthreads();
-            if (tid < (int)it.n_queries) a.cand_cnt[it.list_begin + tid] = (uint32_t)hist[tid];
+            if (tid < nq) a.cand_cnt[it.list_begin + tid] = (uint32_t)min(outpos[tid], (int)a.list_cap);
         }
         PROF_T(t_end);
         PROF_ADD(6, t_end - t_drain1);
