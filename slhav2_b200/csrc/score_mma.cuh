@@ -42,7 +42,7 @@ constexpr int MMA_HALF = 8 * MMA_ROW;                      // row g -> row g + 8
 #endif
 constexpr int MMA_DEPTH = SLHA_MMA_DEPTH;                  // cp.async ring slots per warp
 constexpr int NF4_LUT_BYTES = 256 * 16 * 8;                // [byte][16 lanes] x (hi pair, lo pair)
-constexpr int SEL_HIST_INTS = 4 * 256 + 32;                // block_select_multi: 4 histograms + state
+constexpr int SEL_HIST_INTS = 4 * 256 + 48;                // block_select_multi: 4 histograms + state
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
@@ -506,168 +506,6 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
     return ties;
 }
 
-// Selection over segmented candidate buffers.  Query q's candidates live in one
-// region per warp: keys[(q * nw + w) * rs ..] holds cntw[q * 32 + w] keys, appended
-// and purged by warp w alone.  For every query in `mask` this raises pivot[q] so that
-// between k and about k + slack of the query's keys stay at or above it; nothing is
-// moved - every warp purges its own regions against the new pivots afterwards.
-// Same bucket scheme as block_select_multi (256 equal-width score buckets over the
-// range of the scores at or above the pivot, the pivotal bucket refined while it is
-// too full); the new pivot is half a bucket below the pivotal bucket's lower edge.
-// Returns the queries that cannot be settled this way (equal or non-finite scores).
-// hist: SEL_HIST_INTS ints.  All threads of the block must call; warp w sweeps region w.
-__device__ uint32_t block_select_seg(const uint64_t* keys, uint32_t rs, const int* cntw, int nq, uint32_t mask,
-                                     uint32_t k, uint32_t slack, uint64_t* pivot, int* hist, uint32_t* qmax) {
-    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nt >> 5;
-    // [q][8]: 0 range lo, 1 range hi, 2 need, 3 active, 4 failed, 5 nothing to raise, 6 selected, 7 pivotal bucket
-    uint32_t* st = reinterpret_cast<uint32_t*>(hist + 1024);
-    if (tid < 4) {
-        const bool act = tid < nq && (mask >> tid & 1u);
-        uint32_t* s = st + 8 * tid;
-        s[0] = 0xFFFFFFFFu;
-        s[1] = 0u;
-        s[2] = k;
-        s[3] = act;
-        s[4] = 0u;
-        s[5] = 0u;
-        s[6] = act;
-        s[7] = 0u;
-    }
-    __syncthreads();
-    if (!(st[6] | st[14] | st[22] | st[30])) return 0u;
-    for (int q = 0; q < nq; ++q) {
-        if (!st[8 * q + 3]) continue;
-        const uint64_t* kq = keys + (size_t)(q * nw + warp) * rs;
-        const int c = cntw[q * 32 + warp];
-        const uint32_t floor_h = (uint32_t)(pivot[q] >> 32);
-        uint32_t mx = 0u, mn = 0xFFFFFFFFu;
-        for (int i = lane; i < c; i += 32) {
-            const uint32_t h = (uint32_t)(kq[i] >> 32);
-            if (h >= floor_h) { mx = max(mx, h); mn = min(mn, h); }
-        }
-        mx = __reduce_max_sync(0xFFFFFFFFu, mx);
-        mn = __reduce_min_sync(0xFFFFFFFFu, mn);
-        if (lane == 0) { atomicMax(&st[8 * q + 1], mx); atomicMin(&st[8 * q], mn); }
-    }
-    __syncthreads();
-    if (qmax && tid < nq && st[8 * tid + 3]) qmax[tid] = max(qmax[tid], st[8 * tid + 1]);
-    for (int pass = 0; pass < 12; ++pass) {
-        if (!(st[3] | st[11] | st[19] | st[27])) break;
-        for (int b = tid; b < 1024; b += nt) hist[b] = 0;
-        __syncthreads();
-        for (int q = 0; q < nq; ++q) {
-            if (!st[8 * q + 3]) continue;
-            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
-            float smin, inv;
-            if (!sel_range(lo, hi, smin, inv)) continue;  // settled by the scan below
-            const uint64_t* kq = keys + (size_t)(q * nw + warp) * rs;
-            const int c = cntw[q * 32 + warp];
-            for (int i = lane; i < c; i += 32) {
-                const uint32_t h = (uint32_t)(kq[i] >> 32);
-                if (h >= lo && h <= hi) atomicAdd(&hist[256 * q + sel_bucket(h, smin, inv)], 1);
-            }
-        }
-        __syncthreads();
-        bool refine = false;
-        if (warp < nq && st[8 * warp + 3]) {
-            uint32_t* s = st + 8 * warp;
-            const int* hq = hist + 256 * warp;
-            const uint32_t lo = s[0], hi = s[1], need = s[2];
-            float smin, inv;
-            if (!sel_range(lo, hi, smin, inv)) {
-                __syncwarp();
-                if (lane == 0) { s[3] = 0u; s[4] = 1u; }
-            } else {
-                // lane l owns buckets 255-8l .. 248-8l (descending)
-                int c[8], tot = 0;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) { c[j] = hq[255 - 8 * lane - j]; tot += c[j]; }
-                int incl = tot;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                    if (lane >= o) incl += y;
-                }
-                const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= (int)need);
-                if (ok == 0u) {
-                    // fewer than `need` keys at or above the pivot: nothing can be proven
-                    if (lane == 0) { s[3] = 0u; s[5] = 1u; }
-                } else {
-                    int bsel = 0, run = 0, binc = 0;
-                    const int src = __ffs(ok) - 1;
-                    if (lane == src) {
-                        run = incl - tot;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            if (run + c[j] >= (int)need) { bsel = 255 - 8 * lane - j; binc = c[j]; break; }
-                            run += c[j];
-                        }
-                    }
-                    bsel = __shfl_sync(0xFFFFFFFFu, bsel, src);
-                    run = __shfl_sync(0xFFFFFFFFu, run, src);
-                    binc = __shfl_sync(0xFFFFFFFFu, binc, src);
-                    const uint32_t kept = (k - need) + (uint32_t)(run + binc);
-                    if (kept <= k + slack) {
-                        if (lane == 0) { s[3] = 0u; s[7] = (uint32_t)bsel; }
-                    } else {
-                        refine = true;  // next range: the scores of the pivotal bucket
-                        __syncwarp();
-                        if (lane == 0) { s[2] = need - (uint32_t)run; s[7] = (uint32_t)bsel; }
-                    }
-                }
-            }
-        }
-        if (!__syncthreads_or(refine)) continue;
-        // smallest and largest score inside the pivotal bucket of the queries still active
-        uint32_t nlo[4], nhi[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) { nlo[q] = 0xFFFFFFFFu; nhi[q] = 0u; }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            if (q >= nq || !st[8 * q + 3]) continue;
-            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
-            const int bsel = (int)st[8 * q + 7];
-            float smin, inv;
-            sel_range(lo, hi, smin, inv);
-            const uint64_t* kq = keys + (size_t)(q * nw + warp) * rs;
-            const int c = cntw[q * 32 + warp];
-            for (int i = lane; i < c; i += 32) {
-                const uint32_t h = (uint32_t)(kq[i] >> 32);
-                if (h >= lo && h <= hi && sel_bucket(h, smin, inv) == bsel) { nlo[q] = min(nlo[q], h); nhi[q] = max(nhi[q], h); }
-            }
-            nlo[q] = __reduce_min_sync(0xFFFFFFFFu, nlo[q]);
-            nhi[q] = __reduce_max_sync(0xFFFFFFFFu, nhi[q]);
-        }
-        __syncthreads();  // every thread has read the old range
-        if (tid < 4 && tid < nq && st[8 * tid + 3]) { st[8 * tid] = 0xFFFFFFFFu; st[8 * tid + 1] = 0u; }
-        __syncthreads();
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-            if (q < nq && st[8 * q + 3] && lane == 0) { atomicMin(&st[8 * q], nlo[q]); atomicMax(&st[8 * q + 1], nhi[q]); }
-        __syncthreads();
-    }
-    if (tid < 4 && st[8 * tid + 6]) {
-        uint32_t* s = st + 8 * tid;
-        if (s[3]) { s[3] = 0u; s[4] = 1u; }  // still open after the last pass
-        if (!s[4] && !s[5]) {
-            // at least k keys are in the buckets s[7].. of the last range or above it
-            float smin, inv;
-            sel_range(s[0], s[1], smin, inv);
-            uint32_t ek = s[0];
-            if (s[7] >= 1u) {
-                const uint32_t e = score_key(smin + ((float)s[7] - 0.5f) / inv);
-                ek = max(ek, e > 8u ? e - 8u : 0u);
-            }
-            const uint64_t np = (uint64_t)ek << 32;
-            if (np > pivot[tid]) pivot[tid] = np;
-        }
-    }
-    __syncthreads();
-    const uint32_t failed = (st[4] ? 1u : 0u) | (st[12] ? 2u : 0u) | (st[20] ? 4u : 0u) | (st[28] ? 8u : 0u);
-    __syncthreads();
-    return failed;
-}
-
 // State of one work item of score_mma_kernel that its helper functions share.
 struct MmaItem {
     uint64_t* keys;    // [4][nwarps][rs] candidate regions
@@ -729,7 +567,7 @@ __device__ __forceinline__ void mma_hist_pivot(const ScoreArgs& a, const MmaItem
     if (b < 1) return;
     // half a bucket and a few ulps below the bucket's edge: every counted key of the
     // buckets b.. is above this bound whatever the rounding of the bucket arithmetic
-    const float e = r.x + ((float)b - 0.5f) / r.y;
+    const float e = r.x + ((float)b - 0.5f) / fabsf(r.y);
     const uint32_t ek = score_key(e);
     const unsigned long long np = (unsigned long long)(ek > 8u ? ek - 8u : 0u) << 32;
     if (np > m.pivot[q]) {
@@ -758,33 +596,270 @@ __device__ __forceinline__ void mma_purge(const MmaItem& m, int tq, int warp, in
     if (t == tq) rc = kept;
 }
 
-// Counts the buffers of the queries flagged in adopt[] into their shared histograms
-// (once, when the query's bucket mapping becomes known to this CTA).  Region counts
-// must have been published.  Per-CTA counts are formed in shared memory first: one
-// global atomic per occupied bucket.  All threads of the block.
-__device__ __noinline__ void mma_count_adopted(const ScoreArgs& a, const MmaItem& m) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    for (int b = tid; b < 1024; b += blockDim.x) m.hist[b] = 0;
+// Selection over segmented candidate buffers.  Query q's candidates live in one
+// region per warp: m.keys[(q * nw + w) * rs ..] holds m.cntw[q * 32 + w] keys, appended
+// and purged by warp w alone.  For every query in `mask` this raises m.pivot[q] so that
+// between k and about k + slack of the query's keys stay at or above it; nothing is
+// moved - every warp purges its own regions against the new pivots afterwards.
+//
+// The first histogram pass uses the query's shared bucket mapping (m.rng; created from
+// the smallest and largest score in the buffer and published when the query has none
+// yet), so the same counts serve two purposes: they are added to the query's shared
+// histogram in global memory when this CTA's buffer has not been counted there yet
+// (mapping stored negated in m.rng), and they locate the bucket in which the count from
+// the top reaches k.  While that bucket is too full it becomes the next range, with 256
+// buckets between its smallest and largest score.  The new pivot is half a bucket below
+// the pivotal bucket's lower edge.  Returns the queries that cannot be settled this way
+// (equal or non-finite scores).  All threads of the block must call; warp w sweeps
+// region w.
+__device__ __noinline__ uint32_t block_select_seg(const ScoreArgs& a, const MmaItem& m, uint32_t mask, uint32_t slack) {
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nt >> 5;
+    const int nq = m.nq;
+    const uint32_t k = a.k;
+    int* hist = m.hist;
+    // [q][8]: 0 range lo, 1 range hi (score words, inclusive), 2 need, 3 active, 4 failed, 5 nothing to raise,
+    //         6 selected, 7 pivotal bucket (0xFFFFFFFF: the keys below the mapping)
+    uint32_t* st = reinterpret_cast<uint32_t*>(hist + 1024);
+    float* fm = reinterpret_cast<float*>(hist + 1024 + 32);           // [q][2] smin, inv of the current pass
+    uint32_t* below = reinterpret_cast<uint32_t*>(hist + 1024 + 40);  // [q] keys below the mapping (first pass)
+    uint32_t* flush = below + 4;                                      // [q] first-pass counts go to the shared histogram
+    if (tid < 4) {
+        const bool act = tid < nq && (mask >> tid & 1u);
+        uint32_t* s = st + 8 * tid;
+        s[0] = act ? (uint32_t)(m.pivot[tid] >> 32) : 0u;
+        s[1] = 0xFFFFFFFFu;
+        s[2] = k;
+        s[3] = act;
+        s[4] = 0u;
+        s[5] = 0u;
+        s[6] = act;
+        s[7] = 0u;
+        below[tid] = 0u;
+        flush[tid] = 0u;
+        reinterpret_cast<uint32_t*>(hist)[tid] = 0xFFFFFFFFu;  // smallest / largest score word for a new mapping
+        hist[4 + tid] = 0;
+    }
     __syncthreads();
-#pragma unroll 1
-    for (int q = 0; q < m.nq; ++q) {
-        if (!m.adopt[q]) continue;
-        const float2 r = m.rng[q];
-        const uint64_t* reg = m.keys + (size_t)(q * nwarps + warp) * m.rs;
-        const int c = m.cntw[q * 32 + warp];
-        for (int i = lane; i < c; i += 32) {
-            const float sc = key_score((uint32_t)(reg[i] >> 32));
-            if (sc >= r.x) atomicAdd(&m.hist[256 * q + sel_bucket_f(sc, r.x, r.y)], 1);
+    if (!(st[6] | st[14] | st[22] | st[30])) return 0u;
+    // queries without a mapping: smallest and largest score in the buffer
+    bool fresh = false;
+    for (int q = 0; q < nq; ++q) fresh |= st[8 * q + 3] && m.rng[q].y == 0.0f;
+    if (fresh) {
+        for (int q = 0; q < nq; ++q) {
+            if (!st[8 * q + 3] || m.rng[q].y != 0.0f) continue;
+            const uint64_t* kq = m.keys + (size_t)(q * nw + warp) * m.rs;
+            const int c = m.cntw[q * 32 + warp];
+            uint32_t mx = 0u, mn = 0xFFFFFFFFu;
+            for (int i = lane; i < c; i += 32) {
+                const uint32_t h = (uint32_t)(kq[i] >> 32);
+                mx = max(mx, h);
+                mn = min(mn, h);
+            }
+            mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+            mn = __reduce_min_sync(0xFFFFFFFFu, mn);
+            if (lane == 0) { atomicMin(reinterpret_cast<uint32_t*>(hist) + q, mn); atomicMax(reinterpret_cast<uint32_t*>(hist) + 4 + q, mx); }
+        }
+        __syncthreads();
+        if (tid < nq && st[8 * tid + 3] && m.rng[tid].y == 0.0f) {
+            // from the smallest score to a quarter of the span above the largest; the first CTA to publish wins
+            const float lo = key_score(reinterpret_cast<uint32_t*>(hist)[tid]), top = key_score(reinterpret_cast<uint32_t*>(hist)[4 + tid]);
+            const float hi = top + 0.25f * (top - lo);
+            const float inv = 256.0f / (hi - lo);
+            if (isfinite(lo) && isfinite(hi) && isfinite(inv) && inv > 0.0f) {
+                const unsigned long long mine_r = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(inv) << 32);
+                const unsigned long long old = atomicCAS(a.grange + m.query_begin + tid, 0ull, mine_r);
+                const unsigned long long use = old ? old : mine_r;
+                m.rng[tid] = make_float2(__uint_as_float((uint32_t)use), -__uint_as_float((uint32_t)(use >> 32)));
+            } else {
+                st[8 * tid + 3] = 0u;
+                st[8 * tid + 4] = 1u;
+            }
+        }
+        __syncthreads();
+    }
+    if (tid < nq && st[8 * tid + 3]) {
+        const float2 r = m.rng[tid];
+        fm[2 * tid] = r.x;
+        fm[2 * tid + 1] = fabsf(r.y);
+        flush[tid] = r.y < 0.0f;
+    }
+    for (int pass = 0; pass < 12; ++pass) {
+        for (int b = tid; b < 1024; b += nt) hist[b] = 0;
+        __syncthreads();
+        if (!(st[3] | st[11] | st[19] | st[27])) break;
+        for (int q = 0; q < nq; ++q) {
+            if (!st[8 * q + 3]) continue;
+            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
+            const float smin = fm[2 * q], inv = fm[2 * q + 1];
+            const uint64_t* kq = m.keys + (size_t)(q * nw + warp) * m.rs;
+            const int c = m.cntw[q * 32 + warp];
+            for (int i = lane; i < c; i += 32) {
+                const uint32_t h = (uint32_t)(kq[i] >> 32);
+                if (h < lo || h > hi) continue;
+                const float sc = key_score(h);
+                if (sc < smin) atomicAdd(&below[q], 1u);
+                else atomicAdd(&hist[256 * q + sel_bucket_f(sc, smin, inv)], 1);
+            }
+        }
+        __syncthreads();
+        if (pass == 0) {
+            // this CTA's buffer enters the query's shared histogram
+            for (int b = tid; b < 1024; b += nt) {
+                const int q = b >> 8;
+                if (q < nq && flush[q] && hist[b]) atomicAdd(a.ghist + (size_t)(m.query_begin + q) * 256 + (b & 255), (uint32_t)hist[b]);
+            }
+        }
+        bool refine = false;
+        if (warp < nq && st[8 * warp + 3]) {
+            uint32_t* s = st + 8 * warp;
+            const int* hq = hist + 256 * warp;
+            const uint32_t need = s[2];
+            // lane l owns buckets 255-8l .. 248-8l (descending)
+            int c[8], tot = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { c[j] = hq[255 - 8 * lane - j]; tot += c[j]; }
+            int incl = tot;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += y;
+            }
+            const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= (int)need);
+            const int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+            if (ok == 0u) {
+                if ((uint32_t)total + below[warp] < need) {
+                    // fewer than `need` keys at or above the pivot: nothing can be proven
+                    if (lane == 0) { s[3] = 0u; s[5] = 1u; }
+                } else {
+                    // the k-th key lies below the mapping: the keys down there are the next range
+                    refine = true;
+                    __syncwarp();
+                    if (lane == 0) { s[2] = need - (uint32_t)total; s[7] = 0xFFFFFFFFu; }
+                }
+            } else {
+                int bsel = 0, run = 0, binc = 0;
+                const int src = __ffs(ok) - 1;
+                if (lane == src) {
+                    run = incl - tot;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (run + c[j] >= (int)need) { bsel = 255 - 8 * lane - j; binc = c[j]; break; }
+                        run += c[j];
+                    }
+                }
+                bsel = __shfl_sync(0xFFFFFFFFu, bsel, src);
+                run = __shfl_sync(0xFFFFFFFFu, run, src);
+                binc = __shfl_sync(0xFFFFFFFFu, binc, src);
+                const uint32_t kept = (k - need) + (uint32_t)(run + binc);
+                if (kept <= k + slack) {
+                    if (lane == 0) { s[3] = 0u; s[7] = (uint32_t)bsel; }
+                } else {
+                    refine = true;  // next range: the scores of the pivotal bucket
+                    __syncwarp();
+                    if (lane == 0) { s[2] = need - (uint32_t)run; s[7] = (uint32_t)bsel; }
+                }
+            }
+        }
+        if (!__syncthreads_or(refine)) continue;
+        // smallest and largest score inside the pivotal bucket of the queries still active
+        uint32_t nlo[4], nhi[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { nlo[q] = 0xFFFFFFFFu; nhi[q] = 0u; }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (q >= nq || !st[8 * q + 3]) continue;
+            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
+            const int bsel = (int)st[8 * q + 7];
+            const float smin = fm[2 * q], inv = fm[2 * q + 1];
+            const uint64_t* kq = m.keys + (size_t)(q * nw + warp) * m.rs;
+            const int c = m.cntw[q * 32 + warp];
+            for (int i = lane; i < c; i += 32) {
+                const uint32_t h = (uint32_t)(kq[i] >> 32);
+                if (h < lo || h > hi) continue;
+                const float sc = key_score(h);
+                const int b = sc < smin ? -1 : sel_bucket_f(sc, smin, inv);
+                if (b == bsel) { nlo[q] = min(nlo[q], h); nhi[q] = max(nhi[q], h); }
+            }
+            nlo[q] = __reduce_min_sync(0xFFFFFFFFu, nlo[q]);
+            nhi[q] = __reduce_max_sync(0xFFFFFFFFu, nhi[q]);
+        }
+        __syncthreads();  // every thread has read the old range
+        if (tid < 4 && tid < nq && st[8 * tid + 3]) { st[8 * tid] = 0xFFFFFFFFu; st[8 * tid + 1] = 0u; below[tid] = 0u; }
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (q < nq && st[8 * q + 3] && lane == 0) { atomicMin(&st[8 * q], nlo[q]); atomicMax(&st[8 * q + 1], nhi[q]); }
+        __syncthreads();
+        if (tid < nq && st[8 * tid + 3]) {
+            float smin, inv;
+            if (sel_range(st[8 * tid], st[8 * tid + 1], smin, inv)) {
+                fm[2 * tid] = smin;
+                fm[2 * tid + 1] = inv;
+            } else {
+                st[8 * tid + 3] = 0u;  // one single score, too many keys: equal scores
+                st[8 * tid + 4] = 1u;
+            }
         }
     }
-    __syncthreads();
-    for (int b = tid; b < 1024; b += blockDim.x) {
-        const int q = b >> 8;
-        if (q < m.nq && m.adopt[q] && m.hist[b])
-            atomicAdd(a.ghist + (size_t)(m.query_begin + q) * 256 + (b & 255), (uint32_t)m.hist[b]);
+    if (tid < 4 && st[8 * tid + 6]) {
+        uint32_t* s = st + 8 * tid;
+        if (s[3]) { s[3] = 0u; s[4] = 1u; }  // still open after the last pass
+        if (!s[4] && !s[5]) {
+            // at least k keys are in the buckets s[7].. of the last range or above it
+            const float smin = fm[2 * tid], inv = fm[2 * tid + 1];
+            const uint32_t e = score_key(smin + ((float)s[7] - 0.5f) / inv);
+            const uint32_t ek = max(s[0], e > 8u ? e - 8u : 0u);
+            const uint64_t np = (uint64_t)ek << 32;
+            if (np > m.pivot[tid]) m.pivot[tid] = np;
+        }
+        // the buffer is counted: appends count themselves from now on
+        if (flush[tid]) m.rng[tid].y = fabsf(m.rng[tid].y);
     }
     __syncthreads();
-    if (tid < 4) m.adopt[tid] = 0;
+    const uint32_t failed = (st[4] ? 1u : 0u) | (st[12] ? 2u : 0u) | (st[20] ? 4u : 0u) | (st[28] ? 8u : 0u);
+    __syncthreads();
+    return failed;
+}
+
+// Evens out the region counts of query q: warps holding more than the average hand
+// their surplus keys (the tail of their region) to warps holding less, through a
+// 512-key staging area in m.hist.  Any key may live in any region, so this only makes
+// room; it is needed when the best candidates cluster in the sets of a few warps.
+// All threads of the block; region counts published.  Returns the caller's count.
+__device__ __noinline__ int mma_rebalance(const MmaItem& m, int q, int rc) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5, t = lane & 3;
+    const int c = lane < nw ? m.cntw[q * 32 + lane] : 0;
+    const int total = __reduce_add_sync(0xFFFFFFFFu, c);
+    const int target = (total + nw - 1) / nw;
+    const int sur = lane < nw ? max(0, c - target) : 0, def = lane < nw ? max(0, target - c) : 0;
+    int s_in = sur, d_in = def;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xFFFFFFFFu, s_in, o), z = __shfl_up_sync(0xFFFFFFFFu, d_in, o);
+        if (lane >= o) { s_in += y; d_in += z; }
+    }
+    const int moved = __shfl_sync(0xFFFFFFFFu, s_in, 31);
+    const int c_me = __shfl_sync(0xFFFFFFFFu, c, warp);
+    const int sur_me = __shfl_sync(0xFFFFFFFFu, sur, warp), s_me = __shfl_sync(0xFFFFFFFFu, s_in - sur, warp);
+    const int def_me = __shfl_sync(0xFFFFFFFFu, def, warp), d_me = __shfl_sync(0xFFFFFFFFu, d_in - def, warp);
+    uint64_t* reg = m.keys + (size_t)(q * nw + warp) * m.rs;
+    uint64_t* staging = reinterpret_cast<uint64_t*>(m.hist);  // 512 keys
+    for (int c0 = 0; c0 < moved; c0 += 512) {
+        {
+            const int lo = max(s_me, c0), hi = min(s_me + sur_me, c0 + 512);
+            for (int j = lo + lane; j < hi; j += 32) staging[j - c0] = reg[target + (j - s_me)];
+        }
+        __syncthreads();
+        {
+            const int lo = max(d_me, c0), hi = min(d_me + def_me, min(moved, c0 + 512));
+            for (int j = lo + lane; j < hi; j += 32) reg[c_me + (j - d_me)] = staging[j - c0];
+        }
+        __syncthreads();
+    }
+    const int now = sur_me > 0 ? target : c_me + max(0, min(def_me, moved - d_me));
+    if (lane == 0) m.cntw[q * 32 + warp] = now;
+    __syncthreads();
+    return t == q ? now : rc;
 }
 
 // Block-wide step, entered by all threads after a barrier: refresh the thresholds
@@ -796,69 +871,56 @@ __device__ __noinline__ int mma_settle(const ScoreArgs& a, const MmaItem& m, int
     const int nq = m.nq;
     PROF_T(s0);
     SEL_ADD(0, 1);
-    // a bucket mapping another CTA has published meanwhile
+    // a bucket mapping another CTA has published meanwhile: known from now on, but this
+    // CTA's buffer is not in the shared histogram yet (negated inv, see block_select_seg)
     if (tid < nq && m.rng[tid].y == 0.0f) {
         const unsigned long long pr = *reinterpret_cast<volatile unsigned long long*>(a.grange + m.query_begin + tid);
-        if (pr) {
-            m.rng[tid] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
-            m.adopt[tid] = 1;
-        }
+        if (pr) m.rng[tid] = make_float2(__uint_as_float((uint32_t)pr), -__uint_as_float((uint32_t)(pr >> 32)));
     }
     if (lane < 4) m.cntw[lane * 32 + warp] = rc;  // lane l < 4 is (g = 0, t = l)
     __syncthreads();
-    if (m.adopt[0] | m.adopt[1] | m.adopt[2] | m.adopt[3]) mma_count_adopted(a, m);
     if (warp < nq) mma_hist_pivot(a, m, warp, lane);
     if (warp == nwarps - 1) mma_refresh_pivots(a, m, lane);
     __syncthreads();
     PROF_T(s1);
     SEL_ADD(1, s1 - s0);
+    const bool any_pivot = (m.pivot[0] | m.pivot[1] | m.pivot[2] | m.pivot[3]) != 0ull;
 #pragma unroll 1
     for (int attempt = 0; attempt < 4; ++attempt) {
-#pragma unroll 1
         PROF_T(s2);
-        for (int tq = 0; tq < nq; ++tq) mma_purge(m, tq, warp, nwarps, lane, t, rc);
-        if (lane < 4) m.cntw[lane * 32 + warp] = rc;
-        __syncthreads();
+        if (attempt > 0 || any_pivot) {
+#pragma unroll 1
+            for (int tq = 0; tq < nq; ++tq) mma_purge(m, tq, warp, nwarps, lane, t, rc);
+            if (lane < 4) m.cntw[lane * 32 + warp] = rc;
+            __syncthreads();
+        }
         PROF_T(s3);
         SEL_ADD(2, s3 - s2);
         SEL_ADD(7, 1);
-        uint32_t over = 0u;
+        uint32_t over = 0u, even = 0u;  // queries lacking room; of those, the ones a redistribution settles
 #pragma unroll 1
         for (int q = 0; q < nq; ++q) {
             const int v = lane < nwarps ? m.cntw[q * 32 + lane] : 0;
             const int tot = __reduce_add_sync(0xFFFFFFFFu, v), mx = __reduce_max_sync(0xFFFFFFFFu, v);
-            if (final ? tot > (int)a.list_cap : mx > m.room - 2 * MMA_SET_TILES) over |= 1u << q;
+            if (final ? tot > (int)a.list_cap : mx > m.room - 2 * MMA_SET_TILES) {
+                over |= 1u << q;
+                // few enough keys in all (a selection ran, or would drop nothing): only their spread is the problem
+                if (!final && tot <= nwarps * (m.room - 4 * MMA_SET_TILES) && (attempt > 0 || tot <= (int)(a.k + m.sel_slack))) even |= 1u << q;
+            }
         }
         if (!over) break;
         uint32_t failed = attempt == 3 ? over : 0u;
-        if (!failed)
-            failed = block_select_seg(m.keys, m.rs, m.cntw, nq, over, a.k, final ? a.list_cap - a.k : m.sel_slack, m.pivot,
-                                      m.hist, m.qmax);
+        if (!failed && (over & ~even)) failed = block_select_seg(a, m, over & ~even, final ? a.list_cap - a.k : m.sel_slack);
         PROF_T(s4);
         SEL_ADD(3, s4 - s3);
         if (failed) {
-            // equal scores, or one warp holds too much of the top: the generic kernel takes the item
+            // equal scores: the generic kernel takes the item
             if (tid == 0) *m.bail = 1;
             break;
         }
-        // publish a bucket mapping for queries that have none: from the new pivot to a
-        // quarter of the span above the largest score seen
-        if (tid < nq && m.rng[tid].y == 0.0f && m.qmax[tid] && m.pivot[tid]) {
-            const float lo = key_score((uint32_t)(m.pivot[tid] >> 32)), top = key_score(m.qmax[tid]);
-            const float hi = top + 0.25f * (top - lo);
-            const float inv = 256.0f / (hi - lo);
-            if (isfinite(lo) && isfinite(hi) && isfinite(inv) && inv > 0.0f) {
-                const unsigned long long mine_r = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(inv) << 32);
-                const unsigned long long old = atomicCAS(a.grange + m.query_begin + tid, 0ull, mine_r);
-                const unsigned long long use = old ? old : mine_r;
-                m.rng[tid] = make_float2(__uint_as_float((uint32_t)use), __uint_as_float((uint32_t)(use >> 32)));
-                m.adopt[tid] = 1;
-            }
-        }
-        __syncthreads();
-        if (m.adopt[0] | m.adopt[1] | m.adopt[2] | m.adopt[3]) mma_count_adopted(a, m);
-        PROF_T(s5);
-        SEL_ADD(4, s5 - s4);
+#pragma unroll 1
+        for (int q = 0; q < nq; ++q)
+            if (even >> q & 1u) rc = mma_rebalance(m, q, rc);
     }
     if (tid < nq) atomicMax(a.gpivot + m.query_begin + tid, (unsigned long long)m.pivot[tid]);
     __syncthreads();
@@ -971,13 +1033,19 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
         MmaItem m;
         m.keys = keys; m.pivot = pivot; m.cntw = cntw; m.bail = bail; m.qmax = qmax; m.adopt = adopt; m.rng = rng; m.hist = hist;
         m.rs = rs; m.room = room; m.sel_slack = sel_slack; m.query_begin = it.query_begin; m.nq = nq;
-        // prefetch state: next set to fetch, its source and its ring slot
-        uint32_t s_next = (uint32_t)warp;
-        const unsigned char* src = a.tiles + (it.tile_begin + (size_t)warp * MMA_SET_TILES) * TILE_BYTES + lane * 16;
-        uint32_t slot_next = 0;
+        // Sets are dealt to the warps round by round; the warp that takes a given slot of a
+        // round rotates from round to round, so that a periodic arrangement of the tiles
+        // cannot send all the best candidates to the same warp.
+        const uint32_t rounds = (n_sets + (uint32_t)nwarps - 1) / (uint32_t)nwarps;
+        auto set_of = [&](uint32_t j) { return j * (uint32_t)nwarps + (((uint32_t)warp + j + (j >> 4)) & (uint32_t)(nwarps - 1)); };
+        const unsigned char* tbase = a.tiles + it.tile_begin * TILE_BYTES + lane * 16;
+        // prefetch state: next round to fetch and its ring slot
+        uint32_t j_next = 0, slot_next = 0;
         auto issue = [&]() {
-            if (s_next < n_sets) {
+            const uint32_t s_next = set_of(j_next);
+            if (j_next < rounds && s_next < n_sets) {
                 const uint32_t dst = stage_s + slot_next + dst_lane;
+                const unsigned char* src = tbase + (size_t)s_next * MMA_SET_BYTES;
                 if (s_next < n_full) {
                     cp_async16_s<0, 0>(dst, src, 16);
                     cp_async16_s<512, 4 * MMA_ROW>(dst, src, 16);
@@ -993,8 +1061,7 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
                 }
             }
             cp_async_commit();
-            s_next += (uint32_t)nwarps;
-            src += (size_t)nwarps * MMA_SET_BYTES;
+            ++j_next;
             slot_next = slot_next == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot_next + MMA_SET_STRIDE;
         };
         // All warps meet here when some warp cannot make room in a region alone (flag
@@ -1023,12 +1090,14 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
         PROF_T(t_loop0);
         PROF_ADD(0, t_loop0 - t_item);
         uint32_t slot = 0, polls = 0;
-        for (uint32_t s = (uint32_t)warp; s < n_sets; s += (uint32_t)nwarps) {
+        for (uint32_t j = 0; j < rounds; ++j) {
             issue();
             cp_async_wait<MMA_DEPTH - 1>();
             __syncwarp();
+            const uint32_t s = set_of(j);
             const uint32_t rb = stage_s + slot + row_lane;
             slot = slot == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot + MMA_SET_STRIDE;
+            if (s >= n_sets) continue;  // the last round may be partial
             const uint2 m0 = lds_v2<96>(rb), m1 = lds_v2<96 + MMA_HALF>(rb);    // scale, lambda
             const uint4 x0 = lds_v4<112>(rb), x1 = lds_v4<112 + MMA_HALF>(rb);  // position, head|flags, gs[8]
             const uint32_t f0 = x0.y >> 16, f1 = x1.y >> 16;
@@ -1071,11 +1140,11 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
                     const float2 r = rng[t];
                     if (p0) {
                         my_reg[rc + __popc(b0 & lt_mask)] = comp0;
-                        if (r.y != 0.0f && sc0 >= r.x) atomicAdd(gh + sel_bucket_f(sc0, r.x, r.y), 1u);
+                        if (r.y > 0.0f && sc0 >= r.x) atomicAdd(gh + sel_bucket_f(sc0, r.x, r.y), 1u);
                     }
                     if (p1) {
                         my_reg[rc + n0 + __popc(b1 & lt_mask)] = comp1;
-                        if (r.y != 0.0f && sc1 >= r.x) atomicAdd(gh + sel_bucket_f(sc1, r.x, r.y), 1u);
+                        if (r.y > 0.0f && sc1 >= r.x) atomicAdd(gh + sel_bucket_f(sc1, r.x, r.y), 1u);
                     }
                     rc += n0 + __popc(b1);
                     if (__any_sync(0xFFFFFFFFu, rc > room)) {
