@@ -277,7 +277,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     SLHA_TRY(p->b_items.ensure(all.size() * sizeof(WorkItem)));
     SLHA_TRY(p->b_qbegin.ensure(nq * 4));
     SLHA_TRY(p->b_qcount.ensure(nq * 4));
-    p->list_cap = (k + std::max<uint32_t>(64, k / 4) + 31) / 32 * 32;
+    p->list_cap = (k + std::max<uint32_t>(64, k / 2) + 31) / 32 * 32;
     SLHA_TRY(p->b_keys.ensure((size_t)n_lists * p->list_cap * 8));
     SLHA_TRY(p->b_cnt.ensure((size_t)n_lists * 4));
     SLHA_TRY(p->b_retry.ensure(all.size() * 4));

@@ -801,19 +801,39 @@ __device__ __noinline__ uint32_t block_select_seg(const ScoreArgs& a, const MmaI
             }
         }
     }
-    if (tid < 4 && st[8 * tid + 6]) {
-        uint32_t* s = st + 8 * tid;
-        if (s[3]) { s[3] = 0u; s[4] = 1u; }  // still open after the last pass
-        if (!s[4] && !s[5]) {
-            // at least k keys are in the buckets s[7].. of the last range or above it
-            const float smin = fm[2 * tid], inv = fm[2 * tid + 1];
-            const uint32_t e = score_key(smin + ((float)s[7] - 0.5f) / inv);
-            const uint32_t ek = max(s[0], e > 8u ? e - 8u : 0u);
-            const uint64_t np = (uint64_t)ek << 32;
-            if (np > m.pivot[tid]) m.pivot[tid] = np;
+    if (tid < 4 && st[8 * tid + 6] && st[8 * tid + 3]) { st[8 * tid + 3] = 0u; st[8 * tid + 4] = 1u; }  // still open after the last pass
+    __syncthreads();
+    // The new pivot is the smallest score of the pivotal bucket: exactly the keys counted
+    // above stay.  Warp w reports the minimum of its region, thread q combines them.
+    {
+        uint32_t* wmin = reinterpret_cast<uint32_t*>(hist);  // [q][32]
+#pragma unroll 1
+        for (int q = 0; q < nq; ++q) {
+            if (!st[8 * q + 6] || st[8 * q + 4] || st[8 * q + 5]) continue;
+            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
+            const int bsel = (int)st[8 * q + 7];
+            const float smin = fm[2 * q], inv = fm[2 * q + 1];
+            const uint64_t* kq = m.keys + (size_t)(q * nw + warp) * m.rs;
+            const int c = m.cntw[q * 32 + warp];
+            uint32_t mn = 0xFFFFFFFFu;
+            for (int i = lane; i < c; i += 32) {
+                const uint32_t h = (uint32_t)(kq[i] >> 32);
+                if (h < lo || h > hi) continue;
+                const float sc = key_score(h);
+                const int b = sc < smin ? -1 : sel_bucket_f(sc, smin, inv);
+                if (b == bsel) mn = min(mn, h);
+            }
+            mn = __reduce_min_sync(0xFFFFFFFFu, mn);
+            if (lane == 0) wmin[q * 32 + warp] = mn;
         }
-        // the buffer is counted: appends count themselves from now on
-        if (flush[tid]) m.rng[tid].y = fabsf(m.rng[tid].y);
+        __syncthreads();
+        if (tid < nq && st[8 * tid + 6] && !st[8 * tid + 4] && !st[8 * tid + 5]) {
+            uint32_t mn = 0xFFFFFFFFu;
+            for (int w = 0; w < nw; ++w) mn = min(mn, wmin[tid * 32 + w]);
+            const uint64_t np = (uint64_t)mn << 32;
+            if (mn != 0xFFFFFFFFu && np > m.pivot[tid]) m.pivot[tid] = np;
+        }
+        if (tid < 4 && st[8 * tid + 6] && flush[tid]) m.rng[tid].y = fabsf(m.rng[tid].y);  // the buffer is counted: appends count themselves from now on
     }
     __syncthreads();
     const uint32_t failed = (st[4] ? 1u : 0u) | (st[12] ? 2u : 0u) | (st[20] ? 4u : 0u) | (st[28] ? 8u : 0u);
@@ -914,6 +934,7 @@ __device__ __noinline__ int mma_settle(const ScoreArgs& a, const MmaItem& m, int
         PROF_T(s4);
         SEL_ADD(3, s4 - s3);
         if (failed) {
+            SEL_ADD(attempt == 3 ? 5 : 6, 1);
             // equal scores: the generic kernel takes the item
             if (tid == 0) *m.bail = 1;
             break;
@@ -1128,6 +1149,31 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
                 live0 = live0 && sbase[t0] != ST_COLD;
                 live1 = live1 && sbase[t1] != ST_COLD;
             }
+            if (TOPK && j == 0) {
+                // First set of the warp: a query without a bucket mapping gets one from the 16
+                // scores this warp has just computed for it - their range widened by 1.5 spans
+                // on both sides.  Any monotone mapping is valid; this one only has to put the
+                // final threshold somewhere inside its 256 buckets.  The first CTA to publish wins.
+                float mn = fminf(live0 ? sc0 : INFINITY, live1 ? sc1 : INFINITY), mx = fmaxf(live0 ? sc0 : -INFINITY, live1 ? sc1 : -INFINITY);
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) {
+                    mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, o));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+                }
+                if (g == 0 && mine && rng[t].y == 0.0f) {
+                    unsigned long long pr = *reinterpret_cast<volatile unsigned long long*>(a.grange + it.query_begin + t);
+                    if (!pr && mx > mn) {
+                        const float span = mx - mn, lo = mn - 1.5f * span, inv = 256.0f / (4.0f * span);
+                        if (isfinite(lo) && isfinite(inv) && inv > 0.0f) {
+                            const unsigned long long mine_r = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(inv) << 32);
+                            const unsigned long long old = atomicCAS(a.grange + it.query_begin + t, 0ull, mine_r);
+                            pr = old ? old : mine_r;
+                        }
+                    }
+                    if (pr) rng[t] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
+                }
+                __syncwarp();
+            }
             if (TOPK) {
                 const uint64_t pv = pivot[t];
                 const uint64_t comp0 = ((uint64_t)score_key(sc0) << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t0));
@@ -1151,7 +1197,11 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
                         // a region may not take another set: drop what the current thresholds allow,
                         // and ask for a block-wide step if that does not make room
 #pragma unroll 1
-                        for (int tq = 0; tq < nq; ++tq) mma_purge(m, tq, warp, nwarps, lane, t, rc);
+                        for (int tq = 0; tq < nq; ++tq) {
+                            mma_hist_pivot(a, m, tq, lane);
+                            __syncwarp();
+                            mma_purge(m, tq, warp, nwarps, lane, t, rc);
+                        }
                         if (__any_sync(0xFFFFFFFFu, rc > room - 2 * MMA_SET_TILES) && lane == 0) *reinterpret_cast<volatile int*>(ctl) = 1;
                     }
                 }
