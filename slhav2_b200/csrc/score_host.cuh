@@ -18,7 +18,7 @@ int env_int(const char* name, int dflt) {
 
 size_t mma_smem_bytes(int nwarps, uint32_t cap, bool nf4_table) {
     return (size_t)(nf4_table ? NF4_LUT_BYTES : 0) + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE + (size_t)4 * cap * 8 + 4 * 8 +
-           (128 + 4 + 20 + SEL_HIST_INTS) * 4 + 16;
+           (128 + 4 + 12 + SEL_HIST_INTS) * 4 + 16;
 }
 
 size_t score_smem_bytes(int G, int nwarps, bool topk, uint32_t cap) {

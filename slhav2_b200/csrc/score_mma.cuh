@@ -222,10 +222,8 @@ __device__ __forceinline__ bool sel_range(uint32_t lo, uint32_t hi, float& smin,
 // (uniform over the block) and left for block_select_topk, which also orders by
 // index.  hist: SEL_HIST_INTS ints.  All threads of the block must call.
 // pivot_only: no selection, the buffers are only purged of keys below the pivot.
-// qmax (optional, [4]): receives the largest score word seen by a full selection.
 __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, int nq, uint32_t k, uint32_t slack,
-                                       int trigger, uint64_t* pivot, int* hist, bool pivot_only = false,
-                                       uint32_t* qmax = nullptr) {
+                                       int trigger, uint64_t* pivot, int* hist, bool pivot_only = false) {
     const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
     // [q][8]: 0 range lo, 1 range hi, 2 need, 3 active, 4 exact selection wanted, 5 kept, 6 selected, 7 pivotal bucket
     uint32_t* st = reinterpret_cast<uint32_t*>(hist + 1024);
@@ -263,7 +261,6 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
         if (lane == 0) { atomicMax(&st[8 * q + 1], mx); atomicMin(&st[8 * q], mn); }
     }
     __syncthreads();
-    if (qmax && tid < nq && st[8 * tid + 3]) qmax[tid] = max(qmax[tid], st[8 * tid + 1]);
     PROF_T(ts1);
     SEL_ADD(4, ts1 - ts0);
     for (int pass = 0; pass < 12; ++pass) {
@@ -512,8 +509,6 @@ struct MmaItem {
     uint64_t* pivot;   // [4]
     int* cntw;         // [4][32] published region counts
     int* bail;
-    uint32_t* qmax;    // [4]
-    int* adopt;        // [4]
     float2* rng;       // [4]
     int* hist;         // SEL_HIST_INTS
     uint32_t rs;       // slots per region
@@ -953,7 +948,7 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    // shared layout: nf4 table | stage ring | [keys | pivot | cntw | outpos | ctl | qmax | adopt | rng | hist]
+    // shared layout: nf4 table | stage ring | [keys | pivot | cntw | outpos | ctl | rng | hist]
     const uint32_t lut_bytes = a.nf4_table ? NF4_LUT_BYTES : 0;  // the table is left out when no NF4 tile is expected
     uint2* lut = reinterpret_cast<uint2*>(smem);
     unsigned char* tail = smem + lut_bytes + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE;
@@ -965,10 +960,8 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
     int* outpos = cntw + 128;                                      // [4] write position in the item's candidate lists
     int* ctl = outpos + 4;  // [0] want: a warp cannot make room alone  [1] arrived  [2] done warps  [3] bail
     int* bail = ctl + 3;
-    uint32_t* qmax = reinterpret_cast<uint32_t*>(ctl + 4);  // [4] largest score word a selection has seen
-    int* adopt = ctl + 8;                                   // [4] query whose buffer must be counted into the shared histogram
-    float2* rng = reinterpret_cast<float2*>(ctl + 12);      // [4] (smin, inv) of the query's shared score histogram; inv 0 = none yet
-    int* hist = ctl + 20;  // SEL_HIST_INTS
+    float2* rng = reinterpret_cast<float2*>(ctl + 4);  // [4] (smin, inv) of the query's shared score histogram; inv 0 = none yet
+    int* hist = ctl + 12;  // SEL_HIST_INTS
     const uint32_t smem_s = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t stage_s = smem_s + lut_bytes + (uint32_t)warp * MMA_DEPTH * MMA_SET_STRIDE;
 
@@ -1004,8 +997,6 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
             // start from the threshold other CTAs have already proven for the query, and
             // from the query's shared histogram range if one has been published
             const bool have = tid < nq;
-            qmax[tid] = 0u;
-            adopt[tid] = 0;
             outpos[tid] = 0;
             pivot[tid] = have ? *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + tid) : 0ull;
             const unsigned long long pr = have ? *reinterpret_cast<volatile unsigned long long*>(a.grange + it.query_begin + tid) : 0ull;
@@ -1052,7 +1043,7 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
         uint32_t* gh = a.ghist + (size_t)(it.query_begin + (mine ? t : 0)) * 256;  // my query's shared histogram
         int rc = 0;  // keys in my_reg (the eight lanes of query t hold the same value)
         MmaItem m;
-        m.keys = keys; m.pivot = pivot; m.cntw = cntw; m.bail = bail; m.qmax = qmax; m.adopt = adopt; m.rng = rng; m.hist = hist;
+        m.keys = keys; m.pivot = pivot; m.cntw = cntw; m.bail = bail; m.rng = rng; m.hist = hist;
         m.rs = rs; m.room = room; m.sel_slack = sel_slack; m.query_begin = it.query_begin; m.nq = nq;
         // Sets are dealt to the warps round by round; the warp that takes a given slot of a
         // round rotates from round to round, so that a periodic arrangement of the tiles

@@ -118,6 +118,54 @@ def test_long_segment_many_items_shares_thresholds():
     check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
 
 
+def test_heavy_ties_longer_than_the_candidate_buffers():
+    # every score appears 2000 times and the segment is far longer than the in-kernel candidate
+    # buffers: the bucket selection cannot separate equal scores, so the item is handed to the
+    # generic kernel; the answer is still the exact order, ties to the lower index
+    base = H.random_tiles(50, 1, seed=21)
+    tiles = np.concatenate([base] * 2000)
+    qc, qs = H.random_queries(2, 22)
+    n = len(tiles)
+    dt = S.to_device(tiles)
+    gi, gs_, gc = S.score_topk(dt, S.make_segments([(0, n, 0, 2, 0)]), qc, qs, 2, 100)
+    assert np.all(gc == 100)
+    for j in range(2):
+        gpu_all = S.score_tiles(tiles, n, qc[j:j + 1], qs[j:j + 1], 1)[0]
+        oi, _ = ora.topk(gpu_all, 100)
+        assert np.array_equal(gi[j], oi)
+
+
+def test_periodic_tiles_do_not_starve_a_warp():
+    # a tile pattern that repeats every 4096 tiles sends the same tiles to the same warps of a CTA
+    # unless the set assignment rotates; either way the regions are rebalanced and the answer is exact
+    n, k, nq = 262144, 1024, 4
+    base = H.random_tiles(4096, 2, seed=23)
+    tiles = np.tile(base, n // 4096)
+    tiles["dynamic_lambda"] *= (1 + 0.3 * np.random.default_rng(2).random(n)).astype(F)
+    qc, qs = H.random_queries(2 * nq, 24)
+    dt = S.to_device(tiles)
+    segs = [(0, n // 2, 0, nq, 0), (n // 2, n // 2, nq, nq, 0)]
+    gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, 2 * nq, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+
+
+def test_large_queries_are_scored_by_the_generic_kernel():
+    # |q| above what the fp16 hi/lo split of the tensor-core kernel can carry
+    n, k, nq = 30000, 64, 4
+    tiles = H.random_tiles(n, 1, seed=25)
+    qc, qs = H.random_queries(nq, 26)
+    qc = (qc * F(1.0e4)).astype(F)
+    dt = S.to_device(tiles)
+    gi, gs_, gc = S.score_topk(dt, S.make_segments([(0, n, 0, nq, 0)]), qc, qs, nq, k)
+    assert np.all(gc == k)
+    for j in range(nq):
+        want = ora.score_tiles(tiles, qc[j], qs[j])
+        tol = 1e-3 * (1 + np.abs(want))
+        assert np.all(np.abs(gs_[j] - want[gi[j]]) <= tol[gi[j]])
+        oi, ov = ora.topk(want, k)
+        assert all(abs(want[i] - ov[-1]) <= 2 * tol[i] for i in set(oi) ^ set(gi[j].tolist()))
+
+
 def test_generic_kernel_only_mode_matches():
     # SLHA_B200_SCORE_IMPL=0 disables the tensor-core kernel: same answers from the generic one
     import subprocess
