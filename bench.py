@@ -149,10 +149,13 @@ class ClockSampler:
         return out
 
 
-# DRAM bytes per tile (read + write) of the score kernel, from the ncu captures summarised in
-# profiles/score_mma_kernel_c2_nf4_4layers.md and profiles/score_mma_kernel_c5_int4_128k_tokens.md;
-# traffic grows in proportion to the tile count, so it is scaled to the tiles of a launch.
-NCU_DRAM_BYTES_PER_TILE = {"c2": 131.9, "c5": 132.0}
+# DRAM traffic of the score kernel from the ncu captures summarised in
+# profiles/score_mma_kernel_c2_nf4_4layers.md and profiles/score_mma_kernel_c5_int4_128k_tokens.md:
+# (bytes read per tile, bytes written per work item).  Reads grow with the tile count (every tile is
+# read once), writes with the number of work items (segments + one cut per persistent CTA), so a full
+# launch is reads x tiles + writes x items.
+NCU_DRAM = {"c2": (131.7, 21.1e6 / 179), "c5": (131.7, 20.98e6 / 155)}
+SCORE_CTAS = 148
 
 
 def measured_peak_gbs():
@@ -392,8 +395,9 @@ def gpu_arm(args, w):
                      "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
                      "kernel_ms": k_ms, "merge_kernel_ms": float(np.mean(merge_ms)) if len(merge_ms) else None,
                      "algorithmic_bytes_per_launch": n_tiles * 128,
-                     "traffic": NCU_DRAM_BYTES_PER_TILE.get(args.workload, 132.0) * n_tiles,
-                     "traffic_source": "ncu dram__bytes_read+write per tile on a reduced case, scaled by tiles (profiles/)"},
+                     "traffic": NCU_DRAM[args.workload][0] * n_tiles + NCU_DRAM[args.workload][1] * (len(segs) + SCORE_CTAS - 1),
+                     "traffic_source": "ncu dram__bytes_read per tile and dram__bytes_write per work item on a reduced case, "
+                                       "scaled to this launch's tiles and work items (profiles/)"},
         "e2e": {"value": total_tiles / (e2e_ms / args.steps * 1e-3), "unit": "tiles/s", "ms_per_step": e2e_ms / args.steps,
                 "h2d_bytes_per_step": int(nq * (512 + 32)), "d2h_bytes_per_step": int(nq * k * 8 + (nq * 4 if world == 1 else 0))},
         "gpu_launches": int(launches),

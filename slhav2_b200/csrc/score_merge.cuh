@@ -53,6 +53,9 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
 __device__ void sort_and_emit(uint64_t* buf, uint32_t kp2, uint32_t m, uint32_t k, uint32_t Q,
                               uint32_t* out_index, float* out_score, uint32_t* out_count) {
     const uint32_t tid = threadIdx.x, nt = blockDim.x;
+    // Comparator i of a stage with stride <= 32 touches only elements [64 (i / 32), +64): the 32
+    // comparators a warp executes together stay inside one 64-element chunk, so those stages need no
+    // block barrier, only the stages that cross chunks (and the step into or out of them) do.
     for (uint32_t size = 2; size <= kp2; size <<= 1) {
         for (uint32_t stride = size >> 1; stride; stride >>= 1) {
             for (uint32_t i = tid; i < kp2 / 2; i += nt) {
@@ -62,9 +65,12 @@ __device__ void sort_and_emit(uint64_t* buf, uint32_t kp2, uint32_t m, uint32_t 
                 const uint64_t x = buf[lo], y = buf[hi];
                 if ((x < y) == desc) { buf[lo] = y; buf[hi] = x; }
             }
-            __syncthreads();
+            const uint32_t next_stride = stride > 1 ? stride >> 1 : size;
+            if (stride > 32 || next_stride > 32) __syncthreads();
+            else __syncwarp();
         }
     }
+    __syncthreads();
     for (uint32_t r = tid; r < k; r += nt) {
         const bool v = r < m;
         const uint64_t key = v ? buf[r] : 0ull;
