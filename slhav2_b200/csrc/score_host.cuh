@@ -164,7 +164,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     p->cap = cap;
 
     // tensor-core kernel: persistent CTAs (one per SM unless shared memory allows more)
-    p->mma_threads = env_int("SLHA_B200_MMA_THREADS", 512);
+    p->mma_threads = env_int("SLHA_B200_MMA_THREADS", 512) == 256 ? 256 : 512;  // 8 or 16 warps: the kernel deals sets round-robin with a power-of-two mask
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
     {
