@@ -582,7 +582,7 @@ Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Se
     uint32_t kp2 = 2;
     while (kp2 < k) kp2 <<= 1;
     CompLists L{sc->cand_keys, sc->cand_cnt, sc->q_list_begin, sc->q_list_count, k};
-    const uint32_t cap_s = merge_cap((uint64_t)max_parts * k, kp2);
+    const uint32_t cap_s = merge_cap((uint64_t)max_parts * k, kp2, k);
     topk_merge_kernel<CompLists><<<(uint32_t)nq, cap_s > 4096 ? 512 : 256, merge_smem(cap_s), c->stream>>>(
         L, k, kp2, cap_s, d_out_index, d_out_score, d_out_count);
     count_launch();
@@ -595,6 +595,12 @@ Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Se
 #ifdef SLHA_SCORE_PROFILE
 extern "C" int slha_debug_score_prof(unsigned long long* out) {
     return (int)cudaMemcpyFromSymbol(out, slha::g_score_prof, sizeof(unsigned long long) * 148 * 8);
+}
+extern "C" int slha_debug_merge_prof(unsigned long long* out) {
+    int rc = (int)cudaMemcpyFromSymbol(out, slha::g_merge_prof, sizeof(unsigned long long) * 8);
+    static unsigned long long zero[8];
+    cudaMemcpyToSymbol(slha::g_merge_prof, zero, sizeof(zero));
+    return rc;
 }
 extern "C" int slha_debug_sel_prof(unsigned long long* out, int reset) {
     int rc = (int)cudaMemcpyFromSymbol(out, slha::g_sel_prof, sizeof(unsigned long long) * 148 * 8);

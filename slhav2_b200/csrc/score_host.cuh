@@ -55,9 +55,13 @@ Status launch_score(Ctx* c, int G, const ScoreArgs& a, uint32_t grid, int thread
 int group_width(uint32_t nq) { return nq >= 3 ? 4 : (int)nq; }
 
 // shared-memory candidate slots of the merge kernel for at most `total` candidates per query
-uint32_t merge_cap(uint64_t total, uint32_t kp2) {
-    const uint64_t want = std::max<uint64_t>(kp2, (total + 255) / 256 * 256);
-    return (uint32_t)std::min<uint64_t>(want, std::max<uint32_t>(kp2, 24576));
+// (k results wanted, kp2 = k rounded up to a power of two).  kp2 + k slots let the merge kernel order
+// its winners by bucket placement next to them; more buys nothing: longer inputs go through the
+// kernel's bucket pre-filter, which gathers only k plus one bucket of candidates, and a small buffer
+// lets more CTAs share an SM.
+uint32_t merge_cap(uint64_t total, uint32_t kp2, uint32_t k) {
+    const uint64_t enough = ((uint64_t)kp2 + k + 256 + 255) / 256 * 256;
+    return (uint32_t)std::min<uint64_t>(enough, 24576);
 }
 size_t merge_smem(uint32_t cap_s) { return (size_t)cap_s * 8 + 8 + (SEL_HIST_INTS + 4) * 4; }
 
@@ -419,7 +423,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     }
     if (timed) SLHA_CUDA(cudaEventRecord(tev[1], c->stream));
     CompLists L{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, p->list_cap};
-    const uint32_t cap_s = merge_cap((uint64_t)p->max_parts * p->list_cap, p->kp2);
+    const uint32_t cap_s = merge_cap((uint64_t)p->max_parts * p->list_cap, p->kp2, k);
     const size_t smem = merge_smem(cap_s);
     static thread_local bool configured = false;
     if (!configured) {
@@ -475,7 +479,7 @@ Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* 
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
         configured = true;
     }
-    const uint32_t cap_s = merge_cap(n_lists * k_in, kp2);
+    const uint32_t cap_s = merge_cap((uint64_t)n_lists * k_in, kp2, k_out);
     topk_merge_kernel<PairLists><<<n_queries, cap_s > 4096 ? 512 : 256, merge_smem(cap_s), c->stream>>>(L, k_out, kp2, cap_s, out_index, out_score, nullptr);
     count_launch();
     SLHA_CUDA(cudaGetLastError());

@@ -8,6 +8,10 @@
 namespace slha {
 namespace {
 
+#ifdef SLHA_SCORE_PROFILE
+__device__ unsigned long long g_merge_prof[8];  // development aid: summed phase cycles of the merge CTAs
+#endif
+
 // Candidate accessors: element e of query Q as a composite key, 0 = absent.
 struct CompLists {  // lists written by score_kernel
     const uint64_t* keys;      // [n_lists][k] (k here = slots per list, >= the k asked for)
@@ -49,31 +53,119 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     }
 };
 
-// Sort buf[0..kp2) descending (bitonic, kp2 a power of two) and write the k outputs of query Q.
-__device__ void sort_and_emit(uint64_t* buf, uint32_t kp2, uint32_t m, uint32_t k, uint32_t Q,
-                              uint32_t* out_index, float* out_score, uint32_t* out_count) {
-    const uint32_t tid = threadIdx.x, nt = blockDim.x;
-    // Comparator i of a stage with stride <= 32 touches only elements [64 (i / 32), +64): the 32
-    // comparators a warp executes together stay inside one 64-element chunk, so those stages need no
-    // block barrier, only the stages that cross chunks (and the step into or out of them) do.
-    for (uint32_t size = 2; size <= kp2; size <<= 1) {
-        for (uint32_t stride = size >> 1; stride; stride >>= 1) {
-            for (uint32_t i = tid; i < kp2 / 2; i += nt) {
-                const uint32_t lo = 2 * i - (i & (stride - 1));
-                const uint32_t hi = lo + stride;
-                const bool desc = (lo & size) == 0;
-                const uint64_t x = buf[lo], y = buf[hi];
-                if ((x < y) == desc) { buf[lo] = y; buf[hi] = x; }
-            }
-            const uint32_t next_stride = stride > 1 ? stride >> 1 : size;
-            if (stride > 32 || next_stride > 32) __syncthreads();
-            else __syncwarp();
+// Orders buf[0..m) descending into out[0..m) by bucket placement: 1024 equal-width score buckets
+// between the smallest and the largest score (highest first), a counting pass, an exclusive scan, a
+// scatter, and an insertion sort inside every bucket by one thread.  The winners of a top-k are a
+// thin tail, a handful of keys per bucket, so this replaces the 55 dependent stages of a bitonic
+// sort of 1024 keys by six barriers.  Returns false (nothing written that matters) when a bucket
+// would hold more than 16 keys or the scores cannot be bucketed; the caller then sorts bitonically.
+// hist: SEL_HIST_INTS ints.  All threads of the block.
+__device__ bool bucket_sort(const uint64_t* buf, uint64_t* out, uint32_t m, int* hist) {
+    const uint32_t tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int NB = 1024;
+    uint32_t* st = reinterpret_cast<uint32_t*>(hist + NB);  // 0 min, 1 max, 2 largest bucket, 8.. warp totals
+    if (tid == 0) { st[0] = 0xFFFFFFFFu; st[1] = 0u; st[2] = 0u; }
+    for (uint32_t b = tid; b < NB; b += nt) hist[b] = 0;
+    __syncthreads();
+    uint32_t mn = 0xFFFFFFFFu, mx = 0u;
+    for (uint32_t i = tid; i < m; i += nt) {
+        const uint32_t h = (uint32_t)(buf[i] >> 32);
+        mn = min(mn, h);
+        mx = max(mx, h);
+    }
+    mn = __reduce_min_sync(0xFFFFFFFFu, mn);
+    mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+    if (lane == 0) { atomicMin(&st[0], mn); atomicMax(&st[1], mx); }
+    __syncthreads();
+    const float smin = key_score(st[0]), smax = key_score(st[1]);
+    const float inv = (float)NB / (smax - smin);
+    if (!(st[1] > st[0]) || !isfinite(smin) || !isfinite(smax) || !isfinite(inv)) return false;
+    auto bucket = [&](uint64_t key) {
+        const int b = (int)((smax - key_score((uint32_t)(key >> 32))) * inv);  // highest score -> bucket 0
+        return b < 0 ? 0 : (b > NB - 1 ? NB - 1 : b);
+    };
+    for (uint32_t i = tid; i < m; i += nt) atomicAdd(&hist[bucket(buf[i])], 1);
+    __syncthreads();
+    // exclusive scan of the bucket counts: thread t owns NB / nt consecutive buckets
+    const uint32_t per = NB / nt;  // 2 or 4 (256 or 512 threads)
+    int c[4], sum = 0, big = 0;
+#pragma unroll
+    for (uint32_t jj = 0; jj < 4; ++jj) {
+        c[jj] = jj < per ? hist[tid * per + jj] : 0;
+        sum += c[jj];
+        big = max(big, c[jj]);
+    }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+        if ((int)lane >= o) incl += y;
+    }
+    big = __reduce_max_sync(0xFFFFFFFFu, big);
+    if (lane == 31) st[8 + warp] = (uint32_t)incl;
+    if (lane == 0) atomicMax(&st[2], (uint32_t)big);
+    __syncthreads();
+    if (st[2] > 16u) return false;
+    int base = incl - sum;
+    for (uint32_t w = 0; w < warp; ++w) base += (int)st[8 + w];
+#pragma unroll
+    for (uint32_t jj = 0; jj < 4; ++jj) {
+        if (jj < per) {
+            hist[tid * per + jj] = base;  // start of the bucket; becomes its end during the scatter
+            base += c[jj];
         }
     }
     __syncthreads();
+    for (uint32_t i = tid; i < m; i += nt) {
+        const uint64_t key = buf[i];
+        out[atomicAdd(&hist[bucket(key)], 1)] = key;
+    }
+    __syncthreads();
+    for (uint32_t b = tid; b < NB; b += nt) {
+        const int s0 = b ? hist[b - 1] : 0, e0 = hist[b];
+        for (int x = s0 + 1; x < e0; ++x) {
+            const uint64_t key = out[x];
+            int y = x - 1;
+            while (y >= s0 && out[y] < key) { out[y + 1] = out[y]; --y; }
+            out[y + 1] = key;
+        }
+    }
+    __syncthreads();
+    return true;
+}
+
+// Sort the m winners in buf[0..m) (buf[m..kp2) is zero) descending and write the k outputs of
+// query Q.  buf has cap_s >= kp2 slots; with m more beyond kp2 the bucket placement above is used,
+// otherwise (or when it declines) a bitonic sort of buf[0..kp2), kp2 a power of two.
+__device__ void sort_and_emit(uint64_t* buf, uint32_t cap_s, int* hist, uint32_t kp2, uint32_t m, uint32_t k, uint32_t Q,
+                              uint32_t* out_index, float* out_score, uint32_t* out_count) {
+    const uint32_t tid = threadIdx.x, nt = blockDim.x;
+    const uint64_t* sorted = buf;
+    if (m >= 64 && kp2 + m <= cap_s && (nt == 256 || nt == 512) && bucket_sort(buf, buf + kp2, m, hist)) {
+        sorted = buf + kp2;
+    } else {
+        // Comparator i of a stage with stride <= 32 touches only elements [64 (i / 32), +64): the 32
+        // comparators a warp executes together stay inside one 64-element chunk, so those stages need no
+        // block barrier, only the stages that cross chunks (and the step into or out of them) do.
+        for (uint32_t size = 2; size <= kp2; size <<= 1) {
+            for (uint32_t stride = size >> 1; stride; stride >>= 1) {
+                for (uint32_t i = tid; i < kp2 / 2; i += nt) {
+                    const uint32_t lo = 2 * i - (i & (stride - 1));
+                    const uint32_t hi = lo + stride;
+                    const bool desc = (lo & size) == 0;
+                    const uint64_t x = buf[lo], y = buf[hi];
+                    if ((x < y) == desc) { buf[lo] = y; buf[hi] = x; }
+                }
+                const uint32_t next_stride = stride > 1 ? stride >> 1 : size;
+                if (stride > 32 || next_stride > 32) __syncthreads();
+                else __syncwarp();
+            }
+        }
+        __syncthreads();
+    }
     for (uint32_t r = tid; r < k; r += nt) {
         const bool v = r < m;
-        const uint64_t key = v ? buf[r] : 0ull;
+        const uint64_t key = v ? sorted[r] : 0ull;
         out_index[(size_t)Q * k + r] = v ? 0xFFFFFFFFu - (uint32_t)key : 0xFFFFFFFFu;
         out_score[(size_t)Q * k + r] = v ? key_score((uint32_t)(key >> 32)) : -INFINITY;
     }
@@ -94,6 +186,12 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
     int* n_s = hist + SEL_HIST_INTS;
     const uint32_t Q = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const uint32_t T = L.size(Q);
+#ifdef SLHA_SCORE_PROFILE
+    const long long mt0 = clock64();
+#define MPROF(i, v) do { if (tid == 0) atomicAdd(&g_merge_prof[(i)], (unsigned long long)(v)); } while (0)
+#else
+#define MPROF(i, v)
+#endif
 
     // upper bound of the number of candidates
     uint32_t total = 0;
@@ -116,20 +214,34 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
         __syncthreads();
         const uint32_t present = (uint32_t)*n_s;
         __syncthreads();
+#ifdef SLHA_SCORE_PROFILE
+        const long long mt1 = clock64();
+        MPROF(0, mt1 - mt0); MPROF(4, 1); MPROF(5, present);
+#endif
         if (present > k) {
             // bucket selection on the score word; equal scores around the k-th place
             // fall back to the exact radix selection, which also orders by index
             if (tid == 0) *pivot_s = 0ull;
             __syncthreads();
-            if (block_select_multi(buf, cap_s, n_s, 1, k, 0u, (int)k, pivot_s, hist))
+            if (block_select_multi(buf, cap_s, n_s, 1, k, 0u, (int)k, pivot_s, hist)) {
+                MPROF(6, 1);
                 block_select_topk(buf, n_s, k, pivot_s, hist);
+            }
         }
+#ifdef SLHA_SCORE_PROFILE
+        const long long mt2 = clock64();
+        MPROF(1, mt2 - mt1);
+#endif
         const uint32_t m = present < k ? present : k;
         for (uint32_t i = m + tid; i < kp2; i += nt) buf[i] = 0ull;
         __syncthreads();
-        sort_and_emit(buf, kp2, m, k, Q, out_index, out_score, out_count);
+        sort_and_emit(buf, cap_s, hist, kp2, m, k, Q, out_index, out_score, out_count);
+#ifdef SLHA_SCORE_PROFILE
+        MPROF(2, clock64() - mt2);
+#endif
         return;
     }
+    MPROF(7, 1);
 
     // Too many candidates for shared memory: one bucket pass over the lists where
     // they lie (256 equal-width score buckets between the smallest and the largest
@@ -223,7 +335,7 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
                 const uint32_t m = present < k ? present : k;
                 for (uint32_t i = m + tid; i < kp2; i += nt) buf[i] = 0ull;
                 __syncthreads();
-                sort_and_emit(buf, kp2, m, k, Q, out_index, out_score, out_count);
+                sort_and_emit(buf, cap_s, hist, kp2, m, k, Q, out_index, out_score, out_count);
                 return;
             }
         }
@@ -301,7 +413,7 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
         if (key >= pivot && key) buf[atomicAdd(&hist[259], 1)] = key;
     }
     __syncthreads();
-    sort_and_emit(buf, kp2, m, k, Q, out_index, out_score, out_count);
+    sort_and_emit(buf, cap_s, hist, kp2, m, k, Q, out_index, out_score, out_count);
 }
 
 }  // namespace
