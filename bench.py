@@ -20,6 +20,7 @@ Rank 0 prints ONE JSON line.  `--impl reference` times the CPU restatement of th
 reference's vectorised compute_score (oracle/) on the host cores instead.
 """
 import argparse
+import ctypes
 import json
 import os
 import sys
@@ -419,6 +420,26 @@ def gpu_arm(args, w):
             "isa": ["scalar", "avx2", "avx512"][ora.simd_level()],
             "sample": "%d tiles (%d KV heads x %d tokens) x %d queries, %d passes in %.1f s" % (n_s, heads, n_s // heads, w["group"], reps, dt),
         }
+        # For context only: the reference's own CUDA scoring kernel (one thread per tile, one launch
+        # per query, 256-thread blocks as in its tests) on the same resident tiles, when the built
+        # oracle/_ref library travelled with the repository.  It writes full score vectors and has
+        # no top-k; the figure is tiles per second with every tile scored against its 4 queries.
+        refk = ora.ref_cuda_library()
+        if refk is not None:
+            per = n_s // heads
+            sc = torch.empty(w["group"] * per, dtype=torch.float32, device=dev)
+            ms_out = ctypes.c_float(0.0)
+            total_ms = 0.0
+            for h in range(heads):
+                rc = refk.slha_ref_cuda_time(tiles.data_ptr() + h * per * 128, per, q_coarse[h * w["group"]:].data_ptr(),
+                                             q_sign[h * w["group"]:].data_ptr(), w["group"], sc.data_ptr(), 3, stream.cuda_stream,
+                                             ctypes.byref(ms_out))
+                assert rc == 0, rc
+                total_ms += ms_out.value
+            line["reference_cuda_kernel"] = {
+                "value": n_s / (total_ms * 1e-3), "unit": "tiles/s", "ms": total_ms,
+                "sample": "slhav2-vram/kernels/slha_score.cu unmodified: %d KV heads x %d tiles x %d queries, full score vectors, no top-k" % (heads, per, w["group"]),
+            }
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -421,3 +421,46 @@ def score_sink(tiles, q_coarse, q_sign, which=-1, threads=1):
 
 def simd_level():
     return lib.ora_simd_level()
+
+
+# ---- the reference's own CUDA scoring kernel (optional second checker) --------
+# oracle/_ref/libslha_ref_cuda.so is built by `make -C oracle ref` from
+# slhav2-vram/kernels/slha_score.cu where the reference tree is mounted; it is a
+# built artefact only (never in history) and may be absent.
+_REF_CUDA_SO = os.path.join(_HERE, "_ref", "libslha_ref_cuda.so")
+_ref_cuda = None
+
+
+def build_ref_cuda(reference_root="/root/reference"):
+    """Compiles the reference CUDA kernel if its source tree is present; returns True when the library exists."""
+    if os.path.exists(os.path.join(reference_root, "slhav2-vram", "kernels", "slha_score.cu")):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "REF=" + reference_root], stdout=subprocess.DEVNULL)
+    return os.path.exists(_REF_CUDA_SO)
+
+
+def ref_cuda_library():
+    """ctypes handle of the built reference CUDA kernel driver, or None when it was never built."""
+    global _ref_cuda
+    if _ref_cuda is None and os.path.exists(_REF_CUDA_SO):
+        _ref_cuda = C.CDLL(_REF_CUDA_SO)
+        _ref_cuda.slha_ref_cuda_score.restype = C.c_int
+        _ref_cuda.slha_ref_cuda_score.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        _ref_cuda.slha_ref_cuda_time.restype = C.c_int
+        _ref_cuda.slha_ref_cuda_time.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
+                                                 C.c_void_p, C.c_void_p]
+    return _ref_cuda
+
+
+def ref_cuda_scores(tiles, q_coarse, q_sign):
+    """scores[nq][n] from the reference's CUDA kernel (needs a GPU and the built library)."""
+    r = ref_cuda_library()
+    if r is None:
+        raise RuntimeError("oracle/_ref/libslha_ref_cuda.so has not been built")
+    tiles = np.ascontiguousarray(tiles)
+    qc = np.ascontiguousarray(q_coarse, np.float32).reshape(-1, 128)
+    qs = np.ascontiguousarray(q_sign, np.uint64).reshape(-1, 4)
+    out = np.empty((len(qc), len(tiles)), np.float32)
+    rc = r.slha_ref_cuda_score(_p(tiles), len(tiles), _p(qc), _p(qs), len(qc), _p(out))
+    if rc:
+        raise RuntimeError("reference CUDA kernel failed: cudaError %d" % (rc - 1000))
+    return out

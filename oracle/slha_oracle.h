@@ -7,9 +7,12 @@
  * smoke check and the benchmark's CPU-baseline leg may load it; the shipped
  * library never links or calls anything in this directory.
  *
- * Pinning: the reference is Rust and no Rust toolchain exists on the build
- * machine, so the oracle is pinned by the reference's own known-answer tests
- * and fixtures (see tests/test_oracle_kats.py), not by running the reference.
+ * Pinning: the reference's CPU code is Rust and no Rust toolchain exists on the
+ * build machine, so the oracle is pinned by the reference's own known-answer
+ * tests and fixtures (tests/test_oracle_kats.py, tests/test_oracle_ccos.py).
+ * Its scoring functions are in addition checked against the reference's real
+ * CUDA kernel (slhav2-vram/kernels/slha_score.cu, compiled from the reference
+ * tree into oracle/_ref/ by `make ref`) in tests/test_gpu_reference_kernel.py.
  *
  * Every function names the reference file:line it follows.  Build with
  * -ffp-contract=off: the reference never fuses multiply-add and all sums are
