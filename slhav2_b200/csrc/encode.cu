@@ -217,13 +217,14 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int KB = a.kb;
     const uint32_t d = a.d, dp = a.d_pad;
-    // shared: tiles [KB][128 B] | h [KB][128] | keyT [d][KB] | bufT [d_pad][KB]
+    // shared: tiles [KB][128 B] | h [KB][128] | keyT [d][KB] | bufT [d_pad][KB] | wsT [128][KB]
     // (keys and the sign-LSH input are stored transposed so that one thread
     // reads the KB values of a contraction index with 16-byte loads)
     unsigned char* tl = smem;
     float* hs = reinterpret_cast<float*>(tl + (size_t)KB * TILE_BYTES);
     float* keyT = hs + (size_t)KB * D_C;
     float* buf = keyT + (((size_t)d * KB + 3) & ~size_t(3));
+    float* wsT = buf + (size_t)dp * KB;  // h_k * s_k of every key, transposed like keyT
 
     for (uint64_t base = (uint64_t)blockIdx.x * KB; base < a.n; base += (uint64_t)gridDim.x * KB) {
         const int nk = (int)min((uint64_t)KB, a.n - base);
@@ -291,25 +292,59 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
             for (uint32_t e = tid; e < dp * (uint32_t)KB; e += ENC_THREADS)
                 buf[e] = (e / KB) < d ? keyT[e] : 0.0f;
         } else {
+            // ---- w[k][j] = h_j[k] * s_k, the factor the reconstruction multiplies P[k][:] by ----
+            for (int e = tid; e < D_C * KB; e += ENC_THREADS) {
+                const int k = e / KB, j = e % KB;
+                wsT[e] = __fmul_rn(hs[(size_t)j * D_C + k], a.scale[k]);
+            }
             // ---- quantise: one warp per key ---------------------------------
             for (int j = warp; j < KB; j += ENC_THREADS / 32)
                 quantize_warp(hs + (size_t)j * D_C, a.codec, tl + (size_t)j * TILE_BYTES, lane);
-            // ---- residual e = key - sum_k (h_k*s_k) * P[k][:]  (k outer) ------
-            for (uint32_t e = tid; e < dp * (uint32_t)KB; e += ENC_THREADS) {
-                // thread owns column i of key j; consecutive threads -> consecutive i
-                const int j = e / dp;
-                const uint32_t i = e % dp;
-                float r = 0.0f;
-                if (i < d) {
-                    float acc = 0.0f;
-                    const float* hj = hs + (size_t)j * D_C;
+            __syncthreads();
+            // ---- residual e = key - sum_k (h_k*s_k) * P[k][:]  (k outer, sequential) ------
+            if (KB == 16) {
+                // thread owns column i for eight keys: one P element and two 16-byte loads of w per
+                // sixteen multiply-adds (a thread per single (key, column) spends a load per multiply-add)
+                for (uint32_t wi = tid; wi < 2 * d; wi += ENC_THREADS) {
+                    const uint32_t i = wi % d, half = wi / d;
+                    float acc[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+                    const float* wr = wsT + half * 8;
+#pragma unroll 4
                     for (int k = 0; k < D_C; ++k) {
-                        const float w = __fmul_rn(hj[k], a.scale[k]);
-                        acc = __fadd_rn(acc, __fmul_rn(w, a.p[(size_t)k * d + i]));
+                        const float pv = a.p[(size_t)k * d + i];
+                        const float4 w0 = reinterpret_cast<const float4*>(wr + (size_t)k * 16)[0];
+                        const float4 w1 = reinterpret_cast<const float4*>(wr + (size_t)k * 16)[1];
+                        acc[0] = __fadd_rn(acc[0], __fmul_rn(w0.x, pv));
+                        acc[1] = __fadd_rn(acc[1], __fmul_rn(w0.y, pv));
+                        acc[2] = __fadd_rn(acc[2], __fmul_rn(w0.z, pv));
+                        acc[3] = __fadd_rn(acc[3], __fmul_rn(w0.w, pv));
+                        acc[4] = __fadd_rn(acc[4], __fmul_rn(w1.x, pv));
+                        acc[5] = __fadd_rn(acc[5], __fmul_rn(w1.y, pv));
+                        acc[6] = __fadd_rn(acc[6], __fmul_rn(w1.z, pv));
+                        acc[7] = __fadd_rn(acc[7], __fmul_rn(w1.w, pv));
                     }
-                    r = __fsub_rn(keyT[(size_t)i * KB + j], acc);
+                    float* br = buf + (size_t)i * 16 + half * 8;
+                    const float* kr = keyT + (size_t)i * 16 + half * 8;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) br[j] = __fsub_rn(kr[j], acc[j]);
                 }
-                buf[(size_t)i * KB + j] = r;
+                for (uint32_t e = d * 16 + tid; e < dp * 16; e += ENC_THREADS) buf[e] = 0.0f;  // padding rows
+            } else {
+                for (uint32_t e = tid; e < dp * (uint32_t)KB; e += ENC_THREADS) {
+                    // thread owns column i of key j; consecutive threads -> consecutive i
+                    const int j = e / dp;
+                    const uint32_t i = e % dp;
+                    float r = 0.0f;
+                    if (i < d) {
+                        float acc = 0.0f;
+                        for (int k = 0; k < D_C; ++k)
+                            acc = __fadd_rn(acc, __fmul_rn(wsT[(size_t)k * KB + j], a.p[(size_t)k * d + i]));
+                        r = __fsub_rn(keyT[(size_t)i * KB + j], acc);
+                    }
+                    buf[(size_t)i * KB + j] = r;
+                }
             }
         }
         __syncthreads();
@@ -480,7 +515,7 @@ __global__ void decode_kernel(const unsigned char* tile, const float* p, const f
 }
 
 size_t encode_smem(uint32_t d, uint32_t dp, int kb) {
-    return ((((size_t)d * kb + 3) & ~size_t(3)) + (size_t)kb * D_C + (size_t)kb * dp) * 4 + (size_t)kb * TILE_BYTES;
+    return ((((size_t)d * kb + 3) & ~size_t(3)) + (size_t)kb * D_C + (size_t)kb * dp + (size_t)kb * D_C) * 4 + (size_t)kb * TILE_BYTES;
 }
 
 Status fill_args(const Model* m, EncodeArgs& a, int* kb_out) {
