@@ -583,7 +583,7 @@ Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Se
     while (kp2 < k) kp2 <<= 1;
     CompLists L{sc->cand_keys, sc->cand_cnt, sc->q_list_begin, sc->q_list_count, k};
     const uint32_t cap_s = merge_cap((uint64_t)max_parts * k, kp2, k);
-    topk_merge_kernel<CompLists><<<(uint32_t)nq, cap_s > 4096 ? 512 : 256, merge_smem(cap_s), c->stream>>>(
+    topk_merge_kernel<CompLists><<<(uint32_t)nq, merge_threads(cap_s), merge_smem(cap_s, kp2), c->stream>>>(
         L, k, kp2, cap_s, d_out_index, d_out_score, d_out_count);
     count_launch();
     SLHA_CUDA(cudaGetLastError());

@@ -63,7 +63,10 @@ uint32_t merge_cap(uint64_t total, uint32_t kp2, uint32_t k) {
     const uint64_t enough = ((uint64_t)kp2 + k + 256 + 255) / 256 * 256;
     return (uint32_t)std::min<uint64_t>(enough, 24576);
 }
-size_t merge_smem(uint32_t cap_s) { return (size_t)cap_s * 8 + 8 + (SEL_HIST_INTS + 4) * 4; }
+int merge_threads(uint32_t cap_s) { return cap_s > 4096 ? 512 : 256; }
+size_t merge_smem(uint32_t cap_s, uint32_t kp2) {
+    return (size_t)cap_s * 8 + 8 + (size_t)(std::max(SEL_HIST_INTS, merge_buckets(kp2, (uint32_t)merge_threads(cap_s)) + 48) + 4) * 4;
+}
 
 // Optional per-call CUDA-event timing of the two kernels of score_topk
 // (slha_b200_timing_begin / _end).  Events are recorded on the launching stream.
@@ -424,13 +427,13 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     if (timed) SLHA_CUDA(cudaEventRecord(tev[1], c->stream));
     CompLists L{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, p->list_cap};
     const uint32_t cap_s = merge_cap((uint64_t)p->max_parts * p->list_cap, p->kp2, k);
-    const size_t smem = merge_smem(cap_s);
+    const size_t smem = merge_smem(cap_s, p->kp2);
     static thread_local bool configured = false;
     if (!configured) {
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<CompLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
         configured = true;
     }
-    topk_merge_kernel<CompLists><<<(uint32_t)nq, cap_s > 4096 ? 512 : 256, smem, c->stream>>>(L, k, p->kp2, cap_s, d_out_index, d_out_score, d_out_count);
+    topk_merge_kernel<CompLists><<<(uint32_t)nq, merge_threads(cap_s), smem, c->stream>>>(L, k, p->kp2, cap_s, d_out_index, d_out_score, d_out_count);
     count_launch();
     SLHA_CUDA(cudaGetLastError());
     if (timed) {
@@ -480,7 +483,7 @@ Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* 
         configured = true;
     }
     const uint32_t cap_s = merge_cap((uint64_t)n_lists * k_in, kp2, k_out);
-    topk_merge_kernel<PairLists><<<n_queries, cap_s > 4096 ? 512 : 256, merge_smem(cap_s), c->stream>>>(L, k_out, kp2, cap_s, out_index, out_score, nullptr);
+    topk_merge_kernel<PairLists><<<n_queries, merge_threads(cap_s), merge_smem(cap_s, kp2), c->stream>>>(L, k_out, kp2, cap_s, out_index, out_score, nullptr);
     count_launch();
     SLHA_CUDA(cudaGetLastError());
     return Status();

@@ -53,19 +53,18 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     }
 };
 
-// Orders buf[0..m) descending into out[0..m) by bucket placement: 1024 equal-width score buckets
+// Orders buf[0..m) descending into out[0..m) by bucket placement: NB (1024 or 2048) equal-width score buckets
 // between the smallest and the largest score (highest first), a counting pass, an exclusive scan, a
 // scatter, and an insertion sort inside every bucket by one thread.  The winners of a top-k are a
 // thin tail, a handful of keys per bucket, so this replaces the 55 dependent stages of a bitonic
 // sort of 1024 keys by six barriers.  Returns false (nothing written that matters) when a bucket
 // would hold more than 16 keys or the scores cannot be bucketed; the caller then sorts bitonically.
-// hist: SEL_HIST_INTS ints.  All threads of the block.
-__device__ bool bucket_sort(const uint64_t* buf, uint64_t* out, uint32_t m, int* hist) {
+// hist: NB + 48 ints, NB a multiple of the thread count and at most four times it.  All threads of the block.
+__device__ bool bucket_sort(const uint64_t* buf, uint64_t* out, uint32_t m, int* hist, const int NB) {
     const uint32_t tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
-    constexpr int NB = 1024;
     uint32_t* st = reinterpret_cast<uint32_t*>(hist + NB);  // 0 min, 1 max, 2 largest bucket, 8.. warp totals
     if (tid == 0) { st[0] = 0xFFFFFFFFu; st[1] = 0u; st[2] = 0u; }
-    for (uint32_t b = tid; b < NB; b += nt) hist[b] = 0;
+    for (int b = (int)tid; b < NB; b += (int)nt) hist[b] = 0;
     __syncthreads();
     uint32_t mn = 0xFFFFFFFFu, mx = 0u;
     for (uint32_t i = tid; i < m; i += nt) {
@@ -87,7 +86,7 @@ __device__ bool bucket_sort(const uint64_t* buf, uint64_t* out, uint32_t m, int*
     for (uint32_t i = tid; i < m; i += nt) atomicAdd(&hist[bucket(buf[i])], 1);
     __syncthreads();
     // exclusive scan of the bucket counts: thread t owns NB / nt consecutive buckets
-    const uint32_t per = NB / nt;  // 2 or 4 (256 or 512 threads)
+    const uint32_t per = (uint32_t)NB / nt;  // 2 or 4
     int c[4], sum = 0, big = 0;
 #pragma unroll
     for (uint32_t jj = 0; jj < 4; ++jj) {
@@ -121,7 +120,7 @@ __device__ bool bucket_sort(const uint64_t* buf, uint64_t* out, uint32_t m, int*
         out[atomicAdd(&hist[bucket(key)], 1)] = key;
     }
     __syncthreads();
-    for (uint32_t b = tid; b < NB; b += nt) {
+    for (int b = (int)tid; b < NB; b += (int)nt) {
         const int s0 = b ? hist[b - 1] : 0, e0 = hist[b];
         for (int x = s0 + 1; x < e0; ++x) {
             const uint64_t key = out[x];
@@ -134,6 +133,12 @@ __device__ bool bucket_sort(const uint64_t* buf, uint64_t* out, uint32_t m, int*
     return true;
 }
 
+// Buckets of bucket_sort for a merge of kp2 (k rounded up to a power of two) results by nt threads.
+__host__ __device__ inline int merge_buckets(uint32_t kp2, uint32_t nt) {
+    const uint32_t nb = kp2 < 1024u ? 1024u : kp2;
+    return (int)(nb > 4u * nt ? 4u * nt : nb);
+}
+
 // Sort the m winners in buf[0..m) (buf[m..kp2) is zero) descending and write the k outputs of
 // query Q.  buf has cap_s >= kp2 slots; with m more beyond kp2 the bucket placement above is used,
 // otherwise (or when it declines) a bitonic sort of buf[0..kp2), kp2 a power of two.
@@ -141,7 +146,7 @@ __device__ void sort_and_emit(uint64_t* buf, uint32_t cap_s, int* hist, uint32_t
                               uint32_t* out_index, float* out_score, uint32_t* out_count) {
     const uint32_t tid = threadIdx.x, nt = blockDim.x;
     const uint64_t* sorted = buf;
-    if (m >= 64 && kp2 + m <= cap_s && (nt == 256 || nt == 512) && bucket_sort(buf, buf + kp2, m, hist)) {
+    if (m >= 64 && kp2 + m <= cap_s && (nt == 256 || nt == 512) && bucket_sort(buf, buf + kp2, m, hist, merge_buckets(kp2, nt))) {
         sorted = buf + kp2;
     } else {
         // Comparator i of a stage with stride <= 32 touches only elements [64 (i / 32), +64): the 32
@@ -182,8 +187,8 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
     extern __shared__ __align__(16) unsigned char smem[];
     uint64_t* buf = reinterpret_cast<uint64_t*>(smem);  // [cap_s]
     uint64_t* pivot_s = buf + cap_s;                    // [1]
-    int* hist = reinterpret_cast<int*>(pivot_s + 1);    // SEL_HIST_INTS
-    int* n_s = hist + SEL_HIST_INTS;
+    int* hist = reinterpret_cast<int*>(pivot_s + 1);    // max(SEL_HIST_INTS, buckets of bucket_sort + 48)
+    int* n_s = hist + max(SEL_HIST_INTS, merge_buckets(kp2, blockDim.x) + 48);
     const uint32_t Q = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const uint32_t T = L.size(Q);
 #ifdef SLHA_SCORE_PROFILE
