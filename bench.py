@@ -4,12 +4,12 @@
     python bench.py --gpus N --steps K --warmup W [--workload c2|c5] [--impl reference]
 
 A "step" is one pass of fused eq. 2.3 scoring + top-k over every tile a rank
-holds.  Default workload (N=1): BASELINE config 2, Llama-3-8B-shaped decode KV --
+holds.  Default workload (N=1): decode configuration 2, Llama-3-8B-shaped decode KV --
 32 layers x 8 KV heads x 32768 tokens = 8.4M NF4 tiles (1.07 GB), 32 query heads
 per layer in GQA groups of 4, top-1024 per query head.  For N>1 every rank holds
 such a shard of a N x 32768-token context (weak scaling by token range), takes
 its own top-1024 and the shards are merged with one NCCL all-gather + a merge
-kernel.  `--workload c5` is BASELINE config 5 (1M tokens x 8 KV heads, INT4
+kernel.  `--workload c5` is the long-context configuration 5 (1M tokens x 8 KV heads, INT4
 MX-32, top-2048, token range split over the ranks: strong scaling).
 
 Synthetic data stands in for real activations: seeded N(0,1) keys scaled by

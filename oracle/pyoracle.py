@@ -431,8 +431,12 @@ _REF_CUDA_SO = os.path.join(_HERE, "_ref", "libslha_ref_cuda.so")
 _ref_cuda = None
 
 
-def build_ref_cuda(reference_root="/root/reference"):
-    """Compiles the reference CUDA kernel if its source tree is present; returns True when the library exists."""
+def build_ref_cuda(reference_root=None):
+    """Compiles the reference CUDA kernel if its source tree is present (reference_root, else the environment
+    variable SLHA_REFERENCE_ROOT, else a directory `reference` beside this repository); returns True when the
+    library exists."""
+    if reference_root is None:
+        reference_root = os.environ.get("SLHA_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
     if os.path.exists(os.path.join(reference_root, "slhav2-vram", "kernels", "slha_score.cu")):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "REF=" + reference_root], stdout=subprocess.DEVNULL)
     return os.path.exists(_REF_CUDA_SO)

@@ -1,5 +1,5 @@
 // Tensor-core variant of the fused score + top-k kernel for the nibble codecs
-// (uniform / MX INT4 and NF4), the layouts of BASELINE configs 1, 2 and 5.
+// (uniform / MX INT4 and NF4), the layouts of decode KV caches.
 // Included by score.cu.
 //
 // With a GQA group of four queries the CUDA-core kernel is bound by instruction

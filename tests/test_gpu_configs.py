@@ -1,4 +1,4 @@
-"""The BASELINE configurations as parity cases (reduced lengths where the oracle
+"""The five benchmark configurations as parity cases (reduced lengths where the oracle
 would take minutes; full length through size-independent properties)."""
 import numpy as np
 import pytest

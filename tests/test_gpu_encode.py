@@ -82,7 +82,7 @@ def test_whitened_model_and_decode():
 
 
 def test_encode_then_score_end_to_end_config1_shape():
-    # BASELINE config 1 at reduced length: INT4 single, d=128, outlier channels, top-64
+    # configuration 1 (single-head INT4 cache) at reduced length: INT4 single, d=128, outlier channels, top-64
     om, gm = _models(128, False, seed=0)
     n = 2048
     keys = H.gaussian_keys(0, n, 128, outlier_channels=(7, 93))

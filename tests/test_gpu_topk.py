@@ -180,11 +180,13 @@ def test_generic_kernel_only_mode_matches():
         "i, s, c = S.score_topk(d, S.make_segments([(0, 20000, 0, 4, 0)]), qc, qs, 4, 256)\n"
         "np.save(sys.argv[1] if False else __import__('sys').argv[1], np.concatenate([i.astype(np.float64), s.astype(np.float64)]))\n"
     )
+    import tempfile
+
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     outs = []
+    tmp = tempfile.mkdtemp()
     for impl in ("0", "1"):
-        path = os.path.join(root, "gpurun_out", "impl%s.npy" % impl)
-        os.makedirs(os.path.dirname(path), exist_ok=True)
+        path = os.path.join(tmp, "impl%s.npy" % impl)
         env = dict(os.environ, SLHA_B200_SCORE_IMPL=impl, PYTHONPATH=root)
         subprocess.check_call([sys.executable, "-c", code, path], env=env, cwd=root)
         outs.append(np.load(path))
