@@ -211,11 +211,34 @@ __device__ void quantize_warp(const float* h, int codec, unsigned char* tile, in
     }
 }
 
-template <bool QUERY>
+// acc[j] += x * v[j] for NK keys whose values lie consecutively (16-byte aligned when NK % 4 == 0),
+// each as a separate multiply and add (the reference never fuses them).
+template <int NK>
+__device__ __forceinline__ void axpy_keys(float (&acc)[NK], float x, const float* v) {
+    if (NK % 4 == 0) {
+#pragma unroll
+        for (int j4 = 0; j4 < NK / 4; ++j4) {
+            const float4 b4 = reinterpret_cast<const float4*>(v)[j4];
+            acc[4 * j4 + 0] = __fadd_rn(acc[4 * j4 + 0], __fmul_rn(x, b4.x));
+            acc[4 * j4 + 1] = __fadd_rn(acc[4 * j4 + 1], __fmul_rn(x, b4.y));
+            acc[4 * j4 + 2] = __fadd_rn(acc[4 * j4 + 2], __fmul_rn(x, b4.z));
+            acc[4 * j4 + 3] = __fadd_rn(acc[4 * j4 + 3], __fmul_rn(x, b4.w));
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NK; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(x, v[j]));
+    }
+}
+
+// KB keys per CTA pass (compile time: 32 unless the model dimension leaves no room).  Every
+// contraction is walked sequentially by the thread that owns the output element, for all the keys
+// the thread holds at once: one matrix element and KB/8 (latent, residual: half the keys per thread)
+// or KB/4 (sign bits) vector loads feed KB or 2 KB multiply-adds.
+template <bool QUERY, int KB>
 __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int KB = a.kb;
+    constexpr int PER = KB >= 2 ? KB / 2 : 1;  // keys per thread where two threads share an output row
     const uint32_t d = a.d, dp = a.d_pad;
     // shared: tiles [KB][128 B] | h [KB][128] | keyT [d][KB] | bufT [d_pad][KB] | wsT [128][KB]
     // (keys and the sign-LSH input are stored transposed so that one thread
@@ -248,39 +271,20 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
         // ---- latent / q_coarse: row k = tid & 127, keys of half (tid >> 7) ---
         {
             const int k = tid & 127, half = tid >> 7;
-            const int per = max(KB / 2, 1);
-            const int j0 = (KB >= 2) ? half * per : 0;
+            const int j0 = (KB >= 2) ? half * PER : 0;
             if (KB >= 2 || half == 0) {
-                float acc[8];
+                float acc[PER];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-                for (uint32_t i = 0; i < d; ++i) {
-                    const float pv = a.pt[(size_t)i * D_C + k];
-                    const float* kr = keyT + (size_t)i * KB + j0;
-                    if (KB == 16) {
-                        const float4 k0 = reinterpret_cast<const float4*>(kr)[0];
-                        const float4 k1 = reinterpret_cast<const float4*>(kr)[1];
-                        acc[0] = __fadd_rn(acc[0], __fmul_rn(pv, k0.x));
-                        acc[1] = __fadd_rn(acc[1], __fmul_rn(pv, k0.y));
-                        acc[2] = __fadd_rn(acc[2], __fmul_rn(pv, k0.z));
-                        acc[3] = __fadd_rn(acc[3], __fmul_rn(pv, k0.w));
-                        acc[4] = __fadd_rn(acc[4], __fmul_rn(pv, k1.x));
-                        acc[5] = __fadd_rn(acc[5], __fmul_rn(pv, k1.y));
-                        acc[6] = __fadd_rn(acc[6], __fmul_rn(pv, k1.z));
-                        acc[7] = __fadd_rn(acc[7], __fmul_rn(pv, k1.w));
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (j < per) acc[j] = __fadd_rn(acc[j], __fmul_rn(pv, kr[j]));
-                    }
-                }
+                for (int j = 0; j < PER; ++j) acc[j] = 0.0f;
+#pragma unroll 8
+                for (uint32_t i = 0; i < d; ++i)
+                    axpy_keys<PER>(acc, a.pt[(size_t)i * D_C + k], keyT + (size_t)i * KB + j0);
                 const float sk = a.scale[k];
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (j < per) {
-                        const float hv = QUERY ? __fmul_rn(acc[j], sk) : __fdiv_rn(acc[j], sk);
-                        hs[(size_t)(j0 + j) * D_C + k] = hv;
-                    }
+                for (int j = 0; j < PER; ++j) {
+                    const float hv = QUERY ? __fmul_rn(acc[j], sk) : __fdiv_rn(acc[j], sk);
+                    hs[(size_t)(j0 + j) * D_C + k] = hv;
+                }
             }
         }
         __syncthreads();
@@ -301,51 +305,23 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
             for (int j = warp; j < KB; j += ENC_THREADS / 32)
                 quantize_warp(hs + (size_t)j * D_C, a.codec, tl + (size_t)j * TILE_BYTES, lane);
             __syncthreads();
-            // ---- residual e = key - sum_k (h_k*s_k) * P[k][:]  (k outer, sequential) ------
-            if (KB == 16) {
-                // thread owns column i for eight keys: one P element and two 16-byte loads of w per
-                // sixteen multiply-adds (a thread per single (key, column) spends a load per multiply-add)
-                for (uint32_t wi = tid; wi < 2 * d; wi += ENC_THREADS) {
-                    const uint32_t i = wi % d, half = wi / d;
-                    float acc[8];
+            // ---- residual e = key - sum_k (h_k*s_k) * P[k][:]  (k outer, sequential): a thread owns
+            //      column i for half of the keys ---------------------------------------------------
+            constexpr int HALVES = KB >= 2 ? 2 : 1;
+            for (uint32_t wi = tid; wi < HALVES * d; wi += ENC_THREADS) {
+                const uint32_t i = wi % d, half = wi / d;
+                float acc[PER];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-                    const float* wr = wsT + half * 8;
-#pragma unroll 4
-                    for (int k = 0; k < D_C; ++k) {
-                        const float pv = a.p[(size_t)k * d + i];
-                        const float4 w0 = reinterpret_cast<const float4*>(wr + (size_t)k * 16)[0];
-                        const float4 w1 = reinterpret_cast<const float4*>(wr + (size_t)k * 16)[1];
-                        acc[0] = __fadd_rn(acc[0], __fmul_rn(w0.x, pv));
-                        acc[1] = __fadd_rn(acc[1], __fmul_rn(w0.y, pv));
-                        acc[2] = __fadd_rn(acc[2], __fmul_rn(w0.z, pv));
-                        acc[3] = __fadd_rn(acc[3], __fmul_rn(w0.w, pv));
-                        acc[4] = __fadd_rn(acc[4], __fmul_rn(w1.x, pv));
-                        acc[5] = __fadd_rn(acc[5], __fmul_rn(w1.y, pv));
-                        acc[6] = __fadd_rn(acc[6], __fmul_rn(w1.z, pv));
-                        acc[7] = __fadd_rn(acc[7], __fmul_rn(w1.w, pv));
-                    }
-                    float* br = buf + (size_t)i * 16 + half * 8;
-                    const float* kr = keyT + (size_t)i * 16 + half * 8;
+                for (int j = 0; j < PER; ++j) acc[j] = 0.0f;
+                const float* wr = wsT + half * PER;
+#pragma unroll 8
+                for (int k = 0; k < D_C; ++k) axpy_keys<PER>(acc, a.p[(size_t)k * d + i], wr + (size_t)k * KB);
+                float* br = buf + (size_t)i * KB + half * PER;
+                const float* kr = keyT + (size_t)i * KB + half * PER;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) br[j] = __fsub_rn(kr[j], acc[j]);
-                }
-                for (uint32_t e = d * 16 + tid; e < dp * 16; e += ENC_THREADS) buf[e] = 0.0f;  // padding rows
-            } else {
-                for (uint32_t e = tid; e < dp * (uint32_t)KB; e += ENC_THREADS) {
-                    // thread owns column i of key j; consecutive threads -> consecutive i
-                    const int j = e / dp;
-                    const uint32_t i = e % dp;
-                    float r = 0.0f;
-                    if (i < d) {
-                        float acc = 0.0f;
-                        for (int k = 0; k < D_C; ++k)
-                            acc = __fadd_rn(acc, __fmul_rn(wsT[(size_t)k * KB + j], a.p[(size_t)k * d + i]));
-                        r = __fsub_rn(keyT[(size_t)i * KB + j], acc);
-                    }
-                    buf[(size_t)i * KB + j] = r;
-                }
+                for (int j = 0; j < PER; ++j) br[j] = __fsub_rn(kr[j], acc[j]);
             }
+            for (uint32_t e = d * KB + tid; e < dp * KB; e += ENC_THREADS) buf[e] = 0.0f;  // padding rows
         }
         __syncthreads();
 
@@ -398,37 +374,19 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
         // ---- sign-LSH: thread s owns hyperplane s for all KB keys ------------
         {
             const int s = tid;  // ENC_THREADS == D_S
-            float acc[16];
+            float acc[KB];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
-            for (uint32_t i = 0; i < dp; ++i) {
-                const float zv = a.zt[(size_t)i * D_S + s];
-                const float* br = buf + (size_t)i * KB;
-                if (KB == 16) {
+            for (int j = 0; j < KB; ++j) acc[j] = 0.0f;
+#pragma unroll 8
+            for (uint32_t i = 0; i < dp; ++i) axpy_keys<KB>(acc, a.zt[(size_t)i * D_S + s], buf + (size_t)i * KB);
 #pragma unroll
-                    for (int j4 = 0; j4 < 4; ++j4) {
-                        const float4 b4 = reinterpret_cast<const float4*>(br)[j4];
-                        acc[4 * j4 + 0] = __fadd_rn(acc[4 * j4 + 0], __fmul_rn(zv, b4.x));
-                        acc[4 * j4 + 1] = __fadd_rn(acc[4 * j4 + 1], __fmul_rn(zv, b4.y));
-                        acc[4 * j4 + 2] = __fadd_rn(acc[4 * j4 + 2], __fmul_rn(zv, b4.z));
-                        acc[4 * j4 + 3] = __fadd_rn(acc[4 * j4 + 3], __fmul_rn(zv, b4.w));
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (j < KB) acc[j] = __fadd_rn(acc[j], __fmul_rn(zv, br[j]));
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                if (j < KB) {
-                    const unsigned b = __ballot_sync(0xFFFFFFFFu, acc[j] < 0.0f);
-                    if (lane == 0 && j < nk) {
-                        if (QUERY)
-                            reinterpret_cast<uint32_t*>(a.q_sign)[(base + j) * 8 + warp] = b;
-                        else
-                            reinterpret_cast<uint32_t*>(tl + (size_t)j * TILE_BYTES + 64)[warp] = b;
-                    }
+            for (int j = 0; j < KB; ++j) {
+                const unsigned b = __ballot_sync(0xFFFFFFFFu, acc[j] < 0.0f);
+                if (lane == 0 && j < nk) {
+                    if (QUERY)
+                        reinterpret_cast<uint32_t*>(a.q_sign)[(base + j) * 8 + warp] = b;
+                    else
+                        reinterpret_cast<uint32_t*>(tl + (size_t)j * TILE_BYTES + 64)[warp] = b;
                 }
             }
         }
@@ -528,8 +486,9 @@ Status fill_args(const Model* m, EncodeArgs& a, int* kb_out) {
     a.diag = m->d_diag;
     a.fwht_inv = 1.0f / sqrtf((float)m->d_pad);
     a.lambda_c = sqrtf(3.14159265358979323846f / (2.0f * (float)D_S));
-    int kb = 16;
-    while (kb > 1 && encode_smem(a.d, a.d_pad, kb) > 200 * 1024) kb >>= 1;
+    // 32 keys per CTA pass when three CTAs still share an SM, else fewer
+    int kb = 32;
+    while (kb > 1 && encode_smem(a.d, a.d_pad, kb) > (kb == 32 ? 72 : 200) * 1024) kb >>= 1;
     if (encode_smem(a.d, a.d_pad, kb) > 200 * 1024)
         return Status(SLHA_ERR_DIMENSION, "model dimension too large for the encode kernel");
     *kb_out = kb;
@@ -537,20 +496,32 @@ Status fill_args(const Model* m, EncodeArgs& a, int* kb_out) {
     return Status();
 }
 
-template <bool QUERY>
-Status run_encode(Ctx* c, EncodeArgs& a) {
-    const size_t smem = encode_smem(a.d, a.d_pad, a.kb);
+template <bool QUERY, int KB>
+Status run_encode_kb(Ctx* c, EncodeArgs& a) {
+    const size_t smem = encode_smem(a.d, a.d_pad, KB);
     static thread_local bool configured = false;
     if (!configured) {
-        SLHA_CUDA(cudaFuncSetAttribute(encode_kernel<QUERY>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        SLHA_CUDA(cudaFuncSetAttribute(encode_kernel<QUERY, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         configured = true;
     }
-    const uint64_t groups = (a.n + a.kb - 1) / a.kb;
+    const uint64_t groups = (a.n + KB - 1) / KB;
     const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, 148ull * 8);
-    encode_kernel<QUERY><<<grid, ENC_THREADS, smem, c->stream>>>(a);
+    encode_kernel<QUERY, KB><<<grid, ENC_THREADS, smem, c->stream>>>(a);
     count_launch();
     SLHA_CUDA(cudaGetLastError());
     return Status();
+}
+
+template <bool QUERY>
+Status run_encode(Ctx* c, EncodeArgs& a) {
+    switch (a.kb) {
+        case 32: return run_encode_kb<QUERY, 32>(c, a);
+        case 16: return run_encode_kb<QUERY, 16>(c, a);
+        case 8: return run_encode_kb<QUERY, 8>(c, a);
+        case 4: return run_encode_kb<QUERY, 4>(c, a);
+        case 2: return run_encode_kb<QUERY, 2>(c, a);
+        default: return run_encode_kb<QUERY, 1>(c, a);
+    }
 }
 
 }  // namespace
