@@ -250,8 +250,9 @@ def build_shard(S, torch, w, rank, world, dev):
     chunk_tokens = min(T, 131072)
     for l in range(L):
         model = S.Model.from_projection(seeded_projection(100 + l), HEAD_DIM, 100 + l)
-        gen.manual_seed(1234 + l + 7919 * rank)  # every rank holds different tokens
+        gen.manual_seed(1234 + l)  # the per-channel scale belongs to the layer: the same on every rank
         chan = torch.exp(0.5 * torch.randn(HEAD_DIM, generator=gen, device=dev))
+        gen.manual_seed(5678 + l + 7919 * rank)  # every rank holds different tokens
         # one encode call covers a whole layer when its heads fit one chunk, else one head's chunk
         heads_per_call = H if T <= chunk_tokens else 1
         for h in range(0, H, heads_per_call):
@@ -313,8 +314,26 @@ def gpu_arm(args, w):
     gathered = torch.empty(world, 2, nq, k, dtype=torch.int32, device=dev) if world > 1 else None
     out = torch.empty(2, nq, k, dtype=torch.int32, device=dev)
 
+    short = None
+    k_short = int(os.environ.get("SLHA_BENCH_KSHORT", "0")) or S.shard.short_exchange_len(k, world)
+    if world > 1 and k_short < k:
+        # first exchange round with the best k_short candidates per rank; `overflow` is the collective
+        # check that no rank held back a candidate that belongs to the merged top-k
+        send = torch.empty(2, nq, k_short, dtype=torch.int32, device=dev)
+        gathered_short = torch.empty(world, 2, nq, k_short, dtype=torch.int32, device=dev)
+        flag = torch.zeros(1, dtype=torch.int32, device=dev)
+
+        def overflow(c, o):
+            unsent = c[0][:, k_short] != -1
+            viol = unsent & (c[1][:, k_short].view(torch.float32) >= o[1][:, k - 1].view(torch.float32))
+            flag.copy_(viol.any().to(torch.int32).reshape(1))
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            return bool(flag.item())
+
+        short = S.shard.ShortExchange(k_short, send, gathered_short, lambda s_, c: s_.copy_(c[:, :, :k_short]), overflow)
     scorer = S.shard.ShardedScorer(world, nq, k, cand, gathered, out,
-                                   (lambda g, c: dist.all_gather_into_tensor(g, c)) if world > 1 else None, count=cnt)
+                                   (lambda g, c: dist.all_gather_into_tensor(g, c)) if world > 1 else None, count=cnt,
+                                   short=short)
 
     def step():
         scorer.step(tiles, segs, q_coarse, q_sign)
@@ -405,6 +424,8 @@ def gpu_arm(args, w):
         "encode_tiles_per_s": enc_rate,
         "clocks": clocks,
     }
+    if world > 1:
+        line["exchange"] = {"k_short": k_short if short is not None else k, "steps_needing_full_lists": scorer.full_exchanges}
     if world == 1:
         n_s = min(n_tiles, w["kv_heads"] * min(w["tokens"], 32768))
         heads = w["kv_heads"]

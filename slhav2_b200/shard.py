@@ -4,7 +4,9 @@ Every rank owns a contiguous token range of every KV head, scores only its own
 tiles (resident in its own HBM) and keeps its own top-k per query head; the
 per-rank candidates are exchanged with ONE all-gather and merged by every rank
 with the same deterministic rule (score descending, ties towards the lower
-global index).  The reference has no multi-device path; the per-tile
+global index).  With three or more ranks a shorter first exchange (the best
+2k/world + 128 candidates per rank) usually suffices; a collective check decides
+whether the full lists are needed after all.  The reference has no multi-device path; the per-tile
 independence this relies on is ElasticKvCache::score_all
 (scirust/src/ccos.rs:346-355).
 
@@ -36,6 +38,40 @@ def shard_segments(n_layers, kv_heads, tokens_local, group, position_base):
     return api.make_segments(rows)
 
 
+def short_exchange_len(k, world):
+    """Candidates per rank the short exchange sends: twice a rank's fair share of the top-k plus a
+    margin, or k when that is no shorter."""
+    return min(k, (2 * k + world - 1) // world + 128)
+
+
+class ShortExchange:
+    """Optional first round of ShardedScorer.step for world >= 3: every rank sends only its best
+    k_short candidates per query.  The merged top-k is exact unless some rank holds an unsent candidate
+    whose score reaches the merged k-th score; `overflow` decides that for all ranks together (it is a
+    collective), and the full exchange then runs as if the short one had not happened.
+
+      send      [2][nq][k_short]          this rank's best k_short (indices, then score bits)
+      gathered  [world][2][nq][k_short]
+      pack      callable(send, cand): send[:, :, :] = cand[:, :, :k_short]
+      overflow  callable(cand, out) -> bool, the same value on every rank
+    """
+
+    def __init__(self, k_short, send, gathered, pack, overflow):
+        self.k_short, self.send, self.gathered, self.pack, self.overflow = k_short, send, gathered, pack, overflow
+
+
+def short_exchange_overflows(cand_index, cand_score, merged_score, k_short):
+    """numpy statement of one rank's part of ShortExchange.overflow: cand_* are this rank's [nq][k]
+    lists (sorted, index 0xFFFFFFFF = absent), merged_score the [nq][k] result of the short exchange.
+    True when a candidate this rank did not send could belong to the top-k (ties count: an equal score
+    with a lower index would win)."""
+    k = cand_index.shape[1]
+    if k_short >= k:
+        return False
+    unsent = cand_index[:, k_short] != 0xFFFFFFFF
+    return bool(np.any(unsent & (cand_score[:, k_short] >= merged_score[:, k - 1])))
+
+
 class ShardedScorer:
     """One decode-step scorer of a rank.
 
@@ -45,26 +81,40 @@ class ShardedScorer:
       out      [2][nq][k]         merged indices, then score bits
     """
 
-    def __init__(self, world, nq, k, cand, gathered, out, all_gather, count=None):
+    def __init__(self, world, nq, k, cand, gathered, out, all_gather, count=None, short=None):
         self.world, self.nq, self.k = world, nq, k
         self.cand, self.gathered, self.out, self.count = cand, gathered, out, count
         self.all_gather = all_gather  # callable(gathered, cand)
         self.block = 2 * nq * k       # int32 elements per rank in `gathered`
+        self.short = short if (short is not None and short.k_short < k) else None
+        self.full_exchanges = 0       # steps that needed the full lists (all steps without a short exchange)
 
     # the two device steps; the CPU tests substitute checker implementations
     def local_topk(self, tiles, segments, q_coarse, q_sign):
         api.score_topk(tiles, segments, q_coarse, q_sign, self.nq, self.k, out_index=self.cand[0], out_score=self.cand[1],
                        out_count=self.count)
 
-    def merge(self, out_index=None, out_score=None):
-        api.topk_merge(self.gathered, self.gathered[0][1], self.world, self.nq, self.k, self.k,
+    def merge(self, out_index=None, out_score=None, gathered=None, k_in=None):
+        g = self.gathered if gathered is None else gathered
+        k_in = self.k if k_in is None else k_in
+        api.topk_merge(g, g[0][1], self.world, self.nq, k_in, self.k,
                        out_index=self.out[0] if out_index is None else out_index,
-                       out_score=self.out[1] if out_score is None else out_score, list_stride=self.block)
+                       out_score=self.out[1] if out_score is None else out_score, list_stride=2 * self.nq * k_in)
 
     def step(self, tiles, segments, q_coarse, q_sign, out_index=None, out_score=None):
         self.local_topk(tiles, segments, q_coarse, q_sign)
         if self.world == 1:
             return self.cand
+        if self.short is not None:
+            s = self.short
+            s.pack(s.send, self.cand)
+            self.all_gather(s.gathered, s.send)
+            self.merge(None, None, s.gathered, s.k_short)
+            if not s.overflow(self.cand, self.out):
+                if out_index is not None or out_score is not None:
+                    self.merge(out_index, out_score, s.gathered, s.k_short)
+                return self.out
+        self.full_exchanges += 1
         self.all_gather(self.gathered, self.cand)
         self.merge(out_index, out_score)
         return self.out
