@@ -88,6 +88,7 @@ class ShardedScorer:
         self.block = 2 * nq * k       # int32 elements per rank in `gathered`
         self.short = short if (short is not None and short.k_short < k) else None
         self.full_exchanges = 0       # steps that needed the full lists (all steps without a short exchange)
+        self._skip, self._penalty = 0, 1  # back-off of the short round after it was rejected
 
     # the two device steps; the CPU tests substitute checker implementations
     def local_topk(self, tiles, segments, q_coarse, q_sign):
@@ -105,15 +106,22 @@ class ShardedScorer:
         self.local_topk(tiles, segments, q_coarse, q_sign)
         if self.world == 1:
             return self.cand
-        if self.short is not None:
+        if self.short is not None and self._skip > 0:
+            self._skip -= 1  # (the decision below is collective, so every rank skips the same steps)
+        elif self.short is not None:
             s = self.short
             s.pack(s.send, self.cand)
             self.all_gather(s.gathered, s.send)
             self.merge(None, None, s.gathered, s.k_short)
             if not s.overflow(self.cand, self.out):
+                self._penalty = 1
                 if out_index is not None or out_score is not None:
                     self.merge(out_index, out_score, s.gathered, s.k_short)
                 return self.out
+            # winners concentrated on few ranks (they often stay there from step to step): leave the
+            # short round out for a while, twice as long after every rejection
+            self._skip = self._penalty
+            self._penalty = min(2 * self._penalty, 1024)
         self.full_exchanges += 1
         self.all_gather(self.gathered, self.cand)
         self.merge(out_index, out_score)
