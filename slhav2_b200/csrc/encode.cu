@@ -499,10 +499,10 @@ Status fill_args(const Model* m, EncodeArgs& a, int* kb_out) {
 template <bool QUERY, int KB>
 Status run_encode_kb(Ctx* c, EncodeArgs& a) {
     const size_t smem = encode_smem(a.d, a.d_pad, KB);
-    static thread_local bool configured = false;
-    if (!configured) {
+    static thread_local bool configured[16] = {false};  // the attribute is per device
+    if (!configured[c->device & 15]) {
         SLHA_CUDA(cudaFuncSetAttribute(encode_kernel<QUERY, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        configured = true;
+        configured[c->device & 15] = true;
     }
     const uint64_t groups = (a.n + KB - 1) / KB;
     const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, 148ull * 8);

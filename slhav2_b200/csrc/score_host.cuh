@@ -30,8 +30,8 @@ size_t score_smem_bytes(int G, int nwarps, bool topk, uint32_t cap) {
 
 template <int G, bool TOPK>
 Status launch_score_t(Ctx* c, const ScoreArgs& a, uint32_t grid, int threads, size_t smem) {
-    static thread_local size_t configured[8] = {0};
-    int dev = c->device & 7;
+    static thread_local size_t configured[16] = {0};
+    int dev = c->device & 15;
     if (configured[dev] < smem) {
         SLHA_CUDA(cudaFuncSetAttribute(score_kernel<G, TOPK>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
@@ -400,10 +400,10 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.cap = p->mma_cap;
         a.cand_keys = p->d_cand_keys;
         a.cand_cnt = p->d_cand_cnt;
-        static thread_local bool mma_configured = false;
-        if (!mma_configured) {
+        static thread_local bool mma_configured[16] = {false};  // the attribute is per device
+        if (!mma_configured[c->device & 15]) {
             SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            mma_configured = true;
+            mma_configured[c->device & 15] = true;
         }
         score_mma_kernel<true><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a);
         count_launch();
@@ -428,10 +428,10 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     CompLists L{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, p->list_cap};
     const uint32_t cap_s = merge_cap((uint64_t)p->max_parts * p->list_cap, p->kp2, k);
     const size_t smem = merge_smem(cap_s, p->kp2);
-    static thread_local bool configured = false;
-    if (!configured) {
+    static thread_local bool configured[16] = {false};  // the attribute is per device
+    if (!configured[c->device & 15]) {
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<CompLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-        configured = true;
+        configured[c->device & 15] = true;
     }
     topk_merge_kernel<CompLists><<<(uint32_t)nq, merge_threads(cap_s), smem, c->stream>>>(L, k, p->kp2, cap_s, d_out_index, d_out_score, d_out_count);
     count_launch();
@@ -477,10 +477,10 @@ Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* 
     uint32_t kp2 = 2;
     while (kp2 < k_out) kp2 <<= 1;
     PairLists L{cand_index, cand_score, n_lists, n_queries, k_in, list_stride};
-    static thread_local bool configured = false;
-    if (!configured) {
+    static thread_local bool configured[16] = {false};  // the attribute is per device
+    if (!configured[c->device & 15]) {
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-        configured = true;
+        configured[c->device & 15] = true;
     }
     const uint32_t cap_s = merge_cap((uint64_t)n_lists * k_in, kp2, k_out);
     topk_merge_kernel<PairLists><<<n_queries, merge_threads(cap_s), merge_smem(cap_s, kp2), c->stream>>>(L, k_out, kp2, cap_s, out_index, out_score, nullptr);
