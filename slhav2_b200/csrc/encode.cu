@@ -230,40 +230,105 @@ __device__ __forceinline__ void axpy_keys(float (&acc)[NK], float x, const float
     }
 }
 
+// NK consecutive floats (16-byte aligned when NK % 4 == 0) to / from registers
+template <int NK>
+__device__ __forceinline__ void store_keys(float* dst, const float (&v)[NK]) {
+    if (NK % 4 == 0) {
+#pragma unroll
+        for (int j4 = 0; j4 < NK / 4; ++j4)
+            reinterpret_cast<float4*>(dst)[j4] = make_float4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < NK; ++j) dst[j] = v[j];
+    }
+}
+template <int NK>
+__device__ __forceinline__ void load_keys(float (&v)[NK], const float* src) {
+    if (NK % 4 == 0) {
+#pragma unroll
+        for (int j4 = 0; j4 < NK / 4; ++j4) {
+            const float4 x = reinterpret_cast<const float4*>(src)[j4];
+            v[4 * j4] = x.x; v[4 * j4 + 1] = x.y; v[4 * j4 + 2] = x.z; v[4 * j4 + 3] = x.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NK; ++j) v[j] = src[j];
+    }
+}
+
 // KB keys per CTA pass (compile time: 32 unless the model dimension leaves no room).  Every
 // contraction is walked sequentially by the thread that owns the output element, for all the keys
 // the thread holds at once: one matrix element and KB/8 (latent, residual: half the keys per thread)
 // or KB/4 (sign bits) vector loads feed KB or 2 KB multiply-adds.
+constexpr int enc_row_stride(int kb) { return kb >= 8 ? kb + 4 : kb; }
+
 template <bool QUERY, int KB>
 __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int PER = KB >= 2 ? KB / 2 : 1;  // keys per thread where two threads share an output row
     const uint32_t d = a.d, dp = a.d_pad;
-    // shared: tiles [KB][128 B] | h [KB][128] | keyT [d][KB] | bufT [d_pad][KB] | wsT [128][KB]
+    // shared: tiles [KB][128 B] | h [KB][128] | keyT [d][KS] | bufT [d_pad][KS] | wsT [128][KS]
     // (keys and the sign-LSH input are stored transposed so that one thread
-    // reads the KB values of a contraction index with 16-byte loads)
+    // reads the KB values of a contraction index with 16-byte loads).  Rows are KS = KB + 4
+    // floats apart: a warp whose lanes walk the rows then spreads its 16-byte accesses over
+    // all banks, while lanes that walk the keys of one row stay on consecutive banks.
+    constexpr int KS = enc_row_stride(KB);
     unsigned char* tl = smem;
     float* hs = reinterpret_cast<float*>(tl + (size_t)KB * TILE_BYTES);
     float* keyT = hs + (size_t)KB * D_C;
-    float* buf = keyT + (((size_t)d * KB + 3) & ~size_t(3));
-    float* wsT = buf + (size_t)dp * KB;  // h_k * s_k of every key, transposed like keyT
+    float* buf = keyT + (((size_t)d * KS + 3) & ~size_t(3));
+    float* wsT = buf + (size_t)dp * KS;  // h_k * s_k of every key, transposed like keyT
 
     for (uint64_t base = (uint64_t)blockIdx.x * KB; base < a.n; base += (uint64_t)gridDim.x * KB) {
         const int nk = (int)min((uint64_t)KB, a.n - base);
         __syncthreads();
         // ---- load keys (transposed: keyT[i][j]); absent keys are zero ------
-        for (uint32_t e = tid; e < d * (uint32_t)KB; e += ENC_THREADS) {
-            const int j = e / d;
-            const uint32_t i = e % d;
-            float x = 0.0f;
-            if (j < nk) {
-                const uint64_t o = (base + j) * d + i;
-                x = a.key_dtype == SLHA_B200_F32
-                        ? reinterpret_cast<const float*>(a.keys)[o]
-                        : __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(a.keys)[o] << 16);
+        const bool f32 = a.key_dtype == SLHA_B200_F32;
+        const uint32_t epc = f32 ? 4u : 8u;  // elements per 16-byte chunk
+        if (KB >= 8 && d % epc == 0 && (reinterpret_cast<uintptr_t>(a.keys) & 15) == 0) {
+            // 16-byte chunks; the lanes of a warp take the same chunk of consecutive keys, so
+            // that their transposed stores fall on consecutive banks.  Both loads of a thread
+            // are in flight before the first store.
+            const uint32_t cpk = d / epc, total = cpk * (uint32_t)KB;
+            const uint4* src = reinterpret_cast<const uint4*>(a.keys) + base * cpk;
+            for (uint32_t c0 = tid; c0 < total; c0 += 2 * ENC_THREADS) {
+                uint4 v[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const uint32_t c = c0 + u * ENC_THREADS, j = c % KB, ic = c / KB;
+                    v[u] = make_uint4(0u, 0u, 0u, 0u);
+                    if (c < total && (int)j < nk) v[u] = __ldg(src + (size_t)j * cpk + ic);
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const uint32_t c = c0 + u * ENC_THREADS, j = c % KB, ic = c / KB;
+                    if (c >= total) continue;
+                    float* dst = keyT + (size_t)(ic * epc) * KS + j;
+                    const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if (f32) {
+                            dst[(size_t)q * KS] = __uint_as_float(w[q]);
+                        } else {  // bf16 -> f32 widening is exact
+                            dst[(size_t)(2 * q) * KS] = __uint_as_float(w[q] << 16);
+                            dst[(size_t)(2 * q + 1) * KS] = __uint_as_float(w[q] & 0xFFFF0000u);
+                        }
+                    }
+                }
             }
-            keyT[(size_t)i * KB + j] = x;
+        } else {
+            for (uint32_t e = tid; e < d * (uint32_t)KB; e += ENC_THREADS) {
+                const int j = e / d;
+                const uint32_t i = e % d;
+                float x = 0.0f;
+                if (j < nk) {
+                    const uint64_t o = (base + j) * d + i;
+                    x = f32 ? reinterpret_cast<const float*>(a.keys)[o]
+                            : __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(a.keys)[o] << 16);
+                }
+                keyT[(size_t)i * KS + j] = x;
+            }
         }
         for (int e = tid; e < KB * 32; e += ENC_THREADS) reinterpret_cast<uint32_t*>(tl)[e] = 0;
         __syncthreads();
@@ -278,13 +343,16 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
                 for (int j = 0; j < PER; ++j) acc[j] = 0.0f;
 #pragma unroll 8
                 for (uint32_t i = 0; i < d; ++i)
-                    axpy_keys<PER>(acc, a.pt[(size_t)i * D_C + k], keyT + (size_t)i * KB + j0);
+                    axpy_keys<PER>(acc, a.pt[(size_t)i * D_C + k], keyT + (size_t)i * KS + j0);
                 const float sk = a.scale[k];
 #pragma unroll
                 for (int j = 0; j < PER; ++j) {
                     const float hv = QUERY ? __fmul_rn(acc[j], sk) : __fdiv_rn(acc[j], sk);
                     hs[(size_t)(j0 + j) * D_C + k] = hv;
+                    // w[k][j] = h_j[k] * s_k, the factor the reconstruction multiplies P[k][:] by
+                    acc[j] = __fmul_rn(hv, sk);
                 }
+                if (!QUERY) store_keys<PER>(wsT + (size_t)k * KS + j0, acc);
             }
         }
         __syncthreads();
@@ -293,14 +361,9 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
             for (int e = tid; e < nk * D_C; e += ENC_THREADS)
                 a.q_coarse[(base + e / D_C) * D_C + (e % D_C)] = hs[e];
             // sign-LSH input is the raw query
-            for (uint32_t e = tid; e < dp * (uint32_t)KB; e += ENC_THREADS)
-                buf[e] = (e / KB) < d ? keyT[e] : 0.0f;
+            for (uint32_t e = tid; e < dp * (uint32_t)KS; e += ENC_THREADS)
+                buf[e] = (e / KS) < d ? keyT[e] : 0.0f;
         } else {
-            // ---- w[k][j] = h_j[k] * s_k, the factor the reconstruction multiplies P[k][:] by ----
-            for (int e = tid; e < D_C * KB; e += ENC_THREADS) {
-                const int k = e / KB, j = e % KB;
-                wsT[e] = __fmul_rn(hs[(size_t)j * D_C + k], a.scale[k]);
-            }
             // ---- quantise: one warp per key ---------------------------------
             for (int j = warp; j < KB; j += ENC_THREADS / 32)
                 quantize_warp(hs + (size_t)j * D_C, a.codec, tl + (size_t)j * TILE_BYTES, lane);
@@ -315,13 +378,14 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
                 for (int j = 0; j < PER; ++j) acc[j] = 0.0f;
                 const float* wr = wsT + half * PER;
 #pragma unroll 8
-                for (int k = 0; k < D_C; ++k) axpy_keys<PER>(acc, a.p[(size_t)k * d + i], wr + (size_t)k * KB);
-                float* br = buf + (size_t)i * KB + half * PER;
-                const float* kr = keyT + (size_t)i * KB + half * PER;
+                for (int k = 0; k < D_C; ++k) axpy_keys<PER>(acc, a.p[(size_t)k * d + i], wr + (size_t)k * KS);
+                float kv[PER];
+                load_keys<PER>(kv, keyT + (size_t)i * KS + half * PER);
 #pragma unroll
-                for (int j = 0; j < PER; ++j) br[j] = __fsub_rn(kr[j], acc[j]);
+                for (int j = 0; j < PER; ++j) acc[j] = __fsub_rn(kv[j], acc[j]);
+                store_keys<PER>(buf + (size_t)i * KS + half * PER, acc);
             }
-            for (uint32_t e = d * KB + tid; e < dp * KB; e += ENC_THREADS) buf[e] = 0.0f;  // padding rows
+            for (uint32_t e = d * KS + tid; e < dp * KS; e += ENC_THREADS) buf[e] = 0.0f;  // padding rows
         }
         __syncthreads();
 
@@ -330,7 +394,7 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
             const int j = tid;
             float ss = 0.0f;
             for (uint32_t i = 0; i < d; ++i) {
-                const float x = buf[(size_t)i * KB + j];
+                const float x = buf[(size_t)i * KS + j];
                 ss = __fadd_rn(ss, __fmul_rn(x, x));
             }
             const float sigma = __fsqrt_rn(__fdiv_rn(ss, (float)d));
@@ -352,21 +416,21 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
 
         // ---- optional randomised Hadamard transform of buf ------------------
         if (a.diag) {
-            for (uint32_t e = tid; e < dp * (uint32_t)KB; e += ENC_THREADS)
-                buf[e] = __fmul_rn(buf[e], a.diag[e / KB]);
+            for (uint32_t e = tid; e < dp * (uint32_t)KS; e += ENC_THREADS)
+                buf[e] = __fmul_rn(buf[e], a.diag[e / KS]);
             __syncthreads();
             for (uint32_t h = 1; h < dp; h <<= 1) {
                 for (uint32_t e = tid; e < (dp / 2) * (uint32_t)KB; e += ENC_THREADS) {
                     const uint32_t j = e % KB, pr = e / KB;
                     const uint32_t lo = ((pr / h) * 2 * h) + (pr % h);
                     float* col = buf + j;
-                    const float x = col[(size_t)lo * KB], y = col[(size_t)(lo + h) * KB];
-                    col[(size_t)lo * KB] = __fadd_rn(x, y);
-                    col[(size_t)(lo + h) * KB] = __fsub_rn(x, y);
+                    const float x = col[(size_t)lo * KS], y = col[(size_t)(lo + h) * KS];
+                    col[(size_t)lo * KS] = __fadd_rn(x, y);
+                    col[(size_t)(lo + h) * KS] = __fsub_rn(x, y);
                 }
                 __syncthreads();
             }
-            for (uint32_t e = tid; e < dp * (uint32_t)KB; e += ENC_THREADS)
+            for (uint32_t e = tid; e < dp * (uint32_t)KS; e += ENC_THREADS)
                 buf[e] = __fmul_rn(buf[e], a.fwht_inv);
             __syncthreads();
         }
@@ -378,7 +442,7 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
 #pragma unroll
             for (int j = 0; j < KB; ++j) acc[j] = 0.0f;
 #pragma unroll 8
-            for (uint32_t i = 0; i < dp; ++i) axpy_keys<KB>(acc, a.zt[(size_t)i * D_S + s], buf + (size_t)i * KB);
+            for (uint32_t i = 0; i < dp; ++i) axpy_keys<KB>(acc, a.zt[(size_t)i * D_S + s], buf + (size_t)i * KS);
 #pragma unroll
             for (int j = 0; j < KB; ++j) {
                 const unsigned b = __ballot_sync(0xFFFFFFFFu, acc[j] < 0.0f);
@@ -473,7 +537,8 @@ __global__ void decode_kernel(const unsigned char* tile, const float* p, const f
 }
 
 size_t encode_smem(uint32_t d, uint32_t dp, int kb) {
-    return ((((size_t)d * kb + 3) & ~size_t(3)) + (size_t)kb * D_C + (size_t)kb * dp + (size_t)kb * D_C) * 4 + (size_t)kb * TILE_BYTES;
+    const size_t ks = (size_t)enc_row_stride(kb);
+    return (((d * ks + 3) & ~size_t(3)) + (size_t)kb * D_C + ks * dp + ks * D_C) * 4 + (size_t)kb * TILE_BYTES;
 }
 
 Status fill_args(const Model* m, EncodeArgs& a, int* kb_out) {
@@ -486,9 +551,9 @@ Status fill_args(const Model* m, EncodeArgs& a, int* kb_out) {
     a.diag = m->d_diag;
     a.fwht_inv = 1.0f / sqrtf((float)m->d_pad);
     a.lambda_c = sqrtf(3.14159265358979323846f / (2.0f * (float)D_S));
-    // 32 keys per CTA pass when three CTAs still share an SM, else fewer
+    // 32 keys per CTA pass when two CTAs still share an SM (their registers allow no more), else fewer
     int kb = 32;
-    while (kb > 1 && encode_smem(a.d, a.d_pad, kb) > (kb == 32 ? 72 : 200) * 1024) kb >>= 1;
+    while (kb > 1 && encode_smem(a.d, a.d_pad, kb) > (kb == 32 ? 100 : 200) * 1024) kb >>= 1;
     if (encode_smem(a.d, a.d_pad, kb) > 200 * 1024)
         return Status(SLHA_ERR_DIMENSION, "model dimension too large for the encode kernel");
     *kb_out = kb;
