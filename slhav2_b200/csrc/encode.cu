@@ -256,6 +256,20 @@ __device__ __forceinline__ void load_keys(float (&v)[NK], const float* src) {
     }
 }
 
+// acc[r][j] += m[r] * v[j] for an R x K register tile: R output rows (or columns) times K keys.
+// Each output still sums its products in contraction order, one multiply and one add at a time.
+template <int R, int K>
+__device__ __forceinline__ void outer_keys(float (&acc)[R][K], const float4& m4, const float* v) {
+    static_assert(R == 4, "the matrix operand is one 16-byte load");
+    float kv[K];
+    load_keys<K>(kv, v);
+    const float m[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int j = 0; j < K; ++j) acc[r][j] = __fadd_rn(acc[r][j], __fmul_rn(m[r], kv[j]));
+}
+
 // KB keys per CTA pass (compile time: 32 unless the model dimension leaves no room).  Every
 // contraction is walked sequentially by the thread that owns the output element, for all the keys
 // the thread holds at once: one matrix element and KB/8 (latent, residual: half the keys per thread)
@@ -333,8 +347,42 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
         for (int e = tid; e < KB * 32; e += ENC_THREADS) reinterpret_cast<uint32_t*>(tl)[e] = 0;
         __syncthreads();
 
-        // ---- latent / q_coarse: row k = tid & 127, keys of half (tid >> 7) ---
-        {
+        // With 32 keys per pass every thread holds a 4 x 4 (latent, residual) or 4 x 8 (sign bits)
+        // tile of outputs: four matrix elements (one 16-byte load) and four or eight key values
+        // (one or two 16-byte broadcast loads) feed 16 or 32 multiply-adds, a third of the
+        // register fills per multiply-add of a one-row tile.
+        const bool tiled = KB == 32 && d % 4 == 0 &&
+                           ((reinterpret_cast<uintptr_t>(a.pt) | reinterpret_cast<uintptr_t>(a.p) |
+                             reinterpret_cast<uintptr_t>(a.zt) | reinterpret_cast<uintptr_t>(a.scale)) & 15) == 0;
+        // ---- latent / q_coarse: rows 4 lane .. +3, keys 4 warp .. +3 ------------
+        if (KB == 32 && tiled) {
+            float acc[4][4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[r][j] = 0.0f;
+            const float4* mp = reinterpret_cast<const float4*>(a.pt) + lane;
+#pragma unroll 8
+            for (uint32_t i = 0; i < d; ++i)
+                outer_keys<4, 4>(acc, __ldg(mp + (size_t)i * (D_C / 4)), keyT + (size_t)i * KS + 4 * warp);
+            const float4 s4 = __ldg(reinterpret_cast<const float4*>(a.scale) + lane);
+            const float sk[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float hv[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    hv[r] = QUERY ? __fmul_rn(acc[r][j], sk[r]) : __fdiv_rn(acc[r][j], sk[r]);
+                    acc[r][j] = __fmul_rn(hv[r], sk[r]);  // w[k][j] = h_j[k] * s_k, the factor of P[k][:] in the reconstruction
+                }
+                store_keys<4>(hs + (size_t)(4 * warp + j) * D_C + 4 * lane, hv);
+            }
+            if (!QUERY) {
+#pragma unroll
+                for (int r = 0; r < 4; ++r) store_keys<4>(wsT + (size_t)(4 * lane + r) * KS + 4 * warp, acc[r]);
+            }
+        } else {
+            // row k = tid & 127, keys of half (tid >> 7)
             const int k = tid & 127, half = tid >> 7;
             const int j0 = (KB >= 2) ? half * PER : 0;
             if (KB >= 2 || half == 0) {
@@ -371,7 +419,29 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
             // ---- residual e = key - sum_k (h_k*s_k) * P[k][:]  (k outer, sequential): a thread owns
             //      column i for half of the keys ---------------------------------------------------
             constexpr int HALVES = KB >= 2 ? 2 : 1;
-            for (uint32_t wi = tid; wi < HALVES * d; wi += ENC_THREADS) {
+            // tiled: columns 4 ig .. +3 for keys 4 kg .. +3
+            for (uint32_t wi = tid; KB == 32 && tiled && wi < (d / 4) * 8; wi += ENC_THREADS) {
+                const uint32_t ig = wi % (d / 4), kg = wi / (d / 4);
+                float acc[4][4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[r][j] = 0.0f;
+                const float4* mp = reinterpret_cast<const float4*>(a.p) + ig;
+                const float* wr = wsT + 4 * kg;
+#pragma unroll 8
+                for (int k = 0; k < D_C; ++k)
+                    outer_keys<4, 4>(acc, __ldg(mp + (size_t)k * (d / 4)), wr + (size_t)k * KS);
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    float kv[4];
+                    load_keys<4>(kv, keyT + (size_t)(4 * ig + r) * KS + 4 * kg);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[r][j] = __fsub_rn(kv[j], acc[r][j]);
+                    store_keys<4>(buf + (size_t)(4 * ig + r) * KS + 4 * kg, acc[r]);
+                }
+            }
+            for (uint32_t wi = tid; !(KB == 32 && tiled) && wi < HALVES * d; wi += ENC_THREADS) {
                 const uint32_t i = wi % d, half = wi / d;
                 float acc[PER];
 #pragma unroll
@@ -435,8 +505,37 @@ __global__ void __launch_bounds__(ENC_THREADS) encode_kernel(EncodeArgs a) {
             __syncthreads();
         }
 
-        // ---- sign-LSH: thread s owns hyperplane s for all KB keys ------------
-        {
+        // ---- sign-LSH, tiled: hyperplanes 4 rg .. +3 for keys 8 kg .. +7 -------
+        if (KB == 32 && tiled) {
+            const int rg = tid & 63, kg = tid >> 6;
+            float acc[4][8];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[r][j] = 0.0f;
+            const float4* mp = reinterpret_cast<const float4*>(a.zt) + rg;
+#pragma unroll 8
+            for (uint32_t i = 0; i < dp; ++i)
+                outer_keys<4, 8>(acc, __ldg(mp + (size_t)i * (D_S / 4)), buf + (size_t)i * KS + 8 * kg);
+            // bit s of a key = (acc < 0); this thread holds bits 4 rg .. +3, eight lanes fill a 32-bit word
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint32_t v = (acc[0][j] < 0.0f ? 1u : 0u) | (acc[1][j] < 0.0f ? 2u : 0u) |
+                             (acc[2][j] < 0.0f ? 4u : 0u) | (acc[3][j] < 0.0f ? 8u : 0u);
+                v <<= 4 * (lane & 7);
+                v |= __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+                v |= __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+                v |= __shfl_xor_sync(0xFFFFFFFFu, v, 4);
+                const int key = 8 * kg + j, word = (rg >> 3);
+                if ((lane & 7) == 0 && key < nk) {
+                    if (QUERY)
+                        reinterpret_cast<uint32_t*>(a.q_sign)[(base + key) * 8 + word] = v;
+                    else
+                        reinterpret_cast<uint32_t*>(tl + (size_t)key * TILE_BYTES + 64)[word] = v;
+                }
+            }
+        } else {
+            // thread s owns hyperplane s for all KB keys
             const int s = tid;  // ENC_THREADS == D_S
             float acc[KB];
 #pragma unroll
