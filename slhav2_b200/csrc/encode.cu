@@ -256,18 +256,52 @@ __device__ __forceinline__ void load_keys(float (&v)[NK], const float* src) {
     }
 }
 
+// Packed pairs of float32 (Blackwell f32x2): one instruction multiplies two independent float32
+// pairs, each product rounded to nearest exactly like the scalar multiply, so the two products of
+// a key pair cost one issue slot.  The additions stay scalar: the assembler contracts a packed
+// multiply followed by a packed add into a packed fused multiply-add even when both carry an
+// explicit rounding mode and contraction is switched off (checked on sm_100a, CUDA 12.9), and a
+// fused multiply-add rounds once where the reference rounds twice.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void mul2(uint64_t a, uint64_t b, float& lo, float& hi) {
+    uint64_t m;
+    asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(m) : "l"(a), "l"(b));
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(m));
+}
+
 // acc[r][j] += m[r] * v[j] for an R x K register tile: R output rows (or columns) times K keys.
 // Each output still sums its products in contraction order, one multiply and one add at a time.
 template <int R, int K>
 __device__ __forceinline__ void outer_keys(float (&acc)[R][K], const float4& m4, const float* v) {
-    static_assert(R == 4, "the matrix operand is one 16-byte load");
-    float kv[K];
-    load_keys<K>(kv, v);
-    const float m[4] = {m4.x, m4.y, m4.z, m4.w};
+    static_assert(R == 4 && K % 4 == 0, "the matrix operand is one 16-byte load");
+    uint64_t kv[K / 2];
+#pragma unroll
+    for (int j4 = 0; j4 < K / 4; ++j4) {
+        const float4 x = reinterpret_cast<const float4*>(v)[j4];
+        kv[2 * j4] = pack2(x.x, x.y);
+        kv[2 * j4 + 1] = pack2(x.z, x.w);
+    }
+    const uint64_t m[4] = {pack2(m4.x, m4.x), pack2(m4.y, m4.y), pack2(m4.z, m4.z), pack2(m4.w, m4.w)};
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int j = 0; j < K; ++j) acc[r][j] = __fadd_rn(acc[r][j], __fmul_rn(m[r], kv[j]));
+        for (int j = 0; j < K / 2; ++j) {
+            float p0, p1;
+            mul2(m[r], kv[j], p0, p1);
+            acc[r][2 * j] = __fadd_rn(acc[r][2 * j], p0);
+            acc[r][2 * j + 1] = __fadd_rn(acc[r][2 * j + 1], p1);
+        }
+}
+template <int R, int K>
+__device__ __forceinline__ void zero_tile(float (&acc)[R][K]) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int j = 0; j < K; ++j) acc[r][j] = 0.0f;
 }
 
 // KB keys per CTA pass (compile time: 32 unless the model dimension leaves no room).  Every
@@ -358,10 +392,7 @@ __global__ void __launch_bounds__(ENC_THREADS, KB == 32 ? 3 : 1) encode_kernel(E
         // ---- latent / q_coarse: rows 4 lane .. +3, keys 4 warp .. +3 ------------
         if (KB == 32 && tiled) {
             float acc[4][4];
-#pragma unroll
-            for (int r = 0; r < 4; ++r)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[r][j] = 0.0f;
+            zero_tile<4, 4>(acc);
             const float4* mp = reinterpret_cast<const float4*>(a.pt) + lane;
 #pragma unroll 16
             for (uint32_t i = 0; i < d; ++i)
@@ -424,10 +455,7 @@ __global__ void __launch_bounds__(ENC_THREADS, KB == 32 ? 3 : 1) encode_kernel(E
             for (uint32_t wi = tid; KB == 32 && tiled && wi < (d / 4) * 8; wi += ENC_THREADS) {
                 const uint32_t ig = wi % (d / 4), kg = wi / (d / 4);
                 float acc[4][4];
-#pragma unroll
-                for (int r = 0; r < 4; ++r)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) acc[r][j] = 0.0f;
+                zero_tile<4, 4>(acc);
                 const float4* mp = reinterpret_cast<const float4*>(a.p) + ig;
                 const float* wr = wsT + 4 * kg;
 #pragma unroll 16
@@ -510,10 +538,7 @@ __global__ void __launch_bounds__(ENC_THREADS, KB == 32 ? 3 : 1) encode_kernel(E
         if (KB == 32 && tiled) {
             const int rg = tid & 63, kg = tid >> 6;
             float acc[4][8];
-#pragma unroll
-            for (int r = 0; r < 4; ++r)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[r][j] = 0.0f;
+            zero_tile<4, 8>(acc);
             const float4* mp = reinterpret_cast<const float4*>(a.zt) + rg;
 #pragma unroll 16
             for (uint32_t i = 0; i < dp; ++i)
