@@ -447,7 +447,8 @@ __global__ void __launch_bounds__(ENC_THREADS, KB == 32 ? 3 : 1) encode_kernel(E
             // ---- quantise: one warp per key ---------------------------------
             for (int j = warp; j < KB; j += ENC_THREADS / 32)
                 quantize_warp(hs + (size_t)j * D_C, a.codec, tl + (size_t)j * TILE_BYTES, lane);
-            __syncthreads();
+            // (no barrier: the residual phase reads the keys and the reconstruction factors, which
+            //  the barrier after the latent phase already covers, and does not touch the tiles)
             // ---- residual e = key - sum_k (h_k*s_k) * P[k][:]  (k outer, sequential): a thread owns
             //      column i for half of the keys ---------------------------------------------------
             constexpr int HALVES = KB >= 2 ? 2 : 1;
@@ -695,10 +696,11 @@ Status run_encode_kb(Ctx* c, EncodeArgs& a) {
         configured[c->device & 15] = true;
     }
     const uint64_t groups = (a.n + KB - 1) / KB;
-    // more CTAs than fit at once (1184 against 444 resident at head dimension 128): the hardware
-    // hands out CTAs as others finish, which balances the tail and keeps the CTAs of an SM in
-    // different phases; measured 3 % faster than one resident wave
-    const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, 148ull * 8);
+    // far more CTAs than fit at once (444 are resident at head dimension 128): the hardware hands
+    // out a CTA whenever one finishes, which balances the tail and keeps the CTAs sharing an SM in
+    // different phases, so that the arithmetic of one covers the loads, quantisation and barriers
+    // of the others.  One resident wave measured 182 M keys/s, 8 CTAs per SM 191, one CTA per pass 199.
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(groups, 148ull * 64);
     encode_kernel<QUERY, KB><<<grid, ENC_THREADS, smem, c->stream>>>(a);
     count_launch();
     SLHA_CUDA(cudaGetLastError());
