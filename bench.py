@@ -390,6 +390,47 @@ def gpu_arm(args, w):
     barrier()
     e2e_ms = max(f0.elapsed_time(f1), 1e3 * (time.perf_counter() - t0))  # host waits are part of an end-to-end call
 
+    # The same end-to-end calls from two host threads (the C ABI is re-entrant; every thread has its
+    # own stream and staging buffers inside the library, and the reference's consumers call it from
+    # several worker threads): one caller's copies overlap the other caller's kernels.  Every step still
+    # moves its own queries up and its own results down inside the timed region.
+    e2e_serial_ms, callers = e2e_ms, 1
+    if world == 1:
+        import threading
+
+        callers = 2
+        per = (args.steps + callers - 1) // callers
+        outs = [(torch.empty(nq, k, dtype=torch.int32).pin_memory(), torch.empty(nq, k, dtype=torch.float32).pin_memory(),
+                 torch.empty(nq, dtype=torch.int32).pin_memory()) for _ in range(callers)]
+        go = threading.Barrier(callers + 1)
+        failed = []
+
+        def caller(i, n_calls):
+            try:
+                S.set_device(local)  # thread-local in the library; no stream set: the library's own per-thread stream
+                for _ in range(2):
+                    S.score_topk(tiles, segs, hq, hs, nq, k, out_index=outs[i][0], out_score=outs[i][1], out_count=outs[i][2])
+                go.wait()
+                for _ in range(n_calls):
+                    S.score_topk(tiles, segs, hq, hs, nq, k, out_index=outs[i][0], out_score=outs[i][1], out_count=outs[i][2])
+            except Exception as exc:  # surfaces in the main thread
+                failed.append(exc)
+                go.abort()
+
+        threads = [threading.Thread(target=caller, args=(i, per)) for i in range(callers)]
+        for th in threads:
+            th.start()
+        go.wait()
+        t0 = time.perf_counter()
+        for th in threads:
+            th.join()
+        torch.cuda.synchronize()
+        piped_ms = 1e3 * (time.perf_counter() - t0) * args.steps / (per * callers)
+        if failed:
+            raise failed[0]
+        assert torch.equal(outs[0][0], h_idx) and torch.equal(outs[1][0], h_idx), "concurrent callers disagree with the serial result"
+        e2e_ms = min(piped_ms, e2e_serial_ms)
+
     if world > 1:
         t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -419,7 +460,9 @@ def gpu_arm(args, w):
                      "traffic_source": "ncu dram__bytes_read per tile and dram__bytes_write per work item on a reduced case, "
                                        "scaled to this launch's tiles and work items (profiles/)"},
         "e2e": {"value": total_tiles / (e2e_ms / args.steps * 1e-3), "unit": "tiles/s", "ms_per_step": e2e_ms / args.steps,
-                "h2d_bytes_per_step": int(nq * (512 + 32)), "d2h_bytes_per_step": int(nq * k * 8 + (nq * 4 if world == 1 else 0))},
+                "h2d_bytes_per_step": int(nq * (512 + 32)), "d2h_bytes_per_step": int(nq * k * 8 + (nq * 4 if world == 1 else 0)),
+                "concurrent_callers": callers if e2e_ms < e2e_serial_ms else 1,
+                "one_call_at_a_time": {"value": total_tiles / (e2e_serial_ms / args.steps * 1e-3), "ms_per_step": e2e_serial_ms / args.steps}},
         "gpu_launches": int(launches),
         "encode_tiles_per_s": enc_rate,
         "clocks": clocks,
