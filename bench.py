@@ -315,7 +315,11 @@ def gpu_arm(args, w):
     out = torch.empty(2, nq, k, dtype=torch.int32, device=dev)
 
     short = None
-    k_short = int(os.environ.get("SLHA_BENCH_KSHORT", "0")) or S.shard.short_exchange_len(k, world)
+    # the short first exchange round needs a host decision per step (a collective flag), which costs more
+    # than it saves when steps are this short (config 5 at 8 GPUs: 0.44 ms with it, 0.24 ms without);
+    # SLHA_BENCH_KSHORT=<n> or =auto switches it on for the one-step-at-a-time loop
+    ks_env = os.environ.get("SLHA_BENCH_KSHORT", "0")
+    k_short = S.shard.short_exchange_len(k, world) if ks_env == "auto" else (int(ks_env) or k)
     if world > 1 and k_short < k:
         # first exchange round with the best k_short candidates per rank; `overflow` is the collective
         # check that no rank held back a candidate that belongs to the merged top-k
@@ -364,6 +368,52 @@ def gpu_arm(args, w):
     launches = S.launch_count() - launches0
     score_ms, merge_ms = S.timing_end(args.steps)
     clocks = sampler.stop() if rank == 0 else None
+
+    # ---- N > 1: the same K steps with the exchange and merge of step i on a second stream while step
+    # i+1 is scored (the steps are independent: each has its own candidate / gathered / result buffers)
+    serial_ms, ms_pipe, pipelined = ms, float("inf"), False
+    if world > 1 and os.environ.get("SLHA_BENCH_PIPELINE", "1") != "0":
+        xstream = torch.cuda.Stream(device=dev, priority=-1)
+
+        class TorchStreams:
+            def use_score(self):
+                torch.cuda.set_stream(stream)
+                S.set_stream(stream.cuda_stream)
+
+            def use_exchange(self):
+                torch.cuda.set_stream(xstream)
+                S.set_stream(xstream.cuda_stream)
+
+            def record(self, tag):
+                ev = torch.cuda.Event()
+                ev.record()
+                return ev
+
+            def wait_event(self, ev):
+                torch.cuda.current_stream().wait_event(ev)
+
+            def sync(self, ev):
+                ev.synchronize()
+
+        ag = lambda g, c: dist.all_gather_into_tensor(g, c)
+        slots = [S.shard.ShardedScorer(world, nq, k, torch.empty_like(cand), torch.empty_like(gathered), torch.empty_like(out), ag,
+                                       count=torch.empty_like(cnt)) for _ in range(2)]
+        pipe = S.shard.PipelinedScorer(slots, TorchStreams())
+        for _ in range(4):
+            pipe.submit(tiles, segs, q_coarse, q_sign)
+        pipe.drain()
+        assert torch.equal(slots[0].out, scorer.out) and torch.equal(slots[1].out, scorer.out), "pipelined result differs"
+        barrier()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        for _ in range(args.steps):
+            pipe.submit(tiles, segs, q_coarse, q_sign)
+        for ev in pipe.exchanged:
+            stream.wait_event(ev)
+        p1.record()
+        pipe.drain()
+        barrier()
+        ms_pipe = p0.elapsed_time(p1)
 
     # ---- end to end through the C ABI with host buffers (pinned): queries up, top-k down
     hq = q_coarse.cpu().pin_memory()
@@ -432,9 +482,11 @@ def gpu_arm(args, w):
         e2e_ms = min(piped_ms, e2e_serial_ms)
 
     if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms_pipe, e2e_ms, serial_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+        ms_pipe, e2e_ms, serial_ms = float(t[0]), float(t[1]), float(t[2])
+        pipelined = ms_pipe < serial_ms  # the same decision on every rank (both are maxima over the ranks)
+        ms = min(ms_pipe, serial_ms)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -468,7 +520,8 @@ def gpu_arm(args, w):
         "clocks": clocks,
     }
     if world > 1:
-        line["exchange"] = {"k_short": k_short if short is not None else k, "steps_needing_full_lists": scorer.full_exchanges}
+        line["exchange"] = {"k_short": k_short if short is not None else k, "steps_needing_full_lists": scorer.full_exchanges,
+                            "overlapped_with_next_step": pipelined, "ms_per_step_one_step_at_a_time": serial_ms / args.steps}
     if world == 1:
         n_s = min(n_tiles, w["kv_heads"] * min(w["tokens"], 32768))
         heads = w["kv_heads"]

@@ -128,6 +128,60 @@ class ShardedScorer:
         return self.out
 
 
+class PipelinedScorer:
+    """Throughput mode for independent steps (e.g. the layers of a batch scored back to back): the
+    exchange and merge of step i run on a second stream while step i+1 is being scored, with `depth`
+    sets of candidate / gathered / result buffers.  `submit` returns the slot whose `out` buffers hold
+    the step's result once `wait(slot)` has returned; `drain` waits for everything in flight.
+
+      scorers   `depth` ShardedScorer objects, each with buffers of its own
+      streams   hooks that keep this module free of any framework:
+                  use_score()      make the scoring stream current (framework and library)
+                  use_exchange()   make the exchange stream current
+                  record(tag)      record an event on the current stream, returns it
+                  wait_event(ev)   make the current stream wait for the event
+                  sync(ev)         host wait for the event
+
+    The result of a step does not depend on the pipelining: every step runs the same calls in the same
+    order on its own buffers (tests/test_shard_gloo.py runs this class against the serial scorer).
+    """
+
+    def __init__(self, scorers, streams):
+        self.scorers, self.st = list(scorers), streams
+        self.scored = [None] * len(self.scorers)     # event: candidates of the slot are complete
+        self.exchanged = [None] * len(self.scorers)  # event: merged result of the slot is complete
+        self.n = 0
+
+    def submit(self, tiles, segments, q_coarse, q_sign):
+        slot = self.n % len(self.scorers)
+        sc, st = self.scorers[slot], self.st
+        st.use_score()
+        if self.exchanged[slot] is not None:
+            st.wait_event(self.exchanged[slot])  # the slot's buffers are free again
+        sc.local_topk(tiles, segments, q_coarse, q_sign)
+        self.scored[slot] = st.record("scored")
+        st.use_exchange()
+        st.wait_event(self.scored[slot])
+        if sc.world > 1:
+            sc.full_exchanges += 1
+            sc.all_gather(sc.gathered, sc.cand)
+            sc.merge()
+        self.exchanged[slot] = st.record("exchanged")
+        st.use_score()
+        self.n += 1
+        return slot
+
+    def wait(self, slot):
+        if self.exchanged[slot] is not None:
+            self.st.sync(self.exchanged[slot])
+        sc = self.scorers[slot]
+        return sc.out if sc.world > 1 else sc.cand
+
+    def drain(self):
+        for slot in range(len(self.scorers)):
+            self.wait(slot)
+
+
 def merge_reference(gathered_index, gathered_score, k):
     """numpy statement of the merge rule for [world][nq][k] candidate blocks
     (index 0xFFFFFFFF = absent): used by the CPU tests as the checker."""

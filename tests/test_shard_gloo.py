@@ -85,6 +85,22 @@ def _worker(rank, world, port, total_tokens, q, k_short=0, skew=False):
             j = h * group + g_
             want_i, want_v = ora.topk(ora.score_tiles(all_tiles[h], qc[j], qs[j]), k)
             ok &= np.array_equal(res[0, j].view(np.uint32), want_i) and np.array_equal(res[1, j].view(np.float32), want_v)
+    # the pipelined scorer (exchange of step i beside the scoring of step i+1) gives the same results
+    class NoStreams:
+        def use_score(self): pass
+        def use_exchange(self): pass
+        def record(self, tag): return object()
+        def wait_event(self, ev): pass
+        def sync(self, ev): pass
+
+    ag = lambda g, c: dist.all_gather(list(g.unbind(0)), c.contiguous())
+    slots = [CpuScorer(world, nq, k, torch.zeros(2, nq, k, dtype=torch.int32), torch.zeros(world, 2, nq, k, dtype=torch.int32),
+                       torch.zeros(2, nq, k, dtype=torch.int32), ag) for _ in range(2)]
+    pipe = shard.PipelinedScorer(slots, NoStreams())
+    for _ in range(3):
+        slot = pipe.submit(local, segs, qc, qs)
+        ok &= np.array_equal(pipe.wait(slot).numpy(), res)
+    pipe.drain()
     q.put((rank, bool(ok), (start, count), sc.full_exchanges))
     dist.barrier()
     dist.destroy_process_group()
