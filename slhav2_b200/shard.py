@@ -150,14 +150,23 @@ class PipelinedScorer:
         self.scorers, self.st = list(scorers), streams
         self.scored = [None] * len(self.scorers)     # event: candidates of the slot are complete
         self.exchanged = [None] * len(self.scorers)  # event: merged result of the slot is complete
+        self.sent = [None] * len(self.scorers)       # event: the slot's candidates have been gathered (scoring may overwrite them)
         self.n = 0
 
-    def submit(self, tiles, segments, q_coarse, q_sign):
+    def submit(self, tiles, segments, q_coarse, q_sign, upload=None, download=None):
+        """Queue one step.  `upload(slot)`, if given, runs on the scoring stream once the slot is free
+        and returns the (q_coarse, q_sign) to score with (e.g. after copying host queries into the
+        slot's device buffers); `download(slot)` runs on the exchange stream after the merge (e.g. an
+        asynchronous copy of the slot's result to host memory) and is covered by `wait(slot)`."""
         slot = self.n % len(self.scorers)
         sc, st = self.scorers[slot], self.st
         st.use_score()
-        if self.exchanged[slot] is not None:
-            st.wait_event(self.exchanged[slot])  # the slot's buffers are free again
+        if self.sent[slot] is not None:
+            # the slot's candidate block is free again; its gathered and result buffers are only
+            # touched on the exchange stream, in order
+            st.wait_event(self.sent[slot])
+        if upload is not None:
+            q_coarse, q_sign = upload(slot)
         sc.local_topk(tiles, segments, q_coarse, q_sign)
         self.scored[slot] = st.record("scored")
         st.use_exchange()
@@ -165,8 +174,13 @@ class PipelinedScorer:
         if sc.world > 1:
             sc.full_exchanges += 1
             sc.all_gather(sc.gathered, sc.cand)
+            self.sent[slot] = st.record("sent")
             sc.merge()
+        if download is not None:
+            download(slot)
         self.exchanged[slot] = st.record("exchanged")
+        if sc.world == 1:
+            self.sent[slot] = self.exchanged[slot]  # one rank: `download` reads the candidate block itself
         st.use_score()
         self.n += 1
         return slot
