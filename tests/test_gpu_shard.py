@@ -62,3 +62,87 @@ def test_short_exchange_matches_single_pass(skew):
         got_i = res[0].cpu().numpy().view(np.uint32)
         got_s = res[1].cpu().numpy().view(F)
         assert np.array_equal(got_i, want_i) and np.array_equal(got_s, want_s)
+
+
+def test_pipelined_schedule_matches_single_pass():
+    """The overlapped schedule on real streams: rank 0 of four scores its own shard with the library on
+    one stream while the exchange (peers' blocks delivered by copy) and the strided merge of the previous
+    step run on another; every step's result equals the single-pass top-k of the whole context."""
+    from slhav2_b200 import shard
+
+    world, n, nq, k, steps = 4, 40000, 4, 128, 7
+    tiles = H.random_tiles(n, 1, seed=41)
+    dev = torch.device("cuda", 0)
+    dt = torch.from_numpy(tiles.view(np.uint8).reshape(-1)).to(dev)
+    queries = [H.random_queries(nq, 50 + i) for i in range(steps)]
+    dq = [(torch.from_numpy(qc).to(dev), torch.from_numpy(qs.view(np.int64).reshape(nq, 4)).to(dev)) for qc, qs in queries]
+    torch.cuda.synchronize()
+    want, peers = [], []
+    for qc, qs in queries:
+        want.append(S.score_topk(dt, S.make_segments([(0, n, 0, nq, 0)]), qc, qs, nq, k)[:2])
+        blocks = []
+        for r in range(1, world):
+            start, count = shard.shard_range(n, r, world)
+            c = torch.empty(2, nq, k, dtype=torch.int32, device=dev)
+            S.score_topk(dt[start * 128:(start + count) * 128], S.make_segments([(0, count, 0, nq, start)]), qc, qs, nq, k,
+                         out_index=c[0], out_score=c[1])
+            blocks.append(c)
+        peers.append(blocks)
+    torch.cuda.synchronize()
+
+    score_stream, exchange_stream = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev, priority=-1)
+
+    class Streams:
+        def use_score(self):
+            torch.cuda.set_stream(score_stream)
+            S.set_stream(score_stream.cuda_stream)
+
+        def use_exchange(self):
+            torch.cuda.set_stream(exchange_stream)
+            S.set_stream(exchange_stream.cuda_stream)
+
+        def record(self, tag):
+            ev = torch.cuda.Event()
+            ev.record()
+            return ev
+
+        def wait_event(self, ev):
+            torch.cuda.current_stream().wait_event(ev)
+
+        def sync(self, ev):
+            ev.synchronize()
+
+    step_of_slot = {}
+
+    def make(slot):
+        def all_gather(g, c):  # what the collective would deliver for the step this slot holds
+            g[0].copy_(c)
+            for w in range(1, world):
+                g[w].copy_(peers[step_of_slot[slot]][w - 1])
+
+        return shard.ShardedScorer(world, nq, k, torch.empty(2, nq, k, dtype=torch.int32, device=dev),
+                                   torch.empty(world, 2, nq, k, dtype=torch.int32, device=dev),
+                                   torch.empty(2, nq, k, dtype=torch.int32, device=dev), all_gather)
+
+    slots = [make(0), make(1)]
+    pipe = shard.PipelinedScorer(slots, Streams())
+    start0, count0 = shard.shard_range(n, 0, world)
+    segs0 = S.make_segments([(0, count0, 0, nq, start0)])
+    hout = [torch.empty(2, nq, k, dtype=torch.int32).pin_memory() for _ in range(steps)]
+    try:
+        handles = []
+        for i in range(steps):
+            step_of_slot[i % 2] = i
+            slot = pipe.submit(dt[: count0 * 128], segs0, dq[i][0], dq[i][1],
+                               download=lambda s_, i=i: hout[i].copy_(slots[s_].out, non_blocking=True))
+            handles.append(slot)
+            if i >= 1:  # the previous step's result is read while this one is in flight
+                pipe.wait(handles[i - 1])
+        pipe.drain()
+        torch.cuda.synchronize()
+    finally:
+        torch.cuda.set_stream(torch.cuda.default_stream(dev))
+        S.set_stream(None)
+    for i in range(steps):
+        assert np.array_equal(hout[i][0].numpy().view(np.uint32), want[i][0]), i
+        assert np.array_equal(hout[i][1].numpy().view(F), want[i][1]), i
