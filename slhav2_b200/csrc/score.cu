@@ -298,6 +298,7 @@ struct ScoreArgs {
     unsigned long long* grange;   // per query row: bucket mapping of the shared score histogram (0 = none yet)
     uint32_t* ghist;              // per query row: 256 bucket counts of appended candidates
     uint32_t nf4_table;           // tensor-core kernel: build the NF4 shared-memory table (else NF4 tiles are handed back)
+    uint32_t mixed;               // tensor-core kernel: query fragments arranged for mixed 8/4 tiles (other tiles are handed back)
 };
 
 template <int G, bool TOPK>

@@ -115,6 +115,7 @@ struct Plan {
     uint32_t list_cap = 0;   // slots per candidate list: k plus the slack the tensor-core kernel's last selection may leave
     bool use_mma = false;
     bool nf4_table = true;
+    bool mixed = false;
     int codec_hint_in = -1;
     int mma_threads = 256;
     uint32_t mma_cap = 0, mma_grid = 0;
@@ -180,7 +181,9 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
         // Codec hint: the flags of the first tile of the first non-empty segment decide
         // whether the NF4 table occupies shared memory.  A wrong hint costs speed only
         // (NF4 tiles met without the table are handed to the generic kernel).
-        p->nf4_table = codec_hint != 0;
+        // (hint: -1 = look at the first tile, else bit 0 = NF4 tiles expected, bit 1 = mixed 8/4 tiles only)
+        p->nf4_table = codec_hint < 0 || (codec_hint & 1);
+        p->mixed = codec_hint > 0 && (codec_hint & 2);
         for (size_t i = 0; i < n_segs && codec_hint < 0; ++i)
             if (segs[i].n_tiles) {
                 uint16_t flags = 0;
@@ -188,6 +191,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
                 SLHA_CUDA(cudaMemcpyAsync(&flags, t0 + 118, 2, cudaMemcpyDeviceToHost, c->stream));
                 SLHA_CUDA(cudaStreamSynchronize(c->stream));
                 p->nf4_table = (flags & F_NF4) != 0;
+                p->mixed = (flags & F_MIXED) != 0;
                 break;
             }
         // per query: one region per warp, so a multiple of the warp count (256 covers 8 and 16 warps)
@@ -393,6 +397,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.grange = p->d_gpivot + nq;
         a.ghist = reinterpret_cast<uint32_t*>(p->d_gpivot + 2 * nq);
         a.nf4_table = p->nf4_table ? 1u : 0u;
+        a.mixed = p->mixed ? 1u : 0u;
         a.q_coarse = d_q_coarse;
         a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);
         a.k = k;
@@ -402,10 +407,14 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.cand_cnt = p->d_cand_cnt;
         static thread_local bool mma_configured[16] = {false};  // the attribute is per device
         if (!mma_configured[c->device & 15]) {
-            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
             mma_configured[c->device & 15] = true;
         }
-        score_mma_kernel<true><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a);
+        if (p->mixed)
+            score_mma_kernel<true, true><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a);
+        else
+            score_mma_kernel<true, false><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a);
         count_launch();
         SLHA_CUDA(cudaGetLastError());
     }

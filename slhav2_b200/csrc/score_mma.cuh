@@ -129,7 +129,10 @@ __device__ __forceinline__ int popc8(const uint4& a, const uint4& b, const uint3
 // Coarse sums of one 16-tile set for rows g (acc0) and g+8 (acc1), query t.
 // hb = shared address of row g of the set + 2t: halfword t of every 8-byte scale
 // group holds the four nibbles this thread feeds to the MMA of that group.
-// MODE 0: every row uniform INT4, 1: every row NF4, 2: per-row choice.
+// MODE 0: every row uniform INT4, 1: every row NF4, 2: per-row choice, 3: every row mixed 8/4
+// (group 0 holds the eight 8-bit head levels, halfword t = dims 2t and 2t+1, which fill k slots
+// 2t and 2t+1 as byte - 128 while slots 2t+8 and 2t+9 stay empty; groups 1..7 are INT4 groups of
+// dims 16 J - 8 ..; the B operand is arranged to match when the launch scores mixed tiles).
 template <int MODE, int J>
 __device__ __forceinline__ void coarse_group(uint32_t hb, uint32_t lut_lane, uint32_t magic, const uint32_t (&bq)[8][2], uint32_t f0,
                                              uint32_t f1, const uint4& x0, const uint4& x1, float& acc0, float& acc1) {
@@ -137,6 +140,15 @@ __device__ __forceinline__ void coarse_group(uint32_t hb, uint32_t lut_lane, uin
     uint32_t a0, a1, a2, a3, l0 = 0, l1 = 0, l2 = 0, l3 = 0;
     const bool n0 = MODE == 1 || (MODE == 2 && (f0 & F_NF4));
     const bool n1 = MODE == 1 || (MODE == 2 && (f1 & F_NF4));
+    (void)n0;
+    (void)n1;
+    if (MODE == 3 && J == 0) {
+        // bytes (b0, b1) -> half2 (1024 + b0, 1024 + b1) - 1152
+        asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(a0) : "r"(prmt(h0, magic, 0x7150u)), "r"(0xE480E480u));
+        asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(a1) : "r"(prmt(h1, magic, 0x7150u)), "r"(0xE480E480u));
+        a2 = 0u;
+        a3 = 0u;
+    } else {
     if (MODE != 0 && n0) {
         // table entry of byte b at lut_lane + 128 b
         const uint2 e0 = lds_v2<0>(lut_lane + ((h0 & 0xFFu) << 7));
@@ -152,9 +164,10 @@ __device__ __forceinline__ void coarse_group(uint32_t hb, uint32_t lut_lane, uin
     } else {
         int4_quad(h1, magic, a1, a3);
     }
+    }
     float d[4];
     mma_f16_zero(d, a0, a1, a2, a3, bq[J][0], bq[J][1]);
-    if (MODE != 0) mma_f16(d, l0, l1, l2, l3, bq[J][0], bq[J][1]);
+    if (MODE == 1 || MODE == 2) mma_f16(d, l0, l1, l2, l3, bq[J][0], bq[J][1]);
     // gs[J] as float: byte J of (x.z, x.w)
     const uint32_t gw0 = J < 4 ? x0.z : x0.w, gw1 = J < 4 ? x1.z : x1.w;
     acc0 = fmaf(d[0] + d[1], __uint2float_rn(__byte_perm(gw0, 0u, 0x4440 + (J & 3))), acc0);
@@ -943,7 +956,9 @@ __device__ __noinline__ int mma_settle(const ScoreArgs& a, const MmaItem& m, int
     return rc;
 }
 
-template <bool TOPK>
+// MIXED: the launch scores mixed 8/4 tiles (a separate instantiation, so that the nibble-codec
+// kernel is exactly the code it was without it).
+template <bool TOPK, bool MIXED = false>
 __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -1014,12 +1029,19 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
             const float* q = a.q_coarse + (size_t)(it.query_begin + (have ? qi : 0)) * D_C;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const float4 x = *reinterpret_cast<const float4*>(q + 16 * j + 4 * t);
+                // mixed 8/4 tiles: group 0 = dims 2t, 2t+1 (8-bit levels, plain in both slots, so
+                // both carry 16x the query), groups 1..7 = INT4 groups of dims 16 j - 8 ..
+                const int dim0 = !MIXED ? 16 * j + 4 * t : (j == 0 ? 0 : 16 * j - 8 + 4 * t);
+                float4 x = *reinterpret_cast<const float4*>(q + dim0);
+                if (MIXED && j == 0) {
+                    const float2 y = *reinterpret_cast<const float2*>(q + 2 * t);
+                    x = make_float4(y.x, 16.0f * y.y, 0.0f, 0.0f);
+                }
                 float v[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     if (!have) v[i] = 0.0f;
-                    big |= fabsf(v[i]) > 4000.0f;            // 16 v must stay inside fp16
+                    big |= fabsf(v[i]) > (MIXED && j == 0 && i == 1 ? 64000.0f : 4000.0f);  // 16 v must stay inside fp16
                     if (!(i & 1)) v[i] *= 16.0f;             // even slots carry 16x the query (see int4_quad)
                     if (g & 1) v[i] = half_residual(v[i]);
                 }
@@ -1114,13 +1136,20 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
             const uint4 x0 = lds_v4<112>(rb), x1 = lds_v4<112 + MMA_HALF>(rb);  // position, head|flags, gs[8]
             const uint32_t f0 = x0.y >> 16, f1 = x1.y >> 16;
             const uint32_t fo = __reduce_or_sync(0xFFFFFFFFu, f0 | f1);
-            if ((fo & (F_MIXED | F_TQ3 | F_MIX3)) || ((fo & F_NF4) && !a.nf4_table)) {
+            // a launch arranged for mixed 8/4 tiles takes nothing else (rows past the end of a ragged
+            // last set are zero-filled and their scores dropped, so they count as mixed)
+            const uint32_t row0 = s * MMA_SET_TILES + (uint32_t)g;
+            const bool all_mixed = MIXED && (__reduce_and_sync(0xFFFFFFFFu, (row0 < n ? f0 : F_MIXED) & (row0 + 8 < n ? f1 : F_MIXED)) & F_MIXED);
+            if ((fo & (F_TQ3 | F_MIX3)) || ((fo & F_MIXED) && !all_mixed) || (MIXED && !all_mixed) ||
+                ((fo & F_NF4) && !a.nf4_table)) {
                 if (lane == 0) bail[0] = 1;  // a codec this kernel does not decode: hand the item back
                 break;
             }
             float acc0, acc1;
             const uint32_t hb = rb + 2u * (uint32_t)t;
-            if (!(fo & F_NF4)) {
+            if (MIXED) {  // (all_mixed holds here)
+                coarse_set<3>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+            } else if (!(fo & F_NF4)) {
                 coarse_set<0>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
             } else if (__reduce_and_sync(0xFFFFFFFFu, f0 & f1) & F_NF4) {
                 coarse_set<1>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
