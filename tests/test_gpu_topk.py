@@ -194,3 +194,20 @@ def test_generic_kernel_only_mode_matches():
     i1, s1 = outs[1][:4], outs[1][4:]
     assert np.all(np.abs(s0 - s1) <= 1e-3)
     assert np.mean(i0 == i1) > 0.98
+
+
+@pytest.mark.parametrize("n,nq,k,foreign", [(33333, 4, 256, 0), (50001, 3, 1024, 0), (40007, 4, 128, 2)])
+def test_mixed_8_4_tiles_on_the_tensor_core_kernel(n, nq, k, foreign):
+    # mixed 8/4 tiles (8-bit head group + seven INT4 groups, last eight dims dropped), a ragged last
+    # set, some WARM tiles; with `foreign` a stretch of NF4 tiles sits inside the mixed launch, whose
+    # work items the tensor-core kernel hands back to the generic kernel
+    tiles = H.random_tiles(n, 3, seed=n, warm_every=7)
+    if foreign:
+        other = H.random_tiles(512, foreign, seed=n + 1)
+        tiles[20000:20512] = other
+    qc, qs = H.random_queries(nq, n + 2)
+    qc[1 % nq, :8] *= 30.0  # weight on the 8-bit head dims
+    segs = [(0, n, 0, nq, 5)]
+    dt = S.to_device(tiles)
+    gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, nq, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
