@@ -420,11 +420,12 @@ int32_t slha_b200_pool_score_topk(SlhaB200Pool* pool, const float* q_coarse, con
         const uint32_t cm = pl->codec_mask;
         const bool known = !(cm & 0x80000000u);
         const bool mixed_only = known && cm == (1u << SLHA_CODEC_MIXED);
+        const bool tq3_only = known && cm == (1u << SLHA_CODEC_TQ3);
         const uint32_t nibble = (1u << SLHA_CODEC_INT4_SINGLE) | (1u << SLHA_CODEC_INT4_GROUPED) | (1u << SLHA_CODEC_NF4) | (1u << 6);
         SLHA_TRY(score_topk_device(c, reinterpret_cast<const SciRustSlhaTile*>(pl->dev.tiles), pl->dev.state, &seg, 1,
                                    dq, ds, nq, k, (uint32_t*)outs[0].dev, (float*)outs[1].dev,
-                                   (uint32_t*)outs[2].dev, /*prefer_generic=*/known && cm && !(cm & nibble) && !mixed_only,
-                                   known ? (int)(((cm >> SLHA_CODEC_NF4) & 1u) | (mixed_only ? 2u : 0u)) : -1));
+                                   (uint32_t*)outs[2].dev, /*prefer_generic=*/known && cm && !(cm & nibble) && !mixed_only && !tq3_only,
+                                   known ? (int)(((cm >> SLHA_CODEC_NF4) & 1u) | (mixed_only ? 2u : 0u) | (tq3_only ? 4u : 0u)) : -1));
         return finish_outputs(c, outs, sync_by_default(c));
     });
 }

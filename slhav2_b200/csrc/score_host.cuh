@@ -116,6 +116,7 @@ struct Plan {
     bool use_mma = false;
     bool nf4_table = true;
     bool mixed = false;
+    bool tq3 = false;
     int codec_hint_in = -1;
     int mma_threads = 256;
     uint32_t mma_cap = 0, mma_grid = 0;
@@ -181,9 +182,11 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
         // Codec hint: the flags of the first tile of the first non-empty segment decide
         // whether the NF4 table occupies shared memory.  A wrong hint costs speed only
         // (NF4 tiles met without the table are handed to the generic kernel).
-        // (hint: -1 = look at the first tile, else bit 0 = NF4 tiles expected, bit 1 = mixed 8/4 tiles only)
+        // (hint: -1 = look at the first tile, else bit 0 = NF4 tiles expected, bit 1 = mixed 8/4 tiles only,
+        //  bit 2 = TQ3 tiles only)
         p->nf4_table = codec_hint < 0 || (codec_hint & 1);
         p->mixed = codec_hint > 0 && (codec_hint & 2);
+        p->tq3 = codec_hint > 0 && (codec_hint & 4);
         for (size_t i = 0; i < n_segs && codec_hint < 0; ++i)
             if (segs[i].n_tiles) {
                 uint16_t flags = 0;
@@ -192,6 +195,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
                 SLHA_CUDA(cudaStreamSynchronize(c->stream));
                 p->nf4_table = (flags & F_NF4) != 0;
                 p->mixed = (flags & F_MIXED) != 0;
+                p->tq3 = (flags & F_TQ3) != 0;
                 break;
             }
         // per query: one region per warp, so a multiple of the warp count (256 covers 8 and 16 warps)
@@ -407,14 +411,17 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.cand_cnt = p->d_cand_cnt;
         static thread_local bool mma_configured[16] = {false};  // the attribute is per device
         if (!mma_configured[c->device & 15]) {
-            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
             mma_configured[c->device & 15] = true;
         }
-        if (p->mixed)
-            score_mma_kernel<true, true><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a);
+        if (p->tq3)
+            score_mma_kernel<true, 2><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a);
+        else if (p->mixed)
+            score_mma_kernel<true, 1><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a);
         else
-            score_mma_kernel<true, false><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a);
+            score_mma_kernel<true, 0><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a);
         count_launch();
         SLHA_CUDA(cudaGetLastError());
     }

@@ -121,6 +121,38 @@ __device__ __forceinline__ void cp_async16_s(uint32_t dst, const unsigned char* 
     asm volatile("cp.async.cg.shared.global [%0+%1], [%2+%3], 16, %4;\n" ::"r"(dst), "n"(DST_IMM), "l"(src), "n"(SRC_IMM),
                  "r"(src_bytes));
 }
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+// TQ3 rows of a staged 16-tile set, rewritten in place as nibble rows: nibble d of the 64 latent
+// bytes becomes 2 code_d + correction_d (codes: 3 bits at bit 3d of bytes 0..47; correction bits:
+// bit d of bytes 48..63, zero once the correction plane has been dropped).  A lane rewrites half a
+// row (64 dims: 24 code bytes and 8 correction bytes in, 32 bytes out); every lane reads before
+// any lane writes.
+__device__ __forceinline__ void tq3_to_nibbles(uint32_t set_s, int lane) {
+    const uint32_t h = (uint32_t)lane & 1u, row = set_s + (uint32_t)(lane >> 1) * MMA_ROW;
+    const uint2 c0 = lds_v2<0>(row + 24u * h), c1 = lds_v2<8>(row + 24u * h), c2 = lds_v2<16>(row + 24u * h);
+    const uint2 cr = lds_v2<48>(row + 8u * h);
+    __syncwarp();
+    const uint32_t w[7] = {c0.x, c0.y, c1.x, c1.y, c2.x, c2.y, 0u};
+    uint32_t o[8];
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+        const int wi = (24 * m) >> 5, sh = (24 * m) & 31;
+        uint32_t x = __funnelshift_r(w[wi], w[wi + 1], sh) & 0xFFFFFFu;
+        x = (x & 0xFFFu) | ((x & 0xFFF000u) << 4);
+        x = (x & 0x003F003Fu) | ((x & 0x0FC00FC0u) << 2);
+        x = (x & 0x07070707u) | ((x & 0x38383838u) << 1);
+        uint32_t c = ((m < 4 ? cr.x : cr.y) >> (8 * (m & 3))) & 0xFFu;
+        c = (c | (c << 12)) & 0x000F000Fu;
+        c = (c | (c << 6)) & 0x03030303u;
+        c = (c | (c << 3)) & 0x11111111u;
+        o[m] = (x << 1) | c;
+    }
+    sts_v4(row + 32u * h, o[0], o[1], o[2], o[3]);
+    sts_v4(row + 32u * h + 16u, o[4], o[5], o[6], o[7]);
+    __syncwarp();
+}
 __device__ __forceinline__ int popc8(const uint4& a, const uint4& b, const uint32_t (&q)[8]) {
     return __popc(a.x ^ q[0]) + __popc(a.y ^ q[1]) + __popc(a.z ^ q[2]) + __popc(a.w ^ q[3]) +
            __popc(b.x ^ q[4]) + __popc(b.y ^ q[5]) + __popc(b.z ^ q[6]) + __popc(b.w ^ q[7]);
@@ -956,9 +988,10 @@ __device__ __noinline__ int mma_settle(const ScoreArgs& a, const MmaItem& m, int
     return rc;
 }
 
-// MIXED: the launch scores mixed 8/4 tiles (a separate instantiation, so that the nibble-codec
-// kernel is exactly the code it was without it).
-template <bool TOPK, bool MIXED = false>
+// KIND 0: nibble codecs (INT4, MX-INT4, NF4); 1: the launch scores mixed 8/4 tiles; 2: TQ3 tiles,
+// rewritten in shared memory as nibble rows (2 code + correction bit) before the INT4 path scores
+// them.  Separate instantiations, so that the nibble-codec kernel is exactly the code it was.
+template <bool TOPK, int KIND = 0>
 __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -1022,6 +1055,7 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
         // {2t, 2t+1, 2t+8, 2t+9} of group j carry dims 16j + 4t + {0,1,2,3}
         uint32_t bq[8][2];
         uint32_t qs[8];
+        uint32_t bE = 0;
         bool big = false;
         {
             const int qi = g >> 1;
@@ -1031,9 +1065,9 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
             for (int j = 0; j < 8; ++j) {
                 // mixed 8/4 tiles: group 0 = dims 2t, 2t+1 (8-bit levels, plain in both slots, so
                 // both carry 16x the query), groups 1..7 = INT4 groups of dims 16 j - 8 ..
-                const int dim0 = !MIXED ? 16 * j + 4 * t : (j == 0 ? 0 : 16 * j - 8 + 4 * t);
+                const int dim0 = !(KIND == 1) ? 16 * j + 4 * t : (j == 0 ? 0 : 16 * j - 8 + 4 * t);
                 float4 x = *reinterpret_cast<const float4*>(q + dim0);
-                if (MIXED && j == 0) {
+                if (KIND == 1 && j == 0) {
                     const float2 y = *reinterpret_cast<const float2*>(q + 2 * t);
                     x = make_float4(y.x, 16.0f * y.y, 0.0f, 0.0f);
                 }
@@ -1041,12 +1075,25 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     if (!have) v[i] = 0.0f;
-                    big |= fabsf(v[i]) > (MIXED && j == 0 && i == 1 ? 64000.0f : 4000.0f);  // 16 v must stay inside fp16
+                    big |= fabsf(v[i]) > (KIND == 1 && j == 0 && i == 1 ? 64000.0f : 4000.0f);  // 16 v must stay inside fp16
                     if (!(i & 1)) v[i] *= 16.0f;             // even slots carry 16x the query (see int4_quad)
                     if (g & 1) v[i] = half_residual(v[i]);
                 }
                 bq[j][0] = pack_half2(v[0], v[1]);
                 bq[j][1] = pack_half2(v[2], v[3]);
+            }
+            if (KIND == 2) {
+                // B fragment of the group sums: k slots 2t and 2t+1 = groups 2t and 2t+1 of query g>>1
+                float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    s0 += q[32 * t + i];
+                    s1 += q[32 * t + 16 + i];
+                }
+                if (!have) s0 = s1 = 0.0f;
+                big |= fabsf(s0) > 60000.0f || fabsf(s1) > 60000.0f;
+                if (g & 1) { s0 = half_residual(s0); s1 = half_residual(s1); }
+                bE = pack_half2(s0, s1);
             }
             // sign words of query t (the query whose scores this thread finishes)
 #pragma unroll
@@ -1139,15 +1186,30 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
             // a launch arranged for mixed 8/4 tiles takes nothing else (rows past the end of a ragged
             // last set are zero-filled and their scores dropped, so they count as mixed)
             const uint32_t row0 = s * MMA_SET_TILES + (uint32_t)g;
-            const bool all_mixed = MIXED && (__reduce_and_sync(0xFFFFFFFFu, (row0 < n ? f0 : F_MIXED) & (row0 + 8 < n ? f1 : F_MIXED)) & F_MIXED);
-            if ((fo & (F_TQ3 | F_MIX3)) || ((fo & F_MIXED) && !all_mixed) || (MIXED && !all_mixed) ||
-                ((fo & F_NF4) && !a.nf4_table)) {
+            const bool all_mixed = KIND == 1 && (__reduce_and_sync(0xFFFFFFFFu, (row0 < n ? f0 : F_MIXED) & (row0 + 8 < n ? f1 : F_MIXED)) & F_MIXED);
+            const bool all_tq3 = KIND == 2 && (__reduce_and_sync(0xFFFFFFFFu, (row0 < n ? f0 : F_TQ3) & (row0 + 8 < n ? f1 : F_TQ3)) & F_TQ3);
+            if ((fo & F_MIX3) || ((fo & F_TQ3) && !all_tq3) || (KIND == 2 && !all_tq3) ||
+                ((fo & F_MIXED) && !all_mixed) || (KIND == 1 && !all_mixed) || ((fo & F_NF4) && !a.nf4_table)) {
                 if (lane == 0) bail[0] = 1;  // a codec this kernel does not decode: hand the item back
                 break;
             }
             float acc0, acc1;
             const uint32_t hb = rb + 2u * (uint32_t)t;
-            if (MIXED) {  // (all_mixed holds here)
+            if (KIND == 2) {  // (all_tq3 holds here)
+                tq3_to_nibbles(rb - row_lane, lane);
+                coarse_set<0>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+                // level = (2 nibble - 15) / 4, or (2 nibble - 14) / 4 without the correction plane:
+                // beside the nibble sums X the score needs 8 c sum_g gs_g Q_g (c = 1 or 2, Q_g = the
+                // query's sum over group g), one more MMA with the scale bytes as the A operand
+                const uint32_t sel = (t & 1) ? 0x7352u : 0x7150u;
+                uint32_t ga0, ga1;
+                asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(ga0) : "r"(prmt(t < 2 ? x0.z : x0.w, magic, sel)), "r"(0xE400E400u));
+                asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(ga1) : "r"(prmt(t < 2 ? x1.z : x1.w, magic, sel)), "r"(0xE400E400u));
+                float e[4];
+                mma_f16_zero(e, ga0, ga1, 0u, 0u, bE, 0u);
+                acc0 = fmaf((f0 & F_NOCORR) ? 16.0f : 8.0f, e[0] + e[1], acc0);
+                acc1 = fmaf((f1 & F_NOCORR) ? 16.0f : 8.0f, e[2] + e[3], acc1);
+            } else if (KIND == 1) {  // (all_mixed holds here)
                 coarse_set<3>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
             } else if (!(fo & F_NF4)) {
                 coarse_set<0>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
@@ -1161,8 +1223,9 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
             const int h1 = popc8(lds_v4<64 + MMA_HALF>(rb), lds_v4<80 + MMA_HALF>(rb), qs);
             const float lam0 = (f0 & F_WARM) ? 0.0f : __uint_as_float(m0.y);
             const float lam1 = (f1 & F_WARM) ? 0.0f : __uint_as_float(m1.y);
-            const float sc0 = fmaf(acc0, __uint_as_float(m0.x) * (1.0f / 4080.0f), lam0 * (float)(256 - 2 * h0));
-            const float sc1 = fmaf(acc1, __uint_as_float(m1.x) * (1.0f / 4080.0f), lam1 * (float)(256 - 2 * h1));
+            constexpr float unit = KIND == 2 ? 1.0f / 8160.0f : 1.0f / 4080.0f;  // 1 / (255 x 16 [x 2])
+            const float sc0 = fmaf(acc0, __uint_as_float(m0.x) * unit, lam0 * (float)(256 - 2 * h0));
+            const float sc1 = fmaf(acc1, __uint_as_float(m1.x) * unit, lam1 * (float)(256 - 2 * h1));
             const uint32_t t0 = s * MMA_SET_TILES + (uint32_t)g, t1 = t0 + 8;
             bool live0 = mine && t0 < n, live1 = mine && t1 < n;
             if (sbase) {

@@ -211,3 +211,19 @@ def test_mixed_8_4_tiles_on_the_tensor_core_kernel(n, nq, k, foreign):
     dt = S.to_device(tiles)
     gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, nq, k)
     check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+
+
+@pytest.mark.parametrize("n,nq,k,nocorr_every,foreign", [(33335, 4, 256, 0, None), (50001, 3, 1024, 5, None), (40007, 4, 128, 3, 2)])
+def test_tq3_tiles_on_the_tensor_core_kernel(n, nq, k, nocorr_every, foreign):
+    # TQ3 tiles are rewritten as nibble rows in shared memory and scored by the INT4 path plus one
+    # MMA for the half-level offset; ragged last set, WARM tiles, tiles whose correction plane was
+    # dropped (NOCORR), and with `foreign` a stretch of NF4 tiles that is handed back
+    tiles = H.random_tiles(n, 4, seed=n, warm_every=11, nocorr_every=nocorr_every)
+    if foreign:
+        tiles[16000:16640] = H.random_tiles(640, foreign, seed=n + 1)
+    qc, qs = H.random_queries(nq, n + 2)
+    qc[0] += 0.75  # a query with a large sum over every group weighs the half-level offset
+    segs = [(0, n, 0, nq, 9)]
+    dt = S.to_device(tiles)
+    gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, nq, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
