@@ -121,7 +121,15 @@ struct Plan {
     int mma_threads = 256;
     uint32_t mma_cap = 0, mma_grid = 0;
     size_t mma_smem = 0;
-    DevBuf b_items, b_qbegin, b_qcount, b_keys, b_cnt, b_retry, b_cta, b_gpivot;
+    DevBuf b_items, b_qbegin, b_qcount, b_keys, b_cnt, b_retry, b_cta, b_gpivot, b_vq, b_tmp;
+    // Two-level merge for calls with few queries and many candidate lists per query (a pool scored
+    // by one GQA group: 148 lists each): groups of `group_parts` lists are merged by a CTA each into
+    // `n_groups` intermediate (index, score) lists per query, which a second launch merges.
+    uint32_t n_groups = 0, group_parts = 0;
+    uint32_t* d_vq_begin = nullptr;
+    uint32_t* d_vq_count = nullptr;
+    uint32_t* d_tmp_index = nullptr;
+    float* d_tmp_score = nullptr;
     uint64_t last_use = 0;
 };
 
@@ -309,6 +317,28 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     p->n_items = (uint32_t)all.size();
     // (pageable sources: cudaMemcpyAsync returns once they are staged, so the vectors may die)
     SLHA_CUDA(cudaMemcpyAsync(p->d_cta_begin, cta_begin.data(), cta_begin.size() * 4, cudaMemcpyHostToDevice, c->stream));
+    p->n_groups = 0;
+    if (nq <= 64 && p->max_parts >= 24) {
+        uint32_t G = 1;
+        while (G * G < p->max_parts) ++G;
+        const uint32_t ng = (p->max_parts + G - 1) / G;
+        std::vector<uint32_t> vq(2 * (size_t)ng * nq);
+        for (uint32_t g = 0; g < ng; ++g)
+            for (size_t Q = 0; Q < nq; ++Q) {
+                const uint32_t parts = q_count[Q], lo = g * G;
+                vq[g * nq + Q] = q_begin[Q] + lo * q_stride[Q];
+                vq[(size_t)ng * nq + g * nq + Q] = (parts > lo ? std::min(G, parts - lo) : 0u) | (q_stride[Q] << 24);
+            }
+        SLHA_TRY(p->b_vq.ensure(vq.size() * 4));
+        SLHA_TRY(p->b_tmp.ensure((size_t)ng * nq * k * 8));
+        p->d_vq_begin = (uint32_t*)p->b_vq.p;
+        p->d_vq_count = p->d_vq_begin + (size_t)ng * nq;
+        p->d_tmp_index = (uint32_t*)p->b_tmp.p;
+        p->d_tmp_score = reinterpret_cast<float*>(p->d_tmp_index + (size_t)ng * nq * k);
+        SLHA_CUDA(cudaMemcpyAsync(p->d_vq_begin, vq.data(), vq.size() * 4, cudaMemcpyHostToDevice, c->stream));
+        p->n_groups = ng;
+        p->group_parts = G;
+    }
     for (size_t Q = 0; Q < nq; ++Q) q_count[Q] |= q_stride[Q] << 24;
     SLHA_CUDA(cudaMemcpyAsync(p->d_items, all.data(), all.size() * sizeof(WorkItem), cudaMemcpyHostToDevice, c->stream));
     SLHA_CUDA(cudaMemcpyAsync(p->d_q_list_begin, q_begin.data(), nq * 4, cudaMemcpyHostToDevice, c->stream));
@@ -441,15 +471,30 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         SLHA_TRY(launch_score<true>(c, cl.G, a, cl.count, p->threads, score_smem_bytes(cl.G, nwarps, true, p->cap)));
     }
     if (timed) SLHA_CUDA(cudaEventRecord(tev[1], c->stream));
-    CompLists L{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, p->list_cap};
-    const uint32_t cap_s = merge_cap((uint64_t)p->max_parts * p->list_cap, p->kp2, k);
-    const size_t smem = merge_smem(cap_s, p->kp2);
     static thread_local bool configured[16] = {false};  // the attribute is per device
     if (!configured[c->device & 15]) {
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<CompLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+        SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
         configured[c->device & 15] = true;
     }
-    topk_merge_kernel<CompLists><<<(uint32_t)nq, merge_threads(cap_s), smem, c->stream>>>(L, k, p->kp2, cap_s, d_out_index, d_out_score, d_out_count);
+    if (p->n_groups) {
+        // few queries, many lists each: groups of lists first, then the groups' results
+        CompLists L1{p->d_cand_keys, p->d_cand_cnt, p->d_vq_begin, p->d_vq_count, p->list_cap};
+        const uint32_t cap1 = merge_cap((uint64_t)p->group_parts * p->list_cap, p->kp2, k);
+        topk_merge_kernel<CompLists><<<p->n_groups * (uint32_t)nq, merge_threads(cap1), merge_smem(cap1, p->kp2), c->stream>>>(
+            L1, k, p->kp2, cap1, p->d_tmp_index, p->d_tmp_score, nullptr);
+        count_launch();
+        SLHA_CUDA(cudaGetLastError());
+        PairLists L2{p->d_tmp_index, p->d_tmp_score, p->n_groups, (uint32_t)nq, k, (uint64_t)nq * k};
+        const uint32_t cap2 = merge_cap((uint64_t)p->n_groups * k, p->kp2, k);
+        topk_merge_kernel<PairLists><<<(uint32_t)nq, merge_threads(cap2), merge_smem(cap2, p->kp2), c->stream>>>(
+            L2, k, p->kp2, cap2, d_out_index, d_out_score, d_out_count);
+    } else {
+        CompLists L{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, p->list_cap};
+        const uint32_t cap_s = merge_cap((uint64_t)p->max_parts * p->list_cap, p->kp2, k);
+        topk_merge_kernel<CompLists><<<(uint32_t)nq, merge_threads(cap_s), merge_smem(cap_s, p->kp2), c->stream>>>(
+            L, k, p->kp2, cap_s, d_out_index, d_out_score, d_out_count);
+    }
     count_launch();
     SLHA_CUDA(cudaGetLastError());
     if (timed) {
