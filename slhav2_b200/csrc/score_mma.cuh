@@ -991,7 +991,11 @@ __device__ __noinline__ int mma_settle(const ScoreArgs& a, const MmaItem& m, int
 // KIND 0: nibble codecs (INT4, MX-INT4, NF4); 1: the launch scores mixed 8/4 tiles; 2: TQ3 tiles,
 // rewritten in shared memory as nibble rows (2 code + correction bit) before the INT4 path scores
 // them.  Separate instantiations, so that the nibble-codec kernel is exactly the code it was.
-template <bool TOPK, int KIND = 0>
+// EARLY: many CTAs share every query (one long segment cut over the whole grid).  After one set
+// of every warp the query's shared histogram already holds far more than k candidates, so four
+// warps per CTA fetch a first threshold after their 2nd..5th set instead of waiting for their
+// regions to fill, which they would all do at the same moment.
+template <bool TOPK, int KIND = 0, bool EARLY = false>
 __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -1298,7 +1302,7 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
                 if (*reinterpret_cast<volatile int*>(ctl)) {
                     rendezvous();
                     if (bail[0]) break;
-                } else if ((++polls & 63u) == (uint32_t)(warp >> 2) * 16u + 8u) {
+                } else if ((++polls & 63u) == (uint32_t)(warp >> 2) * 16u + 8u || (EARLY && polls == 2u + (uint32_t)(warp >> 2))) {
                     // in turn, a warp raises the threshold of query (warp & 3)
                     if ((warp & 3) < nq) mma_hist_pivot(a, m, warp & 3, lane);
                     if ((warp & 3) == 0) mma_refresh_pivots(a, m, lane);
