@@ -129,7 +129,9 @@ __device__ __forceinline__ bool is_pinned(const PoolDev& p, uint32_t pos, uint32
     return p.recent_window && (max_pos - pos) < p.recent_window;
 }
 
-// candidate key + bytes freed, per slot, for one phase
+// candidate (key, slot) pairs of one phase, compacted in arbitrary order (keys are unique, so the
+// sort that follows gives one order): only the slots a phase can act on are sorted, e.g. the few
+// HOT tiles just appended for the page-out phase.  n_cand is zero when the kernel starts.
 __global__ void phase_build_kernel(PoolDev p, int phase, uint64_t* keys, uint32_t* vals) {
     const uint64_t len = p.cnt->len;
     const bool over = p.cnt->live > p.cnt->budget;
@@ -138,9 +140,12 @@ __global__ void phase_build_kernel(PoolDev p, int phase, uint64_t* keys, uint32_
         p.cnt->phase_applied = 0;
     }
     const uint32_t max_pos = p.cnt->max_pos;
-    for (uint64_t s = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; s < len; s += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    const uint64_t rounds = over ? (len + stride - 1) / stride : 0;  // whole warps stay together for the ballot
+    for (uint64_t r = 0; r < rounds; ++r) {
+        const uint64_t s = r * stride + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
         uint64_t key = SENTINEL;
-        if (over) {
+        if (s < len) {
             const uint8_t st = p.state[s];
             const unsigned char* t = p.tiles + s * TILE_BYTES;
             const uint32_t flags = *reinterpret_cast<const uint16_t*>(t + 118);
@@ -169,14 +174,24 @@ __global__ void phase_build_kernel(PoolDev p, int phase, uint64_t* keys, uint32_
                 }
             }
         }
-        keys[s] = key;
-        vals[s] = (uint32_t)s;
+        const unsigned hit = __ballot_sync(0xFFFFFFFFu, key != SENTINEL);
+        if (hit) {
+            const int lane = threadIdx.x & 31;
+            uint32_t base = 0;
+            if (lane == 0) base = atomicAdd(&p.cnt->n_cand, (uint32_t)__popc(hit));
+            base = __shfl_sync(0xFFFFFFFFu, base, 0);
+            if (key != SENTINEL) {
+                const uint32_t i = base + (uint32_t)__popc(hit & ((1u << lane) - 1u));
+                keys[i] = key;
+                vals[i] = (uint32_t)s;
+            }
+        }
     }
 }
 
 __global__ void phase_weights_kernel(PoolDev p, int phase, const uint64_t* keys_sorted,
                                      const uint32_t* slots_sorted, uint32_t* w) {
-    const uint64_t len = p.cnt->len;
+    const uint64_t len = p.cnt->n_cand;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += (uint64_t)gridDim.x * blockDim.x) {
         uint32_t bytes = 0;
         if (keys_sorted[i] != SENTINEL) {
@@ -196,7 +211,7 @@ __global__ void phase_weights_kernel(PoolDev p, int phase, const uint64_t* keys_
 __global__ void phase_apply_kernel(PoolDev p, int phase, const uint64_t* keys_sorted,
                                    const uint32_t* slots_sorted, const uint32_t* w,
                                    const uint64_t* excl) {
-    const uint64_t len = p.cnt->len;
+    const uint64_t len = p.cnt->n_cand;
     const uint64_t deficit = p.cnt->phase_deficit;
     const uint64_t free0 = p.cnt->free_len;
     int64_t delta = 0;
@@ -484,15 +499,24 @@ Status pool_enforce_budget(Ctx* c, Pool* pl, int32_t* within) {
     const int phases[5] = {PH_CORR_HOT, PH_PAGE, PH_CORR_WARM, PH_EVICT, PH_EVICT_PINNED};
     for (int ph : phases) {
         if (ph == PH_EVICT_PINNED && pl->cfg.evict_policy != SLHA_B200_EVICT_IMPORTANCE) continue;
+        SLHA_CUDA(cudaMemsetAsync(&pl->dev.cnt->n_cand, 0, 4, c->stream));
         phase_build_kernel<<<grid, 256, 0, c->stream>>>(pl->dev, ph, keys, vals);
+        count_launch();
+        SLHA_CUDA(cudaGetLastError());
+        // the host needs the candidate count for the sort (and learns whether the budget is met)
+        SLHA_TRY(pool_sync_counters(c, pl));
+        if (pl->h_cnt.live <= pl->h_cnt.budget) break;
+        const int nc = (int)pl->h_cnt.n_cand;
+        if (nc == 0) continue;
+        const uint32_t cgrid = grid_for((uint64_t)nc);
         size_t tb = tmp_bytes;
-        SLHA_CUDA(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys_s, vals, vals_s, (int)len, 0, 64, c->stream));
-        phase_weights_kernel<<<grid, 256, 0, c->stream>>>(pl->dev, ph, keys_s, vals_s, w);
+        SLHA_CUDA(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys_s, vals, vals_s, nc, 0, 64, c->stream));
+        phase_weights_kernel<<<cgrid, 256, 0, c->stream>>>(pl->dev, ph, keys_s, vals_s, w);
         tb = tmp_bytes;
-        SLHA_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tb, w, excl, (int)len, c->stream));
-        phase_apply_kernel<<<grid, 256, 0, c->stream>>>(pl->dev, ph, keys_s, vals_s, w, excl);
+        SLHA_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tb, w, excl, nc, c->stream));
+        phase_apply_kernel<<<cgrid, 256, 0, c->stream>>>(pl->dev, ph, keys_s, vals_s, w, excl);
         phase_commit_kernel<<<1, 1, 0, c->stream>>>(pl->dev);
-        count_launch(4);
+        count_launch(3);
         SLHA_CUDA(cudaGetLastError());
     }
     SLHA_TRY(pool_sync_counters(c, pl));

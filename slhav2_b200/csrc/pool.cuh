@@ -17,7 +17,7 @@ struct PoolCounters {
     uint64_t phase_applied;
     int64_t live_delta;
     uint32_t max_pos;
-    uint32_t pad;
+    uint32_t n_cand;     // candidates of the enforce_budget phase being built
 };
 
 struct PoolDev {
