@@ -11,6 +11,7 @@
 // reference's sequential loop would have reached.
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
+#include <vector>
 
 #include "common.cuh"
 #include "pool.cuh"
@@ -188,6 +189,48 @@ __global__ void phase_build_kernel(PoolDev p, int phase, uint64_t* keys, uint32_
         }
     }
 }
+
+// Pre-filter of a long candidate list: a phase stops once the bytes it has freed reach the deficit,
+// and every operation of a phase frees at least `min_freed` bytes (14 for a dropped correction
+// plane, 32 for a page-out, 80 for an eviction), so only the M = deficit / min_freed + 1 smallest
+// keys can be reached.  A histogram over the keys' 12 high bits gives the smallest bin prefix that
+// holds M candidates; only those candidates are sorted.
+constexpr uint32_t PREFILTER_BINS = 4096, PREFILTER_MIN = 65536;
+__global__ void phase_hist_kernel(PoolDev p, const uint64_t* keys, uint32_t* hist) {
+    __shared__ uint32_t h[PREFILTER_BINS];
+    for (uint32_t b = threadIdx.x; b < PREFILTER_BINS; b += blockDim.x) h[b] = 0;
+    __syncthreads();
+    const uint64_t n = p.cnt->n_cand;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        atomicAdd(&h[(uint32_t)(keys[i] >> 52)], 1u);
+    __syncthreads();
+    for (uint32_t b = threadIdx.x; b < PREFILTER_BINS; b += blockDim.x)
+        if (h[b]) atomicAdd(&hist[b], h[b]);
+}
+// keeps the candidates whose bin is at most `last_bin`; n_cand becomes their number (out_n, then copied)
+__global__ void phase_filter_kernel(PoolDev p, const uint64_t* keys, const uint32_t* vals, uint32_t last_bin,
+                                    uint64_t* keys_out, uint32_t* vals_out, uint32_t* out_n) {
+    const uint64_t n = p.cnt->n_cand;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    const uint64_t rounds = (n + stride - 1) / stride;
+    for (uint64_t r = 0; r < rounds; ++r) {
+        const uint64_t i = r * stride + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+        const bool keep = i < n && (uint32_t)(keys[i] >> 52) <= last_bin;
+        const unsigned hit = __ballot_sync(0xFFFFFFFFu, keep);
+        if (hit) {
+            const int lane = threadIdx.x & 31;
+            uint32_t base = 0;
+            if (lane == 0) base = atomicAdd(out_n, (uint32_t)__popc(hit));
+            base = __shfl_sync(0xFFFFFFFFu, base, 0);
+            if (keep) {
+                const uint32_t o = base + (uint32_t)__popc(hit & ((1u << lane) - 1u));
+                keys_out[o] = keys[i];
+                vals_out[o] = vals[i];
+            }
+        }
+    }
+}
+__global__ void phase_set_ncand_kernel(PoolDev p, const uint32_t* n) { p.cnt->n_cand = *n; }
 
 __global__ void phase_weights_kernel(PoolDev p, int phase, const uint64_t* keys_sorted,
                                      const uint32_t* slots_sorted, uint32_t* w) {
@@ -506,11 +549,41 @@ Status pool_enforce_budget(Ctx* c, Pool* pl, int32_t* within) {
         // the host needs the candidate count for the sort (and learns whether the budget is met)
         SLHA_TRY(pool_sync_counters(c, pl));
         if (pl->h_cnt.live <= pl->h_cnt.budget) break;
-        const int nc = (int)pl->h_cnt.n_cand;
+        int nc = (int)pl->h_cnt.n_cand;
         if (nc == 0) continue;
+        uint64_t* keys_in = keys;
+        uint32_t* vals_in = vals;
+        if ((uint32_t)nc >= PREFILTER_MIN) {
+            // only the smallest keys can be reached before the deficit is covered (see phase_hist_kernel)
+            const uint64_t min_freed = ph == PH_PAGE ? 32 : (ph >= PH_EVICT ? 80 : 14);
+            const uint64_t reach = (pl->h_cnt.live - pl->h_cnt.budget) / min_freed + 1;
+            uint32_t* d_hist = reinterpret_cast<uint32_t*>(excl);  // (free until the scan; 8 bytes x len >= 16 KB + 4 here)
+            SLHA_CUDA(cudaMemsetAsync(d_hist, 0, (PREFILTER_BINS + 1) * 4, c->stream));
+            phase_hist_kernel<<<grid_for((uint64_t)nc), 256, 0, c->stream>>>(pl->dev, keys, d_hist);
+            std::vector<uint32_t> hh(PREFILTER_BINS);
+            SLHA_CUDA(cudaMemcpyAsync(hh.data(), d_hist, PREFILTER_BINS * 4, cudaMemcpyDeviceToHost, c->stream));
+            SLHA_CUDA(cudaStreamSynchronize(c->stream));
+            uint64_t cum = 0;
+            uint32_t last = PREFILTER_BINS - 1;
+            for (uint32_t b = 0; b < PREFILTER_BINS; ++b) {
+                cum += hh[b];
+                if (cum >= reach) { last = b; break; }
+            }
+            if (cum < (uint64_t)nc) {  // the filter drops something: compact into the sorted-side buffers, sort back
+                phase_filter_kernel<<<grid_for((uint64_t)nc), 256, 0, c->stream>>>(pl->dev, keys, vals, last, keys_s, vals_s, d_hist + PREFILTER_BINS);
+                phase_set_ncand_kernel<<<1, 1, 0, c->stream>>>(pl->dev, d_hist + PREFILTER_BINS);
+                count_launch(3);
+                SLHA_CUDA(cudaGetLastError());
+                nc = (int)cum;
+                std::swap(keys, keys_s);
+                std::swap(vals, vals_s);
+                keys_in = keys;
+                vals_in = vals;
+            }
+        }
         const uint32_t cgrid = grid_for((uint64_t)nc);
         size_t tb = tmp_bytes;
-        SLHA_CUDA(cub::DeviceRadixSort::SortPairs(tmp, tb, keys, keys_s, vals, vals_s, nc, 0, 64, c->stream));
+        SLHA_CUDA(cub::DeviceRadixSort::SortPairs(tmp, tb, keys_in, keys_s, vals_in, vals_s, nc, 0, 64, c->stream));
         phase_weights_kernel<<<cgrid, 256, 0, c->stream>>>(pl->dev, ph, keys_s, vals_s, w);
         tb = tmp_bytes;
         SLHA_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tb, w, excl, nc, c->stream));
