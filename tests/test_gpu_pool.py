@@ -139,3 +139,32 @@ def test_append_keys_encodes_into_the_pool():
     with pytest.raises(S.SlhaError) as e:
         pool.append_keys(gm, np.tile(keys, (2, 1)), S.CODEC_MIXED)
     assert e.value.code == S.ERR_CAPACITY
+
+
+@pytest.mark.parametrize("codec,page", [(4, 0), (3, 1)])
+def test_large_pool_enforce_budget_with_long_candidate_lists(codec, page):
+    # phases with tens of thousands of candidates: the pool compacts them and sorts only those that can
+    # be reached before the deficit is covered; states, free-list order (slot reuse) and byte accounting
+    # must still equal the oracle's full ordered walk.  First a large deficit (everything is paged, many
+    # tiles evicted), then small deficits after a few more inserts (a handful of operations per phase).
+    n = 90000
+    budget = int(0.6 * 128 * n)
+    pool = S.TilePool(n + 512, budget, page, S.EVICT_IMPORTANCE, 4, 64)
+    cache = ora.Cache(budget, page, 1, 4, 64)
+    tiles = H.random_tiles(n + 256, codec, seed=77 + codec)
+    tiles["position"] = np.arange(n + 256)
+    for b in range(0, n, 30000):
+        chunk = tiles[b:b + 30000]
+        assert list(pool.insert(chunk)) == [cache.insert(chunk[j:j + 1]) for j in range(len(chunk))]
+    live = np.arange(n, dtype=np.uint32)
+    sc = ora.Rng(5).gaussian(n) * 4
+    pool.observe_scores(live, sc, 0.9)
+    cache.observe_scores(live, sc, 0.9)
+    assert pool.enforce_budget() == cache.enforce_budget()
+    assert_same(pool, cache, 1e-3)  # (the oracle sums 90 000 softmax terms sequentially in f32, the pool in a tree)
+    for r in range(4):
+        more = tiles[n + 64 * r:n + 64 * (r + 1)]
+        assert list(pool.insert(more)) == [cache.insert(more[j:j + 1]) for j in range(64)]  # reuses evicted slots in LIFO order
+        assert pool.enforce_budget() == cache.enforce_budget()
+        assert pool.live_bytes() <= budget
+    assert_same(pool, cache, 1e-3)  # (the oracle sums 90 000 softmax terms sequentially in f32, the pool in a tree)
