@@ -542,6 +542,11 @@ Status pool_enforce_budget(Ctx* c, Pool* pl, int32_t* within) {
     const int phases[5] = {PH_CORR_HOT, PH_PAGE, PH_CORR_WARM, PH_EVICT, PH_EVICT_PINNED};
     for (int ph : phases) {
         if (ph == PH_EVICT_PINNED && pl->cfg.evict_policy != SLHA_B200_EVICT_IMPORTANCE) continue;
+        // a pool that has only ever been appended to with codecs without a correction plane (every
+        // codec but TQ3 and MIX3) has no candidate for the two correction phases: no scan for them
+        const uint32_t cm = pl->codec_mask;
+        const bool no_corr_planes = cm && !(cm & 0x80000000u) && !(cm & ((1u << SLHA_CODEC_TQ3) | (1u << SLHA_CODEC_MIX3)));
+        if (no_corr_planes && (ph == PH_CORR_HOT || ph == PH_CORR_WARM)) continue;
         SLHA_CUDA(cudaMemsetAsync(&pl->dev.cnt->n_cand, 0, 4, c->stream));
         phase_build_kernel<<<grid, 256, 0, c->stream>>>(pl->dev, ph, keys, vals);
         count_launch();
