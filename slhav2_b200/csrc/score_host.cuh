@@ -451,7 +451,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         }
         // eight or more CTAs per query (a long segment cut over the grid): first thresholds early (config 5: 0.329 -> 0.317 ms;
         // a 1 M-slot pool scored by one GQA group: 0.200 -> 0.114 ms)
-        const bool early = p->max_parts >= (uint32_t)env_int("SLHA_B200_EARLY_PARTS", 8) && env_int("SLHA_B200_EARLY", 1) != 0;
+        const bool early = p->max_parts >= 8;
         const int kind = p->tq3 ? 2 : (p->mixed ? 1 : 0);
 #define SLHA_LAUNCH_MMA(K, E) score_mma_kernel<true, K, E><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a)
         if (early) {
