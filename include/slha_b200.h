@@ -155,6 +155,12 @@ int32_t slha_b200_set_device(int32_t device);
 int32_t slha_b200_set_stream(void* cuda_stream);
 /* Kernels launched by this library in this process so far. */
 uint64_t slha_b200_launch_count(void);
+/* Checking aid, no counterpart in the reference: with on != 0 the calling
+ * thread's slha_b200_score_topk / slha_b200_pool_score_topk calls use only the
+ * generic CUDA-core scoring kernel (every codec) and never the tensor-core
+ * kernel, so that a test can require both to give the same answers.  The
+ * library reads no environment variable; this call is the only switch. */
+int32_t slha_b200_debug_force_generic_score(int32_t on);
 /* Device timing of the fused score + top-k path: after timing_begin, each of
  * the calling thread's next `max_calls` slha_b200_score_topk /
  * slha_b200_pool_score_topk calls records CUDA events on its stream around the
@@ -243,9 +249,10 @@ int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment
  *
  * Who needs it: code that runs where cudaMalloc is off limits -- a decode loop
  * inside a latency budget that cannot absorb an allocation (cudaMalloc takes
- * a device-wide lock and may synchronise), an inference server whose memory
+ * a device-wide lock and may synchronise), or an inference server whose memory
  * pool owns every byte of HBM so that a stray allocation fails or fragments
- * it, or a host thread that is forbidden to enter the allocator.  The regular
+ * it.  The promise is about DEVICE memory: the host side of the call still
+ * uses ordinary C++ (a small closure per call, error strings on failure).  The regular
  * entry point sizes its work lists and candidate buffers per call shape and
  * obtains them with cudaMalloc; this one keeps them in one fixed array that
  * lives inside the library.
@@ -254,10 +261,11 @@ int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment
  *  - tiles, q_coarse, q_sign and the three outputs must be device memory,
  *    segments must be host memory (nothing is staged);
  *  - limits of the fixed array (4 MiB + 22 KiB per GPU, held from library load
- *    until the process exits): k <= 1024, n_queries <= 256, at most 96
- *    segments (more may fit when they are short), 512 work items / candidate
- *    lists in total.  A call beyond them fails with SLHA_ERR_CAPACITY and says
- *    which limit it hit;
+ *    until the process exits): k <= 1024, n_queries <= 256, and at most 512
+ *    (segment, query) pairs over the non-empty segments; work items are sized
+ *    so that their candidate lists fit, whatever the segment lengths.  A call
+ *    beyond these limits fails with SLHA_ERR_CAPACITY and says which one it
+ *    hit; devices 0..15 only;
  *  - the first call on each device resolves the array's device address and
  *    raises the kernels' shared-memory limit; make that first call outside any
  *    stream capture;
@@ -265,7 +273,9 @@ int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment
  *    left in it; a call overwrites everything it later reads, so back-to-back
  *    calls on one stream are safe, but two calls that overlap on the GPU
  *    (different streams or threads without ordering) race on it.
- * It calls no cudaMalloc / cudaFree and no allocating library routine.
+ * It calls no cudaMalloc / cudaFree and no library routine that allocates
+ * device memory.  The segment table and query ranges are copied from ordinary
+ * (pageable) host arrays, so each call synchronises briefly with its stream.
  */
 int32_t slha_b200_score_topk_noalloc(const SciRustSlhaTile* tiles, const SlhaB200Segment* segments,
                                      size_t n_segments, const float* q_coarse, const uint64_t* q_sign,

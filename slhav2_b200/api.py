@@ -73,6 +73,7 @@ SIGNATURES = {
     "slha_b200_set_device": (_i32, [_i32]),
     "slha_b200_set_stream": (_i32, [_vp]),
     "slha_b200_launch_count": (_u64, []),
+    "slha_b200_debug_force_generic_score": (_i32, [_i32]),
     "slha_b200_timing_begin": (_i32, [_u32]),
     "slha_b200_timing_end": (_i32, [_vp, _vp, _u32, _vp]),
     "slha_b200_malloc": (_i32, [_sz, C.POINTER(_vp)]),
@@ -180,6 +181,11 @@ def launch_count():
     return load_library().slha_b200_launch_count()
 
 
+def debug_force_generic_score(on):
+    """Checking aid: the calling thread's score_topk calls use only the generic CUDA-core kernel."""
+    _check(load_library().slha_b200_debug_force_generic_score(1 if on else 0))
+
+
 def timing_begin(max_calls):
     _check(load_library().slha_b200_timing_begin(max_calls))
 
@@ -219,6 +225,11 @@ class DeviceBuffer:
         _check(load_library().slha_b200_memcpy(out.ctypes.data, self.address, out.nbytes))
         return out
 
+    def view(self, offset, nbytes):
+        """A window of this buffer (not owning; valid while the buffer lives)."""
+        assert 0 <= offset and offset + nbytes <= self.nbytes
+        return _DeviceView(self, offset, nbytes)
+
     def free(self):
         if self.address:
             load_library().slha_b200_free(self.address)
@@ -229,6 +240,14 @@ class DeviceBuffer:
             self.free()
         except Exception:
             pass
+
+
+class _DeviceView:
+    def __init__(self, owner, offset, nbytes):
+        self.owner, self.address, self.nbytes = owner, owner.address + offset, nbytes
+
+    def data_ptr(self):
+        return self.address
 
 
 def to_device(host):

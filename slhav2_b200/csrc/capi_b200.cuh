@@ -45,6 +45,11 @@ int32_t slha_b200_set_stream(void* cuda_stream) {
     return SLHA_OK;
 }
 uint64_t slha_b200_launch_count(void) { return launch_count(); }
+int32_t slha_b200_debug_force_generic_score(int32_t on) {
+    g_last_error[0] = 0;
+    debug_force_generic_score(on != 0);
+    return SLHA_OK;
+}
 int32_t slha_b200_timing_begin(uint32_t max_calls) {
     return ffi([&]() -> Status {
         Ctx* c;

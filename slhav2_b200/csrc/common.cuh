@@ -110,6 +110,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
 Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* h_segments, size_t n_segments,
                           const float* d_q_coarse, const uint64_t* d_q_sign, size_t n_queries, uint32_t k,
                           uint32_t* d_out_index, float* d_out_score, uint32_t* d_out_count);
+void debug_force_generic_score(bool on);  // calling thread only
 Status timing_begin(uint32_t max_calls);
 Status timing_end(Ctx* c, float* score_ms, float* merge_ms, uint32_t capacity, uint32_t* n_out);
 Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* cand_score,

@@ -37,6 +37,12 @@ struct ThreadState {
     bool ctx_init[16] = {false};
     std::vector<Block> blocks[16];
     std::vector<std::pair<void*, size_t>> hblocks[16];
+    // Arena reuse across streams: a call on a caller-supplied stream may return while its
+    // kernels still read the arena; the event marks the end of that work, and a later call on
+    // ANOTHER stream waits for it before it reuses the arena (same stream: stream order suffices).
+    cudaEvent_t arena_done[16] = {nullptr};
+    cudaStream_t arena_stream[16] = {nullptr};
+    bool arena_pending[16] = {false};
 };
 thread_local ThreadState tls;
 }  // namespace
@@ -103,6 +109,10 @@ CallScope::CallScope() {
     st = get_ctx(&c);
     if (!st.ok()) return;
     auto& blocks = tls.blocks[c->device];
+    if (tls.arena_pending[c->device] && tls.arena_stream[c->device] != c->stream) {
+        cudaStreamWaitEvent(c->stream, tls.arena_done[c->device], 0);
+        tls.arena_pending[c->device] = false;
+    }
     // the previous call has returned, so its staging memory may be reused; when
     // the arena had to chain blocks, replace them by one block of the total size
     if (blocks.size() > 1) {
@@ -118,6 +128,22 @@ CallScope::CallScope() {
     for (Block& b : blocks) b.off = 0;
     for (auto& hb : tls.hblocks[c->device]) cudaFreeHost(hb.first);
     tls.hblocks[c->device].clear();
+}
+
+CallScope::~CallScope() {
+    if (!c || c->own_stream) return;  // library stream: the call drained it before returning
+    bool used = false;
+    for (const Block& b : tls.blocks[c->device]) used |= b.off != 0;
+    if (!used) return;
+    cudaEvent_t& ev = tls.arena_done[c->device];
+    if (!ev && cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        cudaStreamSynchronize(c->stream);  // no event to be had: drain instead
+        return;
+    }
+    cudaEventRecord(ev, c->stream);
+    tls.arena_stream[c->device] = c->stream;
+    tls.arena_pending[c->device] = true;
 }
 
 bool is_device_ptr(const void* p) {

@@ -11,10 +11,15 @@ namespace slha {
 
 // Resets the calling thread's scratch arena when constructed; the C ABI creates
 // one per entry point so that staging buffers live exactly as long as the call.
+// On a caller-supplied stream the call may return with its kernels still queued: the
+// destructor then records an event, and the next scope on a different stream waits for it.
 struct CallScope {
     Ctx* c = nullptr;
     Status st;
     CallScope();
+    ~CallScope();
+    CallScope(const CallScope&) = delete;
+    CallScope& operator=(const CallScope&) = delete;
     bool ok() const { return st.ok(); }
 };
 

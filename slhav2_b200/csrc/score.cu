@@ -517,11 +517,32 @@ Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Se
     const uint32_t round = (uint32_t)nwarps * BLK_TILES;
     uint64_t total = 0;
     for (size_t i = 0; i < n_segs; ++i) total += (uint64_t)segs[i].n_tiles * ((segs[i].n_queries + 3) / 4);
-    // every (segment, group of <= 4 queries) stream is cut into items of equal size; the
-    // item size is chosen so that items x 4 lists stay within the fixed scratch
-    const uint64_t target_items = NA_MAX_LISTS / 4 - std::min<uint64_t>(n_segs, NA_MAX_LISTS / 4 - 32);
-    uint64_t item_tiles = std::max<uint64_t>(4096, (total + target_items - 1) / target_items);
+    // Every (segment, group of <= 4 queries) stream is cut into items of equal size.  The item
+    // size starts where 128 items would cover the call and grows until the items and their
+    // candidate lists (one per item and query) fit the fixed scratch; only a call whose streams
+    // alone exceed it (one item each) is refused.
+    uint64_t streams = 0, stream_lists = 0;
+    for (size_t i = 0; i < n_segs; ++i)
+        if (segs[i].n_tiles) {
+            streams += (segs[i].n_queries + 3) / 4;
+            stream_lists += segs[i].n_queries;
+        }
+    if (streams > NA_MAX_ITEMS || stream_lists > NA_MAX_LISTS)
+        return Status(SLHA_ERR_CAPACITY, "score_topk_noalloc: the segments x query groups alone need more than " +
+                                             std::to_string(NA_MAX_ITEMS) + " work items or " + std::to_string(NA_MAX_LISTS) +
+                                             " candidate lists, the size of the fixed scratch");
+    uint64_t item_tiles = std::max<uint64_t>(4096, (total + 127) / 128);
     item_tiles = (item_tiles + round - 1) / round * round;
+    for (;;) {
+        uint64_t need_items = 0, need_lists = 0;
+        for (size_t i = 0; i < n_segs; ++i) {
+            const uint64_t parts = (segs[i].n_tiles + item_tiles - 1) / item_tiles;
+            need_items += parts * ((segs[i].n_queries + 3) / 4);
+            need_lists += parts * segs[i].n_queries;
+        }
+        if (need_items <= NA_MAX_ITEMS && need_lists <= NA_MAX_LISTS) break;
+        item_tiles = (item_tiles + item_tiles / 4 + round - 1) / round * round;  // (ends: one part per stream fits, checked above)
+    }
     uint32_t n_items = 0, n_lists = 0, max_parts = 1;
     for (size_t i = 0; i < n_segs; ++i) {
         const SlhaB200Segment& s = segs[i];

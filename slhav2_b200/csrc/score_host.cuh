@@ -2,7 +2,6 @@
 // Included by score.cu.
 #pragma once
 
-#include <cstdlib>
 #include <memory>
 
 namespace slha {
@@ -11,10 +10,9 @@ namespace {
 
 constexpr size_t MAX_SMEM = 227 * 1024;
 
-int env_int(const char* name, int dflt) {
-    const char* v = std::getenv(name);
-    return (v && *v) ? std::atoi(v) : dflt;
-}
+// slha_b200_debug_force_generic_score: the calling thread's score_topk calls skip the
+// tensor-core kernel (a checking aid: both kernels must give the same answers).
+thread_local bool g_force_generic = false;
 
 size_t mma_smem_bytes(int nwarps, uint32_t cap, bool nf4_table) {
     return (size_t)(nf4_table ? NF4_LUT_BYTES : 0) + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE + (size_t)4 * cap * 8 + 4 * 8 +
@@ -87,7 +85,9 @@ struct DevBuf {
         p = nullptr;
         cap = 0;
         const size_t want = need + need / 2;
-        SLHA_CUDA(cudaMalloc(&p, want));
+        void* q = nullptr;
+        SLHA_CUDA(cudaMalloc(&q, want));  // (on failure the buffer stays empty: p == nullptr, cap == 0)
+        p = q;
         cap = want;
         return Status();
     }
@@ -118,6 +118,7 @@ struct Plan {
     bool mixed = false;
     bool tq3 = false;
     int codec_hint_in = -1;
+    bool force_generic_in = false;
     int mma_threads = 256;
     uint32_t mma_cap = 0, mma_grid = 0;
     size_t mma_smem = 0;
@@ -146,7 +147,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     static thread_local uint64_t tick = 0;
     ++tick;
     for (auto& e : cache)
-        if (e->device == c->device && e->codec_hint_in == codec_hint && e->key == key) {
+        if (e->device == c->device && e->codec_hint_in == codec_hint && e->force_generic_in == g_force_generic && e->key == key) {
             e->last_use = tick;
             *out = e.get();
             return Status();
@@ -162,16 +163,19 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
         p->classes.clear();
         p->max_parts = 1;
     }
+    // The plan is published (key + device set) only once it is complete: any early return
+    // below leaves a slot that no later call can match.
+    p->key.clear();
+    p->device = -1;
     p->last_use = tick;
     p->codec_hint_in = codec_hint;
-    p->key = std::move(key);
-    p->device = c->device;
+    p->force_generic_in = g_force_generic;
     p->k = k;
     p->n_lists = 0;
     p->nq = (uint32_t)nq;
     p->kp2 = 2;
     while (p->kp2 < k) p->kp2 <<= 1;
-    p->threads = env_int("SLHA_B200_SCORE_THREADS", k > 1024 ? 256 : 128);
+    p->threads = k > 1024 ? 256 : 128;
     const int nwarps = p->threads / 32;
     const uint32_t round = (uint32_t)nwarps * BLK_TILES;
     uint32_t cap = std::max<uint32_t>(2 * k, k + 2 * round);
@@ -181,7 +185,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     p->cap = cap;
 
     // tensor-core kernel: persistent CTAs (one per SM unless shared memory allows more)
-    p->mma_threads = env_int("SLHA_B200_MMA_THREADS", 512) == 256 ? 256 : 512;  // 8 or 16 warps: the kernel deals sets round-robin with a power-of-two mask
+    p->mma_threads = 512;  // 16 warps: the kernel deals sets round-robin with a power-of-two mask
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
     {
@@ -209,7 +213,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
         // per query: one region per warp, so a multiple of the warp count (256 covers 8 and 16 warps)
         uint32_t mcap = (std::max<uint32_t>(3 * k, k + 4 * mround) + 255) / 256 * 256;
         while (mcap > k + 2 * mround && mma_smem_bytes(mw, mcap, p->nf4_table) > MAX_SMEM) mcap -= 256;
-        p->use_mma = env_int("SLHA_B200_SCORE_IMPL", 1) != 0 && mma_smem_bytes(mw, mcap, p->nf4_table) <= MAX_SMEM;
+        p->use_mma = !g_force_generic && mma_smem_bytes(mw, mcap, p->nf4_table) <= MAX_SMEM;
         p->mma_cap = mcap;
         p->mma_smem = mma_smem_bytes(mw, mcap, p->nf4_table);
         const uint32_t per_sm = (uint32_t)std::max<size_t>(1, MAX_SMEM / (p->mma_smem + 1024));
@@ -223,11 +227,8 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     // (and at segment ends), so per-item costs are paid once per ~total/grid tiles.
     uint64_t total = 0;
     for (size_t i = 0; i < n_segs; ++i) total += (uint64_t)segs[i].n_tiles * ((segs[i].n_queries + 3) / 4);
-    uint32_t item_tiles = (uint32_t)env_int("SLHA_B200_ITEM_TILES", 0);
-    if (!item_tiles) {
-        item_tiles = std::max<uint32_t>(8192, 8 * k);
-        while (item_tiles > 2048 && total / item_tiles < 592) item_tiles /= 2;
-    }
+    uint32_t item_tiles = std::max<uint32_t>(8192, 8 * k);
+    while (item_tiles > 2048 && total / item_tiles < 592) item_tiles /= 2;
     item_tiles = std::max(round, (item_tiles + round - 1) / round * round);
     uint64_t share = (total + p->mma_grid - 1) / std::max<uint32_t>(p->mma_grid, 1);
     share = std::max<uint64_t>(2048, (share + MMA_SET_TILES - 1) / MMA_SET_TILES * MMA_SET_TILES);
@@ -343,6 +344,8 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     SLHA_CUDA(cudaMemcpyAsync(p->d_items, all.data(), all.size() * sizeof(WorkItem), cudaMemcpyHostToDevice, c->stream));
     SLHA_CUDA(cudaMemcpyAsync(p->d_q_list_begin, q_begin.data(), nq * 4, cudaMemcpyHostToDevice, c->stream));
     SLHA_CUDA(cudaMemcpyAsync(p->d_q_list_count, q_count.data(), nq * 4, cudaMemcpyHostToDevice, c->stream));
+    p->key = std::move(key);
+    p->device = c->device;
     *out = p;
     return Status();
 }
@@ -511,6 +514,8 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     }
     return Status();
 }
+
+void debug_force_generic_score(bool on) { g_force_generic = on; }
 
 Status timing_begin(uint32_t max_calls) {
     for (cudaEvent_t e : g_timing.ev) cudaEventDestroy(e);

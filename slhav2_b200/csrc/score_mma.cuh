@@ -341,10 +341,6 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
                 // everything left in the range stays; more than allowed means equal
                 // (or non-finite) scores: the exact selection sorts it out
                 __syncwarp();
-#ifdef SLHA_SCORE_PROFILE
-                if (lane == 0 && nq > 1 && atomicAdd(&g_sel_prof[148 * 8 - 1], 1ull) < 8)
-                    printf("unbucketable: cta %d q %d lo %08x hi %08x smin %g inv %g need %u cnt %d pass %d\n", blockIdx.x, warp, lo, hi, smin, inv, need, cnt[warp], pass);
-#endif
                 if (lane == 0) { s[3] = 0u; s[4] = 1u; s[7] = 0u; }
             } else {
                 // lane l owns buckets 255-8l .. 248-8l (descending)
@@ -1156,10 +1152,12 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
             PROF_T(t_rv0);
             __syncwarp();
             if (lane == 0) atomicAdd(&ctl[1], 1);
-            for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
-                if (*reinterpret_cast<volatile int*>(ctl + 1) >= nwarps) break;
-                __nanosleep(40);
+            bool met = false;
+            for (uint32_t spin = 0; spin < (1u << 24) && !met; ++spin) {
+                met = *reinterpret_cast<volatile int*>(ctl + 1) >= nwarps;
+                if (!met) __nanosleep(40);
             }
+            if (!met && lane == 0) bail[0] = 1;  // the wait ran out: the generic kernel takes the item
             __syncthreads();
             PROF_T(t_rv1);
             rc = mma_settle(a, m, rc, false);
@@ -1316,11 +1314,13 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
             // drain: warps that ran out of sets keep serving block-wide steps until all are done
             __syncwarp();
             if (lane == 0) atomicAdd(&ctl[2], 1);
-            for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+            bool done = false;
+            for (uint32_t spin = 0; spin < (1u << 24) && !done; ++spin) {
                 if (*reinterpret_cast<volatile int*>(ctl)) rendezvous();
-                else if (*reinterpret_cast<volatile int*>(ctl + 2) >= nwarps) break;
+                else if (*reinterpret_cast<volatile int*>(ctl + 2) >= nwarps) done = true;
                 else __nanosleep(100);
             }
+            if (!done && lane == 0) bail[0] = 1;  // the wait ran out: the generic kernel takes the item
         }
         cp_async_wait<0>();
         __syncthreads();

@@ -29,6 +29,58 @@ def test_config1_single_head_cpu_runnable_reference():
     check_topk(tiles, segs, qc, qs, k, gi, gsc, gc)
 
 
+def llama_decode_keys(seed, heads, tokens, d, pos0=0, theta=500000.0):
+    """Config-2 / config-5 key distribution from the oracle PRNG: N(0,1) x per-channel log-normal(0, 0.5),
+    RoPE (pairs (2i, 2i+1), theta) at positions pos0.., rounded to bf16 (returned widened to f32)."""
+    rng = ora.Rng(seed)
+    chan = np.exp(0.5 * rng.gaussian(d).astype(np.float64)).astype(F)
+    k = rng.gaussian(heads * tokens * d).reshape(heads, tokens, d) * chan
+    pos = np.arange(pos0, pos0 + tokens, dtype=np.float64)
+    inv = theta ** (-np.arange(0, d, 2, dtype=np.float64) / d)
+    ang = pos[:, None] * inv[None, :]
+    c, s_ = np.cos(ang).astype(F), np.sin(ang).astype(F)
+    a, b = k[..., 0::2].copy(), k[..., 1::2].copy()
+    k[..., 0::2] = a * c - b * s_
+    k[..., 1::2] = a * s_ + b * c
+    return H.to_bf16_f32(k.astype(F)).reshape(heads * tokens, d)
+
+
+def test_config2_llama_decode_kv_nf4_gqa4_top1024():
+    # the benchmarked workload at 2 layers x 8 KV heads x 4096 tokens: bf16 log-normal-channel RoPE keys,
+    # NF4, one model per layer, the [layer][kv_head][token] segment table of the sharded scorer, GQA
+    # groups of 4, top-1024 per query head; tile bytes and top-k against the oracle
+    L, Hh, T, G, d, k = 2, 8, 4096, 4, 128, 1024
+    n = L * Hh * T
+    dt = S.DeviceBuffer(n * 128)
+    want_tiles = np.zeros(n, S.TILE_DTYPE)
+    qc = np.zeros((L * Hh * G, 128), F)
+    qs = np.zeros((L * Hh * G, 4), np.uint64)
+    pos = np.tile(np.arange(T, dtype=np.uint32), Hh)
+    heads = np.repeat(np.arange(Hh, dtype=np.uint16), T)
+    for l in range(L):
+        om, p = H.make_model_pair(d, seed=100 + l, pseed=200 + l)
+        gm = S.Model.from_projection(p, d, 100 + l)
+        keys = llama_decode_keys(1234 + l, Hh, T, d)
+        bf16 = (keys.view(np.uint32) >> 16).astype(np.uint16)
+        lo = l * Hh * T
+        gm.encode_keys(bf16, S.CODEC_NF4, n=Hh * T, key_dtype=S.BF16, positions=pos, head_ids=heads, out=dt.view(lo * 128, Hh * T * 128))
+        want_tiles[lo:lo + Hh * T] = om.encode_batch(keys, 2, pos=pos, head=heads)
+        q = H.gaussian_keys(99 + l, Hh * G, d)
+        a, b = gm.prepare_queries(q)
+        qc[l * Hh * G:(l + 1) * Hh * G], qs[l * Hh * G:(l + 1) * Hh * G] = a, b
+        wc, ws = om.prepare_query(q[5])
+        assert np.array_equal(a[5], wc) and np.array_equal(b[5], ws)
+        gm.release()
+    tiles = dt.download(S.TILE_DTYPE, n)
+    assert tiles.tobytes() == want_tiles.tobytes()
+    assert np.all(tiles["flags"] == ora.FLAG_NF4)
+    from slhav2_b200 import shard
+
+    segs = shard.shard_segments(L, Hh, T, G, 0)
+    gi, gsc, gc = S.score_topk(dt, segs, qc, qs, L * Hh * G, k)
+    check_topk(tiles, [tuple(int(x) for x in r) for r in segs.tolist()], qc, qs, k, gi, gsc, gc)
+
+
 def student_t_keys(seed, n, d):
     rng = ora.Rng(seed)
     g = rng.gaussian(n * d * 5).reshape(n, d, 5)
@@ -98,9 +150,10 @@ def test_config4_ccos_under_budget_interleaved_appends_and_decode_steps():
     assert np.all(np.abs(imp[live] - wi[live]) <= 1e-5)
 
 
-def test_config5_full_length_head_fused_topk_equals_sort_of_full_scores():
-    # one KV head of the 1M-token context (134 MB of tiles), MX-32 INT4, 4 queries, top-2048:
-    # the fused path must return exactly the top of the library's own full score vectors
+def test_config5_full_length_head_fused_topk_against_the_oracle():
+    # one KV head of the 1M-token context (134 MB of tiles), MX-32 INT4, 4 queries, top-2048.  The
+    # oracle scores every tile of the head (4 M tile-query pairs, a few seconds with its threads);
+    # the library's full-score mode is checked against it too, then the fused top-k against both
     n, d, k, nq = 1 << 20, 128, 2048, 4
     _, p = H.make_model_pair(d, seed=12, pseed=13)
     gm = S.Model.from_projection(p, d, 12)
@@ -118,6 +171,15 @@ def test_config5_full_length_head_fused_topk_equals_sort_of_full_scores():
     S.score_tiles(tiles, n, qc, qs, nq, out=full)
     gi, gsc, gc = S.score_topk(tiles, S.make_segments([(0, n, 0, nq, 0)]), qc, qs, nq, k)
     full = full.cpu().numpy()
+    host_tiles = np.frombuffer(tiles.cpu().numpy().tobytes(), S.TILE_DTYPE)
+    want = H.oracle_scores(host_tiles, qc, qs)
+    assert np.all(np.abs(full - want) <= 1e-3)
+    full = want  # from here on the oracle's scores are the yardstick
+    # tile bytes of a sub-range against the oracle's encoder (bf16 keys widen exactly)
+    om = ora.Model(p, d, seed=12)
+    sub = slice(500000, 500000 + 4096)
+    kf = keys[sub].float().cpu().numpy()
+    assert host_tiles[sub].tobytes() == om.encode_batch(kf, 6, pos=np.arange(sub.start, sub.stop, dtype=np.uint32)).tobytes()
     assert np.all(gc == k)
     for j in range(nq):
         oi, ov = ora.topk(full[j], k)

@@ -167,31 +167,21 @@ def test_large_queries_are_scored_by_the_generic_kernel():
 
 
 def test_generic_kernel_only_mode_matches():
-    # SLHA_B200_SCORE_IMPL=0 disables the tensor-core kernel: same answers from the generic one
-    import subprocess
-    import sys
-    import os
-
-    code = (
-        "import numpy as np, slhav2_b200 as S\n"
-        "from tests import helpers as H\n"
-        "t = H.random_tiles(20000, 2, seed=4); qc, qs = H.random_queries(4, 5)\n"
-        "d = S.to_device(t)\n"
-        "i, s, c = S.score_topk(d, S.make_segments([(0, 20000, 0, 4, 0)]), qc, qs, 4, 256)\n"
-        "np.save(sys.argv[1] if False else __import__('sys').argv[1], np.concatenate([i.astype(np.float64), s.astype(np.float64)]))\n"
-    )
-    import tempfile
-
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    outs = []
-    tmp = tempfile.mkdtemp()
-    for impl in ("0", "1"):
-        path = os.path.join(tmp, "impl%s.npy" % impl)
-        env = dict(os.environ, SLHA_B200_SCORE_IMPL=impl, PYTHONPATH=root)
-        subprocess.check_call([sys.executable, "-c", code, path], env=env, cwd=root)
-        outs.append(np.load(path))
-    i0, s0 = outs[0][:4], outs[0][4:]
-    i1, s1 = outs[1][:4], outs[1][4:]
+    # slha_b200_debug_force_generic_score switches the tensor-core kernel off for this thread:
+    # the generic kernel must give the same answers, and both must match the oracle
+    n, nq, k = 20000, 4, 256
+    t = H.random_tiles(n, 2, seed=4)
+    qc, qs = H.random_queries(nq, 5)
+    d = S.to_device(t)
+    segs = [(0, n, 0, nq, 0)]
+    i1, s1, c1 = S.score_topk(d, S.make_segments(segs), qc, qs, nq, k)
+    S.debug_force_generic_score(True)
+    try:
+        i0, s0, c0 = S.score_topk(d, S.make_segments(segs), qc, qs, nq, k)
+    finally:
+        S.debug_force_generic_score(False)
+    check_topk(t, segs, qc, qs, k, i0, s0, c0)
+    check_topk(t, segs, qc, qs, k, i1, s1, c1)
     assert np.all(np.abs(s0 - s1) <= 1e-3)
     assert np.mean(i0 == i1) > 0.98
 
