@@ -283,6 +283,49 @@ int32_t slha_b200_score_topk_noalloc(const SciRustSlhaTile* tiles, const SlhaB20
                                      float* out_score, uint32_t* out_count);
 
 /*
+ * Token-range sharding over the GPUs of one node, one handle per rank (one
+ * process or host thread per GPU).  The reference has no multi-device path;
+ * these calls implement the sharding the tile scores' independence allows
+ * (ElasticKvCache::score_all, scirust/src/ccos.rs:346-355): every rank scores
+ * the tiles in its own HBM and keeps its own top k per query row, ONE
+ * ncclAllGather moves every rank's [2][n_queries][k] block (indices, then score
+ * bits), and every rank merges the `world` lists with the ordering rule of
+ * scirust/src/metrics.rs:186-192, so all ranks hold the same global result.
+ *
+ * NCCL is bound at run time (libnccl.so.2, the copy already loaded in the
+ * process when there is one); a host that never calls these functions needs
+ * no NCCL.  Rank 0 obtains the 128-byte unique id and hands it to the other
+ * ranks by any transport the host has (a file, a socket, MPI, a torch
+ * broadcast).  shard_init is collective: every rank of `world` must call it.
+ * With world == 1 no id and no NCCL are needed and a step is plain
+ * slha_b200_score_topk.
+ */
+typedef struct SlhaB200Shard SlhaB200Shard;
+int32_t slha_b200_shard_unique_id(void* id_out /* 128 bytes */);
+int32_t slha_b200_shard_init(const void* nccl_unique_id, int32_t rank, int32_t world, SlhaB200Shard** out);
+int32_t slha_b200_shard_destroy(SlhaB200Shard* shard);
+/*
+ * One sharded decode step, collective over the ranks: same arguments as
+ * slha_b200_score_topk for THIS rank's tiles and segment table (segments in
+ * host memory; index_base = the global token position of the rank's first
+ * tile), every rank passes the same queries and k.  out_index / out_score
+ * ([n_queries][k], host or device) receive the merged global top k on every
+ * rank.  The three device steps (local fused score + top-k, all-gather, merge)
+ * are enqueued back to back on the calling thread's stream without a host
+ * round trip; with a caller-supplied stream and device outputs the call
+ * returns once they are enqueued.
+ */
+int32_t slha_b200_shard_score_topk(SlhaB200Shard* shard, const SciRustSlhaTile* tiles,
+                                   const SlhaB200Segment* segments, size_t n_segments,
+                                   const float* q_coarse, const uint64_t* q_sign, size_t n_queries,
+                                   uint32_t k, uint32_t* out_index, float* out_score);
+/* Device timing of the steps of this handle: with on != 0 every step records
+ * CUDA events on its stream; last_times waits for the latest step and writes
+ * its three durations in milliseconds: local score + top-k, all-gather, merge. */
+int32_t slha_b200_shard_set_timing(SlhaB200Shard* shard, int32_t on);
+int32_t slha_b200_shard_last_times(SlhaB200Shard* shard, float* ms_out /* 3 floats */);
+
+/*
  * Merge n_lists candidate lists per query (layout [list][query][k_in], as an
  * all-gather of per-shard slha_b200_score_topk outputs produces) into the
  * global top k_out per query with the same ordering rule.  Device pointers.

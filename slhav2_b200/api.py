@@ -88,6 +88,12 @@ SIGNATURES = {
     "slha_b200_score_topk_noalloc": (_i32, [_vp, _vp, _sz, _vp, _vp, _sz, _u32, _vp, _vp, _vp]),
     "slha_b200_topk_merge": (_i32, [_vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
     "slha_b200_topk_merge_strided": (_i32, [_vp, _vp, _u32, _u64, _u32, _u32, _u32, _vp, _vp]),
+    "slha_b200_shard_unique_id": (_i32, [_vp]),
+    "slha_b200_shard_init": (_i32, [_vp, _i32, _i32, C.POINTER(_vp)]),
+    "slha_b200_shard_destroy": (_i32, [_vp]),
+    "slha_b200_shard_score_topk": (_i32, [_vp, _vp, _vp, _sz, _vp, _vp, _sz, _u32, _vp, _vp]),
+    "slha_b200_shard_set_timing": (_i32, [_vp, _i32]),
+    "slha_b200_shard_last_times": (_i32, [_vp, _vp]),
     "slha_b200_pool_create": (_i32, [_vp, C.POINTER(_vp)]),
     "slha_b200_pool_destroy": (_i32, [_vp]),
     "slha_b200_pool_insert_tiles": (_i32, [_vp, _vp, _sz, _vp]),
@@ -414,6 +420,54 @@ def topk_merge(cand_index, cand_score, n_lists, n_queries, k_in, k_out, out_inde
         )
     )
     return out_index, out_score
+
+
+def shard_unique_id():
+    """The 128-byte NCCL unique id rank 0 hands to every rank before Shard(...)."""
+    buf = np.zeros(128, np.uint8)
+    _check(load_library().slha_b200_shard_unique_id(ptr(buf)))
+    return buf
+
+
+class Shard:
+    """One rank's handle of the token-range sharded scorer (slha_b200_shard_*): local fused
+    score + top-k, one NCCL all-gather, merge -- all inside the library."""
+
+    def __init__(self, unique_id, rank, world):
+        h = _vp()
+        uid = None if unique_id is None else np.ascontiguousarray(unique_id, np.uint8)
+        _check(load_library().slha_b200_shard_init(ptr(uid), rank, world, C.byref(h)))
+        self.handle, self.rank, self.world = h.value, rank, world
+
+    def score_topk(self, tiles, segments, q_coarse, q_sign, nq, k, out_index=None, out_score=None):
+        seg = np.ascontiguousarray(segments, SEGMENT_DTYPE)
+        if out_index is None:
+            out_index = np.zeros((nq, k), np.uint32)
+        if out_score is None:
+            out_score = np.zeros((nq, k), np.float32)
+        _check(load_library().slha_b200_shard_score_topk(self.handle, ptr(tiles), ptr(seg), len(seg), ptr(_np(q_coarse, np.float32)),
+                                                         ptr(_np(q_sign, np.uint64)), nq, k, ptr(out_index), ptr(out_score)))
+        return out_index, out_score
+
+    def set_timing(self, on=True):
+        _check(load_library().slha_b200_shard_set_timing(self.handle, 1 if on else 0))
+
+    def last_times(self):
+        """(local score + top-k, all-gather, merge) milliseconds of the latest step."""
+        ms = np.zeros(3, np.float32)
+        _check(load_library().slha_b200_shard_last_times(self.handle, ptr(ms)))
+        return ms
+
+    def destroy(self):
+        if self.handle:
+            load_library().slha_b200_shard_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
 
 
 def audit():

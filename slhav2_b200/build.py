@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libslha_b200.so")
-SOURCES = ["score.cu", "encode.cu", "pool.cu", "runtime.cu", "capi.cu"]
+SOURCES = ["score.cu", "encode.cu", "pool.cu", "runtime.cu", "shard.cu", "capi.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 COMMON = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -49,7 +49,7 @@ def build(force=False, verbose=False):
         raise RuntimeError("nvcc failed")
     if force or procs or _stale(OUT, objs):
         cmd = [NVCC, "-shared", "-o", OUT] + objs + ["-gencode", "arch=compute_100a,code=sm_100a",
-                                                      "-ccbin", "/usr/bin/g++", "-lcudart"]
+                                                      "-ccbin", "/usr/bin/g++", "-lcudart", "-ldl"]
         subprocess.check_call(cmd)
     return OUT
 

@@ -273,6 +273,77 @@ int32_t slha_b200_topk_merge(const uint32_t* cand_index, const float* cand_score
                                         k_out, out_index, out_score);
 }
 
+// ------------------------------------------------------------------ shards
+int32_t slha_b200_shard_unique_id(void* id_out) {
+    return ffi([&]() -> Status {
+        if (!id_out) return Status(SLHA_ERR_NULL, "slha_b200_shard_unique_id received a NULL pointer");
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        return shard_unique_id(id_out);
+    });
+}
+int32_t slha_b200_shard_init(const void* nccl_unique_id, int32_t rank, int32_t world, SlhaB200Shard** out) {
+    return ffi([&]() -> Status {
+        if (!out) return Status(SLHA_ERR_NULL, "slha_b200_shard_init received a NULL pointer");
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        Shard* s;
+        SLHA_TRY(shard_init(c, nccl_unique_id, rank, world, &s));
+        *out = reinterpret_cast<SlhaB200Shard*>(s);
+        return Status();
+    });
+}
+int32_t slha_b200_shard_destroy(SlhaB200Shard* shard) {
+    return ffi([&]() -> Status {
+        if (!shard) return Status();
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        SLHA_CUDA(cudaStreamSynchronize(c->stream));
+        return shard_destroy(reinterpret_cast<Shard*>(shard));
+    });
+}
+int32_t slha_b200_shard_score_topk(SlhaB200Shard* shard, const SciRustSlhaTile* tiles, const SlhaB200Segment* segments,
+                                   size_t n_segments, const float* q_coarse, const uint64_t* q_sign, size_t n_queries,
+                                   uint32_t k, uint32_t* out_index, float* out_score) {
+    return ffi([&]() -> Status {
+        if (!shard) return Status(SLHA_ERR_NULL, "shard handle is NULL");
+        if (n_queries == 0) return Status();
+        if (!tiles || !segments || !q_coarse || !q_sign || !out_index || !out_score)
+            return Status(SLHA_ERR_NULL, "slha_b200_shard_score_topk received a NULL pointer");
+        if (!is_device_ptr(tiles)) return Status(SLHA_ERR_DEVICE, "slha_b200_shard_score_topk: tiles must be device memory");
+        if (is_device_ptr(segments)) return Status(SLHA_ERR_DEVICE, "slha_b200_shard_score_topk: segments must be host memory");
+        CallScope cs;
+        if (!cs.ok()) return cs.st;
+        Ctx* c = cs.c;
+        const float* dq;
+        const uint64_t* ds;
+        SLHA_TRY(stage_in_t(c, q_coarse, n_queries * D_C, &dq));
+        SLHA_TRY(stage_in_t(c, q_sign, n_queries * 4, &ds));
+        std::vector<StagedOut> outs(2);
+        SLHA_TRY(stage_out(c, out_index, n_queries * k * 4, &outs[0]));
+        SLHA_TRY(stage_out(c, out_score, n_queries * k * 4, &outs[1]));
+        SLHA_TRY(shard_step_device(c, reinterpret_cast<Shard*>(shard), tiles, segments, n_segments, dq, ds, n_queries, k,
+                                   (uint32_t*)outs[0].dev, (float*)outs[1].dev));
+        return finish_outputs(c, outs, sync_by_default(c));
+    });
+}
+int32_t slha_b200_shard_set_timing(SlhaB200Shard* shard, int32_t on) {
+    return ffi([&]() -> Status {
+        if (!shard) return Status(SLHA_ERR_NULL, "shard handle is NULL");
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        return shard_set_timing(reinterpret_cast<Shard*>(shard), on != 0);
+    });
+}
+int32_t slha_b200_shard_last_times(SlhaB200Shard* shard, float* ms_out) {
+    return ffi([&]() -> Status {
+        if (!shard || !ms_out) return Status(SLHA_ERR_NULL, "slha_b200_shard_last_times received a NULL pointer");
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        return shard_last_times(c, reinterpret_cast<Shard*>(shard), ms_out);
+    });
+}
+
 // ------------------------------------------------------------------ pool
 int32_t slha_b200_pool_create(const SlhaB200PoolConfig* config, SlhaB200Pool** out) {
     return ffi([&]() -> Status {

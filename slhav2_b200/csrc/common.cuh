@@ -117,6 +117,18 @@ Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* 
                                uint32_t n_lists, uint64_t list_stride, uint32_t n_queries, uint32_t k_in,
                                uint32_t k_out, uint32_t* out_index, float* out_score);
 
+// ---- token-range sharding over NCCL (shard.cu) ----------------------------------
+struct Shard;
+Status shard_unique_id(void* id128);
+Status shard_init(Ctx* c, const void* id128, int rank, int world, Shard** out);
+Status shard_destroy(Shard* s);
+void shard_info(const Shard* s, int* rank, int* world);
+Status shard_set_timing(Shard* s, bool on);
+Status shard_last_times(Ctx* c, Shard* s, float* ms3);
+Status shard_step_device(Ctx* c, Shard* s, const SciRustSlhaTile* tiles, const SlhaB200Segment* h_segs, size_t n_segs,
+                         const float* d_qc, const uint64_t* d_qs, size_t nq, uint32_t k, uint32_t* d_out_index,
+                         float* d_out_score);
+
 Status launch_encode(Ctx* c, const Model* m, const void* d_keys, int key_dtype, size_t n,
                      const uint32_t* d_positions, uint32_t position_base, const uint16_t* d_heads,
                      int codec, SciRustSlhaTile* d_tiles, const uint32_t* d_slots);

@@ -450,17 +450,20 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
             SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
             SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
             SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
             mma_configured[c->device & 15] = true;
         }
         // eight or more CTAs per query (a long segment cut over the grid): first thresholds early (config 5: 0.329 -> 0.317 ms;
         // a 1 M-slot pool scored by one GQA group: 0.200 -> 0.114 ms)
         const bool early = p->max_parts >= 8;
-        const int kind = p->tq3 ? 2 : (p->mixed ? 1 : 0);
+        // 3: no NF4 tile is expected, so the launch holds INT4 / MX-INT4 tiles only (any other tile is handed back)
+        const int kind = p->tq3 ? 2 : (p->mixed ? 1 : (p->nf4_table ? 0 : 3));
 #define SLHA_LAUNCH_MMA(K, E) score_mma_kernel<true, K, E><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a)
         if (early) {
-            if (kind == 2) SLHA_LAUNCH_MMA(2, true); else if (kind == 1) SLHA_LAUNCH_MMA(1, true); else SLHA_LAUNCH_MMA(0, true);
+            if (kind == 3) SLHA_LAUNCH_MMA(3, true); else if (kind == 2) SLHA_LAUNCH_MMA(2, true); else if (kind == 1) SLHA_LAUNCH_MMA(1, true); else SLHA_LAUNCH_MMA(0, true);
         } else {
-            if (kind == 2) SLHA_LAUNCH_MMA(2, false); else if (kind == 1) SLHA_LAUNCH_MMA(1, false); else SLHA_LAUNCH_MMA(0, false);
+            if (kind == 3) SLHA_LAUNCH_MMA(3, false); else if (kind == 2) SLHA_LAUNCH_MMA(2, false); else if (kind == 1) SLHA_LAUNCH_MMA(1, false); else SLHA_LAUNCH_MMA(0, false);
         }
 #undef SLHA_LAUNCH_MMA
         count_launch();

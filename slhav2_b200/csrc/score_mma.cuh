@@ -202,8 +202,9 @@ __device__ __forceinline__ void coarse_group(uint32_t hb, uint32_t lut_lane, uin
     if (MODE == 1 || MODE == 2) mma_f16(d, l0, l1, l2, l3, bq[J][0], bq[J][1]);
     // gs[J] as float: byte J of (x.z, x.w)
     const uint32_t gw0 = J < 4 ? x0.z : x0.w, gw1 = J < 4 ? x1.z : x1.w;
-    acc0 = fmaf(d[0] + d[1], __uint2float_rn(__byte_perm(gw0, 0u, 0x4440 + (J & 3))), acc0);
-    acc1 = fmaf(d[2] + d[3], __uint2float_rn(__byte_perm(gw1, 0u, 0x4440 + (J & 3))), acc1);
+    // (byte -> float on the ALU / FMA pipes: 2^23 + b as a bit pattern, minus 2^23)
+    acc0 = fmaf(d[0] + d[1], __uint_as_float(__byte_perm(gw0, 0x4B000000u, 0x7440 + (J & 3))) - 8388608.0f, acc0);
+    acc1 = fmaf(d[2] + d[3], __uint_as_float(__byte_perm(gw1, 0x4B000000u, 0x7440 + (J & 3))) - 8388608.0f, acc1);
 }
 
 template <int MODE>
@@ -219,6 +220,56 @@ __device__ __forceinline__ void coarse_set(uint32_t hb, uint32_t lut_lane, uint3
     coarse_group<MODE, 5>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
     coarse_group<MODE, 6>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
     coarse_group<MODE, 7>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+}
+
+// ---- launches that hold only INT4 / MX-INT4 tiles (KIND 3) --------------------------------
+// Thread (g, t) of the warp owns the 16 latent bytes 16t..16t+15 of rows g and g+8: dims
+// 32t..32t+31, i.e. the two scale groups 2t and 2t+1, fetched with one 16-byte load per row.
+// The group scale is folded into the A operand, so the eight MMAs of a set chain on one
+// accumulator and nothing is scaled per group afterwards:
+//   a nibble n masked in place at bits 4..7 of a 16-bit half is the fp16 value n * 2^-20;
+//   fma(n * 2^-20, gs * 2^8, -8 gs * 2^-12) = (n - 8) gs * 2^-12, exact: |(n - 8) gs| <= 2040
+//   has 11 significant bits and the result is a normal fp16 number (>= 2^-12).
+// k slot pairs (2t, 2t+1) / (2t+8, 2t+9) of MMA 2i take nibbles (0, 4) / (1, 5) of the
+// thread's word i, those of MMA 2i+1 nibbles (2, 6) / (3, 7); the B fragments carry the
+// queries' dims in the same order.  Sum = 2^-12 sum_d level_d gs_g q_d.
+__device__ __forceinline__ void int4c_scales(uint32_t h, uint32_t magic, uint32_t& G0, uint32_t& C0, uint32_t& G1, uint32_t& C1) {
+    // h = the two scale bytes (groups 2t, 2t+1) -> half2 (gs * 256) twice and (-gs * 2^-9) twice
+    uint32_t b0, b1;
+    asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(b0) : "r"(prmt(h, magic, 0x5050u)), "r"(0xE400E400u));
+    asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(b1) : "r"(prmt(h, magic, 0x5151u)), "r"(0xE400E400u));
+    asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(G0) : "r"(b0), "r"(0x5C005C00u));
+    asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(C0) : "r"(b0), "r"(0x98009800u));
+    asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(G1) : "r"(b1), "r"(0x5C005C00u));
+    asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(C1) : "r"(b1), "r"(0x98009800u));
+}
+__device__ __forceinline__ void int4c_word(uint32_t w, uint32_t G, uint32_t C, uint32_t (&o)[4]) {
+    o[0] = hfma2_u32((w << 4) & 0x00F000F0u, G, C);  // nibbles 0, 4
+    o[1] = hfma2_u32(w & 0x00F000F0u, G, C);         // nibbles 1, 5
+    o[2] = hfma2_u32((w >> 4) & 0x00F000F0u, G, C);  // nibbles 2, 6
+    o[3] = hfma2_u32((w >> 8) & 0x00F000F0u, G, C);  // nibbles 3, 7
+}
+// rb = shared address of row g of the staged set; t = lane & 3
+__device__ __forceinline__ void coarse_set_int4c(uint32_t rb, uint32_t t, uint32_t magic, const uint32_t (&bq)[8][2], float& acc0, float& acc1) {
+    const uint32_t cb = rb + 16u * t, hb = rb + 2u * t;
+    const uint4 L0 = lds_v4<0>(cb), L1 = lds_v4<MMA_HALF>(cb);
+    const uint32_t h0 = lds_u16<120>(hb), h1 = lds_u16<120 + MMA_HALF>(hb);
+    uint32_t G00, C00, G01, C01, G10, C10, G11, C11;
+    int4c_scales(h0, magic, G00, C00, G01, C01);
+    int4c_scales(h1, magic, G10, C10, G11, C11);
+    const uint32_t w0[4] = {L0.x, L0.y, L0.z, L0.w}, w1[4] = {L1.x, L1.y, L1.z, L1.w};
+    float d[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t o0[4], o1[4];
+        int4c_word(w0[i], i < 2 ? G00 : G01, i < 2 ? C00 : C01, o0);
+        int4c_word(w1[i], i < 2 ? G10 : G11, i < 2 ? C10 : C11, o1);
+        if (i == 0) mma_f16_zero(d, o0[0], o1[0], o0[1], o1[1], bq[0][0], bq[0][1]);
+        else mma_f16(d, o0[0], o1[0], o0[1], o1[1], bq[2 * i][0], bq[2 * i][1]);
+        mma_f16(d, o0[2], o1[2], o0[3], o1[3], bq[2 * i + 1][0], bq[2 * i + 1][1]);
+    }
+    acc0 = d[0] + d[1];
+    acc1 = d[2] + d[3];
 }
 
 #ifdef SLHA_SCORE_PROFILE
@@ -1063,6 +1114,20 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
             const float* q = a.q_coarse + (size_t)(it.query_begin + (have ? qi : 0)) * D_C;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
+                if (KIND == 3) {
+                    // MMA j takes nibbles (o, o + 4 | o + 1, o + 5), o = 2 (j & 1), of the thread's word j >> 1
+                    const float* qd = q + 32 * t + 8 * (j >> 1) + 2 * (j & 1);
+                    float v[4] = {qd[0], qd[4], qd[1], qd[5]};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (!have) v[i] = 0.0f;
+                        big |= fabsf(v[i]) > 60000.0f;
+                        if (g & 1) v[i] = half_residual(v[i]);
+                    }
+                    bq[j][0] = pack_half2(v[0], v[1]);
+                    bq[j][1] = pack_half2(v[2], v[3]);
+                    continue;
+                }
                 // mixed 8/4 tiles: group 0 = dims 2t, 2t+1 (8-bit levels, plain in both slots, so
                 // both carry 16x the query), groups 1..7 = INT4 groups of dims 16 j - 8 ..
                 const int dim0 = !(KIND == 1) ? 16 * j + 4 * t : (j == 0 ? 0 : 16 * j - 8 + 4 * t);
@@ -1191,13 +1256,15 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
             const bool all_mixed = KIND == 1 && (__reduce_and_sync(0xFFFFFFFFu, (row0 < n ? f0 : F_MIXED) & (row0 + 8 < n ? f1 : F_MIXED)) & F_MIXED);
             const bool all_tq3 = KIND == 2 && (__reduce_and_sync(0xFFFFFFFFu, (row0 < n ? f0 : F_TQ3) & (row0 + 8 < n ? f1 : F_TQ3)) & F_TQ3);
             if ((fo & F_MIX3) || ((fo & F_TQ3) && !all_tq3) || (KIND == 2 && !all_tq3) ||
-                ((fo & F_MIXED) && !all_mixed) || (KIND == 1 && !all_mixed) || ((fo & F_NF4) && !a.nf4_table)) {
+                ((fo & F_MIXED) && !all_mixed) || (KIND == 1 && !all_mixed) || ((fo & F_NF4) && (KIND == 3 || !a.nf4_table))) {
                 if (lane == 0) bail[0] = 1;  // a codec this kernel does not decode: hand the item back
                 break;
             }
             float acc0, acc1;
             const uint32_t hb = rb + 2u * (uint32_t)t;
-            if (KIND == 2) {  // (all_tq3 holds here)
+            if (KIND == 3) {
+                coarse_set_int4c(rb, (uint32_t)t, magic, bq, acc0, acc1);
+            } else if (KIND == 2) {  // (all_tq3 holds here)
                 tq3_to_nibbles(rb - row_lane, lane);
                 coarse_set<0>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
                 // level = (2 nibble - 15) / 4, or (2 nibble - 14) / 4 without the correction plane:
@@ -1225,9 +1292,13 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
             const int h1 = popc8(lds_v4<64 + MMA_HALF>(rb), lds_v4<80 + MMA_HALF>(rb), qs);
             const float lam0 = (f0 & F_WARM) ? 0.0f : __uint_as_float(m0.y);
             const float lam1 = (f1 & F_WARM) ? 0.0f : __uint_as_float(m1.y);
-            constexpr float unit = KIND == 2 ? 1.0f / 8160.0f : 1.0f / 4080.0f;  // 1 / (255 x 16 [x 2])
-            const float sc0 = fmaf(acc0, __uint_as_float(m0.x) * unit, lam0 * (float)(256 - 2 * h0));
-            const float sc1 = fmaf(acc1, __uint_as_float(m1.x) * unit, lam1 * (float)(256 - 2 * h1));
+            // 1 / (255 x 16 [x 2]); KIND 3: the sums carry 2^-12
+            constexpr float unit = KIND == 3 ? 4096.0f / 255.0f : (KIND == 2 ? 1.0f / 8160.0f : 1.0f / 4080.0f);
+            // 256 - 2 h without an integer conversion: (2^23 + h) as a bit pattern, times -2, plus 2^24 + 256 (exact)
+            const float x0f = fmaf(__uint_as_float(0x4B000000u | (uint32_t)h0), -2.0f, 16777472.0f);
+            const float x1f = fmaf(__uint_as_float(0x4B000000u | (uint32_t)h1), -2.0f, 16777472.0f);
+            const float sc0 = fmaf(acc0, __uint_as_float(m0.x) * unit, lam0 * x0f);
+            const float sc1 = fmaf(acc1, __uint_as_float(m1.x) * unit, lam1 * x1f);
             const uint32_t t0 = s * MMA_SET_TILES + (uint32_t)g, t1 = t0 + 8;
             bool live0 = mine && t0 < n, live1 = mine && t1 < n;
             if (sbase) {
@@ -1260,11 +1331,14 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
                 __syncwarp();
             }
             if (TOPK) {
-                const uint64_t pv = pivot[t];
-                const uint64_t comp0 = ((uint64_t)score_key(sc0) << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t0));
-                const uint64_t comp1 = ((uint64_t)score_key(sc1) << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t1));
-                const bool p0 = live0 && comp0 >= pv, p1 = live1 && comp1 >= pv;
+                // filter on the score word alone (a superset of the composite comparison: a key that
+                // only ties with the threshold's score is dropped again by the next purge)
+                const uint32_t pvh = reinterpret_cast<const volatile uint32_t*>(pivot)[2 * t + 1];
+                const uint32_t k0 = score_key(sc0), k1 = score_key(sc1);
+                const bool p0 = live0 && k0 >= pvh, p1 = live1 && k1 >= pvh;
                 if (__any_sync(0xFFFFFFFFu, p0 || p1)) {
+                    const uint64_t comp0 = ((uint64_t)k0 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t0));
+                    const uint64_t comp1 = ((uint64_t)k1 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t1));
                     // the lanes of query t append to the warp's region of that query: slots by ballot, no atomics
                     const unsigned b0 = __ballot_sync(0xFFFFFFFFu, p0) & t_mask, b1 = __ballot_sync(0xFFFFFFFFu, p1) & t_mask;
                     const int n0 = __popc(b0);

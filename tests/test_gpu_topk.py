@@ -217,3 +217,27 @@ def test_tq3_tiles_on_the_tensor_core_kernel(n, nq, k, nocorr_every, foreign):
     dt = S.to_device(tiles)
     gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, nq, k)
     check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+
+
+def test_rejected_call_shape_leaves_no_plan_behind():
+    # a segment table that is refused (query range past n_queries; a query row in two segments) must
+    # be refused every time it is presented, and a valid call afterwards must still be right: a plan
+    # enters the per-thread cache only once it is complete
+    n, nq, k = 6000, 4, 64
+    tiles = H.random_tiles(n, 1, seed=77)
+    qc, qs = H.random_queries(nq, 78)
+    dt = S.to_device(tiles)
+    bad_range = S.make_segments([(0, n, 2, 4, 0)])            # rows 2..5 of 4
+    twice = S.make_segments([(0, 3000, 0, 4, 0), (3000, 3000, 2, 2, 0)])
+    for bad in (bad_range, twice):
+        for _ in range(3):
+            with pytest.raises(S.SlhaError) as e:
+                S.score_topk(dt, bad, qc, qs, nq, k)
+            assert e.value.code == S.ERR_DIMENSION
+    segs = [(0, n, 0, nq, 0)]
+    gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, nq, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+    with pytest.raises(S.SlhaError):
+        S.score_topk(dt, bad_range, qc, qs, nq, k)
+    gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, nq, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
