@@ -297,6 +297,10 @@ struct ScoreArgs {
     unsigned long long* gpivot;   // tensor-core kernel: per query row, shared selection threshold
     unsigned long long* grange;   // per query row: bucket mapping of the shared score histogram (0 = none yet)
     uint32_t* ghist;              // per query row: 256 bucket counts of appended candidates
+    uint32_t* gcount;             // per query row: candidates appended to the row's buffer
+    uint32_t* gflag;              // per query row: 1 = the generic kernel scores the row's work items
+    uint64_t* gbuf;               // per query row: gcap composite keys
+    uint32_t gcap;
     uint32_t nf4_table;           // tensor-core kernel: build the NF4 shared-memory table (else NF4 tiles are handed back)
     uint32_t mixed;               // tensor-core kernel: query fragments arranged for mixed 8/4 tiles (other tiles are handed back)
 };
@@ -613,23 +617,3 @@ Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Se
 }
 
 }  // namespace slha
-
-#ifdef SLHA_SCORE_PROFILE
-extern "C" int slha_debug_score_prof(unsigned long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, slha::g_score_prof, sizeof(unsigned long long) * 148 * 8);
-}
-extern "C" int slha_debug_merge_prof(unsigned long long* out) {
-    int rc = (int)cudaMemcpyFromSymbol(out, slha::g_merge_prof, sizeof(unsigned long long) * 8);
-    static unsigned long long zero[8];
-    cudaMemcpyToSymbol(slha::g_merge_prof, zero, sizeof(zero));
-    return rc;
-}
-extern "C" int slha_debug_sel_prof(unsigned long long* out, int reset) {
-    int rc = (int)cudaMemcpyFromSymbol(out, slha::g_sel_prof, sizeof(unsigned long long) * 148 * 8);
-    if (reset) {
-        static unsigned long long zero[148 * 8];
-        cudaMemcpyToSymbol(slha::g_sel_prof, zero, sizeof(zero));
-    }
-    return rc;
-}
-#endif

@@ -14,10 +14,11 @@ constexpr size_t MAX_SMEM = 227 * 1024;
 // tensor-core kernel (a checking aid: both kernels must give the same answers).
 thread_local bool g_force_generic = false;
 
-size_t mma_smem_bytes(int nwarps, uint32_t cap, bool nf4_table) {
-    return (size_t)(nf4_table ? NF4_LUT_BYTES : 0) + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE + (size_t)4 * cap * 8 + 4 * 8 +
-           (128 + 4 + 12 + SEL_HIST_INTS) * 4 + 16;
+size_t mma_smem_bytes(int nwarps, bool nf4_table) {
+    // nf4 table | stage ring | B fragments | sign words, thresholds, bucket mappings, flag
+    return (size_t)(nf4_table ? NF4_LUT_BYTES : 0) + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE + MMA_BQ_BYTES + 128 + 16 + 32 + 16;
 }
+constexpr int STREAM_THREADS = SLHA_STREAM_THREADS;
 
 size_t score_smem_bytes(int G, int nwarps, bool topk, uint32_t cap) {
     size_t b = (size_t)G * D_C * 4 + 16 * 32 * 4 + (size_t)nwarps * DEPTH * BLK_BYTES;
@@ -109,7 +110,10 @@ struct Plan {
     uint32_t* d_cand_cnt = nullptr;
     uint32_t* d_retry = nullptr;   // per work item: 1 = the tensor-core kernel handed it back
     uint32_t* d_cta_begin = nullptr;  // tensor-core kernel: items [cta_begin[b], cta_begin[b+1]) belong to CTA b
-    unsigned long long* d_gpivot = nullptr;  // per query: best selection threshold any CTA has proven so far
+    unsigned long long* d_gpivot = nullptr;  // per query: streaming top-k state (threshold, mapping, count, flag, histogram)
+    uint64_t* d_gbuf = nullptr;              // per query: gcap candidate keys of the tensor-core kernel
+    uint32_t gcap = 0;
+    size_t gstate_bytes = 0;
     uint32_t n_items = 0;
     uint32_t max_parts = 1;  // most candidate lists any query has
     uint32_t list_cap = 0;   // slots per candidate list: k plus the slack the tensor-core kernel's last selection may leave
@@ -119,10 +123,10 @@ struct Plan {
     bool tq3 = false;
     int codec_hint_in = -1;
     bool force_generic_in = false;
-    int mma_threads = 256;
-    uint32_t mma_cap = 0, mma_grid = 0;
+    int mma_threads = STREAM_THREADS;
+    uint32_t mma_grid = 0;
     size_t mma_smem = 0;
-    DevBuf b_items, b_qbegin, b_qcount, b_keys, b_cnt, b_retry, b_cta, b_gpivot, b_vq, b_tmp;
+    DevBuf b_items, b_qbegin, b_qcount, b_keys, b_cnt, b_retry, b_cta, b_gpivot, b_gbuf, b_vq, b_tmp;
     // Two-level merge for calls with few queries and many candidate lists per query (a pool scored
     // by one GQA group: 148 lists each): groups of `group_parts` lists are merged by a CTA each into
     // `n_groups` intermediate (index, score) lists per query, which a second launch merges.
@@ -184,13 +188,12 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
         return Status(SLHA_ERR_CAPACITY, "top-k: k is too large for the shared-memory selection state");
     p->cap = cap;
 
-    // tensor-core kernel: persistent CTAs (one per SM unless shared memory allows more)
-    p->mma_threads = 512;  // 16 warps: the kernel deals sets round-robin with a power-of-two mask
+    // tensor-core kernel: one persistent CTA per SM
+    p->mma_threads = STREAM_THREADS;
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
     {
         const int mw = p->mma_threads / 32;
-        const uint32_t mround = (uint32_t)mw * 2 * MMA_SET_TILES;  // appends that may follow a raised flag
         // Codec hint: the flags of the first tile of the first non-empty segment decide
         // whether the NF4 table occupies shared memory.  A wrong hint costs speed only
         // (NF4 tiles met without the table are handed to the generic kernel).
@@ -210,14 +213,9 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
                 p->tq3 = (flags & F_TQ3) != 0;
                 break;
             }
-        // per query: one region per warp, so a multiple of the warp count (256 covers 8 and 16 warps)
-        uint32_t mcap = (std::max<uint32_t>(3 * k, k + 4 * mround) + 255) / 256 * 256;
-        while (mcap > k + 2 * mround && mma_smem_bytes(mw, mcap, p->nf4_table) > MAX_SMEM) mcap -= 256;
-        p->use_mma = !g_force_generic && mma_smem_bytes(mw, mcap, p->nf4_table) <= MAX_SMEM;
-        p->mma_cap = mcap;
-        p->mma_smem = mma_smem_bytes(mw, mcap, p->nf4_table);
-        const uint32_t per_sm = (uint32_t)std::max<size_t>(1, MAX_SMEM / (p->mma_smem + 1024));
-        p->mma_grid = (uint32_t)sms * per_sm;
+        p->mma_smem = mma_smem_bytes(mw, p->nf4_table);
+        p->use_mma = !g_force_generic && p->mma_smem <= MAX_SMEM;
+        p->mma_grid = (uint32_t)sms;
     }
 
     // Work items.  Generic kernel: fixed-size runs, large enough that candidate
@@ -306,7 +304,21 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     SLHA_TRY(p->b_cnt.ensure((size_t)n_lists * 4));
     SLHA_TRY(p->b_retry.ensure(all.size() * 4));
     SLHA_TRY(p->b_cta.ensure(cta_begin.size() * 4));
-    SLHA_TRY(p->b_gpivot.ensure(nq * (8 + 8 + 1024)));  // thresholds, bucket mappings, histograms
+    // Streaming top-k state per query row: threshold, bucket mapping, count, flag, 256 bucket counts; and
+    // the row's candidate buffer.  In random order about k (1 + ln(n / k)) tiles pass the rising threshold
+    // plus the unfiltered first sets of every warp; 16 k slots (at most the longest segment) leave a wide
+    // margin, and a row that fills its buffer all the same is scored by the generic kernel.
+    // (a warp reserves slots in chunks of 16 per row and work item, so up to 16 slots per warp and item stay unused)
+    uint32_t longest = 0;
+    for (size_t i = 0; i < n_segs; ++i) longest = std::max(longest, segs[i].n_tiles);
+    const uint64_t all_of_a_row = (uint64_t)longest + 16ull * (uint64_t)(p->mma_threads / 32) * p->max_parts + 64;
+    // (the first set of every warp that scans a row is appended unfiltered: 16 slots per warp and item, twice over)
+    const uint64_t first_sets = 32ull * (uint64_t)(p->mma_threads / 32) * p->max_parts;
+    p->gcap = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(std::max<uint64_t>(16ull * k, 4096), first_sets + 4ull * k), all_of_a_row / 64 * 64);
+    p->gstate_bytes = nq * (8 + 8 + 4 + 4 + 1024);
+    SLHA_TRY(p->b_gpivot.ensure(p->gstate_bytes));
+    if (p->use_mma) SLHA_TRY(p->b_gbuf.ensure(nq * (size_t)p->gcap * 8));
+    p->d_gbuf = (uint64_t*)p->b_gbuf.p;
     p->d_items = (WorkItem*)p->b_items.p;
     p->d_q_list_begin = (uint32_t*)p->b_qbegin.p;
     p->d_q_list_count = (uint32_t*)p->b_qcount.p;
@@ -319,7 +331,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     // (pageable sources: cudaMemcpyAsync returns once they are staged, so the vectors may die)
     SLHA_CUDA(cudaMemcpyAsync(p->d_cta_begin, cta_begin.data(), cta_begin.size() * 4, cudaMemcpyHostToDevice, c->stream));
     p->n_groups = 0;
-    if (nq <= 64 && p->max_parts >= 24) {
+    if (nq <= 64 && p->max_parts >= 24 && !p->use_mma) {
         uint32_t G = 1;
         while (G * G < p->max_parts) ++G;
         const uint32_t ng = (p->max_parts + G - 1) / G;
@@ -420,52 +432,45 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     cudaEvent_t* tev = timed ? &g_timing.ev[3 * g_timing.calls] : nullptr;
     if (timed) SLHA_CUDA(cudaEventRecord(tev[0], c->stream));
     const bool mma = p->use_mma && !prefer_generic;
+    ScoreArgs am{};
     if (mma) {
-        SLHA_CUDA(cudaMemsetAsync(p->d_retry, 0, (size_t)p->n_items * 4, c->stream));
-        SLHA_CUDA(cudaMemsetAsync(p->d_gpivot, 0, nq * (8 + 8 + 1024), c->stream));
-        ScoreArgs a{};
+        SLHA_CUDA(cudaMemsetAsync(p->d_gpivot, 0, p->gstate_bytes, c->stream));
+        ScoreArgs& a = am;
         a.tiles = reinterpret_cast<const unsigned char*>(tiles);
         a.state = state;
         a.items = p->d_items;
         a.n_items = p->n_items;
         a.retry = p->d_retry;
         a.cta_begin = p->d_cta_begin;
-        a.gpivot = p->d_gpivot;
-        a.grange = p->d_gpivot + nq;
-        a.ghist = reinterpret_cast<uint32_t*>(p->d_gpivot + 2 * nq);
+        // (histograms first: they are read with 16-byte loads)
+        a.ghist = reinterpret_cast<uint32_t*>(p->d_gpivot);
+        a.gpivot = p->d_gpivot + 128 * nq;
+        a.grange = a.gpivot + nq;
+        a.gcount = reinterpret_cast<uint32_t*>(a.grange + nq);
+        a.gflag = a.gcount + nq;
+        a.gbuf = p->d_gbuf;
+        a.gcap = p->gcap;
         a.nf4_table = p->nf4_table ? 1u : 0u;
         a.mixed = p->mixed ? 1u : 0u;
         a.q_coarse = d_q_coarse;
         a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);
         a.k = k;
-        a.list_cap = p->list_cap;
-        a.cap = p->mma_cap;
-        a.cand_keys = p->d_cand_keys;
-        a.cand_cnt = p->d_cand_cnt;
         static thread_local bool mma_configured[16] = {false};  // the attribute is per device
         if (!mma_configured[c->device & 15]) {
-            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            SLHA_CUDA(cudaFuncSetAttribute(score_mma_kernel<true, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_stream_kernel<0, STREAM_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_stream_kernel<1, STREAM_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_stream_kernel<2, STREAM_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_stream_kernel<3, STREAM_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
             mma_configured[c->device & 15] = true;
         }
-        // eight or more CTAs per query (a long segment cut over the grid): first thresholds early (config 5: 0.329 -> 0.317 ms;
-        // a 1 M-slot pool scored by one GQA group: 0.200 -> 0.114 ms)
-        const bool early = p->max_parts >= 8;
-        // 3: no NF4 tile is expected, so the launch holds INT4 / MX-INT4 tiles only (any other tile is handed back)
+        // 3: no NF4 tile is expected, so the launch holds INT4 / MX-INT4 tiles only (any other tile hands its rows back)
         const int kind = p->tq3 ? 2 : (p->mixed ? 1 : (p->nf4_table ? 0 : 3));
-#define SLHA_LAUNCH_MMA(K, E) score_mma_kernel<true, K, E><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a)
-        if (early) {
-            if (kind == 3) SLHA_LAUNCH_MMA(3, true); else if (kind == 2) SLHA_LAUNCH_MMA(2, true); else if (kind == 1) SLHA_LAUNCH_MMA(1, true); else SLHA_LAUNCH_MMA(0, true);
-        } else {
-            if (kind == 3) SLHA_LAUNCH_MMA(3, false); else if (kind == 2) SLHA_LAUNCH_MMA(2, false); else if (kind == 1) SLHA_LAUNCH_MMA(1, false); else SLHA_LAUNCH_MMA(0, false);
-        }
+#define SLHA_LAUNCH_MMA(K) score_stream_kernel<K, STREAM_THREADS><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a)
+        if (kind == 3) SLHA_LAUNCH_MMA(3); else if (kind == 2) SLHA_LAUNCH_MMA(2); else if (kind == 1) SLHA_LAUNCH_MMA(1); else SLHA_LAUNCH_MMA(0);
 #undef SLHA_LAUNCH_MMA
+        count_launch();
+        SLHA_CUDA(cudaGetLastError());
+        stream_mark_retry_kernel<<<(p->n_items + 255) / 256, 256, 0, c->stream>>>(p->d_items, p->n_items, a.gflag, p->d_retry);
         count_launch();
         SLHA_CUDA(cudaGetLastError());
     }
@@ -489,9 +494,16 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     if (!configured[c->device & 15]) {
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<CompLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+        SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<StreamLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
         configured[c->device & 15] = true;
     }
-    if (p->n_groups) {
+    if (mma) {
+        StreamLists L{p->d_gbuf, am.gcount, am.gflag, am.gpivot, p->gcap,
+                      CompLists{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, p->list_cap}};
+        const uint32_t cap_s = merge_cap((uint64_t)p->gcap, p->kp2, k);
+        topk_merge_kernel<StreamLists><<<(uint32_t)nq, merge_threads(cap_s), merge_smem(cap_s, p->kp2), c->stream>>>(
+            L, k, p->kp2, cap_s, d_out_index, d_out_score, d_out_count);
+    } else if (p->n_groups) {
         // few queries, many lists each: groups of lists first, then the groups' results
         CompLists L1{p->d_cand_keys, p->d_cand_cnt, p->d_vq_begin, p->d_vq_count, p->list_cap};
         const uint32_t cap1 = merge_cap((uint64_t)p->group_parts * p->list_cap, p->kp2, k);

@@ -8,12 +8,9 @@
 namespace slha {
 namespace {
 
-#ifdef SLHA_SCORE_PROFILE
-__device__ unsigned long long g_merge_prof[8];  // development aid: summed phase cycles of the merge CTAs
-#endif
-
 // Candidate accessors: element e of query Q as a composite key, 0 = absent.
 struct CompLists {  // lists written by score_kernel
+    static constexpr bool kFiltered = false;
     const uint64_t* keys;      // [n_lists][k] (k here = slots per list, >= the k asked for)
     const uint32_t* cnt;       // [n_lists]
     const uint32_t* q_list_begin;  // [nq]
@@ -32,7 +29,30 @@ struct CompLists {  // lists written by score_kernel
         return j < cnt[l] ? keys[(size_t)l * k + j] : 0ull;
     }
 };
+// Candidates of the streaming tensor-core kernel: one buffer per query row (keys below the row's
+// final threshold count as absent), or - for rows that kernel handed to the generic kernel - the
+// generic kernel's per-work-item lists.
+struct StreamLists {
+    static constexpr bool kFiltered = true;
+    const uint64_t* gbuf;                // [nq][gcap]
+    const uint32_t* gcount;              // [nq]
+    const uint32_t* gflag;               // [nq]
+    const unsigned long long* gpivot;    // [nq]
+    uint32_t gcap;
+    CompLists items;
+    __device__ uint32_t len0(uint32_t Q) const { return min(gcount[Q], gcap); }
+    __device__ uint32_t size(uint32_t Q) const { return gflag[Q] ? items.size(Q) : len0(Q); }
+    __device__ uint32_t lists(uint32_t Q) const { return gflag[Q] ? items.lists(Q) : 1u; }
+    __device__ uint32_t list_len(uint32_t Q, uint32_t part) const { return gflag[Q] ? items.list_len(Q, part) : len0(Q); }
+    __device__ uint64_t at(uint32_t Q, uint32_t part, uint32_t j) const {
+        if (gflag[Q]) return items.at(Q, part, j);
+        const uint64_t key = gbuf[(size_t)Q * gcap + j];
+        return key >= gpivot[Q] ? key : 0ull;
+    }
+    __device__ uint64_t get(uint32_t Q, uint32_t e) const { return gflag[Q] ? items.get(Q, e) : (e < len0(Q) ? at(Q, 0, e) : 0ull); }
+};
 struct PairLists {  // (index, score) lists laid out [list][query][k_in]
+    static constexpr bool kFiltered = false;
     const uint32_t* idx;
     const float* score;
     uint32_t n_lists, n_queries, k_in;
@@ -191,62 +211,55 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
     int* n_s = hist + max(SEL_HIST_INTS, merge_buckets(kp2, blockDim.x) + 48);
     const uint32_t Q = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
     const uint32_t T = L.size(Q);
-#ifdef SLHA_SCORE_PROFILE
-    const long long mt0 = clock64();
-#define MPROF(i, v) do { if (tid == 0) atomicAdd(&g_merge_prof[(i)], (unsigned long long)(v)); } while (0)
-#else
-#define MPROF(i, v)
-#endif
 
     // upper bound of the number of candidates
     uint32_t total = 0;
     for (uint32_t l = 0; l < L.lists(Q); ++l) total += L.list_len(Q, l);
-    if (total <= cap_s) {
+    // Lists that drop keys below a known threshold while they are read (Lists::kFiltered) hold far
+    // fewer present keys than slots: one gathering pass usually fits them into shared memory.
+    bool gathered = false;
+    if (total <= cap_s || Lists::kFiltered) {
         if (tid == 0) *n_s = 0;
         __syncthreads();
         for (uint32_t l = 0; l < L.lists(Q); ++l) {
             const uint32_t len = L.list_len(Q, l);
-            for (uint32_t j0 = 0; j0 < len; j0 += nt) {
-                const uint32_t j = j0 + tid;
-                const uint64_t key = j < len ? L.at(Q, l, j) : 0ull;
-                const unsigned bal = __ballot_sync(0xFFFFFFFFu, key != 0ull);
-                int base = 0;
-                if ((tid & 31) == 0 && bal) base = atomicAdd(n_s, __popc(bal));
-                base = __shfl_sync(0xFFFFFFFFu, base, 0);
-                if (key) buf[base + __popc(bal & ((1u << (tid & 31)) - 1))] = key;
+            // four keys per round: the loads go out together, then the compaction
+            for (uint32_t j0 = 0; j0 < len; j0 += 4 * nt) {
+                uint64_t key[4];
+#pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) key[u] = j0 + u * nt + tid < len ? L.at(Q, l, j0 + u * nt + tid) : 0ull;
+#pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const unsigned bal = __ballot_sync(0xFFFFFFFFu, key[u] != 0ull);
+                    if (!bal) continue;
+                    int base = 0;
+                    if ((tid & 31) == 0) base = atomicAdd(n_s, __popc(bal));
+                    base = __shfl_sync(0xFFFFFFFFu, base, 0);
+                    const uint32_t at = (uint32_t)base + __popc(bal & ((1u << (tid & 31)) - 1));
+                    if (key[u] && at < cap_s) buf[at] = key[u];
+                }
             }
         }
         __syncthreads();
+        gathered = (uint32_t)*n_s <= cap_s;
+        __syncthreads();
+    }
+    if (gathered) {
         const uint32_t present = (uint32_t)*n_s;
         __syncthreads();
-#ifdef SLHA_SCORE_PROFILE
-        const long long mt1 = clock64();
-        MPROF(0, mt1 - mt0); MPROF(4, 1); MPROF(5, present);
-#endif
         if (present > k) {
             // bucket selection on the score word; equal scores around the k-th place
             // fall back to the exact radix selection, which also orders by index
             if (tid == 0) *pivot_s = 0ull;
             __syncthreads();
-            if (block_select_multi(buf, cap_s, n_s, 1, k, 0u, (int)k, pivot_s, hist)) {
-                MPROF(6, 1);
-                block_select_topk(buf, n_s, k, pivot_s, hist);
-            }
+            if (block_select_multi(buf, cap_s, n_s, 1, k, 0u, (int)k, pivot_s, hist)) block_select_topk(buf, n_s, k, pivot_s, hist);
         }
-#ifdef SLHA_SCORE_PROFILE
-        const long long mt2 = clock64();
-        MPROF(1, mt2 - mt1);
-#endif
         const uint32_t m = present < k ? present : k;
         for (uint32_t i = m + tid; i < kp2; i += nt) buf[i] = 0ull;
         __syncthreads();
         sort_and_emit(buf, cap_s, hist, kp2, m, k, Q, out_index, out_score, out_count);
-#ifdef SLHA_SCORE_PROFILE
-        MPROF(2, clock64() - mt2);
-#endif
         return;
     }
-    MPROF(7, 1);
 
     // Too many candidates for shared memory: one bucket pass over the lists where
     // they lie (256 equal-width score buckets between the smallest and the largest

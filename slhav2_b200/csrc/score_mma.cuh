@@ -1,32 +1,26 @@
-// Tensor-core variant of the fused score + top-k kernel for the nibble codecs
-// (uniform / MX INT4 and NF4), the layouts of decode KV caches.
-// Included by score.cu.
+// Tensor-core kernel of the fused score + top-k path (score_stream_kernel) and the selection
+// routine the merge kernel shares with it.  Included by score.cu.
 //
-// With a GQA group of four queries the CUDA-core kernel is bound by instruction
-// issue (128 FMAs per tile and query plus the nibble decode), not by HBM.  Here
-// the coarse dot product of eq. 2.3 is an m16n8k16 MMA per 16 tiles and
-// 16-dim scale group:
-//   A (16 tiles x 16 dims)  = the group's nibbles turned into exact fp16 levels
-//                             (n - 8 by an fp16 magic-number trick, or the NF4
-//                             codebook entry as an fp16 hi + lo pair from a
-//                             bank-replicated shared-memory table); odd k slots
-//                             hold 16x the level, which the trick yields for free,
-//   B (16 dims x 8 columns) = the four queries, each as an fp16 hi and lo
-//                             column (q = hi + lo keeps ~22 bits), so a thread's
-//                             two accumulator columns add up to one query; even k
-//                             slots hold 16x the query, so every product is 16x
-//                             and the sum is divided by 16 at the end (exact),
-//   D fp32, started from zero for every group and folded into the running score
-//   with the tile's effective group scale (scale * gs[j] / 255) on the CUDA
-//   cores, which is what keeps per-group micro-scaling exact.
-// The MMA's k index is permuted (identically for A and B) so that the four k
-// slots a thread owns are the four nibbles of one 16-bit word of the tile.
-// The Hamming term is 8 XOR + POPC per tile and query.  Tiles are staged by
-// cp.async into a per-warp ring whose rows are padded to 144 bytes: every
-// shared-memory address of the inner loop is then "row base + immediate" and
-// all fragment loads are conflict-free without an XOR swizzle.
-// Tiles of any other codec make the CTA hand the whole work item back
-// (retry flag) to score_kernel, which is launched right after.
+// With a GQA group of four queries the CUDA-core kernel is bound by instruction issue (128 FMAs
+// per tile and query plus the nibble decode), not by HBM.  Here the coarse dot product of eq. 2.3
+// runs as m16n8k16 MMAs over sets of 16 tiles:
+//   A (16 tiles x 16 k slots) = exact fp16 levels made from the tiles' nibbles in registers,
+//   B (16 k slots x 8 columns) = the four queries, each as an fp16 hi and lo column
+//                                (q = hi + lo keeps ~22 bits), so a thread's two accumulator
+//                                columns add up to one query; fragments live in shared memory,
+//   D fp32.
+// Two arrangements of A exist.  Per scale group (NF4, mixed 8/4, TQ3 and INT4 tiles met in such
+// launches): one MMA per 16-dim group, levels n - 8 by an fp16 magic-number trick or NF4 codebook
+// entries as hi + lo pairs from a bank-replicated shared-memory table, D started from zero per
+// group and folded into the score with the tile's effective group scale on the CUDA cores; the
+// MMA's k index is permuted so that the four k slots a thread owns are the four nibbles of one
+// 16-bit word, odd slots carry 16x the level and B's even slots 16x the query (all exact).
+// Contiguous (launches of INT4 / MX-INT4 tiles only): a thread owns 16 latent bytes of a row, the
+// group scale is folded into A exactly, and the eight MMAs of a set chain on two accumulators.
+// The Hamming term is 8 XOR + POPC per tile and query.  Tiles are staged by cp.async into a per-warp
+// ring whose rows are padded to 144 bytes: every shared-memory address of the inner loop is "row
+// base + immediate".  Candidates go to per-row buffers in global memory (see score_stream_kernel).
+// A tile of another codec than the launch decodes hands its query rows to score_kernel.
 #pragma once
 
 namespace slha {
@@ -40,7 +34,11 @@ constexpr int MMA_HALF = 8 * MMA_ROW;                      // row g -> row g + 8
 #ifndef SLHA_MMA_DEPTH
 #define SLHA_MMA_DEPTH 2
 #endif
+#ifndef SLHA_STREAM_THREADS
+#define SLHA_STREAM_THREADS 768  // 24 warps at 80 registers: the streaming kernel hides its latencies with warps
+#endif
 constexpr int MMA_DEPTH = SLHA_MMA_DEPTH;                  // cp.async ring slots per warp
+constexpr int MMA_BQ_BYTES = 9 * 32 * 8;                   // B fragments of a work item: [9][32 lanes] x 8 bytes
 constexpr int NF4_LUT_BYTES = 256 * 16 * 8;                // [byte][16 lanes] x (hi pair, lo pair)
 constexpr int SEL_HIST_INTS = 4 * 256 + 48;                // block_select_multi: 4 histograms + state
 
@@ -166,8 +164,9 @@ __device__ __forceinline__ int popc8(const uint4& a, const uint4& b, const uint3
 // 2t and 2t+1 as byte - 128 while slots 2t+8 and 2t+9 stay empty; groups 1..7 are INT4 groups of
 // dims 16 J - 8 ..; the B operand is arranged to match when the launch scores mixed tiles).
 template <int MODE, int J>
-__device__ __forceinline__ void coarse_group(uint32_t hb, uint32_t lut_lane, uint32_t magic, const uint32_t (&bq)[8][2], uint32_t f0,
+__device__ __forceinline__ void coarse_group(uint32_t hb, uint32_t lut_lane, uint32_t magic, uint32_t bqa, uint32_t f0,
                                              uint32_t f1, const uint4& x0, const uint4& x1, float& acc0, float& acc1) {
+    const uint2 bq = lds_v2<256 * J>(bqa);  // this lane's B fragment of group J
     const uint32_t h0 = lds_u16<8 * J>(hb), h1 = lds_u16<8 * J + MMA_HALF>(hb);
     uint32_t a0, a1, a2, a3, l0 = 0, l1 = 0, l2 = 0, l3 = 0;
     const bool n0 = MODE == 1 || (MODE == 2 && (f0 & F_NF4));
@@ -198,8 +197,8 @@ __device__ __forceinline__ void coarse_group(uint32_t hb, uint32_t lut_lane, uin
     }
     }
     float d[4];
-    mma_f16_zero(d, a0, a1, a2, a3, bq[J][0], bq[J][1]);
-    if (MODE == 1 || MODE == 2) mma_f16(d, l0, l1, l2, l3, bq[J][0], bq[J][1]);
+    mma_f16_zero(d, a0, a1, a2, a3, bq.x, bq.y);
+    if (MODE == 1 || MODE == 2) mma_f16(d, l0, l1, l2, l3, bq.x, bq.y);
     // gs[J] as float: byte J of (x.z, x.w)
     const uint32_t gw0 = J < 4 ? x0.z : x0.w, gw1 = J < 4 ? x1.z : x1.w;
     // (byte -> float on the ALU / FMA pipes: 2^23 + b as a bit pattern, minus 2^23)
@@ -208,7 +207,7 @@ __device__ __forceinline__ void coarse_group(uint32_t hb, uint32_t lut_lane, uin
 }
 
 template <int MODE>
-__device__ __forceinline__ void coarse_set(uint32_t hb, uint32_t lut_lane, uint32_t magic, const uint32_t (&bq)[8][2], uint32_t f0,
+__device__ __forceinline__ void coarse_set(uint32_t hb, uint32_t lut_lane, uint32_t magic, uint32_t bq, uint32_t f0,
                                            uint32_t f1, const uint4& x0, const uint4& x1, float& acc0, float& acc1) {
     acc0 = 0.0f;
     acc1 = 0.0f;
@@ -250,7 +249,7 @@ __device__ __forceinline__ void int4c_word(uint32_t w, uint32_t G, uint32_t C, u
     o[3] = hfma2_u32((w >> 8) & 0x00F000F0u, G, C);  // nibbles 3, 7
 }
 // rb = shared address of row g of the staged set; t = lane & 3
-__device__ __forceinline__ void coarse_set_int4c(uint32_t rb, uint32_t t, uint32_t magic, const uint32_t (&bq)[8][2], float& acc0, float& acc1) {
+__device__ __forceinline__ void coarse_set_int4c(uint32_t rb, uint32_t t, uint32_t magic, uint32_t bqa, float& acc0, float& acc1) {
     const uint32_t cb = rb + 16u * t, hb = rb + 2u * t;
     const uint4 L0 = lds_v4<0>(cb), L1 = lds_v4<MMA_HALF>(cb);
     const uint32_t h0 = lds_u16<120>(hb), h1 = lds_u16<120 + MMA_HALF>(hb);
@@ -258,32 +257,27 @@ __device__ __forceinline__ void coarse_set_int4c(uint32_t rb, uint32_t t, uint32
     int4c_scales(h0, magic, G00, C00, G01, C01);
     int4c_scales(h1, magic, G10, C10, G11, C11);
     const uint32_t w0[4] = {L0.x, L0.y, L0.z, L0.w}, w1[4] = {L1.x, L1.y, L1.z, L1.w};
-    float d[4];
+    // two accumulator chains (even / odd MMAs) halve the dependent MMA latency of a set
+    float d[4], e[4];
+    const uint2 b0 = lds_v2<0>(bqa), b1 = lds_v2<256>(bqa), b2 = lds_v2<512>(bqa), b3 = lds_v2<768>(bqa);
+    const uint2 b4 = lds_v2<1024>(bqa), b5 = lds_v2<1280>(bqa), b6 = lds_v2<1536>(bqa), b7 = lds_v2<1792>(bqa);
+    const uint2 bq[8] = {b0, b1, b2, b3, b4, b5, b6, b7};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         uint32_t o0[4], o1[4];
         int4c_word(w0[i], i < 2 ? G00 : G01, i < 2 ? C00 : C01, o0);
         int4c_word(w1[i], i < 2 ? G10 : G11, i < 2 ? C10 : C11, o1);
-        if (i == 0) mma_f16_zero(d, o0[0], o1[0], o0[1], o1[1], bq[0][0], bq[0][1]);
-        else mma_f16(d, o0[0], o1[0], o0[1], o1[1], bq[2 * i][0], bq[2 * i][1]);
-        mma_f16(d, o0[2], o1[2], o0[3], o1[3], bq[2 * i + 1][0], bq[2 * i + 1][1]);
+        if (i == 0) {
+            mma_f16_zero(d, o0[0], o1[0], o0[1], o1[1], bq[0].x, bq[0].y);
+            mma_f16_zero(e, o0[2], o1[2], o0[3], o1[3], bq[1].x, bq[1].y);
+        } else {
+            mma_f16(d, o0[0], o1[0], o0[1], o1[1], bq[2 * i].x, bq[2 * i].y);
+            mma_f16(e, o0[2], o1[2], o0[3], o1[3], bq[2 * i + 1].x, bq[2 * i + 1].y);
+        }
     }
-    acc0 = d[0] + d[1];
-    acc1 = d[2] + d[3];
+    acc0 = (d[0] + e[0]) + (d[1] + e[1]);
+    acc1 = (d[2] + e[2]) + (d[3] + e[3]);
 }
-
-#ifdef SLHA_SCORE_PROFILE
-// development aid (never built into the shipped library): per-CTA cycle counts of warp 0
-__device__ unsigned long long g_score_prof[148 * 8];
-__device__ unsigned long long g_sel_prof[148 * 8];  // calls, passes, refines, ties, cycles: minmax, passes, compaction
-#define SEL_ADD(i, v) do { if (threadIdx.x == 0 && nq > 1 && blockIdx.x < 148) atomicAdd(&g_sel_prof[blockIdx.x * 8 + (i)], (unsigned long long)(v)); } while (0)
-#define PROF_T(x) const long long x = clock64()
-#define PROF_ADD(i, v) do { if (tid == 0) prof[i] += (unsigned long long)(v); } while (0)
-#else
-#define SEL_ADD(i, v)
-#define PROF_T(x)
-#define PROF_ADD(i, v)
-#endif
 
 // Bucket of a score inside [smin, smin + 256 / inv): monotone in the score.
 __device__ __forceinline__ int sel_bucket_f(float sc, float smin, float inv) {
@@ -338,8 +332,6 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
     }
     __syncthreads();
     if (!(st[6] | st[14] | st[22] | st[30])) return 0u;
-    SEL_ADD(0, 1);
-    PROF_T(ts0);
     // smallest and largest score at or above the pivot
     for (int q = 0; q < nq; ++q) {
         if (!st[8 * q + 3]) continue;
@@ -357,11 +349,8 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
         if (lane == 0) { atomicMax(&st[8 * q + 1], mx); atomicMin(&st[8 * q], mn); }
     }
     __syncthreads();
-    PROF_T(ts1);
-    SEL_ADD(4, ts1 - ts0);
     for (int pass = 0; pass < 12; ++pass) {
         if (!(st[3] | st[11] | st[19] | st[27])) break;
-        SEL_ADD(1, 1);
         for (int b = tid; b < 1024; b += nt) hist[b] = 0;
         __syncthreads();
         for (int q = 0; q < nq; ++q) {
@@ -435,7 +424,6 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
             }
         }
         if (!__syncthreads_or(refine)) continue;
-        SEL_ADD(2, 1);
         // smallest and largest score inside the pivotal bucket of the queries still active
         uint32_t nlo[4], nhi[4];
 #pragma unroll
@@ -463,8 +451,6 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
             if (q < nq && st[8 * q + 3] && lane == 0) { atomicMin(&st[8 * q], nlo[q]); atomicMax(&st[8 * q + 1], nhi[q]); }
         __syncthreads();
     }
-    PROF_T(ts2);
-    SEL_ADD(5, ts2 - ts1);
     // (a range that is still open after the last pass stays whole and goes to the exact selection)
     if (tid < 4) {
         if (st[8 * tid + 3]) { st[8 * tid + 3] = 0u; st[8 * tid + 4] = 1u; st[8 * tid + 7] = 0u; }
@@ -589,480 +575,93 @@ __device__ uint32_t block_select_multi(uint64_t* keys, uint32_t cap, int* cnt, i
     for (int q = 0; q < 4; ++q)
         if (st[8 * q + 6] && st[8 * q + 4] && st[8 * q + 5] > k + slack) ties |= 1u << q;
     __syncthreads();
-    PROF_T(ts3);
-    SEL_ADD(6, ts3 - ts2);
-    SEL_ADD(3, ties != 0u);
     return ties;
 }
 
-// State of one work item of score_mma_kernel that its helper functions share.
-struct MmaItem {
-    uint64_t* keys;    // [4][nwarps][rs] candidate regions
-    uint64_t* pivot;   // [4]
-    int* cntw;         // [4][32] published region counts
-    int* bail;
-    float2* rng;       // [4]
-    int* hist;         // SEL_HIST_INTS
-    uint32_t rs;       // slots per region
-    int room;          // rs - MMA_SET_TILES
-    uint32_t sel_slack;
-    uint32_t query_begin;
-    int nq;
-};
 
-// Thresholds are shared between the CTAs that scan the same query's tiles: a CTA's
-// pivot (k of its own elements are >= it) is a proven lower bound of the query's k-th
-// best composite key, so the maximum over CTAs is too.  Lanes 0..nq-1 of one warp.
-__device__ __forceinline__ void mma_refresh_pivots(const ScoreArgs& a, const MmaItem& m, int lane) {
-    if (lane < m.nq) {
-        const unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(a.gpivot + m.query_begin + lane);
-        if (seen > m.pivot[lane]) m.pivot[lane] = seen;
+// ---- streaming top-k state shared by all CTAs -----------------------------------------------
+// Per query row, in global memory (L2-resident), zeroed by one memset per call:
+//   gpivot  best proven lower bound of the row's k-th best composite key (score word in the high half)
+//   grange  bucket mapping (smin, inv) of the row's score histogram, 0 = none yet
+//   gcount  candidates appended to the row's buffer so far
+//   gflag   1 = the generic kernel scores the row's work items instead (a tile of another codec,
+//           a query outside the fp16 split, or a full candidate buffer)
+//   ghist   256 bucket counts of the appended candidates
+// and one candidate buffer of gcap composite keys per row.  A CTA keeps no candidates of its own:
+// a tile whose score reaches the row's threshold is appended to the row's buffer (one atomic per
+// warp, query and set), counted in the row's histogram, and the threshold is re-derived from that
+// histogram from time to time - the counts are of real tiles, so the lower edge of the highest
+// bucket whose count from the top reaches k is a proven lower bound of the k-th best score, for
+// all CTAs at once.  Nothing in the hot loop waits for another warp or CTA.
+
+// A whole warp: raise the threshold of query row Q (shared word *pvh) from the row's histogram
+// and from what other CTAs have proven.
+__device__ __forceinline__ void stream_refresh_threshold(const ScoreArgs& a, uint32_t Q, float2 r, uint32_t* pvh, int lane) {
+    const unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(a.gpivot + Q);
+    uint32_t best = (uint32_t)(seen >> 32);
+    if (r.y != 0.0f) {
+        const uint32_t* hq = a.ghist + (size_t)Q * 256 + 248 - 8 * lane;
+        uint32_t c[8];  // buckets 255-8l .. 248-8l (descending)
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[7]), "=r"(c[6]), "=r"(c[5]), "=r"(c[4]) : "l"(hq));
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[3]), "=r"(c[2]), "=r"(c[1]), "=r"(c[0]) : "l"(hq + 4));
+        uint32_t tot = 0;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) tot += c[jj];
+        uint32_t incl = tot;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += y;
+        }
+        const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= a.k);
+        uint32_t ek = 0;
+        if (ok != 0u && lane == __ffs(ok) - 1) {
+            uint32_t run = incl - tot;
+            int b = 0;
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                if (run + c[jj] >= a.k) { b = 255 - 8 * lane - jj; break; }
+                run += c[jj];
+            }
+            if (b >= 1) {
+                // half a bucket and a few ulps below the bucket's edge: every counted key of the
+                // buckets b.. is above this bound whatever the rounding of the bucket arithmetic
+                const uint32_t e = score_key(r.x + ((float)b - 0.5f) / r.y);
+                ek = e > 8u ? e - 8u : 0u;
+            }
+        }
+        ek = __reduce_max_sync(0xFFFFFFFFu, ek);
+        if (ek > best) {
+            best = ek;
+            if (lane == 0) atomicMax(a.gpivot + Q, (unsigned long long)ek << 32);
+        }
     }
+    if (lane == 0 && best > *reinterpret_cast<volatile uint32_t*>(pvh)) atomicMax(pvh, best);
 }
 
-// Shared score histogram of a query: every CTA counts the candidates it appends into
-// 256 buckets of global memory (one bucket mapping per query, published by the first
-// CTA that finishes a selection).  The counts are of real tiles, so the lower edge of
-// the highest bucket whose count from the top reaches k is a proven lower bound of the
-// query's k-th best score - for all CTAs at once, and without a block-wide selection.
-// A whole warp calls this for query q.
-__device__ __forceinline__ void mma_hist_pivot(const ScoreArgs& a, const MmaItem& m, int q, int lane) {
-    const float2 r = m.rng[q];
-    if (r.y == 0.0f) return;
-    const uint32_t* hq = a.ghist + (size_t)(m.query_begin + q) * 256 + 248 - 8 * lane;
-    uint32_t c[8];  // buckets 255-8l .. 248-8l (descending)
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[7]), "=r"(c[6]), "=r"(c[5]), "=r"(c[4]) : "l"(hq));
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[3]), "=r"(c[2]), "=r"(c[1]), "=r"(c[0]) : "l"(hq + 4));
-    uint32_t tot = 0;
-#pragma unroll
-    for (int jj = 0; jj < 8; ++jj) tot += c[jj];
-    uint32_t incl = tot;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-        if (lane >= o) incl += y;
-    }
-    const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= a.k);
-    if (ok == 0u || lane != __ffs(ok) - 1) return;
-    uint32_t run = incl - tot;
-    int b = 0;
-#pragma unroll
-    for (int jj = 0; jj < 8; ++jj) {
-        if (run + c[jj] >= a.k) { b = 255 - 8 * lane - jj; break; }
-        run += c[jj];
-    }
-    if (b < 1) return;
-    // half a bucket and a few ulps below the bucket's edge: every counted key of the
-    // buckets b.. is above this bound whatever the rounding of the bucket arithmetic
-    const float e = r.x + ((float)b - 0.5f) / fabsf(r.y);
-    const uint32_t ek = score_key(e);
-    const unsigned long long np = (unsigned long long)(ek > 8u ? ek - 8u : 0u) << 32;
-    if (np > m.pivot[q]) {
-        m.pivot[q] = np;
-        atomicMax(a.gpivot + m.query_begin + q, np);
-    }
-}
-
-// The calling warp drops the keys of its region of query tq that are below the pivot.
-// rc: the caller's count of the region of its own query t (updated when t == tq).
-__device__ __forceinline__ void mma_purge(const MmaItem& m, int tq, int warp, int nwarps, int lane, int t, int& rc) {
-    const int cn = __shfl_sync(0xFFFFFFFFu, rc, tq);  // lane tq is (g = 0, t = tq)
-    const uint64_t pv = m.pivot[tq];
-    uint64_t* reg = m.keys + (size_t)(tq * nwarps + warp) * m.rs;
-    const uint32_t lt_mask = (1u << lane) - 1u;
-    int kept = 0;
-    for (int i0 = 0; i0 < cn; i0 += 32) {
-        const int i = i0 + lane;
-        const uint64_t key = i < cn ? reg[i] : 0ull;
-        const bool keep = i < cn && key >= pv;
-        const unsigned bal = __ballot_sync(0xFFFFFFFFu, keep);  // all reads of the round are done
-        if (keep) reg[kept + __popc(bal & lt_mask)] = key;      // lands at or below its old slot
-        kept += __popc(bal);
-    }
-    __syncwarp();
-    if (t == tq) rc = kept;
-}
-
-// Selection over segmented candidate buffers.  Query q's candidates live in one
-// region per warp: m.keys[(q * nw + w) * rs ..] holds m.cntw[q * 32 + w] keys, appended
-// and purged by warp w alone.  For every query in `mask` this raises m.pivot[q] so that
-// between k and about k + slack of the query's keys stay at or above it; nothing is
-// moved - every warp purges its own regions against the new pivots afterwards.
-//
-// The first histogram pass uses the query's shared bucket mapping (m.rng; created from
-// the smallest and largest score in the buffer and published when the query has none
-// yet), so the same counts serve two purposes: they are added to the query's shared
-// histogram in global memory when this CTA's buffer has not been counted there yet
-// (mapping stored negated in m.rng), and they locate the bucket in which the count from
-// the top reaches k.  While that bucket is too full it becomes the next range, with 256
-// buckets between its smallest and largest score.  The new pivot is half a bucket below
-// the pivotal bucket's lower edge.  Returns the queries that cannot be settled this way
-// (equal or non-finite scores).  All threads of the block must call; warp w sweeps
-// region w.
-__device__ __noinline__ uint32_t block_select_seg(const ScoreArgs& a, const MmaItem& m, uint32_t mask, uint32_t slack) {
-    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nt >> 5;
-    const int nq = m.nq;
-    const uint32_t k = a.k;
-    int* hist = m.hist;
-    // [q][8]: 0 range lo, 1 range hi (score words, inclusive), 2 need, 3 active, 4 failed, 5 nothing to raise,
-    //         6 selected, 7 pivotal bucket (0xFFFFFFFF: the keys below the mapping)
-    uint32_t* st = reinterpret_cast<uint32_t*>(hist + 1024);
-    float* fm = reinterpret_cast<float*>(hist + 1024 + 32);           // [q][2] smin, inv of the current pass
-    uint32_t* below = reinterpret_cast<uint32_t*>(hist + 1024 + 40);  // [q] keys below the mapping (first pass)
-    uint32_t* flush = below + 4;                                      // [q] first-pass counts go to the shared histogram
-    if (tid < 4) {
-        const bool act = tid < nq && (mask >> tid & 1u);
-        uint32_t* s = st + 8 * tid;
-        s[0] = act ? (uint32_t)(m.pivot[tid] >> 32) : 0u;
-        s[1] = 0xFFFFFFFFu;
-        s[2] = k;
-        s[3] = act;
-        s[4] = 0u;
-        s[5] = 0u;
-        s[6] = act;
-        s[7] = 0u;
-        below[tid] = 0u;
-        flush[tid] = 0u;
-        reinterpret_cast<uint32_t*>(hist)[tid] = 0xFFFFFFFFu;  // smallest / largest score word for a new mapping
-        hist[4 + tid] = 0;
-    }
-    __syncthreads();
-    if (!(st[6] | st[14] | st[22] | st[30])) return 0u;
-    // queries without a mapping: smallest and largest score in the buffer
-    bool fresh = false;
-    for (int q = 0; q < nq; ++q) fresh |= st[8 * q + 3] && m.rng[q].y == 0.0f;
-    if (fresh) {
-        for (int q = 0; q < nq; ++q) {
-            if (!st[8 * q + 3] || m.rng[q].y != 0.0f) continue;
-            const uint64_t* kq = m.keys + (size_t)(q * nw + warp) * m.rs;
-            const int c = m.cntw[q * 32 + warp];
-            uint32_t mx = 0u, mn = 0xFFFFFFFFu;
-            for (int i = lane; i < c; i += 32) {
-                const uint32_t h = (uint32_t)(kq[i] >> 32);
-                mx = max(mx, h);
-                mn = min(mn, h);
-            }
-            mx = __reduce_max_sync(0xFFFFFFFFu, mx);
-            mn = __reduce_min_sync(0xFFFFFFFFu, mn);
-            if (lane == 0) { atomicMin(reinterpret_cast<uint32_t*>(hist) + q, mn); atomicMax(reinterpret_cast<uint32_t*>(hist) + 4 + q, mx); }
-        }
-        __syncthreads();
-        if (tid < nq && st[8 * tid + 3] && m.rng[tid].y == 0.0f) {
-            // from the smallest score to a quarter of the span above the largest; the first CTA to publish wins
-            const float lo = key_score(reinterpret_cast<uint32_t*>(hist)[tid]), top = key_score(reinterpret_cast<uint32_t*>(hist)[4 + tid]);
-            const float hi = top + 0.25f * (top - lo);
-            const float inv = 256.0f / (hi - lo);
-            if (isfinite(lo) && isfinite(hi) && isfinite(inv) && inv > 0.0f) {
-                const unsigned long long mine_r = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(inv) << 32);
-                const unsigned long long old = atomicCAS(a.grange + m.query_begin + tid, 0ull, mine_r);
-                const unsigned long long use = old ? old : mine_r;
-                m.rng[tid] = make_float2(__uint_as_float((uint32_t)use), -__uint_as_float((uint32_t)(use >> 32)));
-            } else {
-                st[8 * tid + 3] = 0u;
-                st[8 * tid + 4] = 1u;
-            }
-        }
-        __syncthreads();
-    }
-    if (tid < nq && st[8 * tid + 3]) {
-        const float2 r = m.rng[tid];
-        fm[2 * tid] = r.x;
-        fm[2 * tid + 1] = fabsf(r.y);
-        flush[tid] = r.y < 0.0f;
-    }
-    for (int pass = 0; pass < 12; ++pass) {
-        for (int b = tid; b < 1024; b += nt) hist[b] = 0;
-        __syncthreads();
-        if (!(st[3] | st[11] | st[19] | st[27])) break;
-        for (int q = 0; q < nq; ++q) {
-            if (!st[8 * q + 3]) continue;
-            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
-            const float smin = fm[2 * q], inv = fm[2 * q + 1];
-            const uint64_t* kq = m.keys + (size_t)(q * nw + warp) * m.rs;
-            const int c = m.cntw[q * 32 + warp];
-            for (int i = lane; i < c; i += 32) {
-                const uint32_t h = (uint32_t)(kq[i] >> 32);
-                if (h < lo || h > hi) continue;
-                const float sc = key_score(h);
-                if (sc < smin) atomicAdd(&below[q], 1u);
-                else atomicAdd(&hist[256 * q + sel_bucket_f(sc, smin, inv)], 1);
-            }
-        }
-        __syncthreads();
-        if (pass == 0) {
-            // this CTA's buffer enters the query's shared histogram
-            for (int b = tid; b < 1024; b += nt) {
-                const int q = b >> 8;
-                if (q < nq && flush[q] && hist[b]) atomicAdd(a.ghist + (size_t)(m.query_begin + q) * 256 + (b & 255), (uint32_t)hist[b]);
-            }
-        }
-        bool refine = false;
-        if (warp < nq && st[8 * warp + 3]) {
-            uint32_t* s = st + 8 * warp;
-            const int* hq = hist + 256 * warp;
-            const uint32_t need = s[2];
-            // lane l owns buckets 255-8l .. 248-8l (descending)
-            int c[8], tot = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) { c[j] = hq[255 - 8 * lane - j]; tot += c[j]; }
-            int incl = tot;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                if (lane >= o) incl += y;
-            }
-            const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= (int)need);
-            const int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
-            if (ok == 0u) {
-                if ((uint32_t)total + below[warp] < need) {
-                    // fewer than `need` keys at or above the pivot: nothing can be proven
-                    if (lane == 0) { s[3] = 0u; s[5] = 1u; }
-                } else {
-                    // the k-th key lies below the mapping: the keys down there are the next range
-                    refine = true;
-                    __syncwarp();
-                    if (lane == 0) { s[2] = need - (uint32_t)total; s[7] = 0xFFFFFFFFu; }
-                }
-            } else {
-                int bsel = 0, run = 0, binc = 0;
-                const int src = __ffs(ok) - 1;
-                if (lane == src) {
-                    run = incl - tot;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        if (run + c[j] >= (int)need) { bsel = 255 - 8 * lane - j; binc = c[j]; break; }
-                        run += c[j];
-                    }
-                }
-                bsel = __shfl_sync(0xFFFFFFFFu, bsel, src);
-                run = __shfl_sync(0xFFFFFFFFu, run, src);
-                binc = __shfl_sync(0xFFFFFFFFu, binc, src);
-                const uint32_t kept = (k - need) + (uint32_t)(run + binc);
-                if (kept <= k + slack) {
-                    if (lane == 0) { s[3] = 0u; s[7] = (uint32_t)bsel; }
-                } else {
-                    refine = true;  // next range: the scores of the pivotal bucket
-                    __syncwarp();
-                    if (lane == 0) { s[2] = need - (uint32_t)run; s[7] = (uint32_t)bsel; }
-                }
-            }
-        }
-        if (!__syncthreads_or(refine)) continue;
-        // smallest and largest score inside the pivotal bucket of the queries still active
-        uint32_t nlo[4], nhi[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) { nlo[q] = 0xFFFFFFFFu; nhi[q] = 0u; }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            if (q >= nq || !st[8 * q + 3]) continue;
-            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
-            const int bsel = (int)st[8 * q + 7];
-            const float smin = fm[2 * q], inv = fm[2 * q + 1];
-            const uint64_t* kq = m.keys + (size_t)(q * nw + warp) * m.rs;
-            const int c = m.cntw[q * 32 + warp];
-            for (int i = lane; i < c; i += 32) {
-                const uint32_t h = (uint32_t)(kq[i] >> 32);
-                if (h < lo || h > hi) continue;
-                const float sc = key_score(h);
-                const int b = sc < smin ? -1 : sel_bucket_f(sc, smin, inv);
-                if (b == bsel) { nlo[q] = min(nlo[q], h); nhi[q] = max(nhi[q], h); }
-            }
-            nlo[q] = __reduce_min_sync(0xFFFFFFFFu, nlo[q]);
-            nhi[q] = __reduce_max_sync(0xFFFFFFFFu, nhi[q]);
-        }
-        __syncthreads();  // every thread has read the old range
-        if (tid < 4 && tid < nq && st[8 * tid + 3]) { st[8 * tid] = 0xFFFFFFFFu; st[8 * tid + 1] = 0u; below[tid] = 0u; }
-        __syncthreads();
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-            if (q < nq && st[8 * q + 3] && lane == 0) { atomicMin(&st[8 * q], nlo[q]); atomicMax(&st[8 * q + 1], nhi[q]); }
-        __syncthreads();
-        if (tid < nq && st[8 * tid + 3]) {
-            float smin, inv;
-            if (sel_range(st[8 * tid], st[8 * tid + 1], smin, inv)) {
-                fm[2 * tid] = smin;
-                fm[2 * tid + 1] = inv;
-            } else {
-                st[8 * tid + 3] = 0u;  // one single score, too many keys: equal scores
-                st[8 * tid + 4] = 1u;
-            }
-        }
-    }
-    if (tid < 4 && st[8 * tid + 6] && st[8 * tid + 3]) { st[8 * tid + 3] = 0u; st[8 * tid + 4] = 1u; }  // still open after the last pass
-    __syncthreads();
-    // The new pivot is the smallest score of the pivotal bucket: exactly the keys counted
-    // above stay.  Warp w reports the minimum of its region, thread q combines them.
-    {
-        uint32_t* wmin = reinterpret_cast<uint32_t*>(hist);  // [q][32]
-#pragma unroll 1
-        for (int q = 0; q < nq; ++q) {
-            if (!st[8 * q + 6] || st[8 * q + 4] || st[8 * q + 5]) continue;
-            const uint32_t lo = st[8 * q], hi = st[8 * q + 1];
-            const int bsel = (int)st[8 * q + 7];
-            const float smin = fm[2 * q], inv = fm[2 * q + 1];
-            const uint64_t* kq = m.keys + (size_t)(q * nw + warp) * m.rs;
-            const int c = m.cntw[q * 32 + warp];
-            uint32_t mn = 0xFFFFFFFFu;
-            for (int i = lane; i < c; i += 32) {
-                const uint32_t h = (uint32_t)(kq[i] >> 32);
-                if (h < lo || h > hi) continue;
-                const float sc = key_score(h);
-                const int b = sc < smin ? -1 : sel_bucket_f(sc, smin, inv);
-                if (b == bsel) mn = min(mn, h);
-            }
-            mn = __reduce_min_sync(0xFFFFFFFFu, mn);
-            if (lane == 0) wmin[q * 32 + warp] = mn;
-        }
-        __syncthreads();
-        if (tid < nq && st[8 * tid + 6] && !st[8 * tid + 4] && !st[8 * tid + 5]) {
-            uint32_t mn = 0xFFFFFFFFu;
-            for (int w = 0; w < nw; ++w) mn = min(mn, wmin[tid * 32 + w]);
-            const uint64_t np = (uint64_t)mn << 32;
-            if (mn != 0xFFFFFFFFu && np > m.pivot[tid]) m.pivot[tid] = np;
-        }
-        if (tid < 4 && st[8 * tid + 6] && flush[tid]) m.rng[tid].y = fabsf(m.rng[tid].y);  // the buffer is counted: appends count themselves from now on
-    }
-    __syncthreads();
-    const uint32_t failed = (st[4] ? 1u : 0u) | (st[12] ? 2u : 0u) | (st[20] ? 4u : 0u) | (st[28] ? 8u : 0u);
-    __syncthreads();
-    return failed;
-}
-
-// Evens out the region counts of query q: warps holding more than the average hand
-// their surplus keys (the tail of their region) to warps holding less, through a
-// 512-key staging area in m.hist.  Any key may live in any region, so this only makes
-// room; it is needed when the best candidates cluster in the sets of a few warps.
-// All threads of the block; region counts published.  Returns the caller's count.
-__device__ __noinline__ int mma_rebalance(const MmaItem& m, int q, int rc) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5, t = lane & 3;
-    const int c = lane < nw ? m.cntw[q * 32 + lane] : 0;
-    const int total = __reduce_add_sync(0xFFFFFFFFu, c);
-    const int target = (total + nw - 1) / nw;
-    const int sur = lane < nw ? max(0, c - target) : 0, def = lane < nw ? max(0, target - c) : 0;
-    int s_in = sur, d_in = def;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int y = __shfl_up_sync(0xFFFFFFFFu, s_in, o), z = __shfl_up_sync(0xFFFFFFFFu, d_in, o);
-        if (lane >= o) { s_in += y; d_in += z; }
-    }
-    const int moved = __shfl_sync(0xFFFFFFFFu, s_in, 31);
-    const int c_me = __shfl_sync(0xFFFFFFFFu, c, warp);
-    const int sur_me = __shfl_sync(0xFFFFFFFFu, sur, warp), s_me = __shfl_sync(0xFFFFFFFFu, s_in - sur, warp);
-    const int def_me = __shfl_sync(0xFFFFFFFFu, def, warp), d_me = __shfl_sync(0xFFFFFFFFu, d_in - def, warp);
-    uint64_t* reg = m.keys + (size_t)(q * nw + warp) * m.rs;
-    uint64_t* staging = reinterpret_cast<uint64_t*>(m.hist);  // 512 keys
-    for (int c0 = 0; c0 < moved; c0 += 512) {
-        {
-            const int lo = max(s_me, c0), hi = min(s_me + sur_me, c0 + 512);
-            for (int j = lo + lane; j < hi; j += 32) staging[j - c0] = reg[target + (j - s_me)];
-        }
-        __syncthreads();
-        {
-            const int lo = max(d_me, c0), hi = min(d_me + def_me, min(moved, c0 + 512));
-            for (int j = lo + lane; j < hi; j += 32) reg[c_me + (j - d_me)] = staging[j - c0];
-        }
-        __syncthreads();
-    }
-    const int now = sur_me > 0 ? target : c_me + max(0, min(def_me, moved - d_me));
-    if (lane == 0) m.cntw[q * 32 + warp] = now;
-    __syncthreads();
-    return t == q ? now : rc;
-}
-
-// Block-wide step, entered by all threads after a barrier: refresh the thresholds
-// (shared histogram, other CTAs), let every warp purge its regions, and run a selection
-// only for queries that still lack room (final: whose candidates still exceed the list
-// size).  Sets *bail when a query cannot be settled.  Returns the caller's region count.
-__device__ __noinline__ int mma_settle(const ScoreArgs& a, const MmaItem& m, int rc, bool final) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5, t = lane & 3;
-    const int nq = m.nq;
-    PROF_T(s0);
-    SEL_ADD(0, 1);
-    // a bucket mapping another CTA has published meanwhile: known from now on, but this
-    // CTA's buffer is not in the shared histogram yet (negated inv, see block_select_seg)
-    if (tid < nq && m.rng[tid].y == 0.0f) {
-        const unsigned long long pr = *reinterpret_cast<volatile unsigned long long*>(a.grange + m.query_begin + tid);
-        if (pr) m.rng[tid] = make_float2(__uint_as_float((uint32_t)pr), -__uint_as_float((uint32_t)(pr >> 32)));
-    }
-    if (lane < 4) m.cntw[lane * 32 + warp] = rc;  // lane l < 4 is (g = 0, t = l)
-    __syncthreads();
-    if (warp < nq) mma_hist_pivot(a, m, warp, lane);
-    if (warp == nwarps - 1) mma_refresh_pivots(a, m, lane);
-    __syncthreads();
-    PROF_T(s1);
-    SEL_ADD(1, s1 - s0);
-    const bool any_pivot = (m.pivot[0] | m.pivot[1] | m.pivot[2] | m.pivot[3]) != 0ull;
-#pragma unroll 1
-    for (int attempt = 0; attempt < 4; ++attempt) {
-        PROF_T(s2);
-        if (attempt > 0 || any_pivot) {
-#pragma unroll 1
-            for (int tq = 0; tq < nq; ++tq) mma_purge(m, tq, warp, nwarps, lane, t, rc);
-            if (lane < 4) m.cntw[lane * 32 + warp] = rc;
-            __syncthreads();
-        }
-        PROF_T(s3);
-        SEL_ADD(2, s3 - s2);
-        SEL_ADD(7, 1);
-        uint32_t over = 0u, even = 0u;  // queries lacking room; of those, the ones a redistribution settles
-#pragma unroll 1
-        for (int q = 0; q < nq; ++q) {
-            const int v = lane < nwarps ? m.cntw[q * 32 + lane] : 0;
-            const int tot = __reduce_add_sync(0xFFFFFFFFu, v), mx = __reduce_max_sync(0xFFFFFFFFu, v);
-            if (final ? tot > (int)a.list_cap : mx > m.room - 2 * MMA_SET_TILES) {
-                over |= 1u << q;
-                // few enough keys in all (a selection ran, or would drop nothing): only their spread is the problem
-                if (!final && tot <= nwarps * (m.room - 4 * MMA_SET_TILES) && (attempt > 0 || tot <= (int)(a.k + m.sel_slack))) even |= 1u << q;
-            }
-        }
-        if (!over) break;
-        uint32_t failed = attempt == 3 ? over : 0u;
-        if (!failed && (over & ~even)) failed = block_select_seg(a, m, over & ~even, final ? a.list_cap - a.k : m.sel_slack);
-        PROF_T(s4);
-        SEL_ADD(3, s4 - s3);
-        if (failed) {
-            SEL_ADD(attempt == 3 ? 5 : 6, 1);
-            // equal scores: the generic kernel takes the item
-            if (tid == 0) *m.bail = 1;
-            break;
-        }
-#pragma unroll 1
-        for (int q = 0; q < nq; ++q)
-            if (even >> q & 1u) rc = mma_rebalance(m, q, rc);
-    }
-    if (tid < nq) atomicMax(a.gpivot + m.query_begin + tid, (unsigned long long)m.pivot[tid]);
-    __syncthreads();
-    return rc;
-}
-
-// KIND 0: nibble codecs (INT4, MX-INT4, NF4); 1: the launch scores mixed 8/4 tiles; 2: TQ3 tiles,
-// rewritten in shared memory as nibble rows (2 code + correction bit) before the INT4 path scores
-// them.  Separate instantiations, so that the nibble-codec kernel is exactly the code it was.
-// EARLY: many CTAs share every query (one long segment cut over the whole grid).  After one set
-// of every warp the query's shared histogram already holds far more than k candidates, so four
-// warps per CTA fetch a first threshold after their 2nd..5th set instead of waiting for their
-// regions to fill, which they would all do at the same moment.
-template <bool TOPK, int KIND = 0, bool EARLY = false>
-__global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
+// KIND 0: nibble codecs (INT4, MX-INT4, NF4 through the shared-memory table); 1: the launch scores
+// mixed 8/4 tiles; 2: TQ3 tiles, rewritten in shared memory as nibble rows (2 code + correction
+// bit) before the INT4 path scores them; 3: INT4 / MX-INT4 tiles only (scale folded into A).
+// Separate instantiations.  A tile of another codec than the launch was arranged for flags the
+// work item's query rows, which the generic kernel then scores.
+template <int KIND, int NT>
+__global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    // shared layout: nf4 table | stage ring | [keys | pivot | cntw | outpos | ctl | rng | hist]
+    // shared layout: nf4 table | stage ring | B fragments | query sign words | thresholds | bucket mappings | flag
     const uint32_t lut_bytes = a.nf4_table ? NF4_LUT_BYTES : 0;  // the table is left out when no NF4 tile is expected
     uint2* lut = reinterpret_cast<uint2*>(smem);
     unsigned char* tail = smem + lut_bytes + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE;
-    // Candidates of query q kept by warp w: keys[(q * nwarps + w) * rs ..], rs = cap / nwarps.
-    // A warp appends to and purges its own regions without any block-wide step.
-    uint64_t* keys = reinterpret_cast<uint64_t*>(tail);            // [4][nwarps][rs]
-    uint64_t* pivot = keys + (TOPK ? (size_t)4 * a.cap : 0);       // [4]
-    int* cntw = reinterpret_cast<int*>(pivot + 4);                 // [4][32] region counts, published for block-wide steps
-    int* outpos = cntw + 128;                                      // [4] write position in the item's candidate lists
-    int* ctl = outpos + 4;  // [0] want: a warp cannot make room alone  [1] arrived  [2] done warps  [3] bail
-    int* bail = ctl + 3;
-    float2* rng = reinterpret_cast<float2*>(ctl + 4);  // [4] (smin, inv) of the query's shared score histogram; inv 0 = none yet
-    int* hist = ctl + 12;  // SEL_HIST_INTS
+    uint2* bq_w = reinterpret_cast<uint2*>(tail);                        // [9][32]
+    uint32_t* qs_w = reinterpret_cast<uint32_t*>(tail + MMA_BQ_BYTES);   // [4][8]
+    uint32_t* pvh = qs_w + 32;                                           // [4] score word of the row's threshold
+    float2* rng = reinterpret_cast<float2*>(pvh + 4);                    // [4] (smin, inv), inv 0 = none yet
+    int* bail = reinterpret_cast<int*>(rng + 4);                         // [1]
     const uint32_t smem_s = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t stage_s = smem_s + lut_bytes + (uint32_t)warp * MMA_DEPTH * MMA_SET_STRIDE;
+    const uint32_t bqa = smem_s + lut_bytes + (uint32_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE + (uint32_t)lane * 8u;
+    const uint32_t qsa = bqa - (uint32_t)lane * 8u + MMA_BQ_BYTES + (uint32_t)t * 32u;
 
     // NF4 codebook as fp16 hi + lo pairs per byte (two nibbles), 16 bank-aligned replicas
     for (int e = tid; e < (a.nf4_table ? 256 * 16 : 0); e += blockDim.x) {
@@ -1077,76 +676,67 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
     // i.e. chunk (lane & 7) of rows (lane >> 3) + {0, 4, 8, 12}
     const uint32_t dst_lane = (uint32_t)((lane >> 3) * MMA_ROW + (lane & 7) * 16);
     const uint32_t row_lane = (uint32_t)g * MMA_ROW;
-    const uint32_t rs = a.cap / (uint32_t)nwarps;          // slots per region
-    const int room = (int)rs - MMA_SET_TILES;              // a set adds at most 16 keys to a region
-    const uint32_t sel_slack = (a.cap - (uint32_t)nwarps * MMA_SET_TILES - a.k) / 4;
-    uint64_t* my_reg = keys + (size_t)(t * nwarps + warp) * rs;  // region of query t of this warp
     const uint32_t lt_mask = (1u << lane) - 1u, t_mask = 0x11111111u << t;
 
-#ifdef SLHA_SCORE_PROFILE
-    unsigned long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#endif
     const uint32_t item_end = a.cta_begin[blockIdx.x + 1];
     for (uint32_t item_id = a.cta_begin[blockIdx.x]; item_id < item_end; ++item_id) {
         const WorkItem it = a.items[item_id];
         const int nq = (int)it.n_queries;
-        PROF_T(t_item);
         __syncthreads();  // previous item fully retired (and the table is visible)
-        if (TOPK && tid < 4) {
-            // start from the threshold other CTAs have already proven for the query, and
-            // from the query's shared histogram range if one has been published
+        if (tid < 4) {
+            // start from the threshold other CTAs have already proven for the row, and from the
+            // row's bucket mapping if one has been published
             const bool have = tid < nq;
-            outpos[tid] = 0;
-            pivot[tid] = have ? *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + tid) : 0ull;
+            const unsigned long long pv = have ? *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + tid) : 0ull;
+            pvh[tid] = (uint32_t)(pv >> 32);
             const unsigned long long pr = have ? *reinterpret_cast<volatile unsigned long long*>(a.grange + it.query_begin + tid) : 0ull;
             rng[tid] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
         }
-        if (tid == 0) { ctl[0] = ctl[1] = ctl[2] = ctl[3] = 0; }
-        // B fragments: column n = g is query g>>1, part g&1 (hi / lo); k slots
-        // {2t, 2t+1, 2t+8, 2t+9} of group j carry dims 16j + 4t + {0,1,2,3}
-        uint32_t bq[8][2];
-        uint32_t qs[8];
-        uint32_t bE = 0;
+        if (tid == 0) bail[0] = 0;
+        if (warp == 1 % nwarps) {
+            // sign words of the item's (up to four) queries
+            const int qi = lane >> 3;
+            qs_w[lane] = qi < nq ? a.q_sign[(size_t)(it.query_begin + qi) * 8 + (lane & 7)] : 0u;
+        }
         bool big = false;
-        {
+        if (warp == 0) {
+            // B fragments: column n = g is query g>>1, part g&1 (fp16 hi / lo of the query)
             const int qi = g >> 1;
             const bool have = qi < nq;
             const float* q = a.q_coarse + (size_t)(it.query_begin + (have ? qi : 0)) * D_C;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
+                float v[4];
                 if (KIND == 3) {
                     // MMA j takes nibbles (o, o + 4 | o + 1, o + 5), o = 2 (j & 1), of the thread's word j >> 1
                     const float* qd = q + 32 * t + 8 * (j >> 1) + 2 * (j & 1);
-                    float v[4] = {qd[0], qd[4], qd[1], qd[5]};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        if (!have) v[i] = 0.0f;
-                        big |= fabsf(v[i]) > 60000.0f;
-                        if (g & 1) v[i] = half_residual(v[i]);
+                    v[0] = qd[0]; v[1] = qd[4]; v[2] = qd[1]; v[3] = qd[5];
+                } else {
+                    // k slots {2t, 2t+1, 2t+8, 2t+9} of group j carry dims 16j + 4t + {0,1,2,3}; mixed 8/4 tiles:
+                    // group 0 = dims 2t, 2t+1 (8-bit levels, plain in both slots, so both carry 16x the
+                    // query), groups 1..7 = INT4 groups of dims 16 j - 8 ..
+                    const int dim0 = !(KIND == 1) ? 16 * j + 4 * t : (j == 0 ? 0 : 16 * j - 8 + 4 * t);
+                    float4 x = *reinterpret_cast<const float4*>(q + dim0);
+                    if (KIND == 1 && j == 0) {
+                        const float2 y = *reinterpret_cast<const float2*>(q + 2 * t);
+                        x = make_float4(y.x, 16.0f * y.y, 0.0f, 0.0f);
                     }
-                    bq[j][0] = pack_half2(v[0], v[1]);
-                    bq[j][1] = pack_half2(v[2], v[3]);
-                    continue;
+                    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
                 }
-                // mixed 8/4 tiles: group 0 = dims 2t, 2t+1 (8-bit levels, plain in both slots, so
-                // both carry 16x the query), groups 1..7 = INT4 groups of dims 16 j - 8 ..
-                const int dim0 = !(KIND == 1) ? 16 * j + 4 * t : (j == 0 ? 0 : 16 * j - 8 + 4 * t);
-                float4 x = *reinterpret_cast<const float4*>(q + dim0);
-                if (KIND == 1 && j == 0) {
-                    const float2 y = *reinterpret_cast<const float2*>(q + 2 * t);
-                    x = make_float4(y.x, 16.0f * y.y, 0.0f, 0.0f);
-                }
-                float v[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     if (!have) v[i] = 0.0f;
-                    big |= fabsf(v[i]) > (KIND == 1 && j == 0 && i == 1 ? 64000.0f : 4000.0f);  // 16 v must stay inside fp16
-                    if (!(i & 1)) v[i] *= 16.0f;             // even slots carry 16x the query (see int4_quad)
+                    if (KIND == 3) {
+                        big |= fabsf(v[i]) > 60000.0f;
+                    } else {
+                        big |= fabsf(v[i]) > (KIND == 1 && j == 0 && i == 1 ? 64000.0f : 4000.0f);  // 16 v must stay inside fp16
+                        if (!(i & 1)) v[i] *= 16.0f;  // even slots carry 16x the query (see int4_quad)
+                    }
                     if (g & 1) v[i] = half_residual(v[i]);
                 }
-                bq[j][0] = pack_half2(v[0], v[1]);
-                bq[j][1] = pack_half2(v[2], v[3]);
+                bq_w[j * 32 + lane] = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
             }
+            uint32_t bE = 0;
             if (KIND == 2) {
                 // B fragment of the group sums: k slots 2t and 2t+1 = groups 2t and 2t+1 of query g>>1
                 float s0 = 0.0f, s1 = 0.0f;
@@ -1160,36 +750,23 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
                 if (g & 1) { s0 = half_residual(s0); s1 = half_residual(s1); }
                 bE = pack_half2(s0, s1);
             }
-            // sign words of query t (the query whose scores this thread finishes)
-#pragma unroll
-            for (int w = 0; w < 8; ++w)
-                qs[w] = t < nq ? a.q_sign[(size_t)(it.query_begin + t) * 8 + w] : 0u;
+            bq_w[8 * 32 + lane] = make_uint2(bE, 0u);
+            if (__any_sync(0xFFFFFFFFu, big) && lane == 0) bail[0] = 1;  // a query too large for the fp16 split
         }
-        // a query too large for the fp16 split: the generic kernel takes the item
-        const bool too_big = __syncthreads_or(big) != 0;
-        if (too_big && tid == 0) bail[0] = 1;
+        __syncthreads();
+        const bool too_big = bail[0] != 0;
 
         const uint8_t* sbase = a.state ? a.state + it.tile_begin : nullptr;
         const uint32_t n = it.n_tiles;
         const uint32_t n_sets = too_big ? 0u : (n + MMA_SET_TILES - 1) / MMA_SET_TILES;
         const uint32_t n_full = n / MMA_SET_TILES;
         const bool mine = t < nq;
-        uint32_t* gh = a.ghist + (size_t)(it.query_begin + (mine ? t : 0)) * 256;  // my query's shared histogram
-        int rc = 0;  // keys in my_reg (the eight lanes of query t hold the same value)
-        MmaItem m;
-        m.keys = keys; m.pivot = pivot; m.cntw = cntw; m.bail = bail; m.rng = rng; m.hist = hist;
-        m.rs = rs; m.room = room; m.sel_slack = sel_slack; m.query_begin = it.query_begin; m.nq = nq;
-        // Sets are dealt to the warps round by round; the warp that takes a given slot of a
-        // round rotates from round to round, so that a periodic arrangement of the tiles
-        // cannot send all the best candidates to the same warp.
-        const uint32_t rounds = (n_sets + (uint32_t)nwarps - 1) / (uint32_t)nwarps;
-        auto set_of = [&](uint32_t j) { return j * (uint32_t)nwarps + (((uint32_t)warp + j + (j >> 4)) & (uint32_t)(nwarps - 1)); };
+        const uint32_t Qt = it.query_begin + (mine ? (uint32_t)t : 0u);  // the row whose scores this thread finishes
+        // sets are dealt to the warps round by round: warp w takes set j * nwarps + w of round j
         const unsigned char* tbase = a.tiles + it.tile_begin * TILE_BYTES + lane * 16;
-        // prefetch state: next round to fetch and its ring slot
-        uint32_t j_next = 0, slot_next = 0;
+        uint32_t s_next = (uint32_t)warp, slot_next = 0;
         auto issue = [&]() {
-            const uint32_t s_next = set_of(j_next);
-            if (j_next < rounds && s_next < n_sets) {
+            if (s_next < n_sets) {
                 const uint32_t dst = stage_s + slot_next + dst_lane;
                 const unsigned char* src = tbase + (size_t)s_next * MMA_SET_BYTES;
                 if (s_next < n_full) {
@@ -1207,66 +784,54 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
                 }
             }
             cp_async_commit();
-            ++j_next;
+            s_next += (uint32_t)nwarps;
             slot_next = slot_next == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot_next + MMA_SET_STRIDE;
-        };
-        // All warps meet here when some warp cannot make room in a region alone (flag
-        // ctl[0]).  No barrier is executed in the steady state: every warp polls the flag
-        // between sets, finished warps poll it in the drain loop, so everyone arrives.
-        auto rendezvous = [&]() {
-            PROF_T(t_rv0);
-            __syncwarp();
-            if (lane == 0) atomicAdd(&ctl[1], 1);
-            bool met = false;
-            for (uint32_t spin = 0; spin < (1u << 24) && !met; ++spin) {
-                met = *reinterpret_cast<volatile int*>(ctl + 1) >= nwarps;
-                if (!met) __nanosleep(40);
-            }
-            if (!met && lane == 0) bail[0] = 1;  // the wait ran out: the generic kernel takes the item
-            __syncthreads();
-            PROF_T(t_rv1);
-            rc = mma_settle(a, m, rc, false);
-            if (tid == 0) { ctl[0] = 0; ctl[1] = 0; }
-            __syncthreads();
-            PROF_T(t_rv2);
-            PROF_ADD(2, t_rv1 - t_rv0);
-            PROF_ADD(3, t_rv2 - t_rv1);
-            PROF_ADD(4, 1);
         };
 #pragma unroll
         for (int i = 0; i < MMA_DEPTH - 1; ++i) issue();
-        PROF_T(t_loop0);
-        PROF_ADD(0, t_loop0 - t_item);
         uint32_t slot = 0, polls = 0;
-        for (uint32_t j = 0; j < rounds; ++j) {
+        uint32_t cur = 0, end = 0;  // this warp's chunk of the buffer of row Qt (the same in the eight lanes of a query)
+        bool dead = false;          // this warp met a tile it cannot decode
+        const uint32_t rounds = (n_sets + (uint32_t)nwarps - 1) / (uint32_t)nwarps;
+        for (uint32_t round = 0; round < rounds; ++round) {
+            const uint32_t s = round * (uint32_t)nwarps + (uint32_t)warp;
+            if (round == 1) {
+                // Every warp of the CTA (and, started together, of the grid) has appended its first set
+                // unfiltered, so the rows' histograms hold 16 candidates per warp: first thresholds now,
+                // before the second sets are filtered.  (All warps pass here: `rounds` is the same for all.)
+                __syncthreads();
+                if (warp < nq) stream_refresh_threshold(a, it.query_begin + (uint32_t)warp, rng[warp], pvh + warp, lane);
+                __syncthreads();
+            }
+            if (dead || s >= n_sets) continue;
             issue();
             cp_async_wait<MMA_DEPTH - 1>();
             __syncwarp();
-            const uint32_t s = set_of(j);
             const uint32_t rb = stage_s + slot + row_lane;
             slot = slot == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot + MMA_SET_STRIDE;
-            if (s >= n_sets) continue;  // the last round may be partial
             const uint2 m0 = lds_v2<96>(rb), m1 = lds_v2<96 + MMA_HALF>(rb);    // scale, lambda
             const uint4 x0 = lds_v4<112>(rb), x1 = lds_v4<112 + MMA_HALF>(rb);  // position, head|flags, gs[8]
             const uint32_t f0 = x0.y >> 16, f1 = x1.y >> 16;
             const uint32_t fo = __reduce_or_sync(0xFFFFFFFFu, f0 | f1);
-            // a launch arranged for mixed 8/4 tiles takes nothing else (rows past the end of a ragged
-            // last set are zero-filled and their scores dropped, so they count as mixed)
-            const uint32_t row0 = s * MMA_SET_TILES + (uint32_t)g;
-            const bool all_mixed = KIND == 1 && (__reduce_and_sync(0xFFFFFFFFu, (row0 < n ? f0 : F_MIXED) & (row0 + 8 < n ? f1 : F_MIXED)) & F_MIXED);
-            const bool all_tq3 = KIND == 2 && (__reduce_and_sync(0xFFFFFFFFu, (row0 < n ? f0 : F_TQ3) & (row0 + 8 < n ? f1 : F_TQ3)) & F_TQ3);
+            const bool ragged = s >= n_full;
+            const uint32_t t0 = s * MMA_SET_TILES + (uint32_t)g, t1 = t0 + 8;
+            // a launch arranged for mixed 8/4 (TQ3) tiles takes nothing else (rows past the end of a ragged
+            // last set are zero-filled and their scores dropped, so they count as such tiles)
+            const bool all_mixed = KIND == 1 && (__reduce_and_sync(0xFFFFFFFFu, (t0 < n ? f0 : F_MIXED) & (t1 < n ? f1 : F_MIXED)) & F_MIXED);
+            const bool all_tq3 = KIND == 2 && (__reduce_and_sync(0xFFFFFFFFu, (t0 < n ? f0 : F_TQ3) & (t1 < n ? f1 : F_TQ3)) & F_TQ3);
             if ((fo & F_MIX3) || ((fo & F_TQ3) && !all_tq3) || (KIND == 2 && !all_tq3) ||
                 ((fo & F_MIXED) && !all_mixed) || (KIND == 1 && !all_mixed) || ((fo & F_NF4) && (KIND == 3 || !a.nf4_table))) {
-                if (lane == 0) bail[0] = 1;  // a codec this kernel does not decode: hand the item back
-                break;
+                if (lane == 0) bail[0] = 1;  // a codec this launch does not decode: the generic kernel takes the rows
+                dead = true;
+                continue;
             }
             float acc0, acc1;
             const uint32_t hb = rb + 2u * (uint32_t)t;
             if (KIND == 3) {
-                coarse_set_int4c(rb, (uint32_t)t, magic, bq, acc0, acc1);
+                coarse_set_int4c(rb, (uint32_t)t, magic, bqa, acc0, acc1);
             } else if (KIND == 2) {  // (all_tq3 holds here)
                 tq3_to_nibbles(rb - row_lane, lane);
-                coarse_set<0>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+                coarse_set<0>(hb, lut_lane, magic, bqa, f0, f1, x0, x1, acc0, acc1);
                 // level = (2 nibble - 15) / 4, or (2 nibble - 14) / 4 without the correction plane:
                 // beside the nibble sums X the score needs 8 c sum_g gs_g Q_g (c = 1 or 2, Q_g = the
                 // query's sum over group g), one more MMA with the scale bytes as the A operand
@@ -1275,41 +840,56 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
                 asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(ga0) : "r"(prmt(t < 2 ? x0.z : x0.w, magic, sel)), "r"(0xE400E400u));
                 asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(ga1) : "r"(prmt(t < 2 ? x1.z : x1.w, magic, sel)), "r"(0xE400E400u));
                 float e[4];
-                mma_f16_zero(e, ga0, ga1, 0u, 0u, bE, 0u);
+                mma_f16_zero(e, ga0, ga1, 0u, 0u, lds_v2<256 * 8>(bqa).x, 0u);
                 acc0 = fmaf((f0 & F_NOCORR) ? 16.0f : 8.0f, e[0] + e[1], acc0);
                 acc1 = fmaf((f1 & F_NOCORR) ? 16.0f : 8.0f, e[2] + e[3], acc1);
             } else if (KIND == 1) {  // (all_mixed holds here)
-                coarse_set<3>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+                coarse_set<3>(hb, lut_lane, magic, bqa, f0, f1, x0, x1, acc0, acc1);
             } else if (!(fo & F_NF4)) {
-                coarse_set<0>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+                coarse_set<0>(hb, lut_lane, magic, bqa, f0, f1, x0, x1, acc0, acc1);
             } else if (__reduce_and_sync(0xFFFFFFFFu, f0 & f1) & F_NF4) {
-                coarse_set<1>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+                coarse_set<1>(hb, lut_lane, magic, bqa, f0, f1, x0, x1, acc0, acc1);
             } else {
-                coarse_set<2>(hb, lut_lane, magic, bq, f0, f1, x0, x1, acc0, acc1);
+                coarse_set<2>(hb, lut_lane, magic, bqa, f0, f1, x0, x1, acc0, acc1);
             }
-            // Hamming term of query t for both rows
-            const int h0 = popc8(lds_v4<64>(rb), lds_v4<80>(rb), qs);
-            const int h1 = popc8(lds_v4<64 + MMA_HALF>(rb), lds_v4<80 + MMA_HALF>(rb), qs);
             const float lam0 = (f0 & F_WARM) ? 0.0f : __uint_as_float(m0.y);
             const float lam1 = (f1 & F_WARM) ? 0.0f : __uint_as_float(m1.y);
             // 1 / (255 x 16 [x 2]); KIND 3: the sums carry 2^-12
             constexpr float unit = KIND == 3 ? 4096.0f / 255.0f : (KIND == 2 ? 1.0f / 8160.0f : 1.0f / 4080.0f);
+            const float c0 = acc0 * (__uint_as_float(m0.x) * unit), c1 = acc1 * (__uint_as_float(m1.x) * unit);
+            const uint32_t pv = reinterpret_cast<const volatile uint32_t*>(pvh)[t];
+            // The residual term lies in [-256 lambda, 256 lambda]: a set none of whose tiles can reach its
+            // row's threshold even with the largest term needs no Hamming distances (and appends nothing).
+            // (257 and the relative slack cover the rounding of the bound itself.)  Only the INT4 launches
+            // test for it: with a few CTAs per row and k / n of a few percent (the NF4 decode caches) nearly
+            // every set holds a candidate and the test costs more than it saves.
+            const bool need = KIND != 3 || round == 0 ||
+                              __any_sync(0xFFFFFFFFu, (mine && score_key(fmaf(lam0, 257.0f, c0 + fabsf(c0) * 1e-6f)) >= pv) ||
+                                                          (mine && score_key(fmaf(lam1, 257.0f, c1 + fabsf(c1) * 1e-6f)) >= pv));
+            if (need) {
+            // Hamming term of query t for both rows
+            int h0, h1;
+            {
+                const uint4 qa = lds_v4<0>(qsa), qb = lds_v4<16>(qsa);
+                const uint32_t qs[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                h0 = popc8(lds_v4<64>(rb), lds_v4<80>(rb), qs);
+                h1 = popc8(lds_v4<64 + MMA_HALF>(rb), lds_v4<80 + MMA_HALF>(rb), qs);
+            }
             // 256 - 2 h without an integer conversion: (2^23 + h) as a bit pattern, times -2, plus 2^24 + 256 (exact)
             const float x0f = fmaf(__uint_as_float(0x4B000000u | (uint32_t)h0), -2.0f, 16777472.0f);
             const float x1f = fmaf(__uint_as_float(0x4B000000u | (uint32_t)h1), -2.0f, 16777472.0f);
-            const float sc0 = fmaf(acc0, __uint_as_float(m0.x) * unit, lam0 * x0f);
-            const float sc1 = fmaf(acc1, __uint_as_float(m1.x) * unit, lam1 * x1f);
-            const uint32_t t0 = s * MMA_SET_TILES + (uint32_t)g, t1 = t0 + 8;
-            bool live0 = mine && t0 < n, live1 = mine && t1 < n;
+            const float sc0 = fmaf(lam0, x0f, c0);
+            const float sc1 = fmaf(lam1, x1f, c1);
+            bool live0 = mine && (!ragged || t0 < n), live1 = mine && (!ragged || t1 < n);
             if (sbase) {
                 live0 = live0 && sbase[t0] != ST_COLD;
                 live1 = live1 && sbase[t1] != ST_COLD;
             }
-            if (TOPK && j == 0) {
-                // First set of the warp: a query without a bucket mapping gets one from the 16
-                // scores this warp has just computed for it - their range widened by 1.5 spans
-                // on both sides.  Any monotone mapping is valid; this one only has to put the
-                // final threshold somewhere inside its 256 buckets.  The first CTA to publish wins.
+            if (round == 0) {
+                // First set of the warp: a row without a bucket mapping gets one from the 16 scores
+                // this warp has just computed for it - their range widened by 1.5 spans on both sides.
+                // Any monotone mapping is valid; this one only has to put the final threshold somewhere
+                // inside its 256 buckets.  The first CTA to publish wins.
                 float mn = fminf(live0 ? sc0 : INFINITY, live1 ? sc1 : INFINITY), mx = fmaxf(live0 ? sc0 : -INFINITY, live1 ? sc1 : -INFINITY);
 #pragma unroll
                 for (int o = 4; o < 32; o <<= 1) {
@@ -1317,12 +897,12 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
                     mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
                 }
                 if (g == 0 && mine && rng[t].y == 0.0f) {
-                    unsigned long long pr = *reinterpret_cast<volatile unsigned long long*>(a.grange + it.query_begin + t);
+                    unsigned long long pr = *reinterpret_cast<volatile unsigned long long*>(a.grange + Qt);
                     if (!pr && mx > mn) {
                         const float span = mx - mn, lo = mn - 1.5f * span, inv = 256.0f / (4.0f * span);
                         if (isfinite(lo) && isfinite(inv) && inv > 0.0f) {
                             const unsigned long long mine_r = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(inv) << 32);
-                            const unsigned long long old = atomicCAS(a.grange + it.query_begin + t, 0ull, mine_r);
+                            const unsigned long long old = atomicCAS(a.grange + Qt, 0ull, mine_r);
                             pr = old ? old : mine_r;
                         }
                     }
@@ -1330,105 +910,76 @@ __global__ void __launch_bounds__(512, 1) score_mma_kernel(ScoreArgs a) {
                 }
                 __syncwarp();
             }
-            if (TOPK) {
-                // filter on the score word alone (a superset of the composite comparison: a key that
-                // only ties with the threshold's score is dropped again by the next purge)
-                const uint32_t pvh = reinterpret_cast<const volatile uint32_t*>(pivot)[2 * t + 1];
-                const uint32_t k0 = score_key(sc0), k1 = score_key(sc1);
-                const bool p0 = live0 && k0 >= pvh, p1 = live1 && k1 >= pvh;
-                if (__any_sync(0xFFFFFFFFu, p0 || p1)) {
-                    const uint64_t comp0 = ((uint64_t)k0 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t0));
-                    const uint64_t comp1 = ((uint64_t)k1 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t1));
-                    // the lanes of query t append to the warp's region of that query: slots by ballot, no atomics
-                    const unsigned b0 = __ballot_sync(0xFFFFFFFFu, p0) & t_mask, b1 = __ballot_sync(0xFFFFFFFFu, p1) & t_mask;
-                    const int n0 = __popc(b0);
-                    const float2 r = rng[t];
-                    if (p0) {
-                        my_reg[rc + __popc(b0 & lt_mask)] = comp0;
-                        if (r.y > 0.0f && sc0 >= r.x) atomicAdd(gh + sel_bucket_f(sc0, r.x, r.y), 1u);
-                    }
-                    if (p1) {
-                        my_reg[rc + n0 + __popc(b1 & lt_mask)] = comp1;
-                        if (r.y > 0.0f && sc1 >= r.x) atomicAdd(gh + sel_bucket_f(sc1, r.x, r.y), 1u);
-                    }
-                    rc += n0 + __popc(b1);
-                    if (__any_sync(0xFFFFFFFFu, rc > room)) {
-                        // a region may not take another set: drop what the current thresholds allow,
-                        // and ask for a block-wide step if that does not make room
-#pragma unroll 1
-                        for (int tq = 0; tq < nq; ++tq) {
-                            mma_hist_pivot(a, m, tq, lane);
-                            __syncwarp();
-                            mma_purge(m, tq, warp, nwarps, lane, t, rc);
-                        }
-                        if (__any_sync(0xFFFFFFFFu, rc > room - 2 * MMA_SET_TILES) && lane == 0) *reinterpret_cast<volatile int*>(ctl) = 1;
+            // filter on the score word alone (a superset of the composite comparison: the merge drops
+            // keys below the final threshold)
+            const uint32_t k0 = score_key(sc0), k1 = score_key(sc1);
+            const bool p0 = live0 && k0 >= pv, p1 = live1 && k1 >= pv;
+            if (__any_sync(0xFFFFFFFFu, p0 || p1)) {
+                // The eight lanes of query t append to the row's buffer, slots by ballot.  The warp owns a
+                // chunk of 16 slots per row, [cur, end), reserved with one atomic; a set brings at most 16
+                // candidates per row, so a fresh chunk always fits them.  The unused rest of a chunk is
+                // zeroed (an absent key) before the next one is taken and at the end of the work item.
+                const unsigned b0 = __ballot_sync(0xFFFFFFFFu, p0) & t_mask, b1 = __ballot_sync(0xFFFFFFFFu, p1) & t_mask;
+                const uint32_t n0 = (uint32_t)__popc(b0), nn = n0 + (uint32_t)__popc(b1);
+                uint64_t* dst = a.gbuf + (size_t)Qt * a.gcap;
+                if (__any_sync(0xFFFFFFFFu, cur + nn > end)) {
+                    if (cur + nn > end) {  // (uniform over the eight lanes of a query)
+                        if (cur + (uint32_t)g < end && cur + (uint32_t)g < a.gcap) dst[cur + (uint32_t)g] = 0ull;
+                        if (cur + 8u + (uint32_t)g < end && cur + 8u + (uint32_t)g < a.gcap) dst[cur + 8u + (uint32_t)g] = 0ull;
+                        uint32_t base = 0;
+                        if (g == 0) base = atomicAdd(a.gcount + Qt, 16u);
+                        cur = __shfl_sync(t_mask, base, t);  // lane t is (g = 0, t)
+                        end = cur + 16u;
                     }
                 }
-            } else if (mine) {
-                float* o = a.scores + (size_t)(it.query_begin + t) * a.score_stride + it.index_base;
-                if (t0 < n) o[t0] = live0 ? sc0 : -INFINITY;
-                if (t1 < n) o[t1] = live1 ? sc1 : -INFINITY;
-            }
-            __syncwarp();
-            if (TOPK) {
-                if (*reinterpret_cast<volatile int*>(ctl)) {
-                    rendezvous();
-                    if (bail[0]) break;
-                } else if ((++polls & 63u) == (uint32_t)(warp >> 2) * 16u + 8u || (EARLY && polls == 2u + (uint32_t)(warp >> 2))) {
-                    // in turn, a warp raises the threshold of query (warp & 3)
-                    if ((warp & 3) < nq) mma_hist_pivot(a, m, warp & 3, lane);
-                    if ((warp & 3) == 0) mma_refresh_pivots(a, m, lane);
-                    __syncwarp();
+                const float2 r = rng[t];
+                bool over = false;
+                if (p0) {
+                    const uint32_t at = cur + (uint32_t)__popc(b0 & lt_mask);
+                    if (at < a.gcap) dst[at] = ((uint64_t)k0 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t0));
+                    else over = true;
+                    if (r.y > 0.0f && sc0 >= r.x) atomicAdd(a.ghist + (size_t)Qt * 256 + sel_bucket_f(sc0, r.x, r.y), 1u);
                 }
+                if (p1) {
+                    const uint32_t at = cur + n0 + (uint32_t)__popc(b1 & lt_mask);
+                    if (at < a.gcap) dst[at] = ((uint64_t)k1 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t1));
+                    else over = true;
+                    if (r.y > 0.0f && sc1 >= r.x) atomicAdd(a.ghist + (size_t)Qt * 256 + sel_bucket_f(sc1, r.x, r.y), 1u);
+                }
+                cur += nn;
+                if (over) a.gflag[Qt] = 1u;  // the row's buffer is full: the generic kernel scores the row
             }
-        }
-        PROF_T(t_loop1);
-        PROF_ADD(1, t_loop1 - t_loop0);
-        if (TOPK) {
-            // drain: warps that ran out of sets keep serving block-wide steps until all are done
+            }  // need
             __syncwarp();
-            if (lane == 0) atomicAdd(&ctl[2], 1);
-            bool done = false;
-            for (uint32_t spin = 0; spin < (1u << 24) && !done; ++spin) {
-                if (*reinterpret_cast<volatile int*>(ctl)) rendezvous();
-                else if (*reinterpret_cast<volatile int*>(ctl + 2) >= nwarps) done = true;
-                else __nanosleep(100);
+            // In turn, a warp raises the threshold of query (warp & 3): after its first few sets (every
+            // warp of the grid has appended its first sets unfiltered, so the row's histogram already
+            // holds far more than k candidates), then every 64 sets, the warps of a query staggered.
+            ++polls;
+            if ((polls & 63u) == (uint32_t)((warp >> 2) & 3) * 16u + 15u || (polls <= 12u && polls >= 2u && ((polls & (polls - 1u)) == 0u || polls == 3u || polls == 6u || polls == 12u))) {
+                const int q = warp & 3;
+                if (q < nq) stream_refresh_threshold(a, it.query_begin + (uint32_t)q, rng[q], pvh + q, lane);
+                __syncwarp();
             }
-            if (!done && lane == 0) bail[0] = 1;  // the wait ran out: the generic kernel takes the item
         }
         cp_async_wait<0>();
+        if (mine) {  // the unused rest of the warp's last chunk holds absent keys
+            uint64_t* dst = a.gbuf + (size_t)Qt * a.gcap;
+            if (cur + (uint32_t)g < end && cur + (uint32_t)g < a.gcap) dst[cur + (uint32_t)g] = 0ull;
+            if (cur + 8u + (uint32_t)g < end && cur + 8u + (uint32_t)g < a.gcap) dst[cur + 8u + (uint32_t)g] = 0ull;
+        }
         __syncthreads();
-        PROF_T(t_drain1);
-        PROF_ADD(5, t_drain1 - t_loop1);
-        if (TOPK && !bail[0]) rc = mma_settle(a, m, rc, true);  // at most list_cap candidates per query remain
-        if (bail[0]) {
-            if (tid == 0) a.retry[item_id] = 1;
-            continue;
-        }
-        if (TOPK) {
-            // every warp copies its regions behind each other into the item's candidate lists
-#pragma unroll 1
-            for (int tq = 0; tq < nq; ++tq) {
-                const int cn = __shfl_sync(0xFFFFFFFFu, rc, tq);
-                int base = 0;
-                if (lane == 0 && cn) base = atomicAdd(&outpos[tq], cn);
-                base = __shfl_sync(0xFFFFFFFFu, base, 0);
-                const uint64_t* reg = keys + (size_t)(tq * nwarps + warp) * rs;
-                uint64_t* dst = a.cand_keys + (size_t)(it.list_begin + tq) * a.list_cap;
-                for (int i = lane; i < cn; i += 32)
-                    if (base + i < (int)a.list_cap) dst[base + i] = reg[i];
-            }
-            __syncthreads();
-            if (tid < nq) a.cand_cnt[it.list_begin + tid] = (uint32_t)min(outpos[tid], (int)a.list_cap);
-        }
-        PROF_T(t_end);
-        PROF_ADD(6, t_end - t_drain1);
-        PROF_ADD(7, 1);
+        // rows this CTA could not score on the tensor cores go to the generic kernel as a whole
+        if (bail[0] && tid < nq) a.gflag[it.query_begin + tid] = 1u;
     }
-#ifdef SLHA_SCORE_PROFILE
-    if (tid == 0)
-        for (int i = 0; i < 8; ++i) g_score_prof[blockIdx.x * 8 + i] = prof[i];
-#endif
+}
+
+// After score_stream_kernel: a work item is handed to the generic kernel when one of its rows is flagged.
+__global__ void stream_mark_retry_kernel(const WorkItem* items, uint32_t n_items, const uint32_t* gflag, uint32_t* retry) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_items) return;
+    uint32_t f = 0;
+    for (uint32_t g = 0; g < items[i].n_queries; ++g) f |= gflag[items[i].query_begin + g];
+    retry[i] = f ? 1u : 0u;
 }
 
 }  // namespace

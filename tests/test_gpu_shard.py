@@ -11,6 +11,19 @@ torch = pytest.importorskip("torch")
 F = np.float32
 
 
+def assert_same_topk(got_i, got_s, want_i, want_s):
+    """Sharded and single-pass results name the same tiles.  Scores agree to a few ulps (a row the
+    tensor-core kernel hands to the generic kernel is summed in another order), and where the order
+    of two entries differs their scores are that close."""
+    assert np.allclose(got_s, want_s, rtol=4e-6, atol=2e-5)
+    for r in range(len(want_i)):
+        diff = got_i[r] != want_i[r]
+        assert set(got_i[r].tolist()) == set(want_i[r].tolist()) or np.all(np.abs(want_s[r][diff] - want_s[r, -1]) <= 1e-4)
+        if diff.any():
+            pos = np.nonzero(diff)[0]
+            assert np.all(np.abs(got_s[r][pos] - want_s[r][pos]) <= 2e-5 + 4e-6 * np.abs(want_s[r][pos]))
+
+
 @pytest.mark.parametrize("skew", [False, True])
 def test_short_exchange_matches_single_pass(skew):
     from slhav2_b200 import shard
@@ -61,7 +74,7 @@ def test_short_exchange_matches_single_pass(skew):
         assert sc.full_exchanges == (1 if skew else 0)
         got_i = res[0].cpu().numpy().view(np.uint32)
         got_s = res[1].cpu().numpy().view(F)
-        assert np.array_equal(got_i, want_i) and np.array_equal(got_s, want_s)
+        assert_same_topk(got_i, got_s, want_i, want_s)
 
 
 def test_pipelined_schedule_matches_single_pass():
@@ -144,5 +157,4 @@ def test_pipelined_schedule_matches_single_pass():
         torch.cuda.set_stream(torch.cuda.default_stream(dev))
         S.set_stream(None)
     for i in range(steps):
-        assert np.array_equal(hout[i][0].numpy().view(np.uint32), want[i][0]), i
-        assert np.array_equal(hout[i][1].numpy().view(F), want[i][1]), i
+        assert_same_topk(hout[i][0].numpy().view(np.uint32), hout[i][1].numpy().view(F), want[i][0], want[i][1])
