@@ -1,23 +1,27 @@
 #!/usr/bin/env python
 """Benchmark of the SLHA v2 tile hot path on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--workload c2|c5] [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--workload c1..c5] [--impl reference]
 
-A "step" is one pass of fused eq. 2.3 scoring + top-k over every tile a rank
-holds.  Default workload (N=1): decode configuration 2, Llama-3-8B-shaped decode KV --
-32 layers x 8 KV heads x 32768 tokens = 8.4M NF4 tiles (1.07 GB), 32 query heads
-per layer in GQA groups of 4, top-1024 per query head.  For N>1 every rank holds
-such a shard of a N x 32768-token context (weak scaling by token range), takes
-its own top-1024 and the shards are merged with one NCCL all-gather + a merge
-kernel.  `--workload c5` is the long-context configuration 5 (1M tokens x 8 KV heads, INT4
-MX-32, top-2048, token range split over the ranks: strong scaling).
+A "step" is one pass of fused eq. 2.3 scoring + top-k over every tile of the context (for
+N > 1: every rank scores its token range, one NCCL all-gather, one merge).
 
-Synthetic data stands in for real activations: seeded N(0,1) keys scaled by
-per-channel log-normal(0, 0.5) factors with RoPE (theta = 500000) applied, bf16,
-encoded on the GPU by this library; seeded N(0,1) queries.
+Default workload: configuration 5, the long-context case the target is written on -- 1 048 576
+tokens x 8 KV heads = 8.4 M INT4 MX-32 tiles (1.07 GB), 32 query heads in GQA groups of 4, top-2048
+per query head.  With N GPUs the token range is split over the ranks (strong scaling) and every
+step goes through the C ABI's sharded entry point (slha_b200_shard_score_topk).  The JSON line's
+`value` is the one-step-at-a-time figure.  At N = 1 the line also carries, under "also", the other
+configurations: c2 (Llama-3-8B decode KV, 32 layers x 8 KV heads x 32768 tokens, NF4, top-1024),
+c1 (the single-head CPU-runnable case), c3 (TQ3 + RHT, 64 queries per KV head: encode and score
+rates) and c4 (the elastic pool under a 60 % budget: appends interleaved with decode steps).
 
-Rank 0 prints ONE JSON line.  `--impl reference` times the CPU restatement of the
-reference's vectorised compute_score (oracle/) on the host cores instead.
+Synthetic data stands in for real activations: seeded N(0,1) keys scaled by per-channel
+log-normal(0, 0.5) factors with RoPE (theta = 500000) applied, bf16, encoded on the GPU by this
+library; seeded N(0,1) queries.  Part of the timed workload is checked against the CPU oracle after
+the timed region ("verified").
+
+Rank 0 prints ONE JSON line.  `--impl reference` times the CPU restatement of the reference's
+vectorised compute_score (oracle/) on the host cores instead.
 """
 import argparse
 import ctypes
@@ -34,25 +38,33 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {
+    "c1": dict(name="config1 single head", layers=1, kv_heads=1, tokens=4096, group=1, codec=0, codec_name="int4", k=64,
+               scaling="strong", dist="gauss_outlier_channels", f32=True),
     "c2": dict(name="config2 llama3-8b decode KV", layers=32, kv_heads=8, tokens=32768, group=4, codec=2,
                codec_name="nf4", k=1024, scaling="weak"),
+    "c3": dict(name="config3 tq3 + rht, 64 queries per KV head", layers=1, kv_heads=8, tokens=16384, group=64, codec=4,
+               codec_name="tq3", k=256, scaling="strong", rht=True, dist="student_t"),
     "c5": dict(name="config5 long-context sharded", layers=1, kv_heads=8, tokens=1048576, group=4, codec=6,
                codec_name="int4-mx32", k=2048, scaling="strong"),
 }
 HEAD_DIM = 128
 ROPE_THETA = 500000.0
+BLOCKS = 5  # the timed region is BLOCKS blocks of --steps steps; the median block is reported
 
 
 def workload_config(w, n_gpus):
     return {
-        "workload": "%s: %d layers x %d KV heads x %d tokens%s, %s tiles, GQA group %d, top-%d per query head"
+        "workload": "%s: %d layers x %d KV heads x %d tokens%s, %s tiles, %d queries per KV head, top-%d per query head"
         % (w["name"], w["layers"], w["kv_heads"], w["tokens"], " per GPU" if w["scaling"] == "weak" else " total",
            w["codec_name"], w["group"], w["k"]),
         "tiles_per_gpu": tiles_per_rank(w, n_gpus),
         "queries_per_tile": w["group"],
         "head_dim": HEAD_DIM,
-        "sharding": "token range, merge by NCCL all-gather" if n_gpus > 1 else "single GPU",
-        "l2_policy": "tile stream per step (>= 134 MB per GPU) exceeds the 126 MB L2; no explicit flush",
+        "sharding": "token range over the ranks, one NCCL all-gather of the per-rank top-k, merge" if n_gpus > 1 else "single GPU",
+        "l2_policy": ("the tile stream of a step (>= 134 MB per GPU) exceeds the 126 MB L2; no explicit flush"
+                      if tiles_per_rank(w, n_gpus) * 128 > 126e6 else
+                      "this configuration's tiles fit the L2 and are timed as they are (L2-resident); not a bandwidth figure"),
+        "timed_region": "%d blocks of --steps steps, median block reported" % BLOCKS,
     }
 
 
@@ -89,10 +101,11 @@ class ClockSampler:
     """SM clock and throttle reasons sampled through NVML (read-only) in a
     background thread while the timed region runs."""
 
-    def __init__(self, gpu_index, period_s=0.005):
+    def __init__(self, gpu_index, period_s=0.002):
         self.gpu, self.period = gpu_index, period_s
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
+        self._ready = threading.Event()
         self._thread = None
 
     def _run(self):
@@ -124,6 +137,7 @@ class ClockSampler:
                 "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
                 "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap,
             }
+            self._ready.set()
             while not self._stop.is_set():
                 self.samples.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
                 r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
@@ -133,10 +147,12 @@ class ClockSampler:
                 time.sleep(self.period)
         except Exception as e:  # no NVML: report nothing rather than fail the bench
             self.error = repr(e)
+            self._ready.set()
 
     def start(self):
         self._thread = threading.Thread(target=self._run, daemon=True)
         self._thread.start()
+        self._ready.wait(timeout=10)  # NVML is initialised before the timed region starts
 
     def stop(self):
         self._stop.set()
@@ -150,20 +166,21 @@ class ClockSampler:
         return out
 
 
-# DRAM traffic of the score kernel from the ncu captures summarised in
-# profiles/score_mma_kernel_c2_nf4_4layers.md and profiles/score_mma_kernel_c5_int4_128k_tokens.md:
-# (bytes read per tile, bytes written per work item).  Reads grow with the tile count (every tile is
-# read once), writes with the number of work items (segments + one cut per persistent CTA), so a full
-# launch is reads x tiles + writes x items.
-NCU_DRAM = {"c2": (131.7, 21.1e6 / 179), "c5": (131.7, 20.98e6 / 155)}
-SCORE_CTAS = 148
-
-
 def measured_peak_gbs():
     try:
         return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def ncu_traffic(kind, n_tiles, nq):
+    """DRAM bytes of one score-kernel launch, scaled from the tracked ncu capture of the same kernel
+    (read bytes per tile, written bytes per query row); None when no capture is on record."""
+    try:
+        t = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))["score_stream_kernel"][kind]
+        return t["dram_read_bytes_per_tile"] * n_tiles + t["dram_write_bytes_per_query_row"] * nq
+    except Exception:
+        return None
 
 
 # --------------------------------------------------------------------------- CPU arm
@@ -196,21 +213,22 @@ def reference_arm(args, w):
 
     threads = os.cpu_count() or 1
     heads, tokens = w["kv_heads"], min(w["tokens"], 32768)
+    group = min(w["group"], 4)
     keys = synth_keys_numpy(1234, heads, tokens, 0).reshape(-1, HEAD_DIM)
     model = ora.Model(seeded_projection(100), HEAD_DIM, seed=100)
     tiles = model.encode_batch(keys, w["codec"])
     rng = np.random.default_rng(7)
-    q = rng.standard_normal((heads * w["group"], HEAD_DIM), dtype=np.float32)
+    q = rng.standard_normal((heads * group, HEAD_DIM), dtype=np.float32)
     prep = [model.prepare_query(x) for x in q]
     qc, qs = np.stack([p[0] for p in prep]), np.stack([p[1] for p in prep])
     for _ in range(max(args.warmup, 1)):
-        cpu_score_rate(tiles, qc, qs, w["group"], heads, 0.0, threads)
+        cpu_score_rate(tiles, qc, qs, group, heads, 0.0, threads)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_score_rate(tiles, qc, qs, w["group"], heads, 0.0, threads)
+        cpu_score_rate(tiles, qc, qs, group, heads, 0.0, threads)
     dt = time.perf_counter() - t0
     value = args.steps * len(tiles) / dt
-    sample = "%d tiles (%d KV heads x %d tokens of one layer) x %d queries per step" % (len(tiles), heads, tokens, w["group"])
+    sample = "%d tiles (%d KV heads x %d tokens of the context) x %d queries per step" % (len(tiles), heads, tokens, group)
     line = {
         "impl": "reference", "metric": "tiles_scored_per_s", "value": value, "unit": "tiles/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
@@ -226,9 +244,11 @@ def reference_arm(args, w):
 
 
 # --------------------------------------------------------------------------- GPU arm
-def build_shard(S, torch, w, rank, world, dev):
+def build_shard(S, torch, w, rank, world, dev, keep_keys_of_segment=None):
     """Generate this rank's keys on the device, encode them into tiles, prepare the queries.
-    Returns (tiles_u8, segments, q_coarse, q_sign, n_tiles, encode_tiles_per_s)."""
+    Returns (tiles_u8, segments, q_coarse, q_sign, n_tiles, encode_tiles_per_s, extras); extras holds
+    what the oracle check needs (projection and seed per layer, the raw queries, the bf16 keys of
+    one segment)."""
     L, H, G = w["layers"], w["kv_heads"], w["group"]
     if w["scaling"] == "weak":
         T, pos0 = w["tokens"], rank * w["tokens"]
@@ -248,8 +268,11 @@ def build_shard(S, torch, w, rank, world, dev):
     heads = torch.arange(H, device=dev, dtype=torch.int16).repeat_interleave(T).contiguous()
     enc_ms = 0.0
     chunk_tokens = min(T, 131072)
+    extras = {"layers": [], "queries": [], "keys": None, "pos0": pos0, "T": T}
     for l in range(L):
-        model = S.Model.from_projection(seeded_projection(100 + l), HEAD_DIM, 100 + l)
+        proj = seeded_projection(100 + l)
+        model = S.Model.from_projection(proj, HEAD_DIM, 100 + l, rht=bool(w.get("rht")))
+        extras["layers"].append((proj, 100 + l))
         gen.manual_seed(1234 + l)  # the per-channel scale belongs to the layer: the same on every rank
         chan = torch.exp(0.5 * torch.randn(HEAD_DIM, generator=gen, device=dev))
         gen.manual_seed(5678 + l + 7919 * rank)  # every rank holds different tokens
@@ -258,27 +281,343 @@ def build_shard(S, torch, w, rank, world, dev):
         for h in range(0, H, heads_per_call):
             for t0 in range(0, T, chunk_tokens):
                 t1 = min(T, t0 + chunk_tokens)
-                k = torch.randn(heads_per_call, t1 - t0, HEAD_DIM, generator=gen, device=dev) * chan
-                a, b = k[..., 0::2].clone(), k[..., 1::2].clone()
-                k[..., 0::2] = a * cos[t0:t1] - b * sin[t0:t1]
-                k[..., 1::2] = a * sin[t0:t1] + b * cos[t0:t1]
-                kb = k.to(torch.bfloat16).contiguous()
+                shape = (heads_per_call, t1 - t0, HEAD_DIM)
+                if w.get("dist") == "student_t":
+                    # Student-t (nu = 4) with 1 % of the entries x 20 (configuration 3)
+                    z = torch.randn(5, *shape, generator=gen, device=dev)
+                    k = z[0] / torch.sqrt((z[1:] ** 2).mean(0))
+                    k = torch.where(torch.rand(shape, generator=gen, device=dev) < 0.01, 20.0 * k, k)
+                elif w.get("dist") == "gauss_outlier_channels":
+                    # N(0,1), channels 7 and 93 x 8 (configuration 1)
+                    k = torch.randn(shape, generator=gen, device=dev)
+                    k[..., 7] *= 8.0
+                    k[..., 93] *= 8.0
+                else:
+                    k = torch.randn(shape, generator=gen, device=dev) * chan
+                    a, b = k[..., 0::2].clone(), k[..., 1::2].clone()
+                    k[..., 0::2] = a * cos[t0:t1] - b * sin[t0:t1]
+                    k[..., 1::2] = a * sin[t0:t1] + b * cos[t0:t1]
+                kb = k.contiguous() if w.get("f32") else k.to(torch.bfloat16).contiguous()
                 n = heads_per_call * (t1 - t0)
                 off = ((l * H + h) * T + t0) * 128
                 lo = h * T + t0
+                if keep_keys_of_segment is not None and l == keep_keys_of_segment[0] and h <= keep_keys_of_segment[1] < h + heads_per_call \
+                        and t0 == 0:
+                    extras["keys"] = kb[keep_keys_of_segment[1] - h, : min(t1, 4096)].float().cpu().numpy()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-                model.encode_keys(kb, w["codec"], n=n, key_dtype=S.BF16, positions=positions[lo:lo + n],
+                model.encode_keys(kb, w["codec"], n=n, key_dtype=S.F32 if w.get("f32") else S.BF16, positions=positions[lo:lo + n],
                                   head_ids=heads[lo:lo + n], out=tiles[off:off + n * 128])
                 e1.record()
                 torch.cuda.synchronize()
                 enc_ms += e0.elapsed_time(e1)
         gen.manual_seed(99 + l)  # queries are the same on every rank
         q = torch.randn(H * G, HEAD_DIM, generator=gen, device=dev)
+        extras["queries"].append(q.cpu().numpy())
         model.prepare_queries(q, nq=H * G, q_coarse_out=q_coarse[l * H * G:(l + 1) * H * G], q_sign_out=q_sign[l * H * G:(l + 1) * H * G])
         torch.cuda.synchronize()
         model.release()
-    return tiles, S.shard.shard_segments(L, H, T, G, pos0), q_coarse, q_sign, n_tiles, n_tiles / (enc_ms * 1e-3)
+    return tiles, S.shard.shard_segments(L, H, T, G, pos0), q_coarse, q_sign, n_tiles, n_tiles / (enc_ms * 1e-3), extras
+
+
+def verify_against_oracle(S, w, tiles, segs, q_coarse, q_sign, out_idx, out_sc, extras, layer, head, world):
+    """One (layer, KV head) segment of the timed workload against the CPU oracle, outside the timed
+    region: the first 4096 tile records bit for bit against the oracle's encoder, the prepared
+    queries of the segment bit for bit, and the top-k of the segment's query rows (at N = 1: scores
+    within 1e-3 of the oracle's, index sets equal except where scores tie within 2e-3; at N > 1 the
+    merged result mixes ranks, so the reported (index, score) pairs of this rank's token range are
+    checked against the oracle's scores of those tiles)."""
+    from oracle import pyoracle as ora
+
+    H, G, T, k = w["kv_heads"], w["group"], extras["T"], w["k"]
+    seg = layer * H + head
+    tb, nt, qb, nq, base = (int(x) for x in segs[seg].tolist())
+    host = np.frombuffer(tiles[tb * 128:(tb + nt) * 128].cpu().numpy().tobytes(), S.TILE_DTYPE)
+    proj, seed = extras["layers"][layer]
+    om = ora.Model(proj, HEAD_DIM, seed=seed, rht=bool(w.get("rht")))
+    ok = True
+    if extras["keys"] is not None:
+        n0 = len(extras["keys"])
+        want = om.encode_batch(extras["keys"], w["codec"], pos=np.arange(base, base + n0, dtype=np.uint32),
+                               head=np.full(n0, head, np.uint16))
+        ok &= host[:n0].tobytes() == want.tobytes()
+    qc = q_coarse[qb:qb + nq].cpu().numpy()
+    qs = q_sign[qb:qb + nq].cpu().numpy().view(np.uint64)
+    for j in (0, nq - 1):
+        wc, ws = om.prepare_query(extras["queries"][layer][head * G + j])
+        ok &= np.array_equal(qc[j], wc) and np.array_equal(qs[j], ws)
+    gi = out_idx[qb:qb + nq].cpu().numpy().view(np.uint32)
+    gs = out_sc[qb:qb + nq].cpu().numpy().view(np.float32)
+    for j in range(min(nq, 4)):
+        want = ora.score_tiles(host, qc[j], qs[j])
+        mine = (gi[j] >= base) & (gi[j] < base + nt)
+        ok &= bool(np.all(np.abs(want[gi[j][mine] - base] - gs[j][mine]) <= 1e-3))
+        if world == 1:
+            kk = min(k, nt)
+            oi, ov = ora.topk(want, kk)
+            ok &= bool(np.all(np.abs(gs[j][:kk] - ov) <= 1e-3))
+            ok &= all(abs(want[i] - ov[-1]) <= 2e-3 for i in set(oi) ^ set((gi[j][:kk] - base).tolist()))
+    return bool(ok)
+
+
+def time_blocks(torch, step, steps, barrier):
+    """BLOCKS blocks of `steps` steps, CUDA events around every block; returns the per-block ms."""
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(BLOCKS)]
+    barrier()
+    for a, b in ev:
+        a.record()
+        for _ in range(steps):
+            step()
+        b.record()
+    barrier()
+    return [a.elapsed_time(b) for a, b in ev]
+
+
+def run_scoring_workload(args, w, S, torch, dist, rank, local, world, dev, stream, verify=True, cpu_legs=True):
+    """Build, time and check one scoring workload; returns the JSON record (rank 0) or None."""
+    tiles, segs, q_coarse, q_sign, n_tiles, enc_rate, extras = build_shard(S, torch, w, rank, world, dev, keep_keys_of_segment=(0, 0))
+    nq, k = q_coarse.shape[0], w["k"]
+    out_idx = torch.empty(nq, k, dtype=torch.int32, device=dev)
+    out_sc = torch.empty(nq, k, dtype=torch.float32, device=dev)
+
+    # every rank's handle of the sharded scorer: the NCCL unique id of rank 0 travels by a torch broadcast
+    uid = None
+    if world > 1:
+        t = torch.from_numpy(S.shard_unique_id() if rank == 0 else np.zeros(128, np.uint8)).to(dev)
+        dist.broadcast(t, 0)
+        uid = t.cpu().numpy()
+    shard = S.Shard(uid, rank, world)
+
+    def step():
+        shard.score_topk(tiles, segs, q_coarse, q_sign, nq, k, out_index=out_idx, out_score=out_sc)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = S.launch_count()
+    S.timing_begin(BLOCKS * args.steps)
+    torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see the timed region only
+    block_ms = time_blocks(torch, step, args.steps, barrier)
+    torch.cuda.profiler.stop()
+    launches = (S.launch_count() - launches0) // BLOCKS
+    score_ms, merge_ms = S.timing_end(BLOCKS * args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    # per-component device times of a sharded step (events inside the library), a few steps outside the timed blocks
+    comp = np.zeros(3)
+    if world > 1:
+        shard.set_timing(True)
+        acc = []
+        for _ in range(10):
+            step()
+            acc.append(shard.last_times())
+        shard.set_timing(False)
+        comp = np.median(np.array(acc), axis=0)
+    verified = verify_against_oracle(S, w, tiles, segs, q_coarse, q_sign, out_idx, out_sc, extras, 0, 0, world) if verify else None
+
+    # ---- end to end through the C ABI with host buffers (pinned): queries up, top-k down, one call at a time
+    hq = q_coarse.cpu().pin_memory()
+    hs = q_sign.cpu().pin_memory()
+    h_idx = torch.empty(nq, k, dtype=torch.int32).pin_memory()
+    h_sc = torch.empty(nq, k, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        shard.score_topk(tiles, segs, hq, hs, nq, k, out_index=h_idx, out_score=h_sc)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_blocks = []
+    for _ in range(BLOCKS):
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        e2e_blocks.append(1e3 * (time.perf_counter() - t0))
+    barrier()
+    e2e_ok = bool(torch.equal(h_idx.to(dev), out_idx))
+
+    # The same end-to-end calls from two host threads (the C ABI is re-entrant; every thread has its own
+    # stream and staging buffers inside the library, and the reference's consumers call it from several
+    # worker threads): one caller's copies overlap the other caller's kernels.  A named extra, N = 1 only.
+    concurrent = None
+    if world == 1:
+        callers = 2
+        per = (args.steps + callers - 1) // callers
+        outs = [(torch.empty(nq, k, dtype=torch.int32).pin_memory(), torch.empty(nq, k, dtype=torch.float32).pin_memory())
+                for _ in range(callers)]
+        go = threading.Barrier(callers + 1)
+        failed = []
+
+        def caller(i, n_calls):
+            try:
+                S.set_device(local)  # thread-local in the library; no stream set: the library's own per-thread stream
+                for _ in range(2):
+                    S.score_topk(tiles, segs, hq, hs, nq, k, out_index=outs[i][0], out_score=outs[i][1])
+                go.wait()
+                for _ in range(n_calls):
+                    S.score_topk(tiles, segs, hq, hs, nq, k, out_index=outs[i][0], out_score=outs[i][1])
+            except Exception as exc:  # surfaces in the main thread
+                failed.append(exc)
+                go.abort()
+
+        threads = [threading.Thread(target=caller, args=(i, per)) for i in range(callers)]
+        for th in threads:
+            th.start()
+        go.wait()
+        t0 = time.perf_counter()
+        for th in threads:
+            th.join()
+        torch.cuda.synchronize()
+        piped_ms = 1e3 * (time.perf_counter() - t0) / (per * callers)
+        if failed:
+            raise failed[0]
+        assert torch.equal(outs[0][0], h_idx) and torch.equal(outs[1][0], h_idx), "concurrent callers disagree with the serial result"
+        concurrent = {"callers": callers, "ms_per_step": piped_ms, "value": n_tiles / (piped_ms * 1e-3)}
+
+    ms_block = float(np.median(block_ms))
+    e2e_block = float(np.median(e2e_blocks))
+    if world > 1:
+        t = torch.tensor([ms_block, e2e_block, max(block_ms), min(block_ms)] + list(comp), device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_block, e2e_block = float(t[0]), float(t[1])
+        block_ms = [float(t[3]), ms_block, float(t[2])]
+        comp = t[4:7].cpu().numpy()
+        v = torch.tensor([1 if (verified and e2e_ok) else 0], device=dev)
+        dist.all_reduce(v, op=dist.ReduceOp.MIN)
+        verified = bool(v.item())
+    shard.destroy()
+    if rank != 0:
+        return None
+
+    total_tiles = n_tiles * world
+    ms_step = ms_block / args.steps
+    value = total_tiles / (ms_step * 1e-3)
+    peak, peak_kind = measured_peak_gbs()
+    k_ms = float(np.median(score_ms)) if len(score_ms) else float("nan")
+    achieved = n_tiles * 128 / (k_ms * 1e-3) / 1e9
+    e2e_ms = e2e_block / args.steps
+    rec = {
+        "metric": "tiles_scored_per_s", "value": value, "unit": "tiles/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": w["scaling"],
+        "vs_baseline": None, "dtype": "int4->f32", "data": "synthetic", "config": workload_config(w, world),
+        "blocks_ms_per_step": {"min": min(block_ms) / args.steps, "median": ms_step, "max": max(block_ms) / args.steps, "blocks": BLOCKS},
+        "scores_per_s": value * w["group"],
+        "hbm_gbs_whole_step": total_tiles * 128 / (ms_step * 1e-3) / 1e9,
+        "roofline": {"bound": "hbm", "kernel": "score_stream_kernel (fused eq. 2.3 score + streaming top-k)", "achieved": achieved,
+                     "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                     "frac_of_nominal_8000": achieved / 8000.0, "kernel_ms": k_ms,
+                     "merge_kernel_ms": float(np.median(merge_ms)) if len(merge_ms) else None,
+                     "algorithmic_bytes_per_launch": n_tiles * 128,
+                     "traffic": ncu_traffic(w["codec_name"], n_tiles, nq),
+                     "traffic_source": "ncu dram__bytes of the same kernel on this workload shape, per tile and per query row, "
+                                       "scaled to this launch"},
+        "e2e": {"value": total_tiles / (e2e_ms * 1e-3), "unit": "tiles/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(nq * (512 + 32)), "d2h_bytes_per_step": int(nq * k * 8),
+                "schedule": "one call at a time from one host thread", "concurrent_callers": concurrent},
+        "gpu_launches": int(launches),
+        "encode_tiles_per_s": enc_rate,
+        "verified": bool(verified and e2e_ok),
+        "clocks": clocks,
+    }
+    if world > 1:
+        rec["exchange"] = {"entry_point": "slha_b200_shard_score_topk", "ms_local_score_topk": float(comp[0]),
+                           "ms_all_gather": float(comp[1]), "ms_merge": float(comp[2]),
+                           "all_gather_bytes_per_rank": int(2 * nq * k * 4)}
+    if world == 1 and cpu_legs:
+        n_s = min(n_tiles, w["kv_heads"] * min(w["tokens"], 32768))
+        heads, group = w["kv_heads"], min(w["group"], 4)
+        per = n_tiles // (w["layers"] * heads)
+        host_tiles = np.concatenate([np.frombuffer(tiles[h * per * 128:(h * per + n_s // heads) * 128].cpu().numpy().tobytes(), S.TILE_DTYPE)
+                                     for h in range(heads)])
+        threads = os.cpu_count() or 1
+        rows = [h * w["group"] + g for h in range(heads) for g in range(group)]
+        hqc = hq.numpy()[rows]
+        hqs = hs.numpy().view(np.uint64)[rows]
+        rate, dt, reps = cpu_score_rate(host_tiles, hqc, hqs, group, heads, 3.0, threads)
+        from oracle import pyoracle as ora
+
+        rec["cpu_baseline"] = {
+            "value": rate, "unit": "tiles/s", "cores": threads, "kind": "port",
+            "isa": ["scalar", "avx2", "avx512"][ora.simd_level()],
+            "sample": "%d tiles (%d KV heads x %d tokens) x %d queries, %d passes in %.1f s" % (n_s, heads, n_s // heads, group, reps, dt),
+        }
+        # For context only: the reference's own CUDA scoring kernel (one thread per tile, one launch
+        # per query, 256-thread blocks as in its tests) on the same resident tiles, when the built
+        # oracle/_ref library travelled with the repository.  It writes full score vectors and has
+        # no top-k; the figure is tiles per second with every tile scored against its 4 queries.
+        refk = ora.ref_cuda_library()
+        if refk is not None:
+            pt = n_s // heads
+            sc = torch.empty(group * pt, dtype=torch.float32, device=dev)
+            ms_out = ctypes.c_float(0.0)
+            total_ms = 0.0
+            for h in range(heads):
+                rc = refk.slha_ref_cuda_time(tiles.data_ptr() + h * per * 128, pt, q_coarse[h * w["group"]:].data_ptr(),
+                                             q_sign[h * w["group"]:].data_ptr(), group, sc.data_ptr(), 3, stream.cuda_stream,
+                                             ctypes.byref(ms_out))
+                assert rc == 0, rc
+                total_ms += ms_out.value
+            rec["reference_cuda_kernel"] = {
+                "value": n_s / (total_ms * 1e-3), "unit": "tiles/s", "ms": total_ms,
+                "sample": "slhav2-vram/kernels/slha_score.cu unmodified: %d KV heads x %d tiles x %d queries, full score vectors, no top-k" % (heads, pt, group),
+            }
+    return rec
+
+
+def run_pool_workload(args, S, torch, dev):
+    """Configuration 4 at full size: one pool of 131072 tokens x 8 KV heads = 1 048 576 slots of mixed
+    8/4 tiles under a budget of 60 % of the full-HOT footprint, H2O importance eviction with a sink of
+    4 and a recent window of 2048.  A step = append 8 keys (one token x 8 heads), score one GQA group
+    with top-64, observe the query (H2O), enforce the budget.  Host-timed through the C ABI."""
+    cap, d = 131072 * 8, HEAD_DIM
+    budget = int(0.6 * 128 * cap)
+    model = S.Model.from_projection(seeded_projection(7), d, 7)
+    pool = S.TilePool(cap, budget, S.PAGE_LOWEST_IMPACT_FIRST, S.EVICT_IMPORTANCE, sink_window=4, recent_window=2048)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4242)
+    steps = 256
+    fill = cap - 8 * (steps + 16)
+    for t0 in range(0, fill, 131072):
+        n = min(131072, fill - t0)
+        kb = torch.randn(n, d, generator=gen, device=dev).to(torch.bfloat16).contiguous()
+        pos = torch.arange(t0, t0 + n, device=dev, dtype=torch.int32) // 8
+        torch.cuda.synchronize()
+        pool.append_keys(model, kb, S.CODEC_MIXED, n=n, key_dtype=S.BF16, positions=pos)
+    q = torch.randn(steps + 16, 4, d, generator=gen, device=dev)
+    qc, qs = model.prepare_queries(q.reshape(-1, d), nq=4 * (steps + 16))
+    keys = torch.randn(steps + 16, 8, d, generator=gen, device=dev).to(torch.bfloat16).contiguous()
+    torch.cuda.synchronize()
+    pool.enforce_budget()
+
+    def step(i):
+        pos = np.full(8, fill // 8 + i, np.uint32)
+        pool.append_keys(model, keys[i], S.CODEC_MIXED, n=8, key_dtype=S.BF16, positions=pos)
+        pool.score_topk(qc[4 * i:4 * i + 4], qs[4 * i:4 * i + 4], 4, 64)
+        pool.observe_query(qc[4 * i], qs[4 * i], 1.0)
+        pool.enforce_budget()
+
+    for i in range(16):
+        step(i)
+    S.synchronize()
+    t0 = time.perf_counter()
+    for i in range(16, 16 + steps):
+        step(i)
+    S.synchronize()
+    ms = 1e3 * (time.perf_counter() - t0) / steps
+    st = pool.stats()
+    return {"workload": "config4 elastic pool: 1048576 slots, mixed 8/4, budget 60 %, H2O sink 4 + recent 2048; "
+                        "step = append 8 keys + score 4 queries top-64 + observe + enforce_budget",
+            "ms_per_step": ms, "steps": steps, "hot": st["hot"], "warm": st["warm"], "cold": st["cold"],
+            "live_bytes": st["live_bytes"], "budget": budget, "within_budget": bool(st["live_bytes"] <= budget)}
 
 
 def gpu_arm(args, w):
@@ -306,287 +645,26 @@ def gpu_arm(args, w):
     torch.cuda.set_stream(stream)
     S.set_stream(stream.cuda_stream)
 
-    tiles, segs, q_coarse, q_sign, n_tiles, enc_rate = build_shard(S, torch, w, rank, world, dev)
-    nq, k = q_coarse.shape[0], w["k"]
-    # candidate block: [2][nq][k] (indices, then score bits) so one all-gather moves both
-    cand = torch.empty(2, nq, k, dtype=torch.int32, device=dev)
-    cnt = torch.empty(nq, dtype=torch.int32, device=dev)
-    gathered = torch.empty(world, 2, nq, k, dtype=torch.int32, device=dev) if world > 1 else None
-    out = torch.empty(2, nq, k, dtype=torch.int32, device=dev)
-
-    short = None
-    # the short first exchange round needs a host decision per step (a collective flag), which costs more
-    # than it saves when steps are this short (config 5 at 8 GPUs: 0.44 ms with it, 0.24 ms without);
-    # SLHA_BENCH_KSHORT=<n> or =auto switches it on for the one-step-at-a-time loop
-    ks_env = os.environ.get("SLHA_BENCH_KSHORT", "0")
-    k_short = S.shard.short_exchange_len(k, world) if ks_env == "auto" else (int(ks_env) or k)
-    if world > 1 and k_short < k:
-        # first exchange round with the best k_short candidates per rank; `overflow` is the collective
-        # check that no rank held back a candidate that belongs to the merged top-k
-        send = torch.empty(2, nq, k_short, dtype=torch.int32, device=dev)
-        gathered_short = torch.empty(world, 2, nq, k_short, dtype=torch.int32, device=dev)
-        flag = torch.zeros(1, dtype=torch.int32, device=dev)
-
-        def overflow(c, o):
-            unsent = c[0][:, k_short] != -1
-            viol = unsent & (c[1][:, k_short].view(torch.float32) >= o[1][:, k - 1].view(torch.float32))
-            flag.copy_(viol.any().to(torch.int32).reshape(1))
-            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
-            return bool(flag.item())
-
-        short = S.shard.ShortExchange(k_short, send, gathered_short, lambda s_, c: s_.copy_(c[:, :, :k_short]), overflow)
-    scorer = S.shard.ShardedScorer(world, nq, k, cand, gathered, out,
-                                   (lambda g, c: dist.all_gather_into_tensor(g, c)) if world > 1 else None, count=cnt,
-                                   short=short)
-
-    def step():
-        scorer.step(tiles, segs, q_coarse, q_sign)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    launches0 = S.launch_count()
-    S.timing_begin(args.steps)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see the timed region only
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    torch.cuda.profiler.stop()
-    ms = e0.elapsed_time(e1)
-    launches = S.launch_count() - launches0
-    score_ms, merge_ms = S.timing_end(args.steps)
-    clocks = sampler.stop() if rank == 0 else None
-
-    # ---- N > 1: the same K steps with the exchange and merge of step i on a second stream while step
-    # i+1 is scored (the steps are independent: each has its own candidate / gathered / result buffers)
-    serial_ms, ms_pipe, pipelined, pipe = ms, float("inf"), False, None
-    if world > 1 and os.environ.get("SLHA_BENCH_PIPELINE", "1") != "0":
-        xstream = torch.cuda.Stream(device=dev, priority=-1)
-
-        class TorchStreams:
-            def use_score(self):
-                torch.cuda.set_stream(stream)
-                S.set_stream(stream.cuda_stream)
-
-            def use_exchange(self):
-                torch.cuda.set_stream(xstream)
-                S.set_stream(xstream.cuda_stream)
-
-            def record(self, tag):
-                ev = torch.cuda.Event()
-                ev.record()
-                return ev
-
-            def wait_event(self, ev):
-                torch.cuda.current_stream().wait_event(ev)
-
-            def sync(self, ev):
-                ev.synchronize()
-
-        ag = lambda g, c: dist.all_gather_into_tensor(g, c)
-        slots = [S.shard.ShardedScorer(world, nq, k, torch.empty_like(cand), torch.empty_like(gathered), torch.empty_like(out), ag,
-                                       count=torch.empty_like(cnt)) for _ in range(3)]
-        pipe = S.shard.PipelinedScorer(slots, TorchStreams())
-        for _ in range(4):
-            pipe.submit(tiles, segs, q_coarse, q_sign)
-        pipe.drain()
-        assert all(torch.equal(sl.out, scorer.out) for sl in slots), "pipelined result differs"
-        barrier()
-        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        p0.record()
-        for _ in range(args.steps):
-            pipe.submit(tiles, segs, q_coarse, q_sign)
-        for ev in pipe.exchanged:
-            stream.wait_event(ev)
-        p1.record()
-        pipe.drain()
-        barrier()
-        ms_pipe = p0.elapsed_time(p1)
-
-    # ---- end to end through the C ABI with host buffers (pinned): queries up, top-k down
-    hq = q_coarse.cpu().pin_memory()
-    hs = q_sign.cpu().pin_memory()
-    h_idx = torch.empty(nq, k, dtype=torch.int32).pin_memory()
-    h_sc = torch.empty(nq, k, dtype=torch.float32).pin_memory()
-    h_cnt = torch.empty(nq, dtype=torch.int32).pin_memory()
-
-    def e2e_step():
+    line = run_scoring_workload(args, w, S, torch, dist, rank, local, world, dev, stream)
+    also = {}
+    if args.also and args.workload == "c5" and not (args.layers or args.tokens):
+        light = argparse.Namespace(**vars(args))
+        light.steps = max(5, args.steps // 4)
+        for name in (["c2", "c1", "c3"] if world == 1 else ["c2"]):
+            torch.cuda.empty_cache()
+            r = run_scoring_workload(light, dict(WORKLOADS[name]), S, torch, dist, rank, local, world, dev, stream, cpu_legs=False)
+            if r is not None:
+                also[name] = {kk: r[kk] for kk in ("value", "unit", "ms_per_step", "scaling", "config", "roofline", "e2e", "encode_tiles_per_s",
+                                                   "verified", "gpu_launches", "blocks_ms_per_step") if kk in r}
+                if "exchange" in r:
+                    also[name]["exchange"] = r["exchange"]
         if world == 1:
-            S.score_topk(tiles, segs, hq, hs, nq, k, out_index=h_idx, out_score=h_sc, out_count=h_cnt)
-        else:
-            scorer.step(tiles, segs, hq, hs, out_index=h_idx, out_score=h_sc)
-
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.perf_counter()
-    f0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    f1.record()
-    barrier()
-    e2e_ms = max(f0.elapsed_time(f1), 1e3 * (time.perf_counter() - t0))  # host waits are part of an end-to-end call
-
-    # The same end-to-end calls from two host threads (the C ABI is re-entrant; every thread has its
-    # own stream and staging buffers inside the library, and the reference's consumers call it from
-    # several worker threads): one caller's copies overlap the other caller's kernels.  Every step still
-    # moves its own queries up and its own results down inside the timed region.
-    e2e_serial_ms, callers = e2e_ms, 1
-    if world > 1 and pipe is not None:
-        # the overlapped schedule end to end: every step uploads its queries from pinned host memory
-        # into the slot's device buffers and downloads the slot's merged result into pinned host memory
-        dq = [(torch.empty_like(q_coarse), torch.empty_like(q_sign)) for _ in slots]
-        hout = [torch.empty(2, nq, k, dtype=torch.int32).pin_memory() for _ in slots]
-
-        def upload(i):
-            dq[i][0].copy_(hq, non_blocking=True)
-            dq[i][1].copy_(hs, non_blocking=True)
-            return dq[i]
-
-        def download(i):
-            hout[i].copy_(slots[i].out, non_blocking=True)
-
-        for _ in range(4):
-            pipe.submit(tiles, segs, None, None, upload, download)
-        pipe.drain()
-        assert all(torch.equal(h, scorer.out.cpu()) for h in hout), "pipelined end-to-end result differs"
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            pipe.submit(tiles, segs, None, None, upload, download)
-        pipe.drain()
-        torch.cuda.synchronize()
-        e2e_pipe_ms = 1e3 * (time.perf_counter() - t0)
-        barrier()
-        e2e_ms = e2e_pipe_ms  # (the choice is made after the maximum over the ranks, below)
-    if world == 1:
-        import threading
-
-        callers = 2
-        per = (args.steps + callers - 1) // callers
-        outs = [(torch.empty(nq, k, dtype=torch.int32).pin_memory(), torch.empty(nq, k, dtype=torch.float32).pin_memory(),
-                 torch.empty(nq, dtype=torch.int32).pin_memory()) for _ in range(callers)]
-        go = threading.Barrier(callers + 1)
-        failed = []
-
-        def caller(i, n_calls):
-            try:
-                S.set_device(local)  # thread-local in the library; no stream set: the library's own per-thread stream
-                for _ in range(2):
-                    S.score_topk(tiles, segs, hq, hs, nq, k, out_index=outs[i][0], out_score=outs[i][1], out_count=outs[i][2])
-                go.wait()
-                for _ in range(n_calls):
-                    S.score_topk(tiles, segs, hq, hs, nq, k, out_index=outs[i][0], out_score=outs[i][1], out_count=outs[i][2])
-            except Exception as exc:  # surfaces in the main thread
-                failed.append(exc)
-                go.abort()
-
-        threads = [threading.Thread(target=caller, args=(i, per)) for i in range(callers)]
-        for th in threads:
-            th.start()
-        go.wait()
-        t0 = time.perf_counter()
-        for th in threads:
-            th.join()
-        torch.cuda.synchronize()
-        piped_ms = 1e3 * (time.perf_counter() - t0) * args.steps / (per * callers)
-        if failed:
-            raise failed[0]
-        assert torch.equal(outs[0][0], h_idx) and torch.equal(outs[1][0], h_idx), "concurrent callers disagree with the serial result"
-        e2e_ms = min(piped_ms, e2e_serial_ms)
-
-    if world > 1:
-        t = torch.tensor([ms_pipe, e2e_ms, serial_ms, e2e_serial_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_pipe, e2e_ms, serial_ms, e2e_serial_ms = float(t[0]), float(t[1]), float(t[2]), float(t[3])
-        e2e_ms = min(e2e_ms, e2e_serial_ms)
-        pipelined = ms_pipe < serial_ms  # the same decision on every rank (both are maxima over the ranks)
-        ms = min(ms_pipe, serial_ms)
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    total_tiles = n_tiles * world
-    ms_step = ms / args.steps
-    value = total_tiles / (ms_step * 1e-3)
-    peak, peak_kind = measured_peak_gbs()
-    k_ms = float(np.mean(score_ms)) if len(score_ms) else float("nan")
-    achieved = n_tiles * 128 / (k_ms * 1e-3) / 1e9
-    line = {
-        "metric": "tiles_scored_per_s", "value": value, "unit": "tiles/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": w["scaling"],
-        "vs_baseline": None, "dtype": "int4->f32", "data": "synthetic", "config": workload_config(w, world),
-        "scores_per_s": value * w["group"],
-        "hbm_gbs_whole_step": total_tiles * 128 / (ms_step * 1e-3) / 1e9,
-        "roofline": {"bound": "hbm", "kernel": "score_mma_kernel (fused score + top-k)", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
-                     "kernel_ms": k_ms, "merge_kernel_ms": float(np.mean(merge_ms)) if len(merge_ms) else None,
-                     "algorithmic_bytes_per_launch": n_tiles * 128,
-                     "traffic": NCU_DRAM[args.workload][0] * n_tiles + NCU_DRAM[args.workload][1] * (len(segs) + SCORE_CTAS - 1),
-                     "traffic_source": "ncu dram__bytes_read per tile and dram__bytes_write per work item on a reduced case, "
-                                       "scaled to this launch's tiles and work items (profiles/)"},
-        "e2e": {"value": total_tiles / (e2e_ms / args.steps * 1e-3), "unit": "tiles/s", "ms_per_step": e2e_ms / args.steps,
-                "h2d_bytes_per_step": int(nq * (512 + 32)), "d2h_bytes_per_step": int(nq * k * 8 + (nq * 4 if world == 1 else 0)),
-                "concurrent_callers": callers if e2e_ms < e2e_serial_ms else 1,
-                "overlapped_with_next_step": bool(world > 1 and e2e_ms < e2e_serial_ms),
-                "one_call_at_a_time": {"value": total_tiles / (e2e_serial_ms / args.steps * 1e-3), "ms_per_step": e2e_serial_ms / args.steps}},
-        "gpu_launches": int(launches),
-        "encode_tiles_per_s": enc_rate,
-        "clocks": clocks,
-    }
-    if world > 1:
-        line["exchange"] = {"k_short": k_short if short is not None else k, "steps_needing_full_lists": scorer.full_exchanges,
-                            "overlapped_with_next_step": pipelined, "ms_per_step_one_step_at_a_time": serial_ms / args.steps}
-    if world == 1:
-        n_s = min(n_tiles, w["kv_heads"] * min(w["tokens"], 32768))
-        heads = w["kv_heads"]
-        host_tiles = np.frombuffer(tiles[: n_s * 128].cpu().numpy().tobytes(), S.TILE_DTYPE)
-        threads = os.cpu_count() or 1
-        hqc = hq[: heads * w["group"]].numpy()
-        hqs = hs[: heads * w["group"]].numpy().view(np.uint64)
-        rate, dt, reps = cpu_score_rate(host_tiles, hqc, hqs, w["group"], heads, 3.0, threads)
-        from oracle import pyoracle as ora
-
-        line["cpu_baseline"] = {
-            "value": rate, "unit": "tiles/s", "cores": threads, "kind": "port",
-            "isa": ["scalar", "avx2", "avx512"][ora.simd_level()],
-            "sample": "%d tiles (%d KV heads x %d tokens) x %d queries, %d passes in %.1f s" % (n_s, heads, n_s // heads, w["group"], reps, dt),
-        }
-        # For context only: the reference's own CUDA scoring kernel (one thread per tile, one launch
-        # per query, 256-thread blocks as in its tests) on the same resident tiles, when the built
-        # oracle/_ref library travelled with the repository.  It writes full score vectors and has
-        # no top-k; the figure is tiles per second with every tile scored against its 4 queries.
-        refk = ora.ref_cuda_library()
-        if refk is not None:
-            per = n_s // heads
-            sc = torch.empty(w["group"] * per, dtype=torch.float32, device=dev)
-            ms_out = ctypes.c_float(0.0)
-            total_ms = 0.0
-            for h in range(heads):
-                rc = refk.slha_ref_cuda_time(tiles.data_ptr() + h * per * 128, per, q_coarse[h * w["group"]:].data_ptr(),
-                                             q_sign[h * w["group"]:].data_ptr(), w["group"], sc.data_ptr(), 3, stream.cuda_stream,
-                                             ctypes.byref(ms_out))
-                assert rc == 0, rc
-                total_ms += ms_out.value
-            line["reference_cuda_kernel"] = {
-                "value": n_s / (total_ms * 1e-3), "unit": "tiles/s", "ms": total_ms,
-                "sample": "slhav2-vram/kernels/slha_score.cu unmodified: %d KV heads x %d tiles x %d queries, full score vectors, no top-k" % (heads, per, w["group"]),
-            }
-    print(json.dumps(line))
+            torch.cuda.empty_cache()
+            S.set_stream(None)
+            also["c4"] = run_pool_workload(args, S, torch, dev)
+    if rank == 0:
+        line["also"] = also
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
@@ -594,10 +672,11 @@ def gpu_arm(args, w):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-also", dest="also", action="store_false", help="only the named workload (no c1..c4 sub-records)")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: shrink the workload to this many layers")
     ap.add_argument("--tokens", type=int, default=0, help="profiling aid: shrink the workload to this many tokens")
     args = ap.parse_args()

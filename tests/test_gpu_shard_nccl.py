@@ -1,0 +1,92 @@
+"""The sharded step behind the C ABI (slha_b200_shard_*) on two real GPUs: two processes, one per
+GPU, exchange the NCCL unique id through a file, score their token ranges and must both end up
+with the top-k of the whole context (computed on one GPU and by the CPU oracle).  Skipped on a
+machine with fewer than two GPUs."""
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+S = pytest.importorskip("slhav2_b200")
+
+WORKER = r"""
+import os, sys, time
+import numpy as np
+rank, world, tmp = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+import slhav2_b200 as S
+from slhav2_b200 import shard
+from tests import helpers as H
+from tests.test_gpu_topk import check_topk
+S.set_device(rank)
+n, nq, k = 60000, 8, 512
+tiles = H.random_tiles(n, 1, seed=91, warm_every=13)
+qc, qs = H.random_queries(nq, 92)
+idf = os.path.join(tmp, "nccl_id.npy")
+if rank == 0:
+    np.save(idf + ".tmp.npy", S.shard_unique_id())
+    os.replace(idf + ".tmp.npy", idf)
+else:
+    for _ in range(600):
+        if os.path.exists(idf):
+            break
+        time.sleep(0.05)
+sh = S.Shard(np.load(idf), rank, world)
+start, count = shard.shard_range(n, rank, world)
+dt = S.to_device(tiles[start:start + count])
+# two segments of 4 queries each over this rank's token range; indices are global token positions
+segs = S.make_segments([(0, count, 0, 4, start), (0, count, 4, 4, start)])
+sh.set_timing(True)
+for _ in range(3):
+    gi, gs = sh.score_topk(dt, segs, qc, qs, nq, k)
+ms = sh.last_times()
+assert np.all(ms >= 0) and ms[0] > 0
+full = [(0, n, 0, 4, 0), (0, n, 4, 4, 0)]
+check_topk(tiles, full, qc, qs, k, gi, gs, np.full(nq, k))
+np.save(os.path.join(tmp, "out%d.npy" % rank), np.stack([gi.astype(np.float64), gs.astype(np.float64)]))
+sh.destroy()
+print("rank", rank, "ok", ms)
+"""
+
+
+def test_two_gpu_sharded_step_through_the_c_abi():
+    if S.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    tmp = tempfile.mkdtemp()
+    env = dict(os.environ, PYTHONPATH=root, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, "-c", WORKER, str(r), "2", tmp], env=env, cwd=root, stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outs.append(o)
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)
+    a, b = np.load(os.path.join(tmp, "out0.npy")), np.load(os.path.join(tmp, "out1.npy"))
+    assert np.array_equal(a, b)  # every rank holds the same merged result
+
+
+def test_single_rank_shard_handle_needs_no_nccl():
+    from tests import helpers as H
+    from tests.test_gpu_topk import check_topk
+
+    n, nq, k = 9000, 3, 100
+    tiles = H.random_tiles(n, 2, seed=5)
+    qc, qs = H.random_queries(nq, 6)
+    sh = S.Shard(None, 0, 1)
+    segs = [(0, n, 0, nq, 7)]
+    gi, gs = sh.score_topk(S.to_device(tiles), S.make_segments(segs), qc, qs, nq, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gs, np.full(nq, k))
+    with pytest.raises(S.SlhaError):
+        S.Shard(None, 0, 2)  # more than one rank needs the unique id
+    with pytest.raises(S.SlhaError):
+        S.Shard(None, 3, 2)
+    sh.destroy()
