@@ -161,6 +161,13 @@ uint64_t slha_b200_launch_count(void);
  * kernel, so that a test can require both to give the same answers.  The
  * library reads no environment variable; this call is the only switch. */
 int32_t slha_b200_debug_force_generic_score(int32_t on);
+/* Counters of the calling thread's latest fused score + top-k call that ran on the
+ * tensor-core kernel (no counterpart in the reference; the stats getter planned
+ * for operators): out[0] query rows, out[1] rows that were handed to the generic
+ * kernel (another codec, a query outside the fp16 split, a full candidate buffer),
+ * out[2] candidates the rows' buffers received in all, out[3] slots per buffer.
+ * Waits for the stream.  All zero when no such call has run. */
+int32_t slha_b200_last_score_stats(uint64_t* out /* 4 values */);
 /* Device timing of the fused score + top-k path: after timing_begin, each of
  * the calling thread's next `max_calls` slha_b200_score_topk /
  * slha_b200_pool_score_topk calls records CUDA events on its stream around the
@@ -281,6 +288,31 @@ int32_t slha_b200_score_topk_noalloc(const SciRustSlhaTile* tiles, const SlhaB20
                                      size_t n_segments, const float* q_coarse, const uint64_t* q_sign,
                                      size_t n_queries, uint32_t k, uint32_t* out_index,
                                      float* out_score, uint32_t* out_count);
+
+/*
+ * Decode tail on the selected tiles: for every query row, softmax over its k
+ * (index, score) winners -- logits score * scale, maximum subtracted, as
+ * metrics::softmax_into (scirust/src/metrics.rs:338-420) -- and the weighted
+ * sum of their value rows, as aggregate_v of the reference's decode proxy
+ * (scirust/examples/benchmark_decode.rs:28-38, :82-95; the proxy runs both over
+ * the whole context, here they run over the top-k).  Entries with index
+ * 0xFFFFFFFF (padding) and entries past top_count[j] weigh nothing.
+ *   values            device memory, rows of d_v elements (float32 or
+ *                     bfloat16), `value_row_stride` elements apart
+ *   value_row_base    per query row (may be NULL = 0): the value row of winner
+ *                     i of row j is value_row_base[j] + top_index[j*k + i],
+ *                     modulo 2^64 (the base carries the KV head's first row
+ *                     minus the segment's index_base)
+ *   out               n_queries x d_v floats; weights_out (may be NULL)
+ *                     n_queries x k softmax weights.  Host or device.
+ * Results agree with the sequential float32 / float64 reference arithmetic to
+ * about 1e-6 relative (sums are taken in a different, fixed order).
+ */
+int32_t slha_b200_attend_topk(const uint32_t* top_index, const float* top_score,
+                              const uint32_t* top_count, size_t n_queries, uint32_t k, float scale,
+                              const void* values, int32_t value_dtype, size_t d_v,
+                              size_t value_row_stride, const uint64_t* value_row_base, float* out,
+                              float* weights_out);
 
 /*
  * Token-range sharding over the GPUs of one node, one handle per rank (one

@@ -468,3 +468,56 @@ def ref_cuda_scores(tiles, q_coarse, q_sign):
     if rc:
         raise RuntimeError("reference CUDA kernel failed: cudaError %d" % (rc - 1000))
     return out
+
+
+def softmax_into(scores, scale):
+    """metrics::softmax_into (scirust/src/metrics.rs:338-420): f64 logits score * scale, maximum
+    subtracted, f32 weights normalised and then renormalised by their rounded sum; NaN, a
+    non-finite scale or an empty / all -inf input give zeros, +inf logits share the mass."""
+    s = np.asarray(scores, np.float32)
+    out = np.zeros(len(s), np.float32)
+    if len(s) == 0 or not np.isfinite(scale) or np.any(np.isnan(s)):
+        return out
+    logit = s.astype(np.float64) * np.float64(np.float32(scale))
+    if np.any(np.isnan(logit)):
+        return out
+    pinf = np.isposinf(logit)
+    if pinf.any():
+        out[pinf] = np.float32(1.0 / pinf.sum())
+        return out
+    mx = logit.max()
+    if np.isneginf(mx):
+        return out
+    e = np.exp(logit - mx)
+    out = e.astype(np.float32)
+    total = e.sum()
+    if not np.isfinite(total) or total <= 0:
+        return np.zeros(len(s), np.float32)
+    out = (out.astype(np.float64) / total).astype(np.float32)
+    rounded = out.astype(np.float64).sum()
+    if np.isfinite(rounded) and rounded > 0:
+        out = (out.astype(np.float64) / rounded).astype(np.float32)
+    return out
+
+
+def attend_topk(top_index, top_score, scale, values, top_count=None, row_base=None):
+    """The reference's decode tail (scirust/examples/benchmark_decode.rs:82-95) over every row's selected
+    tiles: softmax_into over the row's valid (index, score) pairs, then aggregate_v (:28-38,
+    out[j] += w * row[j] in list order, float32).  values: [rows][d_v] float32."""
+    ti = np.asarray(top_index, np.uint32)
+    ts = np.asarray(top_score, np.float32)
+    nq, k = ti.shape
+    v = np.asarray(values, np.float32)
+    out = np.zeros((nq, v.shape[1]), np.float32)
+    weights = np.zeros((nq, k), np.float32)
+    for q in range(nq):
+        n = k if top_count is None else min(int(top_count[q]), k)
+        valid = np.nonzero(ti[q, :n] != 0xFFFFFFFF)[0]
+        w = softmax_into(ts[q, valid], scale)
+        weights[q, valid] = w
+        base = 0 if row_base is None else int(row_base[q])
+        acc = np.zeros(v.shape[1], np.float32)
+        for i, wi in zip(valid, w):
+            acc = (acc + np.float32(wi) * v[(base + int(ti[q, i])) % (1 << 64)]).astype(np.float32)
+        out[q] = acc
+    return out, weights

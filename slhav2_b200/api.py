@@ -74,6 +74,7 @@ SIGNATURES = {
     "slha_b200_set_stream": (_i32, [_vp]),
     "slha_b200_launch_count": (_u64, []),
     "slha_b200_debug_force_generic_score": (_i32, [_i32]),
+    "slha_b200_last_score_stats": (_i32, [_vp]),
     "slha_b200_timing_begin": (_i32, [_u32]),
     "slha_b200_timing_end": (_i32, [_vp, _vp, _u32, _vp]),
     "slha_b200_malloc": (_i32, [_sz, C.POINTER(_vp)]),
@@ -88,6 +89,7 @@ SIGNATURES = {
     "slha_b200_score_topk_noalloc": (_i32, [_vp, _vp, _sz, _vp, _vp, _sz, _u32, _vp, _vp, _vp]),
     "slha_b200_topk_merge": (_i32, [_vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
     "slha_b200_topk_merge_strided": (_i32, [_vp, _vp, _u32, _u64, _u32, _u32, _u32, _vp, _vp]),
+    "slha_b200_attend_topk": (_i32, [_vp, _vp, _vp, _sz, _u32, C.c_float, _vp, _i32, _sz, _sz, _vp, _vp, _vp]),
     "slha_b200_shard_unique_id": (_i32, [_vp]),
     "slha_b200_shard_init": (_i32, [_vp, _i32, _i32, C.POINTER(_vp)]),
     "slha_b200_shard_destroy": (_i32, [_vp]),
@@ -190,6 +192,13 @@ def launch_count():
 def debug_force_generic_score(on):
     """Checking aid: the calling thread's score_topk calls use only the generic CUDA-core kernel."""
     _check(load_library().slha_b200_debug_force_generic_score(1 if on else 0))
+
+
+def last_score_stats():
+    """Counters of this thread's latest tensor-core score_topk call."""
+    out = np.zeros(4, np.uint64)
+    _check(load_library().slha_b200_last_score_stats(ptr(out)))
+    return {"rows": int(out[0]), "rows_handed_to_generic_kernel": int(out[1]), "candidates_appended": int(out[2]), "buffer_slots": int(out[3])}
 
 
 def timing_begin(max_calls):
@@ -420,6 +429,22 @@ def topk_merge(cand_index, cand_score, n_lists, n_queries, k_in, k_out, out_inde
         )
     )
     return out_index, out_score
+
+
+def attend_topk(top_index, top_score, k, scale, values, d_v, value_dtype=F32, top_count=None, value_row_stride=None,
+                value_row_base=None, out=None, weights_out=None):
+    """Decode tail: softmax over every row's k winners, then the weighted sum of their value rows
+    (values: device memory).  Returns out [nq][d_v] (and fills weights_out [nq][k] when given)."""
+    ti, ts = _np(top_index, np.uint32), _np(top_score, np.float32)
+    nq = (ti.size if isinstance(ti, np.ndarray) else ti.numel()) // k
+    if out is None:
+        out = np.zeros((nq, d_v), np.float32)
+    base = None if value_row_base is None else _np(value_row_base, np.uint64)
+    cnt = None if top_count is None else _np(top_count, np.uint32)
+    _check(load_library().slha_b200_attend_topk(ptr(ti), ptr(ts), ptr(cnt), nq, k, scale, ptr(values), value_dtype, d_v,
+                                                d_v if value_row_stride is None else value_row_stride, ptr(base), ptr(out),
+                                                ptr(weights_out)))
+    return out
 
 
 def shard_unique_id():

@@ -50,6 +50,14 @@ int32_t slha_b200_debug_force_generic_score(int32_t on) {
     debug_force_generic_score(on != 0);
     return SLHA_OK;
 }
+int32_t slha_b200_last_score_stats(uint64_t* out) {
+    return ffi([&]() -> Status {
+        if (!out) return Status(SLHA_ERR_NULL, "slha_b200_last_score_stats received a NULL pointer");
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        return last_score_stats(c, out);
+    });
+}
 int32_t slha_b200_timing_begin(uint32_t max_calls) {
     return ffi([&]() -> Status {
         Ctx* c;
@@ -271,6 +279,36 @@ int32_t slha_b200_topk_merge(const uint32_t* cand_index, const float* cand_score
                              float* out_score) {
     return slha_b200_topk_merge_strided(cand_index, cand_score, n_lists, (uint64_t)n_queries * k_in, n_queries, k_in,
                                         k_out, out_index, out_score);
+}
+
+int32_t slha_b200_attend_topk(const uint32_t* top_index, const float* top_score, const uint32_t* top_count, size_t n_queries,
+                              uint32_t k, float scale, const void* values, int32_t value_dtype, size_t d_v,
+                              size_t value_row_stride, const uint64_t* value_row_base, float* out, float* weights_out) {
+    return ffi([&]() -> Status {
+        if (n_queries == 0) return Status();
+        if (!top_index || !top_score || !values || !out)
+            return Status(SLHA_ERR_NULL, "slha_b200_attend_topk received a NULL pointer");
+        if (value_dtype != SLHA_B200_F32 && value_dtype != SLHA_B200_BF16)
+            return Status(SLHA_ERR_DIMENSION, "slha_b200_attend_topk: value_dtype must be SLHA_B200_F32 or SLHA_B200_BF16");
+        if (!is_device_ptr(values)) return Status(SLHA_ERR_DEVICE, "slha_b200_attend_topk: values must be device memory");
+        if (value_row_stride < d_v) return Status(SLHA_ERR_DIMENSION, "slha_b200_attend_topk: value_row_stride is smaller than d_v");
+        CallScope cs;
+        if (!cs.ok()) return cs.st;
+        Ctx* c = cs.c;
+        const uint32_t *di, *dc;
+        const float* dsc;
+        const uint64_t* db;
+        SLHA_TRY(stage_in_t(c, top_index, n_queries * k, &di));
+        SLHA_TRY(stage_in_t(c, top_score, n_queries * k, &dsc));
+        SLHA_TRY(stage_in_t(c, top_count, n_queries, &dc));
+        SLHA_TRY(stage_in_t(c, value_row_base, n_queries, &db));
+        std::vector<StagedOut> outs(2);
+        SLHA_TRY(stage_out(c, out, n_queries * d_v * 4, &outs[0]));
+        SLHA_TRY(stage_out(c, weights_out, n_queries * (size_t)k * 4, &outs[1]));
+        SLHA_TRY(launch_attend_topk(c, di, dsc, dc, n_queries, k, scale, values, value_dtype, d_v, value_row_stride, db,
+                                    (float*)outs[0].dev, (float*)outs[1].dev));
+        return finish_outputs(c, outs, sync_by_default(c));
+    });
 }
 
 // ------------------------------------------------------------------ shards

@@ -111,6 +111,8 @@ Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Se
                           const float* d_q_coarse, const uint64_t* d_q_sign, size_t n_queries, uint32_t k,
                           uint32_t* d_out_index, float* d_out_score, uint32_t* d_out_count);
 void debug_force_generic_score(bool on);  // calling thread only
+Status last_score_stats(Ctx* c, uint64_t* out4);
+bool timing_active();  // the calling thread records kernel events (slha_b200_timing_begin)
 Status timing_begin(uint32_t max_calls);
 Status timing_end(Ctx* c, float* score_ms, float* merge_ms, uint32_t capacity, uint32_t* n_out);
 Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* cand_score,
@@ -128,6 +130,11 @@ Status shard_last_times(Ctx* c, Shard* s, float* ms3);
 Status shard_step_device(Ctx* c, Shard* s, const SciRustSlhaTile* tiles, const SlhaB200Segment* h_segs, size_t n_segs,
                          const float* d_qc, const uint64_t* d_qs, size_t nq, uint32_t k, uint32_t* d_out_index,
                          float* d_out_score);
+
+// decode tail over the selected tiles (attend.cu)
+Status launch_attend_topk(Ctx* c, const uint32_t* d_index, const float* d_score, const uint32_t* d_count, size_t nq, uint32_t k,
+                          float scale, const void* d_values, int value_dtype, size_t d_v, size_t row_stride,
+                          const uint64_t* d_row_base, float* d_out, float* d_weights);
 
 Status launch_encode(Ctx* c, const Model* m, const void* d_keys, int key_dtype, size_t n,
                      const uint32_t* d_positions, uint32_t position_base, const uint16_t* d_heads,

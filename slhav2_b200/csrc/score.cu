@@ -288,11 +288,7 @@ struct ScoreArgs {
     // `item_tiles` consecutive tiles of one array against the launch's queries
     uint64_t total_tiles;
     uint32_t item_tiles, nq_launch;
-    // hand-over between the tensor-core kernel and the generic kernel: the former
-    // marks work items it cannot decode, the latter (when `retry` is set) runs
-    // only those
     uint32_t n_items;
-    uint32_t* retry;
     const uint32_t* cta_begin;    // tensor-core kernel: item range of every persistent CTA
     unsigned long long* gpivot;   // tensor-core kernel: per query row, shared selection threshold
     unsigned long long* grange;   // per query row: bucket mapping of the shared score histogram (0 = none yet)
@@ -312,8 +308,12 @@ __global__ void __launch_bounds__(256) score_kernel(ScoreArgs a) {
     const int t = lane >> 3, s = lane & 7;
     WorkItem it;
     if (a.items) {
-        if (a.retry && a.retry[blockIdx.x] == 0) return;
         it = a.items[blockIdx.x];
+        if (a.gflag) {  // launched behind the tensor-core kernel: only work items one of whose rows it handed back
+            uint32_t f = 0;
+            for (uint32_t g = 0; g < it.n_queries; ++g) f |= a.gflag[it.query_begin + g];
+            if (!f) return;
+        }
     } else {
         it.tile_begin = (uint64_t)blockIdx.x * a.item_tiles;
         it.n_tiles = (uint32_t)min((uint64_t)a.item_tiles, a.total_tiles - it.tile_begin);

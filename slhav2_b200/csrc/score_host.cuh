@@ -13,10 +13,12 @@ constexpr size_t MAX_SMEM = 227 * 1024;
 // slha_b200_debug_force_generic_score: the calling thread's score_topk calls skip the
 // tensor-core kernel (a checking aid: both kernels must give the same answers).
 thread_local bool g_force_generic = false;
+struct Plan;
+thread_local const Plan* g_last_stream_plan = nullptr;  // the calling thread's latest tensor-core call (for its counters)
 
-size_t mma_smem_bytes(int nwarps, bool nf4_table) {
+size_t mma_smem_bytes(int nwarps, bool nf4_table) {  // (keep in step with the kernel's layout)
     // nf4 table | stage ring | B fragments | sign words, thresholds, bucket mappings, flag
-    return (size_t)(nf4_table ? NF4_LUT_BYTES : 0) + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE + MMA_BQ_BYTES + 128 + 16 + 32 + 16;
+    return (size_t)(nf4_table ? NF4_LUT_BYTES : 0) + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE + MMA_BQ_BYTES + 128 + 16 + 32 + 32 + 16;
 }
 constexpr int STREAM_THREADS = SLHA_STREAM_THREADS;
 
@@ -108,12 +110,12 @@ struct Plan {
     uint32_t* d_q_list_count = nullptr;
     uint64_t* d_cand_keys = nullptr;
     uint32_t* d_cand_cnt = nullptr;
-    uint32_t* d_retry = nullptr;   // per work item: 1 = the tensor-core kernel handed it back
     uint32_t* d_cta_begin = nullptr;  // tensor-core kernel: items [cta_begin[b], cta_begin[b+1]) belong to CTA b
     unsigned long long* d_gpivot = nullptr;  // per query: streaming top-k state (threshold, mapping, count, flag, histogram)
     uint64_t* d_gbuf = nullptr;              // per query: gcap candidate keys of the tensor-core kernel
     uint32_t gcap = 0;
     size_t gstate_bytes = 0;
+    uint32_t compact_splits = 0, selcap = 0;  // optional compaction pass before the merge (few rows, long buffers)
     uint32_t n_items = 0;
     uint32_t max_parts = 1;  // most candidate lists any query has
     uint32_t list_cap = 0;   // slots per candidate list: k plus the slack the tensor-core kernel's last selection may leave
@@ -126,7 +128,7 @@ struct Plan {
     int mma_threads = STREAM_THREADS;
     uint32_t mma_grid = 0;
     size_t mma_smem = 0;
-    DevBuf b_items, b_qbegin, b_qcount, b_keys, b_cnt, b_retry, b_cta, b_gpivot, b_gbuf, b_vq, b_tmp;
+    DevBuf b_items, b_qbegin, b_qcount, b_keys, b_cnt, b_cta, b_gpivot, b_gbuf, b_gsel, b_vq, b_tmp;
     // Two-level merge for calls with few queries and many candidate lists per query (a pool scored
     // by one GQA group: 148 lists each): groups of `group_parts` lists are merged by a CTA each into
     // `n_groups` intermediate (index, score) lists per query, which a second launch merges.
@@ -302,7 +304,6 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     p->list_cap = (k + std::max<uint32_t>(64, k / 2) + 31) / 32 * 32;
     SLHA_TRY(p->b_keys.ensure((size_t)n_lists * p->list_cap * 8));
     SLHA_TRY(p->b_cnt.ensure((size_t)n_lists * 4));
-    SLHA_TRY(p->b_retry.ensure(all.size() * 4));
     SLHA_TRY(p->b_cta.ensure(cta_begin.size() * 4));
     // Streaming top-k state per query row: threshold, bucket mapping, count, flag, 256 bucket counts; and
     // the row's candidate buffer.  In random order about k (1 + ln(n / k)) tiles pass the rising threshold
@@ -311,11 +312,15 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     // (a warp reserves slots in chunks of 16 per row and work item, so up to 16 slots per warp and item stay unused)
     uint32_t longest = 0;
     for (size_t i = 0; i < n_segs; ++i) longest = std::max(longest, segs[i].n_tiles);
-    const uint64_t all_of_a_row = (uint64_t)longest + 16ull * (uint64_t)(p->mma_threads / 32) * p->max_parts + 64;
+    const uint64_t all_of_a_row = (uint64_t)longest + (uint64_t)MMA_CHUNK * (uint64_t)(p->mma_threads / 32) * p->max_parts + 64;
     // (the first set of every warp that scans a row is appended unfiltered: 16 slots per warp and item, twice over)
-    const uint64_t first_sets = 32ull * (uint64_t)(p->mma_threads / 32) * p->max_parts;
+    const uint64_t first_sets = (uint64_t)(16 + MMA_CHUNK) * (uint64_t)(p->mma_threads / 32) * p->max_parts;
     p->gcap = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(std::max<uint64_t>(16ull * k, 4096), first_sets + 4ull * k), all_of_a_row / 64 * 64);
-    p->gstate_bytes = nq * (8 + 8 + 4 + 4 + 1024);
+    p->gstate_bytes = nq * (1024 + 8 + 8 + 4 + 4 + 4);
+    // few rows with long buffers: several CTAs per row compact the survivors before the merge
+    p->compact_splits = (p->use_mma && nq < 128 && p->gcap >= 8192) ? (uint32_t)std::min<size_t>(32, (296 + nq - 1) / nq) : 0;
+    p->selcap = merge_cap((uint64_t)p->gcap, p->kp2, k);
+    if (p->compact_splits) SLHA_TRY(p->b_gsel.ensure(nq * (size_t)p->selcap * 8));
     SLHA_TRY(p->b_gpivot.ensure(p->gstate_bytes));
     if (p->use_mma) SLHA_TRY(p->b_gbuf.ensure(nq * (size_t)p->gcap * 8));
     p->d_gbuf = (uint64_t*)p->b_gbuf.p;
@@ -324,7 +329,6 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     p->d_q_list_count = (uint32_t*)p->b_qcount.p;
     p->d_cand_keys = (uint64_t*)p->b_keys.p;
     p->d_cand_cnt = (uint32_t*)p->b_cnt.p;
-    p->d_retry = (uint32_t*)p->b_retry.p;
     p->d_cta_begin = (uint32_t*)p->b_cta.p;
     p->d_gpivot = (unsigned long long*)p->b_gpivot.p;
     p->n_items = (uint32_t)all.size();
@@ -433,6 +437,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     if (timed) SLHA_CUDA(cudaEventRecord(tev[0], c->stream));
     const bool mma = p->use_mma && !prefer_generic;
     ScoreArgs am{};
+    if (mma) g_last_stream_plan = p;
     if (mma) {
         SLHA_CUDA(cudaMemsetAsync(p->d_gpivot, 0, p->gstate_bytes, c->stream));
         ScoreArgs& a = am;
@@ -440,7 +445,6 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.state = state;
         a.items = p->d_items;
         a.n_items = p->n_items;
-        a.retry = p->d_retry;
         a.cta_begin = p->d_cta_begin;
         // (histograms first: they are read with 16-byte loads)
         a.ghist = reinterpret_cast<uint32_t*>(p->d_gpivot);
@@ -470,13 +474,10 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
 #undef SLHA_LAUNCH_MMA
         count_launch();
         SLHA_CUDA(cudaGetLastError());
-        stream_mark_retry_kernel<<<(p->n_items + 255) / 256, 256, 0, c->stream>>>(p->d_items, p->n_items, a.gflag, p->d_retry);
-        count_launch();
-        SLHA_CUDA(cudaGetLastError());
     }
     for (const Plan::Class& cl : p->classes) {
         ScoreArgs a{};
-        a.retry = mma ? p->d_retry + cl.first : nullptr;
+        a.gflag = mma ? am.gflag : nullptr;  // after the tensor-core kernel: only the work items of rows it handed back
         a.tiles = reinterpret_cast<const unsigned char*>(tiles);
         a.state = state;
         a.items = p->d_items + cl.first;
@@ -498,9 +499,17 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         configured[c->device & 15] = true;
     }
     if (mma) {
+        uint32_t* gselcnt = am.gflag + nq;
+        const uint32_t cap_s = p->selcap;
+        if (p->compact_splits) {
+            stream_compact_kernel<<<dim3(p->compact_splits, (uint32_t)nq), 256, 0, c->stream>>>(
+                p->d_gbuf, am.gcount, am.gflag, am.gpivot, p->gcap, (uint64_t*)p->b_gsel.p, gselcnt, cap_s, p->compact_splits);
+            count_launch();
+            SLHA_CUDA(cudaGetLastError());
+        }
         StreamLists L{p->d_gbuf, am.gcount, am.gflag, am.gpivot, p->gcap,
+                      p->compact_splits ? (const uint64_t*)p->b_gsel.p : nullptr, gselcnt, cap_s,
                       CompLists{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, p->list_cap}};
-        const uint32_t cap_s = merge_cap((uint64_t)p->gcap, p->kp2, k);
         topk_merge_kernel<StreamLists><<<(uint32_t)nq, merge_threads(cap_s), merge_smem(cap_s, p->kp2), c->stream>>>(
             L, k, p->kp2, cap_s, d_out_index, d_out_score, d_out_count);
     } else if (p->n_groups) {
@@ -531,6 +540,27 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
 }
 
 void debug_force_generic_score(bool on) { g_force_generic = on; }
+
+// Counters of the calling thread's latest score_topk call that used the tensor-core kernel.
+Status last_score_stats(Ctx* c, uint64_t* out4) {
+    out4[0] = out4[1] = out4[2] = out4[3] = 0;
+    const Plan* p = g_last_stream_plan;
+    if (!p || p->device != c->device || !p->use_mma) return Status();
+    const size_t nq = p->nq;
+    std::vector<uint32_t> h(2 * nq);
+    const uint32_t* gcount = reinterpret_cast<const uint32_t*>(p->d_gpivot + 128 * nq + 2 * nq);
+    SLHA_CUDA(cudaMemcpyAsync(h.data(), gcount, 8 * nq, cudaMemcpyDeviceToHost, c->stream));
+    SLHA_CUDA(cudaStreamSynchronize(c->stream));
+    out4[0] = nq;
+    for (size_t q = 0; q < nq; ++q) {
+        out4[1] += h[nq + q] != 0;
+        out4[2] += h[q];
+    }
+    out4[3] = p->gcap;
+    return Status();
+}
+
+bool timing_active() { return g_timing.calls < g_timing.max_calls; }
 
 Status timing_begin(uint32_t max_calls) {
     for (cudaEvent_t e : g_timing.ev) cudaEventDestroy(e);

@@ -39,13 +39,19 @@ struct StreamLists {
     const uint32_t* gflag;               // [nq]
     const unsigned long long* gpivot;    // [nq]
     uint32_t gcap;
+    // optional: the survivors of every row's buffer, compacted by stream_compact_kernel
+    const uint64_t* gsel;                // [nq][selcap] or null
+    const uint32_t* gselcnt;             // [nq]
+    uint32_t selcap;
     CompLists items;
-    __device__ uint32_t len0(uint32_t Q) const { return min(gcount[Q], gcap); }
+    __device__ bool compacted(uint32_t Q) const { return gsel != nullptr && gselcnt[Q] <= selcap; }
+    __device__ uint32_t len0(uint32_t Q) const { return compacted(Q) ? gselcnt[Q] : min(gcount[Q], gcap); }
     __device__ uint32_t size(uint32_t Q) const { return gflag[Q] ? items.size(Q) : len0(Q); }
     __device__ uint32_t lists(uint32_t Q) const { return gflag[Q] ? items.lists(Q) : 1u; }
     __device__ uint32_t list_len(uint32_t Q, uint32_t part) const { return gflag[Q] ? items.list_len(Q, part) : len0(Q); }
     __device__ uint64_t at(uint32_t Q, uint32_t part, uint32_t j) const {
         if (gflag[Q]) return items.at(Q, part, j);
+        if (compacted(Q)) return gsel[(size_t)Q * selcap + j];
         const uint64_t key = gbuf[(size_t)Q * gcap + j];
         return key >= gpivot[Q] ? key : 0ull;
     }
@@ -72,6 +78,43 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
         return i == 0xFFFFFFFFu ? 0ull : make_comp(score[o], i);
     }
 };
+
+// Calls with few query rows (a long context scored by a handful of heads) leave every row tens of
+// thousands of buffered candidates, most of them below the row's final threshold, and one merge CTA
+// per row would read them alone.  Here `splits` CTAs per row each filter a slice of the row's buffer
+// and append the survivors (keys at or above the threshold) to a compact list; a row whose survivors
+// exceed `selcap` keeps a count above it, which sends the merge back to the full buffer.
+__global__ void __launch_bounds__(256) stream_compact_kernel(const uint64_t* gbuf, const uint32_t* gcount, const uint32_t* gflag,
+                                                             const unsigned long long* gpivot, uint32_t gcap, uint64_t* gsel,
+                                                             uint32_t* gselcnt, uint32_t selcap, uint32_t splits) {
+    const uint32_t Q = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
+    if (gflag[Q]) return;
+    const uint32_t len = min(gcount[Q], gcap);
+    const uint32_t per = ((len + splits - 1) / splits + 3) & ~3u;
+    const uint32_t lo = blockIdx.x * per, hi = min(len, lo + per);
+    const uint64_t pv = gpivot[Q];
+    const uint64_t* src = gbuf + (size_t)Q * gcap;
+    uint64_t* dst = gsel + (size_t)Q * selcap;
+    for (uint32_t j0 = lo; j0 < hi; j0 += 4 * blockDim.x) {
+        uint64_t key[4];
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+            const uint32_t j = j0 + u * blockDim.x + tid;
+            key[u] = j < hi ? src[j] : 0ull;
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+            const bool keep = key[u] != 0ull && key[u] >= pv;
+            const unsigned bal = __ballot_sync(0xFFFFFFFFu, keep);
+            if (!bal) continue;
+            uint32_t base = 0;
+            if (lane == 0) base = atomicAdd(gselcnt + Q, (uint32_t)__popc(bal));
+            base = __shfl_sync(0xFFFFFFFFu, base, 0);
+            const uint32_t at = base + (uint32_t)__popc(bal & ((1u << lane) - 1u));
+            if (keep && at < selcap) dst[at] = key[u];
+        }
+    }
+}
 
 // Orders buf[0..m) descending into out[0..m) by bucket placement: NB (1024 or 2048) equal-width score buckets
 // between the smallest and the largest score (highest first), a counting pass, an exclusive scan, a

@@ -34,6 +34,7 @@ constexpr int MMA_HALF = 8 * MMA_ROW;                      // row g -> row g + 8
 #ifndef SLHA_MMA_DEPTH
 #define SLHA_MMA_DEPTH 2
 #endif
+constexpr uint32_t MMA_CHUNK = 16;  // slots a warp reserves at a time in a row's candidate buffer (larger chunks measured no faster)
 #ifndef SLHA_STREAM_THREADS
 #define SLHA_STREAM_THREADS 768  // 24 warps at 80 registers: the streaming kernel hides its latencies with warps
 #endif
@@ -657,7 +658,8 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
     uint32_t* qs_w = reinterpret_cast<uint32_t*>(tail + MMA_BQ_BYTES);   // [4][8]
     uint32_t* pvh = qs_w + 32;                                           // [4] score word of the row's threshold
     float2* rng = reinterpret_cast<float2*>(pvh + 4);                    // [4] (smin, inv), inv 0 = none yet
-    int* bail = reinterpret_cast<int*>(rng + 4);                         // [1]
+    float2* rmap = rng + 4;                                              // [4] (-smin * inv, inv): the same mapping as the hot path uses it
+    int* bail = reinterpret_cast<int*>(rmap + 4);                        // [1]
     const uint32_t smem_s = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t stage_s = smem_s + lut_bytes + (uint32_t)warp * MMA_DEPTH * MMA_SET_STRIDE;
     const uint32_t bqa = smem_s + lut_bytes + (uint32_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE + (uint32_t)lane * 8u;
@@ -691,6 +693,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
             pvh[tid] = (uint32_t)(pv >> 32);
             const unsigned long long pr = have ? *reinterpret_cast<volatile unsigned long long*>(a.grange + it.query_begin + tid) : 0ull;
             rng[tid] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
+            rmap[tid] = make_float2(-rng[tid].x * rng[tid].y, rng[tid].y);
         }
         if (tid == 0) bail[0] = 0;
         if (warp == 1 % nwarps) {
@@ -762,6 +765,8 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         const uint32_t n_full = n / MMA_SET_TILES;
         const bool mine = t < nq;
         const uint32_t Qt = it.query_begin + (mine ? (uint32_t)t : 0u);  // the row whose scores this thread finishes
+        uint64_t* const dst = a.gbuf + (size_t)Qt * a.gcap;                // the row's candidate buffer
+        uint32_t* const hrow = a.ghist + (size_t)Qt * 256;                 // and its histogram
         // sets are dealt to the warps round by round: warp w takes set j * nwarps + w of round j
         const unsigned char* tbase = a.tiles + it.tile_begin * TILE_BYTES + lane * 16;
         uint32_t s_next = (uint32_t)warp, slot_next = 0;
@@ -906,7 +911,10 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
                             pr = old ? old : mine_r;
                         }
                     }
-                    if (pr) rng[t] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
+                    if (pr) {
+                        rng[t] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
+                        rmap[t] = make_float2(-rng[t].x * rng[t].y, rng[t].y);
+                    }
                 }
                 __syncwarp();
             }
@@ -921,41 +929,43 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
                 // zeroed (an absent key) before the next one is taken and at the end of the work item.
                 const unsigned b0 = __ballot_sync(0xFFFFFFFFu, p0) & t_mask, b1 = __ballot_sync(0xFFFFFFFFu, p1) & t_mask;
                 const uint32_t n0 = (uint32_t)__popc(b0), nn = n0 + (uint32_t)__popc(b1);
-                uint64_t* dst = a.gbuf + (size_t)Qt * a.gcap;
-                if (__any_sync(0xFFFFFFFFu, cur + nn > end)) {
-                    if (cur + nn > end) {  // (uniform over the eight lanes of a query)
-                        if (cur + (uint32_t)g < end && cur + (uint32_t)g < a.gcap) dst[cur + (uint32_t)g] = 0ull;
-                        if (cur + 8u + (uint32_t)g < end && cur + 8u + (uint32_t)g < a.gcap) dst[cur + 8u + (uint32_t)g] = 0ull;
-                        uint32_t base = 0;
-                        if (g == 0) base = atomicAdd(a.gcount + Qt, 16u);
-                        cur = __shfl_sync(t_mask, base, t);  // lane t is (g = 0, t)
-                        end = cur + 16u;
+                if (cur + nn > end) {  // (the same in the eight lanes of a query, which are the lanes of t_mask)
+                    for (uint32_t z = cur + (uint32_t)g; z < end; z += 8u) dst[z] = 0ull;
+                    uint32_t base = 0;
+                    if (g == 0) {
+                        base = atomicAdd(a.gcount + Qt, MMA_CHUNK);
+                        if (base + MMA_CHUNK > a.gcap) {
+                            // the row's buffer is full: the generic kernel scores the row; this warp's further
+                            // candidates of the row land in the buffer's last chunk, which nobody reads then
+                            a.gflag[Qt] = 1u;
+                            base = a.gcap - MMA_CHUNK;
+                        }
                     }
+                    cur = __shfl_sync(t_mask, base, t);  // lane t is (g = 0, t)
+                    end = cur + MMA_CHUNK;
                 }
-                const float2 r = rng[t];
-                bool over = false;
+                // bucket of the row's histogram: (int)(score * inv - smin * inv), clamped; scores below the
+                // mapping (and all scores while the row has no mapping) count in bucket 0, which never decides
+                const float2 r = rmap[t];
                 if (p0) {
-                    const uint32_t at = cur + (uint32_t)__popc(b0 & lt_mask);
-                    if (at < a.gcap) dst[at] = ((uint64_t)k0 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t0));
-                    else over = true;
-                    if (r.y > 0.0f && sc0 >= r.x) atomicAdd(a.ghist + (size_t)Qt * 256 + sel_bucket_f(sc0, r.x, r.y), 1u);
+                    dst[cur + (uint32_t)__popc(b0 & lt_mask)] = ((uint64_t)k0 << 32) | (uint64_t)(~(it.index_base + t0));
+                    atomicAdd(hrow + min(max(__float2int_rz(fmaf(sc0, r.y, r.x)), 0), 255), 1u);
                 }
                 if (p1) {
-                    const uint32_t at = cur + n0 + (uint32_t)__popc(b1 & lt_mask);
-                    if (at < a.gcap) dst[at] = ((uint64_t)k1 << 32) | (uint64_t)(0xFFFFFFFFu - (it.index_base + t1));
-                    else over = true;
-                    if (r.y > 0.0f && sc1 >= r.x) atomicAdd(a.ghist + (size_t)Qt * 256 + sel_bucket_f(sc1, r.x, r.y), 1u);
+                    dst[cur + n0 + (uint32_t)__popc(b1 & lt_mask)] = ((uint64_t)k1 << 32) | (uint64_t)(~(it.index_base + t1));
+                    atomicAdd(hrow + min(max(__float2int_rz(fmaf(sc1, r.y, r.x)), 0), 255), 1u);
                 }
                 cur += nn;
-                if (over) a.gflag[Qt] = 1u;  // the row's buffer is full: the generic kernel scores the row
             }
             }  // need
             __syncwarp();
-            // In turn, a warp raises the threshold of query (warp & 3): after its first few sets (every
-            // warp of the grid has appended its first sets unfiltered, so the row's histogram already
-            // holds far more than k candidates), then every 64 sets, the warps of a query staggered.
+            // In turn, a warp raises the threshold of query (warp & 3): after its 3rd and 7th set (the first
+            // thresholds come from the barrier after the first round), then every 16 sets, the warps of a
+            // query staggered.  A stale threshold costs appends (each one a store, a
+            // histogram count and, downstream, merge work), a refresh costs one 1 KB read of the row's
+            // histogram by one warp.
             ++polls;
-            if ((polls & 63u) == (uint32_t)((warp >> 2) & 3) * 16u + 15u || (polls <= 12u && polls >= 2u && ((polls & (polls - 1u)) == 0u || polls == 3u || polls == 6u || polls == 12u))) {
+            if ((polls & 15u) == (uint32_t)((warp >> 2) & 3) * 4u + 3u || polls == 3u || polls == 7u) {
                 const int q = warp & 3;
                 if (q < nq) stream_refresh_threshold(a, it.query_begin + (uint32_t)q, rng[q], pvh + q, lane);
                 __syncwarp();
@@ -963,23 +973,12 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         }
         cp_async_wait<0>();
         if (mine) {  // the unused rest of the warp's last chunk holds absent keys
-            uint64_t* dst = a.gbuf + (size_t)Qt * a.gcap;
-            if (cur + (uint32_t)g < end && cur + (uint32_t)g < a.gcap) dst[cur + (uint32_t)g] = 0ull;
-            if (cur + 8u + (uint32_t)g < end && cur + 8u + (uint32_t)g < a.gcap) dst[cur + 8u + (uint32_t)g] = 0ull;
+            for (uint32_t z = cur + (uint32_t)g; z < end; z += 8u) dst[z] = 0ull;
         }
         __syncthreads();
         // rows this CTA could not score on the tensor cores go to the generic kernel as a whole
         if (bail[0] && tid < nq) a.gflag[it.query_begin + tid] = 1u;
     }
-}
-
-// After score_stream_kernel: a work item is handed to the generic kernel when one of its rows is flagged.
-__global__ void stream_mark_retry_kernel(const WorkItem* items, uint32_t n_items, const uint32_t* gflag, uint32_t* retry) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_items) return;
-    uint32_t f = 0;
-    for (uint32_t g = 0; g < items[i].n_queries; ++g) f |= gflag[items[i].query_begin + g];
-    retry[i] = f ? 1u : 0u;
 }
 
 }  // namespace

@@ -16,6 +16,7 @@
 #include <cstring>
 #include <memory>
 #include <mutex>
+#include <vector>
 
 #include "runtime.cuh"
 
@@ -101,6 +102,14 @@ struct Shard {
     Buf cand, gathered;  // [2][nq][k] and [world][2][nq][k] int32
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};  // step begin, after local top-k, after all-gather, after merge
     bool timed = false, have_times = false;
+    // A decode loop repeats the same step (same buffers, same segment table) thousands of times, and with a
+    // shard of a few hundred MB the host needs longer to enqueue the step's memset, kernels and all-gather
+    // than the GPU needs to run them.  The second identical call is therefore captured into a CUDA graph,
+    // and every further one is a single graph launch.
+    std::vector<unsigned char> seen_key, graph_key;
+    cudaGraphExec_t graph_exec = nullptr;
+    int graph_launches = 0;     // kernels of one step (for the launch counter)
+    bool graphs_off = false;    // capture failed once on this handle (e.g. a stream that cannot capture)
 };
 
 Status shard_unique_id(void* id128) {
@@ -133,6 +142,7 @@ Status shard_init(Ctx* c, const void* id128, int rank, int world, Shard** out) {
 Status shard_destroy(Shard* s) {
     if (!s) return Status();
     cudaSetDevice(s->device);
+    if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
     for (cudaEvent_t e : s->ev)
         if (e) cudaEventDestroy(e);
     if (s->comm) g_nccl.comm_destroy(s->comm);
@@ -162,12 +172,11 @@ Status shard_last_times(Ctx* c, Shard* s, float* ms3) {
     return Status();
 }
 
-// The device part of one step.  d_q_* are device pointers; d_out_* are device pointers of
-// [nq][k] results (merged over all ranks).  Everything is enqueued on c->stream.
-Status shard_step_device(Ctx* c, Shard* s, const SciRustSlhaTile* tiles, const SlhaB200Segment* h_segs, size_t n_segs,
-                         const float* d_qc, const uint64_t* d_qs, size_t nq, uint32_t k, uint32_t* d_out_index,
-                         float* d_out_score) {
-    if (s->device != c->device) return Status(SLHA_ERR_DEVICE, "shard handle lives on another device than the calling thread's");
+namespace {
+// The device part of one step, enqueued on c->stream.
+Status shard_enqueue(Ctx* c, Shard* s, const SciRustSlhaTile* tiles, const SlhaB200Segment* h_segs, size_t n_segs,
+                     const float* d_qc, const uint64_t* d_qs, size_t nq, uint32_t k, uint32_t* d_out_index,
+                     float* d_out_score) {
     const size_t block = 2 * nq * (size_t)k;  // int32 elements of one rank's candidate block
     if (s->timed) SLHA_CUDA(cudaEventRecord(s->ev[0], c->stream));
     if (s->world == 1) {
@@ -178,13 +187,12 @@ Status shard_step_device(Ctx* c, Shard* s, const SciRustSlhaTile* tiles, const S
         }
         return Status();
     }
-    SLHA_TRY(s->cand.ensure(block * 4));
-    SLHA_TRY(s->gathered.ensure(block * 4 * (size_t)s->world));
     uint32_t* ci = (uint32_t*)s->cand.p;
     float* csc = reinterpret_cast<float*>(ci + nq * (size_t)k);
     SLHA_TRY(score_topk_device(c, tiles, nullptr, h_segs, n_segs, d_qc, d_qs, nq, k, ci, csc, nullptr));
     if (s->timed) SLHA_CUDA(cudaEventRecord(s->ev[1], c->stream));
     SLHA_TRY(nccl_status(&g_nccl, g_nccl.all_gather(s->cand.p, s->gathered.p, block, NCCL_INT32, s->comm, c->stream), "ncclAllGather"));
+    count_launch();
     if (s->timed) SLHA_CUDA(cudaEventRecord(s->ev[2], c->stream));
     const uint32_t* gi = (const uint32_t*)s->gathered.p;
     const float* gsc = reinterpret_cast<const float*>(gi + nq * (size_t)k);
@@ -194,6 +202,65 @@ Status shard_step_device(Ctx* c, Shard* s, const SciRustSlhaTile* tiles, const S
         s->have_times = true;
     }
     return Status();
+}
+}  // namespace
+
+// One step.  d_q_* are device pointers; d_out_* are device pointers of [nq][k] results (merged over
+// all ranks).  Everything is enqueued on c->stream.
+Status shard_step_device(Ctx* c, Shard* s, const SciRustSlhaTile* tiles, const SlhaB200Segment* h_segs, size_t n_segs,
+                         const float* d_qc, const uint64_t* d_qs, size_t nq, uint32_t k, uint32_t* d_out_index,
+                         float* d_out_score) {
+    if (s->device != c->device) return Status(SLHA_ERR_DEVICE, "shard handle lives on another device than the calling thread's");
+    if (s->world > 1) {
+        const size_t block = 2 * nq * (size_t)k;
+        const void *p0 = s->cand.p, *p1 = s->gathered.p;
+        SLHA_TRY(s->cand.ensure(block * 4));
+        SLHA_TRY(s->gathered.ensure(block * 4 * (size_t)s->world));
+        if (p0 != s->cand.p || p1 != s->gathered.p) s->graph_key.clear();  // (a captured step names the old buffers)
+    }
+    if (s->timed || s->graphs_off || timing_active()) return shard_enqueue(c, s, tiles, h_segs, n_segs, d_qc, d_qs, nq, k, d_out_index, d_out_score);
+    // the call's identity: every pointer and size the enqueued work depends on
+    std::vector<unsigned char> key(sizeof(SlhaB200Segment) * n_segs + 8 * 8);
+    const uint64_t head[8] = {(uint64_t)(uintptr_t)tiles, (uint64_t)(uintptr_t)d_qc, (uint64_t)(uintptr_t)d_qs,
+                              (uint64_t)(uintptr_t)d_out_index, (uint64_t)(uintptr_t)d_out_score, (uint64_t)nq, (uint64_t)k,
+                              (uint64_t)(uintptr_t)c->stream};
+    std::memcpy(key.data(), head, sizeof(head));
+    std::memcpy(key.data() + sizeof(head), h_segs, sizeof(SlhaB200Segment) * n_segs);
+    if (s->graph_exec && key == s->graph_key) {
+        SLHA_CUDA(cudaGraphLaunch(s->graph_exec, c->stream));
+        count_launch(s->graph_launches);
+        return Status();
+    }
+    if (key != s->seen_key) {  // first call of this shape: plain (it also sizes the plan's buffers, which a capture may not)
+        s->seen_key = key;
+        return shard_enqueue(c, s, tiles, h_segs, n_segs, d_qc, d_qs, nq, k, d_out_index, d_out_score);
+    }
+    // second identical call: capture it
+    if (cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeRelaxed) != cudaSuccess) {
+        cudaGetLastError();
+        s->graphs_off = true;
+        return shard_enqueue(c, s, tiles, h_segs, n_segs, d_qc, d_qs, nq, k, d_out_index, d_out_score);
+    }
+    const uint64_t before = launch_count();
+    Status st = shard_enqueue(c, s, tiles, h_segs, n_segs, d_qc, d_qs, nq, k, d_out_index, d_out_score);
+    const int launches = (int)(launch_count() - before);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+    cudaGraphExec_t exec = nullptr;
+    if (st.ok() && e == cudaSuccess && graph && cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) {
+        if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
+        s->graph_exec = exec;
+        s->graph_key = key;
+        s->graph_launches = launches;
+        cudaGraphDestroy(graph);
+        SLHA_CUDA(cudaGraphLaunch(s->graph_exec, c->stream));
+        return Status();
+    }
+    // the capture did not work out (nothing of it ran): enqueue the step the plain way from now on
+    cudaGetLastError();
+    if (graph) cudaGraphDestroy(graph);
+    s->graphs_off = true;
+    return shard_enqueue(c, s, tiles, h_segs, n_segs, d_qc, d_qs, nq, k, d_out_index, d_out_score);
 }
 
 }  // namespace slha

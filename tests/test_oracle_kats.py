@@ -222,3 +222,27 @@ def test_topk_order_ties_to_lower_index():
     idx, val = ora.topk(s, 6)
     assert list(idx) == [1, 2, 5, 0, 4, 3]  # +0.0 orders above -0.0 under total_cmp
     assert list(val[:4]) == [3.0, 3.0, 2.0, 1.0]
+
+
+def test_softmax_into_known_answers_of_the_reference():
+    # scirust/src/metrics.rs:331-337 (doc test), :444-449, :483-489, :516-538
+    inf, nan = np.inf, np.nan
+    w = ora.softmax_into([0.0, 0.0, 0.0], 1.0)
+    assert abs(w.sum() - 1.0) < 1e-6 and abs(w[0] - 1.0 / 3.0) < 1e-6
+    assert len(ora.softmax_into([], 1.0)) == 0
+    assert np.array_equal(ora.softmax_into([-inf] * 4, 1.0), np.zeros(4, np.float32))
+    assert np.array_equal(ora.softmax_into([0.0, nan], 1.0), [0.0, 0.0])
+    assert np.array_equal(ora.softmax_into([0.0, 1.0], inf), [0.0, 0.0])
+    assert np.array_equal(ora.softmax_into([1.0, inf, inf, -inf], 1.0), [0.0, 0.5, 0.5, 0.0])
+    o = ora.softmax_into([0.0, -inf, 1.0, -inf], 1.0)
+    assert o[0] > 0 and o[1] == 0 and o[2] > o[0] and o[3] == 0 and abs(o.sum() - 1.0) < 1e-6
+    assert np.all(np.abs(ora.softmax_into([1.0, 2.0, 3.0, 4.0], 0.0) - 0.25) < 1e-6)
+
+
+def test_attend_topk_is_softmax_then_sequential_weighted_sum():
+    # scirust/examples/benchmark_decode.rs:28-38, :82-95 on a hand-checkable case
+    v = np.array([[1.0, 0.0], [0.0, 2.0], [4.0, 4.0]], np.float32)
+    idx = np.array([[2, 0, 0xFFFFFFFF]], np.uint32)
+    sc = np.array([[0.0, 0.0, 5.0]], np.float32)
+    out, w = ora.attend_topk(idx, sc, 1.0, v)
+    assert np.allclose(w, [[0.5, 0.5, 0.0]]) and np.allclose(out, [[2.5, 2.0]])
