@@ -73,12 +73,30 @@ extern "C" {
 #define SLHA_FLAG_TQ3_NOCORR (1u << 4)
 #define SLHA_FLAG_MIX3 (1u << 5)
 
+/* Tile alignment, slha.h:48-57: a host built against a reference library whose
+ * slha_tile_align() is 128 defines SLHA_CACHE_LINE_128=1; this library reports 64
+ * (slha_tile_align()) and accepts tiles at any address (slha.h:150). */
+#if defined(SLHA_CACHE_LINE_128) && SLHA_CACHE_LINE_128
+#define SLHA_TILE_ALIGN 128u
+#else
 #define SLHA_TILE_ALIGN 64u
+#endif
+
+/* compile-time checks in C11, C++11 and MSVC (the role of slha.h:66-79) */
+#if defined(__cplusplus)
+#define SLHA_STATIC_ASSERT(cond, msg) static_assert((cond), msg)
+#elif defined(__STDC_VERSION__) && __STDC_VERSION__ >= 201112L
+#define SLHA_STATIC_ASSERT(cond, msg) _Static_assert((cond), msg)
+#else
+#define SLHA_STATIC_ASSERT(cond, msg) typedef char slha_static_assertion_failed[(cond) ? 1 : -1]
+#endif
 
 /* The 128-byte tile, slha.h:87-110.  Little-endian, no padding. */
 typedef struct
 #if defined(__GNUC__) || defined(__clang__)
     __attribute__((aligned(SLHA_TILE_ALIGN)))
+#elif defined(_MSC_VER)
+    __declspec(align(64))
 #endif
 {
     uint8_t latent_kv[SLHA_LATENT_BYTES];           /*   0 */
@@ -92,6 +110,19 @@ typedef struct
     uint16_t flags;                                 /* 118 */
     uint8_t group_scales[SLHA_N_GROUPS];            /* 120 */
 } SciRustSlhaTile;
+
+/* the layout every exchange of tiles relies on (the checks of slha.h:100-117) */
+SLHA_STATIC_ASSERT(sizeof(SciRustSlhaTile) == 128u, "a tile is 128 bytes");
+SLHA_STATIC_ASSERT(offsetof(SciRustSlhaTile, latent_kv) == 0u, "latent_kv at byte 0");
+SLHA_STATIC_ASSERT(offsetof(SciRustSlhaTile, residual_bitmap) == 64u, "residual_bitmap at byte 64");
+SLHA_STATIC_ASSERT(offsetof(SciRustSlhaTile, scale) == 96u, "scale at byte 96");
+SLHA_STATIC_ASSERT(offsetof(SciRustSlhaTile, dynamic_lambda) == 100u, "dynamic_lambda at byte 100");
+SLHA_STATIC_ASSERT(offsetof(SciRustSlhaTile, residual_sigma) == 104u, "residual_sigma at byte 104");
+SLHA_STATIC_ASSERT(offsetof(SciRustSlhaTile, token_id) == 108u, "token_id at byte 108");
+SLHA_STATIC_ASSERT(offsetof(SciRustSlhaTile, position) == 112u, "position at byte 112");
+SLHA_STATIC_ASSERT(offsetof(SciRustSlhaTile, head_id) == 116u, "head_id at byte 116");
+SLHA_STATIC_ASSERT(offsetof(SciRustSlhaTile, flags) == 118u, "flags at byte 118");
+SLHA_STATIC_ASSERT(offsetof(SciRustSlhaTile, group_scales) == 120u, "group_scales at byte 120");
 
 typedef struct SlhaContext SlhaContext; /* slha.h:119 */
 typedef struct SlhaModel SlhaModel;     /* slha.h:120 */

@@ -75,3 +75,22 @@ def test_product_never_imports_the_oracle():
         for f in files:
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 assert "oracle" not in open(os.path.join(dirpath, f)).read().lower(), f
+
+
+def test_rust_ffi_crate_declares_every_header_function_with_the_same_arity():
+    """rust/slha-b200-sys cannot be compiled where this runs (no Rust toolchain), so its extern
+    block is held to the header textually: the same function names, the same number of arguments."""
+    header = open(os.path.join(ROOT, "include", "slha_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    rust = open(os.path.join(ROOT, "rust", "slha-b200-sys", "src", "lib.rs")).read()
+    rust = re.sub(r"//[^\n]*", "", rust)
+
+    def arity(args):
+        args = args.strip()
+        return 0 if args in ("", "void") else args.count(",") + 1
+
+    c_decl = {m.group(1): arity(m.group(2)) for m in re.finditer(r"\b(slha_[a-z0-9_]+)\s*\(([^()]*)\)\s*;", header)}
+    r_decl = {m.group(1): arity(m.group(2)) for m in re.finditer(r"pub fn (slha_[a-z0-9_]+)\s*\(([^()]*)\)", rust)}
+    assert sorted(c_decl) == declared_functions()
+    assert sorted(r_decl) == sorted(c_decl)
+    assert {n: a for n, a in r_decl.items() if c_decl[n] != a} == {}
