@@ -103,6 +103,8 @@ def _load():
         "ora_cache_enforce_budget": (C.c_int, [vp]),
         "ora_cache_score_all": (sz, [vp, vp, vp, vp, vp]),
         "ora_cache_observe_scores": (None, [vp, vp, vp, sz, C.c_float]),
+        "ora_cache_journal_len": (sz, [vp]),
+        "ora_cache_journal_get": (None, [vp, sz, vp, vp, vp]),
         "ora_cache_nocorr_count": (sz, [vp]),
         "ora_cache_reclaimed_correction_bytes": (sz, [vp]),
         "ora_simd_level": (C.c_int, []),
@@ -406,6 +408,16 @@ class Cache:
         v = _f32(scores)
         lib.ora_cache_observe_scores(self.h, _p(s), _p(v), len(s), temperature)
 
+    def journal(self):
+        """(seq, slot, tile) of every eviction so far, in order: the records an attached EventLog
+        receives (scirust/src/ccos.rs:411-420)."""
+        out = []
+        for i in range(lib.ora_cache_journal_len(self.h)):
+            seq, slot, tile = C.c_uint64(), C.c_uint32(), np.zeros(1, TILE_DTYPE)
+            lib.ora_cache_journal_get(self.h, i, C.byref(seq), C.byref(slot), _p(tile))
+            out.append((seq.value, slot.value, tile))
+        return out
+
     def nocorr_count(self):
         return lib.ora_cache_nocorr_count(self.h)
 
@@ -521,3 +533,52 @@ def attend_topk(top_index, top_score, scale, values, top_count=None, row_base=No
             acc = (acc + np.float32(wi) * v[(base + int(ti[q, i])) % (1 << 64)]).astype(np.float32)
         out[q] = acc
     return out, weights
+
+
+# ---- EventLog (scirust/src/eventlog.rs:9-24): 16-byte header + 144-byte records, little-endian -----------------
+EVENTLOG_MAGIC, EVENTLOG_VERSION = 0x534C4C47, 2
+
+
+def eventlog_checksum(seq, slot, tile_bytes):
+    """record_checksum (eventlog.rs:146-169): FNV-1a over seq (8 LE bytes), slot (4 LE bytes), the 128 tile bytes."""
+    h = 0x811C9DC5
+    for b in int(seq).to_bytes(8, "little") + int(slot).to_bytes(4, "little") + bytes(tile_bytes):
+        h = ((h ^ b) * 0x01000193) & 0xFFFFFFFF
+    return h
+
+
+def eventlog_bytes(records, version=EVENTLOG_VERSION):
+    """The byte-exact file an EventLog holds after `records` ((seq, slot, tile) in order) were appended."""
+    out = bytearray()
+    out += EVENTLOG_MAGIC.to_bytes(4, "little") + int(version).to_bytes(4, "little") + (128).to_bytes(4, "little") + (0).to_bytes(4, "little")
+    for seq, slot, tile in records:
+        tb = np.ascontiguousarray(tile).tobytes()
+        assert len(tb) == 128
+        chk = eventlog_checksum(seq, slot, tb) if version >= 2 else 0
+        out += int(seq).to_bytes(8, "little") + int(slot).to_bytes(4, "little") + chk.to_bytes(4, "little") + tb
+    return bytes(out)
+
+
+def eventlog_parse(data):
+    """Strict reader (EventLog::open, eventlog.rs:236-300): header, whole records, version-2 checksums."""
+    if len(data) < 16:
+        raise ValueError("EventLog: file shorter than header")
+    magic, version, tile_size = (int.from_bytes(data[o:o + 4], "little") for o in (0, 4, 8))
+    if magic != EVENTLOG_MAGIC:
+        raise ValueError("EventLog: bad magic")
+    if version not in (1, 2):
+        raise ValueError("EventLog: unsupported version")
+    if tile_size != 128:
+        raise ValueError("EventLog: tile-size mismatch")
+    if (len(data) - 16) % 144:
+        raise ValueError("EventLog: truncated record")
+    recs = []
+    for o in range(16, len(data), 144):
+        seq = int.from_bytes(data[o:o + 8], "little")
+        slot = int.from_bytes(data[o + 8:o + 12], "little")
+        chk = int.from_bytes(data[o + 12:o + 16], "little")
+        tb = data[o + 16:o + 144]
+        if version >= 2 and chk != eventlog_checksum(seq, slot, tb):
+            raise ValueError("EventLog: checksum mismatch")
+        recs.append((seq, slot, np.frombuffer(tb, TILE_DTYPE).copy()))
+    return version, recs

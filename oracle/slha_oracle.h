@@ -156,6 +156,8 @@ size_t ora_cache_score_all(const ora_cache* c, const float* q_coarse, const uint
                            uint32_t* slots, float* scores);
 void ora_cache_observe_scores(ora_cache* c, const uint32_t* slots, const float* scores,
                               size_t n, float temperature);
+size_t ora_cache_journal_len(const ora_cache* c);
+void ora_cache_journal_get(const ora_cache* c, size_t i, uint64_t* seq, uint32_t* slot, ora_tile* tile);
 size_t ora_cache_nocorr_count(const ora_cache* c);
 size_t ora_cache_reclaimed_correction_bytes(const ora_cache* c);
 

@@ -50,6 +50,11 @@ struct ora_cache {
     uint32_t sink_window;
     uint32_t recent_window; /* extension, 0 = reference behaviour */
     uint64_t next_seq;
+    /* what an attached EventLog would receive (ccos.rs:411-420): one (seq, slot, tile) per eviction, in order */
+    uint64_t* j_seq;
+    uint32_t* j_slot;
+    ora_tile* j_tile;
+    size_t j_len, j_cap;
 };
 
 ora_cache* ora_cache_new(size_t budget, int page_policy, int evict_policy, uint32_t sink_window,
@@ -65,6 +70,7 @@ ora_cache* ora_cache_new(size_t budget, int page_policy, int evict_policy, uint3
 void ora_cache_free(ora_cache* c) {
     if (!c) return;
     free(c->tiles); free(c->state); free(c->seq); free(c->importance); free(c->free_list);
+    free(c->j_seq); free(c->j_slot); free(c->j_tile);
     free(c);
 }
 
@@ -142,9 +148,19 @@ int ora_cache_drop_correction(ora_cache* c, size_t s) {
     return 1;
 }
 
-/* ccos.rs:404-438 without an event log (best-effort durability) */
+/* ccos.rs:404-438 with a log that never fails: the record an EventLog would get is journalled */
 int ora_cache_evict(ora_cache* c, size_t s) {
     if (s >= c->len || c->state[s] == ORA_COLD) return 0;
+    if (c->j_len == c->j_cap) {
+        c->j_cap = c->j_cap ? c->j_cap * 2 : 64;
+        c->j_seq = (uint64_t*)realloc(c->j_seq, c->j_cap * sizeof(uint64_t));
+        c->j_slot = (uint32_t*)realloc(c->j_slot, c->j_cap * sizeof(uint32_t));
+        c->j_tile = (ora_tile*)realloc(c->j_tile, c->j_cap * sizeof(ora_tile));
+    }
+    c->j_seq[c->j_len] = c->seq[s];
+    c->j_slot[c->j_len] = (uint32_t)s;
+    c->j_tile[c->j_len] = c->tiles[s];
+    c->j_len++;
     c->live -= slot_live_bytes(c, s);
     c->state[s] = ORA_COLD;
     if (c->free_len == c->free_cap) {
@@ -280,6 +296,13 @@ void ora_cache_observe_scores(ora_cache* c, const uint32_t* slots, const float* 
     }
     free(ls);
     free(sc);
+}
+
+size_t ora_cache_journal_len(const ora_cache* c) { return c->j_len; }
+void ora_cache_journal_get(const ora_cache* c, size_t i, uint64_t* seq, uint32_t* slot, ora_tile* tile) {
+    *seq = c->j_seq[i];
+    *slot = c->j_slot[i];
+    *tile = c->j_tile[i];
 }
 
 size_t ora_cache_nocorr_count(const ora_cache* c) {

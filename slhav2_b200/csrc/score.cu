@@ -446,6 +446,7 @@ __global__ void __launch_bounds__(256) score_kernel(ScoreArgs a) {
 }  // namespace slha
 
 #include "score_mma.cuh"
+#include "score_wide.cuh"
 #include "score_merge.cuh"
 #include "score_host.cuh"
 

@@ -116,6 +116,11 @@ struct Plan {
     uint32_t gcap = 0;
     size_t gstate_bytes = 0;
     uint32_t compact_splits = 0, selcap = 0;  // optional compaction pass before the merge (few rows, long buffers)
+    // wide scoring (16 or more queries per segment, INT4 / TQ3 launches): work items of up to 64 query rows for score_wide_kernel
+    bool wide = false, allow_wide_in = false;
+    WorkItem* d_wide_items = nullptr;
+    uint32_t* d_wide_cta = nullptr;
+    uint32_t wide_grid = 0, n_wide_items = 0;
     uint32_t n_items = 0;
     uint32_t max_parts = 1;  // most candidate lists any query has
     uint32_t list_cap = 0;   // slots per candidate list: k plus the slack the tensor-core kernel's last selection may leave
@@ -128,7 +133,7 @@ struct Plan {
     int mma_threads = STREAM_THREADS;
     uint32_t mma_grid = 0;
     size_t mma_smem = 0;
-    DevBuf b_items, b_qbegin, b_qcount, b_keys, b_cnt, b_cta, b_gpivot, b_gbuf, b_gsel, b_vq, b_tmp;
+    DevBuf b_items, b_qbegin, b_qcount, b_keys, b_cnt, b_cta, b_gpivot, b_gbuf, b_gsel, b_vq, b_tmp, b_wide_items, b_wide_cta;
     // Two-level merge for calls with few queries and many candidate lists per query (a pool scored
     // by one GQA group: 148 lists each): groups of `group_parts` lists are merged by a CTA each into
     // `n_groups` intermediate (index, score) lists per query, which a second launch merges.
@@ -140,8 +145,10 @@ struct Plan {
     uint64_t last_use = 0;
 };
 
+size_t wide_smem_bytes() { return 3 * WIDE_A_BYTES + 2 * WIDE_RAW_BYTES + 2048 + 256 + 256 + 512 + 512 + 64 + 1024; }
+
 Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* segs, size_t n_segs, size_t nq,
-                  uint32_t k, int codec_hint, Plan** out) {
+                  uint32_t k, int codec_hint, bool allow_wide, Plan** out) {
     std::vector<unsigned char> key(sizeof(SlhaB200Segment) * n_segs + 16);
     std::memcpy(key.data(), segs, sizeof(SlhaB200Segment) * n_segs);
     uint64_t nq64 = nq;
@@ -153,7 +160,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     static thread_local uint64_t tick = 0;
     ++tick;
     for (auto& e : cache)
-        if (e->device == c->device && e->codec_hint_in == codec_hint && e->force_generic_in == g_force_generic && e->key == key) {
+        if (e->device == c->device && e->codec_hint_in == codec_hint && e->force_generic_in == g_force_generic && e->allow_wide_in == allow_wide && e->key == key) {
             e->last_use = tick;
             *out = e.get();
             return Status();
@@ -176,6 +183,8 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     p->last_use = tick;
     p->codec_hint_in = codec_hint;
     p->force_generic_in = g_force_generic;
+    p->allow_wide_in = allow_wide;
+    p->wide = false;
     p->k = k;
     p->n_lists = 0;
     p->nq = (uint32_t)nq;
@@ -305,6 +314,58 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     SLHA_TRY(p->b_keys.ensure((size_t)n_lists * p->list_cap * 8));
     SLHA_TRY(p->b_cnt.ensure((size_t)n_lists * 4));
     SLHA_TRY(p->b_cta.ensure(cta_begin.size() * 4));
+    // Wide scoring: every segment brings 16 or more queries and the launch holds INT4 / MX-INT4 or TQ3 tiles.  Work items
+    // of up to 64 query rows; the (segment, row group) streams are cut into one share per CTA, in whole 128-tile blocks.
+    uint32_t wide_parts = 1;
+    {
+        bool all_wide = p->use_mma && allow_wide && n_segs > 0 && !p->mixed && (p->tq3 || !p->nf4_table);
+        uint64_t wtotal = 0;
+        for (size_t i = 0; i < n_segs && all_wide; ++i) {
+            all_wide = segs[i].n_queries >= 16 || segs[i].n_tiles == 0;
+            wtotal += (uint64_t)segs[i].n_tiles * ((segs[i].n_queries + WIDE_NQ - 1) / WIDE_NQ);
+        }
+        if (all_wide && wtotal > 0 && wide_smem_bytes() <= MAX_SMEM) {
+            uint64_t wshare = (wtotal + sms - 1) / sms;
+            wshare = std::max<uint64_t>(WIDE_M, (wshare + WIDE_M - 1) / WIDE_M * WIDE_M);
+            std::vector<WorkItem> wi;
+            std::vector<uint32_t> wcta(1, 0);
+            uint64_t wfilled = 0;
+            for (size_t i = 0; i < n_segs; ++i) {
+                const SlhaB200Segment& s = segs[i];
+                for (uint32_t q0 = 0; q0 < s.n_queries; q0 += WIDE_NQ) {
+                    uint32_t parts = 0;
+                    for (uint32_t pos = 0; pos < s.n_tiles;) {
+                        const uint32_t take = (uint32_t)std::min<uint64_t>(s.n_tiles - pos, wshare - wfilled);
+                        WorkItem w{};
+                        w.tile_begin = s.tile_begin + pos;
+                        w.n_tiles = take;
+                        w.index_base = s.index_base + pos;
+                        w.query_begin = s.query_begin + q0;
+                        w.n_queries = std::min<uint32_t>(WIDE_NQ, s.n_queries - q0);
+                        wi.push_back(w);
+                        ++parts;
+                        pos += take;
+                        wfilled += take;
+                        if (wfilled >= wshare) {
+                            wfilled = 0;
+                            wcta.push_back((uint32_t)wi.size());
+                        }
+                    }
+                    wide_parts = std::max(wide_parts, parts);
+                }
+            }
+            if (wcta.back() != (uint32_t)wi.size()) wcta.push_back((uint32_t)wi.size());
+            SLHA_TRY(p->b_wide_items.ensure(wi.size() * sizeof(WorkItem)));
+            SLHA_TRY(p->b_wide_cta.ensure(wcta.size() * 4));
+            p->d_wide_items = (WorkItem*)p->b_wide_items.p;
+            p->d_wide_cta = (uint32_t*)p->b_wide_cta.p;
+            SLHA_CUDA(cudaMemcpyAsync(p->d_wide_items, wi.data(), wi.size() * sizeof(WorkItem), cudaMemcpyHostToDevice, c->stream));
+            SLHA_CUDA(cudaMemcpyAsync(p->d_wide_cta, wcta.data(), wcta.size() * 4, cudaMemcpyHostToDevice, c->stream));
+            p->n_wide_items = (uint32_t)wi.size();
+            p->wide_grid = (uint32_t)wcta.size() - 1;
+            p->wide = true;
+        }
+    }
     // Streaming top-k state per query row: threshold, bucket mapping, count, flag, 256 bucket counts; and
     // the row's candidate buffer.  In random order about k (1 + ln(n / k)) tiles pass the rising threshold
     // plus the unfiltered first sets of every warp; 16 k slots (at most the longest segment) leave a wide
@@ -316,6 +377,8 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     // (the first set of every warp that scans a row is appended unfiltered: 16 slots per warp and item, twice over)
     const uint64_t first_sets = (uint64_t)(16 + MMA_CHUNK) * (uint64_t)(p->mma_threads / 32) * p->max_parts;
     p->gcap = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(std::max<uint64_t>(16ull * k, 4096), first_sets + 4ull * k), all_of_a_row / 64 * 64);
+    // (wide scoring: the first 128-tile block of every item is appended unfiltered, and a CTA sees few blocks)
+    if (p->wide) p->gcap = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(p->gcap, 4ull * WIDE_M * wide_parts + 16ull * k), ((uint64_t)longest + 63) / 64 * 64);
     p->gstate_bytes = nq * (1024 + 8 + 8 + 4 + 4 + 4);
     // few rows with long buffers: several CTAs per row compact the survivors before the merge
     p->compact_splits = (p->use_mma && nq < 128 && p->gcap >= 8192) ? (uint32_t)std::min<size_t>(32, (296 + nq - 1) / nq) : 0;
@@ -430,7 +493,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     if (nq == 0) return Status();
     if (k == 0 || k > 8192) return Status(SLHA_ERR_DIMENSION, "top-k: k must be in 1..8192");
     Plan* p = nullptr;
-    SLHA_TRY(build_plan(c, tiles, segs, n_segs, nq, k, codec_hint, &p));
+    SLHA_TRY(build_plan(c, tiles, segs, n_segs, nq, k, codec_hint, /*allow_wide=*/state == nullptr, &p));
     const int nwarps = p->threads / 32;
     const bool timed = g_timing.calls < g_timing.max_calls;
     cudaEvent_t* tev = timed ? &g_timing.ev[3 * g_timing.calls] : nullptr;
@@ -469,9 +532,23 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         }
         // 3: no NF4 tile is expected, so the launch holds INT4 / MX-INT4 tiles only (any other tile hands its rows back)
         const int kind = p->tq3 ? 2 : (p->mixed ? 1 : (p->nf4_table ? 0 : 3));
+        if (p->wide) {
+            static thread_local bool wide_configured[16] = {false};
+            if (!wide_configured[c->device & 15]) {
+                SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+                SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+                wide_configured[c->device & 15] = true;
+            }
+            a.items = p->d_wide_items;
+            a.n_items = p->n_wide_items;
+            a.cta_begin = p->d_wide_cta;
+            if (kind == 2) score_wide_kernel<1><<<p->wide_grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
+            else score_wide_kernel<0><<<p->wide_grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
+        } else {
 #define SLHA_LAUNCH_MMA(K) score_stream_kernel<K, STREAM_THREADS><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a)
-        if (kind == 3) SLHA_LAUNCH_MMA(3); else if (kind == 2) SLHA_LAUNCH_MMA(2); else if (kind == 1) SLHA_LAUNCH_MMA(1); else SLHA_LAUNCH_MMA(0);
+            if (kind == 3) SLHA_LAUNCH_MMA(3); else if (kind == 2) SLHA_LAUNCH_MMA(2); else if (kind == 1) SLHA_LAUNCH_MMA(1); else SLHA_LAUNCH_MMA(0);
 #undef SLHA_LAUNCH_MMA
+        }
         count_launch();
         SLHA_CUDA(cudaGetLastError());
     }

@@ -1,0 +1,438 @@
+// Wide scoring: many queries per KV head (16 or more: batched decode, the 64-queries-per-head
+// configuration).  Included by score.cu after score_mma.cuh.
+//
+// With that many queries per tile the coarse term of eq. 2.3 is a real contraction --
+// 128 tiles x 128 dims x 64 queries per block -- and it runs on the fifth-generation tensor cores:
+//   A (128 tiles x K)  the block's tiles, dequantised to exact fp16 values (n - 8) gs 2^-12 in
+//                      shared memory, K-major with the 128-byte swizzle the MMA unit reads,
+//   B (128 columns x K) the work item's up to 64 queries, each as an fp16 hi and lo column
+//                      (q = hi + lo keeps ~22 bits), resident in shared memory for the whole item,
+//   D (128 x 128 fp32)  in tensor memory (TMEM), two accumulators so that the MMAs of one block run
+//                      while the previous block's scores are finished,
+// issued with tcgen05.mma by one thread, tracked with tcgen05.commit -> mbarrier, read back with
+// tcgen05.ld.  K = 128 dims (+16 for TQ3 tiles: level = (n - 8) / 2 + c / 4 with the nibble
+// n = 2 code + correction bit, so the score also needs c / 4 sum_g gs_g Q_g, Q_g the query's sum over
+// scale group g; those eight products per tile ride along as one more K step).
+// Warp roles (9 warps): 0-3 stage and dequantise tiles, 4-7 turn accumulators into scores (Hamming
+// term on the CUDA cores, only for tiles whose coarse score can reach the row's threshold), filter
+// and append candidates to the rows' buffers (the streaming top-k state of score_stream_kernel),
+// 8 issues the MMAs.  Every wait on an mbarrier is bounded; a wait that runs out flags the item's rows
+// for the generic kernel and lets the CTA finish (tensor memory is always given back).
+// Codecs: INT4 / MX-INT4 launches and TQ3 launches; any other tile hands the item's rows back.
+#pragma once
+
+namespace slha {
+namespace {
+
+constexpr int WIDE_M = 128;                         // tiles per block
+constexpr int WIDE_NQ = 64;                         // query rows per work item
+constexpr int WIDE_SLAB = WIDE_M * 128;             // one 64-element K slab of A or B: 128 rows x 128 bytes
+constexpr int WIDE_A_BYTES = 3 * WIDE_SLAB;         // K = 64 + 64 + 16 (third slab: first 32 bytes of every row)
+constexpr int WIDE_RAW_BYTES = WIDE_M * TILE_BYTES; // the block's tiles as they lie in HBM
+constexpr int WIDE_THREADS = 288;
+constexpr uint32_t WIDE_SPIN = 1u << 22;            // polls of one mbarrier wait before it gives up (~0.2 s)
+
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+// a threshold's score word as a float; words at or below the key of -inf mean "no threshold yet"
+__device__ __forceinline__ float wide_thr(uint32_t key) { return key > 0x00800000u ? key_score(key) : -INFINITY; }
+__device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(addr), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t addr) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(addr) : "memory");
+}
+// false when the phase did not complete within WIDE_SPIN polls
+__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
+    for (uint32_t i = 0; i < WIDE_SPIN; ++i) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+        if (i > 64) __nanosleep(64);
+    }
+    return false;
+}
+// K-major, 128-byte swizzle, 8-row groups 1024 bytes apart (tcgen05 shared-memory matrix descriptor)
+__device__ __forceinline__ uint64_t wide_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// instruction descriptor: D fp32, A and B fp16, both K-major, N = 128, M = 128
+constexpr uint32_t WIDE_IDESC = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void wide_mma(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem), "l"(da), "l"(db), "r"(WIDE_IDESC), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void wide_commit(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void wide_tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+        "%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+          "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+          "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Lane-per-row threshold refresh: lanes 0..15 of the calling warp each walk the histogram of one
+// query row (rows Q0 + lane) from the top until the count reaches k; the proven bound is the lower
+// edge of that bucket minus half a bucket (see stream_refresh_threshold).
+__device__ __forceinline__ void wide_refresh(const ScoreArgs& a, uint32_t Q0, int nrows, const float2* rng, uint32_t* pvh, float* thr, int lane) {
+    if (lane < nrows) {
+        const uint32_t Q = Q0 + (uint32_t)lane;
+        uint32_t best = (uint32_t)(*reinterpret_cast<volatile unsigned long long*>(a.gpivot + Q) >> 32);
+        const float2 r = rng[lane];
+        if (r.y != 0.0f) {
+            const uint4* h4 = reinterpret_cast<const uint4*>(a.ghist + (size_t)Q * 256);
+            uint32_t cum = 0;
+            int found = -1;
+            for (int blk = 63; blk >= 3 && found < 0; blk -= 4) {
+                uint4 c[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[u].x), "=r"(c[u].y), "=r"(c[u].z), "=r"(c[u].w) : "l"(h4 + (blk - u)));
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t v[4] = {c[u].w, c[u].z, c[u].y, c[u].x};  // buckets 4 (blk - u) + 3 .. + 0
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        cum += v[j];
+                        if (found < 0 && cum >= a.k) found = 4 * (blk - u) + 3 - j;
+                    }
+                }
+            }
+            if (found >= 1) {
+                const uint32_t e = score_key(r.x + ((float)found - 0.5f) / r.y);
+                const uint32_t ek = e > 8u ? e - 8u : 0u;
+                if (ek > best) {
+                    best = ek;
+                    atomicMax(a.gpivot + Q, (unsigned long long)ek << 32);
+                }
+            }
+        }
+        if (best > pvh[lane]) {
+            pvh[lane] = best;
+            thr[lane] = wide_thr(best);
+        }
+    }
+}
+
+// KINDW 0: INT4 / MX-INT4 tiles, 1: TQ3 tiles
+template <int KINDW>
+__global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // shared layout (1024-byte aligned base): B | A[0] | A[1] | raw[0] | raw[1] | sign words | thresholds | mappings | barriers
+    const uint32_t base_s = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
+    unsigned char* base = smem_raw + (base_s - (uint32_t)__cvta_generic_to_shared(smem_raw));
+    const uint32_t B_s = base_s, A_s = base_s + WIDE_A_BYTES, raw_s = A_s + 2 * WIDE_A_BYTES;
+    unsigned char* raw = base + 3 * WIDE_A_BYTES;
+    unsigned char* tail = raw + 2 * WIDE_RAW_BYTES;
+    uint32_t* qs_w = reinterpret_cast<uint32_t*>(tail);            // [64][8]
+    uint32_t* pvh = qs_w + 512;                                     // [64] score word of the row's threshold
+    float* thr = reinterpret_cast<float*>(pvh + 64);                // [64] the same threshold as a float
+    float2* rng = reinterpret_cast<float2*>(thr + 64);              // [64] (smin, inv)
+    float2* rmap = rng + 64;                                        // [64] (-smin inv, inv)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(rmap + 64);        // full[2], mma_done[2], epi_done[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);    // [0] TMEM base, [1] error flag, [2] bail
+    const uint32_t bars_s = base_s + 3 * WIDE_A_BYTES + 2 * WIDE_RAW_BYTES + 2048 + 256 + 256 + 512 + 512;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bars_s + 8 * i, 128);      // full: the four staging warps
+            mbar_init(bars_s + 16 + 8 * i, 1);   // mma_done: one tcgen05.commit
+            mbar_init(bars_s + 32 + 8 * i, 128); // epi_done: the four scoring warps
+        }
+        tmem_slot[1] = 0;
+        tmem_slot[2] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 8) {  // two accumulators of 128 columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(bars_s + 48), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = tmem_slot[0];
+    uint32_t magic;
+    asm volatile("mov.u32 %0, 0x64006400;\n" : "=r"(magic));
+
+    uint32_t nblk = 0;  // blocks this CTA has pushed through the two stages so far (all roles count alike)
+    const uint32_t item_end = a.cta_begin[blockIdx.x + 1];
+    for (uint32_t item_id = a.cta_begin[blockIdx.x]; item_id < item_end; ++item_id) {
+        const WorkItem it = a.items[item_id];
+        const int nq = (int)it.n_queries;
+        __syncthreads();  // the previous item's MMAs and scores are finished: B, thresholds and sign words may change
+        if (tid < WIDE_NQ) {
+            const bool have = tid < nq;
+            const unsigned long long pv = have ? *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + tid) : ~0ull;
+            pvh[tid] = (uint32_t)(pv >> 32);
+            thr[tid] = have ? wide_thr((uint32_t)(pv >> 32)) : INFINITY;
+            const unsigned long long pr = have ? *reinterpret_cast<volatile unsigned long long*>(a.grange + it.query_begin + tid) : 0ull;
+            rng[tid] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
+            rmap[tid] = make_float2(-rng[tid].x * rng[tid].y, rng[tid].y);
+        }
+        for (int e = tid; e < WIDE_NQ * 8; e += WIDE_THREADS) qs_w[e] = (e >> 3) < nq ? a.q_sign[(size_t)(it.query_begin + (e >> 3)) * 8 + (e & 7)] : 0u;
+        // B: column n = 2 q + part (fp16 hi / lo of query q); k slot 8 i + j holds dim 8 i + {0,4,1,5,2,6,3,7}[j], the order in
+        // which the staging warps produce a tile's values; 16-byte chunk i of a row at chunk (i ^ (row & 7)) of its 128-byte line
+        bool big = false;
+        for (int u = tid; u < 128 * 18; u += WIDE_THREADS) {
+            const int n = u / 18, i = u % 18, qi = n >> 1;
+            const float* q = a.q_coarse + (size_t)(it.query_begin + (qi < nq ? qi : 0)) * D_C;
+            float v[8];
+            if (i < 16) {
+                const float4 x = *reinterpret_cast<const float4*>(q + 8 * i), y = *reinterpret_cast<const float4*>(q + 8 * i + 4);
+                v[0] = x.x; v[1] = y.x; v[2] = x.y; v[3] = y.y; v[4] = x.z; v[5] = y.z; v[6] = x.w; v[7] = y.w;
+            } else if (i == 16 && KINDW == 1) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    float s = 0.0f;
+                    for (int d = 0; d < 16; ++d) s += q[16 * g + d];
+                    v[g] = s;
+                }
+            } else {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) v[g] = 0.0f;
+            }
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float x0 = qi < nq ? v[2 * j] : 0.0f, x1 = qi < nq ? v[2 * j + 1] : 0.0f;
+                big |= fabsf(x0) > 60000.0f || fabsf(x1) > 60000.0f;
+                if (n & 1) { x0 = half_residual(x0); x1 = half_residual(x1); }
+                w[j] = pack_half2(x0, x1);
+            }
+            const uint32_t slab = (uint32_t)i >> 3, chunk = (uint32_t)i & 7u;
+            sts_v4(B_s + slab * WIDE_SLAB + (uint32_t)n * 128u + ((chunk ^ ((uint32_t)n & 7u)) << 4), w[0], w[1], w[2], w[3]);
+        }
+        if (big) tmem_slot[2] = 1;  // a query too large for the fp16 split
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // B was written with ordinary stores, the MMA reads it through the async proxy
+        __syncthreads();
+        const bool too_big = tmem_slot[2] != 0;
+        const uint32_t n = it.n_tiles;
+        const uint32_t blocks = too_big ? 0u : (n + WIDE_M - 1) / WIDE_M;
+
+        if (warp < 4) {
+            // ---- staging warps: block -> raw[s] (cp.async), then A[s] ----
+            for (uint32_t b = 0; b < blocks; ++b) {
+                const uint32_t g = nblk + b, s = g & 1u, use = g >> 1;
+                if (use > 0 && !mbar_wait(bars_s + 32 + 8 * s, (use - 1) & 1u)) { tmem_slot[1] = 1; break; }
+                const uint32_t t0 = b * WIDE_M;
+                const unsigned char* src = a.tiles + (it.tile_begin + t0) * TILE_BYTES;
+                const uint32_t rs = raw_s + s * WIDE_RAW_BYTES;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t chunk = (uint32_t)i * 128u + (uint32_t)tid, row = chunk >> 3;
+                    const bool in = t0 + row < n;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(rs + chunk * 16u), "l"(in ? src + (size_t)chunk * 16 : a.tiles), "r"(in ? 16 : 0));
+                }
+                cp_async_commit();
+                cp_async_wait<0>();
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");  // the staging warps see each other's copies
+                // thread -> (row, quarter of the latent): 4 x 128 units per block
+                bool foreign = false;
+#pragma unroll 1
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t unit = (uint32_t)i * 128u + (uint32_t)tid, r = unit >> 2, c = unit & 3u;
+                    const uint32_t row_s = rs + r * TILE_BYTES;
+                    const uint32_t flags = lds_u16<118>(row_s);
+                    const bool live = t0 + r < n;
+                    if (live && ((KINDW == 1) ? !(flags & F_TQ3) || (flags & (F_NF4 | F_MIXED | F_MIX3)) : (flags & (F_NF4 | F_MIXED | F_TQ3 | F_MIX3)) != 0)) foreign = true;
+                    uint32_t nib[4];
+                    if (KINDW == 1) {
+                        const uint32_t w0 = lds_u32(row_s + 12u * c), w1 = lds_u32(row_s + 12u * c + 4u), w2 = lds_u32(row_s + 12u * c + 8u);
+                        const uint32_t cr = lds_u32(row_s + 48u + 4u * c);
+                        const uint32_t w[4] = {w0, w1, w2, 0u};
+#pragma unroll
+                        for (int m = 0; m < 4; ++m) {
+                            const int wi = (24 * m) >> 5, sh = (24 * m) & 31;
+                            uint32_t x = __funnelshift_r(w[wi], w[wi + 1], sh) & 0xFFFFFFu;  // eight 3-bit codes
+                            x = (x & 0xFFFu) | ((x & 0xFFF000u) << 4);
+                            x = (x & 0x003F003Fu) | ((x & 0x0FC00FC0u) << 2);
+                            x = (x & 0x07070707u) | ((x & 0x38383838u) << 1);
+                            uint32_t cb = (cr >> (8 * m)) & 0xFFu;                             // their correction bits
+                            cb = (cb | (cb << 12)) & 0x000F000Fu;
+                            cb = (cb | (cb << 6)) & 0x03030303u;
+                            cb = (cb | (cb << 3)) & 0x11111111u;
+                            nib[m] = (x << 1) | cb;
+                        }
+                    } else {
+                        const uint4 L = lds_v4<0>(row_s + 16u * c);
+                        nib[0] = L.x; nib[1] = L.y; nib[2] = L.z; nib[3] = L.w;
+                    }
+                    uint32_t G0, C0, G1, C1;
+                    int4c_scales(lds_u16<120>(row_s + 2u * c), magic, G0, C0, G1, C1);
+                    const uint32_t arow = A_s + s * WIDE_A_BYTES + r * 128u;
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        uint32_t o[4];
+                        int4c_word(nib[m], m < 2 ? G0 : G1, m < 2 ? C0 : C1, o);
+                        if (!live) o[0] = o[1] = o[2] = o[3] = 0u;
+                        const uint32_t word = 4u * c + (uint32_t)m, slab = word >> 3, chunk = word & 7u;
+                        sts_v4(arow + slab * WIDE_SLAB + ((chunk ^ (r & 7u)) << 4), o[0], o[1], o[2], o[3]);
+                    }
+                    if (c == 0) {
+                        // third slab: the eight scale bytes times c 2^-13 (TQ3: c = 1, or 2 once the correction plane is gone), then zeros
+                        uint32_t e[4] = {0u, 0u, 0u, 0u};
+                        if (KINDW == 1 && live) {
+                            const uint2 gsb = lds_v2<120>(row_s);
+                            const uint32_t f = (flags & F_NOCORR) ? 0x0C000C00u : 0x08000800u;  // 2^-12 or 2^-13 as fp16, twice
+                            uint32_t t;
+                            asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.x, magic, 0x7150u)), "r"(0xE400E400u));
+                            asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[0]) : "r"(t), "r"(f));
+                            asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.x, magic, 0x7352u)), "r"(0xE400E400u));
+                            asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[1]) : "r"(t), "r"(f));
+                            asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.y, magic, 0x7150u)), "r"(0xE400E400u));
+                            asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[2]) : "r"(t), "r"(f));
+                            asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.y, magic, 0x7352u)), "r"(0xE400E400u));
+                            asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[3]) : "r"(t), "r"(f));
+                        }
+                        sts_v4(arow + 2 * WIDE_SLAB + ((0u ^ (r & 7u)) << 4), e[0], e[1], e[2], e[3]);
+                        sts_v4(arow + 2 * WIDE_SLAB + ((1u ^ (r & 7u)) << 4), 0u, 0u, 0u, 0u);
+                    }
+                }
+                if (foreign) tmem_slot[2] = 1;  // a codec this launch does not decode: the item's rows go to the generic kernel
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                mbar_arrive(bars_s + 8 * s);
+            }
+        } else if (warp == 8) {
+            // ---- MMA warp: one thread issues the K steps of every block ----
+            for (uint32_t b = 0; b < blocks; ++b) {
+                const uint32_t g = nblk + b, s = g & 1u, use = g >> 1;
+                if (!mbar_wait(bars_s + 8 * s, use & 1u)) { tmem_slot[1] = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                if (lane == 0) {
+                    const uint32_t as = A_s + s * WIDE_A_BYTES;
+#pragma unroll
+                    for (int ks = 0; ks < (KINDW == 1 ? 9 : 8); ++ks) {
+                        const uint32_t off = (uint32_t)(ks >> 2) * WIDE_SLAB + (uint32_t)(ks & 3) * 32u;
+                        wide_mma(tmem + s * 128u, wide_desc(as + off), wide_desc(B_s + off), ks > 0 ? 1u : 0u);
+                    }
+                    wide_commit(bars_s + 16 + 8 * s);
+                }
+                __syncwarp();
+            }
+        } else {
+            // ---- scoring warps: thread = tile row of the block ----
+            const int ew = warp - 4, r = 32 * ew + lane;
+            for (uint32_t b = 0; b < blocks; ++b) {
+                const uint32_t g = nblk + b, s = g & 1u, use = g >> 1;
+                if (!mbar_wait(bars_s + 16 + 8 * s, use & 1u)) { tmem_slot[1] = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t t0 = b * WIDE_M + (uint32_t)r;
+                const uint32_t row_s = raw_s + s * WIDE_RAW_BYTES + (uint32_t)r * TILE_BYTES;
+                const uint2 meta = lds_v2<96>(row_s);
+                const uint32_t flags = lds_u16<118>(row_s);
+                const bool live = t0 < n;
+                const uint4 ra = lds_v4<64>(row_s), rb2 = lds_v4<80>(row_s);
+                const float lam = (flags & F_WARM) ? 0.0f : __uint_as_float(meta.y);
+                const float su = __uint_as_float(meta.x) * (KINDW == 1 ? 2048.0f / 255.0f : 4096.0f / 255.0f);
+                const uint32_t nidx = ~(it.index_base + t0);
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    wide_tmem_ld32(tmem + ((uint32_t)(32 * ew) << 16) + s * 128u + (uint32_t)c * 32u, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int q = 16 * c + j;
+                        if (q >= nq) break;  // (uniform)
+                        const float coarse = (__uint_as_float(v[2 * j]) + __uint_as_float(v[2 * j + 1])) * su;
+                        // the residual term lies in [-256 lambda, 256 lambda]
+                        bool p = live && fmaf(lam, 257.0f, coarse + fabsf(coarse) * 1e-6f) >= thr[q];
+                        float sc = coarse;
+                        uint32_t key = 0;
+                        if (p) {
+                            const uint32_t* qw = qs_w + 8 * q;
+                            const int h = __popc(ra.x ^ qw[0]) + __popc(ra.y ^ qw[1]) + __popc(ra.z ^ qw[2]) + __popc(ra.w ^ qw[3]) +
+                                          __popc(rb2.x ^ qw[4]) + __popc(rb2.y ^ qw[5]) + __popc(rb2.z ^ qw[6]) + __popc(rb2.w ^ qw[7]);
+                            sc = fmaf(lam, (float)(256 - 2 * h), coarse);
+                            key = score_key(sc);
+                            p = key >= pvh[q];
+                        }
+                        const unsigned bal = __ballot_sync(0xFFFFFFFFu, p);
+                        if (bal) {
+                            const uint32_t Q = it.query_begin + (uint32_t)q;
+                            // first candidates of a row without a bucket mapping define one (any monotone mapping is valid)
+                            if (rng[q].y == 0.0f) {
+                                float mn = p ? sc : INFINITY, mx = p ? sc : -INFINITY;
+#pragma unroll
+                                for (int o = 16; o; o >>= 1) {
+                                    mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, o));
+                                    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+                                }
+                                if (lane == 0) {
+                                    unsigned long long pr = *reinterpret_cast<volatile unsigned long long*>(a.grange + Q);
+                                    if (!pr && mx > mn) {
+                                        const float span = mx - mn, lo = mn - 1.5f * span, inv = 256.0f / (4.0f * span);
+                                        if (isfinite(lo) && isfinite(inv) && inv > 0.0f) {
+                                            const unsigned long long mine_r = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(inv) << 32);
+                                            const unsigned long long old = atomicCAS(a.grange + Q, 0ull, mine_r);
+                                            pr = old ? old : mine_r;
+                                        }
+                                    }
+                                    if (pr) {
+                                        const float2 rr = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
+                                        rng[q] = rr;
+                                        rmap[q] = make_float2(-rr.x * rr.y, rr.y);
+                                    }
+                                }
+                                __syncwarp();
+                            }
+                            uint32_t slot0 = 0;
+                            if (lane == 0) slot0 = atomicAdd(a.gcount + Q, (uint32_t)__popc(bal));
+                            slot0 = __shfl_sync(0xFFFFFFFFu, slot0, 0);
+                            if (p) {
+                                const uint32_t at = slot0 + (uint32_t)__popc(bal & ((1u << lane) - 1u));
+                                if (at < a.gcap) a.gbuf[(size_t)Q * a.gcap + at] = ((uint64_t)key << 32) | (uint64_t)nidx;
+                                else a.gflag[Q] = 1u;  // the row's buffer is full: the generic kernel scores the row
+                                const float2 rm = rmap[q];
+                                atomicAdd(a.ghist + (size_t)Q * 256 + min(max(__float2int_rz(fmaf(sc, rm.y, rm.x)), 0), 255), 1u);
+                            }
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+                mbar_arrive(bars_s + 32 + 8 * s);
+                // thresholds: after the first block (every CTA of the grid has appended one unfiltered block by
+                // then) and every second block after it; warp ew looks after rows 16 ew .. 16 ew + 15
+                if ((b & 1u) == 0u) {
+                    __syncwarp();
+                    const int rows = min(16, nq - 16 * ew);
+                    if (rows > 0) wide_refresh(a, it.query_begin + 16u * (uint32_t)ew, rows, rng + 16 * ew, pvh + 16 * ew, thr + 16 * ew, lane);
+                    __syncwarp();
+                }
+            }
+        }
+        nblk += blocks;
+        __syncthreads();
+        // rows this CTA could not score (another codec, a query outside the fp16 split, a wait that ran out) go to the generic kernel
+        if ((tmem_slot[2] || tmem_slot[1]) && tid < nq) a.gflag[it.query_begin + tid] = 1u;
+        if (tmem_slot[1]) break;  // a wait ran out: the barriers' phases are no longer known
+        __syncthreads();
+        if (tid == 0) tmem_slot[2] = 0;  // (ordered before the next item's writers by the barrier at its start)
+    }
+    __syncthreads();
+    if (tmem_slot[1]) {
+        // flag every remaining item of this CTA as well
+        for (uint32_t item_id = a.cta_begin[blockIdx.x]; item_id < item_end; ++item_id)
+            for (uint32_t q = tid; q < a.items[item_id].n_queries; q += WIDE_THREADS) a.gflag[a.items[item_id].query_begin + q] = 1u;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(256u) : "memory");
+}
+
+}  // namespace
+}  // namespace slha

@@ -241,3 +241,38 @@ def test_rejected_call_shape_leaves_no_plan_behind():
         S.score_topk(dt, bad_range, qc, qs, nq, k)
     gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, nq, k)
     check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+
+
+@pytest.mark.parametrize("n,nq,k,codec,warm,nocorr,foreign", [
+    (5000, 64, 64, 1, 0, 0, None),       # MX-INT4, a full 64-row item, ragged last block
+    (33001, 37, 256, 6, 9, 0, None),     # MX-32, 37 rows (a partial item), WARM tiles
+    (12800, 16, 128, 4, 7, 5, None),     # TQ3 with WARM tiles and tiles whose correction plane was dropped
+    (9000, 100, 32, 4, 0, 0, None),      # TQ3, two items of 64 + 36 rows
+    (20000, 24, 100, 0, 0, 0, 2),        # INT4 with a stretch of NF4 tiles: the rows are handed to the generic kernel
+    (127, 20, 200, 1, 0, 0, None),       # fewer tiles than k and than one block
+])
+def test_wide_scoring_on_the_tcgen05_kernel(n, nq, k, codec, warm, nocorr, foreign):
+    # 16 or more queries per segment: score_wide_kernel (128-tile blocks x up to 64 query rows on tcgen05 MMAs)
+    tiles = H.random_tiles(n, codec, seed=n + nq, warm_every=warm, nocorr_every=nocorr)
+    if foreign:
+        tiles[6000:6300] = H.random_tiles(300, foreign, seed=n + 1)
+    qc, qs = H.random_queries(nq, n + 3)
+    qc[nq // 2] += 0.5  # a query with large group sums weighs the TQ3 half-level term
+    segs = [(0, n, 0, nq, 11)]
+    dt = S.to_device(tiles)
+    gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, nq, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+    st = S.last_score_stats()
+    assert st["rows"] == nq and st["rows_handed_to_generic_kernel"] == (nq if foreign else 0)
+
+
+def test_wide_scoring_two_segments_and_repeat():
+    # two KV heads with 48 queries each; the second call must not see anything the first left behind
+    n, qph, k = 7000, 48, 80
+    tiles = H.random_tiles(2 * n, 6, seed=77)
+    dt = S.to_device(tiles)
+    segs = [(0, n, 0, qph, 0), (n, n, qph, qph, 0)]
+    for seed in (1, 2):
+        qc, qs = H.random_queries(2 * qph, seed)
+        gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, 2 * qph, k)
+        check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
