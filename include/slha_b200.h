@@ -455,6 +455,25 @@ int32_t slha_b200_pool_observe_query(SlhaB200Pool* pool, const float* q_coarse,
 int32_t slha_b200_pool_page_out(SlhaB200Pool* pool, uint32_t slot);                      /* ccos.rs:365 */
 int32_t slha_b200_pool_drop_correction(SlhaB200Pool* pool, uint32_t slot, int32_t* dropped); /* ccos.rs:386 */
 int32_t slha_b200_pool_evict(SlhaB200Pool* pool, uint32_t slot, int32_t* evicted);        /* ccos.rs:404 */
+/*
+ * COLD persistence: attach the reference's EventLog (scirust/src/eventlog.rs:9-24 -- 16-byte header,
+ * 144-byte records of (seq, slot, FNV-1a checksum, tile), byte-identical for identical evictions) as
+ * ElasticKvCache::attach_event_log / attach_durable_event_log do (ccos.rs:155-170).  From then on every
+ * eviction (slha_b200_pool_evict and the eviction phase of enforce_budget) first brings the doomed
+ * tiles to the host and appends their records in eviction order, then flips the slots; with
+ * require_durable != 0 each record is fsync'ed and a record that cannot be written keeps its slot live
+ * (ccos.rs:404-438).  mode: 0 create / truncate, 1 create only if absent, 2 open an existing log
+ * strictly (header, whole records, checksums), 3 open and drop one partial record at the tail,
+ * 4 open read-only.  path == NULL detaches.
+ */
+int32_t slha_b200_pool_attach_event_log(SlhaB200Pool* pool, const char* path, int32_t mode,
+                                        int32_t require_durable);
+/* ElasticKvCache::rehydrate (ccos.rs:451-466): the most recent record with eviction sequence `seq`
+ * re-enters the pool as a fresh admission (WARM if its tile carries the WARM flag, else HOT);
+ * slot_out gets its slot, or -1 when no log is attached or no record matches. */
+int32_t slha_b200_pool_rehydrate(SlhaB200Pool* pool, uint64_t seq, int64_t* slot_out);
+/* out[0] records in the attached log, out[1] log_errors, out[2] blocked_evictions (ccos.rs:173-181) */
+int32_t slha_b200_pool_event_log_stats(SlhaB200Pool* pool, uint64_t* out /* 3 values */);
 /* ElasticKvCache::enforce_budget (ccos.rs:555-614); within_budget gets its bool. */
 int32_t slha_b200_pool_enforce_budget(SlhaB200Pool* pool, int32_t* within_budget);
 int32_t slha_b200_pool_set_budget(SlhaB200Pool* pool, uint64_t budget_bytes);

@@ -173,6 +173,9 @@ extern "C" {
     pub fn slha_b200_pool_page_out(pool: *mut SlhaB200Pool, slot: u32) -> i32;
     pub fn slha_b200_pool_drop_correction(pool: *mut SlhaB200Pool, slot: u32, dropped: *mut i32) -> i32;
     pub fn slha_b200_pool_evict(pool: *mut SlhaB200Pool, slot: u32, evicted: *mut i32) -> i32;
+    pub fn slha_b200_pool_attach_event_log(pool: *mut SlhaB200Pool, path: *const c_char, mode: i32, require_durable: i32) -> i32;
+    pub fn slha_b200_pool_rehydrate(pool: *mut SlhaB200Pool, seq: u64, slot_out: *mut i64) -> i32;
+    pub fn slha_b200_pool_event_log_stats(pool: *mut SlhaB200Pool, out: *mut u64) -> i32;
     pub fn slha_b200_pool_enforce_budget(pool: *mut SlhaB200Pool, within_budget: *mut i32) -> i32;
     pub fn slha_b200_pool_set_budget(pool: *mut SlhaB200Pool, budget_bytes: u64) -> i32;
     pub fn slha_b200_pool_stats(pool: *mut SlhaB200Pool, out: *mut u64) -> i32;

@@ -107,6 +107,9 @@ SIGNATURES = {
     "slha_b200_pool_page_out": (_i32, [_vp, _u32]),
     "slha_b200_pool_drop_correction": (_i32, [_vp, _u32, _vp]),
     "slha_b200_pool_evict": (_i32, [_vp, _u32, _vp]),
+    "slha_b200_pool_attach_event_log": (_i32, [_vp, C.c_char_p, _i32, _i32]),
+    "slha_b200_pool_rehydrate": (_i32, [_vp, _u64, _vp]),
+    "slha_b200_pool_event_log_stats": (_i32, [_vp, _vp]),
     "slha_b200_pool_enforce_budget": (_i32, [_vp, _vp]),
     "slha_b200_pool_set_budget": (_i32, [_vp, _u64]),
     "slha_b200_pool_stats": (_i32, [_vp, _vp]),
@@ -603,6 +606,23 @@ class TilePool:
             )
         )
         return out_slot, out_score, out_count
+
+    def attach_event_log(self, path, mode=0, require_durable=False):
+        """attach_event_log / attach_durable_event_log (ccos.rs:155-170); mode 0 create, 1 create_new, 2 open,
+        3 open_recover, 4 read-only; path None detaches."""
+        _check(load_library().slha_b200_pool_attach_event_log(self.handle, None if path is None else str(path).encode(), mode,
+                                                              1 if require_durable else 0))
+
+    def rehydrate(self, seq):
+        """ElasticKvCache::rehydrate (ccos.rs:451-466): slot of the re-admitted tile, or None."""
+        out = C.c_int64(-1)
+        _check(load_library().slha_b200_pool_rehydrate(self.handle, seq, C.addressof(out)))
+        return None if out.value < 0 else int(out.value)
+
+    def event_log_stats(self):
+        out = np.zeros(3, np.uint64)
+        _check(load_library().slha_b200_pool_event_log_stats(self.handle, ptr(out)))
+        return {"records": int(out[0]), "log_errors": int(out[1]), "blocked_evictions": int(out[2])}
 
     def observe_scores(self, slots, scores, temperature):
         s, v = _np(slots, np.uint32), _np(scores, np.float32)

@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libslha_b200.so")
-SOURCES = ["score.cu", "encode.cu", "pool.cu", "runtime.cu", "shard.cu", "attend.cu", "capi.cu"]
+SOURCES = ["score.cu", "encode.cu", "pool.cu", "runtime.cu", "shard.cu", "attend.cu", "eventlog.cu", "capi.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 COMMON = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

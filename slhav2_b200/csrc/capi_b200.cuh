@@ -610,6 +610,42 @@ int32_t slha_b200_pool_evict(SlhaB200Pool* pool, uint32_t slot, int32_t* evicted
     return pool_single(pool, 2, slot, evicted);
 }
 
+int32_t slha_b200_pool_attach_event_log(SlhaB200Pool* pool, const char* path, int32_t mode, int32_t require_durable) {
+    return ffi([&]() -> Status {
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        Pool* pl;
+        SLHA_TRY(pool_check(pool, c, &pl));
+        if (pl->log) eventlog_close(pl->log);
+        pl->log = nullptr;
+        pl->require_durable = require_durable != 0;
+        if (!path) return Status();  // detach (with require_durable set: every eviction is refused, ccos.rs:429-432)
+        return eventlog_open(path, mode, &pl->log);
+    });
+}
+int32_t slha_b200_pool_rehydrate(SlhaB200Pool* pool, uint64_t seq, int64_t* slot_out) {
+    return ffi([&]() -> Status {
+        if (!slot_out) return Status(SLHA_ERR_NULL, "slha_b200_pool_rehydrate received a NULL pointer");
+        CallScope cs;
+        if (!cs.ok()) return cs.st;
+        Pool* pl;
+        SLHA_TRY(pool_check(pool, cs.c, &pl));
+        return pool_rehydrate(cs.c, pl, seq, slot_out);
+    });
+}
+int32_t slha_b200_pool_event_log_stats(SlhaB200Pool* pool, uint64_t* out) {
+    return ffi([&]() -> Status {
+        if (!out) return Status(SLHA_ERR_NULL, "slha_b200_pool_event_log_stats received a NULL pointer");
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        Pool* pl;
+        SLHA_TRY(pool_check(pool, c, &pl));
+        out[0] = pl->log ? eventlog_records(pl->log) : 0;
+        out[1] = pl->log_errors;
+        out[2] = pl->blocked_evictions;
+        return Status();
+    });
+}
 int32_t slha_b200_pool_enforce_budget(SlhaB200Pool* pool, int32_t* within_budget) {
     return ffi([&]() -> Status {
         CallScope cs;

@@ -11,6 +11,8 @@
 #include <unistd.h>
 
 #include <cerrno>
+#include <memory>
+#include <string>
 #include <cstring>
 #include <vector>
 

@@ -253,14 +253,14 @@ __global__ void phase_weights_kernel(PoolDev p, int phase, const uint64_t* keys_
 // live <= budget {return}; op(s) }` loop reaches.
 __global__ void phase_apply_kernel(PoolDev p, int phase, const uint64_t* keys_sorted,
                                    const uint32_t* slots_sorted, const uint32_t* w,
-                                   const uint64_t* excl) {
+                                   const uint64_t* excl, uint64_t limit) {
     const uint64_t len = p.cnt->n_cand;
     const uint64_t deficit = p.cnt->phase_deficit;
     const uint64_t free0 = p.cnt->free_len;
     int64_t delta = 0;
     uint32_t applied = 0;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += (uint64_t)gridDim.x * blockDim.x) {
-        if (keys_sorted[i] == SENTINEL || deficit == 0 || excl[i] >= deficit) continue;
+        if (keys_sorted[i] == SENTINEL || deficit == 0 || excl[i] >= deficit || i >= limit) continue;
         const uint32_t s = slots_sorted[i];
         if (phase == PH_PAGE) do_page_out(p, s, &delta);
         else if (phase <= PH_CORR_WARM) do_drop_correction(p, s, &delta);
@@ -278,6 +278,21 @@ __global__ void phase_apply_kernel(PoolDev p, int phase, const uint64_t* keys_so
     if ((threadIdx.x & 31) == 0) {
         if (delta) atomicAdd((unsigned long long*)&p.cnt->live_delta, (unsigned long long)delta);
         if (applied) atomicAdd((unsigned long long*)&p.cnt->phase_applied, (unsigned long long)applied);
+    }
+}
+// With an event log attached: (seq, slot, tile) of the slots an eviction phase is about to turn COLD,
+// in eviction order (the applied items are a prefix of the sorted candidates), for the host to append.
+__global__ void phase_journal_kernel(PoolDev p, const uint64_t* keys_sorted, const uint32_t* slots_sorted, const uint64_t* excl,
+                                     unsigned long long* count, uint64_t* seq_out, uint32_t* slot_out, uint4* tiles_out) {
+    const uint64_t len = p.cnt->n_cand, deficit = p.cnt->phase_deficit;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += (uint64_t)gridDim.x * blockDim.x) {
+        if (keys_sorted[i] == SENTINEL || deficit == 0 || excl[i] >= deficit) continue;
+        const uint32_t s = slots_sorted[i];
+        seq_out[i] = p.seq[s];
+        slot_out[i] = s;
+        const uint4* src = reinterpret_cast<const uint4*>(p.tiles + (size_t)s * TILE_BYTES);
+        for (int j = 0; j < 8; ++j) tiles_out[i * 8 + j] = src[j];
+        atomicMax(count, (unsigned long long)(i + 1));
     }
 }
 __global__ void phase_commit_kernel(PoolDev p) {
@@ -472,6 +487,7 @@ void pool_destroy(Pool* pl) {
     cudaFree(pl->dev.free_list);
     cudaFree(pl->dev.cnt);
     cudaFree(pl->d_observe);
+    if (pl->log) eventlog_close(pl->log);
     delete pl;
 }
 
@@ -501,6 +517,31 @@ Status pool_scatter(Ctx* c, Pool* pl, const unsigned char* d_src_tiles, const ui
 }
 
 Status pool_single_op(Ctx* c, Pool* pl, int op, uint32_t slot, int32_t* result) {
+    if (op == 2 && (pl->log || pl->require_durable)) {
+        // evict with an event log attached (ccos.rs:404-438): persist the record, then (and only then) go COLD
+        SLHA_TRY(pool_sync_counters(c, pl));
+        uint8_t st = ST_COLD;
+        if (slot < pl->h_cnt.len) SLHA_CUDA(cudaMemcpyAsync(&st, pl->dev.state + slot, 1, cudaMemcpyDeviceToHost, c->stream));
+        SLHA_CUDA(cudaStreamSynchronize(c->stream));
+        if (st == ST_COLD) {
+            *result = 0;
+            return Status();
+        }
+        uint64_t seq = 0;
+        unsigned char tile[TILE_BYTES];
+        SLHA_CUDA(cudaMemcpyAsync(&seq, pl->dev.seq + slot, 8, cudaMemcpyDeviceToHost, c->stream));
+        SLHA_CUDA(cudaMemcpyAsync(tile, pl->dev.tiles + (size_t)slot * TILE_BYTES, TILE_BYTES, cudaMemcpyDeviceToHost, c->stream));
+        SLHA_CUDA(cudaStreamSynchronize(c->stream));
+        const bool ok = pl->log && eventlog_append(pl->log, seq, slot, tile, pl->require_durable).ok();
+        if (!ok) {
+            if (pl->log) ++pl->log_errors;
+            if (pl->require_durable) {
+                ++pl->blocked_evictions;
+                *result = 0;
+                return Status();
+            }
+        }
+    }
     int32_t* d_res;
     SLHA_TRY(ctx_device_scratch(c, 256, (void**)&d_res));
     single_op_kernel<<<1, 1, 0, c->stream>>>(pl->dev, op, slot, d_res);
@@ -592,7 +633,46 @@ Status pool_enforce_budget(Ctx* c, Pool* pl, int32_t* within) {
         phase_weights_kernel<<<cgrid, 256, 0, c->stream>>>(pl->dev, ph, keys_s, vals_s, w);
         tb = tmp_bytes;
         SLHA_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tb, w, excl, nc, c->stream));
-        phase_apply_kernel<<<cgrid, 256, 0, c->stream>>>(pl->dev, ph, keys_s, vals_s, w, excl);
+        uint64_t limit = ~0ull;
+        if (ph >= PH_EVICT && (pl->log || pl->require_durable)) {
+            // persist first (ccos.rs:411-432): the records of the slots this phase will evict, in order
+            unsigned long long* d_cnt;
+            uint64_t* d_seq;
+            uint32_t* d_slot;
+            uint4* d_tiles;
+            SLHA_TRY(ctx_device_scratch(c, 256, (void**)&d_cnt));
+            SLHA_TRY(ctx_device_scratch(c, (size_t)nc * 8, (void**)&d_seq));
+            SLHA_TRY(ctx_device_scratch(c, (size_t)nc * 4, (void**)&d_slot));
+            SLHA_TRY(ctx_device_scratch(c, (size_t)nc * TILE_BYTES, (void**)&d_tiles));
+            SLHA_CUDA(cudaMemsetAsync(d_cnt, 0, 8, c->stream));
+            phase_journal_kernel<<<cgrid, 256, 0, c->stream>>>(pl->dev, keys_s, vals_s, excl, d_cnt, d_seq, d_slot, d_tiles);
+            count_launch();
+            unsigned long long m = 0;
+            SLHA_CUDA(cudaMemcpyAsync(&m, d_cnt, 8, cudaMemcpyDeviceToHost, c->stream));
+            SLHA_CUDA(cudaStreamSynchronize(c->stream));
+            std::vector<uint64_t> hseq(m);
+            std::vector<uint32_t> hslot(m);
+            std::vector<unsigned char> htiles((size_t)m * TILE_BYTES);
+            if (m) {
+                SLHA_CUDA(cudaMemcpyAsync(hseq.data(), d_seq, m * 8, cudaMemcpyDeviceToHost, c->stream));
+                SLHA_CUDA(cudaMemcpyAsync(hslot.data(), d_slot, m * 4, cudaMemcpyDeviceToHost, c->stream));
+                SLHA_CUDA(cudaMemcpyAsync(htiles.data(), d_tiles, (size_t)m * TILE_BYTES, cudaMemcpyDeviceToHost, c->stream));
+                SLHA_CUDA(cudaStreamSynchronize(c->stream));
+            }
+            for (unsigned long long i = 0; i < m; ++i) {
+                const bool ok = pl->log && eventlog_append(pl->log, hseq[i], hslot[i], htiles.data() + (size_t)i * TILE_BYTES, pl->require_durable).ok();
+                if (ok) continue;
+                if (pl->log) ++pl->log_errors;
+                if (pl->require_durable) {
+                    // the slot stays live; the reference goes on to try (and be refused) every remaining live slot
+                    limit = i;
+                    pl->blocked_evictions += (uint64_t)nc - i;
+                    if (pl->log) pl->log_errors += (uint64_t)nc - i - 1;
+                    break;
+                }
+            }
+        }
+        phase_apply_kernel<<<cgrid, 256, 0, c->stream>>>(pl->dev, ph, keys_s, vals_s, w, excl, limit);
         phase_commit_kernel<<<1, 1, 0, c->stream>>>(pl->dev);
         count_launch(3);
         SLHA_CUDA(cudaGetLastError());
@@ -637,4 +717,31 @@ Status pool_compact_live(Ctx* c, Pool* pl, const float* d_scores, uint32_t* d_sl
     return Status();
 }
 
+}  // namespace slha
+
+namespace slha {
+// ElasticKvCache::rehydrate (ccos.rs:451-466): the most recent record with that eviction seq comes back as a
+// fresh admission (new seq, importance 0), WARM when its tile carries the WARM flag, else HOT.
+Status pool_rehydrate(Ctx* c, Pool* pl, uint64_t seq, int64_t* slot_out) {
+    *slot_out = -1;
+    if (!pl->log) return Status();
+    bool found = false;
+    uint32_t old_slot = 0;
+    unsigned char tile[TILE_BYTES];
+    SLHA_TRY(eventlog_fetch_by_seq(pl->log, seq, &found, &old_slot, tile));
+    if (!found) return Status();
+    unsigned char* d_tile;
+    uint32_t* d_slot;
+    SLHA_TRY(ctx_device_scratch(c, TILE_BYTES, (void**)&d_tile));
+    SLHA_TRY(ctx_device_scratch(c, 256, (void**)&d_slot));
+    SLHA_CUDA(cudaMemcpyAsync(d_tile, tile, TILE_BYTES, cudaMemcpyHostToDevice, c->stream));
+    SLHA_TRY(pool_reserve(c, pl, d_tile, 1, d_slot));
+    SLHA_TRY(pool_scatter(c, pl, d_tile, d_slot, 1));
+    uint32_t slot = 0;
+    SLHA_CUDA(cudaMemcpyAsync(&slot, d_slot, 4, cudaMemcpyDeviceToHost, c->stream));
+    SLHA_CUDA(cudaStreamSynchronize(c->stream));
+    pl->codec_mask |= 0x80000000u;
+    *slot_out = (int64_t)slot;
+    return Status();
+}
 }  // namespace slha

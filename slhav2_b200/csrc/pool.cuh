@@ -31,6 +31,14 @@ struct PoolDev {
     uint32_t sink_window = 0, recent_window = 0;
 };
 
+// COLD persistence (eventlog.cu): the reference's EventLog file format
+struct EventLog;
+Status eventlog_open(const char* path, int mode, EventLog** out);
+void eventlog_close(EventLog* log);
+uint64_t eventlog_records(const EventLog* log);
+Status eventlog_append(EventLog* log, uint64_t seq, uint32_t slot, const unsigned char* tile, bool durable);
+Status eventlog_fetch_by_seq(EventLog* log, uint64_t seq, bool* found, uint32_t* slot, unsigned char* tile);
+
 struct Pool {
     SlhaB200PoolConfig cfg;
     int device = 0;
@@ -40,6 +48,10 @@ struct Pool {
     // codecs the pool may hold: bit i = codec id i appended through append_keys; bit 31 = tiles of
     // unknown codec were inserted. Lets the scorer pick its kernel variant without reading tiles back.
     uint32_t codec_mask = 0;
+    // attached event log (ccos.rs:155-170): evicted tiles are appended before their slots go COLD
+    EventLog* log = nullptr;
+    bool require_durable = false;            // EvictionDurability::RequireDurable
+    uint64_t log_errors = 0, blocked_evictions = 0;  // ccos.rs:173-181
 };
 
 Status pool_create(Ctx* c, const SlhaB200PoolConfig& cfg, Pool** out);
@@ -51,6 +63,7 @@ Status pool_single_op(Ctx* c, Pool* pl, int op, uint32_t slot, int32_t* result);
 Status pool_enforce_budget(Ctx* c, Pool* pl, int32_t* within);
 Status pool_observe(Ctx* c, Pool* pl, const uint32_t* d_slots, const float* d_scores, uint64_t n, float temperature);
 Status pool_stats(Ctx* c, Pool* pl, uint64_t out[8]);
+Status pool_rehydrate(Ctx* c, Pool* pl, uint64_t seq, int64_t* slot_out);
 Status pool_compact_live(Ctx* c, Pool* pl, const float* d_scores, uint32_t* d_slots_out, float* d_scores_out,
                          unsigned long long* d_n_out);
 

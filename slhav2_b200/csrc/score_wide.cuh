@@ -97,13 +97,13 @@ __device__ __forceinline__ void wide_refresh(const ScoreArgs& a, uint32_t Q0, in
             const uint4* h4 = reinterpret_cast<const uint4*>(a.ghist + (size_t)Q * 256);
             uint32_t cum = 0;
             int found = -1;
-            for (int blk = 63; blk >= 3 && found < 0; blk -= 4) {
-                uint4 c[4];
+            for (int blk = 63; blk >= 7 && found < 0; blk -= 8) {
+                uint4 c[8];
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
+                for (int u = 0; u < 8; ++u)
                     asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[u].x), "=r"(c[u].y), "=r"(c[u].z), "=r"(c[u].w) : "l"(h4 + (blk - u)));
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < 8; ++u) {
                     const uint32_t v[4] = {c[u].w, c[u].z, c[u].y, c[u].x};  // buckets 4 (blk - u) + 3 .. + 0
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -340,32 +340,41 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
                 const float lam = (flags & F_WARM) ? 0.0f : __uint_as_float(meta.y);
                 const float su = __uint_as_float(meta.x) * (KINDW == 1 ? 2048.0f / 255.0f : 4096.0f / 255.0f);
                 const uint32_t nidx = ~(it.index_base + t0);
+                // The first block of an item is walked twice: a counting pass puts every score into the rows'
+                // histograms without appending anything, the thresholds are derived (all CTAs of the grid count
+                // their first blocks at about the same time, 128 tiles each), and only then the block is filtered
+                // like every later one - otherwise each CTA would append its whole first block.
+                for (int pass = (b == 0 ? 0 : 1); pass < 2; ++pass) {
+                    const bool count_only = pass == 0;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    wide_tmem_ld32(tmem + ((uint32_t)(32 * ew) << 16) + s * 128u + (uint32_t)c * 32u, v);
+                    for (int c = 0; c < 4; ++c) {
+                        if (16 * c >= nq) break;
+                        uint32_t v[32];
+                        wide_tmem_ld32(tmem + ((uint32_t)(32 * ew) << 16) + s * 128u + (uint32_t)c * 32u, v);
+                        uint32_t keys[16], bal[16], pm = 0;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int q = 16 * c + j;
-                        if (q >= nq) break;  // (uniform)
-                        const float coarse = (__uint_as_float(v[2 * j]) + __uint_as_float(v[2 * j + 1])) * su;
-                        // the residual term lies in [-256 lambda, 256 lambda]
-                        bool p = live && fmaf(lam, 257.0f, coarse + fabsf(coarse) * 1e-6f) >= thr[q];
-                        float sc = coarse;
-                        uint32_t key = 0;
-                        if (p) {
-                            const uint32_t* qw = qs_w + 8 * q;
-                            const int h = __popc(ra.x ^ qw[0]) + __popc(ra.y ^ qw[1]) + __popc(ra.z ^ qw[2]) + __popc(ra.w ^ qw[3]) +
-                                          __popc(rb2.x ^ qw[4]) + __popc(rb2.y ^ qw[5]) + __popc(rb2.z ^ qw[6]) + __popc(rb2.w ^ qw[7]);
-                            sc = fmaf(lam, (float)(256 - 2 * h), coarse);
-                            key = score_key(sc);
-                            p = key >= pvh[q];
-                        }
-                        const unsigned bal = __ballot_sync(0xFFFFFFFFu, p);
-                        if (bal) {
-                            const uint32_t Q = it.query_begin + (uint32_t)q;
-                            // first candidates of a row without a bucket mapping define one (any monotone mapping is valid)
-                            if (rng[q].y == 0.0f) {
+                        for (int j = 0; j < 16; ++j) {
+                            const int q = 16 * c + j;
+                            bal[j] = 0;
+                            keys[j] = 0;
+                            if (q >= nq) continue;  // (uniform)
+                            const float coarse = (__uint_as_float(v[2 * j]) + __uint_as_float(v[2 * j + 1])) * su;
+                            // the residual term lies in [-256 lambda, 256 lambda]
+                            bool p = live && (count_only || fmaf(lam, 257.0f, coarse + fabsf(coarse) * 1e-6f) >= thr[q]);
+                            float sc = coarse;
+                            if (p) {
+                                const uint32_t* qw = qs_w + 8 * q;
+                                const int h = __popc(ra.x ^ qw[0]) + __popc(ra.y ^ qw[1]) + __popc(ra.z ^ qw[2]) + __popc(ra.w ^ qw[3]) +
+                                              __popc(rb2.x ^ qw[4]) + __popc(rb2.y ^ qw[5]) + __popc(rb2.z ^ qw[6]) + __popc(rb2.w ^ qw[7]);
+                                sc = fmaf(lam, (float)(256 - 2 * h), coarse);
+                                keys[j] = score_key(sc);
+                                p = count_only || keys[j] >= pvh[q];
+                            }
+                            bal[j] = __ballot_sync(0xFFFFFFFFu, p);
+                            if (p) pm |= 1u << j;
+                            if (bal[j] && rng[q].y == 0.0f) {
+                                // first candidates of a row without a bucket mapping define one (any monotone mapping is valid)
+                                const uint32_t Q = it.query_begin + (uint32_t)q;
                                 float mn = p ? sc : INFINITY, mx = p ? sc : -INFINITY;
 #pragma unroll
                                 for (int o = 16; o; o >>= 1) {
@@ -390,24 +399,46 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
                                 }
                                 __syncwarp();
                             }
-                            uint32_t slot0 = 0;
-                            if (lane == 0) slot0 = atomicAdd(a.gcount + Q, (uint32_t)__popc(bal));
-                            slot0 = __shfl_sync(0xFFFFFFFFu, slot0, 0);
-                            if (p) {
-                                const uint32_t at = slot0 + (uint32_t)__popc(bal & ((1u << lane) - 1u));
-                                if (at < a.gcap) a.gbuf[(size_t)Q * a.gcap + at] = ((uint64_t)key << 32) | (uint64_t)nidx;
-                                else a.gflag[Q] = 1u;  // the row's buffer is full: the generic kernel scores the row
-                                const float2 rm = rmap[q];
-                                atomicAdd(a.ghist + (size_t)Q * 256 + min(max(__float2int_rz(fmaf(sc, rm.y, rm.x)), 0), 255), 1u);
+                        }
+                        // slots of the sixteen rows' candidates: lane j reserves for row 16 c + j, one round trip for all
+                        uint32_t slot0 = 0;
+                        if (!count_only) {
+                            uint32_t mine_bal = 0;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (lane == j) mine_bal = bal[j];
+                            if (mine_bal) slot0 = atomicAdd(a.gcount + it.query_begin + 16u * (uint32_t)c + (uint32_t)lane, (uint32_t)__popc(mine_bal));
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (!bal[j]) continue;  // (uniform)
+                            const uint32_t Q = it.query_begin + 16u * (uint32_t)c + (uint32_t)j;
+                            const uint32_t base_j = __shfl_sync(0xFFFFFFFFu, slot0, j);
+                            if (pm >> j & 1u) {
+                                if (!count_only) {
+                                    const uint32_t at = base_j + (uint32_t)__popc(bal[j] & ((1u << lane) - 1u));
+                                    if (at < a.gcap) a.gbuf[(size_t)Q * a.gcap + at] = ((uint64_t)keys[j] << 32) | (uint64_t)nidx;
+                                    else a.gflag[Q] = 1u;  // the row's buffer is full: the generic kernel scores the row
+                                }
+                                if (count_only || b != 0) {  // (the first block was counted by its counting pass)
+                                    const float2 rm = rmap[16 * c + j];
+                                    atomicAdd(a.ghist + (size_t)Q * 256 + min(max(__float2int_rz(fmaf(key_score(keys[j]), rm.y, rm.x)), 0), 255), 1u);
+                                }
                             }
                         }
+                    }
+                    if (count_only) {
+                        // all four scoring warps have counted: thresholds of the item's rows, then the filtering pass
+                        asm volatile("bar.sync 2, 128;\n" ::: "memory");
+                        const int rows = min(16, nq - 16 * ew);
+                        if (rows > 0) wide_refresh(a, it.query_begin + 16u * (uint32_t)ew, rows, rng + 16 * ew, pvh + 16 * ew, thr + 16 * ew, lane);
+                        asm volatile("bar.sync 2, 128;\n" ::: "memory");
                     }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
                 mbar_arrive(bars_s + 32 + 8 * s);
-                // thresholds: after the first block (every CTA of the grid has appended one unfiltered block by
-                // then) and every second block after it; warp ew looks after rows 16 ew .. 16 ew + 15
-                if ((b & 1u) == 0u) {
+                // thresholds again after every second block; warp ew looks after rows 16 ew .. 16 ew + 15
+                if ((b & 1u) == 1u) {
                     __syncwarp();
                     const int rows = min(16, nq - 16 * ew);
                     if (rows > 0) wide_refresh(a, it.query_begin + 16u * (uint32_t)ew, rows, rng + 16 * ew, pvh + 16 * ew, thr + 16 * ew, lane);

@@ -246,3 +246,27 @@ def test_attend_topk_is_softmax_then_sequential_weighted_sum():
     sc = np.array([[0.0, 0.0, 5.0]], np.float32)
     out, w = ora.attend_topk(idx, sc, 1.0, v)
     assert np.allclose(w, [[0.5, 0.5, 0.0]]) and np.allclose(out, [[2.5, 2.0]])
+
+
+def test_eventlog_layout_matches_the_documented_format():
+    # scirust/src/eventlog.rs:9-24: 16-byte header, 144-byte records, FNV-1a (offset basis 0x811C9DC5, prime 0x01000193)
+    tile = np.zeros(1, ora.TILE_DTYPE)
+    tile["token_id"] = 77
+    data = ora.eventlog_bytes([(5, 9, tile), (6, 2, tile)])
+    assert len(data) == 16 + 2 * 144
+    assert data[:16] == bytes.fromhex("474c4c53" "02000000" "80000000" "00000000")
+    assert data[16:28] == (5).to_bytes(8, "little") + (9).to_bytes(4, "little")
+    h = 0x811C9DC5
+    for b in data[16:28] + data[32:160]:
+        h = ((h ^ b) * 0x01000193) & 0xFFFFFFFF
+    assert int.from_bytes(data[28:32], "little") == h
+    version, recs = ora.eventlog_parse(data)
+    assert version == 2 and [(r[0], r[1]) for r in recs] == [(5, 9), (6, 2)]
+    assert recs[0][2].tobytes() == tile.tobytes()
+    # version 1 carries zero in place of the checksum and stays readable
+    v1 = ora.eventlog_bytes([(5, 9, tile)], version=1)
+    assert v1[28:32] == b"\0\0\0\0" and ora.eventlog_parse(v1)[0] == 1
+    for bad in (data[:10], b"XXXX" + data[4:], data[:4] + (3).to_bytes(4, "little") + data[8:], data + b"\1" * 7,
+                data[:40] + bytes([data[40] ^ 1]) + data[41:]):
+        with pytest.raises(ValueError):
+            ora.eventlog_parse(bad)
