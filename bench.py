@@ -588,40 +588,75 @@ def run_pool_workload(args, S, torch, dev):
     pool = S.TilePool(cap, budget, S.PAGE_LOWEST_IMPACT_FIRST, S.EVICT_IMPORTANCE, sink_window=4, recent_window=2048)
     gen = torch.Generator(device=dev)
     gen.manual_seed(4242)
-    steps = 256
-    fill = cap - 8 * (steps + 16)
+    steps, extra = 256, 64
+    total = 16 + steps + extra
+    fill = cap - 8 * total
     for t0 in range(0, fill, 131072):
         n = min(131072, fill - t0)
         kb = torch.randn(n, d, generator=gen, device=dev).to(torch.bfloat16).contiguous()
         pos = torch.arange(t0, t0 + n, device=dev, dtype=torch.int32) // 8
         torch.cuda.synchronize()
         pool.append_keys(model, kb, S.CODEC_MIXED, n=n, key_dtype=S.BF16, positions=pos)
-    q = torch.randn(steps + 16, 4, d, generator=gen, device=dev)
-    qc, qs = model.prepare_queries(q.reshape(-1, d), nq=4 * (steps + 16))
-    keys = torch.randn(steps + 16, 8, d, generator=gen, device=dev).to(torch.bfloat16).contiguous()
+    q = torch.randn(total, 4, d, generator=gen, device=dev)
+    qc, qs = model.prepare_queries(q.reshape(-1, d), nq=4 * total)
+    keys = torch.randn(total, 8, d, generator=gen, device=dev).to(torch.bfloat16).contiguous()
     torch.cuda.synchronize()
     pool.enforce_budget()
+    parts = {"append_keys": 0.0, "score_topk": 0.0, "observe_query": 0.0, "enforce_budget": 0.0}
 
-    def step(i):
+    def step(i, timed=False):
         pos = np.full(8, fill // 8 + i, np.uint32)
-        pool.append_keys(model, keys[i], S.CODEC_MIXED, n=8, key_dtype=S.BF16, positions=pos)
-        pool.score_topk(qc[4 * i:4 * i + 4], qs[4 * i:4 * i + 4], 4, 64)
-        pool.observe_query(qc[4 * i], qs[4 * i], 1.0)
-        pool.enforce_budget()
+        calls = (("append_keys", lambda: pool.append_keys(model, keys[i], S.CODEC_MIXED, n=8, key_dtype=S.BF16, positions=pos)),
+                 ("score_topk", lambda: pool.score_topk(qc[4 * i:4 * i + 4], qs[4 * i:4 * i + 4], 4, 64)),
+                 ("observe_query", lambda: pool.observe_query(qc[4 * i], qs[4 * i], 1.0)),
+                 ("enforce_budget", lambda: pool.enforce_budget()))
+        for name, call in calls:
+            if timed:
+                S.synchronize()
+                t = time.perf_counter()
+            call()
+            if timed:
+                S.synchronize()
+                parts[name] += 1e3 * (time.perf_counter() - t) / extra
 
     for i in range(16):
         step(i)
     S.synchronize()
+    l0 = S.launch_count()
     t0 = time.perf_counter()
     for i in range(16, 16 + steps):
         step(i)
     S.synchronize()
     ms = 1e3 * (time.perf_counter() - t0) / steps
+    launches = (S.launch_count() - l0) / steps
+    for i in range(16 + steps, total):  # each call alone, a synchronize on both sides: where the step's time goes
+        step(i, timed=True)
     st = pool.stats()
     return {"workload": "config4 elastic pool: 1048576 slots, mixed 8/4, budget 60 %, H2O sink 4 + recent 2048; "
                         "step = append 8 keys + score 4 queries top-64 + observe + enforce_budget",
-            "ms_per_step": ms, "steps": steps, "hot": st["hot"], "warm": st["warm"], "cold": st["cold"],
+            "ms_per_step": ms, "steps": steps, "launches_per_step": launches, "calls_alone_ms": {k: round(v, 4) for k, v in parts.items()},
+            "hot": st["hot"], "warm": st["warm"], "cold": st["cold"],
             "live_bytes": st["live_bytes"], "budget": budget, "within_budget": bool(st["live_bytes"] <= budget)}
+
+
+def pool_arm(args):
+    """--workload c4 on its own: the elastic pool's decode step (one GPU; the pool does not shard)."""
+    import torch
+
+    import slhav2_b200 as S
+
+    if not torch.cuda.is_available() or S.device_count() == 0:
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    torch.cuda.set_device(0)
+    S.set_device(0)
+    r = run_pool_workload(args, S, torch, torch.device("cuda", 0))
+    line = {"metric": "ccos_pool_decode_steps_per_s", "value": 1e3 / r["ms_per_step"], "unit": "steps/s", "n_gpus": 1,
+            "steps": r["steps"], "warmup": 16, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "replicas only",
+            "vs_baseline": None, "dtype": "u8/f32", "data": "synthetic", "config": {"workload": r["workload"]}, "pool": r,
+            "gpu_launches": int(r["launches_per_step"] * r["steps"])}
+    print(json.dumps(line))
 
 
 def gpu_arm(args, w):
@@ -679,11 +714,16 @@ def main():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["c4"])
     ap.add_argument("--no-also", dest="also", action="store_false", help="only the named workload (no c1..c4 sub-records)")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: shrink the workload to this many layers")
     ap.add_argument("--tokens", type=int, default=0, help="profiling aid: shrink the workload to this many tokens")
     args = ap.parse_args()
+    if args.workload == "c4":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the pool workload has no CPU reference arm; the headline workload is c5"}))
+            return
+        return pool_arm(args)
     w = dict(WORKLOADS[args.workload])
     if args.layers:
         w["layers"] = args.layers

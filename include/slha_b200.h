@@ -189,8 +189,10 @@ uint64_t slha_b200_launch_count(void);
 /* Checking aid, no counterpart in the reference: with on != 0 the calling
  * thread's slha_b200_score_topk / slha_b200_pool_score_topk calls use only the
  * generic CUDA-core scoring kernel (every codec) and never the tensor-core
- * kernel, so that a test can require both to give the same answers.  The
- * library reads no environment variable; this call is the only switch. */
+ * kernel, so that a test can require both to give the same answers; the same
+ * thread's slha_b200_pool_enforce_budget calls run their phases one by one
+ * from the host instead of in the single cooperative launch.  The library
+ * reads no environment variable; this call is the only switch. */
 int32_t slha_b200_debug_force_generic_score(int32_t on);
 /* Counters of the calling thread's latest fused score + top-k call that ran on the
  * tensor-core kernel (no counterpart in the reference; the stats getter planned

@@ -111,6 +111,7 @@ Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Se
                           const float* d_q_coarse, const uint64_t* d_q_sign, size_t n_queries, uint32_t k,
                           uint32_t* d_out_index, float* d_out_score, uint32_t* d_out_count);
 void debug_force_generic_score(bool on);  // calling thread only
+bool debug_general_paths();                // the calling thread's switch (also: host-driven enforce_budget phases)
 Status last_score_stats(Ctx* c, uint64_t* out4);
 bool timing_active();  // the calling thread records kernel events (slha_b200_timing_begin)
 Status timing_begin(uint32_t max_calls);

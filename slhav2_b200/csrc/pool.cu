@@ -9,6 +9,9 @@
 // (cub::DeviceRadixSort on a unique 64-bit key), prefix-sums the bytes each
 // candidate would free, and applies the operation to exactly the prefix the
 // reference's sequential loop would have reached.
+#include <cooperative_groups.h>
+#include <cub/block/block_radix_sort.cuh>
+#include <cub/block/block_scan.cuh>
 #include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_scan.cuh>
 #include <vector>
@@ -130,6 +133,34 @@ __device__ __forceinline__ bool is_pinned(const PoolDev& p, uint32_t pos, uint32
     return p.recent_window && (max_pos - pos) < p.recent_window;
 }
 
+// the sort key of slot s in `phase`, or SENTINEL when the phase cannot act on it
+__device__ __forceinline__ uint64_t phase_key(const PoolDev& p, int phase, uint64_t s, uint32_t max_pos) {
+    const uint8_t st = p.state[s];
+    if (st == ST_COLD) return SENTINEL;
+    const unsigned char* t = p.tiles + s * TILE_BYTES;
+    const uint32_t flags = *reinterpret_cast<const uint16_t*>(t + 118);
+    bool cand = false;
+    if (phase == PH_CORR_HOT) cand = st == ST_HOT && corr_bytes(flags) && !(flags & F_NOCORR);
+    else if (phase == PH_PAGE) cand = st == ST_HOT;
+    else if (phase == PH_CORR_WARM) cand = st == ST_WARM && corr_bytes(flags) && !(flags & F_NOCORR);
+    else {
+        const bool pin = p.evict_policy == SLHA_B200_EVICT_IMPORTANCE &&
+                         is_pinned(p, *reinterpret_cast<const uint32_t*>(t + 112), max_pos);
+        cand = (phase == PH_EVICT_PINNED) == pin;
+    }
+    if (!cand) return SENTINEL;
+    const uint32_t seq32 = (uint32_t)p.seq[s];
+    if (phase <= PH_CORR_WARM) {
+        // slots_in_paging_order, ccos.rs:526-539: stable sort of the
+        // slot-ascending list by sigma (total order) or by seq
+        return p.page_policy == SLHA_B200_PAGE_LOWEST_IMPACT_FIRST
+                   ? ((uint64_t)f32_total_key(*reinterpret_cast<const float*>(t + 104)) << 32) | (uint32_t)s
+                   : (uint64_t)seq32;
+    }
+    // ccos.rs:586-603: causal = by seq; importance = (importance, seq)
+    return p.evict_policy == SLHA_B200_EVICT_CAUSAL ? (uint64_t)seq32 : ((uint64_t)f32_total_key(p.importance[s]) << 32) | seq32;
+}
+
 // candidate (key, slot) pairs of one phase, compacted in arbitrary order (keys are unique, so the
 // sort that follows gives one order): only the slots a phase can act on are sorted, e.g. the few
 // HOT tiles just appended for the page-out phase.  n_cand is zero when the kernel starts.
@@ -146,35 +177,7 @@ __global__ void phase_build_kernel(PoolDev p, int phase, uint64_t* keys, uint32_
     for (uint64_t r = 0; r < rounds; ++r) {
         const uint64_t s = r * stride + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
         uint64_t key = SENTINEL;
-        if (s < len) {
-            const uint8_t st = p.state[s];
-            const unsigned char* t = p.tiles + s * TILE_BYTES;
-            const uint32_t flags = *reinterpret_cast<const uint16_t*>(t + 118);
-            bool cand = false;
-            if (phase == PH_CORR_HOT) cand = st == ST_HOT && corr_bytes(flags) && !(flags & F_NOCORR);
-            else if (phase == PH_PAGE) cand = st == ST_HOT;
-            else if (phase == PH_CORR_WARM) cand = st == ST_WARM && corr_bytes(flags) && !(flags & F_NOCORR);
-            else if (st != ST_COLD) {
-                const bool pin = p.evict_policy == SLHA_B200_EVICT_IMPORTANCE &&
-                                 is_pinned(p, *reinterpret_cast<const uint32_t*>(t + 112), max_pos);
-                cand = (phase == PH_EVICT_PINNED) == pin;
-            }
-            if (cand) {
-                const uint32_t seq32 = (uint32_t)p.seq[s];
-                if (phase <= PH_CORR_WARM) {
-                    // slots_in_paging_order, ccos.rs:526-539: stable sort of the
-                    // slot-ascending list by sigma (total order) or by seq
-                    key = p.page_policy == SLHA_B200_PAGE_LOWEST_IMPACT_FIRST
-                              ? ((uint64_t)f32_total_key(*reinterpret_cast<const float*>(t + 104)) << 32) | (uint32_t)s
-                              : (uint64_t)seq32;
-                } else {
-                    // ccos.rs:586-603: causal = by seq; importance = (importance, seq)
-                    key = p.evict_policy == SLHA_B200_EVICT_CAUSAL
-                              ? (uint64_t)seq32
-                              : ((uint64_t)f32_total_key(p.importance[s]) << 32) | seq32;
-                }
-            }
-        }
+        if (s < len) key = phase_key(p, phase, s, max_pos);
         const unsigned hit = __ballot_sync(0xFFFFFFFFu, key != SENTINEL);
         if (hit) {
             const int lane = threadIdx.x & 31;
@@ -300,6 +303,253 @@ __global__ void phase_commit_kernel(PoolDev p) {
     p.cnt->live_delta = 0;
     p.cnt->free_len += p.cnt->phase_applied;
     p.cnt->phase_applied = 0;
+}
+
+// ---- enforce_budget in one cooperative launch --------------------------------------
+// The host-driven phases above need the candidate count (for the sort) and the prefilter cut on the
+// host, one stream round trip each.  When no event log is attached nothing of a phase needs the
+// host: this kernel runs every phase with grid-wide barriers in between.  Per phase
+//   build    candidates (key, slot) compacted as above, with the smallest and largest key;
+//   select   when there are more than EB_CAP candidates, a radix select (12 key bits per level,
+//            starting at the highest bit in which the keys differ) finds a key bound below which at
+//            least `reach` = deficit / min_freed + 1 and at most EB_CAP candidates lie -- no more
+//            than `reach` can be reached before the deficit is covered;
+//   finish   one block sorts those (cub::BlockRadixSort), prefix-sums the bytes each would free and
+//            applies the operation to exactly the prefix the reference's loop reaches.
+// A phase the select cannot bound (a deficit worth more than EB_CAP operations) raises `overflow`
+// and ends the kernel; the phases already finished are complete, and the host-driven path then
+// continues from the state they left (a finished phase has no candidates left or met the budget).
+constexpr int EB_THREADS = 512, EB_ITEMS = 8, EB_CAP = EB_THREADS * EB_ITEMS, EB_LEVELS = 6, EB_BINS = 4096;
+struct EnforceState {
+    unsigned long long inv_min_key, max_key;  // ~min and max over the phase's candidates (zero = none yet)
+    uint32_t n_keep, overflow, pad[2];
+    uint32_t hist[5][EB_LEVELS][EB_BINS];
+};
+
+__global__ void __launch_bounds__(EB_THREADS) enforce_kernel(PoolDev p, uint32_t phase_mask, uint64_t* keys, uint32_t* vals,
+                                                             uint64_t* skeys, uint32_t* svals, EnforceState* es) {
+    namespace cg = cooperative_groups;
+    cg::grid_group grid = cg::this_grid();
+    using Sort = cub::BlockRadixSort<uint64_t, EB_THREADS, EB_ITEMS, uint32_t>;
+    using Scan64 = cub::BlockScan<uint64_t, EB_THREADS>;
+    using Scan32 = cub::BlockScan<uint32_t, EB_THREADS>;
+    __shared__ union {
+        typename Sort::TempStorage sort;
+        typename Scan64::TempStorage scan64;
+        typename Scan32::TempStorage scan32;
+        uint32_t hist[EB_BINS];
+    } sm;
+    __shared__ uint32_t cut_bin, cut_hist;
+    __shared__ unsigned long long cut_cum, fin_applied;
+    __shared__ long long fin_delta;
+    volatile PoolCounters* cnt = p.cnt;
+    const uint64_t len = cnt->len;
+    const uint64_t gtid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (uint64_t)gridDim.x * blockDim.x;
+    const int lane = threadIdx.x & 31;
+    if (cnt->live <= cnt->budget) return;  // (nothing has been written yet: every block sees the same)
+    if (p.recent_window) {
+        uint32_t m = 0;
+        for (uint64_t s = gtid; s < len; s += stride)
+            if (p.state[s] != ST_COLD) m = max(m, *reinterpret_cast<const uint32_t*>(p.tiles + s * TILE_BYTES + 112));
+        for (int o = 16; o; o >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        if (lane == 0 && m) atomicMax(&p.cnt->max_pos, m);
+        grid.sync();
+    }
+    const uint32_t max_pos = cnt->max_pos;
+    for (int phase = 0; phase < 5; ++phase) {
+        if (!((phase_mask >> phase) & 1u)) continue;
+        const uint64_t live = cnt->live, budget = cnt->budget;
+        if (live <= budget) break;
+        const uint64_t deficit = live - budget;
+        // ---- build
+        {
+            uint64_t kmin = SENTINEL, kmax = 0;
+            const uint64_t rounds = (len + stride - 1) / stride;
+            for (uint64_t r = 0; r < rounds; ++r) {
+                const uint64_t s = r * stride + gtid;
+                uint64_t key = SENTINEL;
+                if (s < len) key = phase_key(p, phase, s, max_pos);
+                const unsigned hit = __ballot_sync(0xFFFFFFFFu, key != SENTINEL);
+                if (hit) {
+                    uint32_t base = 0;
+                    if (lane == 0) base = atomicAdd(&p.cnt->n_cand, (uint32_t)__popc(hit));
+                    base = __shfl_sync(0xFFFFFFFFu, base, 0);
+                    if (key != SENTINEL) {
+                        const uint32_t i = base + (uint32_t)__popc(hit & ((1u << lane) - 1u));
+                        keys[i] = key;
+                        vals[i] = (uint32_t)s;
+                        kmin = min(kmin, key);
+                        kmax = max(kmax, key);
+                    }
+                }
+            }
+            for (int o = 16; o; o >>= 1) {
+                kmin = min(kmin, __shfl_xor_sync(0xFFFFFFFFu, kmin, o));
+                kmax = max(kmax, __shfl_xor_sync(0xFFFFFFFFu, kmax, o));
+            }
+            if (lane == 0 && kmin != SENTINEL) {
+                atomicMax(&es->inv_min_key, ~kmin);
+                atomicMax(&es->max_key, kmax);
+            }
+        }
+        grid.sync();
+        const uint64_t nc = cnt->n_cand;
+        if (nc) {
+            const uint64_t min_freed = phase == PH_PAGE ? 32 : (phase >= PH_EVICT ? 80 : 14);
+            const uint64_t reach = deficit / min_freed + 1;
+            const bool take_all = nc <= (uint64_t)EB_CAP;
+            uint64_t base = ~*(volatile unsigned long long*)&es->inv_min_key, thr_rel = ~0ull, below = 0;
+            bool bounded = take_all;
+            if (!take_all && reach <= (uint64_t)EB_CAP) {
+                const uint64_t span = *(volatile unsigned long long*)&es->max_key - base;
+                int shift = max(0, 64 - __clzll((long long)span) - 12);
+                for (int level = 0; level < EB_LEVELS && !bounded; ++level) {
+                    uint32_t* ghist = es->hist[phase][level];
+                    for (uint32_t b = threadIdx.x; b < EB_BINS; b += EB_THREADS) sm.hist[b] = 0;
+                    __syncthreads();
+                    for (uint64_t i = gtid; i < nc; i += stride) {
+                        const uint64_t k = keys[i];
+                        if (k >= base && ((k - base) >> shift) < (uint64_t)EB_BINS) atomicAdd(&sm.hist[(uint32_t)((k - base) >> shift)], 1u);
+                    }
+                    __syncthreads();
+                    for (uint32_t b = threadIdx.x; b < EB_BINS; b += EB_THREADS)
+                        if (sm.hist[b]) atomicAdd(&ghist[b], sm.hist[b]);
+                    grid.sync();
+                    // every block finds the cut itself: the first bin at which `below` + the running count reaches `reach`
+                    uint32_t h[EB_ITEMS], mine = 0;
+                    for (int j = 0; j < EB_ITEMS; ++j) {
+                        h[j] = *(volatile uint32_t*)&ghist[threadIdx.x * EB_ITEMS + j];
+                        mine += h[j];
+                    }
+                    if (threadIdx.x == 0) cut_bin = 0xFFFFFFFFu;
+                    __syncthreads();
+                    uint32_t before;
+                    Scan32(sm.scan32).ExclusiveSum(mine, before);
+                    uint64_t cum = below + before;
+                    if (cum < reach && cum + mine >= reach) {
+                        for (int j = 0; j < EB_ITEMS; ++j) {
+                            cum += h[j];
+                            if (cum >= reach) {
+                                cut_bin = threadIdx.x * EB_ITEMS + j;
+                                cut_hist = h[j];
+                                cut_cum = cum;
+                                break;
+                            }
+                        }
+                    }
+                    __syncthreads();
+                    const uint32_t b = cut_bin;
+                    const uint64_t kept = cut_cum;
+                    const uint32_t hb = cut_hist;
+                    __syncthreads();
+                    if (b == 0xFFFFFFFFu) break;  // fewer candidates than `reach`: all of them are needed, and they do not fit
+                    if (kept <= (uint64_t)EB_CAP) {
+                        thr_rel = (((uint64_t)b + 1) << shift) - 1;
+                        bounded = true;
+                    } else if (shift == 0) {
+                        break;  // equal keys beyond the block sort's capacity
+                    } else {
+                        below = kept - hb;
+                        base += (uint64_t)b << shift;
+                        shift = max(0, shift - 12);
+                    }
+                }
+            }
+            if (!bounded) {
+                if (gtid == 0) es->overflow = 1;
+                return;  // every block takes this branch
+            }
+            if (!take_all) {
+                const uint64_t rounds = (nc + stride - 1) / stride;
+                for (uint64_t r = 0; r < rounds; ++r) {
+                    const uint64_t i = r * stride + gtid;
+                    uint64_t k = 0;
+                    bool keep = false;
+                    if (i < nc) {
+                        k = keys[i];
+                        keep = k < base || (k - base) <= thr_rel;
+                    }
+                    const unsigned hit = __ballot_sync(0xFFFFFFFFu, keep);
+                    if (hit) {
+                        uint32_t o = 0;
+                        if (lane == 0) o = atomicAdd(&es->n_keep, (uint32_t)__popc(hit));
+                        o = __shfl_sync(0xFFFFFFFFu, o, 0) + (uint32_t)__popc(hit & ((1u << lane) - 1u));
+                        if (keep && o < (uint32_t)EB_CAP) {
+                            skeys[o] = k;
+                            svals[o] = vals[i];
+                        }
+                    }
+                }
+                grid.sync();
+            }
+            // ---- finish (block 0)
+            if (blockIdx.x == 0) {
+                const uint64_t* ks = take_all ? keys : skeys;
+                const uint32_t* vs = take_all ? vals : svals;
+                const uint32_t n = take_all ? (uint32_t)nc : min(*(volatile uint32_t*)&es->n_keep, (uint32_t)EB_CAP);
+                uint64_t k[EB_ITEMS];
+                uint32_t v[EB_ITEMS];
+                for (int j = 0; j < EB_ITEMS; ++j) {
+                    const uint32_t i = threadIdx.x * EB_ITEMS + j;
+                    k[j] = i < n ? ks[i] : SENTINEL;
+                    v[j] = i < n ? vs[i] : 0u;
+                }
+                if (threadIdx.x == 0) {
+                    fin_applied = 0;
+                    fin_delta = 0;
+                }
+                __syncthreads();
+                Sort(sm.sort).Sort(k, v);
+                __syncthreads();
+                uint64_t w[EB_ITEMS], excl[EB_ITEMS];
+                for (int j = 0; j < EB_ITEMS; ++j) {
+                    uint32_t bytes = 0;
+                    if (k[j] != SENTINEL) {
+                        const uint32_t flags = tile_flags(p.tiles, v[j]);
+                        if (phase == PH_PAGE) bytes = 32;
+                        else if (phase <= PH_CORR_WARM) bytes = corr_bytes(flags);
+                        else bytes = live_bytes_of(p.state[v[j]], flags);
+                    }
+                    w[j] = bytes;
+                }
+                Scan64(sm.scan64).ExclusiveSum(w, excl);
+                const uint64_t free0 = cnt->free_len;
+                int64_t delta = 0;
+                uint32_t applied = 0;
+                for (int j = 0; j < EB_ITEMS; ++j) {
+                    if (k[j] == SENTINEL || excl[j] >= deficit) continue;
+                    const uint32_t s = v[j];
+                    if (phase == PH_PAGE) do_page_out(p, s, &delta);
+                    else if (phase <= PH_CORR_WARM) do_drop_correction(p, s, &delta);
+                    else {
+                        delta -= (int64_t)w[j];
+                        p.state[s] = ST_COLD;
+                        p.free_list[free0 + threadIdx.x * EB_ITEMS + j] = s;  // applied items are a prefix of the sorted order
+                        ++applied;
+                    }
+                }
+                for (int o = 16; o; o >>= 1) {
+                    delta += __shfl_xor_sync(0xFFFFFFFFu, delta, o);
+                    applied += __shfl_xor_sync(0xFFFFFFFFu, applied, o);
+                }
+                if (lane == 0) {
+                    if (delta) atomicAdd((unsigned long long*)&fin_delta, (unsigned long long)delta);
+                    if (applied) atomicAdd(&fin_applied, (unsigned long long)applied);
+                }
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    cnt->live = (uint64_t)((int64_t)live + fin_delta);
+                    cnt->free_len = free0 + fin_applied;
+                    cnt->n_cand = 0;
+                    es->inv_min_key = 0;
+                    es->max_key = 0;
+                    es->n_keep = 0;
+                    __threadfence();
+                }
+            }
+        }
+        grid.sync();
+    }
 }
 
 // ---- observe_scores (ccos.rs:275-314) -----------------------------------------
@@ -551,7 +801,58 @@ Status pool_single_op(Ctx* c, Pool* pl, int op, uint32_t slot, int32_t* result) 
     return pool_sync_counters(c, pl);
 }
 
+// One cooperative launch for all phases, one read-back of the counters.  Sets *done when the
+// budget question is settled; leaves it clear when a phase needs the host-driven path.
+static Status pool_enforce_budget_fused(Ctx* c, Pool* pl, int32_t* within, bool* done) {
+    *done = false;
+    static int blocks_per_sm[64] = {0}, sms[64] = {0};
+    const int dev = pl->device & 63;
+    if (!blocks_per_sm[dev]) {
+        int coop = 0, n = 0, b = 0;
+        SLHA_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, pl->device));
+        SLHA_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, pl->device));
+        SLHA_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, enforce_kernel, EB_THREADS, 0));
+        sms[dev] = n;
+        blocks_per_sm[dev] = coop && b > 0 ? std::min(b, 2) : -1;
+    }
+    if (blocks_per_sm[dev] < 0) return Status();
+    const uint64_t len = pl->h_cnt.len;  // (the host mirror of len is exact: only inserts move it)
+    if (len == 0) return Status();
+    Scratch sc{c};
+    SLHA_TRY(sc.reserve(pad256(len * 8) + pad256(len * 4) + pad256(EB_CAP * 8) + pad256(EB_CAP * 4) + pad256(sizeof(EnforceState)) + 4096));
+    uint64_t* keys = sc.take<uint64_t>(len);
+    uint32_t* vals = sc.take<uint32_t>(len);
+    uint64_t* skeys = sc.take<uint64_t>(EB_CAP);
+    uint32_t* svals = sc.take<uint32_t>(EB_CAP);
+    EnforceState* es = sc.take<EnforceState>(1);
+    uint32_t mask = 0x1Fu;
+    if (pl->cfg.evict_policy != SLHA_B200_EVICT_IMPORTANCE) mask &= ~(1u << PH_EVICT_PINNED);
+    const uint32_t cm = pl->codec_mask;
+    if (cm && !(cm & 0x80000000u) && !(cm & ((1u << SLHA_CODEC_TQ3) | (1u << SLHA_CODEC_MIX3))))
+        mask &= ~((1u << PH_CORR_HOT) | (1u << PH_CORR_WARM));  // no tile with a correction plane can be in the pool
+    SLHA_CUDA(cudaMemsetAsync(es, 0, sizeof(EnforceState), c->stream));
+    SLHA_CUDA(cudaMemsetAsync(&pl->dev.cnt->max_pos, 0, 8, c->stream));  // max_pos and n_cand
+    PoolDev d = pl->dev;
+    void* args[] = {&d, &mask, &keys, &vals, &skeys, &svals, &es};
+    const uint64_t want = (len + EB_THREADS - 1) / EB_THREADS;
+    const unsigned grid = (unsigned)std::max<uint64_t>(1, std::min<uint64_t>(want, (uint64_t)sms[dev] * blocks_per_sm[dev]));
+    SLHA_CUDA(cudaLaunchCooperativeKernel((const void*)enforce_kernel, dim3(grid), dim3(EB_THREADS), args, 0, c->stream));
+    count_launch();
+    uint32_t overflow = 0;
+    SLHA_CUDA(cudaMemcpyAsync(&overflow, &es->overflow, 4, cudaMemcpyDeviceToHost, c->stream));
+    SLHA_TRY(pool_sync_counters(c, pl));
+    if (overflow) return Status();
+    *within = pl->h_cnt.live <= pl->h_cnt.budget ? 1 : 0;
+    *done = true;
+    return Status();
+}
+
 Status pool_enforce_budget(Ctx* c, Pool* pl, int32_t* within) {
+    if (!pl->log && !pl->require_durable && !debug_general_paths()) {
+        bool done = false;
+        SLHA_TRY(pool_enforce_budget_fused(c, pl, within, &done));
+        if (done) return Status();
+    }
     SLHA_TRY(pool_sync_counters(c, pl));
     PoolCounters& h = pl->h_cnt;
     if (h.live <= h.budget) {

@@ -617,6 +617,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
 }
 
 void debug_force_generic_score(bool on) { g_force_generic = on; }
+bool debug_general_paths() { return g_force_generic; }
 
 // Counters of the calling thread's latest score_topk call that used the tensor-core kernel.
 Status last_score_stats(Ctx* c, uint64_t* out4) {

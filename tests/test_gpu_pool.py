@@ -45,8 +45,9 @@ def test_insert_page_drop_evict_and_lifo_reuse():
     assert_same(pool, cache)
 
 
+@pytest.mark.parametrize("host_phases", [False, True], indirect=True)
 @pytest.mark.parametrize("trial", range(24))
-def test_randomised_enforce_budget_matches_oracle(trial):
+def test_randomised_enforce_budget_matches_oracle(trial, host_phases):
     # construction of scirust/tests/ccos.rs:36-76 with codecs and policies varied
     rng = ora.Rng(1000 + trial)
     n = 1 + rng.next_u64() % 200
@@ -141,16 +142,27 @@ def test_append_keys_encodes_into_the_pool():
     assert e.value.code == S.ERR_CAPACITY
 
 
-@pytest.mark.parametrize("codec,page", [(4, 0), (3, 1)])
-def test_large_pool_enforce_budget_with_long_candidate_lists(codec, page):
+@pytest.fixture
+def host_phases(request):
+    """With the parameter set, enforce_budget runs its phases one by one from the host (the path an attached
+    event log or an unbounded phase takes) instead of in the single cooperative launch."""
+    if request.param:
+        S.debug_force_generic_score(True)
+    yield request.param
+    S.debug_force_generic_score(False)
+
+
+@pytest.mark.parametrize("host_phases", [False, True], indirect=True)
+@pytest.mark.parametrize("codec,page,evict", [(4, 0, 1), (3, 1, 1), (1, 1, 0)])
+def test_large_pool_enforce_budget_with_long_candidate_lists(codec, page, evict, host_phases):
     # phases with tens of thousands of candidates: the pool compacts them and sorts only those that can
     # be reached before the deficit is covered; states, free-list order (slot reuse) and byte accounting
     # must still equal the oracle's full ordered walk.  First a large deficit (everything is paged, many
     # tiles evicted), then small deficits after a few more inserts (a handful of operations per phase).
     n = 90000
     budget = int(0.6 * 128 * n)
-    pool = S.TilePool(n + 512, budget, page, S.EVICT_IMPORTANCE, 4, 64)
-    cache = ora.Cache(budget, page, 1, 4, 64)
+    pool = S.TilePool(n + 512, budget, page, evict, 4 * evict, 64 * evict)
+    cache = ora.Cache(budget, page, evict, 4 * evict, 64 * evict)
     tiles = H.random_tiles(n + 256, codec, seed=77 + codec)
     tiles["position"] = np.arange(n + 256)
     for b in range(0, n, 30000):
