@@ -618,3 +618,12 @@ Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Se
 }
 
 }  // namespace slha
+
+#ifdef SLHA_STREAM_PROBE
+extern "C" int slha_debug_stream_probe(unsigned long long* out) {  // development build only
+    return (int)cudaMemcpyFromSymbol(out, slha::g_stream_probe, sizeof(unsigned long long) * 160 * 8);
+}
+extern "C" int slha_debug_wide_probe(unsigned long long* out) {  // development build only
+    return (int)cudaMemcpyFromSymbol(out, slha::g_wide_probe, sizeof(unsigned long long) * 160 * 24);
+}
+#endif

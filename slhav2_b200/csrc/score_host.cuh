@@ -145,7 +145,7 @@ struct Plan {
     uint64_t last_use = 0;
 };
 
-size_t wide_smem_bytes() { return 3 * WIDE_A_BYTES + 2 * WIDE_RAW_BYTES + 2048 + 256 + 256 + 512 + 512 + 64 + 1024; }
+size_t wide_smem_bytes() { return 3 * WIDE_A_BYTES + 2 * WIDE_RAW_BYTES + 2048 + 256 + 256 + 512 + 512 + 64 + 2048 + 1024; }
 
 Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* segs, size_t n_segs, size_t nq,
                   uint32_t k, int codec_hint, bool allow_wide, Plan** out) {

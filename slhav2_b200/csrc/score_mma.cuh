@@ -43,6 +43,22 @@ constexpr int MMA_BQ_BYTES = 9 * 32 * 8;                   // B fragments of a w
 constexpr int NF4_LUT_BYTES = 256 * 16 * 8;                // [byte][16 lanes] x (hi pair, lo pair)
 constexpr int SEL_HIST_INTS = 4 * 256 + 48;                // block_select_multi: 4 histograms + state
 
+#ifdef SLHA_STREAM_PROBE
+// development build only: per-CTA timeline of score_stream_kernel (nanoseconds of %globaltimer)
+__device__ unsigned long long g_stream_probe[160][8];
+__device__ __forceinline__ unsigned long long probe_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
+#define PROBE_SET(i) do { if (threadIdx.x == 0) g_stream_probe[blockIdx.x][i] = probe_now(); } while (0)
+#define PROBE_MAX(i) do { if ((threadIdx.x & 31) == 0) atomicMax(&g_stream_probe[blockIdx.x][i], probe_now()); } while (0)
+#define PROBE_MIN(i) do { if ((threadIdx.x & 31) == 0) atomicMin(&g_stream_probe[blockIdx.x][i], probe_now()); } while (0)
+#else
+#define PROBE_SET(i)
+#define PROBE_MAX(i)
+#define PROBE_MIN(i)
+#endif
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -653,6 +669,13 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
     // shared layout: nf4 table | stage ring | B fragments | query sign words | thresholds | bucket mappings | flag
     const uint32_t lut_bytes = a.nf4_table ? NF4_LUT_BYTES : 0;  // the table is left out when no NF4 tile is expected
     uint2* lut = reinterpret_cast<uint2*>(smem);
+#ifdef SLHA_STREAM_PROBE
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 8; ++i) g_stream_probe[blockIdx.x][i] = i == 6 ? ~0ull : 0ull;
+        g_stream_probe[blockIdx.x][0] = probe_now();
+    }
+    __syncthreads();
+#endif
     unsigned char* tail = smem + lut_bytes + (size_t)nwarps * MMA_DEPTH * MMA_SET_STRIDE;
     uint2* bq_w = reinterpret_cast<uint2*>(tail);                        // [9][32]
     uint32_t* qs_w = reinterpret_cast<uint32_t*>(tail + MMA_BQ_BYTES);   // [4][8]
@@ -757,6 +780,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
             if (__any_sync(0xFFFFFFFFu, big) && lane == 0) bail[0] = 1;  // a query too large for the fp16 split
         }
         __syncthreads();
+        PROBE_SET(1);
         const bool too_big = bail[0] != 0;
 
         const uint8_t* sbase = a.state ? a.state + it.tile_begin : nullptr;
@@ -804,9 +828,11 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
                 // Every warp of the CTA (and, started together, of the grid) has appended its first set
                 // unfiltered, so the rows' histograms hold 16 candidates per warp: first thresholds now,
                 // before the second sets are filtered.  (All warps pass here: `rounds` is the same for all.)
+                PROBE_MAX(2);
                 __syncthreads();
                 if (warp < nq) stream_refresh_threshold(a, it.query_begin + (uint32_t)warp, rng[warp], pvh + warp, lane);
                 __syncthreads();
+                PROBE_SET(3);
             }
             if (dead || s >= n_sets) continue;
             issue();
@@ -972,12 +998,15 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
             }
         }
         cp_async_wait<0>();
+        PROBE_MAX(4);
+        PROBE_MIN(6);
         if (mine) {  // the unused rest of the warp's last chunk holds absent keys
             for (uint32_t z = cur + (uint32_t)g; z < end; z += 8u) dst[z] = 0ull;
         }
         __syncthreads();
         // rows this CTA could not score on the tensor cores go to the generic kernel as a whole
         if (bail[0] && tid < nq) a.gflag[it.query_begin + tid] = 1u;
+        PROBE_SET(5);
     }
 }
 

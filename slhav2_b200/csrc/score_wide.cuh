@@ -13,23 +13,38 @@
 // tcgen05.ld.  K = 128 dims (+16 for TQ3 tiles: level = (n - 8) / 2 + c / 4 with the nibble
 // n = 2 code + correction bit, so the score also needs c / 4 sum_g gs_g Q_g, Q_g the query's sum over
 // scale group g; those eight products per tile ride along as one more K step).
-// Warp roles (9 warps): 0-3 stage and dequantise tiles, 4-7 turn accumulators into scores (Hamming
-// term on the CUDA cores, only for tiles whose coarse score can reach the row's threshold), filter
-// and append candidates to the rows' buffers (the streaming top-k state of score_stream_kernel),
-// 8 issues the MMAs.  Every wait on an mbarrier is bounded; a wait that runs out flags the item's rows
-// for the generic kernel and lets the CTA finish (tensor memory is always given back).
+// Warps: sixteen workers and one MMA warp.  The work around the MMA is latency-bound CUDA-core code
+// (dequantisation, 64 Hamming distances per tile), so it is spread over as many warps as the
+// register file allows: every worker stages its share of block b + 1 (one tile row quarter each)
+// while the MMAs of block b run, then turns its share of block b's accumulators into scores --
+// worker w reads TMEM lanes 32 (w & 3) .. + 31 (its 32 tiles) and the 16 queries of column chunk
+// w >> 2 -- adds the Hamming term only where the coarse score can reach the row's threshold, filters
+// and appends candidates to the rows' buffers (the streaming top-k state of score_stream_kernel).
+// Every wait on an mbarrier is bounded; a wait that runs out flags the item's rows for the generic
+// kernel and lets the CTA finish (tensor memory is always given back).
 // Codecs: INT4 / MX-INT4 launches and TQ3 launches; any other tile hands the item's rows back.
 #pragma once
 
 namespace slha {
 namespace {
 
+#ifdef SLHA_STREAM_PROBE
+#define WPROBE_DECL unsigned long long wp_t = probe_now(), wp_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
+#define WPROBE_LAP(i) do { const unsigned long long n_ = probe_now(); wp_acc[i] += n_ - wp_t; wp_t = n_; } while (0)
+#define WPROBE_OUT(base, cnt) do { if ((threadIdx.x & 31) == 0) for (int i_ = 0; i_ < cnt; ++i_) g_wide_probe[blockIdx.x][base + i_] = wp_acc[i_]; } while (0)
+__device__ unsigned long long g_wide_probe[160][24];
+#else
+#define WPROBE_DECL
+#define WPROBE_LAP(i)
+#define WPROBE_OUT(base, cnt)
+#endif
 constexpr int WIDE_M = 128;                         // tiles per block
 constexpr int WIDE_NQ = 64;                         // query rows per work item
 constexpr int WIDE_SLAB = WIDE_M * 128;             // one 64-element K slab of A or B: 128 rows x 128 bytes
 constexpr int WIDE_A_BYTES = 3 * WIDE_SLAB;         // K = 64 + 64 + 16 (third slab: first 32 bytes of every row)
 constexpr int WIDE_RAW_BYTES = WIDE_M * TILE_BYTES; // the block's tiles as they lie in HBM
-constexpr int WIDE_THREADS = 288;
+constexpr int WIDE_WORKERS = 512;                   // threads of the sixteen worker warps
+constexpr int WIDE_THREADS = WIDE_WORKERS + 32;     // + the MMA warp
 constexpr uint32_t WIDE_SPIN = 1u << 22;            // polls of one mbarrier wait before it gives up (~0.2 s)
 
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
@@ -55,6 +70,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
         if (i > 64) __nanosleep(64);
     }
     return false;
+}
+// Named barrier `id` over `nthreads` threads that also tells every one of them whether any brought `fail`: the
+// warps of a role leave their loop together, so that none is left waiting at a later barrier of the role.
+__device__ __forceinline__ bool role_any(uint32_t id, uint32_t nthreads, bool fail) {
+    uint32_t any;
+    asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.or.pred p, %2, %3, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(any) : "r"((uint32_t)fail), "r"(id), "r"(nthreads) : "memory");
+    return any != 0;
 }
 // K-major, 128-byte swizzle, 8-row groups 1024 bytes apart (tcgen05 shared-memory matrix descriptor)
 __device__ __forceinline__ uint64_t wide_desc(uint32_t saddr) {
@@ -85,45 +108,63 @@ __device__ __forceinline__ void wide_tmem_ld32(uint32_t taddr, uint32_t (&v)[32]
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
-// Lane-per-row threshold refresh: lanes 0..15 of the calling warp each walk the histogram of one
-// query row (rows Q0 + lane) from the top until the count reaches k; the proven bound is the lower
-// edge of that bucket minus half a bucket (see stream_refresh_threshold).
-__device__ __forceinline__ void wide_refresh(const ScoreArgs& a, uint32_t Q0, int nrows, const float2* rng, uint32_t* pvh, float* thr, int lane) {
-    if (lane < nrows) {
-        const uint32_t Q = Q0 + (uint32_t)lane;
-        uint32_t best = (uint32_t)(*reinterpret_cast<volatile unsigned long long*>(a.gpivot + Q) >> 32);
-        const float2 r = rng[lane];
-        if (r.y != 0.0f) {
-            const uint4* h4 = reinterpret_cast<const uint4*>(a.ghist + (size_t)Q * 256);
-            uint32_t cum = 0;
-            int found = -1;
-            for (int blk = 63; blk >= 7 && found < 0; blk -= 8) {
-                uint4 c[8];
+// Threshold refresh of NR consecutive query rows by one warp (all loads of the NR histograms in flight
+// together): the lower edge of the highest bucket whose count from the top reaches k, minus half a
+// bucket, is a proven bound (see stream_refresh_threshold).
+template <int NR>
+__device__ __forceinline__ void wide_refresh_rows(const ScoreArgs& a, uint32_t Q0, int nrows, const float2* rng, uint32_t* pvh, float* thr, int lane) {
+    uint32_t c[NR][8];
+    unsigned long long seen = 0ull;
+    if (lane < nrows) seen = *reinterpret_cast<volatile unsigned long long*>(a.gpivot + Q0 + lane);
 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[u].x), "=r"(c[u].y), "=r"(c[u].z), "=r"(c[u].w) : "l"(h4 + (blk - u)));
+    for (int r = 0; r < NR; ++r) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const uint32_t v[4] = {c[u].w, c[u].z, c[u].y, c[u].x};  // buckets 4 (blk - u) + 3 .. + 0
+        for (int j = 0; j < 8; ++j) c[r][j] = 0u;
+        if (r < nrows && rng[r].y != 0.0f) {  // (uniform)
+            const uint32_t* hq = a.ghist + (size_t)(Q0 + r) * 256 + 248 - 8 * lane;  // buckets 255-8l .. 248-8l (descending)
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[r][7]), "=r"(c[r][6]), "=r"(c[r][5]), "=r"(c[r][4]) : "l"(hq));
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(c[r][3]), "=r"(c[r][2]), "=r"(c[r][1]), "=r"(c[r][0]) : "l"(hq + 4));
+        }
+    }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        cum += v[j];
-                        if (found < 0 && cum >= a.k) found = 4 * (blk - u) + 3 - j;
-                    }
+    for (int r = 0; r < NR; ++r) {
+        if (r >= nrows) break;  // (uniform)
+        uint32_t best = (uint32_t)(__shfl_sync(0xFFFFFFFFu, seen, r) >> 32);
+        const float2 rr = rng[r];
+        if (rr.y != 0.0f) {
+            uint32_t tot = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) tot += c[r][j];
+            uint32_t incl = tot;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t y = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += y;
+            }
+            const unsigned ok = __ballot_sync(0xFFFFFFFFu, incl >= a.k);
+            uint32_t ek = 0;
+            if (ok != 0u && lane == __ffs(ok) - 1) {
+                uint32_t run = incl - tot;
+                int b = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (run + c[r][j] >= a.k) { b = 255 - 8 * lane - j; break; }
+                    run += c[r][j];
+                }
+                if (b >= 1) {
+                    const uint32_t e = score_key(rr.x + ((float)b - 0.5f) / rr.y);
+                    ek = e > 8u ? e - 8u : 0u;
                 }
             }
-            if (found >= 1) {
-                const uint32_t e = score_key(r.x + ((float)found - 0.5f) / r.y);
-                const uint32_t ek = e > 8u ? e - 8u : 0u;
-                if (ek > best) {
-                    best = ek;
-                    atomicMax(a.gpivot + Q, (unsigned long long)ek << 32);
-                }
+            ek = __reduce_max_sync(0xFFFFFFFFu, ek);
+            if (ek > best) {
+                best = ek;
+                if (lane == 0) atomicMax(a.gpivot + Q0 + r, (unsigned long long)ek << 32);
             }
         }
-        if (best > pvh[lane]) {
-            pvh[lane] = best;
-            thr[lane] = wide_thr(best);
+        if (lane == 0 && best > pvh[r]) {
+            pvh[r] = best;
+            thr[r] = wide_thr(best);
         }
     }
 }
@@ -143,22 +184,23 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
     float* thr = reinterpret_cast<float*>(pvh + 64);                // [64] the same threshold as a float
     float2* rng = reinterpret_cast<float2*>(thr + 64);              // [64] (smin, inv)
     float2* rmap = rng + 64;                                        // [64] (-smin inv, inv)
-    uint64_t* bars = reinterpret_cast<uint64_t*>(rmap + 64);        // full[2], mma_done[2], epi_done[2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(rmap + 64);        // full[2], mma_done[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);    // [0] TMEM base, [1] error flag, [2] bail
+    float2* colmm = reinterpret_cast<float2*>(bars + 8);            // [4][64] per tile quarter: (min, max) coarse score of a column
     const uint32_t bars_s = base_s + 3 * WIDE_A_BYTES + 2 * WIDE_RAW_BYTES + 2048 + 256 + 256 + 512 + 512;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int MMA_WARP = WIDE_WORKERS / 32;
 
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) {
-            mbar_init(bars_s + 8 * i, 128);      // full: the four staging warps
-            mbar_init(bars_s + 16 + 8 * i, 1);   // mma_done: one tcgen05.commit
-            mbar_init(bars_s + 32 + 8 * i, 128); // epi_done: the four scoring warps
+            mbar_init(bars_s + 8 * i, WIDE_WORKERS);  // full: every worker has staged its share
+            mbar_init(bars_s + 16 + 8 * i, 1);        // mma_done: one tcgen05.commit
         }
         tmem_slot[1] = 0;
         tmem_slot[2] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 8) {  // two accumulators of 128 columns
+    if (warp == MMA_WARP) {  // two accumulators of 128 columns
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(bars_s + 48), "r"(256u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
@@ -168,6 +210,8 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
     const uint32_t tmem = tmem_slot[0];
     uint32_t magic;
     asm volatile("mov.u32 %0, 0x64006400;\n" : "=r"(magic));
+    WPROBE_DECL;
+    WPROBE_LAP(7);
 
     uint32_t nblk = 0;  // blocks this CTA has pushed through the two stages so far (all roles count alike)
     const uint32_t item_end = a.cta_begin[blockIdx.x + 1];
@@ -186,7 +230,7 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
         }
         for (int e = tid; e < WIDE_NQ * 8; e += WIDE_THREADS) qs_w[e] = (e >> 3) < nq ? a.q_sign[(size_t)(it.query_begin + (e >> 3)) * 8 + (e & 7)] : 0u;
         // B: column n = 2 q + part (fp16 hi / lo of query q); k slot 8 i + j holds dim 8 i + {0,4,1,5,2,6,3,7}[j], the order in
-        // which the staging warps produce a tile's values; 16-byte chunk i of a row at chunk (i ^ (row & 7)) of its 128-byte line
+        // which the workers produce a tile's values; 16-byte chunk i of a row at chunk (i ^ (row & 7)) of its 128-byte line
         bool big = false;
         for (int u = tid; u < 128 * 18; u += WIDE_THREADS) {
             const int n = u / 18, i = u % 18, qi = n >> 1;
@@ -219,95 +263,13 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
         }
         if (big) tmem_slot[2] = 1;  // a query too large for the fp16 split
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // B was written with ordinary stores, the MMA reads it through the async proxy
-        __syncthreads();
+        const bool need_map = __syncthreads_or(tid < nq && rng[tid].y == 0.0f) != 0;  // a row of the item has no bucket mapping yet
         const bool too_big = tmem_slot[2] != 0;
         const uint32_t n = it.n_tiles;
+        WPROBE_LAP(0);  // item set-up
         const uint32_t blocks = too_big ? 0u : (n + WIDE_M - 1) / WIDE_M;
 
-        if (warp < 4) {
-            // ---- staging warps: block -> raw[s] (cp.async), then A[s] ----
-            for (uint32_t b = 0; b < blocks; ++b) {
-                const uint32_t g = nblk + b, s = g & 1u, use = g >> 1;
-                if (use > 0 && !mbar_wait(bars_s + 32 + 8 * s, (use - 1) & 1u)) { tmem_slot[1] = 1; break; }
-                const uint32_t t0 = b * WIDE_M;
-                const unsigned char* src = a.tiles + (it.tile_begin + t0) * TILE_BYTES;
-                const uint32_t rs = raw_s + s * WIDE_RAW_BYTES;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t chunk = (uint32_t)i * 128u + (uint32_t)tid, row = chunk >> 3;
-                    const bool in = t0 + row < n;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(rs + chunk * 16u), "l"(in ? src + (size_t)chunk * 16 : a.tiles), "r"(in ? 16 : 0));
-                }
-                cp_async_commit();
-                cp_async_wait<0>();
-                asm volatile("bar.sync 1, 128;\n" ::: "memory");  // the staging warps see each other's copies
-                // thread -> (row, quarter of the latent): 4 x 128 units per block
-                bool foreign = false;
-#pragma unroll 1
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t unit = (uint32_t)i * 128u + (uint32_t)tid, r = unit >> 2, c = unit & 3u;
-                    const uint32_t row_s = rs + r * TILE_BYTES;
-                    const uint32_t flags = lds_u16<118>(row_s);
-                    const bool live = t0 + r < n;
-                    if (live && ((KINDW == 1) ? !(flags & F_TQ3) || (flags & (F_NF4 | F_MIXED | F_MIX3)) : (flags & (F_NF4 | F_MIXED | F_TQ3 | F_MIX3)) != 0)) foreign = true;
-                    uint32_t nib[4];
-                    if (KINDW == 1) {
-                        const uint32_t w0 = lds_u32(row_s + 12u * c), w1 = lds_u32(row_s + 12u * c + 4u), w2 = lds_u32(row_s + 12u * c + 8u);
-                        const uint32_t cr = lds_u32(row_s + 48u + 4u * c);
-                        const uint32_t w[4] = {w0, w1, w2, 0u};
-#pragma unroll
-                        for (int m = 0; m < 4; ++m) {
-                            const int wi = (24 * m) >> 5, sh = (24 * m) & 31;
-                            uint32_t x = __funnelshift_r(w[wi], w[wi + 1], sh) & 0xFFFFFFu;  // eight 3-bit codes
-                            x = (x & 0xFFFu) | ((x & 0xFFF000u) << 4);
-                            x = (x & 0x003F003Fu) | ((x & 0x0FC00FC0u) << 2);
-                            x = (x & 0x07070707u) | ((x & 0x38383838u) << 1);
-                            uint32_t cb = (cr >> (8 * m)) & 0xFFu;                             // their correction bits
-                            cb = (cb | (cb << 12)) & 0x000F000Fu;
-                            cb = (cb | (cb << 6)) & 0x03030303u;
-                            cb = (cb | (cb << 3)) & 0x11111111u;
-                            nib[m] = (x << 1) | cb;
-                        }
-                    } else {
-                        const uint4 L = lds_v4<0>(row_s + 16u * c);
-                        nib[0] = L.x; nib[1] = L.y; nib[2] = L.z; nib[3] = L.w;
-                    }
-                    uint32_t G0, C0, G1, C1;
-                    int4c_scales(lds_u16<120>(row_s + 2u * c), magic, G0, C0, G1, C1);
-                    const uint32_t arow = A_s + s * WIDE_A_BYTES + r * 128u;
-#pragma unroll
-                    for (int m = 0; m < 4; ++m) {
-                        uint32_t o[4];
-                        int4c_word(nib[m], m < 2 ? G0 : G1, m < 2 ? C0 : C1, o);
-                        if (!live) o[0] = o[1] = o[2] = o[3] = 0u;
-                        const uint32_t word = 4u * c + (uint32_t)m, slab = word >> 3, chunk = word & 7u;
-                        sts_v4(arow + slab * WIDE_SLAB + ((chunk ^ (r & 7u)) << 4), o[0], o[1], o[2], o[3]);
-                    }
-                    if (c == 0) {
-                        // third slab: the eight scale bytes times c 2^-13 (TQ3: c = 1, or 2 once the correction plane is gone), then zeros
-                        uint32_t e[4] = {0u, 0u, 0u, 0u};
-                        if (KINDW == 1 && live) {
-                            const uint2 gsb = lds_v2<120>(row_s);
-                            const uint32_t f = (flags & F_NOCORR) ? 0x0C000C00u : 0x08000800u;  // 2^-12 or 2^-13 as fp16, twice
-                            uint32_t t;
-                            asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.x, magic, 0x7150u)), "r"(0xE400E400u));
-                            asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[0]) : "r"(t), "r"(f));
-                            asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.x, magic, 0x7352u)), "r"(0xE400E400u));
-                            asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[1]) : "r"(t), "r"(f));
-                            asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.y, magic, 0x7150u)), "r"(0xE400E400u));
-                            asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[2]) : "r"(t), "r"(f));
-                            asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.y, magic, 0x7352u)), "r"(0xE400E400u));
-                            asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[3]) : "r"(t), "r"(f));
-                        }
-                        sts_v4(arow + 2 * WIDE_SLAB + ((0u ^ (r & 7u)) << 4), e[0], e[1], e[2], e[3]);
-                        sts_v4(arow + 2 * WIDE_SLAB + ((1u ^ (r & 7u)) << 4), 0u, 0u, 0u, 0u);
-                    }
-                }
-                if (foreign) tmem_slot[2] = 1;  // a codec this launch does not decode: the item's rows go to the generic kernel
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                mbar_arrive(bars_s + 8 * s);
-            }
-        } else if (warp == 8) {
+        if (warp == MMA_WARP) {
             // ---- MMA warp: one thread issues the K steps of every block ----
             for (uint32_t b = 0; b < blocks; ++b) {
                 const uint32_t g = nblk + b, s = g & 1u, use = g >> 1;
@@ -325,12 +287,97 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
                 __syncwarp();
             }
         } else {
-            // ---- scoring warps: thread = tile row of the block ----
-            const int ew = warp - 4, r = 32 * ew + lane;
+            // ---- workers ----
+            // staging share: tile row tid / 4 of the block, latent quarter tid & 3; two 16-byte chunks of the raw copy
+            auto stage = [&](uint32_t b) {
+                const uint32_t s = (nblk + b) & 1u;
+                const uint32_t t0 = b * WIDE_M;
+                const unsigned char* src = a.tiles + (it.tile_begin + t0) * TILE_BYTES;
+                const uint32_t rs = raw_s + s * WIDE_RAW_BYTES;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const uint32_t chunk = (uint32_t)i * WIDE_WORKERS + (uint32_t)tid, row = chunk >> 3;
+                    const bool in = t0 + row < n;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(rs + chunk * 16u), "l"(in ? src + (size_t)chunk * 16 : a.tiles), "r"(in ? 16 : 0));
+                }
+                cp_async_commit();
+                cp_async_wait<0>();
+                asm volatile("bar.sync 3, 512;\n" ::: "memory");  // the workers see each other's copies
+                WPROBE_LAP(2);  // copy
+                const uint32_t r = (uint32_t)tid >> 2, c = (uint32_t)tid & 3u;
+                const uint32_t row_s = rs + r * TILE_BYTES;
+                const uint32_t flags = lds_u16<118>(row_s);
+                const bool live = t0 + r < n;
+                // a codec this launch does not decode: the item's rows go to the generic kernel
+                if (live && ((KINDW == 1) ? !(flags & F_TQ3) || (flags & (F_NF4 | F_MIXED | F_MIX3)) : (flags & (F_NF4 | F_MIXED | F_TQ3 | F_MIX3)) != 0)) tmem_slot[2] = 1;
+                uint32_t nib[4];
+                if (KINDW == 1) {
+                    const uint32_t w0 = lds_u32(row_s + 12u * c), w1 = lds_u32(row_s + 12u * c + 4u), w2 = lds_u32(row_s + 12u * c + 8u);
+                    const uint32_t cr = lds_u32(row_s + 48u + 4u * c);
+                    const uint32_t w[4] = {w0, w1, w2, 0u};
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        const int wi = (24 * m) >> 5, sh = (24 * m) & 31;
+                        uint32_t x = __funnelshift_r(w[wi], w[wi + 1], sh) & 0xFFFFFFu;  // eight 3-bit codes
+                        x = (x & 0xFFFu) | ((x & 0xFFF000u) << 4);
+                        x = (x & 0x003F003Fu) | ((x & 0x0FC00FC0u) << 2);
+                        x = (x & 0x07070707u) | ((x & 0x38383838u) << 1);
+                        uint32_t cb = (cr >> (8 * m)) & 0xFFu;                             // their correction bits
+                        cb = (cb | (cb << 12)) & 0x000F000Fu;
+                        cb = (cb | (cb << 6)) & 0x03030303u;
+                        cb = (cb | (cb << 3)) & 0x11111111u;
+                        nib[m] = (x << 1) | cb;
+                    }
+                } else {
+                    const uint4 L = lds_v4<0>(row_s + 16u * c);
+                    nib[0] = L.x; nib[1] = L.y; nib[2] = L.z; nib[3] = L.w;
+                }
+                uint32_t G0, C0, G1, C1;
+                int4c_scales(lds_u16<120>(row_s + 2u * c), magic, G0, C0, G1, C1);
+                const uint32_t arow = A_s + s * WIDE_A_BYTES + r * 128u;
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    uint32_t o[4];
+                    int4c_word(nib[m], m < 2 ? G0 : G1, m < 2 ? C0 : C1, o);
+                    if (!live) o[0] = o[1] = o[2] = o[3] = 0u;
+                    const uint32_t word = 4u * c + (uint32_t)m, slab = word >> 3, chunk = word & 7u;
+                    sts_v4(arow + slab * WIDE_SLAB + ((chunk ^ (r & 7u)) << 4), o[0], o[1], o[2], o[3]);
+                }
+                if (c == 0) {
+                    // third slab: the eight scale bytes times c 2^-13 (TQ3: c = 1, or 2 once the correction plane is gone), then zeros
+                    uint32_t e[4] = {0u, 0u, 0u, 0u};
+                    if (KINDW == 1 && live) {
+                        const uint2 gsb = lds_v2<120>(row_s);
+                        const uint32_t f = (flags & F_NOCORR) ? 0x0C000C00u : 0x08000800u;  // 2^-12 or 2^-13 as fp16, twice
+                        uint32_t t;
+                        asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.x, magic, 0x7150u)), "r"(0xE400E400u));
+                        asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[0]) : "r"(t), "r"(f));
+                        asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.x, magic, 0x7352u)), "r"(0xE400E400u));
+                        asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[1]) : "r"(t), "r"(f));
+                        asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.y, magic, 0x7150u)), "r"(0xE400E400u));
+                        asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[2]) : "r"(t), "r"(f));
+                        asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(prmt(gsb.y, magic, 0x7352u)), "r"(0xE400E400u));
+                        asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(e[3]) : "r"(t), "r"(f));
+                    }
+                    sts_v4(arow + 2 * WIDE_SLAB + ((0u ^ (r & 7u)) << 4), e[0], e[1], e[2], e[3]);
+                    sts_v4(arow + 2 * WIDE_SLAB + ((1u ^ (r & 7u)) << 4), 0u, 0u, 0u, 0u);
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                mbar_arrive(bars_s + 8 * s);
+                WPROBE_LAP(3);  // dequantise
+            };
+            // scoring share: TMEM lanes (tile rows) 32 qt .. + 31, query columns 16 ch .. + 15
+            const int qt = warp & 3, ch = warp >> 2, r = 32 * qt + lane;
+            const bool cols = 16 * ch < nq;  // this worker has query columns in this item
+            if (blocks) stage(0);
             for (uint32_t b = 0; b < blocks; ++b) {
                 const uint32_t g = nblk + b, s = g & 1u, use = g >> 1;
-                if (!mbar_wait(bars_s + 16 + 8 * s, use & 1u)) { tmem_slot[1] = 1; break; }
+                if (b + 1 < blocks) stage(b + 1);  // (its buffers were released by the barrier that ended block b - 1)
+                // (a wait that ran out anywhere ends the item for all workers together: barriers follow)
+                if (role_any(1, WIDE_WORKERS, !mbar_wait(bars_s + 16 + 8 * s, use & 1u))) { tmem_slot[1] = 1; break; }
+                WPROBE_LAP(1);  // wait for the accumulators
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                {
                 const uint32_t t0 = b * WIDE_M + (uint32_t)r;
                 const uint32_t row_s = raw_s + s * WIDE_RAW_BYTES + (uint32_t)r * TILE_BYTES;
                 const uint2 meta = lds_v2<96>(row_s);
@@ -340,111 +387,147 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
                 const float lam = (flags & F_WARM) ? 0.0f : __uint_as_float(meta.y);
                 const float su = __uint_as_float(meta.x) * (KINDW == 1 ? 2048.0f / 255.0f : 4096.0f / 255.0f);
                 const uint32_t nidx = ~(it.index_base + t0);
-                // The first block of an item is walked twice: a counting pass puts every score into the rows'
-                // histograms without appending anything, the thresholds are derived (all CTAs of the grid count
-                // their first blocks at about the same time, 128 tiles each), and only then the block is filtered
-                // like every later one - otherwise each CTA would append its whole first block.
-                for (int pass = (b == 0 ? 0 : 1); pass < 2; ++pass) {
-                    const bool count_only = pass == 0;
-#pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        if (16 * c >= nq) break;
+                const uint32_t tm = tmem + ((uint32_t)(32 * qt) << 16) + s * 128u + (uint32_t)ch * 32u;
+                const uint32_t Q0 = it.query_begin + 16u * (uint32_t)ch;
+                auto full_score = [&](float coarse, int q) {
+                    const uint32_t* qw = qs_w + 8 * q;
+                    const int h = __popc(ra.x ^ qw[0]) + __popc(ra.y ^ qw[1]) + __popc(ra.z ^ qw[2]) + __popc(ra.w ^ qw[3]) +
+                                  __popc(rb2.x ^ qw[4]) + __popc(rb2.y ^ qw[5]) + __popc(rb2.z ^ qw[6]) + __popc(rb2.w ^ qw[7]);
+                    return fmaf(lam, (float)(256 - 2 * h), coarse);
+                };
+                if (b == 0) {
+                    // The first block of an item is walked before it is filtered.  (1) Rows without a bucket mapping get one
+                    // from the block's coarse scores (any monotone mapping is valid): column minima and maxima per tile
+                    // quarter by a butterfly, combined by one thread per row, one load and one compare-and-swap for all rows
+                    // at once.  (2) A counting pass puts every score of the block into the rows' histograms without
+                    // appending anything, and the thresholds are derived -- all CTAs of the grid count their first blocks at
+                    // about the same time, 128 tiles each; otherwise each CTA would append its whole first block.
+                    if (need_map) {
+                        if (cols) {
+                            uint32_t v[32];
+                            wide_tmem_ld32(tm, v);
+                            float mn[16], mx[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const float coarse = (__uint_as_float(v[2 * j]) + __uint_as_float(v[2 * j + 1])) * su;
+                                mn[j] = live ? coarse : INFINITY;
+                                mx[j] = live ? coarse : -INFINITY;
+                            }
+#pragma unroll
+                            for (int step = 0; step < 4; ++step) {
+                                const int half = 8 >> step, off = 16 >> step;
+                                const bool up = (lane & off) != 0;
+#pragma unroll
+                                for (int i = 0; i < half; ++i) {
+                                    const float rmn = __shfl_xor_sync(0xFFFFFFFFu, up ? mn[i] : mn[i + half], off);
+                                    const float rmx = __shfl_xor_sync(0xFFFFFFFFu, up ? mx[i] : mx[i + half], off);
+                                    mn[i] = fminf(up ? mn[i + half] : mn[i], rmn);
+                                    mx[i] = fmaxf(up ? mx[i + half] : mx[i], rmx);
+                                }
+                            }
+                            mn[0] = fminf(mn[0], __shfl_xor_sync(0xFFFFFFFFu, mn[0], 1));
+                            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xFFFFFFFFu, mx[0], 1));
+                            if (!(lane & 1)) colmm[qt * WIDE_NQ + 16 * ch + (lane >> 1)] = make_float2(mn[0], mx[0]);  // column 16 ch + lane / 2
+                        }
+                        asm volatile("bar.sync 2, 512;\n" ::: "memory");
+                        if (tid < nq && rng[tid].y == 0.0f) {
+                            float lo_s = INFINITY, hi_s = -INFINITY;
+                            for (int w2 = 0; w2 < 4; ++w2) {
+                                lo_s = fminf(lo_s, colmm[w2 * WIDE_NQ + tid].x);
+                                hi_s = fmaxf(hi_s, colmm[w2 * WIDE_NQ + tid].y);
+                            }
+                            const uint32_t Q = it.query_begin + (uint32_t)tid;
+                            unsigned long long pr = *reinterpret_cast<volatile unsigned long long*>(a.grange + Q);
+                            if (!pr && hi_s > lo_s) {
+                                const float span = hi_s - lo_s, lo = lo_s - 1.5f * span, inv = 256.0f / (4.0f * span);
+                                if (isfinite(lo) && isfinite(inv) && inv > 0.0f) {
+                                    const unsigned long long mine_r = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(inv) << 32);
+                                    const unsigned long long old = atomicCAS(a.grange + Q, 0ull, mine_r);
+                                    pr = old ? old : mine_r;
+                                }
+                            }
+                            if (pr) {
+                                const float2 rr = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
+                                rng[tid] = rr;
+                                rmap[tid] = make_float2(-rr.x * rr.y, rr.y);
+                            }
+                        }
+                        asm volatile("bar.sync 2, 512;\n" ::: "memory");
+                    }
+                    WPROBE_LAP(4);  // bucket mappings
+                    if (cols) {
                         uint32_t v[32];
-                        wide_tmem_ld32(tmem + ((uint32_t)(32 * ew) << 16) + s * 128u + (uint32_t)c * 32u, v);
-                        uint32_t keys[16], bal[16], pm = 0;
+                        wide_tmem_ld32(tm, v);  // (collective: every lane of the warp takes part, live tile or not)
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            const int q = 16 * c + j;
-                            bal[j] = 0;
-                            keys[j] = 0;
-                            if (q >= nq) continue;  // (uniform)
-                            const float coarse = (__uint_as_float(v[2 * j]) + __uint_as_float(v[2 * j + 1])) * su;
-                            // the residual term lies in [-256 lambda, 256 lambda]
-                            bool p = live && (count_only || fmaf(lam, 257.0f, coarse + fabsf(coarse) * 1e-6f) >= thr[q]);
-                            float sc = coarse;
-                            if (p) {
-                                const uint32_t* qw = qs_w + 8 * q;
-                                const int h = __popc(ra.x ^ qw[0]) + __popc(ra.y ^ qw[1]) + __popc(ra.z ^ qw[2]) + __popc(ra.w ^ qw[3]) +
-                                              __popc(rb2.x ^ qw[4]) + __popc(rb2.y ^ qw[5]) + __popc(rb2.z ^ qw[6]) + __popc(rb2.w ^ qw[7]);
-                                sc = fmaf(lam, (float)(256 - 2 * h), coarse);
-                                keys[j] = score_key(sc);
-                                p = count_only || keys[j] >= pvh[q];
-                            }
-                            bal[j] = __ballot_sync(0xFFFFFFFFu, p);
-                            if (p) pm |= 1u << j;
-                            if (bal[j] && rng[q].y == 0.0f) {
-                                // first candidates of a row without a bucket mapping define one (any monotone mapping is valid)
-                                const uint32_t Q = it.query_begin + (uint32_t)q;
-                                float mn = p ? sc : INFINITY, mx = p ? sc : -INFINITY;
-#pragma unroll
-                                for (int o = 16; o; o >>= 1) {
-                                    mn = fminf(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, o));
-                                    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-                                }
-                                if (lane == 0) {
-                                    unsigned long long pr = *reinterpret_cast<volatile unsigned long long*>(a.grange + Q);
-                                    if (!pr && mx > mn) {
-                                        const float span = mx - mn, lo = mn - 1.5f * span, inv = 256.0f / (4.0f * span);
-                                        if (isfinite(lo) && isfinite(inv) && inv > 0.0f) {
-                                            const unsigned long long mine_r = (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(inv) << 32);
-                                            const unsigned long long old = atomicCAS(a.grange + Q, 0ull, mine_r);
-                                            pr = old ? old : mine_r;
-                                        }
-                                    }
-                                    if (pr) {
-                                        const float2 rr = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
-                                        rng[q] = rr;
-                                        rmap[q] = make_float2(-rr.x * rr.y, rr.y);
-                                    }
-                                }
-                                __syncwarp();
-                            }
+                            const int q = 16 * ch + j;
+                            if (q >= nq || !live) continue;
+                            const float sc = full_score((__uint_as_float(v[2 * j]) + __uint_as_float(v[2 * j + 1])) * su, q);
+                            const float2 rm = rmap[q];
+                            atomicAdd(a.ghist + (size_t)(Q0 + (uint32_t)j) * 256 + min(max(__float2int_rz(fmaf(sc, rm.y, rm.x)), 0), 255), 1u);
                         }
-                        // slots of the sixteen rows' candidates: lane j reserves for row 16 c + j, one round trip for all
-                        uint32_t slot0 = 0;
-                        if (!count_only) {
-                            uint32_t mine_bal = 0;
+                    }
+                    asm volatile("bar.sync 2, 512;\n" ::: "memory");
+                    WPROBE_LAP(5);  // counting pass
+                    const int rows = min(4, nq - 4 * warp);
+                    if (rows > 0) wide_refresh_rows<4>(a, it.query_begin + 4u * (uint32_t)warp, rows, rng + 4 * warp, pvh + 4 * warp, thr + 4 * warp, lane);
+                    asm volatile("bar.sync 2, 512;\n" ::: "memory");
+                    WPROBE_LAP(6);  // thresholds
+                }
+                if (cols) {
+                    uint32_t v[32];
+                    wide_tmem_ld32(tm, v);
+                    uint32_t keys[16], bal[16], pm = 0, mine_cnt = 0;
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (lane == j) mine_bal = bal[j];
-                            if (mine_bal) slot0 = atomicAdd(a.gcount + it.query_begin + 16u * (uint32_t)c + (uint32_t)lane, (uint32_t)__popc(mine_bal));
+                    for (int j = 0; j < 16; ++j) {
+                        const int q = 16 * ch + j;
+                        bal[j] = 0;
+                        keys[j] = 0;
+                        if (q >= nq) continue;  // (uniform)
+                        const float coarse = (__uint_as_float(v[2 * j]) + __uint_as_float(v[2 * j + 1])) * su;
+                        // the residual term lies in [-256 lambda, 256 lambda]
+                        bool p = live && fmaf(lam, 257.0f, coarse + fabsf(coarse) * 1e-6f) >= thr[q];
+                        if (p) {
+                            keys[j] = score_key(full_score(coarse, q));
+                            p = keys[j] >= pvh[q];
                         }
+                        bal[j] = __ballot_sync(0xFFFFFFFFu, p);
+                        if (p) pm |= 1u << j;
+                        if (lane == j) mine_cnt = (uint32_t)__popc(bal[j]);
+                    }
+                    // slots of the sixteen rows' candidates: lane j reserves for row 16 ch + j, one round trip for all
+                    uint32_t slot0 = 0;
+                    if (mine_cnt) slot0 = atomicAdd(a.gcount + Q0 + (uint32_t)lane, mine_cnt);
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (!bal[j]) continue;  // (uniform)
-                            const uint32_t Q = it.query_begin + 16u * (uint32_t)c + (uint32_t)j;
-                            const uint32_t base_j = __shfl_sync(0xFFFFFFFFu, slot0, j);
-                            if (pm >> j & 1u) {
-                                if (!count_only) {
-                                    const uint32_t at = base_j + (uint32_t)__popc(bal[j] & ((1u << lane) - 1u));
-                                    if (at < a.gcap) a.gbuf[(size_t)Q * a.gcap + at] = ((uint64_t)keys[j] << 32) | (uint64_t)nidx;
-                                    else a.gflag[Q] = 1u;  // the row's buffer is full: the generic kernel scores the row
-                                }
-                                if (count_only || b != 0) {  // (the first block was counted by its counting pass)
-                                    const float2 rm = rmap[16 * c + j];
-                                    atomicAdd(a.ghist + (size_t)Q * 256 + min(max(__float2int_rz(fmaf(key_score(keys[j]), rm.y, rm.x)), 0), 255), 1u);
-                                }
+                    for (int j = 0; j < 16; ++j) {
+                        if (!bal[j]) continue;  // (uniform)
+                        const uint32_t base_j = __shfl_sync(0xFFFFFFFFu, slot0, j);
+                        if (pm >> j & 1u) {
+                            const uint32_t Q = Q0 + (uint32_t)j;
+                            const uint32_t at = base_j + (uint32_t)__popc(bal[j] & ((1u << lane) - 1u));
+                            if (at < a.gcap) a.gbuf[(size_t)Q * a.gcap + at] = ((uint64_t)keys[j] << 32) | (uint64_t)nidx;
+                            else a.gflag[Q] = 1u;  // the row's buffer is full: the generic kernel scores the row
+                            if (b != 0) {  // (the first block was counted by its counting pass)
+                                const float2 rm = rmap[16 * ch + j];
+                                atomicAdd(a.ghist + (size_t)Q * 256 + min(max(__float2int_rz(fmaf(key_score(keys[j]), rm.y, rm.x)), 0), 255), 1u);
                             }
                         }
                     }
-                    if (count_only) {
-                        // all four scoring warps have counted: thresholds of the item's rows, then the filtering pass
-                        asm volatile("bar.sync 2, 128;\n" ::: "memory");
-                        const int rows = min(16, nq - 16 * ew);
-                        if (rows > 0) wide_refresh(a, it.query_begin + 16u * (uint32_t)ew, rows, rng + 16 * ew, pvh + 16 * ew, thr + 16 * ew, lane);
-                        asm volatile("bar.sync 2, 128;\n" ::: "memory");
-                    }
+                }
+                WPROBE_LAP(1 + 8);  // filter and append (index 9)
+                // thresholds again after every second block; worker w looks after rows 4 w .. 4 w + 3
+                if ((b & 1u) == 1u && b + 1 < blocks) {
+                    const int rows = min(4, nq - 4 * warp);
+                    if (rows > 0) wide_refresh_rows<4>(a, it.query_begin + 4u * (uint32_t)warp, rows, rng + 4 * warp, pvh + 4 * warp, thr + 4 * warp, lane);
+                    WPROBE_LAP(6);
+                }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-                mbar_arrive(bars_s + 32 + 8 * s);
-                // thresholds again after every second block; warp ew looks after rows 16 ew .. 16 ew + 15
-                if ((b & 1u) == 1u) {
-                    __syncwarp();
-                    const int rows = min(16, nq - 16 * ew);
-                    if (rows > 0) wide_refresh(a, it.query_begin + 16u * (uint32_t)ew, rows, rng + 16 * ew, pvh + 16 * ew, thr + 16 * ew, lane);
-                    __syncwarp();
-                }
+                // all workers are done with block b (its raw tiles, its accumulator): the stage may be refilled
+                asm volatile("bar.sync 1, 512;\n" ::: "memory");
+                WPROBE_LAP(2 + 8);  // end-of-block barrier (index 10)
             }
+            if (warp == 0) WPROBE_OUT(0, 12);
         }
         nblk += blocks;
         __syncthreads();
@@ -462,7 +545,7 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(256u) : "memory");
+    if (warp == MMA_WARP) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(256u) : "memory");
 }
 
 }  // namespace
