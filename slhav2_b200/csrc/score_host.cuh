@@ -115,6 +115,7 @@ struct Plan {
     uint64_t* d_gbuf = nullptr;              // per query: gcap candidate keys of the tensor-core kernel
     uint32_t gcap = 0;
     size_t gstate_bytes = 0;
+    bool state_clean = false;  // the previous call's merge left the streaming state cleared (see StreamLists::finish)
     uint32_t compact_splits = 0, selcap = 0;  // optional compaction pass before the merge (few rows, long buffers)
     // wide scoring (16 or more queries per segment, INT4 / TQ3 launches): work items of up to 64 query rows for score_wide_kernel
     bool wide = false, allow_wide_in = false;
@@ -287,7 +288,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
                 w.query_begin = s.query_begin + q0;
                 w.n_queries = gq;
                 w.list_begin = n_lists + part * gq;
-                w.pad = gq;  // list stride between parts, used by the merge accessor
+                w.pad = gq | (std::min<uint32_t>(parts, 0xFFFFFFu) << 8);  // low byte: list stride between parts (merge accessor); above: parts of the row group
                 items[p->use_mma ? 2 : (G == 1 ? 0 : (G == 2 ? 1 : 2))].push_back(w);
             }
             n_lists += parts * gq;
@@ -306,7 +307,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     // per query: list id of part p is q_begin + p * stride; store stride in the count's high bits
     std::vector<uint32_t> q_stride(nq, 1);
     for (const WorkItem& w : all)
-        for (uint32_t g = 0; g < w.n_queries; ++g) q_stride[w.query_begin + g] = w.pad;
+        for (uint32_t g = 0; g < w.n_queries; ++g) q_stride[w.query_begin + g] = w.pad & 0xFFu;
     SLHA_TRY(p->b_items.ensure(all.size() * sizeof(WorkItem)));
     SLHA_TRY(p->b_qbegin.ensure(nq * 4));
     SLHA_TRY(p->b_qcount.ensure(nq * 4));
@@ -379,7 +380,8 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     p->gcap = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(std::max<uint64_t>(16ull * k, 4096), first_sets + 4ull * k), all_of_a_row / 64 * 64);
     // (wide scoring: the first 128-tile block of every item is appended unfiltered, and a CTA sees few blocks)
     if (p->wide) p->gcap = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(p->gcap, 4ull * WIDE_M * wide_parts + 16ull * k), ((uint64_t)longest + 63) / 64 * 64);
-    p->gstate_bytes = nq * (1024 + 8 + 8 + 4 + 4 + 4);
+    p->gstate_bytes = nq * (1024 + 8 + 8 + 4 + 4 + 4 + 8);  // histogram, threshold, mapping, count, flag, compacted count, statistics
+    p->state_clean = false;
     // few rows with long buffers: several CTAs per row compact the survivors before the merge
     p->compact_splits = (p->use_mma && nq < 128 && p->gcap >= 8192) ? (uint32_t)std::min<size_t>(32, (296 + nq - 1) / nq) : 0;
     p->selcap = merge_cap((uint64_t)p->gcap, p->kp2, k);
@@ -502,7 +504,8 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     ScoreArgs am{};
     if (mma) g_last_stream_plan = p;
     if (mma) {
-        SLHA_CUDA(cudaMemsetAsync(p->d_gpivot, 0, p->gstate_bytes, c->stream));
+        if (!p->state_clean) SLHA_CUDA(cudaMemsetAsync(p->d_gpivot, 0, p->gstate_bytes, c->stream));
+        p->state_clean = false;
         ScoreArgs& a = am;
         a.tiles = reinterpret_cast<const unsigned char*>(tiles);
         a.state = state;
@@ -586,9 +589,11 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         }
         StreamLists L{p->d_gbuf, am.gcount, am.gflag, am.gpivot, p->gcap,
                       p->compact_splits ? (const uint64_t*)p->b_gsel.p : nullptr, gselcnt, cap_s,
-                      CompLists{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, p->list_cap}};
+                      CompLists{p->d_cand_keys, p->d_cand_cnt, p->d_q_list_begin, p->d_q_list_count, p->list_cap},
+                      am.ghist, gselcnt + nq};
         topk_merge_kernel<StreamLists><<<(uint32_t)nq, merge_threads(cap_s), merge_smem(cap_s, p->kp2), c->stream>>>(
             L, k, p->kp2, cap_s, d_out_index, d_out_score, d_out_count);
+        p->state_clean = cudaPeekAtLastError() == cudaSuccess;
     } else if (p->n_groups) {
         // few queries, many lists each: groups of lists first, then the groups' results
         CompLists L1{p->d_cand_keys, p->d_cand_cnt, p->d_vq_begin, p->d_vq_count, p->list_cap};
@@ -626,13 +631,13 @@ Status last_score_stats(Ctx* c, uint64_t* out4) {
     if (!p || p->device != c->device || !p->use_mma) return Status();
     const size_t nq = p->nq;
     std::vector<uint32_t> h(2 * nq);
-    const uint32_t* gcount = reinterpret_cast<const uint32_t*>(p->d_gpivot + 128 * nq + 2 * nq);
-    SLHA_CUDA(cudaMemcpyAsync(h.data(), gcount, 8 * nq, cudaMemcpyDeviceToHost, c->stream));
+    const uint32_t* stats = reinterpret_cast<const uint32_t*>(p->d_gpivot + 128 * nq + 2 * nq) + 3 * nq;  // kept by the merge
+    SLHA_CUDA(cudaMemcpyAsync(h.data(), stats, 8 * nq, cudaMemcpyDeviceToHost, c->stream));
     SLHA_CUDA(cudaStreamSynchronize(c->stream));
     out4[0] = nq;
     for (size_t q = 0; q < nq; ++q) {
-        out4[1] += h[nq + q] != 0;
-        out4[2] += h[q];
+        out4[1] += h[2 * q + 1] != 0;
+        out4[2] += h[2 * q];
     }
     out4[3] = p->gcap;
     return Status();

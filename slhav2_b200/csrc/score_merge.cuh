@@ -28,6 +28,7 @@ struct CompLists {  // lists written by score_kernel
         const uint32_t l = q_list_begin[Q] + (e / k) * (q_list_count[Q] >> 24), j = e % k;
         return j < cnt[l] ? keys[(size_t)l * k + j] : 0ull;
     }
+    __device__ void finish(uint32_t) const {}
 };
 // Candidates of the streaming tensor-core kernel: one buffer per query row (keys below the row's
 // final threshold count as absent), or - for rows that kernel handed to the generic kernel - the
@@ -56,6 +57,22 @@ struct StreamLists {
         return key >= gpivot[Q] ? key : 0ull;
     }
     __device__ uint64_t get(uint32_t Q, uint32_t e) const { return gflag[Q] ? items.get(Q, e) : (e < len0(Q) ? at(Q, 0, e) : 0ull); }
+    // The merge is the last reader of a row's streaming state: it leaves the state cleared for the next call
+    // (which then needs no memset in front of its score kernel) and keeps the row's figures for the statistics call.
+    uint32_t* ghist;     // [nq][256]; the state arrays follow it in one allocation
+    uint32_t* stats;     // [nq][2] candidates appended, handed to the generic kernel
+    __device__ void finish(uint32_t Q) const {
+        for (uint32_t i = threadIdx.x; i < 256; i += blockDim.x) ghist[(size_t)Q * 256 + i] = 0u;
+        if (threadIdx.x == 0) {
+            stats[2 * Q] = gcount[Q];
+            stats[2 * Q + 1] = gflag[Q];
+            const_cast<unsigned long long*>(gpivot)[Q] = 0ull;
+            const_cast<unsigned long long*>(gpivot)[gridDim.x + Q] = 0ull;  // (the bucket mapping lies behind the thresholds)
+            const_cast<uint32_t*>(gcount)[Q] = 0u;
+            const_cast<uint32_t*>(gflag)[Q] = 0u;
+            const_cast<uint32_t*>(gselcnt)[Q] = 0u;
+        }
+    }
 };
 struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     static constexpr bool kFiltered = false;
@@ -77,6 +94,7 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
         const uint32_t i = idx[o];
         return i == 0xFFFFFFFFu ? 0ull : make_comp(score[o], i);
     }
+    __device__ void finish(uint32_t) const {}
 };
 
 // Calls with few query rows (a long context scored by a handful of heads) leave every row tens of
@@ -244,10 +262,8 @@ __device__ void sort_and_emit(uint64_t* buf, uint32_t cap_s, int* hist, uint32_t
 // candidates fit they are gathered once and selected / sorted in shared memory;
 // otherwise the radix select runs over global memory.
 template <typename Lists>
-__global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, uint32_t kp2, uint32_t cap_s,
-                                                         uint32_t* out_index, float* out_score,
-                                                         uint32_t* out_count) {
-    extern __shared__ __align__(16) unsigned char smem[];
+__device__ __forceinline__ void topk_merge_body(const Lists& L, uint32_t k, uint32_t kp2, uint32_t cap_s, uint32_t* out_index,
+                                                float* out_score, uint32_t* out_count, unsigned char* smem) {
     uint64_t* buf = reinterpret_cast<uint64_t*>(smem);  // [cap_s]
     uint64_t* pivot_s = buf + cap_s;                    // [1]
     int* hist = reinterpret_cast<int*>(pivot_s + 1);    // max(SEL_HIST_INTS, buckets of bucket_sort + 48)
@@ -475,6 +491,15 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
     }
     __syncthreads();
     sort_and_emit(buf, cap_s, hist, kp2, m, k, Q, out_index, out_score, out_count);
+}
+template <typename Lists>
+__global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, uint32_t kp2, uint32_t cap_s,
+                                                         uint32_t* out_index, float* out_score,
+                                                         uint32_t* out_count) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    topk_merge_body(L, k, kp2, cap_s, out_index, out_score, out_count, smem);
+    __syncthreads();
+    L.finish(blockIdx.x);
 }
 
 }  // namespace

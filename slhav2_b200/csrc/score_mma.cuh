@@ -708,12 +708,14 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         const WorkItem it = a.items[item_id];
         const int nq = (int)it.n_queries;
         __syncthreads();  // previous item fully retired (and the table is visible)
+        bool row_warm = true;
         if (tid < 4) {
             // start from the threshold other CTAs have already proven for the row, and from the
             // row's bucket mapping if one has been published
             const bool have = tid < nq;
             const unsigned long long pv = have ? *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + tid) : 0ull;
             pvh[tid] = (uint32_t)(pv >> 32);
+            row_warm = !have || (uint32_t)(pv >> 32) != 0u;
             const unsigned long long pr = have ? *reinterpret_cast<volatile unsigned long long*>(a.grange + it.query_begin + tid) : 0ull;
             rng[tid] = make_float2(__uint_as_float((uint32_t)pr), __uint_as_float((uint32_t)(pr >> 32)));
             rmap[tid] = make_float2(-rng[tid].x * rng[tid].y, rng[tid].y);
@@ -779,7 +781,11 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
             bq_w[8 * 32 + lane] = make_uint2(bE, 0u);
             if (__any_sync(0xFFFFFFFFu, big) && lane == 0) bail[0] = 1;  // a query too large for the fp16 split
         }
-        __syncthreads();
+        // The barrier after the first round (below) pays when the round can supply k candidates to a row -- 16 per warp
+        // of every CTA that works on the row -- and the rows do not already have thresholds (a CTA that starts its
+        // second item on rows other CTAs have been scoring for a while).
+        const bool all_warm = __syncthreads_and(row_warm) != 0;
+        const bool first_round_barrier = !all_warm && (uint64_t)a.k <= 16ull * (uint64_t)nwarps * (uint64_t)max(it.pad >> 8, 1u);
         PROBE_SET(1);
         const bool too_big = bail[0] != 0;
 
@@ -824,7 +830,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         const uint32_t rounds = (n_sets + (uint32_t)nwarps - 1) / (uint32_t)nwarps;
         for (uint32_t round = 0; round < rounds; ++round) {
             const uint32_t s = round * (uint32_t)nwarps + (uint32_t)warp;
-            if (round == 1) {
+            if (round == 1 && first_round_barrier) {
                 // Every warp of the CTA (and, started together, of the grid) has appended its first set
                 // unfiltered, so the rows' histograms hold 16 candidates per warp: first thresholds now,
                 // before the second sets are filtered.  (All warps pass here: `rounds` is the same for all.)
