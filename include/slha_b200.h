@@ -283,6 +283,23 @@ int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment
                              size_t n_queries, uint32_t k, uint32_t* out_index, float* out_score,
                              uint32_t* out_count);
 
+/* The scoring step of the llama.cpp shim (integration/llama.cpp/shim/
+ * slha_llama.cpp:1387-1503: one slha_score_tiles call per (token, head) vector,
+ * each zero-filling its row first) for a whole layer in ONE call: every query
+ * row of a segment against every tile of the segment (a segment = the tile
+ * store of one KV head; its query rows = the (token, head) vectors of the GQA
+ * group).  Row q is written at scores_out[row_offsets[q] + index_base + i] for
+ * tile i of its segment and the rest of the row, up to element row_len, is set
+ * to `fill` (the shim: 0.0f for the padded positions [n_written, n_kv)); rows
+ * may lie anywhere inside scores_out[0 .. scores_len) (the strides of ggml's
+ * [n_kv, n_token, n_head] destination become row offsets).  tiles: device
+ * memory; every other pointer host or device.  With a host scores_out the
+ * elements no row covers come back as zero; a device scores_out is written
+ * only where rows lie.  No counterpart in the reference's C ABI. */
+int32_t slha_b200_score_segments(const SciRustSlhaTile* tiles, const SlhaB200Segment* segments, size_t n_segments,
+                                 const float* q_coarse, const uint64_t* q_sign, size_t n_queries, float* scores_out,
+                                 size_t scores_len, const uint64_t* row_offsets, uint32_t row_len, float fill);
+
 /*
  * slha_b200_score_topk for callers that must not allocate.  It has no
  * counterpart in the reference.

@@ -153,6 +153,7 @@ extern "C" {
     pub fn slha_b200_score_tiles(tiles: *const SciRustSlhaTile, n: usize, q_coarse: *const f32, q_sign: *const u64, nq: usize, scores_out: *mut f32) -> i32;
     pub fn slha_b200_score_topk(tiles: *const SciRustSlhaTile, segments: *const SlhaB200Segment, n_segments: usize, q_coarse: *const f32, q_sign: *const u64, n_queries: usize, k: u32, out_index: *mut u32, out_score: *mut f32, out_count: *mut u32) -> i32;
     pub fn slha_b200_score_topk_noalloc(tiles: *const SciRustSlhaTile, segments: *const SlhaB200Segment, n_segments: usize, q_coarse: *const f32, q_sign: *const u64, n_queries: usize, k: u32, out_index: *mut u32, out_score: *mut f32, out_count: *mut u32) -> i32;
+    pub fn slha_b200_score_segments(tiles: *const SciRustSlhaTile, segments: *const SlhaB200Segment, n_segments: usize, q_coarse: *const f32, q_sign: *const u64, n_queries: usize, scores_out: *mut f32, scores_len: usize, row_offsets: *const u64, row_len: u32, fill: f32) -> i32;
     pub fn slha_b200_attend_topk(top_index: *const u32, top_score: *const f32, top_count: *const u32, n_queries: usize, k: u32, scale: f32, values: *const c_void, value_dtype: i32, d_v: usize, value_row_stride: usize, value_row_base: *const u64, out: *mut f32, weights_out: *mut f32) -> i32;
     pub fn slha_b200_shard_unique_id(id_out: *mut c_void) -> i32;
     pub fn slha_b200_shard_init(nccl_unique_id: *const c_void, rank: i32, world: i32, out: *mut *mut SlhaB200Shard) -> i32;

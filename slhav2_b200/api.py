@@ -85,6 +85,7 @@ SIGNATURES = {
     "slha_b200_encode_keys": (_i32, [_vp, _vp, _i32, _sz, _vp, _u32, _vp, _i32, _vp]),
     "slha_b200_prepare_queries": (_i32, [_vp, _vp, _sz, _vp, _vp]),
     "slha_b200_score_tiles": (_i32, [_vp, _sz, _vp, _vp, _sz, _vp]),
+    "slha_b200_score_segments": (_i32, [_vp, _vp, _sz, _vp, _vp, _sz, _vp, _sz, _vp, _u32, C.c_float]),
     "slha_b200_score_topk": (_i32, [_vp, _vp, _sz, _vp, _vp, _sz, _u32, _vp, _vp, _vp]),
     "slha_b200_score_topk_noalloc": (_i32, [_vp, _vp, _sz, _vp, _vp, _sz, _u32, _vp, _vp, _vp]),
     "slha_b200_topk_merge": (_i32, [_vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
@@ -376,6 +377,17 @@ def score_tiles(tiles, n, q_coarse, q_sign, nq, out=None):
     if out is None:
         out = np.zeros((nq, n), np.float32)
     _check(load_library().slha_b200_score_tiles(ptr(tiles), n, ptr(_np(q_coarse, np.float32)), ptr(_np(q_sign, np.uint64)), nq, ptr(out)))
+    return out
+
+
+def score_segments(tiles, segments, q_coarse, q_sign, nq, out, row_offsets, row_len, fill=0.0):
+    """Dense scores of whole segments in one call (the llama.cpp shim's per-layer scoring step): row q of `out`
+    starts at element row_offsets[q]; see slha_b200_score_segments."""
+    seg = np.ascontiguousarray(segments, SEGMENT_DTYPE)
+    off = _np(row_offsets, np.uint64)
+    n_out = out.numel() if hasattr(out, "numel") else (out.size if hasattr(out, "size") else out.nbytes // 4)
+    _check(load_library().slha_b200_score_segments(ptr(tiles), ptr(seg), len(seg), ptr(_np(q_coarse, np.float32)), ptr(_np(q_sign, np.uint64)),
+                                                   nq, ptr(out), n_out, ptr(off), row_len, fill))
     return out
 
 

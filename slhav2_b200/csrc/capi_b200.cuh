@@ -195,6 +195,42 @@ int32_t slha_b200_score_tiles(const SciRustSlhaTile* tiles, size_t n, const floa
     });
 }
 
+int32_t slha_b200_score_segments(const SciRustSlhaTile* tiles, const SlhaB200Segment* segments, size_t n_segments,
+                                 const float* q_coarse, const uint64_t* q_sign, size_t n_queries, float* scores_out,
+                                 size_t scores_len, const uint64_t* row_offsets, uint32_t row_len, float fill) {
+    return ffi([&]() -> Status {
+        if (n_queries == 0 || n_segments == 0) return Status();
+        if (!tiles || !segments || !q_coarse || !q_sign || !scores_out || !row_offsets)
+            return Status(SLHA_ERR_NULL, "slha_b200_score_segments received a NULL pointer");
+        if (!is_device_ptr(tiles)) return Status(SLHA_ERR_DEVICE, "slha_b200_score_segments: tiles must be device memory");
+        CallScope cs;
+        if (!cs.ok()) return cs.st;
+        Ctx* c = cs.c;
+        std::vector<SlhaB200Segment> hseg(n_segments);
+        std::vector<uint64_t> hoff(n_queries);
+        if (is_device_ptr(segments)) SLHA_CUDA(cudaMemcpy(hseg.data(), segments, n_segments * sizeof(SlhaB200Segment), cudaMemcpyDeviceToHost));
+        else std::memcpy(hseg.data(), segments, n_segments * sizeof(SlhaB200Segment));
+        if (is_device_ptr(row_offsets)) SLHA_CUDA(cudaMemcpy(hoff.data(), row_offsets, n_queries * 8, cudaMemcpyDeviceToHost));
+        else std::memcpy(hoff.data(), row_offsets, n_queries * 8);
+        for (size_t q = 0; q < n_queries; ++q)
+            if (hoff[q] > scores_len || (uint64_t)row_len > scores_len - hoff[q])
+                return Status(SLHA_ERR_DIMENSION, "slha_b200_score_segments: a row reaches beyond scores_len");
+        const float* dq;
+        const uint64_t* ds;
+        const uint64_t* doff;
+        SLHA_TRY(stage_in_t(c, q_coarse, n_queries * D_C, &dq));
+        SLHA_TRY(stage_in_t(c, q_sign, n_queries * 4, &ds));
+        SLHA_TRY(stage_in_t(c, row_offsets, n_queries, &doff));
+        std::vector<StagedOut> outs(1);
+        SLHA_TRY(stage_out(c, scores_out, scores_len * 4, &outs[0]));
+        // a host destination comes back whole: what no row covers is zero
+        if (outs[0].is_host) SLHA_CUDA(cudaMemsetAsync(outs[0].dev, 0, scores_len * 4, c->stream));
+        SLHA_TRY(launch_score_segments(c, tiles, hseg.data(), n_segments, dq, ds, n_queries, (float*)outs[0].dev,
+                                       reinterpret_cast<const unsigned long long*>(doff), row_len, fill));
+        return finish_outputs(c, outs, sync_by_default(c));
+    });
+}
+
 int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment* segments, size_t n_segments,
                              const float* q_coarse, const uint64_t* q_sign, size_t n_queries, uint32_t k,
                              uint32_t* out_index, float* out_score, uint32_t* out_count) {

@@ -96,6 +96,9 @@ struct Model {
 // ---- kernels' host launchers (score.cu / encode.cu / pool.cu) -------------
 struct ScorePlan;  // cached work decomposition of one slha_b200_score_topk call shape
 
+Status launch_score_segments(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* segs, size_t n_segs, const float* d_q_coarse,
+                             const uint64_t* d_q_sign, size_t nq, float* d_scores, const unsigned long long* d_row_offsets,
+                             uint32_t row_len, float fill);
 Status launch_score_full(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* state, size_t n,
                          const float* q_coarse, const uint64_t* q_sign, size_t nq, float* scores);
 // d_status must hold ~0ull on entry; receives min over bad tiles of (index << 8 | code) with

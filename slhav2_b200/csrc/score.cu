@@ -279,6 +279,9 @@ struct ScoreArgs {
     // full mode
     float* scores;            // [nq][score_stride]
     uint64_t score_stride;
+    const unsigned long long* row_offset;  // optional (full-score mode): row q starts at scores + row_offset[q] instead of q * score_stride
+    uint32_t row_len;         // with row_offset: work items marked as the last of their segment fill the row's elements
+    float row_fill;           //   [index_base + n_tiles, row_len) with row_fill
     // top-k mode
     uint32_t k, cap;
     uint32_t list_cap;        // slots per candidate list (>= k)
@@ -406,8 +409,8 @@ __global__ void __launch_bounds__(256) score_kernel(ScoreArgs a) {
                             if (comp >= pivot[g]) keys[(size_t)g * a.cap + atomicAdd(&cnt[g], 1)] = comp;
                         }
                     } else if (ti < n) {
-                        a.scores[(size_t)(it.query_begin + g) * a.score_stride + it.index_base + ti] =
-                            live ? sc : -INFINITY;
+                        const size_t row0 = a.row_offset ? (size_t)a.row_offset[it.query_begin + g] : (size_t)(it.query_begin + g) * a.score_stride;
+                        a.scores[row0 + it.index_base + ti] = live ? sc : -INFINITY;
                     }
                 }
             }
@@ -430,6 +433,13 @@ __global__ void __launch_bounds__(256) score_kernel(ScoreArgs a) {
         }
     }
     cp_async_wait<0>();
+    if (!TOPK && a.row_offset && it.pad) {
+        // the last work item of a segment: the rest of the rows up to row_len
+        for (uint32_t g = 0; g < it.n_queries; ++g) {
+            float* row = a.scores + a.row_offset[it.query_begin + g];
+            for (uint32_t e = it.index_base + it.n_tiles + (uint32_t)tid; e < a.row_len; e += blockDim.x) row[e] = a.row_fill;
+        }
+    }
     if (TOPK) {
         __syncthreads();
         for (int g = 0; g < (int)it.n_queries; ++g) {

@@ -36,6 +36,9 @@ Status launch_score_t(Ctx* c, const ScoreArgs& a, uint32_t grid, int threads, si
     if (configured[dev] < smem) {
         SLHA_CUDA(cudaFuncSetAttribute(score_kernel<G, TOPK>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+        // every kernel of a scoring call asks for the same shared-memory / L1 split, so that an SM does not have to
+        // be drained and reconfigured between the kernels of one call
+        SLHA_CUDA(cudaFuncSetAttribute(score_kernel<G, TOPK>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured[dev] = MAX_SMEM;
     }
     score_kernel<G, TOPK><<<grid, threads, smem, c->stream>>>(a);
@@ -383,7 +386,8 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     p->gstate_bytes = nq * (1024 + 8 + 8 + 4 + 4 + 4 + 8);  // histogram, threshold, mapping, count, flag, compacted count, statistics
     p->state_clean = false;
     // few rows with long buffers: several CTAs per row compact the survivors before the merge
-    p->compact_splits = (p->use_mma && nq < 128 && p->gcap >= 8192) ? (uint32_t)std::min<size_t>(32, (296 + nq - 1) / nq) : 0;
+    // (a slice of at most 1024 slots per CTA: one round of four keys per thread)
+    p->compact_splits = (p->use_mma && nq < 128 && p->gcap >= 8192) ? (uint32_t)std::min<size_t>(64, std::max<size_t>((296 + nq - 1) / nq, (p->gcap + 1023) / 1024)) : 0;
     p->selcap = merge_cap((uint64_t)p->gcap, p->kp2, k);
     if (p->compact_splits) SLHA_TRY(p->b_gsel.ensure(nq * (size_t)p->selcap * 8));
     SLHA_TRY(p->b_gpivot.ensure(p->gstate_bytes));
@@ -488,6 +492,51 @@ Status launch_score_full(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
     return Status();
 }
 
+// Dense scores of whole segments in one launch: every query row of a segment against every tile of the segment,
+// row q written at scores + row_offsets[q] + index_base + tile, the rest of the row up to row_len set to `fill`.
+// Work items: (segment, group of up to four query rows, run of 4096 tiles) on the generic kernel.
+Status launch_score_segments(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* segs, size_t n_segs, const float* d_q_coarse,
+                             const uint64_t* d_q_sign, size_t nq, float* d_scores, const unsigned long long* d_row_offsets,
+                             uint32_t row_len, float fill) {
+    const uint32_t item_tiles = 4096;
+    std::vector<WorkItem> items;
+    for (size_t i = 0; i < n_segs; ++i) {
+        const SlhaB200Segment& s = segs[i];
+        if ((uint64_t)s.query_begin + s.n_queries > nq) return Status(SLHA_ERR_DIMENSION, "segment query range exceeds n_queries");
+        if ((uint64_t)s.index_base + s.n_tiles > row_len) return Status(SLHA_ERR_DIMENSION, "segment does not fit a row of row_len scores");
+        for (uint32_t q0 = 0; q0 < s.n_queries; q0 += 4) {
+            uint32_t pos = 0;
+            do {  // (a segment without tiles still fills its rows)
+                WorkItem w{};
+                w.tile_begin = s.tile_begin + pos;
+                w.n_tiles = std::min<uint32_t>(item_tiles, s.n_tiles - pos);
+                w.index_base = s.index_base + pos;
+                w.query_begin = s.query_begin + q0;
+                w.n_queries = std::min<uint32_t>(4, s.n_queries - q0);
+                pos += w.n_tiles;
+                w.pad = pos >= s.n_tiles ? 1u : 0u;
+                items.push_back(w);
+            } while (pos < s.n_tiles);
+        }
+    }
+    if (items.empty()) return Status();
+    WorkItem* d_items;
+    SLHA_TRY(ctx_device_scratch(c, items.size() * sizeof(WorkItem), (void**)&d_items));
+    SLHA_CUDA(cudaMemcpyAsync(d_items, items.data(), items.size() * sizeof(WorkItem), cudaMemcpyHostToDevice, c->stream));
+    SLHA_CUDA(cudaStreamSynchronize(c->stream));  // (the host vector goes away)
+    const int threads = 128, nwarps = threads / 32;
+    ScoreArgs a{};
+    a.tiles = reinterpret_cast<const unsigned char*>(tiles);
+    a.items = d_items;
+    a.q_coarse = d_q_coarse;
+    a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);
+    a.scores = d_scores;
+    a.row_offset = d_row_offsets;
+    a.row_len = row_len;
+    a.row_fill = fill;
+    return launch_score<false>(c, 4, a, (uint32_t)items.size(), threads, score_smem_bytes(4, nwarps, false, 0));
+}
+
 Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* state,
                          const SlhaB200Segment* segs, size_t n_segs, const float* d_q_coarse,
                          const uint64_t* d_q_sign, size_t nq, uint32_t k, uint32_t* d_out_index,
@@ -576,6 +625,10 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<CompLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<StreamLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+        SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<CompLists>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<StreamLists>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        SLHA_CUDA(cudaFuncSetAttribute(stream_compact_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured[c->device & 15] = true;
     }
     if (mma) {

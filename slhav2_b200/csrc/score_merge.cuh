@@ -120,16 +120,24 @@ __global__ void __launch_bounds__(256) stream_compact_kernel(const uint64_t* gbu
             const uint32_t j = j0 + u * blockDim.x + tid;
             key[u] = j < hi ? src[j] : 0ull;
         }
+        // one reservation per warp for the four keys of its lanes (the slice of a CTA is one such round when the
+        // launch has enough splits, so a CTA pays one load and one atomic round trip)
+        unsigned bal[4];
+        uint32_t tot = 0;
 #pragma unroll
         for (uint32_t u = 0; u < 4; ++u) {
-            const bool keep = key[u] != 0ull && key[u] >= pv;
-            const unsigned bal = __ballot_sync(0xFFFFFFFFu, keep);
-            if (!bal) continue;
-            uint32_t base = 0;
-            if (lane == 0) base = atomicAdd(gselcnt + Q, (uint32_t)__popc(bal));
-            base = __shfl_sync(0xFFFFFFFFu, base, 0);
-            const uint32_t at = base + (uint32_t)__popc(bal & ((1u << lane) - 1u));
-            if (keep && at < selcap) dst[at] = key[u];
+            bal[u] = __ballot_sync(0xFFFFFFFFu, key[u] != 0ull && key[u] >= pv);
+            tot += (uint32_t)__popc(bal[u]);
+        }
+        if (!tot) continue;
+        uint32_t base = 0;
+        if (lane == 0) base = atomicAdd(gselcnt + Q, tot);
+        base = __shfl_sync(0xFFFFFFFFu, base, 0);
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+            const uint32_t at = base + (uint32_t)__popc(bal[u] & ((1u << lane) - 1u));
+            if ((bal[u] >> lane & 1u) && at < selcap) dst[at] = key[u];
+            base += (uint32_t)__popc(bal[u]);
         }
     }
 }
@@ -220,6 +228,18 @@ __host__ __device__ inline int merge_buckets(uint32_t kp2, uint32_t nt) {
     return (int)(nb > 4u * nt ? 4u * nt : nb);
 }
 
+// The k outputs of query Q from keys sorted descending, the first m of them valid.
+__device__ __forceinline__ void emit_sorted(const uint64_t* sorted, uint32_t m, uint32_t k, uint32_t Q, uint32_t* out_index, float* out_score,
+                                            uint32_t* out_count) {
+    for (uint32_t r = threadIdx.x; r < k; r += blockDim.x) {
+        const bool v = r < m;
+        const uint64_t key = v ? sorted[r] : 0ull;
+        out_index[(size_t)Q * k + r] = v ? 0xFFFFFFFFu - (uint32_t)key : 0xFFFFFFFFu;
+        out_score[(size_t)Q * k + r] = v ? key_score((uint32_t)(key >> 32)) : -INFINITY;
+    }
+    if (out_count && threadIdx.x == 0) out_count[Q] = m;
+}
+
 // Sort the m winners in buf[0..m) (buf[m..kp2) is zero) descending and write the k outputs of
 // query Q.  buf has cap_s >= kp2 slots; with m more beyond kp2 the bucket placement above is used,
 // otherwise (or when it declines) a bitonic sort of buf[0..kp2), kp2 a power of two.
@@ -249,13 +269,7 @@ __device__ void sort_and_emit(uint64_t* buf, uint32_t cap_s, int* hist, uint32_t
         }
         __syncthreads();
     }
-    for (uint32_t r = tid; r < k; r += nt) {
-        const bool v = r < m;
-        const uint64_t key = v ? sorted[r] : 0ull;
-        out_index[(size_t)Q * k + r] = v ? 0xFFFFFFFFu - (uint32_t)key : 0xFFFFFFFFu;
-        out_score[(size_t)Q * k + r] = v ? key_score((uint32_t)(key >> 32)) : -INFINITY;
-    }
-    if (out_count && tid == 0) out_count[Q] = m;
+    emit_sorted(sorted, m, k, Q, out_index, out_score, out_count);
 }
 
 // cap_s: candidate slots of the shared-memory buffer (>= kp2).  When the query's
@@ -307,6 +321,15 @@ __device__ __forceinline__ void topk_merge_body(const Lists& L, uint32_t k, uint
         const uint32_t present = (uint32_t)*n_s;
         __syncthreads();
         if (present > k) {
+            // Lists filtered by a threshold that is proven to keep k candidates hold only a few percent more than k:
+            // ordering them all and writing the first k is cheaper than selecting the k first.
+            const uint32_t pa = (present + 1u) & ~1u;
+            if (Lists::kFiltered && present <= k + (k >> 2) && 2 * pa <= cap_s && (nt == 256 || nt == 512) &&
+                bucket_sort(buf, buf + pa, present, hist, merge_buckets(kp2, nt))) {
+                emit_sorted(buf + pa, k, k, Q, out_index, out_score, out_count);
+                return;
+            }
+            __syncthreads();
             // bucket selection on the score word; equal scores around the k-th place
             // fall back to the exact radix selection, which also orders by index
             if (tid == 0) *pivot_s = 0ull;

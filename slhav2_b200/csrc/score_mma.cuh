@@ -708,6 +708,43 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         const WorkItem it = a.items[item_id];
         const int nq = (int)it.n_queries;
         __syncthreads();  // previous item fully retired (and the table is visible)
+        // The first sets are fetched before anything else of the item is prepared: the copy runs while the query
+        // fragments are built.
+        const uint8_t* sbase = a.state ? a.state + it.tile_begin : nullptr;
+        const uint32_t n = it.n_tiles;
+        uint32_t n_sets = (n + MMA_SET_TILES - 1) / MMA_SET_TILES;
+        const uint32_t n_full = n / MMA_SET_TILES;
+        const bool mine = t < nq;
+        const uint32_t Qt = it.query_begin + (mine ? (uint32_t)t : 0u);  // the row whose scores this thread finishes
+        uint64_t* const dst = a.gbuf + (size_t)Qt * a.gcap;                // the row's candidate buffer
+        uint32_t* const hrow = a.ghist + (size_t)Qt * 256;                 // and its histogram
+        // sets are dealt to the warps round by round: warp w takes set j * nwarps + w of round j
+        const unsigned char* tbase = a.tiles + it.tile_begin * TILE_BYTES + lane * 16;
+        uint32_t s_next = (uint32_t)warp, slot_next = 0;
+        auto issue = [&]() {
+            if (s_next < n_sets) {
+                const uint32_t dst = stage_s + slot_next + dst_lane;
+                const unsigned char* src = tbase + (size_t)s_next * MMA_SET_BYTES;
+                if (s_next < n_full) {
+                    cp_async16_s<0, 0>(dst, src, 16);
+                    cp_async16_s<512, 4 * MMA_ROW>(dst, src, 16);
+                    cp_async16_s<1024, 8 * MMA_ROW>(dst, src, 16);
+                    cp_async16_s<1536, 12 * MMA_ROW>(dst, src, 16);
+                } else {
+                    // ragged last set: rows past the end are zero-filled (source not read)
+                    const uint32_t r = s_next * MMA_SET_TILES + (uint32_t)(lane >> 3);
+                    cp_async16_s<0, 0>(dst, r < n ? src : a.tiles, r < n ? 16 : 0);
+                    cp_async16_s<0, 4 * MMA_ROW>(dst, r + 4 < n ? src + 512 : a.tiles, r + 4 < n ? 16 : 0);
+                    cp_async16_s<0, 8 * MMA_ROW>(dst, r + 8 < n ? src + 1024 : a.tiles, r + 8 < n ? 16 : 0);
+                    cp_async16_s<0, 12 * MMA_ROW>(dst, r + 12 < n ? src + 1536 : a.tiles, r + 12 < n ? 16 : 0);
+                }
+            }
+            cp_async_commit();
+            s_next += (uint32_t)nwarps;
+            slot_next = slot_next == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot_next + MMA_SET_STRIDE;
+        };
+#pragma unroll
+        for (int i = 0; i < MMA_DEPTH - 1; ++i) issue();
         bool row_warm = true;
         if (tid < 4) {
             // start from the threshold other CTAs have already proven for the row, and from the
@@ -788,42 +825,8 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         const bool first_round_barrier = !all_warm && (uint64_t)a.k <= 16ull * (uint64_t)nwarps * (uint64_t)max(it.pad >> 8, 1u);
         PROBE_SET(1);
         const bool too_big = bail[0] != 0;
+        if (too_big) n_sets = 0;  // (the sets already on their way are waited for at the item's end and never read)
 
-        const uint8_t* sbase = a.state ? a.state + it.tile_begin : nullptr;
-        const uint32_t n = it.n_tiles;
-        const uint32_t n_sets = too_big ? 0u : (n + MMA_SET_TILES - 1) / MMA_SET_TILES;
-        const uint32_t n_full = n / MMA_SET_TILES;
-        const bool mine = t < nq;
-        const uint32_t Qt = it.query_begin + (mine ? (uint32_t)t : 0u);  // the row whose scores this thread finishes
-        uint64_t* const dst = a.gbuf + (size_t)Qt * a.gcap;                // the row's candidate buffer
-        uint32_t* const hrow = a.ghist + (size_t)Qt * 256;                 // and its histogram
-        // sets are dealt to the warps round by round: warp w takes set j * nwarps + w of round j
-        const unsigned char* tbase = a.tiles + it.tile_begin * TILE_BYTES + lane * 16;
-        uint32_t s_next = (uint32_t)warp, slot_next = 0;
-        auto issue = [&]() {
-            if (s_next < n_sets) {
-                const uint32_t dst = stage_s + slot_next + dst_lane;
-                const unsigned char* src = tbase + (size_t)s_next * MMA_SET_BYTES;
-                if (s_next < n_full) {
-                    cp_async16_s<0, 0>(dst, src, 16);
-                    cp_async16_s<512, 4 * MMA_ROW>(dst, src, 16);
-                    cp_async16_s<1024, 8 * MMA_ROW>(dst, src, 16);
-                    cp_async16_s<1536, 12 * MMA_ROW>(dst, src, 16);
-                } else {
-                    // ragged last set: rows past the end are zero-filled (source not read)
-                    const uint32_t r = s_next * MMA_SET_TILES + (uint32_t)(lane >> 3);
-                    cp_async16_s<0, 0>(dst, r < n ? src : a.tiles, r < n ? 16 : 0);
-                    cp_async16_s<0, 4 * MMA_ROW>(dst, r + 4 < n ? src + 512 : a.tiles, r + 4 < n ? 16 : 0);
-                    cp_async16_s<0, 8 * MMA_ROW>(dst, r + 8 < n ? src + 1024 : a.tiles, r + 8 < n ? 16 : 0);
-                    cp_async16_s<0, 12 * MMA_ROW>(dst, r + 12 < n ? src + 1536 : a.tiles, r + 12 < n ? 16 : 0);
-                }
-            }
-            cp_async_commit();
-            s_next += (uint32_t)nwarps;
-            slot_next = slot_next == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot_next + MMA_SET_STRIDE;
-        };
-#pragma unroll
-        for (int i = 0; i < MMA_DEPTH - 1; ++i) issue();
         uint32_t slot = 0, polls = 0;
         uint32_t cur = 0, end = 0;  // this warp's chunk of the buffer of row Qt (the same in the eight lanes of a query)
         bool dead = false;          // this warp met a tile it cannot decode

@@ -89,3 +89,49 @@ def test_device_resident_inputs_and_outputs():
     S.synchronize()
     _close(dout.download(F, n * nq).reshape(nq, n), H.oracle_scores(tiles, qc, qs))
     assert S.launch_count() > 0
+
+
+def test_score_segments_writes_a_layer_of_dense_rows_in_one_call():
+    # The llama.cpp shim's layout (integration/llama.cpp/shim/slha_llama.cpp:1387-1503): dst[head][token][n_kv] with
+    # n_kv padded beyond the tiles that exist; one segment per KV head, its query rows the (token, head) vectors of
+    # the GQA group in token-major order.  Codecs differ per KV head; one head has no tiles yet.
+    n_kv_head, gqa, n_token, n_kv = 3, 2, 5, 6000
+    written = [4099, 0, 5000]
+    codecs = [0, 3, 4]
+    tiles = np.concatenate([H.random_tiles(max(w, 1), c, seed=40 + c, warm_every=9)[:w] for w, c in zip(written, codecs)])
+    dt = S.to_device(tiles)
+    n_head = n_kv_head * gqa
+    qc, qs = H.random_queries(n_token * n_head, 77)  # query row = t * n_head + h
+    # rows of the launch: per KV head, (token, head in group); destination element offset of row (t, h): (h * n_token + t) * n_kv
+    order, offsets, segs, begin = [], [], [], 0
+    for kvh in range(n_kv_head):
+        rows = [(t, kvh * gqa + j) for t in range(n_token) for j in range(gqa)]
+        segs.append((begin, written[kvh], len(order), len(rows), 0))
+        begin += written[kvh]
+        for t, h in rows:
+            order.append(t * n_head + h)
+            offsets.append((h * n_token + t) * n_kv)
+    qc_l, qs_l = qc[order], qs[order]
+    out = np.full((n_head, n_token, n_kv), 123.0, F)
+    S.score_segments(dt, S.make_segments(segs), qc_l, qs_l, len(order), out, offsets, n_kv, fill=0.0)
+    begin = 0
+    for kvh in range(n_kv_head):
+        seg_tiles = tiles[begin:begin + written[kvh]]
+        begin += written[kvh]
+        for j in range(gqa):
+            h = kvh * gqa + j
+            for t in range(n_token):
+                q = t * n_head + h
+                if written[kvh]:
+                    _close(out[h, t, :written[kvh]], H.oracle_scores(seg_tiles, qc[q:q + 1], qs[q:q + 1])[0])
+                assert np.all(out[h, t, written[kvh]:] == 0.0)
+    # device destination, rows that cover only part of it: the rest stays as it was
+    dev = S.to_device(np.full(4 * n_kv, 7.0, F))
+    S.score_segments(dt, S.make_segments([(0, written[0], 0, 2, 0)]), qc_l[:2], qs_l[:2], 2, dev, [0, 2 * n_kv], n_kv, fill=-1.0)
+    got = dev.download(F, 4 * n_kv).reshape(4, n_kv)
+    _close(got[0, :written[0]], H.oracle_scores(tiles[:written[0]], qc_l[:1], qs_l[:1])[0])
+    assert np.all(got[0, written[0]:] == -1.0) and np.all(got[2, written[0]:] == -1.0) and np.all(got[1] == 7.0) and np.all(got[3] == 7.0)
+    # a row that would reach beyond the destination is refused
+    with pytest.raises(S.SlhaError) as e:
+        S.score_segments(dt, S.make_segments([(0, 10, 0, 1, 0)]), qc_l[:1], qs_l[:1], 1, dev, [3 * n_kv + 1], n_kv)
+    assert e.value.code == S.ERR_DIMENSION
