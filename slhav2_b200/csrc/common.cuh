@@ -121,7 +121,7 @@ Status timing_begin(uint32_t max_calls);
 Status timing_end(Ctx* c, float* score_ms, float* merge_ms, uint32_t capacity, uint32_t* n_out);
 Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* cand_score,
                                uint32_t n_lists, uint64_t list_stride, uint32_t n_queries, uint32_t k_in,
-                               uint32_t k_out, uint32_t* out_index, float* out_score);
+                               uint32_t k_out, uint32_t* out_index, float* out_score, bool lists_sorted = false);
 
 // ---- token-range sharding over NCCL (shard.cu) ----------------------------------
 struct Shard;

@@ -245,6 +245,8 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     item_tiles = std::max(round, (item_tiles + round - 1) / round * round);
     uint64_t share = (total + p->mma_grid - 1) / std::max<uint32_t>(p->mma_grid, 1);
     share = std::max<uint64_t>(2048, (share + MMA_SET_TILES - 1) / MMA_SET_TILES * MMA_SET_TILES);
+    const uint64_t snap = std::min<uint64_t>(share / 16, 2048);
+    uint64_t spare = share * std::max<uint32_t>(p->mma_grid, 1) > total ? share * std::max<uint32_t>(p->mma_grid, 1) - total : 0;  // room the equal shares leave
     uint64_t filled = 0;  // tiles already given to the current CTA (tensor-core mode)
     std::vector<uint32_t> cta_begin(1, 0);
 
@@ -263,14 +265,27 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
             for (uint32_t pos = 0; pos < s.n_tiles;) {
                 uint32_t take;
                 if (p->use_mma) {
+                    // A work item costs its set-up and first set (several microseconds) whatever its length, so cuts that
+                    // would leave a sliver are moved to the segment's end: a CTA with little room left does not start the
+                    // next segment, and a cut that would leave a short rest of a segment takes the rest along.
+                    if (pos == 0 && filled > 0 && share - filled < snap && spare >= share - filled) {
+                        spare -= share - filled;  // (the grid must not grow beyond one CTA per SM)
+                        filled = 0;
+                        cta_begin.push_back((uint32_t)items[2].size() + (uint32_t)cuts.size());
+                    }
                     take = (uint32_t)std::min<uint64_t>(s.n_tiles - pos, share - filled);
+                    const uint32_t rest = s.n_tiles - pos - take;
+                    if (rest > 0 && rest < snap) {
+                        take += rest;
+                        spare += rest;
+                    }
                     filled += take;
                 } else {
                     take = std::min<uint32_t>(item_tiles, s.n_tiles - pos);
                 }
                 cuts.push_back({pos, take});
                 pos += take;
-                if (p->use_mma && filled == share) {
+                if (p->use_mma && filled >= share) {
                     filled = 0;
                     cta_begin.push_back((uint32_t)items[2].size() + (uint32_t)cuts.size());
                 }
@@ -655,7 +670,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
             L1, k, p->kp2, cap1, p->d_tmp_index, p->d_tmp_score, nullptr);
         count_launch();
         SLHA_CUDA(cudaGetLastError());
-        PairLists L2{p->d_tmp_index, p->d_tmp_score, p->n_groups, (uint32_t)nq, k, (uint64_t)nq * k};
+        PairLists L2{p->d_tmp_index, p->d_tmp_score, p->n_groups, (uint32_t)nq, k, (uint64_t)nq * k, 1u};
         const uint32_t cap2 = merge_cap((uint64_t)p->n_groups * k, p->kp2, k);
         topk_merge_kernel<PairLists><<<(uint32_t)nq, merge_threads(cap2), merge_smem(cap2, p->kp2), c->stream>>>(
             L2, k, p->kp2, cap2, d_out_index, d_out_score, d_out_count);
@@ -726,12 +741,12 @@ Status timing_end(Ctx* c, float* score_ms, float* merge_ms, uint32_t capacity, u
 
 Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* cand_score,
                                uint32_t n_lists, uint64_t list_stride, uint32_t n_queries, uint32_t k_in,
-                               uint32_t k_out, uint32_t* out_index, float* out_score) {
+                               uint32_t k_out, uint32_t* out_index, float* out_score, bool lists_sorted) {
     if (n_queries == 0) return Status();
     if (k_out == 0 || k_out > 8192) return Status(SLHA_ERR_DIMENSION, "merge: k_out must be in 1..8192");
     uint32_t kp2 = 2;
     while (kp2 < k_out) kp2 <<= 1;
-    PairLists L{cand_index, cand_score, n_lists, n_queries, k_in, list_stride};
+    PairLists L{cand_index, cand_score, n_lists, n_queries, k_in, list_stride, lists_sorted ? 1u : 0u};
     static thread_local bool configured[16] = {false};  // the attribute is per device
     if (!configured[c->device & 15]) {
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));

@@ -29,6 +29,7 @@ struct CompLists {  // lists written by score_kernel
         return j < cnt[l] ? keys[(size_t)l * k + j] : 0ull;
     }
     __device__ void finish(uint32_t) const {}
+    __device__ uint64_t floor_key(uint32_t, uint32_t) const { return 0ull; }
 };
 // Candidates of the streaming tensor-core kernel: one buffer per query row (keys below the row's
 // final threshold count as absent), or - for rows that kernel handed to the generic kernel - the
@@ -59,6 +60,7 @@ struct StreamLists {
     __device__ uint64_t get(uint32_t Q, uint32_t e) const { return gflag[Q] ? items.get(Q, e) : (e < len0(Q) ? at(Q, 0, e) : 0ull); }
     // The merge is the last reader of a row's streaming state: it leaves the state cleared for the next call
     // (which then needs no memset in front of its score kernel) and keeps the row's figures for the statistics call.
+    __device__ uint64_t floor_key(uint32_t, uint32_t) const { return 0ull; }  // (at() filters by the row's threshold already)
     uint32_t* ghist;     // [nq][256]; the state arrays follow it in one allocation
     uint32_t* stats;     // [nq][2] candidates appended, handed to the generic kernel
     __device__ void finish(uint32_t Q) const {
@@ -80,6 +82,19 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     const float* score;
     uint32_t n_lists, n_queries, k_in;
     uint64_t list_stride;  // elements between the blocks of consecutive lists
+    uint32_t sorted;       // every list is ordered best first (lists this library produced)
+    // A key that at least k candidates reach, from sorted lists alone: with p = ceil(k / n_lists) every list holds p
+    // candidates at or above its p-th entry, so n_lists * p >= k candidates reach the smallest of those entries.
+    // Shards of one context hold about k / n_lists of the k best each, so this bound sits just below the k-th best
+    // and the merge gathers little more than k keys instead of n_lists * k.  Zero: no bound.
+    __device__ uint64_t floor_key(uint32_t Q, uint32_t k) const {
+        if (!sorted || n_lists < 2) return 0ull;
+        const uint32_t p = (k + n_lists - 1) / n_lists;
+        if (p == 0 || p > k_in) return 0ull;
+        uint64_t lo = ~0ull;
+        for (uint32_t l = 0; l < n_lists; ++l) lo = min(lo, at(Q, l, p - 1));  // (an absent entry is key 0: no bound)
+        return lo;
+    }
     __device__ uint32_t size(uint32_t) const { return n_lists * k_in; }
     __device__ uint32_t lists(uint32_t) const { return n_lists; }
     __device__ uint32_t list_len(uint32_t, uint32_t) const { return k_in; }
@@ -291,7 +306,9 @@ __device__ __forceinline__ void topk_merge_body(const Lists& L, uint32_t k, uint
     // Lists that drop keys below a known threshold while they are read (Lists::kFiltered) hold far
     // fewer present keys than slots: one gathering pass usually fits them into shared memory.
     bool gathered = false;
-    if (total <= cap_s || Lists::kFiltered) {
+    const uint64_t floor_key = L.floor_key(Q, k);  // (the same in every thread)
+    const bool filtered = Lists::kFiltered || floor_key != 0ull;
+    if (total <= cap_s || filtered) {
         if (tid == 0) *n_s = 0;
         __syncthreads();
         for (uint32_t l = 0; l < L.lists(Q); ++l) {
@@ -300,7 +317,10 @@ __device__ __forceinline__ void topk_merge_body(const Lists& L, uint32_t k, uint
             for (uint32_t j0 = 0; j0 < len; j0 += 4 * nt) {
                 uint64_t key[4];
 #pragma unroll
-                for (uint32_t u = 0; u < 4; ++u) key[u] = j0 + u * nt + tid < len ? L.at(Q, l, j0 + u * nt + tid) : 0ull;
+                for (uint32_t u = 0; u < 4; ++u) {
+                    key[u] = j0 + u * nt + tid < len ? L.at(Q, l, j0 + u * nt + tid) : 0ull;
+                    if (key[u] < floor_key) key[u] = 0ull;
+                }
 #pragma unroll
                 for (uint32_t u = 0; u < 4; ++u) {
                     const unsigned bal = __ballot_sync(0xFFFFFFFFu, key[u] != 0ull);
@@ -324,7 +344,7 @@ __device__ __forceinline__ void topk_merge_body(const Lists& L, uint32_t k, uint
             // Lists filtered by a threshold that is proven to keep k candidates hold only a few percent more than k:
             // ordering them all and writing the first k is cheaper than selecting the k first.
             const uint32_t pa = (present + 1u) & ~1u;
-            if (Lists::kFiltered && present <= k + (k >> 2) && 2 * pa <= cap_s && (nt == 256 || nt == 512) &&
+            if (filtered && present <= k + (k >> 2) && 2 * pa <= cap_s && (nt == 256 || nt == 512) &&
                 bucket_sort(buf, buf + pa, present, hist, merge_buckets(kp2, nt))) {
                 emit_sorted(buf + pa, k, k, Q, out_index, out_score, out_count);
                 return;

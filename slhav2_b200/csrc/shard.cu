@@ -196,7 +196,7 @@ Status shard_enqueue(Ctx* c, Shard* s, const SciRustSlhaTile* tiles, const SlhaB
     if (s->timed) SLHA_CUDA(cudaEventRecord(s->ev[2], c->stream));
     const uint32_t* gi = (const uint32_t*)s->gathered.p;
     const float* gsc = reinterpret_cast<const float*>(gi + nq * (size_t)k);
-    SLHA_TRY(launch_topk_merge_pairs(c, gi, gsc, (uint32_t)s->world, block, (uint32_t)nq, k, k, d_out_index, d_out_score));
+    SLHA_TRY(launch_topk_merge_pairs(c, gi, gsc, (uint32_t)s->world, block, (uint32_t)nq, k, k, d_out_index, d_out_score, /*lists_sorted=*/true));
     if (s->timed) {
         SLHA_CUDA(cudaEventRecord(s->ev[3], c->stream));
         s->have_times = true;
