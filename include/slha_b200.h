@@ -423,6 +423,17 @@ int32_t slha_b200_topk_merge_strided(const uint32_t* cand_index, const float* ca
                                      uint32_t k_in, uint32_t k_out, uint32_t* out_index,
                                      float* out_score);
 
+/* Same, for lists that are each ordered best first with absent entries (index
+ * 0xFFFFFFFF) only at their ends -- what slha_b200_score_topk writes.  The
+ * merge then reads the lists' ceil(k_out / n_lists)-th entries first: the
+ * smallest of them is reached by at least k_out candidates, so only the keys
+ * at or above it are gathered (shards of one context leave little more than
+ * k_out of the n_lists * k_in).  Lists that are not ordered give wrong results. */
+int32_t slha_b200_topk_merge_sorted_strided(const uint32_t* cand_index, const float* cand_score,
+                                            uint32_t n_lists, uint64_t list_stride, uint32_t n_queries,
+                                            uint32_t k_in, uint32_t k_out, uint32_t* out_index,
+                                            float* out_score);
+
 /* -------- CCOS elastic tile pool (scirust/src/ccos.rs ElasticKvCache) -------- */
 
 typedef struct SlhaB200Pool SlhaB200Pool;

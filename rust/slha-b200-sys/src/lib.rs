@@ -163,6 +163,7 @@ extern "C" {
     pub fn slha_b200_shard_last_times(shard: *mut SlhaB200Shard, ms_out: *mut f32) -> i32;
     pub fn slha_b200_topk_merge(cand_index: *const u32, cand_score: *const f32, n_lists: u32, n_queries: u32, k_in: u32, k_out: u32, out_index: *mut u32, out_score: *mut f32) -> i32;
     pub fn slha_b200_topk_merge_strided(cand_index: *const u32, cand_score: *const f32, n_lists: u32, list_stride: u64, n_queries: u32, k_in: u32, k_out: u32, out_index: *mut u32, out_score: *mut f32) -> i32;
+    pub fn slha_b200_topk_merge_sorted_strided(cand_index: *const u32, cand_score: *const f32, n_lists: u32, list_stride: u64, n_queries: u32, k_in: u32, k_out: u32, out_index: *mut u32, out_score: *mut f32) -> i32;
     pub fn slha_b200_pool_create(config: *const SlhaB200PoolConfig, out: *mut *mut SlhaB200Pool) -> i32;
     pub fn slha_b200_pool_destroy(pool: *mut SlhaB200Pool) -> i32;
     pub fn slha_b200_pool_insert_tiles(pool: *mut SlhaB200Pool, tiles: *const SciRustSlhaTile, n: usize, slots_out: *mut u32) -> i32;

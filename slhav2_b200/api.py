@@ -90,6 +90,7 @@ SIGNATURES = {
     "slha_b200_score_topk_noalloc": (_i32, [_vp, _vp, _sz, _vp, _vp, _sz, _u32, _vp, _vp, _vp]),
     "slha_b200_topk_merge": (_i32, [_vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
     "slha_b200_topk_merge_strided": (_i32, [_vp, _vp, _u32, _u64, _u32, _u32, _u32, _vp, _vp]),
+    "slha_b200_topk_merge_sorted_strided": (_i32, [_vp, _vp, _u32, _u64, _u32, _u32, _u32, _vp, _vp]),
     "slha_b200_attend_topk": (_i32, [_vp, _vp, _vp, _sz, _u32, C.c_float, _vp, _i32, _sz, _sz, _vp, _vp, _vp]),
     "slha_b200_shard_unique_id": (_i32, [_vp]),
     "slha_b200_shard_init": (_i32, [_vp, _i32, _i32, C.POINTER(_vp)]),
@@ -429,16 +430,19 @@ def score_topk_noalloc(tiles, segments, q_coarse, q_sign, nq, k, out_index, out_
     )
 
 
-def topk_merge(cand_index, cand_score, n_lists, n_queries, k_in, k_out, out_index=None, out_score=None, list_stride=None):
-    """Merge per-shard top-k lists laid out [list][query][k_in] (list blocks `list_stride` elements apart)."""
+def topk_merge(cand_index, cand_score, n_lists, n_queries, k_in, k_out, out_index=None, out_score=None, list_stride=None,
+               lists_sorted=False):
+    """Merge per-shard top-k lists laid out [list][query][k_in] (list blocks `list_stride` elements apart);
+    lists_sorted: every list is ordered best first, as score_topk writes it (slha_b200_topk_merge_sorted_strided)."""
     if out_index is None:
         out_index = np.zeros((n_queries, k_out), np.uint32)
     if out_score is None:
         out_score = np.zeros((n_queries, k_out), np.float32)
     if list_stride is None:
         list_stride = n_queries * k_in
+    fn = load_library().slha_b200_topk_merge_sorted_strided if lists_sorted else load_library().slha_b200_topk_merge_strided
     _check(
-        load_library().slha_b200_topk_merge_strided(
+        fn(
             ptr(_np(cand_index, np.uint32)), ptr(_np(cand_score, np.float32)), n_lists, list_stride, n_queries, k_in,
             k_out, ptr(out_index), ptr(out_score),
         )

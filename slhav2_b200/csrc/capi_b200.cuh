@@ -286,9 +286,9 @@ int32_t slha_b200_score_topk_noalloc(const SciRustSlhaTile* tiles, const SlhaB20
     });
 }
 
-int32_t slha_b200_topk_merge_strided(const uint32_t* cand_index, const float* cand_score, uint32_t n_lists,
-                                     uint64_t list_stride, uint32_t n_queries, uint32_t k_in, uint32_t k_out,
-                                     uint32_t* out_index, float* out_score) {
+static int32_t topk_merge_any(const uint32_t* cand_index, const float* cand_score, uint32_t n_lists, uint64_t list_stride,
+                              uint32_t n_queries, uint32_t k_in, uint32_t k_out, uint32_t* out_index, float* out_score,
+                              bool lists_sorted) {
     return ffi([&]() -> Status {
         if (!cand_index || !cand_score || !out_index || !out_score)
             return Status(SLHA_ERR_NULL, "slha_b200_topk_merge received a NULL pointer");
@@ -306,9 +306,19 @@ int32_t slha_b200_topk_merge_strided(const uint32_t* cand_index, const float* ca
         SLHA_TRY(stage_out(c, out_index, (size_t)n_queries * k_out * 4, &outs[0]));
         SLHA_TRY(stage_out(c, out_score, (size_t)n_queries * k_out * 4, &outs[1]));
         SLHA_TRY(launch_topk_merge_pairs(c, di, dsc, n_lists, list_stride, n_queries, k_in, k_out,
-                                         (uint32_t*)outs[0].dev, (float*)outs[1].dev));
+                                         (uint32_t*)outs[0].dev, (float*)outs[1].dev, lists_sorted));
         return finish_outputs(c, outs, sync_by_default(c));
     });
+}
+int32_t slha_b200_topk_merge_strided(const uint32_t* cand_index, const float* cand_score, uint32_t n_lists,
+                                     uint64_t list_stride, uint32_t n_queries, uint32_t k_in, uint32_t k_out,
+                                     uint32_t* out_index, float* out_score) {
+    return topk_merge_any(cand_index, cand_score, n_lists, list_stride, n_queries, k_in, k_out, out_index, out_score, false);
+}
+int32_t slha_b200_topk_merge_sorted_strided(const uint32_t* cand_index, const float* cand_score, uint32_t n_lists,
+                                            uint64_t list_stride, uint32_t n_queries, uint32_t k_in, uint32_t k_out,
+                                            uint32_t* out_index, float* out_score) {
+    return topk_merge_any(cand_index, cand_score, n_lists, list_stride, n_queries, k_in, k_out, out_index, out_score, true);
 }
 int32_t slha_b200_topk_merge(const uint32_t* cand_index, const float* cand_score, uint32_t n_lists,
                              uint32_t n_queries, uint32_t k_in, uint32_t k_out, uint32_t* out_index,

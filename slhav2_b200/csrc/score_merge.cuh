@@ -8,6 +8,14 @@
 namespace slha {
 namespace {
 
+// A list as the gathering loop wants it: when `p` is set, its keys are p[0 .. len) and a key counts when it is
+// at least `pivot` (everything the accessors below would re-read per key, read once); else the loop asks at().
+struct ListView {
+    const uint64_t* p;
+    uint64_t pivot;
+    uint32_t len;
+};
+
 // Candidate accessors: element e of query Q as a composite key, 0 = absent.
 struct CompLists {  // lists written by score_kernel
     static constexpr bool kFiltered = false;
@@ -30,6 +38,10 @@ struct CompLists {  // lists written by score_kernel
     }
     __device__ void finish(uint32_t) const {}
     __device__ uint64_t floor_key(uint32_t, uint32_t) const { return 0ull; }
+    __device__ ListView view(uint32_t Q, uint32_t part) const {
+        const uint32_t l = q_list_begin[Q] + part * (q_list_count[Q] >> 24);
+        return ListView{keys + (size_t)l * k, 0ull, cnt[l]};
+    }
 };
 // Candidates of the streaming tensor-core kernel: one buffer per query row (keys below the row's
 // final threshold count as absent), or - for rows that kernel handed to the generic kernel - the
@@ -61,6 +73,11 @@ struct StreamLists {
     // The merge is the last reader of a row's streaming state: it leaves the state cleared for the next call
     // (which then needs no memset in front of its score kernel) and keeps the row's figures for the statistics call.
     __device__ uint64_t floor_key(uint32_t, uint32_t) const { return 0ull; }  // (at() filters by the row's threshold already)
+    __device__ ListView view(uint32_t Q, uint32_t part) const {
+        if (gflag[Q]) return items.view(Q, part);
+        if (compacted(Q)) return ListView{gsel + (size_t)Q * selcap, 0ull, gselcnt[Q]};
+        return ListView{gbuf + (size_t)Q * gcap, gpivot[Q], min(gcount[Q], gcap)};
+    }
     uint32_t* ghist;     // [nq][256]; the state arrays follow it in one allocation
     uint32_t* stats;     // [nq][2] candidates appended, handed to the generic kernel
     __device__ void finish(uint32_t Q) const {
@@ -87,6 +104,7 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     // candidates at or above its p-th entry, so n_lists * p >= k candidates reach the smallest of those entries.
     // Shards of one context hold about k / n_lists of the k best each, so this bound sits just below the k-th best
     // and the merge gathers little more than k keys instead of n_lists * k.  Zero: no bound.
+    __device__ ListView view(uint32_t, uint32_t) const { return ListView{nullptr, 0ull, k_in}; }
     __device__ uint64_t floor_key(uint32_t Q, uint32_t k) const {
         if (!sorted || n_lists < 2) return 0ull;
         const uint32_t p = (k + n_lists - 1) / n_lists;
@@ -311,15 +329,19 @@ __device__ __forceinline__ void topk_merge_body(const Lists& L, uint32_t k, uint
     if (total <= cap_s || filtered) {
         if (tid == 0) *n_s = 0;
         __syncthreads();
-        for (uint32_t l = 0; l < L.lists(Q); ++l) {
-            const uint32_t len = L.list_len(Q, l);
+        const uint32_t n_lists_q = L.lists(Q);
+        for (uint32_t l = 0; l < n_lists_q; ++l) {
+            const ListView V = L.view(Q, l);
+            const uint32_t len = V.len;
+            const uint64_t low = V.p ? (V.pivot > floor_key ? V.pivot : floor_key) : floor_key;
             // four keys per round: the loads go out together, then the compaction
             for (uint32_t j0 = 0; j0 < len; j0 += 4 * nt) {
                 uint64_t key[4];
 #pragma unroll
                 for (uint32_t u = 0; u < 4; ++u) {
-                    key[u] = j0 + u * nt + tid < len ? L.at(Q, l, j0 + u * nt + tid) : 0ull;
-                    if (key[u] < floor_key) key[u] = 0ull;
+                    const uint32_t j = j0 + u * nt + tid;
+                    key[u] = j < len ? (V.p ? V.p[j] : L.at(Q, l, j)) : 0ull;
+                    if (key[u] < low) key[u] = 0ull;
                 }
 #pragma unroll
                 for (uint32_t u = 0; u < 4; ++u) {

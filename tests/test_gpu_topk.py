@@ -91,6 +91,28 @@ def test_topk_merge_of_shard_lists():
     assert np.array_equal(mi, full[0]) and np.array_equal(ms, full[1])
 
 
+@pytest.mark.parametrize("n_lists,k,skew", [(2, 256, 1.0), (8, 2048, 1.0), (8, 2048, 4.0), (5, 300, 0.0), (3, 64, 1.0)])
+def test_merge_of_sorted_lists_uses_a_proven_floor_and_gives_the_same_answer(n_lists, k, skew):
+    # lists ordered best first, as score_topk writes them: the merge gathers only the keys at or above the smallest
+    # ceil(k / n_lists)-th entry.  Even shards, a shard that holds most of the winners (skew: its scores are shifted
+    # up), equal scores everywhere (skew 0: ties decided by index), short lists with absent entries at their ends.
+    from slhav2_b200 import shard
+
+    rng = np.random.default_rng(100 + n_lists)
+    nq, k_in = 5, k
+    sc = rng.standard_normal((n_lists, nq, k_in)).astype(F) if skew else np.zeros((n_lists, nq, k_in), F)
+    sc[0] += F(skew if skew != 1.0 else 0.0)
+    idx = rng.permutation(n_lists * nq * k_in).astype(np.uint32).reshape(n_lists, nq, k_in)
+    order = np.lexsort((idx, -sc), axis=-1)  # best first, ties to the lower index
+    sc, idx = np.take_along_axis(sc, order, -1), np.take_along_axis(idx, order, -1)
+    idx[1, 2, k_in // 3:] = 0xFFFFFFFF  # a short list: fewer than ceil(k / n_lists) entries in one row disables the floor there
+    idx[n_lists - 1, 4, k_in - 3:] = 0xFFFFFFFF
+    wi, ws = shard.merge_reference(idx, sc, k)
+    for lists_sorted in (True, False):
+        mi, ms = S.topk_merge(idx, sc, n_lists, nq, k_in, k, lists_sorted=lists_sorted)
+        assert np.array_equal(mi, wi) and np.array_equal(ms, ws), lists_sorted
+
+
 def test_merge_with_more_candidates_than_the_shared_buffer():
     # 8 lists x 4096 candidates per query exceeds the in-shared-memory path
     rng = np.random.default_rng(3)
