@@ -633,6 +633,9 @@ Status score_topk_noalloc(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Se
 extern "C" int slha_debug_stream_probe(unsigned long long* out) {  // development build only
     return (int)cudaMemcpyFromSymbol(out, slha::g_stream_probe, sizeof(unsigned long long) * 160 * 8);
 }
+extern "C" int slha_debug_merge_probe(unsigned long long* out) {  // development build only
+    return (int)cudaMemcpyFromSymbol(out, slha::g_merge_probe, sizeof(unsigned long long) * 64 * 12);
+}
 extern "C" int slha_debug_wide_probe(unsigned long long* out) {  // development build only
     return (int)cudaMemcpyFromSymbol(out, slha::g_wide_probe, sizeof(unsigned long long) * 160 * 24);
 }

@@ -64,7 +64,8 @@ int group_width(uint32_t nq) { return nq >= 3 ? 4 : (int)nq; }
 // kernel's bucket pre-filter, which gathers only k plus one bucket of candidates, and a small buffer
 // lets more CTAs share an SM.
 uint32_t merge_cap(uint64_t total, uint32_t kp2, uint32_t k) {
-    const uint64_t enough = ((uint64_t)kp2 + k + 256 + 255) / 256 * 256;
+    // (and room to order up to 1.5 k gathered keys next to themselves: the merge's sort-all path)
+    const uint64_t enough = (std::max<uint64_t>((uint64_t)kp2 + k + 256, 2 * ((uint64_t)k + k / 2) + 512) + 255) / 256 * 256;
     return (uint32_t)std::min<uint64_t>(enough, 24576);
 }
 int merge_threads(uint32_t cap_s) { return cap_s > 4096 ? 512 : 256; }

@@ -8,6 +8,14 @@
 namespace slha {
 namespace {
 
+#ifdef SLHA_STREAM_PROBE
+__device__ unsigned long long g_merge_probe[64][12];
+#define MPROBE(i) do { if (threadIdx.x == 0 && blockIdx.x < 64) g_merge_probe[blockIdx.x][i] = probe_now(); } while (0)
+#define MPROBE_VAL(i, v) do { if (threadIdx.x == 0 && blockIdx.x < 64) g_merge_probe[blockIdx.x][i] = (unsigned long long)(v); } while (0)
+#else
+#define MPROBE(i)
+#define MPROBE_VAL(i, v)
+#endif
 // A list as the gathering loop wants it: when `p` is set, its keys are p[0 .. len) and a key counts when it is
 // at least `pivot` (everything the accessors below would re-read per key, read once); else the loop asks at().
 struct ListView {
@@ -37,7 +45,7 @@ struct CompLists {  // lists written by score_kernel
         return j < cnt[l] ? keys[(size_t)l * k + j] : 0ull;
     }
     __device__ void finish(uint32_t) const {}
-    __device__ uint64_t floor_key(uint32_t, uint32_t) const { return 0ull; }
+    __device__ uint64_t floor_key(uint32_t, uint32_t, uint64_t*, uint32_t) const { return 0ull; }
     __device__ ListView view(uint32_t Q, uint32_t part) const {
         const uint32_t l = q_list_begin[Q] + part * (q_list_count[Q] >> 24);
         return ListView{keys + (size_t)l * k, 0ull, cnt[l]};
@@ -72,7 +80,7 @@ struct StreamLists {
     __device__ uint64_t get(uint32_t Q, uint32_t e) const { return gflag[Q] ? items.get(Q, e) : (e < len0(Q) ? at(Q, 0, e) : 0ull); }
     // The merge is the last reader of a row's streaming state: it leaves the state cleared for the next call
     // (which then needs no memset in front of its score kernel) and keeps the row's figures for the statistics call.
-    __device__ uint64_t floor_key(uint32_t, uint32_t) const { return 0ull; }  // (at() filters by the row's threshold already)
+    __device__ uint64_t floor_key(uint32_t, uint32_t, uint64_t*, uint32_t) const { return 0ull; }  // (the row's threshold filters already)
     __device__ ListView view(uint32_t Q, uint32_t part) const {
         if (gflag[Q]) return items.view(Q, part);
         if (compacted(Q)) return ListView{gsel + (size_t)Q * selcap, 0ull, gselcnt[Q]};
@@ -100,18 +108,43 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     uint32_t n_lists, n_queries, k_in;
     uint64_t list_stride;  // elements between the blocks of consecutive lists
     uint32_t sorted;       // every list is ordered best first (lists this library produced)
-    // A key that at least k candidates reach, from sorted lists alone: with p = ceil(k / n_lists) every list holds p
-    // candidates at or above its p-th entry, so n_lists * p >= k candidates reach the smallest of those entries.
-    // Shards of one context hold about k / n_lists of the k best each, so this bound sits just below the k-th best
-    // and the merge gathers little more than k keys instead of n_lists * k.  Zero: no bound.
     __device__ ListView view(uint32_t, uint32_t) const { return ListView{nullptr, 0ull, k_in}; }
-    __device__ uint64_t floor_key(uint32_t Q, uint32_t k) const {
+    // A key that at least k candidates reach -- and few more -- from sorted lists alone.  Every list is sampled at every
+    // `stride`-th entry (stride = k / (8 n_lists)); a sample certifies that `stride` more entries of its list are at
+    // least as large.  For a sample v, L(v) = stride x (samples of all lists >= v) entries reach v for certain; the
+    // largest sample with L >= k is the floor.  Fewer than stride (n_lists + 1) further entries can lie above it, so
+    // the merge gathers fewer than k + k / 8 + stride keys instead of n_lists * k, however unevenly the lists share the
+    // k best (token-range shards do: recent tokens score higher).  All threads of the block call this; `scratch` is
+    // shared memory of `slots` keys.  Zero: no bound (unsorted lists, too few entries, no room).
+    __device__ uint64_t floor_key(uint32_t Q, uint32_t k, uint64_t* scratch, uint32_t slots) const {
         if (!sorted || n_lists < 2) return 0ull;
-        const uint32_t p = (k + n_lists - 1) / n_lists;
-        if (p == 0 || p > k_in) return 0ull;
-        uint64_t lo = ~0ull;
-        for (uint32_t l = 0; l < n_lists; ++l) lo = min(lo, at(Q, l, p - 1));  // (an absent entry is key 0: no bound)
-        return lo;
+        const uint32_t stride = max(1u, k / (8u * n_lists)), m = k_in / stride, S = n_lists * m;
+        if (m == 0 || S + 1 > slots) return 0ull;
+        const uint32_t tid = threadIdx.x, nt = blockDim.x;
+        for (uint32_t i = tid; i < S; i += nt) scratch[i] = at(Q, i / m, stride * (i % m + 1) - 1);  // (an absent entry is key 0)
+        if (tid == 0) scratch[S] = 0ull;
+        __syncthreads();
+        for (uint32_t i = tid; i < S; i += nt) {
+            const uint64_t v = scratch[i];
+            if (!v) continue;
+            uint32_t reach = 0;
+            for (uint32_t l = 0; l < n_lists; ++l) {
+                // samples of list l that are >= v: the list is ordered best first
+                const uint64_t* a = scratch + l * m;
+                uint32_t lo = 0, hi = m;
+                while (lo < hi) {
+                    const uint32_t mid = (lo + hi) >> 1;
+                    if (a[mid] >= v) lo = mid + 1;
+                    else hi = mid;
+                }
+                reach += lo;
+            }
+            if ((uint64_t)reach * stride >= k) atomicMax(reinterpret_cast<unsigned long long*>(scratch + S), (unsigned long long)v);
+        }
+        __syncthreads();
+        const uint64_t f = scratch[S];
+        __syncthreads();
+        return f;
     }
     __device__ uint32_t size(uint32_t) const { return n_lists * k_in; }
     __device__ uint32_t lists(uint32_t) const { return n_lists; }
@@ -175,8 +208,8 @@ __global__ void __launch_bounds__(256) stream_compact_kernel(const uint64_t* gbu
     }
 }
 
-// Orders buf[0..m) descending into out[0..m) by bucket placement: NB (1024 or 2048) equal-width score buckets
-// between the smallest and the largest score (highest first), a counting pass, an exclusive scan, a
+// Orders buf[0..m) descending into out[0..m) by bucket placement: NB (1024 or 2048) score buckets between the
+// smallest and the largest score (highest first, widths shrinking towards the dense low end), a counting pass, an exclusive scan, a
 // scatter, and an insertion sort inside every bucket by one thread.  The winners of a top-k are a
 // thin tail, a handful of keys per bucket, so this replaces the 55 dependent stages of a bitonic
 // sort of 1024 keys by six barriers.  Returns false (nothing written that matters) when a bucket
@@ -199,10 +232,15 @@ __device__ bool bucket_sort(const uint64_t* buf, uint64_t* out, uint32_t m, int*
     if (lane == 0) { atomicMin(&st[0], mn); atomicMax(&st[1], mx); }
     __syncthreads();
     const float smin = key_score(st[0]), smax = key_score(st[1]);
-    const float inv = (float)NB / (smax - smin);
+    const float inv = 1.0f / (smax - smin);
+    MPROBE(4);
     if (!(st[1] > st[0]) || !isfinite(smin) || !isfinite(smax) || !isfinite(inv)) return false;
+    // The best of a long list thin out towards the top: most keys sit just above the smallest.  Bucketing the
+    // square root of the normalised score (every step monotone: subtraction, multiplication by a positive
+    // constant, the correctly rounded square root, truncation) spreads that dense end over more buckets.
     auto bucket = [&](uint64_t key) {
-        const int b = (int)((smax - key_score((uint32_t)(key >> 32))) * inv);  // highest score -> bucket 0
+        const float v = sqrtf(fmaxf((key_score((uint32_t)(key >> 32)) - smin) * inv, 0.0f));  // 1 = highest score
+        const int b = (int)((1.0f - v) * (float)NB);                                            // -> bucket 0
         return b < 0 ? 0 : (b > NB - 1 ? NB - 1 : b);
     };
     for (uint32_t i = tid; i < m; i += nt) atomicAdd(&hist[bucket(buf[i])], 1);
@@ -226,6 +264,8 @@ __device__ bool bucket_sort(const uint64_t* buf, uint64_t* out, uint32_t m, int*
     if (lane == 31) st[8 + warp] = (uint32_t)incl;
     if (lane == 0) atomicMax(&st[2], (uint32_t)big);
     __syncthreads();
+    MPROBE(5);
+    MPROBE_VAL(3, st[2]);
     if (st[2] > 16u) return false;
     int base = incl - sum;
     for (uint32_t w = 0; w < warp; ++w) base += (int)st[8 + w];
@@ -242,6 +282,7 @@ __device__ bool bucket_sort(const uint64_t* buf, uint64_t* out, uint32_t m, int*
         out[atomicAdd(&hist[bucket(key)], 1)] = key;
     }
     __syncthreads();
+    MPROBE(6);
     for (int b = (int)tid; b < NB; b += (int)nt) {
         const int s0 = b ? hist[b - 1] : 0, e0 = hist[b];
         for (int x = s0 + 1; x < e0; ++x) {
@@ -316,6 +357,7 @@ __device__ __forceinline__ void topk_merge_body(const Lists& L, uint32_t k, uint
     int* hist = reinterpret_cast<int*>(pivot_s + 1);    // max(SEL_HIST_INTS, buckets of bucket_sort + 48)
     int* n_s = hist + max(SEL_HIST_INTS, merge_buckets(kp2, blockDim.x) + 48);
     const uint32_t Q = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+    MPROBE(0);
     const uint32_t T = L.size(Q);
 
     // upper bound of the number of candidates
@@ -324,8 +366,9 @@ __device__ __forceinline__ void topk_merge_body(const Lists& L, uint32_t k, uint
     // Lists that drop keys below a known threshold while they are read (Lists::kFiltered) hold far
     // fewer present keys than slots: one gathering pass usually fits them into shared memory.
     bool gathered = false;
-    const uint64_t floor_key = L.floor_key(Q, k);  // (the same in every thread)
+    const uint64_t floor_key = L.floor_key(Q, k, buf, cap_s);  // (the same in every thread; buf is free until the gathering)
     const bool filtered = Lists::kFiltered || floor_key != 0ull;
+    MPROBE(1);
     if (total <= cap_s || filtered) {
         if (tid == 0) *n_s = 0;
         __syncthreads();
@@ -358,17 +401,21 @@ __device__ __forceinline__ void topk_merge_body(const Lists& L, uint32_t k, uint
         __syncthreads();
         gathered = (uint32_t)*n_s <= cap_s;
         __syncthreads();
+        MPROBE(2);
     }
     if (gathered) {
         const uint32_t present = (uint32_t)*n_s;
         __syncthreads();
+        MPROBE_VAL(11, present);
         if (present > k) {
-            // Lists filtered by a threshold that is proven to keep k candidates hold only a few percent more than k:
+            // Lists filtered by a threshold that is proven to keep k candidates hold little more than k (up to 1.5 k here):
             // ordering them all and writing the first k is cheaper than selecting the k first.
             const uint32_t pa = (present + 1u) & ~1u;
-            if (filtered && present <= k + (k >> 2) && 2 * pa <= cap_s && (nt == 256 || nt == 512) &&
+            if (filtered && present <= k + (k >> 1) && 2 * pa <= cap_s && (nt == 256 || nt == 512) &&
                 bucket_sort(buf, buf + pa, present, hist, merge_buckets(kp2, nt))) {
+                MPROBE(7);
                 emit_sorted(buf + pa, k, k, Q, out_index, out_score, out_count);
+                MPROBE(8);
                 return;
             }
             __syncthreads();
@@ -564,7 +611,9 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
     extern __shared__ __align__(16) unsigned char smem[];
     topk_merge_body(L, k, kp2, cap_s, out_index, out_score, out_count, smem);
     __syncthreads();
+    MPROBE(9);
     L.finish(blockIdx.x);
+    MPROBE(10);
 }
 
 }  // namespace

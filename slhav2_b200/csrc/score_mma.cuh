@@ -136,6 +136,13 @@ __device__ __forceinline__ void cp_async16_s(uint32_t dst, const unsigned char* 
     asm volatile("cp.async.cg.shared.global [%0+%1], [%2+%3], 16, %4;\n" ::"r"(dst), "n"(DST_IMM), "l"(src), "n"(SRC_IMM),
                  "r"(src_bytes));
 }
+// the same with an L2 eviction policy: tiles are read once, so their lines are the first to go and the rows'
+// candidate buffers and histograms, which the merge reads next, stay in the L2
+template <int SRC_IMM, int DST_IMM>
+__device__ __forceinline__ void cp_async16_sp(uint32_t dst, const unsigned char* src, int src_bytes, uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0+%1], [%2+%3], 16, %4, %5;\n" ::"r"(dst), "n"(DST_IMM), "l"(src),
+                 "n"(SRC_IMM), "r"(src_bytes), "l"(policy));
+}
 __device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
@@ -702,6 +709,8 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
     const uint32_t dst_lane = (uint32_t)((lane >> 3) * MMA_ROW + (lane & 7) * 16);
     const uint32_t row_lane = (uint32_t)g * MMA_ROW;
     const uint32_t lt_mask = (1u << lane) - 1u, t_mask = 0x11111111u << t;
+    uint64_t stream_policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(stream_policy));
 
     const uint32_t item_end = a.cta_begin[blockIdx.x + 1];
     for (uint32_t item_id = a.cta_begin[blockIdx.x]; item_id < item_end; ++item_id) {
@@ -726,10 +735,10 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
                 const uint32_t dst = stage_s + slot_next + dst_lane;
                 const unsigned char* src = tbase + (size_t)s_next * MMA_SET_BYTES;
                 if (s_next < n_full) {
-                    cp_async16_s<0, 0>(dst, src, 16);
-                    cp_async16_s<512, 4 * MMA_ROW>(dst, src, 16);
-                    cp_async16_s<1024, 8 * MMA_ROW>(dst, src, 16);
-                    cp_async16_s<1536, 12 * MMA_ROW>(dst, src, 16);
+                    cp_async16_sp<0, 0>(dst, src, 16, stream_policy);
+                    cp_async16_sp<512, 4 * MMA_ROW>(dst, src, 16, stream_policy);
+                    cp_async16_sp<1024, 8 * MMA_ROW>(dst, src, 16, stream_policy);
+                    cp_async16_sp<1536, 12 * MMA_ROW>(dst, src, 16, stream_policy);
                 } else {
                     // ragged last set: rows past the end are zero-filled (source not read)
                     const uint32_t r = s_next * MMA_SET_TILES + (uint32_t)(lane >> 3);
