@@ -275,8 +275,11 @@ typedef struct {
  * the reference itself has no top-k step).  Rows with fewer than k tiles are
  * padded with index 0xFFFFFFFF and score -inf; out_count[j] (may be NULL) is
  * the number of valid entries.  tiles must be device memory; segments,
- * queries and outputs are host or device.  Full score vectors are never
- * written to memory.
+ * queries and outputs are host or device.  Outputs in page-locked host memory
+ * that the GPU can address (cudaHostAlloc, mapped cudaHostRegister) are written
+ * in place by the kernel that produces them, other host outputs through a
+ * staging copy; the same holds for the other top-k entry points below.  Full
+ * score vectors are never written to memory.
  */
 int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment* segments,
                              size_t n_segments, const float* q_coarse, const uint64_t* q_sign,

@@ -252,9 +252,9 @@ int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment
         SLHA_TRY(stage_in_t(c, q_coarse, n_queries * D_C, &dq));
         SLHA_TRY(stage_in_t(c, q_sign, n_queries * 4, &ds));
         std::vector<StagedOut> outs(3);
-        SLHA_TRY(stage_out(c, out_index, n_queries * k * 4, &outs[0]));
-        SLHA_TRY(stage_out(c, out_score, n_queries * k * 4, &outs[1]));
-        SLHA_TRY(stage_out(c, out_count, n_queries * 4, &outs[2]));
+        SLHA_TRY(stage_out(c, out_index, n_queries * k * 4, &outs[0], /*in_place_if_pinned=*/true));
+        SLHA_TRY(stage_out(c, out_score, n_queries * k * 4, &outs[1], /*in_place_if_pinned=*/true));
+        SLHA_TRY(stage_out(c, out_count, n_queries * 4, &outs[2], /*in_place_if_pinned=*/true));
         SLHA_TRY(score_topk_device(c, tiles, nullptr, hseg.data(), n_segments, dq, ds, n_queries, k,
                                    (uint32_t*)outs[0].dev, (float*)outs[1].dev, (uint32_t*)outs[2].dev));
         return finish_outputs(c, outs, sync_by_default(c));
@@ -303,8 +303,8 @@ static int32_t topk_merge_any(const uint32_t* cand_index, const float* cand_scor
         SLHA_TRY(stage_in_t(c, cand_index, nc, &di));
         SLHA_TRY(stage_in_t(c, cand_score, nc, &dsc));
         std::vector<StagedOut> outs(2);
-        SLHA_TRY(stage_out(c, out_index, (size_t)n_queries * k_out * 4, &outs[0]));
-        SLHA_TRY(stage_out(c, out_score, (size_t)n_queries * k_out * 4, &outs[1]));
+        SLHA_TRY(stage_out(c, out_index, (size_t)n_queries * k_out * 4, &outs[0], /*in_place_if_pinned=*/true));
+        SLHA_TRY(stage_out(c, out_score, (size_t)n_queries * k_out * 4, &outs[1], /*in_place_if_pinned=*/true));
         SLHA_TRY(launch_topk_merge_pairs(c, di, dsc, n_lists, list_stride, n_queries, k_in, k_out,
                                          (uint32_t*)outs[0].dev, (float*)outs[1].dev, lists_sorted));
         return finish_outputs(c, outs, sync_by_default(c));
@@ -404,8 +404,8 @@ int32_t slha_b200_shard_score_topk(SlhaB200Shard* shard, const SciRustSlhaTile* 
         SLHA_TRY(stage_in_t(c, q_coarse, n_queries * D_C, &dq));
         SLHA_TRY(stage_in_t(c, q_sign, n_queries * 4, &ds));
         std::vector<StagedOut> outs(2);
-        SLHA_TRY(stage_out(c, out_index, n_queries * k * 4, &outs[0]));
-        SLHA_TRY(stage_out(c, out_score, n_queries * k * 4, &outs[1]));
+        SLHA_TRY(stage_out(c, out_index, n_queries * k * 4, &outs[0], /*in_place_if_pinned=*/true));
+        SLHA_TRY(stage_out(c, out_score, n_queries * k * 4, &outs[1], /*in_place_if_pinned=*/true));
         SLHA_TRY(shard_step_device(c, reinterpret_cast<Shard*>(shard), tiles, segments, n_segments, dq, ds, n_queries, k,
                                    (uint32_t*)outs[0].dev, (float*)outs[1].dev));
         return finish_outputs(c, outs, sync_by_default(c));
@@ -573,9 +573,9 @@ int32_t slha_b200_pool_score_topk(SlhaB200Pool* pool, const float* q_coarse, con
         SLHA_TRY(stage_in_t(c, q_coarse, nq * D_C, &dq));
         SLHA_TRY(stage_in_t(c, q_sign, nq * 4, &ds));
         std::vector<StagedOut> outs(3);
-        SLHA_TRY(stage_out(c, out_slot, nq * k * 4, &outs[0]));
-        SLHA_TRY(stage_out(c, out_score, nq * k * 4, &outs[1]));
-        SLHA_TRY(stage_out(c, out_count, nq * 4, &outs[2]));
+        SLHA_TRY(stage_out(c, out_slot, nq * k * 4, &outs[0], /*in_place_if_pinned=*/true));
+        SLHA_TRY(stage_out(c, out_score, nq * k * 4, &outs[1], /*in_place_if_pinned=*/true));
+        SLHA_TRY(stage_out(c, out_count, nq * 4, &outs[2], /*in_place_if_pinned=*/true));
         SlhaB200Segment seg{0, (uint32_t)pl->h_cnt.len, 0, (uint32_t)nq, 0};
         const uint32_t cm = pl->codec_mask;
         const bool known = !(cm & 0x80000000u);

@@ -167,7 +167,7 @@ Status stage_in(Ctx* c, const void* p, size_t bytes, const void** dev) {
     return Status();
 }
 
-Status stage_out(Ctx* c, void* user, size_t bytes, StagedOut* out) {
+Status stage_out(Ctx* c, void* user, size_t bytes, StagedOut* out, bool in_place_if_pinned) {
     out->user = user;
     out->bytes = bytes;
     if (user == nullptr || bytes == 0 || is_device_ptr(user)) {
@@ -175,6 +175,16 @@ Status stage_out(Ctx* c, void* user, size_t bytes, StagedOut* out) {
         out->is_host = false;
         return Status();
     }
+    // Page-locked host memory the GPU can address (cudaHostAlloc, cudaHostRegister with mapping) is written in place by the
+    // kernels: the results cross the bus while the kernel that produces them runs, instead of in a copy queued behind it.
+    // Only for outputs that the call's kernels write once and never read (the caller says so).
+    cudaPointerAttributes a;
+    if (in_place_if_pinned && cudaPointerGetAttributes(&a, user) == cudaSuccess && a.type == cudaMemoryTypeHost && a.devicePointer != nullptr) {
+        out->dev = a.devicePointer;
+        out->is_host = false;
+        return Status();
+    }
+    cudaGetLastError();
     out->is_host = true;
     return ctx_device_scratch(c, bytes, &out->dev);
 }

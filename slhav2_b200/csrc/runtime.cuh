@@ -39,7 +39,7 @@ struct StagedOut {
     size_t bytes = 0;
     bool is_host = false;
 };
-Status stage_out(Ctx* c, void* user, size_t bytes, StagedOut* out);
+Status stage_out(Ctx* c, void* user, size_t bytes, StagedOut* out, bool in_place_if_pinned = false);
 // Copies every host-bound output back and synchronises the stream when any
 // copy was needed or `force_sync` is set.
 Status finish_outputs(Ctx* c, std::vector<StagedOut>& outs, bool force_sync);

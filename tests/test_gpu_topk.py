@@ -298,3 +298,21 @@ def test_wide_scoring_two_segments_and_repeat():
         qc, qs = H.random_queries(2 * qph, seed)
         gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, 2 * qph, k)
         check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+
+
+def test_outputs_in_page_locked_host_memory_are_written_in_place():
+    # the same call with pageable numpy outputs (staging copy) and with page-locked outputs the GPU addresses directly
+    torch = pytest.importorskip("torch")
+    n, k, nq = 20000, 128, 4
+    tiles = H.random_tiles(n, 0, seed=31)
+    qc, qs = H.random_queries(nq, 32)
+    dt = S.to_device(tiles)
+    segs = S.make_segments([(0, n, 0, nq, 0)])
+    want = S.score_topk(dt, segs, qc, qs, nq, k)
+    pi = torch.full((nq, k), -1, dtype=torch.int32).pin_memory()
+    ps = torch.zeros(nq, k, dtype=torch.float32).pin_memory()
+    pc = torch.zeros(nq, dtype=torch.int32).pin_memory()
+    S.score_topk(dt, segs, qc, qs, nq, k, out_index=pi, out_score=ps, out_count=pc)
+    S.synchronize()
+    assert np.array_equal(pi.numpy().view(np.uint32), want[0]) and np.array_equal(ps.numpy(), want[1])
+    assert np.array_equal(pc.numpy().view(np.uint32), want[2])
