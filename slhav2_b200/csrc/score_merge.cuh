@@ -45,7 +45,7 @@ struct CompLists {  // lists written by score_kernel
         return j < cnt[l] ? keys[(size_t)l * k + j] : 0ull;
     }
     __device__ void finish(uint32_t) const {}
-    __device__ uint64_t floor_key(uint32_t, uint32_t, uint64_t*, uint32_t) const { return 0ull; }
+    __device__ uint64_t floor_key(uint32_t, uint32_t, uint64_t*, uint32_t, int*) const { return 0ull; }
     __device__ ListView view(uint32_t Q, uint32_t part) const {
         const uint32_t l = q_list_begin[Q] + part * (q_list_count[Q] >> 24);
         return ListView{keys + (size_t)l * k, 0ull, cnt[l]};
@@ -80,7 +80,7 @@ struct StreamLists {
     __device__ uint64_t get(uint32_t Q, uint32_t e) const { return gflag[Q] ? items.get(Q, e) : (e < len0(Q) ? at(Q, 0, e) : 0ull); }
     // The merge is the last reader of a row's streaming state: it leaves the state cleared for the next call
     // (which then needs no memset in front of its score kernel) and keeps the row's figures for the statistics call.
-    __device__ uint64_t floor_key(uint32_t, uint32_t, uint64_t*, uint32_t) const { return 0ull; }  // (the row's threshold filters already)
+    __device__ uint64_t floor_key(uint32_t, uint32_t, uint64_t*, uint32_t, int*) const { return 0ull; }  // (the row's threshold filters already)
     __device__ ListView view(uint32_t Q, uint32_t part) const {
         if (gflag[Q]) return items.view(Q, part);
         if (compacted(Q)) return ListView{gsel + (size_t)Q * selcap, 0ull, gselcnt[Q]};
@@ -115,9 +115,11 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     // largest sample with L >= k is the floor.  Fewer than stride (n_lists + 1) further entries can lie above it, so
     // the merge gathers fewer than k + k / 8 + stride keys instead of n_lists * k, however unevenly the lists share the
     // k best (token-range shards do: recent tokens score higher).  All threads of the block call this; `scratch` is
-    // shared memory of `slots` keys.  Zero: no bound (unsorted lists, too few entries, no room).
-    __device__ uint64_t floor_key(uint32_t Q, uint32_t k, uint64_t* scratch, uint32_t slots) const {
-        if (!sorted || n_lists < 2) return 0ull;
+    // shared memory of `slots` keys.  Zero: no bound (unsorted lists, too few entries, no room).  With a floor,
+    // prefix[0 .. n_lists] receives the exclusive prefix sums of how many leading entries of every list can reach it
+    // (the list's first sample below the floor ends them), so that only those are read.
+    __device__ uint64_t floor_key(uint32_t Q, uint32_t k, uint64_t* scratch, uint32_t slots, int* prefix) const {
+        if (!sorted || n_lists < 2 || n_lists > 64) return 0ull;
         const uint32_t stride = max(1u, k / (8u * n_lists)), m = k_in / stride, S = n_lists * m;
         if (m == 0 || S + 1 > slots) return 0ull;
         const uint32_t tid = threadIdx.x, nt = blockDim.x;
@@ -143,6 +145,21 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
         }
         __syncthreads();
         const uint64_t f = scratch[S];
+        if (f && tid == 0) {
+            int run = 0;
+            for (uint32_t l = 0; l < n_lists; ++l) {
+                const uint64_t* a = scratch + l * m;
+                uint32_t lo = 0, hi = m;
+                while (lo < hi) {  // samples of list l that are >= f
+                    const uint32_t mid = (lo + hi) >> 1;
+                    if (a[mid] >= f) lo = mid + 1;
+                    else hi = mid;
+                }
+                prefix[l] = run;
+                run += (int)min(k_in, stride * (lo + 1));
+            }
+            prefix[n_lists] = run;
+        }
         __syncthreads();
         return f;
     }
@@ -366,14 +383,42 @@ __device__ __forceinline__ void topk_merge_body(const Lists& L, uint32_t k, uint
     // Lists that drop keys below a known threshold while they are read (Lists::kFiltered) hold far
     // fewer present keys than slots: one gathering pass usually fits them into shared memory.
     bool gathered = false;
-    const uint64_t floor_key = L.floor_key(Q, k, buf, cap_s);  // (the same in every thread; buf is free until the gathering)
+    const uint64_t floor_key = L.floor_key(Q, k, buf, cap_s, hist);  // (the same in every thread; buf and hist are free until the gathering)
     const bool filtered = Lists::kFiltered || floor_key != 0ull;
     MPROBE(1);
     if (total <= cap_s || filtered) {
         if (tid == 0) *n_s = 0;
         __syncthreads();
         const uint32_t n_lists_q = L.lists(Q);
-        for (uint32_t l = 0; l < n_lists_q; ++l) {
+        if (floor_key != 0ull) {
+            // lists ordered best first: only the leading entries that can reach the floor, all lists in one sweep
+            const uint32_t total_pre = (uint32_t)hist[n_lists_q];
+            for (uint32_t e0 = 0; e0 < total_pre; e0 += 4 * nt) {
+                uint64_t key[4];
+#pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t e = e0 + u * nt + tid;
+                    key[u] = 0ull;
+                    if (e < total_pre) {
+                        uint32_t l = 0;
+                        while (l + 1 < n_lists_q && (uint32_t)hist[l + 1] <= e) ++l;
+                        key[u] = L.at(Q, l, e - (uint32_t)hist[l]);
+                        if (key[u] < floor_key) key[u] = 0ull;
+                    }
+                }
+#pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const unsigned bal = __ballot_sync(0xFFFFFFFFu, key[u] != 0ull);
+                    if (!bal) continue;
+                    int base = 0;
+                    if ((tid & 31) == 0) base = atomicAdd(n_s, __popc(bal));
+                    base = __shfl_sync(0xFFFFFFFFu, base, 0);
+                    const uint32_t at = (uint32_t)base + __popc(bal & ((1u << (tid & 31)) - 1));
+                    if (key[u] && at < cap_s) buf[at] = key[u];
+                }
+            }
+        }
+        for (uint32_t l = 0; floor_key == 0ull && l < n_lists_q; ++l) {
             const ListView V = L.view(Q, l);
             const uint32_t len = V.len;
             const uint64_t low = V.p ? (V.pivot > floor_key ? V.pivot : floor_key) : floor_key;
