@@ -316,3 +316,29 @@ def test_outputs_in_page_locked_host_memory_are_written_in_place():
     S.synchronize()
     assert np.array_equal(pi.numpy().view(np.uint32), want[0]) and np.array_equal(ps.numpy(), want[1])
     assert np.array_equal(pc.numpy().view(np.uint32), want[2])
+
+
+@pytest.mark.parametrize("trial", range(16))
+def test_random_call_shapes_match_the_oracle(trial):
+    # segments of random lengths (some empty, some a single tile, some long enough to be cut over many CTAs), 1 to 9
+    # or 20 to 40 query rows each (so the four-query, the generic and the 64-query kernels all get work), random k and
+    # index bases, one codec per call; a second identical call exercises the cached plan and the cleared streaming state
+    rng = np.random.default_rng(7000 + trial)
+    codec = [0, 1, 2, 3, 4, 6][trial % 6]
+    wide = trial % 4 == 3 and codec in (0, 1, 4, 6)
+    n_seg = int(rng.integers(1, 7))
+    lens = [int(rng.choice([0, 1, 17, int(rng.integers(2, 3000)), int(rng.integers(3000, 60000))])) for _ in range(n_seg)]
+    nqs = [int(rng.integers(20, 41)) if wide else int(rng.integers(1, 10)) for _ in range(n_seg)]
+    k = int(rng.choice([1, 7, 64, 500, 1024, 3000]))
+    total = max(sum(lens), 1)
+    tiles = H.random_tiles(total, codec, seed=300 + trial, warm_every=11, nocorr_every=7)[:sum(lens)]
+    qc, qs = H.random_queries(sum(nqs), 400 + trial)
+    segs, tb, qb = [], 0, 0
+    for n, q in zip(lens, nqs):
+        segs.append((tb, n, qb, q, int(rng.integers(0, 1000))))
+        tb += n
+        qb += q
+    dt = S.to_device(tiles if len(tiles) else np.zeros(1, S.TILE_DTYPE))
+    for _ in range(2):
+        gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, sum(nqs), k)
+        check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
