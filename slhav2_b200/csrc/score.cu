@@ -274,6 +274,7 @@ struct ScoreArgs {
     const unsigned char* tiles;
     const uint8_t* state;  // optional per-tile CCOS state (COLD tiles are skipped)
     const WorkItem* items;
+    const WorkItem* stream_items;  // score_stream_kernel: item i as that kernel walks it (interleaved chunks of a stream, or items[i] itself)
     const float* q_coarse;    // [nq][128]
     const uint32_t* q_sign;   // [nq][8]
     // full mode

@@ -124,6 +124,7 @@ struct Plan {
     // wide scoring (16 or more queries per segment, INT4 / TQ3 launches): work items of up to 64 query rows for score_wide_kernel
     bool wide = false, allow_wide_in = false;
     WorkItem* d_wide_items = nullptr;
+    WorkItem* d_stream_items = nullptr;  // interleaved description of every CTA's work for score_stream_kernel (null: the work items themselves)
     uint32_t* d_wide_cta = nullptr;
     uint32_t wide_grid = 0, n_wide_items = 0;
     uint32_t n_items = 0;
@@ -138,7 +139,7 @@ struct Plan {
     int mma_threads = STREAM_THREADS;
     uint32_t mma_grid = 0;
     size_t mma_smem = 0;
-    DevBuf b_items, b_qbegin, b_qcount, b_keys, b_cnt, b_cta, b_gpivot, b_gbuf, b_gsel, b_vq, b_tmp, b_wide_items, b_wide_cta;
+    DevBuf b_stream_items, b_items, b_qbegin, b_qcount, b_keys, b_cnt, b_cta, b_gpivot, b_gbuf, b_gsel, b_vq, b_tmp, b_wide_items, b_wide_cta;
     // Two-level merge for calls with few queries and many candidate lists per query (a pool scored
     // by one GQA group: 148 lists each): groups of `group_parts` lists are merged by a CTA each into
     // `n_groups` intermediate (index, score) lists per query, which a second launch merges.
@@ -250,6 +251,46 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     uint64_t spare = share * std::max<uint32_t>(p->mma_grid, 1) > total ? share * std::max<uint32_t>(p->mma_grid, 1) - total : 0;  // room the equal shares leave
     uint64_t filled = 0;  // tiles already given to the current CTA (tensor-core mode)
     std::vector<uint32_t> cta_begin(1, 0);
+    // Few long streams (a stream = one segment's tiles for one group of up to four query rows; at most half as many as
+    // there are CTAs): every stream gets whole CTAs in proportion to its tiles, and the CTAs of a stream take its tiles
+    // interleaved -- CTA c of C takes the 24-set chunks c, c + C, c + 2 C .. -- instead of one contiguous range each.
+    // Equal ranges are not equal work: where the scores are high (recent tokens) a CTA appends far more candidates, and
+    // the CTA with the densest range ended 13 us after the median one; interleaved, every CTA sees the same mix.  The
+    // work items below stay contiguous ranges (one per CTA): they are what the generic kernel scores when a row is
+    // handed back; the tensor-core kernel reads the interleaved description of the same CTA from `stream_items`.
+    std::vector<uint32_t> stream_ctas;
+    std::vector<WorkItem> stream_items;
+    if (p->use_mma && total > 0) {
+        std::vector<uint64_t> st_tiles;
+        for (size_t i = 0; i < n_segs; ++i)
+            for (uint32_t q0 = 0; q0 < segs[i].n_queries; q0 += 4)
+                if (segs[i].n_tiles) st_tiles.push_back(segs[i].n_tiles);
+        // Only for short shares (less than 20 000 tiles per CTA: shards of a long context, measured at 7 k and 14 k tiles
+        // per CTA): with whole CTAs per stream the streams' CTA counts differ by one (18 or 19 of 148 for eight streams),
+        // which costs the slower streams 5 % -- less than the second set-up of a CTA that works on two streams when a
+        // share lasts 40 us, more when it lasts 200 us.
+        if (!st_tiles.empty() && st_tiles.size() * 2 <= p->mma_grid && total / p->mma_grid < 20000) {
+            stream_ctas.resize(st_tiles.size());
+            uint32_t used = 0;
+            for (size_t j = 0; j < st_tiles.size(); ++j) {
+                const uint64_t most = (st_tiles[j] + 2047) / 2048;  // (no CTA for less than 2048 tiles)
+                stream_ctas[j] = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(most, st_tiles[j] * p->mma_grid / total));
+                used += stream_ctas[j];
+            }
+            while (used < p->mma_grid) {  // the CTAs left over go where a CTA has the most tiles
+                size_t best = st_tiles.size();
+                uint64_t worst = 0;
+                for (size_t j = 0; j < st_tiles.size(); ++j) {
+                    const uint64_t per = st_tiles[j] / stream_ctas[j];
+                    if (per > worst && (uint64_t)stream_ctas[j] < (st_tiles[j] + 2047) / 2048) { worst = per; best = j; }
+                }
+                if (best == st_tiles.size()) break;
+                ++stream_ctas[best];
+                ++used;
+            }
+        }
+    }
+    size_t stream_no = 0;
 
     std::vector<WorkItem> items[3];  // by class G = 1, 2, 4 (generic mode); all in [2] in tensor-core mode
     std::vector<uint32_t> q_begin(nq, 0), q_count(nq, 0);
@@ -263,7 +304,25 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
             const int G = group_width(gq);
             // cut points of this (segment, query group) stream
             std::vector<std::pair<uint32_t, uint32_t>> cuts;  // (offset, length)
-            for (uint32_t pos = 0; pos < s.n_tiles;) {
+            if (!stream_ctas.empty() && s.n_tiles) {
+                uint32_t ctas = stream_ctas[stream_no++];
+                const uint32_t per = (uint32_t)(((uint64_t)s.n_tiles + ctas - 1) / ctas + MMA_SET_TILES - 1) / MMA_SET_TILES * MMA_SET_TILES;
+                ctas = (s.n_tiles + per - 1) / per;  // (rounding to whole sets can leave the last CTA nothing)
+                for (uint32_t part = 0; part < ctas; ++part) {
+                    cuts.push_back({part * per, std::min<uint32_t>(per, s.n_tiles - part * per)});
+                    cta_begin.push_back((uint32_t)items[2].size() + (uint32_t)cuts.size());
+                    WorkItem w{};
+                    w.tile_begin = s.tile_begin;
+                    w.n_tiles = s.n_tiles;
+                    w.index_base = s.index_base;
+                    w.query_begin = s.query_begin + q0;
+                    w.n_queries = gq;
+                    w.list_begin = part;                              // this CTA's place among the stream's CTAs
+                    w.pad = gq | (ctas << 8) | 0x80000000u;           // their number; bit 31: interleaved
+                    stream_items.push_back(w);
+                }
+            }
+            for (uint32_t pos = 0; stream_ctas.empty() && pos < s.n_tiles;) {
                 uint32_t take;
                 if (p->use_mma) {
                     // A work item costs its set-up and first set (several microseconds) whatever its length, so cuts that
@@ -328,6 +387,11 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     for (const WorkItem& w : all)
         for (uint32_t g = 0; g < w.n_queries; ++g) q_stride[w.query_begin + g] = w.pad & 0xFFu;
     SLHA_TRY(p->b_items.ensure(all.size() * sizeof(WorkItem)));
+    if (!stream_items.empty() && stream_items.size() != all.size()) return Status(SLHA_ERR_PANIC, "score plan: stream items out of step");
+    SLHA_TRY(p->b_stream_items.ensure(stream_items.size() * sizeof(WorkItem)));
+    p->d_stream_items = stream_items.empty() ? nullptr : (WorkItem*)p->b_stream_items.p;
+    if (p->d_stream_items)
+        SLHA_CUDA(cudaMemcpyAsync(p->d_stream_items, stream_items.data(), stream_items.size() * sizeof(WorkItem), cudaMemcpyHostToDevice, c->stream));
     SLHA_TRY(p->b_qbegin.ensure(nq * 4));
     SLHA_TRY(p->b_qcount.ensure(nq * 4));
     p->list_cap = (k + std::max<uint32_t>(64, k / 2) + 31) / 32 * 32;
@@ -575,6 +639,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.tiles = reinterpret_cast<const unsigned char*>(tiles);
         a.state = state;
         a.items = p->d_items;
+        a.stream_items = p->d_stream_items ? p->d_stream_items : p->d_items;
         a.n_items = p->n_items;
         a.cta_begin = p->d_cta_begin;
         // (histograms first: they are read with 16-byte loads)

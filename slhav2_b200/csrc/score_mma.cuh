@@ -714,8 +714,13 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
 
     const uint32_t item_end = a.cta_begin[blockIdx.x + 1];
     for (uint32_t item_id = a.cta_begin[blockIdx.x]; item_id < item_end; ++item_id) {
-        const WorkItem it = a.items[item_id];
+        const WorkItem it = a.stream_items[item_id];
         const int nq = (int)it.n_queries;
+        // interleaved: this CTA is number il_c of the il_n CTAs that share the stream [tile_begin, + n_tiles); round r of
+        // the stream's static deal belongs to CTA r mod il_n.  Otherwise the item is this CTA's own range.
+        const bool il = (it.pad >> 31) != 0;
+        const uint32_t il_n = il ? ((it.pad >> 8) & 0x7FFFFFu) : 1u, il_c = il ? it.list_begin : 0u;
+        const uint32_t s_step = il_n * (uint32_t)nwarps;  // from one of this warp's sets to its next
         __syncthreads();  // previous item fully retired (and the table is visible)
         // The first sets are fetched before anything else of the item is prepared: the copy runs while the query
         // fragments are built.
@@ -729,7 +734,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         uint32_t* const hrow = a.ghist + (size_t)Qt * 256;                 // and its histogram
         // sets are dealt to the warps round by round: warp w takes set j * nwarps + w of round j
         const unsigned char* tbase = a.tiles + it.tile_begin * TILE_BYTES + lane * 16;
-        uint32_t s_next = (uint32_t)warp, slot_next = 0;
+        uint32_t s_next = il_c * (uint32_t)nwarps + (uint32_t)warp, slot_next = 0;
         auto issue = [&]() {
             if (s_next < n_sets) {
                 const uint32_t dst = stage_s + slot_next + dst_lane;
@@ -749,7 +754,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
                 }
             }
             cp_async_commit();
-            s_next += (uint32_t)nwarps;
+            s_next += s_step;
             slot_next = slot_next == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot_next + MMA_SET_STRIDE;
         };
 #pragma unroll
@@ -831,7 +836,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         // of every CTA that works on the row -- and the rows do not already have thresholds (a CTA that starts its
         // second item on rows other CTAs have been scoring for a while).
         const bool all_warm = __syncthreads_and(row_warm) != 0;
-        const bool first_round_barrier = !all_warm && (uint64_t)a.k <= 16ull * (uint64_t)nwarps * (uint64_t)max(it.pad >> 8, 1u);
+        const bool first_round_barrier = !all_warm && (uint64_t)a.k <= 16ull * (uint64_t)nwarps * (uint64_t)max((it.pad >> 8) & 0x7FFFFFu, 1u);
         PROBE_SET(1);
         const bool too_big = bail[0] != 0;
         if (too_big) n_sets = 0;  // (the sets already on their way are waited for at the item's end and never read)
@@ -839,9 +844,10 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         uint32_t slot = 0, polls = 0;
         uint32_t cur = 0, end = 0;  // this warp's chunk of the buffer of row Qt (the same in the eight lanes of a query)
         bool dead = false;          // this warp met a tile it cannot decode
-        const uint32_t rounds = (n_sets + (uint32_t)nwarps - 1) / (uint32_t)nwarps;
+        const uint32_t all_rounds = (n_sets + (uint32_t)nwarps - 1) / (uint32_t)nwarps;
+        const uint32_t rounds = all_rounds > il_c ? (all_rounds - il_c + il_n - 1) / il_n : 0u;  // (the same for all warps of the CTA)
         for (uint32_t round = 0; round < rounds; ++round) {
-            const uint32_t s = round * (uint32_t)nwarps + (uint32_t)warp;
+            const uint32_t s = (round * il_n + il_c) * (uint32_t)nwarps + (uint32_t)warp;
             if (round == 1 && first_round_barrier) {
                 // Every warp of the CTA (and, started together, of the grid) has appended its first set
                 // unfiltered, so the rows' histograms hold 16 candidates per warp: first thresholds now,
