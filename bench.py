@@ -657,6 +657,88 @@ def run_pool_workload(args, S, torch, dev):
             "live_bytes": st["live_bytes"], "budget": budget, "within_budget": bool(st["live_bytes"] <= budget)}
 
 
+def run_next_rows(S, torch, dev):
+    """Timed figures of the rows beside the hot path (one GPU, device-resident inputs, CUDA events on the launching
+    stream, 20 calls after 3): the decode tail over a step's winners, a layer's dense scores for the llama.cpp shim,
+    and evictions journalled in the reference's event-log format."""
+    import tempfile
+
+    out = {}
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    S.set_stream(stream.cuda_stream)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(99)
+
+    def timed(fn, n=20):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    # decode tail: softmax over the 2048 winners of 32 query rows + weighted sum of their bf16 value rows (d_v = 128);
+    # winners drawn from a 2^20-row value array per KV head as configuration 5's would be
+    nq, k, d_v, rows_per_head = 32, 2048, HEAD_DIM, 1 << 20
+    values = torch.randn(8 * rows_per_head, d_v, generator=gen, device=dev).to(torch.bfloat16).contiguous()
+    top_i = torch.stack([torch.randperm(rows_per_head, generator=gen, device=dev)[:k] for _ in range(nq)]).to(torch.int32).contiguous()
+    top_s = (torch.randn(nq, k, generator=gen, device=dev).sort(dim=1, descending=True).values * 4).contiguous()
+    base = (torch.arange(nq, device=dev) // 4 * rows_per_head).to(torch.int64)
+    o = torch.empty(nq, d_v, dtype=torch.float32, device=dev)
+    ms = timed(lambda: S.attend_topk(top_i, top_s, k, 1.0 / np.sqrt(HEAD_DIM), values, d_v, value_dtype=S.BF16, value_row_base=base, out=o))
+    out["attend_topk"] = {"workload": "32 query rows x top-2048, bf16 value rows of 128 (gathered from 8 x 2^20 rows)", "ms": ms,
+                          "gathered_gb_per_s": nq * k * d_v * 2 / (ms * 1e-3) / 1e9}
+    del values
+
+    # a layer's dense scores in one call: 8 KV heads x 32768 mixed 8/4 tiles, 16 tokens x 4 query heads per KV head
+    heads, tokens, n_tok, gqa = 8, 32768, 16, 4
+    model = S.Model.from_projection(seeded_projection(11), HEAD_DIM, 11)
+    keys = torch.randn(heads * tokens, HEAD_DIM, generator=gen, device=dev).to(torch.bfloat16).contiguous()
+    tiles = S.DeviceBuffer(heads * tokens * 128)
+    model.encode_keys(keys, S.CODEC_MIXED, n=heads * tokens, key_dtype=S.BF16, out=tiles)
+    rows = heads * n_tok * gqa
+    q = torch.randn(rows, HEAD_DIM, generator=gen, device=dev)
+    qc = torch.empty(rows, 128, dtype=torch.float32, device=dev)
+    qs = torch.empty(rows, 4, dtype=torch.int64, device=dev)
+    model.prepare_queries(q, nq=rows, q_coarse_out=qc, q_sign_out=qs)
+    segs = S.make_segments([(h * tokens, tokens, h * n_tok * gqa, n_tok * gqa, 0) for h in range(heads)])
+    offs = np.arange(rows, dtype=np.uint64) * np.uint64(tokens)  # (host descriptors: the call reads them without a stream round trip)
+    dst = torch.empty(rows, tokens, dtype=torch.float32, device=dev)
+    ms = timed(lambda: S.score_segments(tiles, segs, qc, qs, rows, dst, offs, tokens), n=10)
+    out["score_segments"] = {"workload": "8 KV heads x 32768 mixed 8/4 tiles, 64 query rows per head, dense float32 scores", "ms": ms,
+                             "scores_per_s": rows * tokens / (ms * 1e-3), "written_gb_per_s": rows * tokens * 4 / (ms * 1e-3) / 1e9,
+                             "kernel": "generic CUDA-core kernel, four query rows per pass"}
+    del dst, keys
+    tiles.free()
+
+    # evictions journalled in the reference's event-log format: 262144 HOT tiles, budget for 65536, causal policy
+    S.set_stream(None)
+    n = 262144
+    pool = S.TilePool(n, 128 * n, S.PAGE_OLDEST_FIRST, S.EVICT_CAUSAL)
+    kb = torch.randn(n, HEAD_DIM, generator=gen, device=dev).to(torch.bfloat16).contiguous()
+    torch.cuda.synchronize()
+    pool.append_keys(model, kb, S.CODEC_INT4_GROUPED, n=n, key_dtype=S.BF16, want_slots=False)
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "evicted.sllg")
+        pool.attach_event_log(path)
+        pool.set_budget(96 * (n // 4))  # everything is paged out (96 B per WARM tile), then three quarters are evicted
+        S.synchronize()
+        t0 = time.perf_counter()
+        within = pool.enforce_budget()
+        S.synchronize()
+        dt = time.perf_counter() - t0
+        st = pool.event_log_stats()
+        out["event_log"] = {"workload": "262144 tiles, budget for a quarter of them: page-out of all, eviction of 196608 with their records appended",
+                            "ms": 1e3 * dt, "records": st["records"], "log_mb": (16 + 144 * st["records"]) / 1e6,
+                            "evicted_tiles_per_s": st["records"] / dt, "within_budget": bool(within), "log_errors": st["log_errors"]}
+    pool.destroy()
+    return out
+
+
 def pool_arm(args):
     """--workload c4 on its own: the elastic pool's decode step (one GPU; the pool does not shard)."""
     import torch
@@ -719,6 +801,8 @@ def gpu_arm(args, w):
             torch.cuda.empty_cache()
             S.set_stream(None)
             also["c4"] = run_pool_workload(args, S, torch, dev)
+            torch.cuda.empty_cache()
+            also["next_rows"] = run_next_rows(S, torch, dev)
     if rank == 0:
         line["also"] = also
         print(json.dumps(line))

@@ -208,9 +208,9 @@ int32_t slha_b200_score_segments(const SciRustSlhaTile* tiles, const SlhaB200Seg
         Ctx* c = cs.c;
         std::vector<SlhaB200Segment> hseg(n_segments);
         std::vector<uint64_t> hoff(n_queries);
-        if (is_device_ptr(segments)) SLHA_CUDA(cudaMemcpy(hseg.data(), segments, n_segments * sizeof(SlhaB200Segment), cudaMemcpyDeviceToHost));
+        if (is_device_ptr(segments)) { SLHA_CUDA(cudaMemcpyAsync(hseg.data(), segments, n_segments * sizeof(SlhaB200Segment), cudaMemcpyDeviceToHost, c->stream)); SLHA_CUDA(cudaStreamSynchronize(c->stream)); }  // (after the caller's work on this stream)
         else std::memcpy(hseg.data(), segments, n_segments * sizeof(SlhaB200Segment));
-        if (is_device_ptr(row_offsets)) SLHA_CUDA(cudaMemcpy(hoff.data(), row_offsets, n_queries * 8, cudaMemcpyDeviceToHost));
+        if (is_device_ptr(row_offsets)) { SLHA_CUDA(cudaMemcpyAsync(hoff.data(), row_offsets, n_queries * 8, cudaMemcpyDeviceToHost, c->stream)); SLHA_CUDA(cudaStreamSynchronize(c->stream)); }  // (after the caller's work on this stream)
         else std::memcpy(hoff.data(), row_offsets, n_queries * 8);
         for (size_t q = 0; q < n_queries; ++q)
             if (hoff[q] > scores_len || (uint64_t)row_len > scores_len - hoff[q])
@@ -244,7 +244,7 @@ int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment
         Ctx* c = cs.c;
         std::vector<SlhaB200Segment> hseg(n_segments);
         if (is_device_ptr(segments))
-            SLHA_CUDA(cudaMemcpy(hseg.data(), segments, n_segments * sizeof(SlhaB200Segment), cudaMemcpyDeviceToHost));
+            { SLHA_CUDA(cudaMemcpyAsync(hseg.data(), segments, n_segments * sizeof(SlhaB200Segment), cudaMemcpyDeviceToHost, c->stream)); SLHA_CUDA(cudaStreamSynchronize(c->stream)); }  // (after the caller's work on this stream)
         else
             std::memcpy(hseg.data(), segments, n_segments * sizeof(SlhaB200Segment));
         const float* dq;

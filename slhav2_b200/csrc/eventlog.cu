@@ -118,6 +118,51 @@ Status eventlog_append(EventLog* log, uint64_t seq, uint32_t slot, const unsigne
     return Status();
 }
 
+// The records of one eviction phase in one write (and, durable, one fsync): `*written` receives the number of leading
+// records that are in the file afterwards -- all of them, or, when the write fell short or failed, the complete records
+// that made it (the file is cut back to the last complete record; durable: to where it was, a batch is durable as a
+// whole or not at all).  The records' order and bytes are those of n single appends.
+Status eventlog_append_batch(EventLog* log, uint64_t n, const uint64_t* seq, const uint32_t* slot, const unsigned char* tiles,
+                             bool durable, uint64_t* written) {
+    *written = 0;
+    if (n == 0) return Status();
+    if (!log->writable) return Status(SLHA_ERR_IO, "EventLog: opened read-only");
+    std::vector<unsigned char> buf((size_t)n * LOG_RECORD);
+    for (uint64_t i = 0; i < n; ++i) {
+        unsigned char* r = buf.data() + (size_t)i * LOG_RECORD;
+        put64(r, seq[i]);
+        put32(r + 8, slot[i]);
+        std::memcpy(r + 16, tiles + (size_t)i * 128, 128);
+        put32(r + 12, log->version >= 2 ? record_checksum(r, r + 16) : 0u);
+    }
+    const off_t at = (off_t)(LOG_HEADER + log->records * LOG_RECORD);
+    size_t done = 0;
+    bool failed = false;
+    while (done < buf.size()) {
+        const ssize_t w = ::pwrite(log->fd, buf.data() + done, buf.size() - done, at + (off_t)done);
+        if (w <= 0) {
+            failed = true;
+            break;
+        }
+        done += (size_t)w;
+    }
+    if (!failed && durable && fsync(log->fd) != 0) {
+        failed = true;
+        done = 0;
+    }
+    if (failed) {
+        const Status st = io_error("cannot append records");
+        const uint64_t whole = done / LOG_RECORD;
+        if (ftruncate(log->fd, at + (off_t)(whole * LOG_RECORD)) != 0) { /* the next open_recover drops the tail */ }
+        log->records += whole;
+        *written = whole;
+        return st;
+    }
+    log->records += n;
+    *written = n;
+    return Status();
+}
+
 // EventLog::fetch_by_seq (eventlog.rs:475-477): the most recently appended record with that seq.
 Status eventlog_fetch_by_seq(EventLog* log, uint64_t seq, bool* found, uint32_t* slot, unsigned char* tile) {
     *found = false;

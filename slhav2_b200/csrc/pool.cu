@@ -960,16 +960,17 @@ Status pool_enforce_budget(Ctx* c, Pool* pl, int32_t* within) {
                 SLHA_CUDA(cudaMemcpyAsync(htiles.data(), d_tiles, (size_t)m * TILE_BYTES, cudaMemcpyDeviceToHost, c->stream));
                 SLHA_CUDA(cudaStreamSynchronize(c->stream));
             }
-            for (unsigned long long i = 0; i < m; ++i) {
-                const bool ok = pl->log && eventlog_append(pl->log, hseq[i], hslot[i], htiles.data() + (size_t)i * TILE_BYTES, pl->require_durable).ok();
-                if (ok) continue;
+            // all records of the phase in one write (the same bytes in the same order as one append per eviction)
+            uint64_t written = 0;
+            const bool ok = m == 0 || (pl->log && eventlog_append_batch(pl->log, m, hseq.data(), hslot.data(), htiles.data(), pl->require_durable, &written).ok());
+            if (!ok) {
                 if (pl->log) ++pl->log_errors;
                 if (pl->require_durable) {
-                    // the slot stays live; the reference goes on to try (and be refused) every remaining live slot
-                    limit = i;
-                    pl->blocked_evictions += (uint64_t)nc - i;
-                    if (pl->log) pl->log_errors += (uint64_t)nc - i - 1;
-                    break;
+                    // record `written` could not be persisted: its slot stays live; the reference goes on to try (and be
+                    // refused) every remaining live slot
+                    limit = written;
+                    pl->blocked_evictions += (uint64_t)nc - written;
+                    if (pl->log) pl->log_errors += (uint64_t)nc - written - 1;
                 }
             }
         }

@@ -37,6 +37,8 @@ Status eventlog_open(const char* path, int mode, EventLog** out);
 void eventlog_close(EventLog* log);
 uint64_t eventlog_records(const EventLog* log);
 Status eventlog_append(EventLog* log, uint64_t seq, uint32_t slot, const unsigned char* tile, bool durable);
+Status eventlog_append_batch(EventLog* log, uint64_t n, const uint64_t* seq, const uint32_t* slot, const unsigned char* tiles,
+                             bool durable, uint64_t* written);
 Status eventlog_fetch_by_seq(EventLog* log, uint64_t seq, bool* found, uint32_t* slot, unsigned char* tile);
 
 struct Pool {

@@ -720,7 +720,6 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         // the stream's static deal belongs to CTA r mod il_n.  Otherwise the item is this CTA's own range.
         const bool il = (it.pad >> 31) != 0;
         const uint32_t il_n = il ? ((it.pad >> 8) & 0x7FFFFFu) : 1u, il_c = il ? it.list_begin : 0u;
-        const uint32_t s_step = il_n * (uint32_t)nwarps;  // from one of this warp's sets to its next
         __syncthreads();  // previous item fully retired (and the table is visible)
         // The first sets are fetched before anything else of the item is prepared: the copy runs while the query
         // fragments are built.
@@ -734,8 +733,22 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         uint32_t* const hrow = a.ghist + (size_t)Qt * 256;                 // and its histogram
         // sets are dealt to the warps round by round: warp w takes set j * nwarps + w of round j
         const unsigned char* tbase = a.tiles + it.tile_begin * TILE_BYTES + lane * 16;
-        uint32_t s_next = il_c * (uint32_t)nwarps + (uint32_t)warp, slot_next = 0;
+        // This CTA's rounds of the deal, r = il_c, il_c + il_n, ..; an interleaved CTA walks them starting from a place of its
+        // own and wraps around (CTA c of C starts c / C of the way through), so that at any moment the CTAs of a stream are
+        // spread over the whole stream -- the first thresholds then come from a sample of all positions even when one
+        // end of the stream holds nothing to score (the oldest slots of a pool are mostly COLD).
+        const uint32_t all_rounds = (n_sets + (uint32_t)nwarps - 1) / (uint32_t)nwarps;
+        const uint32_t my_rounds = all_rounds > il_c ? (all_rounds - il_c + il_n - 1) / il_n : 0u;  // (the same for all warps of the CTA)
+        const uint32_t first_round = il ? (uint32_t)(((uint64_t)il_c * my_rounds) / il_n) : 0u;
+        auto set_of = [&](uint32_t i) {  // the set this warp takes in its i-th iteration
+            uint32_t j = i + first_round;
+            if (j >= my_rounds) j -= my_rounds;
+            return (j * il_n + il_c) * (uint32_t)nwarps + (uint32_t)warp;
+        };
+        uint32_t iss_no = 0, slot_next = 0;
         auto issue = [&]() {
+            const uint32_t s_next = iss_no < my_rounds ? set_of(iss_no) : 0xFFFFFFFFu;
+            ++iss_no;
             if (s_next < n_sets) {
                 const uint32_t dst = stage_s + slot_next + dst_lane;
                 const unsigned char* src = tbase + (size_t)s_next * MMA_SET_BYTES;
@@ -754,7 +767,6 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
                 }
             }
             cp_async_commit();
-            s_next += s_step;
             slot_next = slot_next == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot_next + MMA_SET_STRIDE;
         };
 #pragma unroll
@@ -844,10 +856,9 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         uint32_t slot = 0, polls = 0;
         uint32_t cur = 0, end = 0;  // this warp's chunk of the buffer of row Qt (the same in the eight lanes of a query)
         bool dead = false;          // this warp met a tile it cannot decode
-        const uint32_t all_rounds = (n_sets + (uint32_t)nwarps - 1) / (uint32_t)nwarps;
-        const uint32_t rounds = all_rounds > il_c ? (all_rounds - il_c + il_n - 1) / il_n : 0u;  // (the same for all warps of the CTA)
+        const uint32_t rounds = too_big ? 0u : my_rounds;
         for (uint32_t round = 0; round < rounds; ++round) {
-            const uint32_t s = (round * il_n + il_c) * (uint32_t)nwarps + (uint32_t)warp;
+            const uint32_t s = set_of(round);
             if (round == 1 && first_round_barrier) {
                 // Every warp of the CTA (and, started together, of the grid) has appended its first set
                 // unfiltered, so the rows' histograms hold 16 candidates per warp: first thresholds now,
@@ -858,12 +869,14 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
                 __syncthreads();
                 PROBE_SET(3);
             }
-            if (dead || s >= n_sets) continue;
+            // (the ring advances in every iteration, also when this warp has no set in this round -- the short last round of
+            // the stream can come anywhere in a rotated walk -- so that fetches and reads stay in step)
             issue();
             cp_async_wait<MMA_DEPTH - 1>();
             __syncwarp();
             const uint32_t rb = stage_s + slot + row_lane;
             slot = slot == (MMA_DEPTH - 1) * MMA_SET_STRIDE ? 0u : slot + MMA_SET_STRIDE;
+            if (dead || s >= n_sets) continue;
             const uint2 m0 = lds_v2<96>(rb), m1 = lds_v2<96 + MMA_HALF>(rb);    // scale, lambda
             const uint4 x0 = lds_v4<112>(rb), x1 = lds_v4<112 + MMA_HALF>(rb);  // position, head|flags, gs[8]
             const uint32_t f0 = x0.y >> 16, f1 = x1.y >> 16;

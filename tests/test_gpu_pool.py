@@ -180,3 +180,30 @@ def test_large_pool_enforce_budget_with_long_candidate_lists(codec, page, evict,
         assert pool.enforce_budget() == cache.enforce_budget()
         assert pool.live_bytes() <= budget
     assert_same(pool, cache, 1e-3)  # (the oracle sums 90 000 softmax terms sequentially in f32, the pool in a tree)
+
+
+def test_scoring_a_pool_whose_oldest_slots_are_cold_stays_on_the_tensor_core_kernel():
+    # One long stream scored by every CTA, with nothing to score at its start (the oldest third of the slots is COLD):
+    # the first thresholds must still form early, otherwise the rows' candidate buffers overflow and the rows are handed
+    # to the generic kernel (correct, but several times slower) -- the statistics call shows which happened.
+    n, k = 300000, 64
+    base = H.random_tiles(5000, 3, seed=55)
+    tiles = np.tile(base, n // 5000)
+    tiles["dynamic_lambda"] *= (1 + np.random.default_rng(2).random(n)).astype(F)
+    pool = S.TilePool(n, 2**40, S.PAGE_OLDEST_FIRST, S.EVICT_CAUSAL)
+    for b in range(0, n, 50000):
+        pool.insert(tiles[b:b + 50000])
+    pool.set_budget(96 * (n - 100000))
+    assert pool.enforce_budget()  # every tile is paged out (96 live bytes each), then causal eviction takes exactly the oldest 100000
+    now, state = pool.read()[:2]
+    assert np.all(state[:100000] == ora.COLD) and np.all(state[100000:] == ora.WARM)
+    qc, qs = H.random_queries(4, 56)
+    ti, tv, tc = pool.score_topk(qc, qs, 4, k)
+    stats = S.last_score_stats()
+    assert stats["rows_handed_to_generic_kernel"] == 0, stats
+    assert stats["candidates_appended"] < 4 * 60000, stats
+    for j in range(4):
+        want = ora.score_tiles(now[100000:], qc[j], qs[j])
+        oi, ov = ora.topk(want, k)
+        assert tc[j] == k and np.all(np.abs(tv[j] - ov) <= 1e-3)
+        assert np.all(ti[j] >= 100000)
