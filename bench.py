@@ -537,7 +537,7 @@ def run_scoring_workload(args, w, S, torch, dist, rank, local, world, dev, strea
         "roofline": {"bound": "hbm", "kernel": "score_stream_kernel (fused eq. 2.3 score + streaming top-k)", "achieved": achieved,
                      "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "frac_of_nominal_8000": achieved / 8000.0, "kernel_ms": k_ms,
-                     "merge_kernel_ms": float(np.median(merge_ms)) if len(merge_ms) else None,
+                     "merge_kernel_ms": float(np.median(merge_ms)) if len(merge_ms) else None,  # (early-exit pass of the generic kernel, compaction, merge)
                      "algorithmic_bytes_per_launch": n_tiles * 128,
                      "traffic": ncu_traffic(w["codec_name"], n_tiles, nq),
                      "traffic_source": "ncu dram__bytes of the same kernel on this workload shape, per tile and per query row, "

@@ -204,7 +204,9 @@ int32_t slha_b200_last_score_stats(uint64_t* out /* 4 values */);
 /* Device timing of the fused score + top-k path: after timing_begin, each of
  * the calling thread's next `max_calls` slha_b200_score_topk /
  * slha_b200_pool_score_topk calls records CUDA events on its stream around the
- * scoring kernel(s) and around the merge kernel.  timing_end drains the stream,
+ * scoring kernel (the tensor-core kernel when it runs, else the generic kernel)
+ * and around what follows it (the generic kernel's pass over rows the
+ * tensor-core kernel handed back, compaction, merge).  timing_end drains the stream,
  * writes per-call milliseconds (host arrays of `capacity` floats, may be NULL)
  * and the number of recorded calls, and stops recording. */
 int32_t slha_b200_timing_begin(uint32_t max_calls);

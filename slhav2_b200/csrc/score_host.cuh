@@ -688,6 +688,9 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         }
         count_launch();
         SLHA_CUDA(cudaGetLastError());
+        // (timing: the first bracket is the tensor-core kernel alone; the generic kernel's pass over handed-back rows, an
+        // early exit when there are none, counts with the compaction and the merge)
+        if (timed) SLHA_CUDA(cudaEventRecord(tev[1], c->stream));
     }
     for (const Plan::Class& cl : p->classes) {
         ScoreArgs a{};
@@ -704,7 +707,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         a.cand_cnt = p->d_cand_cnt;
         SLHA_TRY(launch_score<true>(c, cl.G, a, cl.count, p->threads, score_smem_bytes(cl.G, nwarps, true, p->cap)));
     }
-    if (timed) SLHA_CUDA(cudaEventRecord(tev[1], c->stream));
+    if (timed && !mma) SLHA_CUDA(cudaEventRecord(tev[1], c->stream));
     static thread_local bool configured[16] = {false};  // the attribute is per device
     if (!configured[c->device & 15]) {
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<CompLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
