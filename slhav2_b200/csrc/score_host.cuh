@@ -575,9 +575,103 @@ Status launch_score_full(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
 // Dense scores of whole segments in one launch: every query row of a segment against every tile of the segment,
 // row q written at scores + row_offsets[q] + index_base + tile, the rest of the row up to row_len set to `fill`.
 // Work items: (segment, group of up to four query rows, run of 4096 tiles) on the generic kernel.
+// fill of the rows' tails [tail_begin[q], row_len) (one CTA per row)
+__global__ void fill_rows_kernel(float* scores, const unsigned long long* row_offset, const uint32_t* tail_begin, uint32_t row_len, float fill) {
+    float* row = scores + row_offset[blockIdx.x];
+    for (uint32_t e = tail_begin[blockIdx.x] + threadIdx.x; e < row_len; e += blockDim.x) row[e] = fill;
+}
+
 Status launch_score_segments(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* segs, size_t n_segs, const float* d_q_coarse,
                              const uint64_t* d_q_sign, size_t nq, float* d_scores, const unsigned long long* d_row_offsets,
                              uint32_t row_len, float fill) {
+    // Sixteen or more query rows per segment and INT4 / MX-INT4 or TQ3 tiles (by the first tile): the contraction runs on the
+    // tensor cores (score_wide_kernel in its dense mode); rows it cannot score (a tile of another codec, a query outside the
+    // fp16 split) are flagged and the generic kernel below scores them.
+    bool wide = n_segs > 0 && wide_smem_bytes() <= MAX_SMEM;
+    uint64_t wtotal = 0;
+    for (size_t i = 0; i < n_segs && wide; ++i) {
+        wide = segs[i].n_queries >= 16 || segs[i].n_tiles == 0;
+        wtotal += (uint64_t)segs[i].n_tiles * ((segs[i].n_queries + WIDE_NQ - 1) / WIDE_NQ);
+    }
+    int kindw = -1;
+    for (size_t i = 0; i < n_segs && wide && wtotal && kindw < 0; ++i)
+        if (segs[i].n_tiles) {
+            uint16_t flags = 0;
+            const unsigned char* t0 = reinterpret_cast<const unsigned char*>(tiles) + segs[i].tile_begin * TILE_BYTES;
+            SLHA_CUDA(cudaMemcpyAsync(&flags, t0 + 118, 2, cudaMemcpyDeviceToHost, c->stream));
+            SLHA_CUDA(cudaStreamSynchronize(c->stream));
+            kindw = (flags & (F_NF4 | F_MIXED | F_MIX3)) ? 2 : ((flags & F_TQ3) ? 1 : 0);
+        }
+    wide = wide && wtotal > 0 && (kindw == 0 || kindw == 1);
+    uint32_t* d_gflag = nullptr;
+    if (wide) {
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
+        uint64_t wshare = (wtotal + sms - 1) / sms;
+        wshare = std::max<uint64_t>(WIDE_M, (wshare + WIDE_M - 1) / WIDE_M * WIDE_M);
+        std::vector<WorkItem> wi;
+        std::vector<uint32_t> wcta(1, 0), tail(nq, row_len);
+        uint64_t wfilled = 0;
+        for (size_t i = 0; i < n_segs; ++i) {
+            const SlhaB200Segment& s = segs[i];
+            if ((uint64_t)s.query_begin + s.n_queries > nq) return Status(SLHA_ERR_DIMENSION, "segment query range exceeds n_queries");
+            if ((uint64_t)s.index_base + s.n_tiles > row_len) return Status(SLHA_ERR_DIMENSION, "segment does not fit a row of row_len scores");
+            for (uint32_t q = 0; q < s.n_queries; ++q) tail[s.query_begin + q] = s.index_base + s.n_tiles;
+            for (uint32_t q0 = 0; q0 < s.n_queries; q0 += WIDE_NQ)
+                for (uint32_t pos = 0; pos < s.n_tiles;) {
+                    const uint32_t take = (uint32_t)std::min<uint64_t>(s.n_tiles - pos, wshare - wfilled);
+                    WorkItem w{};
+                    w.tile_begin = s.tile_begin + pos;
+                    w.n_tiles = take;
+                    w.index_base = s.index_base + pos;
+                    w.query_begin = s.query_begin + q0;
+                    w.n_queries = std::min<uint32_t>(WIDE_NQ, s.n_queries - q0);
+                    wi.push_back(w);
+                    pos += take;
+                    wfilled += take;
+                    if (wfilled >= wshare) {
+                        wfilled = 0;
+                        wcta.push_back((uint32_t)wi.size());
+                    }
+                }
+        }
+        if (wcta.back() != (uint32_t)wi.size()) wcta.push_back((uint32_t)wi.size());
+        WorkItem* d_wi;
+        uint32_t *d_wcta, *d_tail;
+        SLHA_TRY(ctx_device_scratch(c, wi.size() * sizeof(WorkItem), (void**)&d_wi));
+        SLHA_TRY(ctx_device_scratch(c, wcta.size() * 4, (void**)&d_wcta));
+        SLHA_TRY(ctx_device_scratch(c, nq * 4, (void**)&d_tail));
+        SLHA_TRY(ctx_device_scratch(c, nq * 4, (void**)&d_gflag));
+        SLHA_CUDA(cudaMemcpyAsync(d_wi, wi.data(), wi.size() * sizeof(WorkItem), cudaMemcpyHostToDevice, c->stream));
+        SLHA_CUDA(cudaMemcpyAsync(d_wcta, wcta.data(), wcta.size() * 4, cudaMemcpyHostToDevice, c->stream));
+        SLHA_CUDA(cudaMemcpyAsync(d_tail, tail.data(), nq * 4, cudaMemcpyHostToDevice, c->stream));
+        SLHA_CUDA(cudaMemsetAsync(d_gflag, 0, nq * 4, c->stream));
+        SLHA_CUDA(cudaStreamSynchronize(c->stream));  // (the host vectors go away)
+        static thread_local bool configured[16] = {false};
+        if (!configured[c->device & 15]) {
+            SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            configured[c->device & 15] = true;
+        }
+        ScoreArgs a{};
+        a.tiles = reinterpret_cast<const unsigned char*>(tiles);
+        a.items = d_wi;
+        a.n_items = (uint32_t)wi.size();
+        a.cta_begin = d_wcta;
+        a.q_coarse = d_q_coarse;
+        a.q_sign = reinterpret_cast<const uint32_t*>(d_q_sign);
+        a.scores = d_scores;
+        a.row_offset = d_row_offsets;
+        a.gflag = d_gflag;
+        const uint32_t grid = (uint32_t)wcta.size() - 1;
+        if (kindw == 1) score_wide_kernel<1, true><<<grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
+        else score_wide_kernel<0, true><<<grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
+        count_launch();
+        SLHA_CUDA(cudaGetLastError());
+        fill_rows_kernel<<<(uint32_t)nq, 256, 0, c->stream>>>(d_scores, d_row_offsets, d_tail, row_len, fill);
+        count_launch();
+        SLHA_CUDA(cudaGetLastError());
+    }
     const uint32_t item_tiles = 4096;
     std::vector<WorkItem> items;
     for (size_t i = 0; i < n_segs; ++i) {
@@ -594,7 +688,7 @@ Status launch_score_segments(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB20
                 w.query_begin = s.query_begin + q0;
                 w.n_queries = std::min<uint32_t>(4, s.n_queries - q0);
                 pos += w.n_tiles;
-                w.pad = pos >= s.n_tiles ? 1u : 0u;
+                w.pad = (pos >= s.n_tiles && !wide) ? 1u : 0u;  // (the rows' tails: filled above when the tensor-core kernel ran)
                 items.push_back(w);
             } while (pos < s.n_tiles);
         }
@@ -614,6 +708,7 @@ Status launch_score_segments(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB20
     a.row_offset = d_row_offsets;
     a.row_len = row_len;
     a.row_fill = fill;
+    a.gflag = d_gflag;  // (behind the tensor-core kernel: only the work items of rows it handed back)
     return launch_score<false>(c, 4, a, (uint32_t)items.size(), threads, score_smem_bytes(4, nwarps, false, 0));
 }
 
@@ -668,15 +763,15 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
         if (p->wide) {
             static thread_local bool wide_configured[16] = {false};
             if (!wide_configured[c->device & 15]) {
-                SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
-                SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+                SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+                SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
                 wide_configured[c->device & 15] = true;
             }
             a.items = p->d_wide_items;
             a.n_items = p->n_wide_items;
             a.cta_begin = p->d_wide_cta;
-            if (kind == 2) score_wide_kernel<1><<<p->wide_grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
-            else score_wide_kernel<0><<<p->wide_grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
+            if (kind == 2) score_wide_kernel<1, false><<<p->wide_grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
+            else score_wide_kernel<0, false><<<p->wide_grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
         } else {
 #define SLHA_LAUNCH_MMA(K)                                                                                             \
     do {                                                                                                               \

@@ -169,8 +169,10 @@ __device__ __forceinline__ void wide_refresh_rows(const ScoreArgs& a, uint32_t Q
     }
 }
 
-// KINDW 0: INT4 / MX-INT4 tiles, 1: TQ3 tiles
-template <int KINDW>
+// KINDW 0: INT4 / MX-INT4 tiles, 1: TQ3 tiles.  DENSE: every score is written to its row of a.scores (row q starts at
+// a.row_offset[q]) instead of going through the top-k filter: the dense scores of a layer for callers that replace
+// attention logits (the llama.cpp shim).
+template <int KINDW, bool DENSE>
 __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // shared layout (1024-byte aligned base): B | A[0] | A[1] | raw[0] | raw[1] | sign words | thresholds | mappings | barriers
@@ -187,6 +189,7 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
     uint64_t* bars = reinterpret_cast<uint64_t*>(rmap + 64);        // full[2], mma_done[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);    // [0] TMEM base, [1] error flag, [2] bail
     float2* colmm = reinterpret_cast<float2*>(bars + 8);            // [4][64] per tile quarter: (min, max) coarse score of a column
+    unsigned long long* roff = reinterpret_cast<unsigned long long*>(colmm);  // DENSE: [64] where the item's rows start in a.scores
     const uint32_t bars_s = base_s + 3 * WIDE_A_BYTES + 2 * WIDE_RAW_BYTES + 2048 + 256 + 256 + 512 + 512;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int MMA_WARP = WIDE_WORKERS / 32;
@@ -219,7 +222,8 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
         const WorkItem it = a.items[item_id];
         const int nq = (int)it.n_queries;
         __syncthreads();  // the previous item's MMAs and scores are finished: B, thresholds and sign words may change
-        if (tid < WIDE_NQ) {
+        if (DENSE && tid < WIDE_NQ) roff[tid] = tid < nq ? a.row_offset[it.query_begin + tid] : 0ull;
+        if (!DENSE && tid < WIDE_NQ) {
             const bool have = tid < nq;
             const unsigned long long pv = have ? *reinterpret_cast<volatile unsigned long long*>(a.gpivot + it.query_begin + tid) : ~0ull;
             pvh[tid] = (uint32_t)(pv >> 32);
@@ -263,7 +267,7 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
         }
         if (big) tmem_slot[2] = 1;  // a query too large for the fp16 split
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // B was written with ordinary stores, the MMA reads it through the async proxy
-        const bool need_map = __syncthreads_or(tid < nq && rng[tid].y == 0.0f) != 0;  // a row of the item has no bucket mapping yet
+        const bool need_map = __syncthreads_or(!DENSE && tid < nq && rng[tid].y == 0.0f) != 0;  // a row of the item has no bucket mapping yet
         const bool too_big = tmem_slot[2] != 0;
         const uint32_t n = it.n_tiles;
         WPROBE_LAP(0);  // item set-up
@@ -395,6 +399,19 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
                                   __popc(rb2.x ^ qw[4]) + __popc(rb2.y ^ qw[5]) + __popc(rb2.z ^ qw[6]) + __popc(rb2.w ^ qw[7]);
                     return fmaf(lam, (float)(256 - 2 * h), coarse);
                 };
+                if (DENSE) {
+                    if (cols) {
+                        uint32_t v[32];
+                        wide_tmem_ld32(tm, v);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int q = 16 * ch + j;
+                            if (q >= nq || !live) continue;
+                            // (the 32 lanes of the warp hold 32 consecutive tiles: one 128-byte store per row)
+                            a.scores[roff[q] + it.index_base + t0] = full_score((__uint_as_float(v[2 * j]) + __uint_as_float(v[2 * j + 1])) * su, q);
+                        }
+                    }
+                } else {
                 if (b == 0) {
                     // The first block of an item is walked before it is filtered.  (1) Rows without a bucket mapping get one
                     // from the block's coarse scores (any monotone mapping is valid): column minima and maxima per tile
@@ -514,9 +531,10 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
                         }
                     }
                 }
+                }  // !DENSE
                 WPROBE_LAP(1 + 8);  // filter and append (index 9)
                 // thresholds again after every second block; worker w looks after rows 4 w .. 4 w + 3
-                if ((b & 1u) == 1u && b + 1 < blocks) {
+                if (!DENSE && (b & 1u) == 1u && b + 1 < blocks) {
                     const int rows = min(4, nq - 4 * warp);
                     if (rows > 0) wide_refresh_rows<4>(a, it.query_begin + 4u * (uint32_t)warp, rows, rng + 4 * warp, pvh + 4 * warp, thr + 4 * warp, lane);
                     WPROBE_LAP(6);

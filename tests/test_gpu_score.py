@@ -135,3 +135,36 @@ def test_score_segments_writes_a_layer_of_dense_rows_in_one_call():
     with pytest.raises(S.SlhaError) as e:
         S.score_segments(dt, S.make_segments([(0, 10, 0, 1, 0)]), qc_l[:1], qs_l[:1], 1, dev, [3 * n_kv + 1], n_kv)
     assert e.value.code == S.ERR_DIMENSION
+
+
+@pytest.mark.parametrize("codec,foreign", [(0, False), (1, False), (6, False), (4, False), (4, True), (0, True), (3, False)])
+def test_score_segments_with_many_query_rows_uses_the_tensor_cores_and_agrees_with_the_oracle(codec, foreign):
+    # sixteen or more query rows per segment: INT4 / MX-INT4 / TQ3 tiles are scored by the tcgen05 kernel in its dense mode
+    # (other codecs, here mixed 8/4, by the generic kernel).  `foreign`: a few tiles of another codec inside a segment --
+    # the rows of the work items that meet them are handed to the generic kernel, the results stay the same.
+    lens = [5000, 0, 777, 128, 9001]
+    nqs = [16, 20, 64, 70, 33]
+    tiles = H.random_tiles(sum(lens), codec, seed=60 + codec, warm_every=13, nocorr_every=6)
+    if foreign:
+        other = H.random_tiles(sum(lens), 2, seed=61)
+        for i in (4000, 5000 + 777 + 128 + 4500):
+            tiles[i] = other[i]
+    dt = S.to_device(tiles)
+    qc, qs = H.random_queries(sum(nqs), 62 + codec)
+    row_len = 9100
+    segs, offsets, tb, qb = [], [], 0, 0
+    for n, q in zip(lens, nqs):
+        segs.append((tb, n, qb, q, 3))
+        tb += n
+        qb += q
+    order = np.random.default_rng(5).permutation(sum(nqs))  # rows lie in the destination in another order than the query rows
+    offsets = (order * row_len).astype(np.uint64)
+    out = np.full((sum(nqs), row_len), 55.0, F)
+    S.score_segments(dt, S.make_segments(segs), qc, qs, sum(nqs), out, offsets, row_len, fill=-2.0)
+    for (tb, n, qb, q, base) in segs:
+        for j in range(qb, qb + q):
+            row = out[order[j]]
+            if n:
+                _close(row[base:base + n], ora.score_tiles(tiles[tb:tb + n], qc[j], qs[j]))
+            assert np.all(row[base + n:] == -2.0)
+            assert np.all(row[:base] == 0.0)  # (before the segment's index base: no row covers it, a host destination comes back zero there)
