@@ -696,12 +696,11 @@ def run_next_rows(S, torch, dev):
                           "gathered_gb_per_s": nq * k * d_v * 2 / (ms * 1e-3) / 1e9}
     del values
 
-    # a layer's dense scores in one call: 8 KV heads x 32768 mixed 8/4 tiles, 16 tokens x 4 query heads per KV head
+    # a layer's dense scores in one call: 8 KV heads x 32768 tiles, 16 tokens x 4 query heads per KV head; once with the
+    # shim's default codec (mixed 8/4) and once with grouped INT4
     heads, tokens, n_tok, gqa = 8, 32768, 16, 4
     model = S.Model.from_projection(seeded_projection(11), HEAD_DIM, 11)
     keys = torch.randn(heads * tokens, HEAD_DIM, generator=gen, device=dev).to(torch.bfloat16).contiguous()
-    tiles = S.DeviceBuffer(heads * tokens * 128)
-    model.encode_keys(keys, S.CODEC_MIXED, n=heads * tokens, key_dtype=S.BF16, out=tiles)
     rows = heads * n_tok * gqa
     q = torch.randn(rows, HEAD_DIM, generator=gen, device=dev)
     qc = torch.empty(rows, 128, dtype=torch.float32, device=dev)
@@ -710,10 +709,14 @@ def run_next_rows(S, torch, dev):
     segs = S.make_segments([(h * tokens, tokens, h * n_tok * gqa, n_tok * gqa, 0) for h in range(heads)])
     offs = np.arange(rows, dtype=np.uint64) * np.uint64(tokens)  # (host descriptors: the call reads them without a stream round trip)
     dst = torch.empty(rows, tokens, dtype=torch.float32, device=dev)
-    ms = timed(lambda: S.score_segments(tiles, segs, qc, qs, rows, dst, offs, tokens), n=10)
-    out["score_segments"] = {"workload": "8 KV heads x 32768 mixed 8/4 tiles, 64 query rows per head, dense float32 scores", "ms": ms,
-                             "scores_per_s": rows * tokens / (ms * 1e-3), "written_gb_per_s": rows * tokens * 4 / (ms * 1e-3) / 1e9,
-                             "kernel": "generic CUDA-core kernel, four query rows per pass"}
+    tiles = S.DeviceBuffer(heads * tokens * 128)
+    out["score_segments"] = {"workload": "8 KV heads x 32768 tiles, 64 query rows per head, dense float32 scores (67 MB written per call)"}
+    for name, codec in (("mixed-8/4", S.CODEC_MIXED), ("int4-grouped", S.CODEC_INT4_GROUPED)):
+        model.encode_keys(keys, codec, n=heads * tokens, key_dtype=S.BF16, out=tiles)
+        l0 = S.launch_count()
+        ms = timed(lambda: S.score_segments(tiles, segs, qc, qs, rows, dst, offs, tokens), n=10)
+        out["score_segments"][name] = {"ms": ms, "scores_per_s": rows * tokens / (ms * 1e-3), "written_gb_per_s": rows * tokens * 4 / (ms * 1e-3) / 1e9,
+                                       "launches_per_call": (S.launch_count() - l0) / 13}
     del dst, keys
     tiles.free()
 

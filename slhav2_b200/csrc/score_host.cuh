@@ -402,7 +402,7 @@ Status build_plan(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* s
     // of up to 64 query rows; the (segment, row group) streams are cut into one share per CTA, in whole 128-tile blocks.
     uint32_t wide_parts = 1;
     {
-        bool all_wide = p->use_mma && allow_wide && n_segs > 0 && !p->mixed && (p->tq3 || !p->nf4_table);
+        bool all_wide = p->use_mma && allow_wide && n_segs > 0 && (p->mixed || p->tq3 || !p->nf4_table);
         uint64_t wtotal = 0;
         for (size_t i = 0; i < n_segs && all_wide; ++i) {
             all_wide = segs[i].n_queries >= 16 || segs[i].n_tiles == 0;
@@ -584,7 +584,7 @@ __global__ void fill_rows_kernel(float* scores, const unsigned long long* row_of
 Status launch_score_segments(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB200Segment* segs, size_t n_segs, const float* d_q_coarse,
                              const uint64_t* d_q_sign, size_t nq, float* d_scores, const unsigned long long* d_row_offsets,
                              uint32_t row_len, float fill) {
-    // Sixteen or more query rows per segment and INT4 / MX-INT4 or TQ3 tiles (by the first tile): the contraction runs on the
+    // Sixteen or more query rows per segment and INT4 / MX-INT4, TQ3 or mixed 8/4 tiles (by the first tile): the contraction runs on the
     // tensor cores (score_wide_kernel in its dense mode); rows it cannot score (a tile of another codec, a query outside the
     // fp16 split) are flagged and the generic kernel below scores them.
     bool wide = n_segs > 0 && wide_smem_bytes() <= MAX_SMEM;
@@ -600,9 +600,9 @@ Status launch_score_segments(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB20
             const unsigned char* t0 = reinterpret_cast<const unsigned char*>(tiles) + segs[i].tile_begin * TILE_BYTES;
             SLHA_CUDA(cudaMemcpyAsync(&flags, t0 + 118, 2, cudaMemcpyDeviceToHost, c->stream));
             SLHA_CUDA(cudaStreamSynchronize(c->stream));
-            kindw = (flags & (F_NF4 | F_MIXED | F_MIX3)) ? 2 : ((flags & F_TQ3) ? 1 : 0);
+            kindw = (flags & (F_NF4 | F_MIX3)) ? 3 : ((flags & F_MIXED) ? 2 : ((flags & F_TQ3) ? 1 : 0));
         }
-    wide = wide && wtotal > 0 && (kindw == 0 || kindw == 1);
+    wide = wide && wtotal > 0 && kindw >= 0 && kindw <= 2;
     uint32_t* d_gflag = nullptr;
     if (wide) {
         int sms = 148;
@@ -651,6 +651,7 @@ Status launch_score_segments(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB20
         if (!configured[c->device & 15]) {
             SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
             SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+            SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
             configured[c->device & 15] = true;
         }
         ScoreArgs a{};
@@ -665,6 +666,7 @@ Status launch_score_segments(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB20
         a.gflag = d_gflag;
         const uint32_t grid = (uint32_t)wcta.size() - 1;
         if (kindw == 1) score_wide_kernel<1, true><<<grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
+        else if (kindw == 2) score_wide_kernel<2, true><<<grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
         else score_wide_kernel<0, true><<<grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
         count_launch();
         SLHA_CUDA(cudaGetLastError());
@@ -765,12 +767,14 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
             if (!wide_configured[c->device & 15]) {
                 SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
                 SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+                SLHA_CUDA(cudaFuncSetAttribute(score_wide_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
                 wide_configured[c->device & 15] = true;
             }
             a.items = p->d_wide_items;
             a.n_items = p->n_wide_items;
             a.cta_begin = p->d_wide_cta;
             if (kind == 2) score_wide_kernel<1, false><<<p->wide_grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
+            else if (kind == 1) score_wide_kernel<2, false><<<p->wide_grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
             else score_wide_kernel<0, false><<<p->wide_grid, WIDE_THREADS, wide_smem_bytes(), c->stream>>>(a);
         } else {
 #define SLHA_LAUNCH_MMA(K)                                                                                             \

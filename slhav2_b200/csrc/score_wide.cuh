@@ -169,7 +169,9 @@ __device__ __forceinline__ void wide_refresh_rows(const ScoreArgs& a, uint32_t Q
     }
 }
 
-// KINDW 0: INT4 / MX-INT4 tiles, 1: TQ3 tiles.  DENSE: every score is written to its row of a.scores (row q starts at
+// KINDW 0: INT4 / MX-INT4 tiles, 1: TQ3 tiles, 2: mixed 8/4 tiles (the eight 8-bit head levels b - 128 take the K slots of
+// their own eight dims and of the eight dropped tail dims: (b - 128) gs = (b - 128) (16 gh + gl) with the scale byte's two
+// nibbles, two exact fp16 products per dim; the 112 INT4 dims follow as in kind 0, shifted by one word).  DENSE: every score is written to its row of a.scores (row q starts at
 // a.row_offset[q]) instead of going through the top-k filter: the dense scores of a layer for callers that replace
 // attention logits (the llama.cpp shim).
 template <int KINDW, bool DENSE>
@@ -240,8 +242,13 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
             const int n = u / 18, i = u % 18, qi = n >> 1;
             const float* q = a.q_coarse + (size_t)(it.query_begin + (qi < nq ? qi : 0)) * D_C;
             float v[8];
-            if (i < 16) {
-                const float4 x = *reinterpret_cast<const float4*>(q + 8 * i), y = *reinterpret_cast<const float4*>(q + 8 * i + 4);
+            if (KINDW == 2 && i < 2) {
+                // head chunk i: slots 0..3 meet the high-nibble products of dims 4 i .. 4 i + 3, slots 4..7 the low-nibble ones
+                const float4 x = *reinterpret_cast<const float4*>(q + 4 * i);
+                v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = x.x; v[5] = x.y; v[6] = x.z; v[7] = x.w;
+            } else if (i < 16) {
+                const int d0 = KINDW == 2 ? 8 * (i - 1) : 8 * i;  // (mixed: latent word i holds dims 8 (i - 1) ..)
+                const float4 x = *reinterpret_cast<const float4*>(q + d0), y = *reinterpret_cast<const float4*>(q + d0 + 4);
                 v[0] = x.x; v[1] = y.x; v[2] = x.y; v[3] = y.y; v[4] = x.z; v[5] = y.z; v[6] = x.w; v[7] = y.w;
             } else if (i == 16 && KINDW == 1) {
 #pragma unroll
@@ -313,7 +320,10 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
                 const uint32_t flags = lds_u16<118>(row_s);
                 const bool live = t0 + r < n;
                 // a codec this launch does not decode: the item's rows go to the generic kernel
-                if (live && ((KINDW == 1) ? !(flags & F_TQ3) || (flags & (F_NF4 | F_MIXED | F_MIX3)) : (flags & (F_NF4 | F_MIXED | F_TQ3 | F_MIX3)) != 0)) tmem_slot[2] = 1;
+                if (live && ((KINDW == 1)   ? !(flags & F_TQ3) || (flags & (F_NF4 | F_MIXED | F_MIX3))
+                             : (KINDW == 2) ? !(flags & F_MIXED) || (flags & (F_NF4 | F_TQ3 | F_MIX3))
+                                            : (flags & (F_NF4 | F_MIXED | F_TQ3 | F_MIX3)) != 0))
+                    tmem_slot[2] = 1;
                 uint32_t nib[4];
                 if (KINDW == 1) {
                     const uint32_t w0 = lds_u32(row_s + 12u * c), w1 = lds_u32(row_s + 12u * c + 4u), w2 = lds_u32(row_s + 12u * c + 8u);
@@ -342,7 +352,24 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
 #pragma unroll
                 for (int m = 0; m < 4; ++m) {
                     uint32_t o[4];
-                    int4c_word(nib[m], m < 2 ? G0 : G1, m < 2 ? C0 : C1, o);
+                    if (KINDW == 2 && c == 0 && m < 2) {
+                        // four head bytes b -> (b - 128) gh 2^-8 (slots 0..3) and (b - 128) gl 2^-12 (slots 4..7), gh / gl the nibbles
+                        // of the head's scale byte: products below 2048, exact in fp16
+                        const uint32_t gs0 = lds_u16<120>(row_s) & 0xFFu;
+                        uint32_t gh, gl, b01, b23;
+                        asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(gh) : "r"(0x64006400u | (gs0 >> 4) * 0x10001u), "r"(0xE400E400u));   // (gh, gh)
+                        asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(gl) : "r"(0x64006400u | (gs0 & 15u) * 0x10001u), "r"(0xE400E400u));  // (gl, gl)
+                        asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(gh) : "r"(gh), "r"(0x1C001C00u));  // x 2^-8
+                        asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(gl) : "r"(gl), "r"(0x0C000C00u));  // x 2^-12
+                        asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(b01) : "r"(prmt(nib[m], magic, 0x7150u)), "r"(0xE480E480u));  // bytes 0, 1 minus 128
+                        asm("add.rn.f16x2 %0, %1, %2;\n" : "=r"(b23) : "r"(prmt(nib[m], magic, 0x7352u)), "r"(0xE480E480u));  // bytes 2, 3
+                        asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(o[0]) : "r"(b01), "r"(gh));
+                        asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(o[1]) : "r"(b23), "r"(gh));
+                        asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(o[2]) : "r"(b01), "r"(gl));
+                        asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(o[3]) : "r"(b23), "r"(gl));
+                    } else {
+                        int4c_word(nib[m], m < 2 ? G0 : G1, m < 2 ? C0 : C1, o);
+                    }
                     if (!live) o[0] = o[1] = o[2] = o[3] = 0u;
                     const uint32_t word = 4u * c + (uint32_t)m, slab = word >> 3, chunk = word & 7u;
                     sts_v4(arow + slab * WIDE_SLAB + ((chunk ^ (r & 7u)) << 4), o[0], o[1], o[2], o[3]);

@@ -272,6 +272,8 @@ def test_rejected_call_shape_leaves_no_plan_behind():
     (9000, 100, 32, 4, 0, 0, None),      # TQ3, two items of 64 + 36 rows
     (20000, 24, 100, 0, 0, 0, 2),        # INT4 with a stretch of NF4 tiles: the rows are handed to the generic kernel
     (127, 20, 200, 1, 0, 0, None),       # fewer tiles than k and than one block
+    (21000, 40, 128, 3, 8, 0, None),     # mixed 8/4 (8-bit head levels split over two K slots each), WARM tiles
+    (7000, 64, 512, 3, 0, 0, 1),         # mixed 8/4 with a stretch of MX-INT4 tiles: handed to the generic kernel
 ])
 def test_wide_scoring_on_the_tcgen05_kernel(n, nq, k, codec, warm, nocorr, foreign):
     # 16 or more queries per segment: score_wide_kernel (128-tile blocks x up to 64 query rows on tcgen05 MMAs)
@@ -325,7 +327,7 @@ def test_random_call_shapes_match_the_oracle(trial):
     # index bases, one codec per call; a second identical call exercises the cached plan and the cleared streaming state
     rng = np.random.default_rng(7000 + trial)
     codec = [0, 1, 2, 3, 4, 6][trial % 6]
-    wide = trial % 4 == 3 and codec in (0, 1, 4, 6)
+    wide = trial % 4 == 3 and codec in (0, 1, 3, 4, 6)
     n_seg = int(rng.integers(1, 7))
     lens = [int(rng.choice([0, 1, 17, int(rng.integers(2, 3000)), int(rng.integers(3000, 60000))])) for _ in range(n_seg)]
     nqs = [int(rng.integers(20, 41)) if wide else int(rng.integers(1, 10)) for _ in range(n_seg)]
