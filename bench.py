@@ -387,6 +387,8 @@ def run_scoring_workload(args, w, S, torch, dist, rank, local, world, dev, strea
         dist.broadcast(t, 0)
         uid = t.cpu().numpy()
     shard = S.Shard(uid, rank, world)
+    if world > 1 and args.exchange != "peer":
+        shard.set_exchange(args.exchange)
 
     def step():
         shard.score_topk(tiles, segs, q_coarse, q_sign, nq, k, out_index=out_idx, out_score=out_sc)
@@ -435,6 +437,7 @@ def run_scoring_workload(args, w, S, torch, dist, rank, local, world, dev, strea
     def e2e_step():
         shard.score_topk(tiles, segs, hq, hs, nq, k, out_index=h_idx, out_score=h_sc)
 
+    barrier()  # (the ranks' verification took different times: start the next steps together)
     for _ in range(3):
         e2e_step()
     barrier()
@@ -516,6 +519,7 @@ def run_scoring_workload(args, w, S, torch, dist, rank, local, world, dev, strea
         v = torch.tensor([1 if (verified and e2e_ok) else 0], device=dev)
         dist.all_reduce(v, op=dist.ReduceOp.MIN)
         verified = bool(v.item())
+    shard_how = shard.status()
     shard.destroy()
     if rank != 0:
         return None
@@ -553,7 +557,7 @@ def run_scoring_workload(args, w, S, torch, dist, rank, local, world, dev, strea
         "clocks": clocks,
     }
     if world > 1:
-        rec["exchange"] = {"entry_point": "slha_b200_shard_score_topk", "ms_local_score_topk": float(comp[0]),
+        rec["exchange"] = {"entry_point": "slha_b200_shard_score_topk", "how": shard_how, "ms_local_score_topk": float(comp[0]),
                            "ms_all_gather": float(comp[1]), "ms_merge": float(comp[2]),
                            "all_gather_bytes_per_rank": int(2 * nq * k * 4)}
     if world == 1 and cpu_legs:
@@ -822,6 +826,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["c4"])
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the ranks' top-k lists meet (peer-memory loads by the merge kernel, or an NCCL all-gather)")
     ap.add_argument("--no-also", dest="also", action="store_false", help="only the named workload (no c1..c4 sub-records)")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: shrink the workload to this many layers")
     ap.add_argument("--tokens", type=int, default=0, help="profiling aid: shrink the workload to this many tokens")

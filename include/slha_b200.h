@@ -411,6 +411,15 @@ int32_t slha_b200_shard_score_topk(SlhaB200Shard* shard, const SciRustSlhaTile* 
  * its three durations in milliseconds: local score + top-k, all-gather, merge. */
 int32_t slha_b200_shard_set_timing(SlhaB200Shard* shard, int32_t on);
 int32_t slha_b200_shard_last_times(SlhaB200Shard* shard, float* ms_out /* 3 floats */);
+/* out[0]: how the ranks' lists meet -- 0 one rank, 1 ncclAllGather, 2 peer-memory loads: where the ranks are
+ * processes of one node whose GPUs can map each other's memory (CUDA IPC), no all-gather runs; every rank
+ * leaves its sorted block in its own memory, raises a flag in every peer's memory, and the merge kernel reads
+ * from the owners' blocks the few entries it needs over NVLink.  out[1]: 1 when a wait for a peer's flag ran
+ * out (ten seconds; the rows of that step came back empty).  out[2]: steps enqueued on this handle. */
+int32_t slha_b200_shard_status(SlhaB200Shard* shard, uint64_t* out /* 3 values */);
+/* mode 2 (the default): peer-memory loads where possible, else ncclAllGather; mode 1: ncclAllGather always.
+ * Every rank makes the same call, between steps. */
+int32_t slha_b200_shard_set_exchange(SlhaB200Shard* shard, int32_t mode);
 
 /*
  * Merge n_lists candidate lists per query (layout [list][query][k_in], as an

@@ -161,6 +161,8 @@ extern "C" {
     pub fn slha_b200_shard_score_topk(shard: *mut SlhaB200Shard, tiles: *const SciRustSlhaTile, segments: *const SlhaB200Segment, n_segments: usize, q_coarse: *const f32, q_sign: *const u64, n_queries: usize, k: u32, out_index: *mut u32, out_score: *mut f32) -> i32;
     pub fn slha_b200_shard_set_timing(shard: *mut SlhaB200Shard, on: i32) -> i32;
     pub fn slha_b200_shard_last_times(shard: *mut SlhaB200Shard, ms_out: *mut f32) -> i32;
+    pub fn slha_b200_shard_status(shard: *mut SlhaB200Shard, out: *mut u64) -> i32;
+    pub fn slha_b200_shard_set_exchange(shard: *mut SlhaB200Shard, mode: i32) -> i32;
     pub fn slha_b200_topk_merge(cand_index: *const u32, cand_score: *const f32, n_lists: u32, n_queries: u32, k_in: u32, k_out: u32, out_index: *mut u32, out_score: *mut f32) -> i32;
     pub fn slha_b200_topk_merge_strided(cand_index: *const u32, cand_score: *const f32, n_lists: u32, list_stride: u64, n_queries: u32, k_in: u32, k_out: u32, out_index: *mut u32, out_score: *mut f32) -> i32;
     pub fn slha_b200_topk_merge_sorted_strided(cand_index: *const u32, cand_score: *const f32, n_lists: u32, list_stride: u64, n_queries: u32, k_in: u32, k_out: u32, out_index: *mut u32, out_score: *mut f32) -> i32;

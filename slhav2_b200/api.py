@@ -98,6 +98,8 @@ SIGNATURES = {
     "slha_b200_shard_score_topk": (_i32, [_vp, _vp, _vp, _sz, _vp, _vp, _sz, _u32, _vp, _vp]),
     "slha_b200_shard_set_timing": (_i32, [_vp, _i32]),
     "slha_b200_shard_last_times": (_i32, [_vp, _vp]),
+    "slha_b200_shard_status": (_i32, [_vp, _vp]),
+    "slha_b200_shard_set_exchange": (_i32, [_vp, _i32]),
     "slha_b200_pool_create": (_i32, [_vp, C.POINTER(_vp)]),
     "slha_b200_pool_destroy": (_i32, [_vp]),
     "slha_b200_pool_insert_tiles": (_i32, [_vp, _vp, _sz, _vp]),
@@ -501,6 +503,16 @@ class Shard:
         ms = np.zeros(3, np.float32)
         _check(load_library().slha_b200_shard_last_times(self.handle, ptr(ms)))
         return ms
+
+    def set_exchange(self, mode):
+        """"peer" (default: peer-memory loads where the GPUs can map each other's memory) or "nccl" (always the all-gather)."""
+        _check(load_library().slha_b200_shard_set_exchange(self.handle, {"nccl": 1, "peer": 2}[mode]))
+
+    def status(self):
+        """How the ranks' lists meet ("single rank", "nccl all-gather", "peer-memory loads"), whether a wait for a peer ran out, steps so far."""
+        out = np.zeros(3, np.uint64)
+        _check(load_library().slha_b200_shard_status(self.handle, ptr(out)))
+        return {"exchange": ("single rank", "nccl all-gather", "peer-memory loads")[int(out[0])], "wait_ran_out": bool(out[1]), "steps": int(out[2])}
 
     def destroy(self):
         if self.handle:

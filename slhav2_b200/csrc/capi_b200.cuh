@@ -419,6 +419,23 @@ int32_t slha_b200_shard_set_timing(SlhaB200Shard* shard, int32_t on) {
         return shard_set_timing(reinterpret_cast<Shard*>(shard), on != 0);
     });
 }
+int32_t slha_b200_shard_set_exchange(SlhaB200Shard* shard, int32_t mode) {
+    return ffi([&]() -> Status {
+        if (!shard) return Status(SLHA_ERR_NULL, "slha_b200_shard_set_exchange received a NULL pointer");
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        SLHA_CUDA(cudaStreamSynchronize(c->stream));
+        return shard_set_exchange(reinterpret_cast<Shard*>(shard), mode);
+    });
+}
+int32_t slha_b200_shard_status(SlhaB200Shard* shard, uint64_t* out) {
+    return ffi([&]() -> Status {
+        if (!shard || !out) return Status(SLHA_ERR_NULL, "slha_b200_shard_status received a NULL pointer");
+        Ctx* c;
+        SLHA_TRY(get_ctx(&c));
+        return shard_status(c, reinterpret_cast<Shard*>(shard), out);
+    });
+}
 int32_t slha_b200_shard_last_times(SlhaB200Shard* shard, float* ms_out) {
     return ffi([&]() -> Status {
         if (!shard || !ms_out) return Status(SLHA_ERR_NULL, "slha_b200_shard_last_times received a NULL pointer");

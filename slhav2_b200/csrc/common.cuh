@@ -123,6 +123,9 @@ Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* 
                                uint32_t n_lists, uint64_t list_stride, uint32_t n_queries, uint32_t k_in,
                                uint32_t k_out, uint32_t* out_index, float* out_score, bool lists_sorted = false);
 
+Status launch_topk_merge_peers(Ctx* c, const uint32_t* const* d_bases, uint32_t n_lists, uint32_t n_queries, uint32_t k, const uint32_t* d_ready,
+                               uint32_t* d_step, uint32_t* d_done, uint32_t* d_status, uint32_t* out_index, float* out_score);
+
 // ---- token-range sharding over NCCL (shard.cu) ----------------------------------
 struct Shard;
 Status shard_unique_id(void* id128);
@@ -131,6 +134,8 @@ Status shard_destroy(Shard* s);
 void shard_info(const Shard* s, int* rank, int* world);
 Status shard_set_timing(Shard* s, bool on);
 Status shard_last_times(Ctx* c, Shard* s, float* ms3);
+Status shard_status(Ctx* c, Shard* s, uint64_t* out3);
+Status shard_set_exchange(Shard* s, int mode);
 Status shard_step_device(Ctx* c, Shard* s, const SciRustSlhaTile* tiles, const SlhaB200Segment* h_segs, size_t n_segs,
                          const float* d_qc, const uint64_t* d_qs, size_t nq, uint32_t k, uint32_t* d_out_index,
                          float* d_out_score);

@@ -842,7 +842,7 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
             L1, k, p->kp2, cap1, p->d_tmp_index, p->d_tmp_score, nullptr);
         count_launch();
         SLHA_CUDA(cudaGetLastError());
-        PairLists L2{p->d_tmp_index, p->d_tmp_score, p->n_groups, (uint32_t)nq, k, (uint64_t)nq * k, 1u};
+        PairLists L2{p->d_tmp_index, p->d_tmp_score, p->n_groups, (uint32_t)nq, k, (uint64_t)nq * k, 1u, nullptr, nullptr, nullptr, nullptr, nullptr};
         const uint32_t cap2 = merge_cap((uint64_t)p->n_groups * k, p->kp2, k);
         topk_merge_kernel<PairLists><<<(uint32_t)nq, merge_threads(cap2), merge_smem(cap2, p->kp2), c->stream>>>(
             L2, k, p->kp2, cap2, d_out_index, d_out_score, d_out_count);
@@ -918,7 +918,7 @@ Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* 
     if (k_out == 0 || k_out > 8192) return Status(SLHA_ERR_DIMENSION, "merge: k_out must be in 1..8192");
     uint32_t kp2 = 2;
     while (kp2 < k_out) kp2 <<= 1;
-    PairLists L{cand_index, cand_score, n_lists, n_queries, k_in, list_stride, lists_sorted ? 1u : 0u};
+    PairLists L{cand_index, cand_score, n_lists, n_queries, k_in, list_stride, lists_sorted ? 1u : 0u, nullptr, nullptr, nullptr, nullptr, nullptr};
     static thread_local bool configured[16] = {false};  // the attribute is per device
     if (!configured[c->device & 15]) {
         SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
@@ -926,6 +926,26 @@ Status launch_topk_merge_pairs(Ctx* c, const uint32_t* cand_index, const float* 
     }
     const uint32_t cap_s = merge_cap((uint64_t)n_lists * k_in, kp2, k_out);
     topk_merge_kernel<PairLists><<<n_queries, merge_threads(cap_s), merge_smem(cap_s, kp2), c->stream>>>(L, k_out, kp2, cap_s, out_index, out_score, nullptr);
+    count_launch();
+    SLHA_CUDA(cudaGetLastError());
+    return Status();
+}
+
+// The merge of a sharded step whose lists lie in their owners' memory (see PairLists::bases): lists ordered best first.
+Status launch_topk_merge_peers(Ctx* c, const uint32_t* const* d_bases, uint32_t n_lists, uint32_t n_queries, uint32_t k, const uint32_t* d_ready,
+                               uint32_t* d_step, uint32_t* d_done, uint32_t* d_status, uint32_t* out_index, float* out_score) {
+    if (n_queries == 0) return Status();
+    if (k == 0 || k > 8192) return Status(SLHA_ERR_DIMENSION, "merge: k must be in 1..8192");
+    uint32_t kp2 = 2;
+    while (kp2 < k) kp2 <<= 1;
+    PairLists L{nullptr, nullptr, n_lists, n_queries, k, 0, 1u, d_bases, d_ready, d_step, d_done, d_status};
+    static thread_local bool configured[16] = {false};  // the attribute is per device
+    if (!configured[c->device & 15]) {
+        SLHA_CUDA(cudaFuncSetAttribute(topk_merge_kernel<PairLists>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM));
+        configured[c->device & 15] = true;
+    }
+    const uint32_t cap_s = merge_cap((uint64_t)n_lists * k, kp2, k);
+    topk_merge_kernel<PairLists><<<n_queries, merge_threads(cap_s), merge_smem(cap_s, kp2), c->stream>>>(L, k, kp2, cap_s, out_index, out_score, nullptr);
     count_launch();
     SLHA_CUDA(cudaGetLastError());
     return Status();

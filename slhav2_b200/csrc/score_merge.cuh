@@ -45,6 +45,7 @@ struct CompLists {  // lists written by score_kernel
         return j < cnt[l] ? keys[(size_t)l * k + j] : 0ull;
     }
     __device__ void finish(uint32_t) const {}
+    __device__ bool wait_ready(int*) const { return true; }
     __device__ uint64_t floor_key(uint32_t, uint32_t, uint64_t*, uint32_t, int*) const { return 0ull; }
     __device__ ListView view(uint32_t Q, uint32_t part) const {
         const uint32_t l = q_list_begin[Q] + part * (q_list_count[Q] >> 24);
@@ -81,6 +82,7 @@ struct StreamLists {
     // The merge is the last reader of a row's streaming state: it leaves the state cleared for the next call
     // (which then needs no memset in front of its score kernel) and keeps the row's figures for the statistics call.
     __device__ uint64_t floor_key(uint32_t, uint32_t, uint64_t*, uint32_t, int*) const { return 0ull; }  // (the row's threshold filters already)
+    __device__ bool wait_ready(int*) const { return true; }
     __device__ ListView view(uint32_t Q, uint32_t part) const {
         if (gflag[Q]) return items.view(Q, part);
         if (compacted(Q)) return ListView{gsel + (size_t)Q * selcap, 0ull, gselcnt[Q]};
@@ -108,7 +110,46 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     uint32_t n_lists, n_queries, k_in;
     uint64_t list_stride;  // elements between the blocks of consecutive lists
     uint32_t sorted;       // every list is ordered best first (lists this library produced)
+    // Lists that lie where their owners wrote them, in the memory of other GPUs of the node (token-range sharding without
+    // an all-gather: the merge reads the few entries it needs over NVLink).  bases[l] = list l's index block, its score
+    // block n_queries * k_in words behind it; ready[l] (this GPU's memory, written by list l's owner) must have reached
+    // *step before list l is read; the last CTA to finish advances *step.  All null for lists in one local buffer.
+    const uint32_t* const* bases;
+    const uint32_t* ready;
+    uint32_t* step;
+    uint32_t* done;
+    uint32_t* status;
     __device__ ListView view(uint32_t, uint32_t) const { return ListView{nullptr, 0ull, k_in}; }
+    // false when an owner's flag did not arrive within ten seconds (*status is set; the caller writes an empty row)
+    __device__ bool wait_ready(int* ok_s_ptr) const {  // ok_s_ptr: one word of shared memory
+        if (!ready) return true;
+        int& ok_s = *ok_s_ptr;
+        if (threadIdx.x == 0) {
+            const uint32_t want = *reinterpret_cast<volatile uint32_t*>(step);
+            unsigned long long t0, t1;
+            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
+            int ok = 1;
+            for (uint32_t l = 0; l < n_lists && ok; ++l) {
+                for (;;) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(ready + l) : "memory");
+                    if ((int32_t)(v - want) >= 0) break;
+                    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t1));
+                    if (t1 - t0 > 10000000000ull) {  // ten seconds: the owner is gone
+                        ok = 0;
+                        atomicExch(status, 1u);
+                        break;
+                    }
+                    __nanosleep(200);
+                }
+            }
+            ok_s = ok;
+        }
+        __syncthreads();
+        const bool all_ok = ok_s != 0;
+        __syncthreads();  // (the word belongs to the merge's buffer from here on)
+        return all_ok;
+    }
     // A key that at least k candidates reach -- and few more -- from sorted lists alone.  Every list is sampled at every
     // `stride`-th entry (stride = k / (8 n_lists)); a sample certifies that `stride` more entries of its list are at
     // least as large.  For a sample v, L(v) = stride x (samples of all lists >= v) entries reach v for certain; the
@@ -167,17 +208,23 @@ struct PairLists {  // (index, score) lists laid out [list][query][k_in]
     __device__ uint32_t lists(uint32_t) const { return n_lists; }
     __device__ uint32_t list_len(uint32_t, uint32_t) const { return k_in; }
     __device__ uint64_t at(uint32_t Q, uint32_t part, uint32_t j) const {
+        if (bases) {  // (another GPU's memory: read past the L1)
+            const uint32_t* b = bases[part] + (size_t)Q * k_in + j;
+            const uint32_t i = __ldcg(b);
+            return i == 0xFFFFFFFFu ? 0ull : make_comp(__uint_as_float(__ldcg(b + (size_t)n_queries * k_in)), i);
+        }
         const size_t o = (size_t)part * list_stride + (size_t)Q * k_in + j;
         const uint32_t i = idx[o];
         return i == 0xFFFFFFFFu ? 0ull : make_comp(score[o], i);
     }
-    __device__ uint64_t get(uint32_t Q, uint32_t e) const {
-        const uint32_t l = e / k_in, j = e % k_in;
-        const size_t o = (size_t)l * list_stride + (size_t)Q * k_in + j;
-        const uint32_t i = idx[o];
-        return i == 0xFFFFFFFFu ? 0ull : make_comp(score[o], i);
+    __device__ uint64_t get(uint32_t Q, uint32_t e) const { return at(Q, e / k_in, e % k_in); }
+    __device__ void finish(uint32_t) const {
+        if (!step) return;
+        if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {  // every CTA has read *step at its start
+            *done = 0u;
+            *reinterpret_cast<volatile uint32_t*>(step) = *reinterpret_cast<volatile uint32_t*>(step) + 1u;
+        }
     }
-    __device__ void finish(uint32_t) const {}
 };
 
 // Calls with few query rows (a long context scored by a handful of heads) leave every row tens of
@@ -654,7 +701,15 @@ __global__ void __launch_bounds__(512) topk_merge_kernel(Lists L, uint32_t k, ui
                                                          uint32_t* out_index, float* out_score,
                                                          uint32_t* out_count) {
     extern __shared__ __align__(16) unsigned char smem[];
-    topk_merge_body(L, k, kp2, cap_s, out_index, out_score, out_count, smem);
+    if (L.wait_ready(reinterpret_cast<int*>(smem))) {
+        topk_merge_body(L, k, kp2, cap_s, out_index, out_score, out_count, smem);
+    } else {
+        for (uint32_t r = threadIdx.x; r < k; r += blockDim.x) {  // a list's owner did not answer: an empty row
+            out_index[(size_t)blockIdx.x * k + r] = 0xFFFFFFFFu;
+            out_score[(size_t)blockIdx.x * k + r] = -INFINITY;
+        }
+        if (out_count && threadIdx.x == 0) out_count[blockIdx.x] = 0;
+    }
     __syncthreads();
     MPROBE(9);
     L.finish(blockIdx.x);

@@ -46,9 +46,19 @@ ms = sh.last_times()
 assert np.all(ms >= 0) and ms[0] > 0
 full = [(0, n, 0, 4, 0), (0, n, 4, 4, 0)]
 check_topk(tiles, full, qc, qs, k, gi, gs, np.full(nq, k))
+# the repeated step without timing: captured into a graph per buffer parity and replayed; every step must give the same
+sh.set_timing(False)
+gi2, gs2 = np.zeros_like(gi), np.zeros_like(gs)
+dq, ds = S.to_device(qc), S.to_device(qs)
+for _ in range(7):
+    gi2[:] = 0
+    sh.score_topk(dt, segs, dq, ds, nq, k, out_index=gi2, out_score=gs2)
+    assert np.array_equal(gi2, gi) and np.array_equal(gs2, gs)
+st = sh.status()
+assert st["exchange"] in ("peer-memory loads", "nccl all-gather") and not st["wait_ran_out"] and st["steps"] == 10, st
 np.save(os.path.join(tmp, "out%d.npy" % rank), np.stack([gi.astype(np.float64), gs.astype(np.float64)]))
 sh.destroy()
-print("rank", rank, "ok", ms)
+print("rank", rank, "ok", ms, st)
 """
 
 
