@@ -537,6 +537,17 @@ int32_t slha_b200_pool_append_keys(SlhaB200Pool* pool, const SlhaModel* model, c
     });
 }
 
+// What a pool's record of appended codecs says to the scorers: -1 unknown (look at the first tile), -2 only codecs the
+// tensor-core kernels do not decode, else bit 0 = NF4 tiles expected, bit 1 = mixed 8/4 only, bit 2 = TQ3 only.
+static int pool_codec_hint(const Pool* pl) {
+    const uint32_t cm = pl->codec_mask;
+    if ((cm & 0x80000000u) || !cm) return -1;
+    const bool mixed_only = cm == (1u << SLHA_CODEC_MIXED), tq3_only = cm == (1u << SLHA_CODEC_TQ3);
+    const uint32_t nibble = (1u << SLHA_CODEC_INT4_SINGLE) | (1u << SLHA_CODEC_INT4_GROUPED) | (1u << SLHA_CODEC_NF4) | (1u << 6);
+    if (!(cm & nibble) && !mixed_only && !tq3_only) return -2;
+    return (int)(((cm >> SLHA_CODEC_NF4) & 1u) | (mixed_only ? 2u : 0u) | (tq3_only ? 4u : 0u));
+}
+
 int32_t slha_b200_pool_score_all(SlhaB200Pool* pool, const float* q_coarse, const uint64_t* q_sign,
                                  uint32_t* slots_out, float* scores_out, uint64_t* n_out) {
     return ffi([&]() -> Status {
@@ -564,7 +575,7 @@ int32_t slha_b200_pool_score_all(SlhaB200Pool* pool, const float* q_coarse, cons
         SLHA_TRY(stage_out(c, slots_out, len * 4, &outs[0]));
         SLHA_TRY(stage_out(c, scores_out, len * 4, &outs[1]));
         SLHA_TRY(launch_score_full(c, reinterpret_cast<const SciRustSlhaTile*>(pl->dev.tiles), pl->dev.state, len, dq,
-                                   ds, 1, all));
+                                   ds, 1, all, pool_codec_hint(pl)));
         SLHA_TRY(pool_compact_live(c, pl, all, (uint32_t*)outs[0].dev, (float*)outs[1].dev, dn));
         unsigned long long hn = 0;
         SLHA_CUDA(cudaMemcpyAsync(&hn, dn, 8, cudaMemcpyDeviceToHost, c->stream));
@@ -645,7 +656,7 @@ int32_t slha_b200_pool_observe_query(SlhaB200Pool* pool, const float* q_coarse, 
         float* all;
         SLHA_TRY(ctx_device_scratch(c, len * 4, (void**)&all));
         SLHA_TRY(launch_score_full(c, reinterpret_cast<const SciRustSlhaTile*>(pl->dev.tiles), pl->dev.state, len, dq,
-                                   ds, 1, all));
+                                   ds, 1, all, pool_codec_hint(pl)));
         SLHA_TRY(pool_observe(c, pl, nullptr, all, len, temperature));
         if (sync_by_default(c)) SLHA_CUDA(cudaStreamSynchronize(c->stream));
         return Status();

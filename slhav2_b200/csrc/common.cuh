@@ -100,7 +100,7 @@ Status launch_score_segments(Ctx* c, const SciRustSlhaTile* tiles, const SlhaB20
                              const uint64_t* d_q_sign, size_t nq, float* d_scores, const unsigned long long* d_row_offsets,
                              uint32_t row_len, float fill);
 Status launch_score_full(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* state, size_t n,
-                         const float* q_coarse, const uint64_t* q_sign, size_t nq, float* scores);
+                         const float* q_coarse, const uint64_t* q_sign, size_t nq, float* scores, int codec_hint = -1);
 // d_status must hold ~0ull on entry; receives min over bad tiles of (index << 8 | code) with
 // code 5 = non-finite metadata, 6 = invalid tile
 Status launch_validate_tiles(Ctx* c, const SciRustSlhaTile* tiles, size_t n, unsigned long long* d_status);

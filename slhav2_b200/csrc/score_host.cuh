@@ -546,8 +546,95 @@ Status launch_validate_tiles(Ctx* c, const SciRustSlhaTile* tiles, size_t n, uns
 }
 
 Status launch_score_full(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* state, size_t n,
-                         const float* q_coarse, const uint64_t* q_sign, size_t nq, float* scores) {
+                         const float* q_coarse, const uint64_t* q_sign, size_t nq, float* scores, int codec_hint) {
     if (n == 0 || nq == 0) return Status();
+    // Long arenas: the streaming tensor-core kernel in its dense mode (all query groups of four in one launch, every CTA an
+    // equal share of the tiles), then the generic kernel for the rows of work items it handed back (a codec it does not
+    // decode, a query outside the fp16 split).  codec_hint as for score_topk_device: -1 = look at the first tile, -2 = generic.
+    if (n >= 32768 && n < 0xFFFFFFFFull && codec_hint != -2 && !g_force_generic) {
+        bool nf4 = codec_hint < 0 || (codec_hint & 1), mixed = codec_hint > 0 && (codec_hint & 2), tq3 = codec_hint > 0 && (codec_hint & 4), other = false;
+        if (codec_hint < 0) {
+            uint16_t flags = 0;
+            SLHA_CUDA(cudaMemcpyAsync(&flags, reinterpret_cast<const unsigned char*>(tiles) + 118, 2, cudaMemcpyDeviceToHost, c->stream));
+            SLHA_CUDA(cudaStreamSynchronize(c->stream));
+            nf4 = (flags & F_NF4) != 0;
+            mixed = (flags & F_MIXED) != 0;
+            tq3 = (flags & F_TQ3) != 0;
+            other = (flags & F_MIX3) != 0;
+        }
+        const int kind = tq3 ? 2 : (mixed ? 1 : (nf4 ? 0 : 3));
+        const int mw = STREAM_THREADS / 32;
+        const size_t smem = mma_smem_bytes(mw, kind == 0);
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
+        if (!other && smem <= MAX_SMEM) {
+            const uint32_t groups = (uint32_t)((nq + 3) / 4);
+            const uint64_t total = (uint64_t)n * groups;
+            uint64_t share = (total + sms - 1) / sms;
+            share = std::max<uint64_t>(2048, (share + MMA_SET_TILES - 1) / MMA_SET_TILES * MMA_SET_TILES);
+            std::vector<WorkItem> items;
+            std::vector<uint32_t> cta(1, 0);
+            uint64_t filled = 0;
+            for (uint32_t grp = 0; grp < groups; ++grp)
+                for (uint64_t pos = 0; pos < n;) {
+                    const uint32_t take = (uint32_t)std::min<uint64_t>(n - pos, share - filled);
+                    WorkItem w{};
+                    w.tile_begin = pos;
+                    w.n_tiles = take;
+                    w.index_base = (uint32_t)pos;
+                    w.query_begin = 4 * grp;
+                    w.n_queries = (uint32_t)std::min<size_t>(4, nq - 4 * (size_t)grp);
+                    w.pad = w.n_queries;
+                    items.push_back(w);
+                    pos += take;
+                    filled += take;
+                    if (filled >= share) {
+                        filled = 0;
+                        cta.push_back((uint32_t)items.size());
+                    }
+                }
+            if (cta.back() != (uint32_t)items.size()) cta.push_back((uint32_t)items.size());
+            WorkItem* d_items;
+            uint32_t *d_cta, *d_gflag;
+            SLHA_TRY(ctx_device_scratch(c, items.size() * sizeof(WorkItem), (void**)&d_items));
+            SLHA_TRY(ctx_device_scratch(c, cta.size() * 4, (void**)&d_cta));
+            SLHA_TRY(ctx_device_scratch(c, nq * 4, (void**)&d_gflag));
+            SLHA_CUDA(cudaMemcpyAsync(d_items, items.data(), items.size() * sizeof(WorkItem), cudaMemcpyHostToDevice, c->stream));
+            SLHA_CUDA(cudaMemcpyAsync(d_cta, cta.data(), cta.size() * 4, cudaMemcpyHostToDevice, c->stream));
+            SLHA_CUDA(cudaMemsetAsync(d_gflag, 0, nq * 4, c->stream));
+            SLHA_CUDA(cudaStreamSynchronize(c->stream));  // (the host vectors go away)
+            static thread_local bool configured[16] = {false};
+            if (!configured[c->device & 15]) {
+#define SLHA_DENSE_SMEM(K) SLHA_CUDA(cudaFuncSetAttribute(score_stream_kernel<K, STREAM_THREADS, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_SMEM))
+                SLHA_DENSE_SMEM(0); SLHA_DENSE_SMEM(1); SLHA_DENSE_SMEM(2); SLHA_DENSE_SMEM(3);
+#undef SLHA_DENSE_SMEM
+                configured[c->device & 15] = true;
+            }
+            ScoreArgs a{};
+            a.tiles = reinterpret_cast<const unsigned char*>(tiles);
+            a.state = state;
+            a.items = d_items;
+            a.stream_items = d_items;
+            a.n_items = (uint32_t)items.size();
+            a.cta_begin = d_cta;
+            a.q_coarse = q_coarse;
+            a.q_sign = reinterpret_cast<const uint32_t*>(q_sign);
+            a.scores = scores;
+            a.score_stride = n;
+            a.gflag = d_gflag;
+            a.nf4_table = kind == 0 ? 1u : 0u;
+            a.mixed = kind == 1 ? 1u : 0u;
+            const uint32_t grid = (uint32_t)cta.size() - 1;
+#define SLHA_LAUNCH_DENSE(K) score_stream_kernel<K, STREAM_THREADS, false, true><<<grid, STREAM_THREADS, smem, c->stream>>>(a)
+            if (kind == 3) SLHA_LAUNCH_DENSE(3); else if (kind == 2) SLHA_LAUNCH_DENSE(2); else if (kind == 1) SLHA_LAUNCH_DENSE(1); else SLHA_LAUNCH_DENSE(0);
+#undef SLHA_LAUNCH_DENSE
+            count_launch();
+            SLHA_CUDA(cudaGetLastError());
+            // the generic kernel over the same work items, only those whose rows were handed back
+            const int threads = 128, nwarps = threads / 32;
+            return launch_score<false>(c, 4, a, (uint32_t)items.size(), threads, score_smem_bytes(4, nwarps, false, 0));
+        }
+    }
     const int threads = 128, nwarps = threads / 32;
     const uint32_t item_tiles = 4096;
     const uint32_t chunks = (uint32_t)((n + item_tiles - 1) / item_tiles);

@@ -669,8 +669,10 @@ __device__ __forceinline__ void stream_refresh_threshold(const ScoreArgs& a, uin
 // Separate instantiations.  A tile of another codec than the launch was arranged for flags the
 // work item's query rows, which the generic kernel then scores.
 // IL: the work items are interleaved shares of whole streams (see the planner); the plain instantiation keeps the
-// set arithmetic of contiguous ranges out of its loop.
-template <int KIND, int NT, bool IL>
+// set arithmetic of contiguous ranges out of its loop.  DENSE: every score is written to a.scores (row q at
+// q * a.score_stride, tile i of the item at index_base + i; -inf for COLD slots) and nothing is filtered or appended:
+// full score vectors (slha_score_tiles, score_all, the softmax of observe_scores) at the streaming kernel's speed.
+template <int KIND, int NT, bool IL, bool DENSE = false>
 __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -775,7 +777,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
 #pragma unroll
         for (int i = 0; i < MMA_DEPTH - 1; ++i) issue();
         bool row_warm = true;
-        if (tid < 4) {
+        if (!DENSE && tid < 4) {
             // start from the threshold other CTAs have already proven for the row, and from the
             // row's bucket mapping if one has been published
             const bool have = tid < nq;
@@ -851,7 +853,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         // of every CTA that works on the row -- and the rows do not already have thresholds (a CTA that starts its
         // second item on rows other CTAs have been scoring for a while).
         const bool all_warm = __syncthreads_and(row_warm) != 0;
-        const bool first_round_barrier = !all_warm && (uint64_t)a.k <= 16ull * (uint64_t)nwarps * (uint64_t)max((it.pad >> 8) & 0x7FFFFFu, 1u);
+        const bool first_round_barrier = !DENSE && !all_warm && (uint64_t)a.k <= 16ull * (uint64_t)nwarps * (uint64_t)max((it.pad >> 8) & 0x7FFFFFu, 1u);
         PROBE_SET(1);
         const bool too_big = bail[0] != 0;
         if (too_big) n_sets = 0;  // (the sets already on their way are waited for at the item's end and never read)
@@ -934,7 +936,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
             // (257 and the relative slack cover the rounding of the bound itself.)  Only the INT4 launches
             // test for it: with a few CTAs per row and k / n of a few percent (the NF4 decode caches) nearly
             // every set holds a candidate and the test costs more than it saves.
-            const bool need = KIND != 3 || round == 0 ||
+            const bool need = DENSE || KIND != 3 || round == 0 ||
                               __any_sync(0xFFFFFFFFu, (mine && score_key(fmaf(lam0, 257.0f, c0 + fabsf(c0) * 1e-6f)) >= pv) ||
                                                           (mine && score_key(fmaf(lam1, 257.0f, c1 + fabsf(c1) * 1e-6f)) >= pv));
             if (need) {
@@ -955,6 +957,15 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
             if (sbase) {
                 live0 = live0 && sbase[t0] != ST_COLD;
                 live1 = live1 && sbase[t1] != ST_COLD;
+            }
+            if (DENSE) {
+                if (mine) {  // (eight lanes of a query hold eight consecutive tiles: 32-byte runs per row)
+                    float* row = a.scores + (size_t)Qt * a.score_stride + it.index_base;
+                    if (t0 < n) row[t0] = live0 ? sc0 : -INFINITY;
+                    if (t1 < n) row[t1] = live1 ? sc1 : -INFINITY;
+                }
+                __syncwarp();
+                continue;
             }
             if (round == 0) {
                 // First set of the warp: a row without a bucket mapping gets one from the 16 scores
@@ -1040,7 +1051,7 @@ __global__ void __launch_bounds__(NT, 1) score_stream_kernel(ScoreArgs a) {
         cp_async_wait<0>();
         PROBE_MAX(4);
         PROBE_MIN(6);
-        if (mine) {  // the unused rest of the warp's last chunk holds absent keys
+        if (!DENSE && mine) {  // the unused rest of the warp's last chunk holds absent keys
             for (uint32_t z = cur + (uint32_t)g; z < end; z += 8u) dst[z] = 0ull;
         }
         __syncthreads();

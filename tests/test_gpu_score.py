@@ -168,3 +168,17 @@ def test_score_segments_with_many_query_rows_uses_the_tensor_cores_and_agrees_wi
                 _close(row[base:base + n], ora.score_tiles(tiles[tb:tb + n], qc[j], qs[j]))
             assert np.all(row[base + n:] == -2.0)
             assert np.all(row[:base] == 0.0)  # (before the segment's index base: no row covers it, a host destination comes back zero there)
+
+
+@pytest.mark.parametrize("codec,nq,foreign", [(0, 1, None), (1, 4, None), (2, 5, None), (3, 3, None), (4, 2, None), (6, 9, None), (5, 2, None),
+                                              (1, 4, 2), (2, 3, 4), (3, 4, 0)])
+def test_score_tiles_of_a_long_arena_runs_on_the_streaming_kernel(codec, nq, foreign):
+    # 32768 tiles or more: full score vectors come from the tensor-core kernel's dense mode (MIX3 and tiles of another
+    # codec than the first tile's through the generic kernel); same bar as the short arenas above
+    n = 70000 + 13 * codec
+    tiles = H.random_tiles(n, codec, seed=500 + codec, warm_every=7, nocorr_every=5)
+    if foreign is not None:
+        tiles[30000:30500] = H.random_tiles(500, foreign, seed=501)
+    qc, qs = H.random_queries(nq, 502 + codec)
+    got = S.score_tiles(tiles, n, qc, qs, nq)
+    _close(got, H.oracle_scores(tiles, qc, qs))
