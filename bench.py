@@ -721,7 +721,12 @@ def run_next_rows(S, torch, dev):
         ms = timed(lambda: S.score_segments(tiles, segs, qc, qs, rows, dst, offs, tokens), n=10)
         out["score_segments"][name] = {"ms": ms, "scores_per_s": rows * tokens / (ms * 1e-3), "written_gb_per_s": rows * tokens * 4 / (ms * 1e-3) / 1e9,
                                        "launches_per_call": (S.launch_count() - l0) / 13}
-    del dst, keys
+    # full score vectors (slha_score_tiles over a device arena): the int4 tiles of above, four queries, one float per tile and query
+    full = torch.empty(4, heads * tokens, dtype=torch.float32, device=dev)
+    ms = timed(lambda: S.score_tiles(tiles, heads * tokens, qc[:4], qs[:4], 4, out=full))
+    out["score_tiles"] = {"workload": "262144 int4-grouped tiles x 4 queries, full float32 score vectors", "ms": ms,
+                          "tiles_per_s": heads * tokens / (ms * 1e-3), "tile_gb_per_s": heads * tokens * 128 / (ms * 1e-3) / 1e9}
+    del dst, keys, full
     tiles.free()
 
     # evictions journalled in the reference's event-log format: 262144 HOT tiles, budget for 65536, causal policy
