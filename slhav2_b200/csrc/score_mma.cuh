@@ -148,13 +148,15 @@ __device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t x, uint32_t y, ui
 }
 // TQ3 rows of a staged 16-tile set, rewritten in place as nibble rows: nibble d of the 64 latent
 // bytes becomes 2 code_d + correction_d (codes: 3 bits at bit 3d of bytes 0..47; correction bits:
-// bit d of bytes 48..63, zero once the correction plane has been dropped).  A lane rewrites half a
+// bit d of bytes 48..63, taken as zero for a tile flagged as without its correction plane).  A lane rewrites half a
 // row (64 dims: 24 code bytes and 8 correction bytes in, 32 bytes out); every lane reads before
 // any lane writes.
 __device__ __forceinline__ void tq3_to_nibbles(uint32_t set_s, int lane) {
     const uint32_t h = (uint32_t)lane & 1u, row = set_s + (uint32_t)(lane >> 1) * MMA_ROW;
     const uint2 c0 = lds_v2<0>(row + 24u * h), c1 = lds_v2<8>(row + 24u * h), c2 = lds_v2<16>(row + 24u * h);
-    const uint2 cr = lds_v2<48>(row + 8u * h);
+    uint2 cr = lds_v2<48>(row + 8u * h);
+    // a tile flagged as without its correction plane is decoded from the codes alone, whatever the plane's bytes hold
+    if (lds_u16<118>(row) & F_NOCORR) cr.x = cr.y = 0u;
     __syncwarp();
     const uint32_t w[7] = {c0.x, c0.y, c1.x, c1.y, c2.x, c2.y, 0u};
     uint32_t o[8];

@@ -327,7 +327,7 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) score_wide_kernel(ScoreArgs a
                 uint32_t nib[4];
                 if (KINDW == 1) {
                     const uint32_t w0 = lds_u32(row_s + 12u * c), w1 = lds_u32(row_s + 12u * c + 4u), w2 = lds_u32(row_s + 12u * c + 8u);
-                    const uint32_t cr = lds_u32(row_s + 48u + 4u * c);
+                    const uint32_t cr = (flags & F_NOCORR) ? 0u : lds_u32(row_s + 48u + 4u * c);  // (the plane's bytes are ignored once flagged as dropped)
                     const uint32_t w[4] = {w0, w1, w2, 0u};
 #pragma unroll
                     for (int m = 0; m < 4; ++m) {

@@ -93,7 +93,8 @@ def random_tiles(n, codec, seed, d=128, warm_every=0, nocorr_every=0, model=None
     if nocorr_every and codec in (4, 5):
         idx = np.arange(n) % nocorr_every == 1
         nb = 16 if codec == 4 else 14
-        tiles["latent_kv"][idx, 64 - nb:] = 0
+        # every second of them keeps the plane's bytes: a decoder must go by the flag (tests.rs:356-384 builds such tiles)
+        tiles["latent_kv"][idx & (np.arange(n) % (2 * nocorr_every) == 1), 64 - nb:] = 0
         tiles["flags"][idx] |= ora.FLAG_TQ3_NOCORR
     return tiles
 
