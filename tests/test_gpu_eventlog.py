@@ -111,3 +111,86 @@ def test_durable_eviction_refuses_cold_when_the_log_cannot_be_written(tmp_path):
     # best effort: the eviction proceeds and only the error is counted
     pool.attach_event_log(path, mode=4, require_durable=False)
     assert pool.evict(2) is True and pool.event_log_stats()["log_errors"] >= 2
+
+
+# ---- the reference's own persistence tests (scirust/tests/ccos.rs:609-785), same seeds and budgets ----------------
+def _scenario_tiles(proj_seed, gen_seed, n, rho):
+    z = H.scenario_projection(proj_seed)
+    _, toks = H.scenario_generate(gen_seed, n, rho)
+    return [H.scenario_tile(z, t, i) for i, t in enumerate(toks)]
+
+
+def test_durable_eviction_persists_before_recycling(tmp_path):
+    # ccos.rs:609-639
+    path = tmp_path / "durable_success"
+    pool = S.TilePool(4, 2 ** 62)
+    pool.attach_event_log(path, require_durable=True)
+    slot = int(pool.insert(_scenario_tiles(0xD001, 0xD001, 1, 0.3)[0])[0])
+    assert pool.evict(slot) and pool.read(slot, 1)[1][0] == ora.COLD
+    assert pool.event_log_stats() == {"records": 1, "log_errors": 0, "blocked_evictions": 0}
+    pool.destroy()
+    assert len(ora.eventlog_parse(open(path, "rb").read())[1]) == 1
+
+
+def test_durable_eviction_failure_keeps_tile_live(tmp_path):
+    # ccos.rs:641-686: budget zero stays unmet, the tile stays live, its slot is not recycled, the log stays empty
+    path = tmp_path / "durable_failure"
+    first = S.TilePool(1, 0)
+    first.attach_event_log(path)  # creates an empty log
+    first.destroy()
+    pool = S.TilePool(4, 0)
+    pool.attach_event_log(path, mode=4, require_durable=True)
+    tile = _scenario_tiles(0xD002, 0xD002, 1, 0.3)[0]
+    slot = int(pool.insert(tile)[0])
+    assert pool.enforce_budget() is False
+    assert pool.read(slot, 1)[1][0] != ora.COLD and pool.live_bytes() > 0
+    st = pool.event_log_stats()
+    assert st["log_errors"] == 1 and st["blocked_evictions"] == 1
+    tile["position"] = 1
+    assert int(pool.insert(tile)[0]) != slot
+    pool.destroy()
+    assert len(ora.eventlog_parse(open(path, "rb").read())[1]) == 0
+
+
+def test_evict_snapshots_to_event_log_then_rehydrates_identically(tmp_path):
+    # ccos.rs:688-747
+    path = tmp_path / "roundtrip"
+    pool = S.TilePool(16, 2 * 128)
+    pool.attach_event_log(path)
+    tiles = _scenario_tiles(0xE7, 9, 5, 0.4)
+    for t in tiles:
+        pool.insert(t)
+    pool.enforce_budget()
+    cold = pool.counts()[2]
+    assert cold >= 3 and pool.event_log_stats()["log_errors"] == 0
+    _, recs = ora.eventlog_parse(open(path, "rb").read())
+    assert len(recs) == cold
+    for seq, _slot, tile in recs:
+        assert tile["latent_kv"].tobytes() == tiles[seq]["latent_kv"].tobytes()
+        assert int(tile["flags"][0]) & ora.FLAG_WARM  # paged WARM before it was evicted
+    logged0 = next(r for r in recs if r[0] == 0)[2]
+    slot = pool.rehydrate(0)
+    assert slot is not None
+    t, state, _, _ = pool.read(slot, 1)
+    assert state[0] == ora.WARM and t.tobytes() == np.ascontiguousarray(logged0).tobytes()
+
+
+def test_eviction_order_is_reflected_in_the_log(tmp_path):
+    # ccos.rs:749-767: causal eviction, one enforce per insert -> records of seq 0, 1, 2
+    path = tmp_path / "order"
+    pool = S.TilePool(8, 128)
+    pool.attach_event_log(path)
+    for t in _scenario_tiles(0xA5, 3, 4, 0.3):
+        pool.insert(t)
+        pool.enforce_budget()
+    assert [r[0] for r in ora.eventlog_parse(open(path, "rb").read())[1]] == [0, 1, 2]
+
+
+def test_no_event_log_leaves_behavior_and_rehydrate_inert():
+    # ccos.rs:769-785
+    pool = S.TilePool(8, 128)
+    for t in _scenario_tiles(0x11, 2, 3, 0.3):
+        pool.insert(t)
+    pool.enforce_budget()
+    assert pool.event_log_stats()["log_errors"] == 0
+    assert pool.rehydrate(0) is None
