@@ -344,3 +344,21 @@ def test_random_call_shapes_match_the_oracle(trial):
     for _ in range(2):
         gi, gs_, gc = S.score_topk(dt, S.make_segments(segs), qc, qs, sum(nqs), k)
         check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+
+
+@pytest.mark.parametrize("codec,n,nq,k", [(6, 300000, 4, 1024), (2, 120000, 4, 512), (4, 16384, 64, 256), (5, 50000, 3, 100)])
+def test_repeated_calls_are_bitwise_identical(codec, n, nq, k):
+    # slhav2-vram/tests/cuda.rs:327 (deterministic scoring) and :405 (a thousand launches) for the fused call: the order in
+    # which warps append candidates varies from launch to launch, the winners, their order and their scores must not
+    tiles = H.random_tiles(n, codec, seed=90 + codec, warm_every=9, nocorr_every=4)
+    dt = S.to_device(np.concatenate([tiles, tiles]))
+    segs = S.make_segments([(0, n, 0, nq, 0), (n, n, nq, nq, 7)])
+    qc, qs = H.random_queries(2 * nq, 91)
+    first = S.score_topk(dt, segs, qc, qs, 2 * nq, k)
+    for _ in range(6):
+        again = S.score_topk(dt, segs, qc, qs, 2 * nq, k)
+        for a, b in zip(first, again):
+            assert a.tobytes() == b.tobytes()
+    m = min(nq, 4)
+    full = S.score_tiles(dt, 2 * n, qc[:m], qs[:m], m)
+    assert S.score_tiles(dt, 2 * n, qc[:m], qs[:m], m).tobytes() == full.tobytes()
