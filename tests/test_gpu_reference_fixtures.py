@@ -67,3 +67,74 @@ def test_fixture_against_sixteen_or_more_query_rows(name):
         _within_reference_bound(score[j], want[j][idx[j]])
         kth = np.sort(want[j])[::-1][7]
         assert np.all(want[j][idx[j]] >= kth - 2e-3 * (1.0 + abs(kth)))
+
+
+def _degenerate_arena(codec, n):
+    """Valid tiles at the edges of the format: scirust/tests/properties.rs:259-273 (zero latent, zero scale, lambda 1e6,
+    group scales 1) and scales / lambdas far from the usual range."""
+    tiles = H.random_tiles(n, codec, seed=700 + codec, warm_every=11, nocorr_every=3)
+    z = slice(0, 100)
+    tiles["latent_kv"][z] = 0
+    tiles["scale"][z] = 0.0
+    tiles["dynamic_lambda"][z] = 1.0e6
+    tiles["group_scales"][z] = 1
+    tiles["scale"][100:200] = 1e-30
+    tiles["scale"][200:300] *= F(1e20)
+    tiles["dynamic_lambda"][300:400] = 0.0
+    tiles["dynamic_lambda"][400:500] = -3.0
+    tiles["group_scales"][500:600] = 0
+    tiles["residual_bitmap"][600:700] = np.uint64(0xFFFFFFFFFFFFFFFF)
+    return tiles
+
+
+def _degenerate_queries(nq):
+    qc, qs = H.random_queries(nq, 77)
+    qc[0], qs[0] = 1.0e3, np.uint64(0xFFFFFFFFFFFFFFFF)  # properties.rs:267-268
+    if nq > 2:
+        qc[2] *= F(1e5)    # beyond the fp16 split of the tensor-core kernels
+    if nq > 3:
+        qc[3] *= F(1e-12)
+    if nq > 4:
+        qc[4], qs[4] = 0.0, 0
+    return qc, qs
+
+
+def _term_magnitudes(tiles, qc):
+    """sum_d |dequant_d q_d| + 256 |lambda| per (query, tile): the scale of the rounding error of any summation order."""
+    d = np.abs(np.stack([ora.dequant(tiles[i:i + 1]) for i in range(len(tiles))]).astype(np.float64))
+    lam = np.where(tiles["flags"] & ora.FLAG_WARM, 0.0, np.abs(tiles["dynamic_lambda"].astype(np.float64)))
+    return np.abs(qc.astype(np.float64)) @ d.T + 256.0 * lam[None, :]
+
+
+def _within_summation_bound(got, want, mags):
+    # the reference's bound 1e-3 (1 + |s|) presumes terms of the size of the sum; where they cancel (a constant query of
+    # 1e3 against signed levels: the reference's own vector paths leave the bound there too) 32 ulp of the terms' total
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert np.all(err <= 1e-3 * (1.0 + np.abs(want)) + 4e-6 * mags), float((err / (1e-3 * (1.0 + np.abs(want)) + 4e-6 * mags)).max())
+
+
+@pytest.mark.parametrize("codec", [0, 6, 2, 3, 4, 5])
+@pytest.mark.parametrize("n,nq", [(3000, 5), (40000, 5), (40000, 20)])
+def test_degenerate_tiles_and_queries_stay_finite_and_agree(codec, n, nq):
+    tiles = _degenerate_arena(codec, n)
+    qc, qs = _degenerate_queries(nq)
+    want = H.oracle_scores(tiles, qc, qs)
+    mags = _term_magnitudes(tiles, qc)
+    assert np.isfinite(want).all()
+    dt = S.to_device(tiles)
+    if nq <= 5:
+        got = S.score_tiles(dt, n, qc, qs, nq)
+    else:
+        got = np.zeros((nq, n), F)
+        S.score_segments(dt, S.make_segments([(0, n, 0, nq, 0)]), qc, qs, nq, got, (np.arange(nq) * n).astype(np.uint64), n)
+    assert np.isfinite(got).all()
+    _within_summation_bound(got, want, mags)
+    k = 300
+    idx, score, cnt = S.score_topk(dt, S.make_segments([(0, n, 0, nq, 0)]), qc, qs, nq, k)
+    for j in range(nq):
+        assert cnt[j] == k
+        _within_summation_bound(score[j], want[j][idx[j]], mags[j][idx[j]])
+        assert len(set(idx[j].tolist())) == k
+        slack = 2e-3 * (1.0 + np.abs(want[j])) + 8e-6 * mags[j]
+        kth = np.sort(want[j])[::-1][k - 1]
+        assert np.all(want[j][idx[j]] + slack[idx[j]] >= kth - slack.max())  # nothing clearly below the k-th was chosen
