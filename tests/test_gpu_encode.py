@@ -96,3 +96,50 @@ def test_encode_then_score_end_to_end_config1_shape():
     want = ora.score_tiles(tiles, qc[0], qs[0])
     oi, ov = ora.topk(want, 64)
     assert set(gi[0]) == set(oi) or np.all(np.abs(np.sort(gsc[0])[::-1] - ov) <= 1e-3)
+
+
+def _edge_keys(d, seed):
+    """Keys that sit on the quantisers' decision points: with a coordinate projection the latent is the key itself, so
+    half-integer multiples of the step are exact rounding ties, the residual has exact zeros, and whole groups vanish."""
+    rng = np.random.default_rng(seed)
+    rows = []
+    half_steps = (rng.integers(-14, 15, size=(24, d)) * 0.5).astype(F)
+    half_steps[:, 0] = 7.0  # absmax 7 -> INT4 step exactly 1
+    rows.append(half_steps)
+    rows.append(half_steps * F(2.0 ** -20))
+    rows.append(half_steps * F(2.0 ** 40))
+    rows.append((half_steps * F(1e15)).astype(F))              # (squares stay finite: no overflow in the residual's rms)
+    rows.append((half_steps * F(1e-38)).astype(F))           # denormal range
+    spike = np.zeros((8, d), F)
+    spike[np.arange(8), rng.integers(0, d, 8)] = rng.choice([-1.0, 1.0, 3e18, -1e-45], 8).astype(F)
+    rows.append(spike)
+    const = np.repeat(rng.choice([1.0, -1.0, 0.3, -2.5e-7], 8).astype(F)[:, None], d, axis=1)
+    rows.append(const)
+    zeros = np.zeros((2, d), F)
+    zeros[1] = -0.0
+    rows.append(zeros)
+    one_group = np.zeros((8, d), F)
+    one_group[:, 16:32] = rng.standard_normal((8, 16)).astype(F)   # all other groups empty
+    rows.append(one_group)
+    tq3_grid = ((rng.integers(0, 8, size=(16, d)) - 3.5) * 2.0).astype(F)  # exactly the TQ3 levels at half range 7
+    rows.append(tq3_grid)
+    return np.ascontiguousarray(np.concatenate(rows), F)
+
+
+@pytest.mark.parametrize("codec", range(7))
+@pytest.mark.parametrize("d,rht,coord", [(128, False, True), (256, False, True), (128, True, True), (200, True, False), (128, False, False)])
+def test_encode_bit_exact_on_rounding_ties_zeros_and_extreme_magnitudes(codec, d, rht, coord):
+    if coord:
+        p = np.zeros((128, d), F)
+        p[np.arange(128), np.arange(128)] = 1.0  # latent dimension i = key coordinate i
+    else:
+        p = H.orthogonal_projection(31, d)
+    om, gm = ora.Model(p, d, seed=3, rht=rht), S.Model.from_projection(p, d, 3, rht=rht)
+    keys = _edge_keys(d, 40 + codec)
+    want = om.encode_batch(keys, codec)
+    got = gm.encode_keys(keys, codec)
+    assert got.tobytes() == want.tobytes(), _diff(got, want)
+    qc, qs = gm.prepare_queries(keys)
+    for j in range(0, len(keys), 5):
+        wc, ws = om.prepare_query(keys[j])
+        assert np.array_equal(qs[j], ws) and np.array_equal(qc[j].view(np.uint32), wc.view(np.uint32))
