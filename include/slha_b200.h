@@ -281,7 +281,13 @@ typedef struct {
  * that the GPU can address (cudaHostAlloc, mapped cudaHostRegister) are written
  * in place by the kernel that produces them, other host outputs through a
  * staging copy; the same holds for the other top-k entry points below.  Full
- * score vectors are never written to memory.
+ * score vectors are never written to memory.  Tiles in device memory are not
+ * validated (slha_score_tiles validates, slha-c/src/lib.rs:244-286): every
+ * kernel decodes a tile by the precedence of SciRustSlhaTile::dequant_at
+ * (scirust/src/attention/slha_v2/tile.rs:141-151: mixed, TQ3, MIX3, NF4, INT4;
+ * SLHA_FLAG_TQ3_NOCORR makes a TQ3 / MIX3 decode ignore the correction plane's
+ * bytes and means nothing elsewhere), so a tile the validator would refuse still
+ * scores as the reference's compute_score scores it.
  */
 int32_t slha_b200_score_topk(const SciRustSlhaTile* tiles, const SlhaB200Segment* segments,
                              size_t n_segments, const float* q_coarse, const uint64_t* q_sign,

@@ -93,7 +93,9 @@ template <int G>
 __device__ __forceinline__ void tile_partial(const unsigned char* st, int t, int s, int lane,
                                              const float (&qreg)[G][16], const uint32_t (&qs)[G],
                                              const float* qsm, const float* lut, float (&out)[G]) {
-    const uint32_t flags = lds32(st + stage_off(t, 116)) >> 16;
+    uint32_t flags = lds32(st + stage_off(t, 116)) >> 16;
+    // precedence of dequant_at (tile.rs:141-151) for tiles that carry several codec flags: mixed, then TQ3, then MIX3
+    if ((flags & F_TQ3) && !(flags & F_MIXED)) flags &= ~(uint32_t)F_MIX3;
     const float scale = __uint_as_float(lds32(st + stage_off(t, 96)));
     const float lam = (flags & F_WARM) ? 0.0f : __uint_as_float(lds32(st + stage_off(t, 100)));
     const float gsb = (float)((lds32(st + stage_off(t, 120 + (s & 4))) >> ((s & 3) * 8)) & 0xFFu);

@@ -97,3 +97,58 @@ def test_audit_reports_known_answers():
 
     rep = json.loads(S.audit())
     assert rep["tile_size"] == 128 and rep["int4_known_answers"] is True and rep["devices"] >= 1
+
+
+def test_weights_file_contract_of_the_reference(tmp_path):
+    # scirust/src/weights.rs tests :352-512 through slha_weights_load: every malformed file is refused with the reference's
+    # message, a version-1 file stays readable, and a loaded model encodes like the model it was saved from
+    lib = S.load_library()
+    d = 129  # the smallest valid dimension (weights.rs:318)
+    p = H.orthogonal_projection(8, d)
+
+    def load(blob, name="w.slhw"):
+        path = tmp_path / name
+        path.write_bytes(bytes(blob))
+        h = lib.slha_weights_load(str(path).encode())
+        return h, lib.slha_last_error_message()
+
+    v2 = bytearray(ora.weights_to_bytes(p, d, 0xC0FFEE, False))
+    v1 = bytearray(ora.weights_to_bytes(p, d, 0x1E6AC001, True, version=1))
+    assert int.from_bytes(v2[4:8], "little") == 2
+    for blob, seed, rht in ((v2, 0xC0FFEE, False), (v1, 0x1E6AC001, True)):
+        h, _ = load(blob)
+        assert h and lib.slha_model_dim(h) == d
+        key = H.gaussian_keys(4, 1, d)[0]
+        out = np.zeros(1, S.TILE_DTYPE)
+        assert lib.slha_encode_key(h, S.ptr(key), d, 3, S.CODEC_MIXED, S.ptr(out)) == S.OK
+        assert out.tobytes() == ora.Model(p, d, seed=seed, rht=rht).encode(key, 3, codec=3).tobytes()
+        assert lib.slha_weights_release(h) == S.OK
+    header = len(v2) - 4 * 128 * d
+    bad = bytearray(v2)
+    bad[header + 17] ^= 0x80                      # payload corruption (:386-400)
+    h, msg = load(bad)
+    assert not h and b"checksum mismatch" in msg
+    bad = bytearray(v2)
+    bad[12] ^= 0x01                               # one seed byte: the checksum covers the header (:402-418)
+    h, msg = load(bad)
+    assert not h and b"checksum mismatch" in msg
+    small = bytearray(24)
+    small[0:8] = v1[0:8]
+    small[8:12] = (128).to_bytes(4, "little")     # d <= D_C (:432-452)
+    h, msg = load(small)
+    assert not h and b"invalid dimension" in msg
+    small[8:12] = (0xFFFFFFFF).to_bytes(4, "little")
+    assert not load(small)[0]
+    bad = bytearray(v1)
+    bad[20] = 2                                   # (:454-474)
+    h, msg = load(bad)
+    assert not h and b"invalid RHT flag" in msg
+    bad = bytearray(v1)
+    bad[22] = 1
+    h, msg = load(bad)
+    assert not h and b"reserved" in msg
+    bad = bytearray(v1)
+    bad[24:28] = np.array([np.nan], F).tobytes()  # (:476-491)
+    h, msg = load(bad)
+    assert not h and b"non-finite projection value" in msg
+    assert not load(bytes([0, 1, 2]))[0] and not load(bytes(32))[0]  # (:508-512)

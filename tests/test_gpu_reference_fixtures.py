@@ -138,3 +138,31 @@ def test_degenerate_tiles_and_queries_stay_finite_and_agree(codec, n, nq):
         slack = 2e-3 * (1.0 + np.abs(want[j])) + 8e-6 * mags[j]
         kth = np.sort(want[j])[::-1][k - 1]
         assert np.all(want[j][idx[j]] + slack[idx[j]] >= kth - slack.max())  # nothing clearly below the k-th was chosen
+
+
+@pytest.mark.parametrize("n,nq", [(4096, 3), (40960, 4), (40960, 16)])
+def test_every_flag_combination_is_decoded_as_compute_score_decodes_it(n, nq):
+    # Tiles in device memory are not validated (slha_score_tiles validates, slha-c/src/lib.rs:244-286): whatever the six
+    # flag bits say, contradictory combinations included, every kernel must decode a tile by the precedence of the
+    # reference's dequant_at / compute_score (tile.rs:133-281), which the oracle restates.
+    tiles = H.random_tiles(n, 1, seed=800)
+    rng = np.random.default_rng(801)
+    tiles["latent_kv"] = rng.integers(0, 256, size=(n, 64), dtype=np.uint8)
+    tiles["flags"] = (np.arange(n) % 64).astype(np.uint16)
+    qc, qs = H.random_queries(nq, 802)
+    want = H.oracle_scores(tiles, qc, qs)
+    dt = S.to_device(tiles)
+    if nq < 16:
+        got = S.score_tiles(dt, n, qc, qs, nq)
+    else:
+        got = np.zeros((nq, n), F)
+        S.score_segments(dt, S.make_segments([(0, n, 0, nq, 0)]), qc, qs, nq, got, (np.arange(nq) * n).astype(np.uint64), n)
+    _within_summation_bound(got, want, _term_magnitudes(tiles, qc))
+    for first in (0, 2, 4, 8, 12):  # the first tile's codec selects the tensor-core instantiation: INT4, NF4, mixed, TQ3, mixed|TQ3
+        rolled = np.roll(tiles, -first)
+        idx, score, cnt = S.score_topk(S.to_device(rolled), S.make_segments([(0, n, 0, nq, 0)]), qc, qs, nq, 64)
+        w = np.roll(want, -first, axis=1)
+        for j in range(nq):
+            _within_reference_bound(score[j], w[j][idx[j]])
+            kth = np.sort(w[j])[::-1][63]
+            assert np.all(w[j][idx[j]] >= kth - 2e-3 * (1.0 + abs(kth)))
