@@ -276,7 +276,8 @@ typedef struct {
  * the lower index (the ordering convention of scirust/src/metrics.rs:186-192;
  * the reference itself has no top-k step).  Rows with fewer than k tiles are
  * padded with index 0xFFFFFFFF and score -inf; out_count[j] (may be NULL) is
- * the number of valid entries.  tiles must be device memory; segments,
+ * the number of valid entries.  k is 1..4096 (SLHA_ERR_DIMENSION beyond).
+ * tiles must be device memory; segments,
  * queries and outputs are host or device.  Outputs in page-locked host memory
  * that the GPU can address (cudaHostAlloc, mapped cudaHostRegister) are written
  * in place by the kernel that produces them, other host outputs through a

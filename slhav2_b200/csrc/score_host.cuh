@@ -806,7 +806,9 @@ Status score_topk_device(Ctx* c, const SciRustSlhaTile* tiles, const uint8_t* st
                          const uint64_t* d_q_sign, size_t nq, uint32_t k, uint32_t* d_out_index,
                          float* d_out_score, uint32_t* d_out_count, bool prefer_generic, int codec_hint) {
     if (nq == 0) return Status();
-    if (k == 0 || k > 8192) return Status(SLHA_ERR_DIMENSION, "top-k: k must be in 1..8192");
+    // (4096 winners per row is what the generic kernel's block-wide selection state holds in shared memory beside its
+    // tile ring; the plan builder checks the exact figure)
+    if (k == 0 || k > 4096) return Status(SLHA_ERR_DIMENSION, "top-k: k must be in 1..4096");
     Plan* p = nullptr;
     SLHA_TRY(build_plan(c, tiles, segs, n_segs, nq, k, codec_hint, /*allow_wide=*/state == nullptr, &p));
     const int nwarps = p->threads / 32;

@@ -91,7 +91,8 @@ def test_topk_merge_of_shard_lists():
     assert np.array_equal(mi, full[0]) and np.array_equal(ms, full[1])
 
 
-@pytest.mark.parametrize("n_lists,k,skew", [(2, 256, 1.0), (8, 2048, 1.0), (8, 2048, 4.0), (5, 300, 0.0), (3, 64, 1.0)])
+@pytest.mark.parametrize("n_lists,k,skew", [(2, 256, 1.0), (8, 2048, 1.0), (8, 2048, 4.0), (5, 300, 0.0), (3, 64, 1.0), (3, 8192, 1.0), (16, 4096, 2.0),
+                                            (64, 512, 1.0)])
 def test_merge_of_sorted_lists_uses_a_proven_floor_and_gives_the_same_answer(n_lists, k, skew):
     # lists ordered best first, as score_topk writes them: the merge gathers only the keys at or above the smallest
     # ceil(k / n_lists)-th entry.  Even shards, a shard that holds most of the winners (skew: its scores are shifted
@@ -362,3 +363,57 @@ def test_repeated_calls_are_bitwise_identical(codec, n, nq, k):
     m = min(nq, 4)
     full = S.score_tiles(dt, 2 * n, qc[:m], qs[:m], m)
     assert S.score_tiles(dt, 2 * n, qc[:m], qs[:m], m).tobytes() == full.tobytes()
+
+
+def test_largest_k_long_and_short_segments():
+    # k at its maximum (4096): a long segment on the streaming kernel, one shorter than k, one a little longer than k
+    k = 4096
+    lens = [150000, 3000, 4100]
+    tiles = H.random_tiles(sum(lens), 6, seed=611, warm_every=13)
+    qc, qs = H.random_queries(3 * 3, 612)
+    segs, tb = [], 0
+    for i, n in enumerate(lens):
+        segs.append((tb, n, 3 * i, 3, 10 * i))
+        tb += n
+    gi, gs_, gc = S.score_topk(S.to_device(tiles), S.make_segments(segs), qc, qs, 9, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+    with pytest.raises(S.SlhaError) as e:
+        S.score_topk(S.to_device(tiles), S.make_segments(segs), qc, qs, 9, k + 1)
+    assert e.value.code == S.ERR_DIMENSION
+
+
+def test_thousands_of_tiny_segments():
+    # 3000 segments of 0..40 tiles with one or two query rows each (a batch of short sequences)
+    rng = np.random.default_rng(613)
+    lens = rng.integers(0, 41, 3000)
+    nqs = rng.integers(1, 3, 3000)
+    tiles = H.random_tiles(int(lens.sum()), 2, seed=614, warm_every=5)
+    qc, qs = H.random_queries(int(nqs.sum()), 615)
+    segs, tb, qb = [], 0, 0
+    for n, q in zip(lens, nqs):
+        segs.append((tb, int(n), qb, int(q), 0))
+        tb += int(n)
+        qb += int(q)
+    gi, gs_, gc = S.score_topk(S.to_device(tiles), S.make_segments(segs), qc, qs, qb, 16)
+    check_topk(tiles, segs, qc, qs, 16, gi, gs_, gc)
+
+
+@pytest.mark.parametrize("codec", [0, 3, 4, 2])
+def test_hundreds_of_query_rows_on_one_segment(codec):
+    # 250 rows against one KV head (a long prompt chunk): several 64-row groups of the tcgen05 kernel, a ragged last one
+    n, nq, k = 20000, 250, 96
+    tiles = H.random_tiles(n, codec, seed=616 + codec, warm_every=17, nocorr_every=3)
+    qc, qs = H.random_queries(nq, 617)
+    segs = [(0, n, 0, nq, 5)]
+    gi, gs_, gc = S.score_topk(S.to_device(tiles), S.make_segments(segs), qc, qs, nq, k)
+    check_topk(tiles, segs, qc, qs, k, gi, gs_, gc)
+
+
+def test_segments_that_share_tiles():
+    # two query groups over overlapping tile ranges with different index bases (a sliding window beside the full context)
+    n = 60000
+    tiles = H.random_tiles(n, 1, seed=618)
+    qc, qs = H.random_queries(8, 619)
+    segs = [(0, n, 0, 4, 0), (n - 9000, 9000, 4, 4, 1000000), (100, 40000, 0, 0, 0)]
+    gi, gs_, gc = S.score_topk(S.to_device(tiles), S.make_segments(segs), qc, qs, 8, 200)
+    check_topk(tiles, segs[:2], qc, qs, 200, gi, gs_, gc)
