@@ -143,3 +143,26 @@ def test_encode_bit_exact_on_rounding_ties_zeros_and_extreme_magnitudes(codec, d
     for j in range(0, len(keys), 5):
         wc, ws = om.prepare_query(keys[j])
         assert np.array_equal(qs[j], ws) and np.array_equal(qc[j].view(np.uint32), wc.view(np.uint32))
+
+
+@pytest.mark.parametrize("codec", range(6))
+@pytest.mark.parametrize("d,rht", [(160, False), (200, True), (256, False)])
+def test_decode_latent_and_key_for_every_codec(codec, d, rht):
+    # slha_decode_latent / slha_decode_key (slha-c/src/lib.rs:1034-1191) against the oracle's LearnedModel decode, NOCORR
+    # tiles with their plane bytes left in place included; the sums run in another order, hence 1e-5 of the vector's norm.
+    # And the reference's own property: the key decode (latent + residual estimate) is closer to the key than the latent alone.
+    om, gm = _models(d, rht, seed=11)
+    keys = H.gaussian_keys(70 + codec, 40, d, outlier_channels=(3,))
+    tiles = om.encode_batch(keys, codec)
+    if codec in (4, 5):
+        tiles["flags"][::3] |= ora.FLAG_TQ3_NOCORR
+    better = 0
+    for i in range(len(keys)):
+        t = tiles[i:i + 1]
+        wl, wk = om.decode_latent(t), om.decode_key(t)
+        gl, gk = gm.decode_latent(t), gm.decode_key(t)
+        assert np.all(np.abs(gl - wl) <= 1e-5 * (1.0 + np.linalg.norm(wl)))
+        assert np.all(np.abs(gk - wk) <= 1e-5 * (1.0 + np.linalg.norm(wk)))
+        better += np.linalg.norm(keys[i] - gk) < np.linalg.norm(keys[i] - gl)
+    # (with the Hadamard rotation the residual estimate is left out, learned.rs:295-299: both decodes coincide)
+    assert better == (0 if rht else len(keys))
