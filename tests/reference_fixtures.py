@@ -128,3 +128,39 @@ FIXTURES = {
     "tq3": tq3_equivalence_fixture,
     "mix3": mix3_equivalence_fixture,
 }
+
+
+# ---- scirust/tests/properties.rs: randomised tiles and queries from the reference's generator -----------------------
+def rand_q(rng):
+    """properties.rs:21-25"""
+    return rng.gaussian(128)
+
+
+def rand_q_sign(rng):
+    """properties.rs:27-33"""
+    return np.array([rng.next_u64() for _ in range(4)], np.uint64)
+
+
+def rand_int4_tile(rng, warm):
+    """properties.rs:36-58: random latent bytes, group scales 1..255 (odd), scale in [0.01, 2.01), lambda ~ 0.1 N(0,1)."""
+    latent = np.array([rng.next_u64() & 0xFF for _ in range(64)], np.uint8)
+    gs = np.array([(rng.next_u64() & 0xFF) | 1 for _ in range(8)], np.uint8)
+    bitmap = tuple(int(x) for x in rand_q_sign(rng))
+    scale = F(F(rng.next_unit()) * F(2.0) + F(0.01))
+    lam = F(F(rng.next_gaussian()) * F(0.1))
+    sigma = F(rng.next_unit())
+    return ora.make_tile(latent, scale, gs, flags=ora.FLAG_WARM if warm else 0, lam=lam, sigma=sigma, residual=bitmap)
+
+
+def property_triples(seed, n, warm_of, nf4_of=lambda it: False):
+    """n iterations of (tile, q, q_sign) drawn in the order the reference's loops draw them."""
+    rng = ora.Rng(seed)
+    tiles, qc, qs = [], [], []
+    for it in range(n):
+        t = rand_int4_tile(rng, warm_of(it))
+        if nf4_of(it):
+            t["flags"] |= ora.FLAG_NF4
+        tiles.append(t)
+        qc.append(rand_q(rng))
+        qs.append(rand_q_sign(rng))
+    return np.concatenate(tiles), np.stack(qc), np.stack(qs)

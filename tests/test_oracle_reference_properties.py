@@ -160,3 +160,56 @@ def test_hamming_distance_matches_bruteforce():
         a = [rng.next_u64() for _ in range(4)]
         b = [rng.next_u64() for _ in range(4)]
         assert ora.hamming(a, b) == sum(bin(x ^ y).count("1") for x, y in zip(a, b))
+
+
+# ---- scirust/tests/properties.rs, same seeds ---------------------------------------------------------------------
+def test_prop_simd_restatement_equals_scalar():
+    """properties.rs:60-86"""
+    tiles, qc, qs = rf.property_triples(0xF00D, 1000, lambda it: it % 3 == 0)
+    for i in range(1000):
+        s = ora.score_tiles(tiles[i:i + 1], qc[i], qs[i])[0]
+        for which in (1, 2):
+            if which <= ora.simd_level():
+                assert abs(s - ora.score_simd(tiles[i:i + 1], qc[i], qs[i], which)) <= 1e-3 * (1.0 + abs(s)), (i, which)
+
+
+def test_prop_score_is_always_finite():
+    """properties.rs:88-100"""
+    tiles, qc, qs = rf.property_triples(0xBEEF, 3000, lambda it: it % 5 == 0, lambda it: it % 2 == 0)
+    assert all(np.isfinite(ora.score_tiles(tiles[i:i + 1], qc[i], qs[i])[0]) for i in range(3000))
+
+
+def test_prop_warm_equals_coarse_only_and_residual_term_is_bounded():
+    """properties.rs:102-118, :226-240"""
+    for seed in (7, 4):
+        hot, qc, qs = rf.property_triples(seed, 500, lambda it: False)
+        warm, hot0 = hot.copy(), hot.copy()
+        warm["flags"] |= ora.FLAG_WARM
+        hot0["dynamic_lambda"] = 0.0
+        for i in range(500):
+            sh, sw, s0 = (ora.score_tiles(t[i:i + 1], qc[i], qs[i])[0] for t in (hot, warm, hot0))
+            assert abs(sw - s0) <= 1e-4 * (1.0 + abs(sw))
+            assert abs(sh - sw) <= abs(hot["dynamic_lambda"][i]) * 256.0 + 1e-2
+
+
+def test_prop_dequant_error_within_bound():
+    """properties.rs:138-180"""
+    rng = ora.Rng(99)
+    for _ in range(300):
+        v = np.array([F(F(rng.next_gaussian()) * F(F(rng.next_unit()) * F(5.0) + F(0.1))) for _ in range(128)], F)
+        for codec, factor in ((rf.GROUPED, 1.0), (rf.NF4, 0.16)):
+            tile, scale, gs = rf.tile_of(v, codec)
+            eff = np.repeat(F(scale) * (gs.astype(F) / F(255.0)), 16)
+            assert np.all(np.abs(ora.dequant(tile) - v) <= factor * eff + 1e-5)
+
+
+def test_prop_rng_is_deterministic_and_sign_bits_flip_under_negation():
+    """properties.rs:184-224"""
+    a, b = ora.Rng(42), ora.Rng(42)
+    assert all(a.next_u64() == b.next_u64() for _ in range(256))
+    from .helpers import scenario_projection, scenario_sign_bits
+    z = scenario_projection(2)
+    rng = ora.Rng(3)
+    for _ in range(200):
+        v = rng.gaussian(128)
+        assert ora.hamming(scenario_sign_bits(z, v), scenario_sign_bits(z, -v)) == 256
