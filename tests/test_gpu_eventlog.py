@@ -194,3 +194,33 @@ def test_no_event_log_leaves_behavior_and_rehydrate_inert():
     pool.enforce_budget()
     assert pool.event_log_stats()["log_errors"] == 0
     assert pool.rehydrate(0) is None
+
+
+def test_legacy_version_one_log_stays_readable_and_appendable(tmp_path):
+    # scirust/src/eventlog.rs:753-786: a version-1 file (no record checksums) is accepted, and what is appended to it
+    # stays in version-1 form (checksum field zero), so the reference's reader accepts the whole file
+    path = tmp_path / "legacy_v1"
+    tiles = H.random_tiles(3, 1, seed=12)
+    path.write_bytes(ora.eventlog_bytes([(1, 4, tiles[0:1])], version=1))
+    pool = S.TilePool(8, 2 ** 62)
+    pool.attach_event_log(path, mode=2)
+    assert pool.event_log_stats()["records"] == 1
+    slot = int(pool.insert(tiles[1:2])[0])
+    assert pool.evict(slot)
+    pool.destroy()
+    data = path.read_bytes()
+    version, recs = ora.eventlog_parse(data)
+    assert version == 1 and len(recs) == 2 and data[16 + 144 + 12:16 + 144 + 16] == bytes(4)
+    assert recs[1][2].tobytes() == tiles[1:2].tobytes()
+
+
+def test_rehydrate_takes_the_latest_record_of_a_sequence_number(tmp_path):
+    # eventlog.rs:592-609 (fetch_by_seq returns the newest record of a seq) through slha_b200_pool_rehydrate
+    path = tmp_path / "fetch"
+    tiles = H.random_tiles(3, 2, seed=13)
+    path.write_bytes(ora.eventlog_bytes([(100, 0, tiles[0:1]), (100, 0, tiles[1:2]), (200, 1, tiles[2:3])]))
+    pool = S.TilePool(8, 2 ** 62)
+    pool.attach_event_log(path, mode=2)
+    slot = pool.rehydrate(100)
+    assert slot is not None and pool.read(slot, 1)[0].tobytes() == tiles[1:2].tobytes()
+    assert pool.rehydrate(999) is None
