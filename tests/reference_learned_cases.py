@@ -180,7 +180,67 @@ def encode_decode_round_trip_and_key_decode(make):
     assert snr(key[0], model.decode_key(tile)) > snr(key[0], model.decode_latent(tile))
 
 
+def scenario_scores_match_equation_2_3_and_warm_drops_the_binary_term(make):
+    """scirust/tests/slha.rs:48-91"""
+    from .helpers import scenario_generate, scenario_projection, scenario_sign_bits, scenario_tile
+    model = make(np.zeros((128, 128), F), 128, 3, False)  # (only its scorer is used)
+    z = scenario_projection(3)
+    q, toks = scenario_generate(4, 1, 0.4)
+    tile = scenario_tile(z, toks[0], 0)
+    q_sign = scenario_sign_bits(z, q)
+    k = ora.dequant(tile)
+    coarse = F(0.0)
+    for d in range(128):
+        coarse = F(coarse + F(q[d] * k[d]))
+    manual = coarse + tile["dynamic_lambda"][0] * F(256.0 - 2.0 * ora.hamming(q_sign, tile["residual_bitmap"][0]))
+    assert abs(model.score(tile, q, q_sign)[0] - manual) < 1e-4
+    z = scenario_projection(2)
+    q, toks = scenario_generate(2, 1, 0.5)
+    q_sign = scenario_sign_bits(z, q)
+    hot = scenario_tile(z, toks[0], 0)
+    warm, hot0 = hot.copy(), hot.copy()
+    warm["flags"] |= ora.FLAG_WARM
+    hot0["dynamic_lambda"] = 0.0
+    s_hot, s_warm, s_hot0 = (model.score(t, q, q_sign)[0] for t in (hot, warm, hot0))
+    assert abs(s_warm - s_hot0) < 1e-5 and abs(s_hot - s_warm) > 0.0
+
+
+def sign_lsh_residual_tracks_cosine(make):
+    """scirust/tests/slha.rs:93-133; a model of d = 128 with seed s draws the same sign matrix as Projection::new(s)"""
+    model = make(np.zeros((128, 128), F), 128, 11, False)
+    rng = ora.Rng(99)
+    q = rng.gaussian(128)
+    q = (q / F(np.sqrt(np.sum(q * q, dtype=F)))).astype(F)
+    q_sign = model.prepare(q)[1]
+    est, cos = [], []
+    for _ in range(400):
+        e = rng.gaussian(128)
+        align = F(F(F(rng.next_unit()) * F(2.0) - F(1.0)) * F(np.sqrt(F(128.0))))
+        e = (e + align * q).astype(F)
+        est.append(256.0 - 2.0 * ora.hamming(q_sign, model.prepare(e)[1]))
+        cos.append(float(q.astype(np.float64) @ e.astype(np.float64) / np.sqrt(e.astype(np.float64) @ e.astype(np.float64))))
+    assert spearman(est, cos) > 0.85
+
+
+def hot_ranks_at_least_as_well_as_warm(make):
+    """scirust/tests/slha.rs:135-161"""
+    from .helpers import scenario_generate, scenario_projection, scenario_sign_bits, scenario_tile
+    model = make(np.zeros((128, 128), F), 128, 5, False)
+    z = scenario_projection(5)
+    q, toks = scenario_generate(123, 256, 0.4)
+    q_sign = scenario_sign_bits(z, q)
+    hot = np.concatenate([scenario_tile(z, t, i) for i, t in enumerate(toks)])
+    warm = hot.copy()
+    warm["flags"] |= ora.FLAG_WARM
+    s_true = [float((kc + e).astype(np.float64) @ q.astype(np.float64)) for kc, e in toks]
+    sp_hot, sp_warm = spearman(model.score(hot, q, q_sign), s_true), spearman(model.score(warm, q, q_sign), s_true)
+    assert sp_hot > 0.8 and sp_hot + 0.02 >= sp_warm, (sp_hot, sp_warm)
+
+
 CASES = [
+    scenario_scores_match_equation_2_3_and_warm_drops_the_binary_term,
+    sign_lsh_residual_tracks_cosine,
+    hot_ranks_at_least_as_well_as_warm,
     pca_captures_dominant_subspace_and_hot_beats_warm,
     grouped_int4_does_not_hurt_end_to_end,
     attention_output_is_high_fidelity_and_hot_ge_warm,
