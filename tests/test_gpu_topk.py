@@ -417,3 +417,47 @@ def test_segments_that_share_tiles():
     segs = [(0, n, 0, 4, 0), (n - 9000, 9000, 4, 4, 1000000), (100, 40000, 0, 0, 0)]
     gi, gs_, gc = S.score_topk(S.to_device(tiles), S.make_segments(segs), qc, qs, 8, 200)
     check_topk(tiles, segs[:2], qc, qs, 200, gi, gs_, gc)
+
+
+def test_concurrent_callers_on_their_own_threads_get_their_own_results():
+    # Four host threads (the ggml worker pool of the llama.cpp shim calls from several threads, slha_llama.cpp:1387-1503),
+    # each with its own tiles, queries and codec, call encode / score + top-k / full scores at the same time; every
+    # thread must get what it gets when it runs alone.
+    import threading
+
+    jobs = []
+    for t, codec in enumerate([6, 2, 4, 3]):
+        n = 40000 + 1000 * t
+        tiles = H.random_tiles(n, codec, seed=900 + t, warm_every=7, nocorr_every=3)
+        qc, qs = H.random_queries(4, 910 + t)
+        jobs.append((tiles, qc, qs, n, 100 + 50 * t))
+    _, p = H.make_model_pair(160, seed=5)
+    model = S.Model.from_projection(p, 160, 5)  # one model shared by all threads
+    keys = H.gaussian_keys(920, 500, 160)
+
+    def run(job):
+        tiles, qc, qs, n, k = job
+        dt = S.to_device(tiles)
+        a = S.score_topk(dt, S.make_segments([(0, n, 0, 4, 0)]), qc, qs, 4, k)
+        b = S.score_tiles(dt, n, qc, qs, 4)
+        c = model.encode_keys(keys, S.CODEC_MIXED)
+        return [x.copy() for x in a] + [b, c]
+
+    alone = [run(j) for j in jobs]
+    results, errors = [None] * len(jobs), []
+
+    def worker(i):
+        try:
+            for _ in range(5):
+                results[i] = run(jobs[i])
+                for x, y in zip(results[i], alone[i]):
+                    assert x.tobytes() == y.tobytes()
+        except BaseException as e:  # surfaced in the main thread below
+            errors.append((i, repr(e)))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(len(jobs))]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
