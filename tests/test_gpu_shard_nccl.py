@@ -57,6 +57,18 @@ for _ in range(7):
 st = sh.status()
 assert st["exchange"] in ("peer-memory loads", "nccl all-gather") and not st["wait_ran_out"] and st["steps"] == 10, st
 np.save(os.path.join(tmp, "out%d.npy" % rank), np.stack([gi.astype(np.float64), gs.astype(np.float64)]))
+# other shapes on the same handle, through both exchanges: shards shorter than k (lists with absent entries at their
+# ends), a context shorter than k (padded result), an uneven split, another codec
+for mode in ("nccl", "peer", "nccl"):
+    sh.set_exchange(mode)
+    for n2, k2 in ((300, 256), (200, 256), (5001, 64)):
+        t2 = H.random_tiles(n2, 3, seed=93 + n2)
+        s2, c2 = shard.shard_range(n2, rank, world)
+        d2 = S.to_device(t2[s2:s2 + c2])
+        for _ in range(3):
+            g = sh.score_topk(d2, S.make_segments([(0, c2, 0, 3, s2)]), qc[:3], qs[:3], 3, k2)
+        check_topk(t2, [(0, n2, 0, 3, 0)], qc[:3], qs[:3], k2, g[0], g[1], np.full(3, min(k2, n2)))
+assert not sh.status()["wait_ran_out"]
 sh.destroy()
 print("rank", rank, "ok", ms, st)
 """
