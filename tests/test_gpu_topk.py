@@ -461,3 +461,26 @@ def test_concurrent_callers_on_their_own_threads_get_their_own_results():
     for th in threads:
         th.join()
     assert not errors, errors
+
+
+def test_a_thousand_launches_alternating_between_call_shapes():
+    # slhav2-vram/tests/cuda.rs:405 (a thousand launches): three call shapes that share the thread's streaming state and
+    # plan cache, interleaved 334 times each; every call must return what its first call returned
+    shapes = []
+    for i, (codec, n, nq, k) in enumerate([(6, 90000, 4, 512), (2, 50000, 7, 1000), (4, 40000, 32, 64)]):
+        tiles = H.random_tiles(n, codec, seed=930 + i, warm_every=9, nocorr_every=4)
+        qc, qs = H.random_queries(nq, 940 + i)
+        # (second segment of each table: no query rows -- a head nobody asks about in this call)
+        shapes.append((S.to_device(tiles), S.make_segments([(0, n // 2, 0, nq, 0), (n // 2, n - n // 2, 0, 0, 5)]), qc, qs, nq, k))
+    first = [None] * len(shapes)
+    for it in range(1002):
+        j = it % len(shapes)
+        dt, segs, qc, qs, nq, k = shapes[j]
+        got = S.score_topk(dt, segs, qc, qs, nq, k)
+        if first[j] is None:
+            first[j] = [x.copy() for x in got]
+        else:
+            for a, b in zip(first[j], got):
+                assert a.tobytes() == b.tobytes(), (it, j)
+    st = S.last_score_stats()
+    assert st["rows_handed_to_generic_kernel"] == 0
