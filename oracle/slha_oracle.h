@@ -9,8 +9,13 @@
  *
  * Pinning: the reference's CPU code is Rust and no Rust toolchain exists on the
  * build machine, so the oracle is pinned by the reference's own known-answer
- * tests and fixtures (tests/test_oracle_kats.py, tests/test_oracle_ccos.py).
- * Its scoring functions are in addition checked against the reference's real
+ * tests and fixtures (tests/test_oracle_kats.py, tests/test_oracle_ccos.py) and by
+ * the reference's unit, property and end-to-end tests rebuilt from its own
+ * seeds on its restated PRNG (tests/test_oracle_reference_properties.py,
+ * tests/test_oracle_ccos_reference_suite.py,
+ * tests/test_oracle_learned_reference_suite.py).  The reference holds no golden
+ * tile bytes: the encode path is pinned at the level of those tests'
+ * thresholds, not byte for byte.  Its scoring functions are in addition checked against the reference's real
  * CUDA kernel (slhav2-vram/kernels/slha_score.cu, compiled from the reference
  * tree into oracle/_ref/ by `make ref`) in tests/test_gpu_reference_kernel.py.
  *
